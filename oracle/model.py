@@ -1,0 +1,227 @@
+"""TEST INFRASTRUCTURE - not a product path.
+
+The dense decoder block composed from the oracle's functions, in the two arithmetic modes the reference has:
+
+``CpuTier``   f32 activations over bf16 weights, 16-lane GEMV (btb/engine/host.py:98-134 -> native/src/gemv.rs),
+              Hugging Face's Qwen3 block in f32. This is the mode the reference's receipts were banked in
+              (tests/integration/test_receipts.py), so it is what pins the oracle to the reference.
+``CardPath``  bf16 activations, the card graph's kernel sequence (btb/engine/cuda.py:1722-1834): add_rmsnorm ->
+              qkv GEMV -> norm_rope_kv -> attention -> o GEMV -> add_rmsnorm -> gate/up GEMV -> SwiGLU-folded down
+              GEMV ... final add_rmsnorm -> head GEMV -> bf16 logits -> lowest-index argmax. This is what the CUDA
+              engine is compared with.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import oracle as O
+
+
+@dataclass
+class DenseCfg:
+    hidden: int
+    layers: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    inter: int
+    vocab: int
+    theta: float = 1e6
+    eps: float = 1e-6
+    qk_norm: bool = True
+
+
+def rope_tables_f32(cfg: DenseCfg, n: int) -> tuple[np.ndarray, np.ndarray]:
+    """cos/sin [n, D] in f32 as Hugging Face's default rotary makes them: inv_freq = theta^(-2i/D) in f32, the angle
+    pos * inv_freq in f32, the halves concatenated"""
+    D = cfg.head_dim
+    inv = (1.0 / (np.float32(cfg.theta) ** (np.arange(0, D, 2, dtype=np.float32) / np.float32(D)))).astype(np.float32)
+    ang = (np.arange(n, dtype=np.float32)[:, None] * inv[None, :]).astype(np.float32)
+    emb = np.concatenate([ang, ang], axis=-1)
+    return np.cos(emb).astype(np.float32), np.sin(emb).astype(np.float32)
+
+
+def rope_tables_bf16(cfg: DenseCfg, n: int) -> tuple[np.ndarray, np.ndarray]:
+    """the card's tables: the f32 tables rounded to bf16 (btb/engine/cuda.py:1166-1182), as bit patterns"""
+    c, s = rope_tables_f32(cfg, n)
+    return O.f32_to_bits(c), O.f32_to_bits(s)
+
+
+class Weights:
+    """one model's tensors as bf16 bit patterns, by Hugging Face names"""
+
+    def __init__(self, cfg: DenseCfg, tensors: dict[str, np.ndarray]):
+        self.cfg = cfg
+        self.t = tensors
+
+    def layer(self, i: int, name: str) -> np.ndarray:
+        return self.t[f"model.layers.{i}.{name}.weight"]
+
+    def merged_qkv(self, i: int) -> np.ndarray:
+        return np.concatenate(
+            [self.layer(i, "self_attn.q_proj"), self.layer(i, "self_attn.k_proj"), self.layer(i, "self_attn.v_proj")]
+        )
+
+    def merged_gu(self, i: int) -> np.ndarray:
+        return np.concatenate([self.layer(i, "mlp.gate_proj"), self.layer(i, "mlp.up_proj")])
+
+    @property
+    def embed(self) -> np.ndarray:
+        return self.t["model.embed_tokens.weight"]
+
+    @property
+    def final_norm(self) -> np.ndarray:
+        return self.t["model.norm.weight"]
+
+
+# --------------------------------------------------------------------------------------------------------------
+# the CPU tier (f32 activations)
+# --------------------------------------------------------------------------------------------------------------
+
+
+class CpuTier:
+    def __init__(self, w: Weights, cap: int = 512, gemv=None):
+        self.w, self.cfg = w, w.cfg
+        c = self.cfg
+        self.cos, self.sin = rope_tables_f32(c, cap)
+        self.K = np.zeros((c.layers, c.kv_heads, cap, c.head_dim), np.float32)
+        self.V = np.zeros_like(self.K)
+        self.n = 0
+        self.gemv = gemv or (lambda wt, x: O.cpu_gemv_bf16(wt, x))
+
+    @staticmethod
+    def _rms(x: np.ndarray, w_bits: np.ndarray, eps: float) -> np.ndarray:
+        x = x.astype(np.float32)
+        var = np.mean(x * x, axis=-1, keepdims=True, dtype=np.float32)
+        return (O.bits_to_f32(w_bits) * (x * (1.0 / np.sqrt(var + np.float32(eps))).astype(np.float32))).astype(
+            np.float32
+        )
+
+    def forward(self, ids, positions=None, parents=None) -> np.ndarray:
+        """T rows after the cache's n rows; row t at positions[t], seeing the cache and its ancestors (parents, -1
+        the root; a chain by default). Rows are written to cache slots n + t. Returns logits [T, V] f32."""
+        c = self.cfg
+        T = len(ids)
+        n0 = self.n
+        positions = list(range(n0, n0 + T)) if positions is None else list(positions)
+        parents = list(range(-1, T - 1)) if parents is None else list(parents)
+        G = c.q_heads // c.kv_heads
+        D = c.head_dim
+        h = O.bits_to_f32(self.w.embed[np.asarray(ids)]).copy()
+        # visibility of pass rows: row t sees pass row u iff u is t or an ancestor of t
+        vis = np.zeros((T, T), bool)
+        for t in range(T):
+            p = t
+            while p >= 0:
+                vis[t, p] = True
+                p = parents[p]
+        for i in range(c.layers):
+            x = self._rms(h, self.w.layer(i, "input_layernorm"), c.eps)
+            q = self.gemv(self.w.layer(i, "self_attn.q_proj"), x).reshape(T, c.q_heads, D)
+            k = self.gemv(self.w.layer(i, "self_attn.k_proj"), x).reshape(T, c.kv_heads, D)
+            v = self.gemv(self.w.layer(i, "self_attn.v_proj"), x).reshape(T, c.kv_heads, D)
+            if c.qk_norm:
+                q = self._rms(q, self.w.layer(i, "self_attn.q_norm"), c.eps)
+                k = self._rms(k, self.w.layer(i, "self_attn.k_norm"), c.eps)
+            cos, sin = self.cos[positions][:, None, :], self.sin[positions][:, None, :]
+
+            def rot(a):
+                return np.concatenate([-a[..., D // 2 :], a[..., : D // 2]], axis=-1)
+
+            q = (q * cos + rot(q) * sin).astype(np.float32)
+            k = (k * cos + rot(k) * sin).astype(np.float32)
+            self.K[i, :, n0 : n0 + T] = k.transpose(1, 0, 2)
+            self.V[i, :, n0 : n0 + T] = v.transpose(1, 0, 2)
+            att = np.zeros((T, c.q_heads, D), np.float32)
+            scale = np.float32(D**-0.5)
+            for t in range(T):
+                keep = np.concatenate([np.ones(n0, bool), vis[t]])
+                for hq in range(c.q_heads):
+                    g = hq // G
+                    kk = self.K[i, g, : n0 + T][keep]
+                    vv = self.V[i, g, : n0 + T][keep]
+                    s = (kk @ q[t, hq]).astype(np.float32) * scale
+                    p = np.exp(s - s.max()).astype(np.float32)
+                    att[t, hq] = (p @ vv) / p.sum(dtype=np.float32)
+            y = self.gemv(self.w.layer(i, "self_attn.o_proj"), att.reshape(T, -1))
+            h = (h + y).astype(np.float32)
+            x = self._rms(h, self.w.layer(i, "post_attention_layernorm"), c.eps)
+            gt = self.gemv(self.w.layer(i, "mlp.gate_proj"), x)
+            up = self.gemv(self.w.layer(i, "mlp.up_proj"), x)
+            act = (gt / (1.0 + np.exp(-gt, dtype=np.float32))).astype(np.float32)
+            y = self.gemv(self.w.layer(i, "mlp.down_proj"), (act * up).astype(np.float32))
+            h = (h + y).astype(np.float32)
+        self.n = n0 + T
+        x = self._rms(h, self.w.final_norm, c.eps)
+        return self.gemv(self.w.embed, x)
+
+    def keep_path(self, base: int, path) -> None:
+        """the accepted branch's rows gathered to the cache's front (btb/engine/cuda.py:3563-3575)"""
+        for j, node in enumerate(path):
+            self.K[:, :, base + j] = self.K[:, :, base + node].copy()
+            self.V[:, :, base + j] = self.V[:, :, base + node].copy()
+        self.n = base + len(path)
+
+
+# --------------------------------------------------------------------------------------------------------------
+# the card path (bf16 activations, the card graph's kernel order)
+# --------------------------------------------------------------------------------------------------------------
+
+
+class CardPath:
+    """KV position-major [cap, Hk, D] (hs = D, rs = Hk * D), btb/engine/arena.py:1-5"""
+
+    def __init__(self, w: Weights, cap: int = 512, silu_fold: bool = True):
+        self.w, self.cfg = w, w.cfg
+        c = self.cfg
+        self.cap = cap
+        self.cos, self.sin = rope_tables_bf16(c, cap)
+        self.K = np.zeros((c.layers, cap, c.kv_heads, c.head_dim), np.uint16)
+        self.V = np.zeros_like(self.K)
+        self.n = 0
+        self.qkv = [w.merged_qkv(i) for i in range(c.layers)]
+        self.gu = [w.merged_gu(i) for i in range(c.layers)]
+        self.silu_fold = silu_fold
+
+    def forward(self, ids, depth=None, parents=None) -> np.ndarray:
+        """one pass of T rows; returns the bf16 logits' bit patterns [T, V]"""
+        c = self.cfg
+        T = len(ids)
+        n0 = self.n
+        depth = np.arange(T, dtype=np.int32) if depth is None else np.asarray(depth, np.int32)
+        par = np.arange(-1, T - 1, dtype=np.int32) if parents is None else np.asarray(parents, np.int32)
+        D, Hq, Hk = c.head_dim, c.q_heads, c.kv_heads
+        hs, rs = D, Hk * D
+        h = self.w.embed[np.asarray(ids)].copy()
+        y_prev = None
+        for i in range(c.layers):
+            h, x = O.add_rmsnorm(h, y_prev, self.w.layer(i, "input_layernorm"), c.eps)
+            qkv = O.gemv_card_bf16(self.qkv[i], x)
+            wq = self.w.layer(i, "self_attn.q_norm") if c.qk_norm else None
+            wk = self.w.layer(i, "self_attn.k_norm") if c.qk_norm else None
+            q = O.norm_rope_kv(qkv, wq, wk, c.eps, self.cos, self.sin, n0, depth, self.K[i], self.V[i], Hq, Hk, D, hs, rs)
+            att = O.attn_decode(q, self.K[i], self.V[i], n0, par, Hq, Hk, D, hs, rs, float(D**-0.5))
+            y = O.gemv_card_bf16(self.w.layer(i, "self_attn.o_proj"), att)
+            h, x = O.add_rmsnorm(h, y, self.w.layer(i, "post_attention_layernorm"), c.eps)
+            gu = O.gemv_card_bf16(self.gu[i], x)
+            if self.silu_fold:
+                y_prev = O.gemv_card_silu_bf16(self.w.layer(i, "mlp.down_proj"), gu)
+            else:
+                y_prev = O.gemv_card_bf16(self.w.layer(i, "mlp.down_proj"), O.silu_mul(gu))
+        h, x = O.add_rmsnorm(h, y_prev, self.w.final_norm, c.eps)
+        self.n = n0 + T
+        return O.gemv_card_bf16(self.w.embed, x)
+
+    def greedy(self, prompt, n_new: int) -> list[int]:
+        """prefill as chain passes of up to 32 rows through the step's own arithmetic, then one row a step"""
+        lg = None
+        for a in range(0, len(prompt), 32):
+            lg = self.forward(prompt[a : a + 32])
+        toks = [int(O.argmax_bf16(lg[-1:])[0])]
+        while len(toks) < n_new:
+            lg = self.forward([toks[-1]])
+            toks.append(int(O.argmax_bf16(lg)[0]))
+        return toks
