@@ -1,0 +1,369 @@
+"""Decode benchmark of the B200 hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload qwen3-4b-bf16|qwen3-4b-p12]
+
+A step is one greedy decode step (one token) at batch 1 of the Qwen3-4B-shaped model with seeded random bf16 weights
+(N(0, 0.02), norm weights 1) after a 128-token uniform-random prompt: the configuration the metric is quoted on.
+Rank 0 prints ONE JSON line. `value` is tokens/s with everything resident on the card (CUDA events around K replays of
+the captured step graph, max over ranks); `e2e` is the same through the public one-token call with the token crossing
+the bus both ways every step; `roofline` is the GEMV kernel's achieved weight-streaming rate (CUDA events around one
+token's worth of GEMV launches over the model's real weights, 8 GB >> L2) against the measured HBM copy peak;
+`cpu_baseline` is the CPU tier's arithmetic (oracle port of btb's 16-lane AVX-512 GEMV, all host cores) on the same
+model. With --impl reference the CPU tier is the thing timed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "bf16 decode tok/s @bs1 (Qwen3-4B shape)"
+PROMPT = 128
+
+
+def measured_hbm_peak() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class Clocks:
+    """samples nvidia-smi while the timed region runs"""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")  # fmt: skip
+
+    def __init__(self, index: int):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].startswith("Active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}  # fmt: skip
+
+
+# ---- the CPU tier (oracle port of btb's CPU path) -------------------------------------------------------------------
+
+
+def cpu_tier_step_fn(cfg, host_w):
+    """one decode step on the host: f32 activations over bf16 weights, 16-lane GEMV on every core (the arithmetic of
+    btb's CPU tier, btb/engine/host.py:98-134 -> native/src/gemv.rs), a numpy attention over an f32 cache"""
+    import numpy as np
+
+    from oracle import oracle as O
+
+    H, D, Hq, Hk = cfg.hidden, cfg.head_dim, cfg.q_heads, cfg.kv_heads
+    cap = 512
+    K = np.zeros((cfg.layers, Hk, cap, D), np.float32)
+    V = np.zeros_like(K)
+    inv = (1.0 / (np.float32(cfg.theta) ** (np.arange(0, D, 2, dtype=np.float32) / np.float32(D)))).astype(np.float32)
+    state = {"n": PROMPT}
+
+    def rms(x, eps):
+        return x * (1.0 / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + np.float32(eps)))
+
+    def step(tok: int) -> int:
+        n = state["n"]
+        h = O.bits_to_f32(host_w["embed"][tok : tok + 1])
+        ang = np.float32(n) * inv
+        cos, sin = np.cos(np.concatenate([ang, ang])), np.sin(np.concatenate([ang, ang]))
+        rot = lambda a: np.concatenate([-a[..., D // 2 :], a[..., : D // 2]], -1)  # noqa: E731
+        for i in range(cfg.layers):
+            L = host_w["layers"][i]
+            x = rms(h, cfg.eps).astype(np.float32)
+            qkv = O.cpu_gemv_bf16(L["qkv"], x)[0]
+            q = rms(qkv[: Hq * D].reshape(Hq, D), cfg.eps)
+            k = rms(qkv[Hq * D : (Hq + Hk) * D].reshape(Hk, D), cfg.eps)
+            v = qkv[(Hq + Hk) * D :].reshape(Hk, D)
+            q, k = q * cos + rot(q) * sin, k * cos + rot(k) * sin
+            K[i, :, n], V[i, :, n] = k, v
+            G = Hq // Hk
+            s = np.einsum("gud,gnd->gun", q.reshape(Hk, G, D), K[i, :, : n + 1]) * np.float32(D**-0.5)
+            p = np.exp(s - s.max(-1, keepdims=True))
+            att = np.einsum("gun,gnd->gud", p / p.sum(-1, keepdims=True), V[i, :, : n + 1]).reshape(1, Hq * D)
+            h = h + O.cpu_gemv_bf16(L["o"], att.astype(np.float32))
+            x = rms(h, cfg.eps).astype(np.float32)
+            gu = O.cpu_gemv_bf16(L["gu"], x)[0]
+            g, u = gu[: cfg.inter], gu[cfg.inter :]
+            m = (g / (1.0 + np.exp(-g)) * u).astype(np.float32)[None]
+            h = h + O.cpu_gemv_bf16(L["down"], m)
+        x = rms(h, cfg.eps).astype(np.float32)
+        logits = O.cpu_gemv_bf16(host_w["embed"], x)[0]
+        state["n"] = n + 1
+        return int(np.argmax(logits))
+
+    return step
+
+
+def host_weights_from_engine(mw):
+    import numpy as np
+    import torch
+
+    def b(t):
+        return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    return {"embed": b(mw.embed),
+            "layers": [{"qkv": b(L.qkv), "o": b(L.o), "gu": b(L.gu), "down": b(L.down)} for L in mw.layers]}  # fmt: skip
+
+
+def host_weights_synth(cfg, seed=0):
+    """the same shapes and distribution drawn on the host (the reference arm needs no card)"""
+    import numpy as np
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+
+    def lin(r, c):
+        t = torch.empty(r, c, dtype=torch.bfloat16)
+        t.normal_(0.0, 0.02, generator=g)
+        return t.view(torch.int16).numpy().view(np.uint16)
+
+    H, D = cfg.hidden, cfg.head_dim
+    out = {"embed": lin(cfg.vocab, H), "layers": []}
+    for _ in range(cfg.layers):
+        out["layers"].append({"qkv": lin(cfg.qkv_rows, H), "o": lin(H, cfg.q_heads * D), "gu": lin(2 * cfg.inter, H),
+                              "down": lin(H, cfg.inter)})  # fmt: skip
+    return out
+
+
+def time_cpu_tier(cfg, host_w, steps: int, warmup: int = 1) -> tuple[float, int]:
+    from oracle import oracle as O
+
+    O.build()
+    step = cpu_tier_step_fn(cfg, host_w)
+    tok = 1
+    for _ in range(warmup):
+        tok = step(tok)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = step(tok)
+    dt = time.perf_counter() - t0
+    return steps / dt, os.cpu_count() or 1
+
+
+# ---- arms ---------------------------------------------------------------------------------------------------------------
+
+
+def run_reference(args, rank: int) -> None:
+    from btb_b200.engine import QWEN3_4B as cfg
+
+    if rank != 0:
+        return
+    hw = host_weights_synth(cfg)
+    steps = max(1, min(args.steps, 64))
+    tps, cores = time_cpu_tier(cfg, hw, steps, warmup=min(args.warmup, 2))
+    from oracle import oracle as O
+
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 2), "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 activations over bf16 weights", "data": "synthetic",
+        "config": {"workload": "qwen3-4b-shape bf16, batch 1, greedy decode after a 128-token prompt (CPU tier)"},
+        "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "port",
+                         "sample": f"{steps} full decode steps, isa {O.isa()}"},
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args, rank: int, world: int, local_rank: int) -> None:
+    import torch
+
+    from btb_b200 import capi
+    from btb_b200 import engine as E
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: PLC0415
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    cfg = E.QWEN3_4B
+    storage = "p12" if args.workload.endswith("p12") else "bf16"
+    if args.pdl is not None:
+        capi.set_tuning(pdl=args.pdl)
+    K, W = args.steps, max(args.warmup, 3)
+    cap = ((PROMPT + 2 * (K + W) + 64 + 511) // 512) * 512
+    mw = E.synth_weights(cfg, seed=0, storage=storage)
+    eng = E.CardEngine(mw, cap=cap)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (PROMPT,), generator=g)
+    eng.reset()
+    last = eng.prefill(prompt)
+    first = int(last.float().argmax(-1))
+    eng.bufs(1)["ids"][0] = first
+    graph = eng.step_graph(args.graph_steps, publish=True)
+    reps = lambda n: -(-n // args.graph_steps)  # noqa: E731
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(reps(W)):
+        graph.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with Clocks(local_rank) as clk:
+        e0.record()
+        for _ in range(reps(K)):
+            graph.replay()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    steps_done = reps(K) * args.graph_steps
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    assert capi.status() == 0, "a kernel recorded a device-side refusal"
+    tps = world * steps_done / (ms / 1000.0)
+
+    # e2e: the public one-token call, the token crossing the bus both ways every step
+    tok = int(eng.pin_tok[0])
+    for _ in range(3):
+        tok = eng.step(tok)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        tok = eng.step(tok)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t[0])
+    e2e = world * K / e2e_s
+
+    # roofline: one token's GEMV launches over the model's own weights, nothing else on the stream
+    g1 = eng.bufs(1)
+    s = capi.stream_ptr()
+
+    def gemvs():
+        H, D, I = cfg.hidden, cfg.head_dim, cfg.inter
+        for L in mw.layers:
+            eng._matvec(L.qkv, g1["x"], g1["qkv"], 1, cfg.qkv_rows, H, s)
+            eng._matvec(L.o, g1["att"], g1["y"], 1, H, cfg.q_heads * D, s)
+            eng._matvec(L.gu, g1["x"], g1["gu"], 1, 2 * I, H, s)
+            eng._matvec(L.down, g1["m"], g1["y"], 1, H, I, s)
+        eng._matvec(mw.embed, g1["x"], g1["logits"], 1, cfg.vocab, H, s)
+
+    n_gemv = 4 * cfg.layers + 1
+    for _ in range(3):
+        gemvs()
+    torch.cuda.synchronize()
+    e0.record()
+    ROUNDS = 5
+    for _ in range(ROUNDS):
+        gemvs()
+    e1.record()
+    torch.cuda.synchronize()
+    gemv_ms = e0.elapsed_time(e1) / ROUNDS
+    wbytes = eng.weight_bytes()
+    # algorithmic bytes of one token's GEMVs: the weights as stored, plus each launch's x and y vectors
+    H_, A_, I_ = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.inter
+    abytes = wbytes + cfg.layers * 2 * (3 * H_ + cfg.qkv_rows + A_ + 3 * I_ + H_) + 2 * (H_ + cfg.vocab)
+    peak, which = measured_hbm_peak()
+    achieved = abytes / (gemv_ms / 1000.0) / 1e9
+    roof = {"bound": "hbm", "kernel": "gemv_stream (all of a token's GEMVs)", "achieved": achieved, "peak": peak,
+            "unit": "GB/s", "frac": achieved / peak, "peak_source": which, "frac_of_8tbs": achieved / 8000.0,
+            "launches": n_gemv, "avg_launch_us": gemv_ms * 1000.0 / n_gemv, "traffic": TRAFFIC.get(storage)}  # fmt: skip
+
+    line = {
+        "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": world, "steps": steps_done, "warmup": W,
+        "ms_per_step": ms / steps_done, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if storage == "bf16" else "bf16 (pack12 weights widened in registers)", "data": "synthetic",
+        "config": {"workload": f"qwen3-4b-shape {storage}, batch 1, greedy decode after a 128-token prompt",
+                   "parallelism": "replicas only" if world > 1 else "1 gpu", "graph_steps": args.graph_steps,
+                   "l2": "weights per step 8.0 GB > L2 126 MB (inputs larger than L2)", "pdl": args.pdl,
+                   "bytes_per_token": cfg.weight_bytes_per_token(storage)},
+        "clocks": clk.summary(),
+        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
+        "gpu_launches": eng.launches_per_step * steps_done,
+        "roofline": roof,
+        "token_roofline_frac": (cfg.weight_bytes_per_token(storage) * tps / world / 1e9) / peak,
+    }  # fmt: skip
+    if rank == 0 and world == 1 and not args.no_cpu:
+        hw = host_weights_from_engine(mw) if storage == "bf16" else host_weights_synth(cfg)
+        from oracle import oracle as O
+
+        ctps, cores = time_cpu_tier(cfg, hw, steps=args.cpu_steps, warmup=1)
+        line["cpu_baseline"] = {"value": ctps, "unit": "tok/s", "cores": cores, "kind": "port",
+                                "sample": f"{args.cpu_steps} full decode steps of the same model, isa {O.isa()}"}  # fmt: skip
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# per-launch DRAM traffic of the dominant kernel from the committed ncu summary (profiles/), filled once captured
+TRAFFIC: dict[str, float | None] = {"bf16": None, "p12": None}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="qwen3-4b-bf16", choices=["qwen3-4b-bf16", "qwen3-4b-p12"])
+    ap.add_argument("--graph-steps", type=int, default=1)
+    ap.add_argument("--pdl", type=int, default=None)
+    ap.add_argument("--cpu-steps", type=int, default=4)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_b200(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

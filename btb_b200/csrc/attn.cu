@@ -1,0 +1,304 @@
+// Paged GQA decode attention for sm_100a: a step's row, or a verify pass's chain or tree of T <= 32 rows, over a
+// position-major bf16 cache [rows, Hk, D] read through an optional row map (64-row pages).
+//
+// The fold structure is the reference's (native/cuda/btb_attn_flash.cuh:7-14 of btb): a row's keys [first, last] are
+// cut at fixed boundaries into tiles of 64 keys and groups of 8 tiles; a TILE's state (max, sum, output) is computed
+// from nothing - scores scaled to log2 units, 2^(s - max) weights, the weights rounded to bf16 before they multiply V;
+// a GROUP's state is its tiles' folded in tile order, the ROW's its groups' folded in group order, the output O / L
+// in bf16. No tile waits on another and nothing depends on how many rows share the launch, so a verify pass's row is
+// the step's row. The dot products here are f32 FMA chains in index order on the SIMT cores (decode attention is bound
+// by the cache's bytes, not by math), so results agree with the reference's tensor-core tiles to rounding, not to
+// the bit; the tests hold them to 2^-6 of the row's largest output like the reference's own attention test.
+//
+// Launch: block (grp, g, t) takes group grp of kv head g for token t's G query heads; warp w takes tile w of the
+// group (a lane two keys for the scores, D/32 dims for the output). Groups past the row's keys return at once, so
+// one captured launch serves every length up to the capacity. A row reaching several groups stores each group's
+// state and the last block to arrive folds them in group order - no block ever waits for another.
+#include "common.cuh"
+#include "btb_b200_internal.h"
+
+B2_DEFINE_STATUS(attn)
+
+namespace {
+
+constexpr int BN = 64;        // keys a tile
+constexpr int GT = 8;         // tiles a group: one a warp
+constexpr int GK = BN * GT;   // keys a group
+constexpr int TMAX = 32;      // rows a pass at most
+constexpr int GMAX = 8;       // query heads a kv head at most
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// a state (m, l) folded into the running (M, L): each side scaled to the larger max, the larger side's factor
+// exactly 1; an empty side (max -inf) contributes nothing. Returns the factors for the outputs' fold.
+__device__ __forceinline__ void fold_ml(float& M, float& L, float m, float l, float& cO, float& co) {
+    const bool em = m == NEG_INF, eM = M == NEG_INF;
+    const float hi = fmaxf(M, m), lo = fminf(M, m);
+    const float e = ex2(em || eM ? 0.f : __fsub_rn(lo, hi));
+    cO = em ? 1.f : eM ? 0.f : (M >= m ? 1.f : e);
+    co = em ? 0.f : eM ? 1.f : (M > m ? e : 1.f);
+    L = __fmaf_rn(l, co, __fmul_rn(L, cO));
+    M = hi;
+}
+__device__ __forceinline__ float fold_e(float O, float o, float cO, float co) {
+    return __fmaf_rn(o, co, __fmul_rn(O, cO));
+}
+
+struct AttnArgs {
+    const bf16* q;    // [T, Hq, D]
+    const bf16* K;    // head g, slot j at g * hs + j * rs
+    const bf16* V;
+    bf16* out;        // [T, Hq * D]
+    const int* n0p;   // rows standing before the pass
+    const int* par;   // [T] parents, -1 the root
+    const int* tbl;   // logical slot -> cache row, or null
+    const float* sinks;  // [Hq] a logit joined to the denominator, or null
+    float* part_m;    // [S, T, Hq]
+    float* part_l;
+    float* part_acc;  // [S, T, Hq, D]
+    int* cnt;         // [T, Hk] arrivals, zero between launches
+    float scale;
+    int T, Hq, Hk, win, cap;
+    long long hs, rs;
+};
+
+template <int D>
+__global__ void __launch_bounds__(GT * 32) attn_decode(const AttnArgs A) {
+    constexpr int E = D / 32;  // dims a lane owns of an output row
+    pdl_launch_dependents();
+    pdl_wait();
+    const int grp = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Hq = A.Hq, Hk = A.Hk, T = A.T, G = Hq / Hk;
+    const int n0 = *A.n0p;
+
+    __shared__ int anc[TMAX];  // token t's path, root first
+    __shared__ int s_len;
+    __shared__ float tm[GT][GMAX], tl[GT][GMAX];
+    __shared__ int s_last_block;
+    // dynamic: the token's G queries, each warp's tile weights (bf16-rounded) and the tiles' outputs
+    extern __shared__ __align__(16) float dsm[];
+    float(*qs)[D] = reinterpret_cast<float(*)[D]>(dsm);                             // [G][D]
+    float(*ps)[BN] = reinterpret_cast<float(*)[BN]>(dsm + G * D);                   // [GT * G][BN]
+    float(*to)[D] = reinterpret_cast<float(*)[D]>(dsm + G * D + GT * G * BN);       // [GT * G][D]
+
+    if (threadIdx.x == 0) {
+        int len = 0;
+        for (int p = t; p >= 0 && p < T && len < TMAX; p = A.par[p]) ++len;
+        int k = len;
+        for (int p = t; k > 0; p = A.par[p]) anc[--k] = p;
+        s_len = len;
+    }
+    __syncthreads();
+    const int last = n0 + s_len - 1;
+    const int first = A.win > 0 ? max(last + 1 - A.win, 0) : 0;
+    const int lo = grp * GK, hi = lo + GK - 1;
+    if (lo > last || hi < first || last >= A.cap) {
+        if (last >= A.cap && threadIdx.x == 0 && grp == 0) b2_fail(B2_ERR_DOMAIN);
+        return;  // the group holds none of the row's keys: nothing stored, nothing counted
+    }
+    for (int i = threadIdx.x; i < G * D; i += GT * 32) {
+        const int hh = i / D, d = i - hh * D;
+        qs[hh][d] = bf2f(A.q[((size_t)t * Hq + g * G + hh) * D + d]);
+    }
+    __syncthreads();
+
+    const float scale2 = __fmul_rn(A.scale, LOG2E);
+    const bf16* Kg = A.K + (size_t)g * A.hs;
+    const bf16* Vg = A.V + (size_t)g * A.hs;
+    // ---- this warp's tile, a state from nothing ----------------------------------------------------------------
+    const int j0 = lo + warp * BN;
+    const bool tile_live = !(j0 > last || j0 + BN - 1 < first);
+    if (tile_live) {
+        int row[2];
+        float s[2][GMAX];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int j = j0 + k * 32 + lane;
+            row[k] = -1;
+            if (j >= first && j <= last) {
+                int sl = j < n0 ? j : n0 + anc[j - n0];
+                if (A.tbl != nullptr) sl = A.tbl[sl];
+                row[k] = sl;
+            }
+#pragma unroll
+            for (int hh = 0; hh < GMAX; ++hh) s[k][hh] = 0.f;
+            if (row[k] >= 0) {
+                const uint4* kr = reinterpret_cast<const uint4*>(Kg + (size_t)row[k] * A.rs);
+#pragma unroll 4
+                for (int c = 0; c < D / 8; ++c) {
+                    const uint4 kv = __ldg(kr + c);
+                    const float kf[8] = {bf_lo(kv.x), bf_hi(kv.x), bf_lo(kv.y), bf_hi(kv.y),
+                                         bf_lo(kv.z), bf_hi(kv.z), bf_lo(kv.w), bf_hi(kv.w)};
+#pragma unroll
+                    for (int hh = 0; hh < GMAX; ++hh) {
+                        if (hh < G) {
+                            float a = s[k][hh];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) a = fmaf(kf[e], qs[hh][c * 8 + e], a);
+                            s[k][hh] = a;
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < GMAX; ++hh) {
+            if (hh < G) {
+                float s0 = row[0] >= 0 ? __fmul_rn(s[0][hh], scale2) : NEG_INF;
+                float s1 = row[1] >= 0 ? __fmul_rn(s[1][hh], scale2) : NEG_INF;
+                float m = fmaxf(s0, s1);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                const float p0 = (m == NEG_INF || row[0] < 0) ? 0.f : ex2(__fsub_rn(s0, m));
+                const float p1 = (m == NEG_INF || row[1] < 0) ? 0.f : ex2(__fsub_rn(s1, m));
+                float l = __fadd_rn(p0, p1);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, o));
+                ps[warp * G + hh][lane] = bfround(p0);
+                ps[warp * G + hh][32 + lane] = bfround(p1);
+                if (lane == 0) {
+                    tm[warp][hh] = m;
+                    tl[warp][hh] = l;
+                }
+            }
+        }
+        __syncwarp();
+        // P . V: the lane's E dims of every head's output, the tile's keys in order
+        float o[GMAX][E];
+#pragma unroll
+        for (int hh = 0; hh < GMAX; ++hh)
+#pragma unroll
+            for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
+        for (int k = 0; k < 2; ++k) {
+            for (int i = 0; i < 32; ++i) {
+                const int rk = __shfl_sync(0xffffffffu, row[k], i);
+                if (rk < 0) continue;  // warp-uniform
+                float vf[E];
+                const bf16* vr = Vg + (size_t)rk * A.rs + lane * E;
+                if (E == 4) {
+                    const uint2 vv = __ldg(reinterpret_cast<const uint2*>(vr));
+                    vf[0] = bf_lo(vv.x), vf[1] = bf_hi(vv.x), vf[2] = bf_lo(vv.y), vf[3] = bf_hi(vv.y);
+                } else if (E == 2) {
+                    const uint32_t vv = __ldg(reinterpret_cast<const uint32_t*>(vr));
+                    vf[0] = bf_lo(vv), vf[1] = bf_hi(vv);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < E; ++e) vf[e] = bf2f(vr[e]);
+                }
+#pragma unroll
+                for (int hh = 0; hh < GMAX; ++hh) {
+                    if (hh < G) {
+                        const float p = ps[warp * G + hh][k * 32 + i];
+#pragma unroll
+                        for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[e], o[hh][e]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < GMAX; ++hh)
+            if (hh < G)
+#pragma unroll
+                for (int e = 0; e < E; ++e) to[warp * G + hh][lane * E + e] = o[hh][e];
+    } else if (lane < GMAX) {
+        tm[warp][lane] = NEG_INF;
+        tl[warp][lane] = 0.f;
+    }
+    __syncthreads();
+
+    // ---- the group's state: the tiles folded in tile order, a thread a run of (head, dim) elements -------------
+    const int s_first = first / GK, s_last = last / GK;
+    const bool single = s_first == s_last;
+    for (int i = threadIdx.x; i < G * D; i += GT * 32) {
+        const int hh = i / D, d = i - hh * D;
+        float M = NEG_INF, L = 0.f, O = 0.f;
+        for (int w = 0; w < GT; ++w) {
+            const float m = tm[w][hh];
+            if (m == NEG_INF) continue;  // an empty tile changes nothing
+            float cO, co;
+            fold_ml(M, L, m, tl[w][hh], cO, co);
+            O = fold_e(O, to[w * G + hh][d], cO, co);
+        }
+        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        if (single) {
+            if (A.sinks != nullptr) {
+                float cO, co;
+                fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+                O = __fmul_rn(O, cO);
+            }
+            A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+        } else {
+            const size_t idx = (size_t)grp * T * Hq + rowi;
+            if (d == 0) {
+                A.part_m[idx] = M;
+                A.part_l[idx] = L;
+            }
+            A.part_acc[idx * D + d] = O;
+        }
+    }
+    if (single) return;
+    // ---- several groups: count this block in; the last one folds the row's groups in group order ----------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last_block = atomicAdd(A.cnt + (size_t)t * Hk + g, 1) == s_last - s_first ? 1 : 0;
+    __syncthreads();
+    if (!s_last_block) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < G * D; i += GT * 32) {
+        const int hh = i / D, d = i - hh * D;
+        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        float M = NEG_INF, L = 0.f, O = 0.f;
+        for (int sp = s_first; sp <= s_last; ++sp) {
+            const size_t iu = (size_t)sp * T * Hq + rowi;
+            float cO, co;
+            fold_ml(M, L, __ldcg(A.part_m + iu), __ldcg(A.part_l + iu), cO, co);
+            O = fold_e(O, __ldcg(A.part_acc + iu * D + d), cO, co);
+        }
+        if (A.sinks != nullptr) {
+            float cO, co;
+            fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+            O = __fmul_rn(O, cO);
+        }
+        A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+    }
+    if (threadIdx.x == 0) A.cnt[(size_t)t * Hk + g] = 0;
+}
+
+}  // namespace
+
+extern "C" size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D) {
+    return (size_t)S * T * Hq * (D + 2);
+}
+
+extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V, void* out, const void* n0p,
+                                    const void* par, int T, int Hq, int Hk, int D, long long hs, long long rs,
+                                    float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
+                                    const void* tbl, const void* sinks, int cap, void* stream) {
+    if (!q || !K || !V || !out || !n0p || !par || !part_m || !part_l || !part_acc || !cnt) return B2_ERR_NULL;
+    if (T <= 0 || T > TMAX || Hk <= 0 || Hq <= 0 || Hq % Hk || Hq / Hk > GMAX || cap <= 0 || !(scale == scale))
+        return B2_ERR_DOMAIN;
+    AttnArgs a{};
+    a.q = static_cast<const bf16*>(q), a.K = static_cast<const bf16*>(K), a.V = static_cast<const bf16*>(V);
+    a.out = static_cast<bf16*>(out), a.n0p = static_cast<const int*>(n0p), a.par = static_cast<const int*>(par);
+    a.tbl = static_cast<const int*>(tbl), a.sinks = static_cast<const float*>(sinks);
+    a.part_m = static_cast<float*>(part_m), a.part_l = static_cast<float*>(part_l);
+    a.part_acc = static_cast<float*>(part_acc), a.cnt = static_cast<int*>(cnt);
+    a.scale = scale, a.T = T, a.Hq = Hq, a.Hk = Hk, a.win = win, a.cap = cap, a.hs = hs, a.rs = rs;
+    const int S = (cap + GK - 1) / GK;
+    const dim3 grid(S, Hk, T);
+    const int G = Hq / Hk;
+    const size_t smem = sizeof(float) * ((size_t)G * D + (size_t)GT * G * BN + (size_t)GT * G * D);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    static bool allowed[2][64];
+    const void* kern = D == 64 ? (const void*)attn_decode<64> : D == 128 ? (const void*)attn_decode<128> : nullptr;
+    if (kern == nullptr) return B2_ERR_DOMAIN;
+    int rc = b2_allow_smem(kern, allowed[D == 128]);
+    if (rc) return rc;
+    return b2_launch(kern, grid, dim3(GT * 32), smem, s, a);
+}

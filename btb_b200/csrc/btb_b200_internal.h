@@ -1,0 +1,60 @@
+// Host-side plumbing shared by the kernels' translation units: tunables, the device's SM count, and the one launch
+// path (cudaLaunchKernelEx with the programmatic-dependent-launch attribute when it is switched on).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "common.cuh"
+
+struct B2Tuning {
+    int ring_bytes;   // shared memory a GEMV CTA spends on its warps' rings
+    int seg_bytes;    // a ring stage holds at most this many weight bytes of a row
+    int x_smem_max;   // x is staged in shared memory when M * C * 2 is at most this
+    int ctas_per_sm;  // GEMV CTAs an SM (the grid is persistent)
+    int evict_first;  // weight copies carry an L2 evict-first hint
+    int pdl;          // launch with programmatic stream serialization
+};
+B2Tuning& b2_tuning();
+int b2_sm_count();
+
+// one launch: `args` is the kernel's single by-value parameter struct
+template <typename Args>
+static inline int b2_launch(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            const Args& args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    if (b2_tuning().pdl) {
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+    }
+    void* params[1] = {const_cast<Args*>(&args)};
+    const cudaError_t e = cudaLaunchKernelExC(&cfg, kern, params);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return B2_ERR_CUDA;
+    }
+    return B2_OK;
+}
+
+// opt a kernel in to large dynamic shared memory once a device
+static inline int b2_allow_smem(const void* kern, bool* done_for_device) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
+    if (!done_for_device[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return B2_ERR_CUDA;
+        }
+        done_for_device[dev] = true;
+    }
+    return B2_OK;
+}

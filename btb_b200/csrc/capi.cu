@@ -1,0 +1,65 @@
+// Library-wide entry points: version, device facts, tunables, the device status word.
+#include <stdlib.h>
+
+#include "btb_b200_internal.h"
+#include "../../include/btb_b200.h"
+
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return (v != nullptr && *v != '\0') ? atoi(v) : dflt;
+}
+
+B2Tuning& b2_tuning() {
+    static B2Tuning t = {
+        env_int("BTB_B200_RING_BYTES", 96 * 1024), env_int("BTB_B200_SEG_BYTES", 4096),
+        env_int("BTB_B200_X_SMEM_MAX", 64 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
+        env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 0),
+    };
+    return t;
+}
+
+int b2_sm_count() {
+    static int sms[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (sms[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev] = n;
+    }
+    return sms[dev];
+}
+
+extern "C" int btb_b200_version(void) { return 1; }
+
+extern "C" int btb_b200_sm_count(void) { return b2_sm_count(); }
+
+extern "C" int btb_b200_set_tuning(const char* key, int value) {
+    if (key == nullptr) return B2_ERR_NULL;
+    B2Tuning& t = b2_tuning();
+    if (!strcmp(key, "ring_bytes")) t.ring_bytes = value;
+    else if (!strcmp(key, "seg_bytes")) t.seg_bytes = value;
+    else if (!strcmp(key, "x_smem_max")) t.x_smem_max = value;
+    else if (!strcmp(key, "ctas_per_sm")) t.ctas_per_sm = value;
+    else if (!strcmp(key, "evict_first")) t.evict_first = value;
+    else if (!strcmp(key, "pdl")) t.pdl = value;
+    else return B2_ERR_DOMAIN;
+    return B2_OK;
+}
+
+int b2_status_take_gemv(int*);
+int b2_status_take_layer(int*);
+int b2_status_take_attn(int*);
+
+extern "C" int btb_b200_status(int* code) {
+    if (code == nullptr) return B2_ERR_NULL;
+    int (*const take[])(int*) = {b2_status_take_gemv, b2_status_take_layer, b2_status_take_attn};
+    *code = 0;
+    for (auto f : take) {
+        int v = 0;
+        const int rc = f(&v);
+        if (rc) return rc;
+        if (v != 0 && *code == 0) *code = v;
+    }
+    return B2_OK;
+}

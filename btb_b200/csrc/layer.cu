@@ -1,0 +1,323 @@
+// The step's small kernels: embedding gather, residual + RMSNorm, q/k norm + RoPE + cache write, SwiGLU product,
+// greedy pick, the token's handoff to pinned host memory. Each is the arithmetic of the reference's kernel of the same
+// name (native/cuda/btb_kernels.cu of btb, lines cited per kernel): same per-element operations, same reduction
+// trees, so the bits are the reference's; what changes is that every kernel waits on the grid dependency itself
+// (programmatic dependent launch) and nothing traps.
+#include "common.cuh"
+#include "btb_b200_internal.h"
+
+B2_DEFINE_STATUS(layer)
+
+namespace {
+
+// ---- embedding gather: h[t, :] = table[ids[t], :] (btb/engine/cuda.py:2227-2232) -----------------------------------
+struct EmbedArgs {
+    const bf16* table;
+    const long long* ids;
+    bf16* h;
+    int T, H, V;
+};
+__global__ void __launch_bounds__(256) embed_rows(const EmbedArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    long long id = A.ids[t];
+    if (id < 0 || id >= A.V) {  // never read outside the table: record and clamp
+        if (threadIdx.x == 0) b2_fail(B2_ERR_DOMAIN);
+        id = 0;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(A.table + (size_t)id * A.H);
+    uint4* dst = reinterpret_cast<uint4*>(A.h + (size_t)t * A.H);
+    for (int i = threadIdx.x; i < A.H / 8; i += 256) dst[i] = __ldg(src + i);
+}
+
+// ---- residual + RMSNorm (btb_kernels.cu:365-393) -------------------------------------------------------------------
+// thread i of 256 sums the squares of elements i, i + 256, .. in order, then the fixed 256 -> 1 tree.
+struct NormArgs {
+    bf16* h;
+    const bf16* y;
+    const bf16* w;
+    bf16* x;
+    float eps;
+    int H, centered;
+};
+__global__ void __launch_bounds__(256) add_rmsnorm(const NormArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, tid = threadIdx.x, H = A.H;
+    bf16* hr = A.h + (size_t)t * H;
+    const bf16* yr = A.y == nullptr ? nullptr : A.y + (size_t)t * H;
+    bf16* xr = A.x + (size_t)t * H;
+    float ss = 0.f;
+    for (int i = tid; i < H; i += 256) {
+        float hv = bf2f(hr[i]);
+        if (yr != nullptr) {
+            hv = bfround(hv + bf2f(yr[i]));
+            hr[i] = f2bf(hv);
+        }
+        ss = fmaf(hv, hv, ss);
+    }
+    __shared__ float red[256];
+    red[tid] = ss;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (tid < s) red[tid] += red[tid + s];
+        __syncthreads();
+    }
+    const float rstd = rsqrtf(red[0] / (float)H + A.eps);
+    for (int i = tid; i < H; i += 256) {
+        const float wv = bf2f(A.w[i]);
+        xr[i] = f2bf(bf2f(hr[i]) * rstd * (A.centered ? 1.f + wv : wv));
+    }
+}
+
+// ---- act(g) * up over a [T, 2I] block (btb_kernels.cu:470-480) -----------------------------------------------------
+struct ActArgs {
+    const bf16* gu;
+    bf16* m;
+    int T, I;
+};
+__global__ void __launch_bounds__(256) silu_mul(const ActArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t n = (size_t)A.T * A.I;
+    for (size_t k = (size_t)blockIdx.x * 256 + threadIdx.x; k < n; k += (size_t)gridDim.x * 256) {
+        const size_t t = k / A.I, i = k - t * A.I;
+        const float g = bf2f(A.gu[t * (2 * (size_t)A.I) + i]);
+        const float u = bf2f(A.gu[t * (2 * (size_t)A.I) + A.I + i]);
+        const float s = bfround(g / (1.f + expf(-g)));
+        A.m[k] = f2bf(s * u);
+    }
+}
+
+// ---- q/k RMSNorm + RoPE + cache write (btb_kernels.cu:261-327) -----------------------------------------------------
+// One warp per (head, row): lane l holds dims l*E .. l*E+E-1, so rotate_half's partner is lane ^ 16.
+struct RopeArgs {
+    const bf16* qkv;
+    const bf16* wq;
+    const bf16* wk;
+    const bf16* cos_t;
+    const bf16* sin_t;
+    const int* n0p;
+    const int* depth;
+    const int* tbl;
+    bf16* K;
+    bf16* V;
+    bf16* qo;
+    float eps;
+    int T, Hq, Hk, centered;
+    long long hs, rs;
+    int cap;  // cache rows: a slot at or past it is refused
+};
+template <int D>
+__global__ void __launch_bounds__(32) norm_rope_kv(const RopeArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int E = D / 32;
+    const int head = blockIdx.x, t = blockIdx.y, lane = threadIdx.x;
+    const int n0 = *A.n0p;
+    int slot = n0 + t;
+    const int pos = n0 + A.depth[t];
+    if (slot < 0 || slot >= A.cap || pos < 0 || pos >= A.cap) {
+        if (lane == 0) b2_fail(B2_ERR_DOMAIN);
+        return;
+    }
+    if (A.tbl != nullptr) slot = A.tbl[slot];
+    const int Hq = A.Hq, Hk = A.Hk;
+    const int width = (Hq + 2 * Hk) * D;
+    const bf16* src = A.qkv + (size_t)t * width + (size_t)head * D + lane * E;
+    if (head >= Hq + Hk) {
+        bf16* dst = A.V + (size_t)(head - Hq - Hk) * A.hs + (size_t)slot * A.rs + lane * E;
+#pragma unroll
+        for (int e = 0; e < E; ++e) dst[e] = src[e];
+        return;
+    }
+    const bool is_q = head < Hq;
+    const bf16* wn = is_q ? A.wq : A.wk;
+    float v[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) v[e] = bf2f(src[e]);
+    if (wn != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) ss = fmaf(v[e], v[e], ss);
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / (float)D + A.eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float wv = bf2f(wn[lane * E + e]);
+            v[e] = bfround(v[e] * rstd * (A.centered ? 1.f + wv : wv));
+        }
+    }
+    const bf16* cp = A.cos_t + (size_t)pos * D + lane * E;
+    const bf16* sp = A.sin_t + (size_t)pos * D + lane * E;
+    const float sgn = lane < 16 ? -1.f : 1.f;
+    bf16* dst = is_q ? (A.qo + ((size_t)t * Hq + head) * D + lane * E)
+                     : (A.K + (size_t)(head - Hq) * A.hs + (size_t)slot * A.rs + lane * E);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const float rot = __shfl_xor_sync(0xffffffffu, v[e], 16);
+        const float qc = bfround(v[e] * bf2f(cp[e]));
+        dst[e] = f2bf(fmaf(sgn * rot, bf2f(sp[e]), qc));
+    }
+}
+
+// ---- greedy pick: lowest-index argmax over a bf16 logits row (btb/engine/cuda.py:2237; ties as
+// native/src/sample.rs:57-67) --------------------------------------------------------------------------------------
+// Every block folds its slice into one 64-bit key - the value's ordered bits above the complemented index - and
+// atomicMax'es it into the row's slot of `scratch`; the last block to arrive writes the token and clears the slot
+// and the counter for the next launch. scratch: T u64 keys then T u32 counters, zero before the first launch.
+struct ArgmaxArgs {
+    const bf16* logits;
+    unsigned long long* keys;
+    unsigned int* counts;
+    long long* out;
+    int V;
+};
+__device__ __forceinline__ unsigned long long pick_key(float v, int idx) {
+    const unsigned b = __float_as_uint(v);
+    const unsigned u = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (unsigned)idx);
+}
+__global__ void __launch_bounds__(256) argmax_rows(const ArgmaxArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const bf16* row = A.logits + (size_t)t * A.V;
+    unsigned long long best = 0ull;
+    const int nvec = A.V >> 3;
+    for (int c = blockIdx.x * 256 + threadIdx.x; c < nvec; c += gridDim.x * 256) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(row) + c);
+        const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const unsigned long long a = pick_key(bf_lo(wds[k]), c * 8 + 2 * k);
+            const unsigned long long b = pick_key(bf_hi(wds[k]), c * 8 + 2 * k + 1);
+            best = best > a ? best : a;
+            best = best > b ? best : b;
+        }
+    }
+    if (blockIdx.x == 0)  // a vocabulary that is not a multiple of 8: the tail, element by element
+        for (int i = nvec * 8 + threadIdx.x; i < A.V; i += 256) {
+            const unsigned long long a = pick_key(bf2f(row[i]), i);
+            best = best > a ? best : a;
+        }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = best > other ? best : other;
+    }
+    __shared__ unsigned long long wbest[8];
+    __shared__ int last;
+    if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) best = best > wbest[w] ? best : wbest[w];
+        atomicMax(A.keys + t, best);
+        __threadfence();
+        last = atomicAdd(A.counts + t, 1u) == gridDim.x - 1;
+        if (last) {
+            __threadfence();
+            const unsigned long long k = atomicExch(A.keys + t, 0ull);
+            A.out[t] = (long long)(0xffffffffu - (unsigned)(k & 0xffffffffull));
+            A.counts[t] = 0u;
+        }
+    }
+}
+
+// ---- the step's handoff (btb_kernels.cu:455-465): token and device clock, a system fence, then the length -------
+struct PublishArgs {
+    int* n0;
+    const long long* ids;
+    long long* out_tok;
+    int* out_n0;
+    long long* out_ts;
+    int advance;  // n0 += advance before it is published (the graph advances itself)
+};
+__global__ void publish_step(const PublishArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const int n = *A.n0 + A.advance;
+        *A.n0 = n;
+        if (A.out_tok != nullptr) {
+            *A.out_tok = *A.ids;
+            unsigned long long ts;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ts));
+            *A.out_ts = (long long)ts;
+            __threadfence_system();
+            *A.out_n0 = n;
+        }
+    }
+}
+
+}  // namespace
+
+// ---- C-ABI ------------------------------------------------------------------------------------------------------------
+
+extern "C" int btb_b200_embed(const void* table, const void* ids, void* h, int T, int H, int V, void* stream) {
+    if (!table || !ids || !h) return B2_ERR_NULL;
+    if (T <= 0 || H <= 0 || (H & 7) || V <= 0) return B2_ERR_DOMAIN;
+    EmbedArgs a{static_cast<const bf16*>(table), static_cast<const long long*>(ids), static_cast<bf16*>(h), T, H, V};
+    return b2_launch((const void*)embed_rows, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" int btb_b200_add_rmsnorm(void* h, const void* y, const void* w, float eps, void* x, int T, int H,
+                                    int centered, void* stream) {
+    if (!h || !w || !x) return B2_ERR_NULL;
+    if (T <= 0 || H <= 0 || !(eps == eps)) return B2_ERR_DOMAIN;
+    NormArgs a{static_cast<bf16*>(h), static_cast<const bf16*>(y), static_cast<const bf16*>(w), static_cast<bf16*>(x),
+               eps, H, centered};
+    return b2_launch((const void*)add_rmsnorm, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" int btb_b200_silu_mul(const void* gu, void* m, int T, int I, void* stream) {
+    if (!gu || !m) return B2_ERR_NULL;
+    if (T <= 0 || I <= 0) return B2_ERR_DOMAIN;
+    ActArgs a{static_cast<const bf16*>(gu), static_cast<bf16*>(m), T, I};
+    const long long n = (long long)T * I;
+    const int grid = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    return b2_launch((const void*)silu_mul, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                     const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
+                                     int T, int Hq, int Hk, int D, long long hs, long long rs, int centered,
+                                     const void* tbl, int cap, void* stream) {
+    if (!qkv || !cos_t || !sin_t || !n0p || !depth || !K || !V || !q) return B2_ERR_NULL;
+    if (T <= 0 || Hq <= 0 || Hk <= 0 || cap <= 0) return B2_ERR_DOMAIN;
+    RopeArgs a{static_cast<const bf16*>(qkv), static_cast<const bf16*>(wq), static_cast<const bf16*>(wk),
+               static_cast<const bf16*>(cos_t), static_cast<const bf16*>(sin_t), static_cast<const int*>(n0p),
+               static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),
+               static_cast<bf16*>(V), static_cast<bf16*>(q), eps, T, Hq, Hk, centered, hs, rs, cap};
+    const dim3 grid(Hq + 2 * Hk, T);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (D) {
+        case 64: return b2_launch((const void*)norm_rope_kv<64>, grid, dim3(32), 0, s, a);
+        case 128: return b2_launch((const void*)norm_rope_kv<128>, grid, dim3(32), 0, s, a);
+        case 256: return b2_launch((const void*)norm_rope_kv<256>, grid, dim3(32), 0, s, a);
+        default: return B2_ERR_DOMAIN;
+    }
+}
+
+extern "C" int btb_b200_argmax_bf16(const void* logits, int T, int V, void* scratch, void* out, void* stream) {
+    if (!logits || !scratch || !out) return B2_ERR_NULL;
+    if (T <= 0 || V <= 0 || (reinterpret_cast<uintptr_t>(scratch) & 7)) return B2_ERR_DOMAIN;
+    ArgmaxArgs a{static_cast<const bf16*>(logits), static_cast<unsigned long long*>(scratch),
+                 reinterpret_cast<unsigned int*>(static_cast<unsigned long long*>(scratch) + T),
+                 static_cast<long long*>(out), V};
+    int blocks = (V / 8 + 255) / 256;
+    blocks = blocks < 1 ? 1 : (blocks > 148 ? 148 : blocks);
+    return b2_launch((const void*)argmax_rows, dim3(blocks, T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" size_t btb_b200_argmax_scratch_bytes(int T) { return (size_t)T * 12 + 4; }
+
+extern "C" int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance,
+                                void* stream) {
+    if (!n0) return B2_ERR_NULL;
+    if (out_tok != nullptr && (!ids || !out_n0 || !out_ts)) return B2_ERR_NULL;
+    PublishArgs a{static_cast<int*>(n0), static_cast<const long long*>(ids), static_cast<long long*>(out_tok),
+                  static_cast<int*>(out_n0), static_cast<long long*>(out_ts), advance};
+    return b2_launch((const void*)publish_step, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), a);
+}

@@ -1,0 +1,373 @@
+"""The card decode engine: the per-layer kernel sequence of btb's card graph, on the B200 library.
+
+What this mirrors (all under btb/engine/cuda.py of btb): the load-time layout ``_card_weights``/``_card_merged``
+(q, k, v merged into one row block, gate and up merged, cuda.py:1044-1164), the rope tables ``_card_tables``
+(cuda.py:1166-1182), the static pass buffers ``_card_buffers`` (cuda.py:1491-1562), the pass body ``_card_body``
+(cuda.py:1601-1837), the self-advancing step graph ``_card_step_graph`` (cuda.py:2101-2251) and the greedy loop
+``_card_generate_greedy`` (cuda.py:2253-2459). Prefill runs chain passes of up to 32 rows through the same kernels,
+so a prompt's cache rows are the rows the steps would have written.
+
+PyTorch is plumbing here: device memory, streams, graph capture. Every kernel is the library's; a missing library
+raises at construction.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from . import capi
+from .capi import call, ptr
+
+CARD_ROWS = (1, 2, 4, 8, 16, 32)  # a pass's padded widths (btb/kinds.py CARD_ROWS)
+GROUP_KEYS = 512  # keys a split of the attention takes
+
+
+@dataclass
+class DenseConfig:
+    name: str
+    hidden: int
+    layers: int
+    q_heads: int
+    kv_heads: int
+    head_dim: int
+    inter: int
+    vocab: int
+    theta: float = 1e6
+    eps: float = 1e-6
+    qk_norm: bool = True
+
+    @property
+    def qkv_rows(self) -> int:
+        return (self.q_heads + 2 * self.kv_heads) * self.head_dim
+
+    def weight_bytes_per_token(self, storage: str = "bf16") -> int:
+        """algorithmic weight bytes one decoded token reads: every layer's four matrices and the head"""
+        per = self.hidden * (self.qkv_rows + self.q_heads * self.head_dim + 3 * self.inter)
+        head = self.vocab * self.hidden * 2
+        if storage == "bf16":
+            return self.layers * per * 2 + head
+        if storage == "p12":
+            return self.layers * per * 3 // 2 + head  # the head stays bf16 (btb/engine/pack.py:82,105)
+        raise ValueError(storage)
+
+    def kv_bytes_per_row(self) -> int:
+        return self.layers * 2 * self.kv_heads * self.head_dim * 2
+
+
+QWEN3_4B = DenseConfig("qwen3-4b", 2560, 36, 32, 8, 128, 9728, 151936)
+LLAMA31_70B = DenseConfig("llama-3.1-70b", 8192, 80, 64, 8, 128, 28672, 128256, theta=5e5, eps=1e-5, qk_norm=False)
+
+
+def rope_tables(cfg: DenseConfig, cap: int, device: Any) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin [cap, D] bf16 from the default rotary: f32 inv_freq, f32 angles, halves concatenated, rounded once"""
+    D = cfg.head_dim
+    inv = 1.0 / (torch.tensor(cfg.theta, dtype=torch.float32) ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    ang = torch.arange(cap, dtype=torch.float32)[:, None] * inv[None, :]
+    emb = torch.cat([ang, ang], dim=-1)
+    return emb.cos().to(torch.bfloat16).to(device), emb.sin().to(torch.bfloat16).to(device)
+
+
+class P12Matrix:
+    """one pack12 matrix on the card, as stored (btb/pack12.py:48-68) plus the per-row escape cursor"""
+
+    def __init__(self, parts: tuple, rows: int, cols: int, device: Any):
+        lo, hi4, table, esc_idx, esc_val = parts
+        self.rows, self.cols = rows, cols
+        as_t = lambda a, dt: torch.as_tensor(a, dtype=dt).to(device).contiguous()  # noqa: E731
+        self.lo, self.hi4 = as_t(lo, torch.uint8), as_t(hi4, torch.uint8)
+        self.table = bytes(bytearray(int(v) for v in table))  # 16 bytes, host: it travels in the launch's arguments
+        self.n_esc = int(len(esc_idx))
+        self.esc_idx = as_t(esc_idx, torch.int32) if self.n_esc else None
+        self.esc_val = as_t(esc_val, torch.uint8) if self.n_esc else None
+        self.esc_row = None
+        if self.n_esc:
+            self.esc_row = torch.empty(rows + 1, dtype=torch.int32, device=device)
+            call("btb_b200_p12_rows", ptr(self.esc_idx), self.n_esc, rows, cols, ptr(self.esc_row), capi.stream_ptr())
+
+    @property
+    def nbytes(self) -> int:
+        return self.lo.numel() + self.hi4.numel() + 5 * self.n_esc
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    qkv: Any  # torch bf16 [rows, H] or P12Matrix
+    o: Any
+    gu: Any
+    down: Any
+    wq: torch.Tensor | None = None
+    wk: torch.Tensor | None = None
+
+
+@dataclass
+class ModelWeights:
+    cfg: DenseConfig
+    embed: torch.Tensor  # [V, H] bf16, the tied head
+    norm: torch.Tensor
+    layers: list[LayerWeights] = field(default_factory=list)
+
+
+def synth_weights(cfg: DenseConfig, seed: int = 0, device: Any = "cuda", storage: str = "bf16",
+                  on_cpu: bool = False) -> ModelWeights:  # fmt: skip
+    """random-init weights of the config's shapes: linears bf16 N(0, 0.02), norm weights 1.0, in a fixed tensor order
+    (embed; per layer q, k, v, o, gate, up, down). `on_cpu` draws with the CPU generator (small configs whose weights
+    the CPU oracle must share); otherwise on the device. storage "p12" encodes every layer linear with pack12."""
+    from . import pack12
+
+    gdev = "cpu" if on_cpu else device
+    g = torch.Generator(device=gdev).manual_seed(seed)
+
+    def lin(r: int, c: int) -> torch.Tensor:
+        return (torch.randn(r, c, generator=g, device=gdev, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(device)
+
+    def ones(n: int) -> torch.Tensor:
+        return torch.ones(n, dtype=torch.bfloat16, device=device)
+
+    def store(w: torch.Tensor) -> Any:
+        if storage == "bf16":
+            return w
+        return P12Matrix(pack12.pack_bf16(w), w.shape[0], w.shape[1], device)
+
+    H, D = cfg.hidden, cfg.head_dim
+    mw = ModelWeights(cfg, lin(cfg.vocab, H), ones(H))
+    for _ in range(cfg.layers):
+        q, k, v = lin(cfg.q_heads * D, H), lin(cfg.kv_heads * D, H), lin(cfg.kv_heads * D, H)
+        o = lin(H, cfg.q_heads * D)
+        gate, up, down = lin(cfg.inter, H), lin(cfg.inter, H), lin(H, cfg.inter)
+        mw.layers.append(
+            LayerWeights(
+                ones(H), ones(H), store(torch.cat([q, k, v])), store(o), store(torch.cat([gate, up])), store(down),
+                ones(D) if cfg.qk_norm else None, ones(D) if cfg.qk_norm else None,
+            )
+        )  # fmt: skip
+        del q, k, v, gate, up
+    return mw
+
+
+def pad_rows(T: int) -> int:
+    for m in CARD_ROWS:
+        if T <= m:
+            return m
+    raise ValueError(f"a pass holds at most {CARD_ROWS[-1]} rows, got {T}")
+
+
+class CardEngine:
+    """one model on one card: its cache arena, pass buffers, step graph and greedy loop"""
+
+    def __init__(self, weights: ModelWeights, cap: int = 4096, silu_fold: bool = True, device: Any = "cuda"):
+        capi.lib()  # fail here, loudly, when the library is not built
+        if not torch.cuda.is_available():
+            raise RuntimeError("btb_b200 needs a CUDA device: there is no CPU path")
+        self.w, self.cfg = weights, weights.cfg
+        self.dev = torch.device(device)
+        self.cap = int(cap)
+        c = self.cfg
+        self.cos, self.sin = rope_tables(c, self.cap, self.dev)
+        # the arena: per layer K and V position-major [cap, Hk, D] (btb/engine/arena.py:1-5)
+        self.K = torch.zeros(c.layers, self.cap, c.kv_heads, c.head_dim, dtype=torch.bfloat16, device=self.dev)
+        self.V = torch.zeros_like(self.K)
+        self.hs, self.rs = c.head_dim, c.kv_heads * c.head_dim
+        self.S = (self.cap + GROUP_KEYS - 1) // GROUP_KEYS
+        self.n0 = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.silu_fold = silu_fold
+        self._bufs: dict[int, dict[str, torch.Tensor]] = {}
+        self._graphs: dict[Any, Any] = {}
+        self.pin_tok = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self.pin_n0 = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.pin_ts = torch.zeros(1, dtype=torch.int64).pin_memory()
+        self.pin_in = torch.zeros(CARD_ROWS[-1], dtype=torch.int64).pin_memory()
+        self.launches_per_step = 0
+        self._n = 0
+
+    # -- buffers -------------------------------------------------------------------------------------------------
+    def bufs(self, M: int) -> dict[str, torch.Tensor]:
+        """the static buffers of a pass of padded width M (btb/engine/cuda.py:1491-1562)"""
+        if M in self._bufs:
+            return self._bufs[M]
+        c, dev = self.cfg, self.dev
+        bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)  # noqa: E731
+        H, Hq, D = c.hidden, c.q_heads, c.head_dim
+        g = {
+            "h": bf(M, H), "x": bf(M, H), "y": bf(M, H), "qkv": bf(M, c.qkv_rows), "q": bf(M, Hq, D),
+            "att": bf(M, Hq * D), "gu": bf(M, 2 * c.inter), "m": bf(M, c.inter), "logits": bf(M, c.vocab),
+            "ids": torch.zeros(M, dtype=torch.int64, device=dev),
+            "tok": torch.zeros(M, dtype=torch.int64, device=dev),
+            "depth": torch.arange(M, dtype=torch.int32, device=dev),
+            "par": torch.arange(-1, M - 1, dtype=torch.int32, device=dev),
+            "part_m": torch.zeros(self.S * M * Hq, dtype=torch.float32, device=dev),
+            "part_l": torch.zeros(self.S * M * Hq, dtype=torch.float32, device=dev),
+            "part_acc": torch.zeros(self.S * M * Hq * D, dtype=torch.float32, device=dev),
+            "cnt": torch.zeros(M * c.kv_heads, dtype=torch.int32, device=dev),
+            "pick": torch.zeros((int(capi.lib().btb_b200_argmax_scratch_bytes(M)) + 7) // 8, dtype=torch.int64,
+                                device=dev),
+        }  # fmt: skip
+        self._bufs[M] = g
+        return g
+
+    # -- the pass ------------------------------------------------------------------------------------------------
+    def _k(self, name: str, *args: Any) -> None:
+        """one kernel launch through the C-ABI, counted"""
+        call(name, *args)
+        self._n += 1
+
+    def _matvec(self, W: Any, x: torch.Tensor, y: torch.Tensor, M: int, R: int, C_: int, s: int) -> None:
+        if isinstance(W, P12Matrix):
+            self._k("btb_b200_gemv_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),
+                    ptr(W.esc_row), ptr(x), ptr(y), M, R, C_, s)  # fmt: skip
+        else:
+            self._k("btb_b200_gemv_bf16", ptr(W), ptr(x), ptr(y), M, R, C_, s)
+
+    def body(self, T: int, tail: bool = True, stream_ptr: int | None = None) -> None:
+        """the pass's kernels over the width's buffers (btb/engine/cuda.py:1601-1837): T live rows, padded to M"""
+        c = self.cfg
+        M = pad_rows(T)
+        g = self.bufs(M)
+        s = capi.stream_ptr() if stream_ptr is None else stream_ptr
+        H, Hq, Hk, D, I = c.hidden, c.q_heads, c.kv_heads, c.head_dim, c.inter
+        k = self._k
+        y_prev = None
+        for i, L in enumerate(self.w.layers):
+            k("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(g["x"]), T, H, 0, s)
+            self._matvec(L.qkv, g["x"], g["qkv"], M, c.qkv_rows, H, s)
+            k("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
+              ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
+              self.rs, 0, 0, self.cap, s)  # fmt: skip
+            k("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["att"]), ptr(self.n0),
+              ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
+              ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
+            self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
+            k("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
+            self._matvec(L.gu, g["x"], g["gu"], M, 2 * I, H, s)
+            if self.silu_fold and M <= 8 and not isinstance(L.down, P12Matrix):
+                k("btb_b200_gemv_silu_bf16", ptr(L.down), ptr(g["gu"]), ptr(g["y"]), M, H, I, s)
+            else:
+                k("btb_b200_silu_mul", ptr(g["gu"]), ptr(g["m"]), M, I, s)
+                self._matvec(L.down, g["m"], g["y"], M, H, I, s)
+            y_prev = g["y"]
+        if tail:
+            k("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(self.w.norm), c.eps, ptr(g["x"]), T, H, 0, s)
+            self._matvec(self.w.embed, g["x"], g["logits"], M, c.vocab, H, s)
+
+    def _embed(self, g: dict, T: int, s: int) -> None:
+        self._k("btb_b200_embed", ptr(self.w.embed), ptr(g["ids"]), ptr(g["h"]), T, self.cfg.hidden, self.cfg.vocab, s)
+
+    def _pick(self, g: dict, T: int, s: int, out: torch.Tensor) -> None:
+        self._k("btb_b200_argmax_bf16", ptr(g["logits"]), T, self.cfg.vocab, ptr(g["pick"]), ptr(out), s)
+
+    # -- passes --------------------------------------------------------------------------------------------------
+    def reset(self) -> None:
+        self.n0.zero_()
+
+    def forward(self, ids: torch.Tensor, depth: Any = None, parents: Any = None, advance: bool = True) -> torch.Tensor:
+        """one eager pass of T rows after the cache's rows (a chain by default); returns bf16 logits [T, V]"""
+        T = int(ids.numel())
+        M = pad_rows(T)
+        g = self.bufs(M)
+        s = capi.stream_ptr()
+        g["ids"][:T].copy_(ids.to(self.dev, torch.int64))
+        if depth is not None:
+            g["depth"][:T].copy_(torch.as_tensor(depth, dtype=torch.int32))
+            g["par"][:T].copy_(torch.as_tensor(parents, dtype=torch.int32))
+        else:
+            g["depth"][:M].copy_(torch.arange(M, dtype=torch.int32))
+            g["par"][:M].copy_(torch.arange(-1, M - 1, dtype=torch.int32))
+        self._embed(g, T, s)
+        self.body(T)
+        if advance:
+            call("btb_b200_publish", ptr(self.n0), 0, 0, 0, 0, T, s)
+        return g["logits"][:T]
+
+    def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
+        """the prompt through chain passes of up to 32 rows; returns the last row's logits"""
+        lg = None
+        for a in range(0, int(prompt.numel()), CARD_ROWS[-1]):
+            lg = self.forward(prompt[a : a + CARD_ROWS[-1]])
+        assert lg is not None
+        return lg[-1:]
+
+    # -- the step graph ------------------------------------------------------------------------------------------
+    def _step_body(self, s: int, publish: bool) -> None:
+        """embed(ids) -> layers -> head -> greedy pick into ids -> n0 += 1 (and the handoff to pinned memory)"""
+        g = self.bufs(1)
+        self._n = 0
+        self._embed(g, 1, s)
+        self.body(1, stream_ptr=s)
+        self._pick(g, 1, s, g["ids"])
+        if publish:
+            self._k("btb_b200_publish", ptr(self.n0), ptr(g["ids"]), ptr(self.pin_tok), ptr(self.pin_n0),
+                    ptr(self.pin_ts), 1, s)  # fmt: skip
+        else:
+            self._k("btb_b200_publish", ptr(self.n0), 0, 0, 0, 0, 1, s)
+        self.launches_per_step = self._n
+
+    def step_graph(self, steps: int = 1, publish: bool = True) -> Any:
+        """`steps` self-advancing decode steps as one CUDA graph (btb/engine/cuda.py:2101-2251)"""
+        key = ("step", steps, publish)
+        if key in self._graphs:
+            return self._graphs[key]
+        # run once eagerly on a side stream (allocations, shared-memory opt-ins), with the state put back after
+        n_keep, ids_keep = self.n0.clone(), self.bufs(1)["ids"].clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._step_body(capi.stream_ptr(side), publish)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.n0.copy_(n_keep)
+        self.bufs(1)["ids"].copy_(ids_keep)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            s = capi.stream_ptr()
+            for _ in range(steps):
+                self._step_body(s, publish)
+        self.n0.copy_(n_keep)
+        self.bufs(1)["ids"].copy_(ids_keep)
+        self._graphs[key] = graph
+        return graph
+
+    def generate_greedy(self, prompt: Any, max_new: int, graph_steps: int = 1) -> list[int]:
+        """prefill, the first token from the prompt's last logits, then the step graph replayed; tokens come back
+        through pinned host memory (btb/engine/cuda.py:2253-2459)"""
+        prompt = torch.as_tensor(prompt, dtype=torch.int64)
+        self.reset()
+        last = self.prefill(prompt)
+        g = self.bufs(1)
+        s = capi.stream_ptr()
+        self._pick({"logits": last.contiguous(), "pick": g["pick"]}, 1, s, g["ids"])
+        toks = [int(g["ids"][0].item())]
+        graph = self.step_graph(1, publish=True)
+        while len(toks) < max_new:
+            graph.replay()
+            torch.cuda.current_stream().synchronize()
+            toks.append(int(self.pin_tok[0]))
+        return toks
+
+    def step(self, token: int) -> int:
+        """the public one-token call: the token from pinned host memory to the card, one step, the next token back"""
+        g = self.bufs(1)
+        self.pin_in[0] = token
+        g["ids"][:1].copy_(self.pin_in[:1], non_blocking=True)
+        self.step_graph(1, publish=True).replay()
+        torch.cuda.current_stream().synchronize()
+        return int(self.pin_tok[0])
+
+    def weight_bytes(self) -> int:
+        tot = self.w.embed.numel() * 2
+        for L in self.w.layers:
+            for W in (L.qkv, L.o, L.gu, L.down):
+                tot += W.nbytes if isinstance(W, P12Matrix) else W.numel() * 2
+        return tot
+
+
+def ceil_div(a: int, b: int) -> int:
+    return -(-a // b)
+
+
+__all__ = ["CardEngine", "DenseConfig", "ModelWeights", "LayerWeights", "P12Matrix", "QWEN3_4B", "LLAMA31_70B",
+           "synth_weights", "rope_tables", "pad_rows", "math"]  # fmt: skip

@@ -1,0 +1,97 @@
+/* btb_b200 - the C-ABI of the sm_100a decode hot path.
+ *
+ * What binds here: btb launches its card kernels by name through a `Launcher`
+ * (btb/engine/card_launch.py:428-440: launch(name, grid, block, args, stream, shared)) whose one implementation
+ * loads native/cuda/btb_kernels.cu's fatbin with the CUDA driver API (btb/engine/native.py:1262-1316, 1405-1442).
+ * Each function below replaces one kernel family of that fatbin; the reference kernel it stands in for is cited
+ * beside it (file:line under native/cuda/ of btb). A `Launcher` built on these functions is a drop-in for the
+ * reference's: same buffers, same argument meaning, same bits where the comment says so.
+ *
+ * Conventions (native/src/lib.rs:1-33 of btb, kept): every function returns 0 or a negative code, writes only
+ * caller-owned buffers, never allocates and never synchronises. Pointers are DEVICE pointers unless the comment
+ * says host. `stream` is a cudaStream_t (NULL = the legacy default stream); every call only enqueues and is legal
+ * inside a stream capture. bf16 tensors are raw 16-bit patterns. Weight and activation pointers must be 16-byte
+ * aligned. Device-side refusals (a cache slot past the capacity, a token id outside the table, a bounded wait that
+ * ran out) are recorded in a status word read by btb_b200_status(); no kernel traps or spins without a limit.
+ */
+#ifndef BTB_B200_H
+#define BTB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BTB_B200_OK 0
+#define BTB_B200_ERR_NULL (-1)     /* a required pointer is null (lib.rs:20) */
+#define BTB_B200_ERR_DOMAIN (-6)   /* a zero, misaligned or unsupported dimension (lib.rs:27) */
+#define BTB_B200_ERR_CUDA (-10)    /* the CUDA runtime refused the launch */
+#define BTB_B200_ERR_TIMEOUT (-11) /* a bounded device-side wait ran out (status word only) */
+
+int btb_b200_version(void);
+int btb_b200_sm_count(void);
+/* tunables: "ring_bytes", "seg_bytes", "x_smem_max", "ctas_per_sm", "evict_first", "pdl" (host string) */
+int btb_b200_set_tuning(const char* key, int value);
+/* reads the device status word into *code (host pointer) and clears it; synchronises the default stream's copy */
+int btb_b200_status(int* code);
+
+/* ---- GEMV family: y[M,R] = bf16(sum_c w[r][c] * x[m][c]), f32 accumulate, the card's chain order ---------------
+ * M in {1,2,4,8,16,32}, C a multiple of 8. Row r of an M-row pass is the one-row step's row r to the bit. */
+
+/* btb_gemv_bf16_m{M} (btb_kernels.cu:89-155). w [R,C] bf16, x [M,C] bf16, y [M,R] bf16. */
+int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* stream);
+/* btb_gemv_silu_bf16_m{M} (btb_kernels.cu:171-227): gu [M,2C] (gate then up), x = bf16(bf16(silu(g)) * u)
+ * computed on the way in. M <= 8 and M*C*2 <= the x staging budget, else BTB_B200_ERR_DOMAIN (use
+ * btb_b200_silu_mul + btb_b200_gemv_bf16: the same bits). */
+int btb_b200_gemv_silu_bf16(const void* w, const void* gu, void* y, int M, int R, int C, void* stream);
+/* pack12 weights (btb/pack12.py:48-97; the CPU form is btb_gemv_p12_rows, native/src/lib.rs:106-135) widened in
+ * registers inside the GEMV; on a card the reference widens to a bf16 copy first (btb/engine/tiers.py:1198-1218)
+ * and runs btb_gemv_bf16 - the output here is that output to the bit. lo u8[R*C], hi4 u8[R*C/2], table HOST
+ * u8[16], esc_idx i32 / esc_val u8 the ascending escape list, esc_row i32[R+1] = for each row the first escape at
+ * or past its start (btb_b200_p12_rows builds it; null when there are no escapes). C a multiple of 32. */
+int btb_b200_gemv_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
+                      const void* esc_row, const void* x, void* y, int M, int R, int C, void* stream);
+/* esc_row[r] = lower_bound(esc_idx, r * C) for r in 0..R (the CPU kernel's per-row cursor, native/src/gemv.rs:720-735,
+ * computed once at load instead of per call) */
+int btb_b200_p12_rows(const void* esc_idx, int n_esc, int R, int C, void* esc_row, void* stream);
+
+/* ---- the step's small kernels ------------------------------------------------------------------------------------ */
+
+/* h[t,:] = table[ids[t],:] (btb/engine/cuda.py:2227-2232). ids int64 [T]. */
+int btb_b200_embed(const void* table, const void* ids, void* h, int T, int H, int V, void* stream);
+/* btb_add_rmsnorm (btb_kernels.cu:365-393): h += y (y may be null), x = bf16(h * rstd * w) or * (1 + w). */
+int btb_b200_add_rmsnorm(void* h, const void* y, const void* w, float eps, void* x, int T, int H, int centered,
+                         void* stream);
+/* btb_silu_mul (btb_kernels.cu:481-484): m[T,I] = bf16(bf16(silu(g)) * u) over gu [T,2I]. */
+int btb_b200_silu_mul(const void* gu, void* m, int T, int I, void* stream);
+/* btb_norm_rope_kv{,_tbl}_d{64,128,256} (btb_kernels.cu:261-358): q/k RMSNorm (null weights: none), RoPE from bf16
+ * tables [cap, D], K/V rows written to slot n0+t (through tbl when not null), q to [T,Hq,D]. cap: rows of the
+ * tables and of the cache's logical range; a row past it is refused (status word). */
+int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                          const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, int T,
+                          int Hq, int Hk, int D, long long hs, long long rs, int centered, const void* tbl, int cap,
+                          void* stream);
+/* btb_attn_flash_d{64,128} (btb_attn_flash.cuh:372-675): decode / tree attention over the cache, split over groups
+ * of 512 keys. part_m, part_l f32 [S,T,Hq], part_acc f32 [S,T,Hq,D], cnt i32 [T,Hk] zeroed once, S = ceil(cap/512).
+ * sinks f32 [Hq] or null (gpt-oss: a logit joined to the softmax denominator, btb/engine/families/gpt_oss/sinks.py:
+ * 203-229). Same tile/group/row folds as the reference; dot products in f32 on the SIMT cores (agrees to rounding). */
+int btb_b200_attn_decode(const void* q, const void* K, const void* V, void* out, const void* n0p, const void* par,
+                         int T, int Hq, int Hk, int D, long long hs, long long rs, float scale, void* part_m,
+                         void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
+                         void* stream);
+size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D);
+/* the greedy pick: lowest-index argmax of each bf16 logits row (torch.argmax in btb/engine/cuda.py:2237; tie rule
+ * native/src/sample.rs:57-67). scratch: btb_b200_argmax_scratch_bytes(T) bytes, 8-byte aligned, zeroed once.
+ * out int64 [T]. */
+int btb_b200_argmax_bf16(const void* logits, int T, int V, void* scratch, void* out, void* stream);
+size_t btb_b200_argmax_scratch_bytes(int T);
+/* btb_publish (btb_kernels.cu:455-465): n0 += advance, then token, device clock (ns) and length to pinned host memory,
+ * the length last behind a system fence. out_* null: only the advance. */
+int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -174,11 +174,12 @@ class CpuTier:
 class CardPath:
     """KV position-major [cap, Hk, D] (hs = D, rs = Hk * D), btb/engine/arena.py:1-5"""
 
-    def __init__(self, w: Weights, cap: int = 512, silu_fold: bool = True):
+    def __init__(self, w: Weights, cap: int = 512, silu_fold: bool = True, tables=None):
         self.w, self.cfg = w, w.cfg
         c = self.cfg
         self.cap = cap
-        self.cos, self.sin = rope_tables_bf16(c, cap)
+        # `tables`: the engine's own bf16 cos/sin bit patterns, so both sides read the same table
+        self.cos, self.sin = rope_tables_bf16(c, cap) if tables is None else tables
         self.K = np.zeros((c.layers, cap, c.kv_heads, c.head_dim), np.uint16)
         self.V = np.zeros_like(self.K)
         self.n = 0
