@@ -283,6 +283,9 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
     if (!q || !K || !V || !out || !n0p || !par || !part_m || !part_l || !part_acc || !cnt) return B2_ERR_NULL;
     if (T <= 0 || T > TMAX || Hk <= 0 || Hq <= 0 || Hq % Hk || Hq / Hk > GMAX || cap <= 0 || !(scale == scale))
         return B2_ERR_DOMAIN;
+    // a key row is read as 16-byte chunks, a value row as D/32-element runs
+    if ((hs & 7) || (rs & 7) || (reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15))
+        return B2_ERR_DOMAIN;
     AttnArgs a{};
     a.q = static_cast<const bf16*>(q), a.K = static_cast<const bf16*>(K), a.V = static_cast<const bf16*>(V);
     a.out = static_cast<bf16*>(out), a.n0p = static_cast<const int*>(n0p), a.par = static_cast<const int*>(par);

@@ -50,7 +50,14 @@ static inline int b2_allow_smem(const void* kern, bool* done_for_device) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
     if (!done_for_device[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) {
+        // the opt-in ceiling (227 KB a block) covers static and dynamic shared memory together
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return B2_ERR_CUDA;
+        }
+        const int room = 227 * 1024 - (int)fa.sharedSizeBytes;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, room) != cudaSuccess) {
             (void)cudaGetLastError();
             return B2_ERR_CUDA;
         }

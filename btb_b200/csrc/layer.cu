@@ -185,7 +185,9 @@ __global__ void __launch_bounds__(256) argmax_rows(const ArgmaxArgs A) {
     const int t = blockIdx.y;
     const bf16* row = A.logits + (size_t)t * A.V;
     unsigned long long best = 0ull;
-    const int nvec = A.V >> 3;
+    // 16-byte loads only where every row starts on 16 bytes: the vocabulary a multiple of 8 and the base aligned
+    const bool vec = (A.V & 7) == 0 && (reinterpret_cast<uintptr_t>(A.logits) & 15) == 0;
+    const int nvec = vec ? A.V >> 3 : 0;
     for (int c = blockIdx.x * 256 + threadIdx.x; c < nvec; c += gridDim.x * 256) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(row) + c);
         const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
@@ -197,8 +199,8 @@ __global__ void __launch_bounds__(256) argmax_rows(const ArgmaxArgs A) {
             best = best > b ? best : b;
         }
     }
-    if (blockIdx.x == 0)  // a vocabulary that is not a multiple of 8: the tail, element by element
-        for (int i = nvec * 8 + threadIdx.x; i < A.V; i += 256) {
+    if (!vec)  // element by element
+        for (int i = blockIdx.x * 256 + threadIdx.x; i < A.V; i += gridDim.x * 256) {
             const unsigned long long a = pick_key(bf2f(row[i]), i);
             best = best > a ? best : a;
         }
@@ -258,6 +260,7 @@ __global__ void publish_step(const PublishArgs A) {
 extern "C" int btb_b200_embed(const void* table, const void* ids, void* h, int T, int H, int V, void* stream) {
     if (!table || !ids || !h) return B2_ERR_NULL;
     if (T <= 0 || H <= 0 || (H & 7) || V <= 0) return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(table) & 15) || (reinterpret_cast<uintptr_t>(h) & 15)) return B2_ERR_DOMAIN;
     EmbedArgs a{static_cast<const bf16*>(table), static_cast<const long long*>(ids), static_cast<bf16*>(h), T, H, V};
     return b2_launch((const void*)embed_rows, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
 }

@@ -244,7 +244,7 @@ class CardEngine:
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             k("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
             self._matvec(L.gu, g["x"], g["gu"], M, 2 * I, H, s)
-            if self.silu_fold and M <= 8 and not isinstance(L.down, P12Matrix):
+            if self.silu_fold and M * I * 2 <= 64 * 1024 and not isinstance(L.down, P12Matrix):
                 k("btb_b200_gemv_silu_bf16", ptr(L.down), ptr(g["gu"]), ptr(g["y"]), M, H, I, s)
             else:
                 k("btb_b200_silu_mul", ptr(g["gu"]), ptr(g["m"]), M, I, s)

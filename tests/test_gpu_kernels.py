@@ -126,6 +126,11 @@ def test_gemv_silu_fold_equals_two_kernels(M, R, Cc):
     w, gu = rand_bf(rng, (R, Cc), 0.02), rand_bf(rng, (M, 2 * Cc), 1.5)
     wt, gt = bf(w), bf(gu)
     y = torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
+    if M * Cc * 2 > 64 * 1024:  # the activated x does not fit its shared-memory budget: refused, by contract
+        with pytest.raises(capi.NativeError) as e:
+            call("btb_b200_gemv_silu_bf16", ptr(wt), ptr(gt), ptr(y), M, R, Cc, s())
+        assert e.value.rc == capi.ERR_DOMAIN
+        return
     call("btb_b200_gemv_silu_bf16", ptr(wt), ptr(gt), ptr(y), M, R, Cc, s())
     m = torch.zeros(M, Cc, dtype=torch.bfloat16, device=DEV)
     y2 = torch.zeros_like(y)
@@ -381,7 +386,7 @@ def test_ref_gemv_bits(ref, b200, M):
         for lz, y in ((ref, ya), (b200, yb)):
             L.btb_gemv_bf16(lz, M, ((R + 3) // 4, 1, 1), (128, 1, 1), _P(w), _P(x), _P(y), R, Cc)
         assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
-        if M <= 8:
+        if M <= 8 and M * Cc * 2 <= 64 * 1024:  # the fold's shared-memory budget for the activated x
             gu = bf(rand_bf(rng, (M, 2 * Cc), 1.5))
             for lz, y in ((ref, ya), (b200, yb)):
                 L.btb_gemv_silu_bf16(lz, M, ((R + 3) // 4, 1, 1), (128, 1, 1), _P(w), _P(gu), _P(y), R, Cc)
