@@ -126,23 +126,28 @@ __global__ void __launch_bounds__(GT * 32) attn_decode(const AttnArgs A) {
                 if (A.tbl != nullptr) sl = A.tbl[sl];
                 row[k] = sl;
             }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            // the key's whole row in flight at once (D/8 independent 16-byte loads), then the G dot products, each
+            // an f32 chain over the dims in index order
+            uint4 kv[D / 8];
+            const uint4* kr = reinterpret_cast<const uint4*>(Kg + (size_t)(row[k] >= 0 ? row[k] : 0) * A.rs);
+#pragma unroll
+            for (int c = 0; c < D / 8; ++c) kv[c] = row[k] >= 0 ? __ldg(kr + c) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
             for (int hh = 0; hh < GMAX; ++hh) s[k][hh] = 0.f;
-            if (row[k] >= 0) {
-                const uint4* kr = reinterpret_cast<const uint4*>(Kg + (size_t)row[k] * A.rs);
-#pragma unroll 4
-                for (int c = 0; c < D / 8; ++c) {
-                    const uint4 kv = __ldg(kr + c);
-                    const float kf[8] = {bf_lo(kv.x), bf_hi(kv.x), bf_lo(kv.y), bf_hi(kv.y),
-                                         bf_lo(kv.z), bf_hi(kv.z), bf_lo(kv.w), bf_hi(kv.w)};
 #pragma unroll
-                    for (int hh = 0; hh < GMAX; ++hh) {
-                        if (hh < G) {
-                            float a = s[k][hh];
+            for (int c = 0; c < D / 8; ++c) {
+                const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
+                                     bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) a = fmaf(kf[e], qs[hh][c * 8 + e], a);
-                            s[k][hh] = a;
-                        }
+                for (int hh = 0; hh < GMAX; ++hh) {
+                    if (hh < G) {
+                        float a = s[k][hh];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) a = fmaf(kf[e], qs[hh][c * 8 + e], a);
+                        s[k][hh] = a;
                     }
                 }
             }
@@ -175,28 +180,34 @@ __global__ void __launch_bounds__(GT * 32) attn_decode(const AttnArgs A) {
         for (int hh = 0; hh < GMAX; ++hh)
 #pragma unroll
             for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
-        for (int k = 0; k < 2; ++k) {
-            for (int i = 0; i < 32; ++i) {
-                const int rk = __shfl_sync(0xffffffffu, row[k], i);
-                if (rk < 0) continue;  // warp-uniform
-                float vf[E];
-                const bf16* vr = Vg + (size_t)rk * A.rs + lane * E;
-                if (E == 4) {
-                    const uint2 vv = __ldg(reinterpret_cast<const uint2*>(vr));
-                    vf[0] = bf_lo(vv.x), vf[1] = bf_hi(vv.x), vf[2] = bf_lo(vv.y), vf[3] = bf_hi(vv.y);
-                } else if (E == 2) {
-                    const uint32_t vv = __ldg(reinterpret_cast<const uint32_t*>(vr));
-                    vf[0] = bf_lo(vv), vf[1] = bf_hi(vv);
-                } else {
+        // sixteen keys' value runs in flight at a time; a key no row sees contributes weight 0 over zeros
+        constexpr int VB = 16;
 #pragma unroll
-                    for (int e = 0; e < E; ++e) vf[e] = bf2f(vr[e]);
+        for (int k = 0; k < 2; ++k) {
+#pragma unroll
+            for (int i0 = 0; i0 < 32; i0 += VB) {
+                float vf[VB][E];
+#pragma unroll
+                for (int u = 0; u < VB; ++u) {
+                    const int rk = __shfl_sync(0xffffffffu, row[k], i0 + u);
+                    const bf16* vr = Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
+                    if (E == 4) {
+                        const uint2 vv = rk >= 0 ? __ldg(reinterpret_cast<const uint2*>(vr)) : make_uint2(0u, 0u);
+                        vf[u][0] = bf_lo(vv.x), vf[u][1] = bf_hi(vv.x), vf[u][2] = bf_lo(vv.y), vf[u][3] = bf_hi(vv.y);
+                    } else {
+                        const uint32_t vv = rk >= 0 ? __ldg(reinterpret_cast<const uint32_t*>(vr)) : 0u;
+                        vf[u][0] = bf_lo(vv), vf[u][E - 1] = bf_hi(vv);
+                    }
                 }
 #pragma unroll
-                for (int hh = 0; hh < GMAX; ++hh) {
-                    if (hh < G) {
-                        const float p = ps[warp * G + hh][k * 32 + i];
+                for (int u = 0; u < VB; ++u) {
 #pragma unroll
-                        for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[e], o[hh][e]);
+                    for (int hh = 0; hh < GMAX; ++hh) {
+                        if (hh < G) {
+                            const float p = ps[warp * G + hh][k * 32 + i0 + u];
+#pragma unroll
+                            for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[u][e], o[hh][e]);
+                        }
                     }
                 }
             }

@@ -26,7 +26,7 @@ constexpr int NW = 8;             // warps a CTA, a ring each
 constexpr int THREADS = NW * 32;  // 256
 
 enum Fmt { F_BF16 = 0, F_P12 = 1 };
-enum XMode { X_SMEM = 0, X_SMEM_SILU = 1, X_GLOBAL = 2 };
+enum XMode { X_SMEM = 0, X_SMEM_SILU = 1, X_GLOBAL = 2, X_SMEM_NORM = 3 };
 
 struct GemvArgs {
     const uint8_t* w;    // bf16: [R, C] bf16; p12: lo bytes [R*C]
@@ -41,6 +41,15 @@ struct GemvArgs {
     int seg;     // elements a stage holds (a multiple of 256)
     int stages;  // ring depth
     int evict_first;
+    // the residual + RMSNorm prologue (X_SMEM_NORM): x = rmsnorm(h_in + y) * w computed by every CTA on the way in,
+    // h_out = h_in + y written by CTA 0 (h_in is never written here, so no CTA reads a half-updated row)
+    const bf16* h_in;
+    const bf16* y_add;   // null: no add
+    const bf16* norm_w;
+    bf16* h_out;         // null when y_add is null
+    float eps;
+    int centered;
+    int T;               // live rows (rows T..M-1 of x are zeros)
 };
 
 // a stage's bytes for `n` elements of a row
@@ -93,9 +102,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
     constexpr bool XS = XM != X_GLOBAL;
 
     // shared memory: [x: M*C bf16 when staged][rings: NW * S stages][barriers: NW * S]
-    const int xbytes = XS ? ((M * C * 2 + 127) & ~127) : 0;
+    // (the norm prologue adds one f32 row of h and the 256 partial sums in front)
+    const int nbytes = XM == X_SMEM_NORM ? ((C * 4 + THREADS * 4 + 127) & ~127) : 0;
+    const int xbytes = (XS ? ((M * C * 2 + 127) & ~127) : 0) + nbytes;
     const int sbytes = (stage_bytes<FMT>(seg) + 127) & ~127;
-    bf16* xs = reinterpret_cast<bf16*>(smem);
+    bf16* xs = reinterpret_cast<bf16*>(smem + nbytes);
     uint8_t* ring = smem + xbytes + (size_t)warp * S * sbytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + xbytes + (size_t)NW * S * sbytes) + warp * S;
 
@@ -149,13 +160,75 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
             const uint4* src = reinterpret_cast<const uint4*>(A.x);
             uint4* dst = reinterpret_cast<uint4*>(xs);
             for (int i = threadIdx.x; i < M * C / 8; i += THREADS) dst[i] = __ldg(src + i);
+        } else if (XM == X_SMEM_SILU) {
+            // x[m][c] = bf16(bf16(silu(g)) * u), gu [M, 2C] gate then up: the values btb_silu_mul would have written;
+            // eight elements a thread a trip (16-byte loads), elementwise so the order is free
+            const int cv = C >> 3;
+            for (int i = threadIdx.x; i < M * cv; i += THREADS) {
+                const int m = i / cv, c8 = i - m * cv;
+                const uint4 gv = __ldg(reinterpret_cast<const uint4*>(A.x + (size_t)m * 2 * C) + c8);
+                const uint4 uv = __ldg(reinterpret_cast<const uint4*>(A.x + (size_t)m * 2 * C + C) + c8);
+                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float a = bfround(act_silu(bf_lo(gw[k]))) * bf_lo(uw[k]);
+                    const float b = bfround(act_silu(bf_hi(gw[k]))) * bf_hi(uw[k]);
+                    const __nv_bfloat162 pr = __floats2bfloat162_rn(a, b);
+                    o[k] = *reinterpret_cast<const uint32_t*>(&pr);
+                }
+                reinterpret_cast<uint4*>(xs + (size_t)m * C)[c8] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
         } else {
-            // x[m][c] = bf16(bf16(silu(g)) * u), gu [M, 2C] gate then up: the values btb_silu_mul would have written
-            for (int i = threadIdx.x; i < M * C; i += THREADS) {
-                const int m = i / C, c = i - m * C;
-                const float g = bf2f(A.x[(size_t)m * 2 * C + c]);
-                const float u = bf2f(A.x[(size_t)m * 2 * C + C + c]);
-                xs[i] = f2bf(bfround(act_silu(g)) * u);
+            // residual + RMSNorm on the way in (the arithmetic of add_rmsnorm, native/cuda/btb_kernels.cu:365-393 of
+            // the reference): hv = bf16(h + y); thread i of 256 sums hv^2 over i, i + 256, .. in order; the fixed
+            // 256 -> 1 tree; x = bf16(hv * rsqrt(ss / H + eps) * w). Every CTA computes the same values; CTA 0
+            // writes the new residual.
+            float* hsm = reinterpret_cast<float*>(smem);
+            float* red = hsm + C;
+            const int cv = C >> 3, tid = threadIdx.x;
+            for (int m = 0; m < M; ++m) {
+                if (m >= A.T) {  // a padding row: zeros
+                    for (int i = tid; i < cv; i += THREADS)
+                        reinterpret_cast<uint4*>(xs + (size_t)m * C)[i] = make_uint4(0u, 0u, 0u, 0u);
+                    continue;
+                }
+                for (int i = tid; i < cv; i += THREADS) {
+                    const uint4 hv = __ldg(reinterpret_cast<const uint4*>(A.h_in + (size_t)m * C) + i);
+                    uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                    if (A.y_add != nullptr) {
+                        const uint4 yv = __ldg(reinterpret_cast<const uint4*>(A.y_add + (size_t)m * C) + i);
+                        const uint32_t yw[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const __nv_bfloat162 pr =
+                                __floats2bfloat162_rn(bf_lo(hw[k]) + bf_lo(yw[k]), bf_hi(hw[k]) + bf_hi(yw[k]));
+                            hw[k] = *reinterpret_cast<const uint32_t*>(&pr);
+                        }
+                        if (blockIdx.x == 0)
+                            reinterpret_cast<uint4*>(A.h_out + (size_t)m * C)[i] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        hsm[i * 8 + 2 * k] = bf_lo(hw[k]);
+                        hsm[i * 8 + 2 * k + 1] = bf_hi(hw[k]);
+                    }
+                }
+                __syncthreads();
+                float ss = 0.f;
+                for (int i = tid; i < C; i += THREADS) ss = fmaf(hsm[i], hsm[i], ss);
+                red[tid] = ss;
+                __syncthreads();
+                for (int st = THREADS / 2; st > 0; st >>= 1) {
+                    if (tid < st) red[tid] += red[tid + st];
+                    __syncthreads();
+                }
+                const float rstd = rsqrtf(red[0] / (float)C + A.eps);
+                for (int i = tid; i < C; i += THREADS) {
+                    const float wv = bf2f(A.norm_w[i]);
+                    xs[(size_t)m * C + i] = f2bf(hsm[i] * rstd * (A.centered ? 1.f + wv : wv));
+                }
+                __syncthreads();
             }
         }
         __syncthreads();
@@ -258,11 +331,11 @@ struct Plan {
 // ring geometry: split a row into equal segments of at most `max_seg_bytes`, each a multiple of 256 elements (so a
 // lane's chunk l + 32 j of the row is chunk l + 32 j' of its segment), as many stages as the per-warp budget holds
 template <int FMT>
-Plan make_plan(int M, int R, int C, bool want_xs) {
+Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     const B2Tuning& t = b2_tuning();
     Plan p;
-    const int xbytes = (M * C * 2 + 127) & ~127;
-    p.xs = want_xs && xbytes <= t.x_smem_max;
+    const int xbytes = ((M * C * 2 + 127) & ~127) + (norm ? ((C * 4 + THREADS * 4 + 127) & ~127) : 0);
+    p.xs = want_xs && (M * C * 2) <= t.x_smem_max;
     const int ring = t.ring_bytes;
     int per_warp = ring / NW;
     int max_seg_el = t.seg_bytes / (FMT == F_BF16 ? 2 : 1);  // elements
@@ -368,6 +441,36 @@ extern "C" int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, 
     return p.xs ? launch_m<F_BF16, X_SMEM>(M, a, p, s) : launch_m_global<F_BF16>(M, a, p, s);
 }
 
+// x = rmsnorm(h_in + y) * w computed inside the GEMV (bf16 weights, or pack12 when hi4 is not null)
+extern "C" int btb_b200_gemv_norm(const void* w, const void* hi4, const void* table, const void* esc_idx,
+                                  const void* esc_val, const void* esc_row, const void* h_in, const void* y_add,
+                                  const void* norm_w, float eps, int centered, void* h_out, void* y, int T, int M, int R,
+                                  int C, void* stream) {
+    int rc = check_dims(w, h_in, y, M, R, C);
+    if (rc) return rc;
+    if (norm_w == nullptr || (y_add != nullptr && h_out == nullptr)) return B2_ERR_NULL;
+    if (T <= 0 || T > M || M > 8 || !(eps == eps) || h_out == h_in) return B2_ERR_DOMAIN;
+    const bool p12 = hi4 != nullptr;
+    if (p12 && (table == nullptr || (C & 31) != 0 || (reinterpret_cast<uintptr_t>(hi4) & 15))) return B2_ERR_DOMAIN;
+    GemvArgs a{};
+    a.w = static_cast<const uint8_t*>(w);
+    a.hi4 = static_cast<const uint8_t*>(hi4);
+    a.esc_idx = static_cast<const int32_t*>(esc_idx);
+    a.esc_val = static_cast<const uint8_t*>(esc_val);
+    a.esc_row = static_cast<const int32_t*>(esc_row);
+    if (p12) memcpy(a.table, table, 16);
+    a.y = static_cast<bf16*>(y);
+    a.R = R, a.C = C;
+    a.h_in = static_cast<const bf16*>(h_in), a.y_add = static_cast<const bf16*>(y_add);
+    a.norm_w = static_cast<const bf16*>(norm_w), a.h_out = static_cast<bf16*>(h_out);
+    a.eps = eps, a.centered = centered, a.T = T;
+    Plan p = p12 ? make_plan<F_P12>(M, R, C, true, true) : make_plan<F_BF16>(M, R, C, true, true);
+    if (!p.xs) return B2_ERR_DOMAIN;  // too wide to stage: the caller runs btb_b200_add_rmsnorm and the plain GEMV
+    a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return p12 ? launch_m<F_P12, X_SMEM_NORM>(M, a, p, s) : launch_m<F_BF16, X_SMEM_NORM>(M, a, p, s);
+}
+
 extern "C" int btb_b200_gemv_silu_bf16(const void* w, const void* gu, void* y, int M, int R, int C, void* stream) {
     int rc = check_dims(w, gu, y, M, R, C);
     if (rc) return rc;
@@ -382,6 +485,31 @@ extern "C" int btb_b200_gemv_silu_bf16(const void* w, const void* gu, void* y, i
     if (!p.xs || M > 8) return B2_ERR_DOMAIN;
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
     return launch_m<F_BF16, X_SMEM_SILU>(M, a, p, static_cast<cudaStream_t>(stream));
+}
+
+// the SwiGLU fold over pack12 weights
+extern "C" int btb_b200_gemv_silu_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx,
+                                      const void* esc_val, const void* esc_row, const void* gu, void* y, int M, int R,
+                                      int C, void* stream) {
+    int rc = check_dims(lo, gu, y, M, R, C);
+    if (rc) return rc;
+    if (hi4 == nullptr || table == nullptr) return B2_ERR_NULL;
+    if ((C & 31) != 0 || (reinterpret_cast<uintptr_t>(hi4) & 15)) return B2_ERR_DOMAIN;
+    GemvArgs a{};
+    a.w = static_cast<const uint8_t*>(lo);
+    a.hi4 = static_cast<const uint8_t*>(hi4);
+    a.esc_idx = static_cast<const int32_t*>(esc_idx);
+    a.esc_val = static_cast<const uint8_t*>(esc_val);
+    a.esc_row = static_cast<const int32_t*>(esc_row);
+    if (a.esc_row != nullptr && (a.esc_idx == nullptr || a.esc_val == nullptr)) return B2_ERR_NULL;
+    memcpy(a.table, table, 16);
+    a.x = static_cast<const bf16*>(gu);
+    a.y = static_cast<bf16*>(y);
+    a.R = R, a.C = C;
+    Plan p = make_plan<F_P12>(M, R, C, true);
+    if (!p.xs || M > 8) return B2_ERR_DOMAIN;
+    a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
+    return launch_m<F_P12, X_SMEM_SILU>(M, a, p, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int btb_b200_gemv_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx,

@@ -160,7 +160,8 @@ def pad_rows(T: int) -> int:
 class CardEngine:
     """one model on one card: its cache arena, pass buffers, step graph and greedy loop"""
 
-    def __init__(self, weights: ModelWeights, cap: int = 4096, silu_fold: bool = True, device: Any = "cuda"):
+    def __init__(self, weights: ModelWeights, cap: int = 4096, silu_fold: bool = True, fuse_norm: bool = True,
+                 device: Any = "cuda"):
         capi.lib()  # fail here, loudly, when the library is not built
         if not torch.cuda.is_available():
             raise RuntimeError("btb_b200 needs a CUDA device: there is no CPU path")
@@ -176,6 +177,7 @@ class CardEngine:
         self.S = (self.cap + GROUP_KEYS - 1) // GROUP_KEYS
         self.n0 = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.silu_fold = silu_fold
+        self.fuse_norm = fuse_norm
         self._bufs: dict[int, dict[str, torch.Tensor]] = {}
         self._graphs: dict[Any, Any] = {}
         self.pin_tok = torch.zeros(1, dtype=torch.int64).pin_memory()
@@ -194,7 +196,7 @@ class CardEngine:
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)  # noqa: E731
         H, Hq, D = c.hidden, c.q_heads, c.head_dim
         g = {
-            "h": bf(M, H), "x": bf(M, H), "y": bf(M, H), "qkv": bf(M, c.qkv_rows), "q": bf(M, Hq, D),
+            "h": bf(M, H), "h2": bf(M, H), "x": bf(M, H), "y": bf(M, H), "qkv": bf(M, c.qkv_rows), "q": bf(M, Hq, D),
             "att": bf(M, Hq * D), "gu": bf(M, 2 * c.inter), "m": bf(M, c.inter), "logits": bf(M, c.vocab),
             "ids": torch.zeros(M, dtype=torch.int64, device=dev),
             "tok": torch.zeros(M, dtype=torch.int64, device=dev),
@@ -231,10 +233,28 @@ class CardEngine:
         s = capi.stream_ptr() if stream_ptr is None else stream_ptr
         H, Hq, Hk, D, I = c.hidden, c.q_heads, c.kv_heads, c.head_dim, c.inter
         k = self._k
+        # the residual ping-pongs between two buffers when the norm is folded into the GEMV that reads it (a CTA must
+        # not read a row another CTA is updating); the pass starts and ends on g["h"]
+        fuse = self.fuse_norm and M <= 8 and M * max(H, 1) * 2 <= 64 * 1024
+        hcur, halt = g["h"], g["h2"]
+
+        def normed_matvec(W: Any, norm_w: torch.Tensor, y_add: Any, out: torch.Tensor, R: int) -> None:
+            nonlocal hcur, halt
+            if fuse:
+                p12 = isinstance(W, P12Matrix)
+                parts = ((ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val), ptr(W.esc_row)) if p12
+                         else (ptr(W), 0, 0, 0, 0, 0))  # fmt: skip
+                k("btb_b200_gemv_norm", *parts, ptr(hcur), ptr(y_add), ptr(norm_w), c.eps, 0,
+                  ptr(halt) if y_add is not None else 0, ptr(out), T, M, R, H, s)
+                if y_add is not None:
+                    hcur, halt = halt, hcur
+            else:
+                k("btb_b200_add_rmsnorm", ptr(hcur), ptr(y_add), ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
+                self._matvec(W, g["x"], out, M, R, H, s)
+
         y_prev = None
         for i, L in enumerate(self.w.layers):
-            k("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(g["x"]), T, H, 0, s)
-            self._matvec(L.qkv, g["x"], g["qkv"], M, c.qkv_rows, H, s)
+            normed_matvec(L.qkv, L.ln1, y_prev, g["qkv"], c.qkv_rows)
             k("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
               ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
               self.rs, 0, 0, self.cap, s)  # fmt: skip
@@ -242,17 +262,22 @@ class CardEngine:
               ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
               ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
-            k("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
-            self._matvec(L.gu, g["x"], g["gu"], M, 2 * I, H, s)
-            if self.silu_fold and M * I * 2 <= 64 * 1024 and not isinstance(L.down, P12Matrix):
-                k("btb_b200_gemv_silu_bf16", ptr(L.down), ptr(g["gu"]), ptr(g["y"]), M, H, I, s)
+            normed_matvec(L.gu, L.ln2, g["y"], g["gu"], 2 * I)
+            if self.silu_fold and M * I * 2 <= 64 * 1024:
+                if isinstance(L.down, P12Matrix):
+                    W = L.down
+                    k("btb_b200_gemv_silu_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),
+                      ptr(W.esc_row), ptr(g["gu"]), ptr(g["y"]), M, H, I, s)  # fmt: skip
+                else:
+                    k("btb_b200_gemv_silu_bf16", ptr(L.down), ptr(g["gu"]), ptr(g["y"]), M, H, I, s)
             else:
                 k("btb_b200_silu_mul", ptr(g["gu"]), ptr(g["m"]), M, I, s)
                 self._matvec(L.down, g["m"], g["y"], M, H, I, s)
             y_prev = g["y"]
         if tail:
-            k("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(self.w.norm), c.eps, ptr(g["x"]), T, H, 0, s)
-            self._matvec(self.w.embed, g["x"], g["logits"], M, c.vocab, H, s)
+            normed_matvec(self.w.embed, self.w.norm, y_prev, g["logits"], c.vocab)
+        if hcur is not g["h"]:  # an odd number of folded adds (a pass without its tail): bring the residual home
+            g["h"].copy_(hcur)
 
     def _embed(self, g: dict, T: int, s: int) -> None:
         self._k("btb_b200_embed", ptr(self.w.embed), ptr(g["ids"]), ptr(g["h"]), T, self.cfg.hidden, self.cfg.vocab, s)

@@ -53,6 +53,19 @@ int btb_b200_gemv_silu_bf16(const void* w, const void* gu, void* y, int M, int R
  * or past its start (btb_b200_p12_rows builds it; null when there are no escapes). C a multiple of 32. */
 int btb_b200_gemv_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
                       const void* esc_row, const void* x, void* y, int M, int R, int C, void* stream);
+/* btb_gemv_silu over pack12 weights: the fold of btb_b200_gemv_silu_bf16 with the widen of btb_b200_gemv_p12. */
+int btb_b200_gemv_silu_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx,
+                           const void* esc_val, const void* esc_row, const void* gu, void* y, int M, int R, int C,
+                           void* stream);
+/* btb_add_rmsnorm (btb_kernels.cu:365-393) folded into the GEMV that reads its output (btb_gemv_bf16_m{M}, :89-155):
+ * every CTA computes x = rmsnorm(h_in + y_add) * norm_w on the way in (the same operations in the same order, so the
+ * same bits as the two kernels), CTA 0 writes h_out = h_in + y_add. One launch instead of two, and the weight
+ * copies are already in flight while the norm runs. y_add null: no add, h_out unused. h_out must not be h_in.
+ * w alone: bf16 weights; hi4 not null: pack12 parts as btb_b200_gemv_p12 (table a HOST pointer). T live rows of the
+ * M the pass is padded to (M <= 8); rows T..M-1 of y are computed over zeros. */
+int btb_b200_gemv_norm(const void* w, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
+                       const void* esc_row, const void* h_in, const void* y_add, const void* norm_w, float eps,
+                       int centered, void* h_out, void* y, int T, int M, int R, int C, void* stream);
 /* esc_row[r] = lower_bound(esc_idx, r * C) for r in 0..R (the CPU kernel's per-row cursor, native/src/gemv.rs:720-735,
  * computed once at load instead of per call) */
 int btb_b200_p12_rows(const void* esc_idx, int n_esc, int R, int C, void* esc_row, void* stream);

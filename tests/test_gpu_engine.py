@@ -150,6 +150,20 @@ def test_public_step_call(small):
     assert got == toks
 
 
+def test_folded_kernels_change_no_bit(small):
+    """the norm folded into the GEMV and the SwiGLU fold are the separate kernels' arithmetic: same logits, bit for bit"""
+    mw, eng = small
+    plain = E.CardEngine(mw, cap=eng.cap, silu_fold=False, fuse_norm=False)
+    ids = torch.arange(100, 107)
+    for T in (1, 3, 7):
+        eng.reset()
+        plain.reset()
+        a, b = eng.forward(ids[:T]), plain.forward(ids[:T])
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), T
+        assert torch.equal(eng.bufs(E.pad_rows(T))["h"][:T].view(torch.int16),
+                           plain.bufs(E.pad_rows(T))["h"][:T].view(torch.int16))
+
+
 def test_p12_model_equals_bf16_model_bits():
     """config 2's requirement: the packed store's logits are the bf16 store's, bit for bit"""
     cfg = E.DenseConfig("small-p12", hidden=256, layers=2, q_heads=8, kv_heads=2, head_dim=128, inter=512, vocab=512)

@@ -147,6 +147,29 @@ def test_gemv_silu_fold_equals_two_kernels(M, R, Cc):
     assert np.max(np.abs(diff)) <= 1 and np.mean(diff != 0) < 1e-3
 
 
+@pytest.mark.parametrize("M,T", [(1, 1), (4, 3), (8, 8)])
+@pytest.mark.parametrize("R,H", [(300, 2560), (64, 264), (1000, 4096)])
+@pytest.mark.parametrize("add", [True, False])
+def test_gemv_with_norm_prologue_equals_two_kernels(M, T, R, H, add):
+    rng = np.random.default_rng(R + H + M)
+    w, h0, yv, nw = rand_bf(rng, (R, H), 0.02), rand_bf(rng, (M, H)), rand_bf(rng, (M, H), 0.1), rand_bf(rng, (H,))
+    wt, nt = bf(w), bf(nw)
+    yt = bf(yv) if add else None
+    # two kernels
+    h1, x1, y1 = bf(h0), torch.zeros(M, H, dtype=torch.bfloat16, device=DEV), torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_add_rmsnorm", ptr(h1), ptr(yt), ptr(nt), 1e-6, ptr(x1), T, H, 0, s())
+    call("btb_b200_gemv_bf16", ptr(wt), ptr(x1), ptr(y1), M, R, H, s())
+    # one
+    hin, hout, y2 = bf(h0), torch.zeros(M, H, dtype=torch.bfloat16, device=DEV), torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_gemv_norm", ptr(wt), 0, 0, 0, 0, 0, ptr(hin), ptr(yt), ptr(nt), 1e-6, 0, ptr(hout) if add else 0,
+         ptr(y2), T, M, R, H, s())  # fmt: skip
+    assert torch.equal(y1[:T].view(torch.int16), y2[:T].view(torch.int16))
+    assert int(y2[T:].float().abs().sum()) == 0  # padding rows multiply zeros
+    assert np.array_equal(bits(hin), h0)  # the input residual is left alone
+    if add:
+        assert torch.equal(h1[:T].view(torch.int16), hout[:T].view(torch.int16))
+
+
 # ---- pack12 ------------------------------------------------------------------------------------------------------
 
 
@@ -179,6 +202,19 @@ def test_gemv_p12_equals_bf16_gemv_bits(R, Cc, dense, M):
          ptr(y), M, R, Cc, s())  # fmt: skip
     assert np.array_equal(bits(y), O.gemv_card_bf16(wb, x))
     assert np.array_equal(bits(y), O.gemv_card_p12(*parts, x, R, Cc))
+    if M <= 8 and M * Cc * 2 <= 64 * 1024:
+        # the folds over packed weights equal the folds over the bf16 matrix
+        wt = bf(wb)
+        gu, nw = bf(rand_bf(rng, (M, 2 * Cc), 1.5)), bf(rand_bf(rng, (Cc,)))
+        ya, yb = torch.zeros_like(y), torch.zeros_like(y)
+        call("btb_b200_gemv_silu_bf16", ptr(wt), ptr(gu), ptr(ya), M, R, Cc, s())
+        call("btb_b200_gemv_silu_p12", ptr(P.lo), ptr(P.hi4), P.table, ptr(P.esc_idx), ptr(P.esc_val), ptr(P.esc_row),
+             ptr(gu), ptr(yb), M, R, Cc, s())  # fmt: skip
+        assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
+        call("btb_b200_gemv_norm", ptr(wt), 0, 0, 0, 0, 0, ptr(xt), 0, ptr(nw), 1e-6, 0, 0, ptr(ya), M, M, R, Cc, s())
+        call("btb_b200_gemv_norm", ptr(P.lo), ptr(P.hi4), P.table, ptr(P.esc_idx), ptr(P.esc_val), ptr(P.esc_row),
+             ptr(xt), 0, ptr(nw), 1e-6, 0, 0, ptr(yb), M, M, R, Cc, s())  # fmt: skip
+        assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
 
 
 # ---- the small kernels -------------------------------------------------------------------------------------------
