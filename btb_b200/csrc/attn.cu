@@ -10,8 +10,9 @@
 // by the cache's bytes, not by math), so results agree with the reference's tensor-core tiles to rounding, not to
 // the bit; the tests hold them to 2^-6 of the row's largest output like the reference's own attention test.
 //
-// Launch: block (grp, g, t) takes group grp of kv head g for token t's G query heads; warp w takes tile w of the
-// group (a lane two keys for the scores, D/32 dims for the output). Groups past the row's keys return at once, so
+// Launch: block (grp, g, t) takes group grp of kv head g for token t's G query heads (G = 1, 2, 4 or 8); two warps
+// take each tile of the group (a lane one key for the scores, D/32 dims for the output; the halves share the tile's
+// max and their sums and outputs are added). Groups past the row's keys return at once, so
 // one captured launch serves every length up to the capacity. A row reaching several groups stores each group's
 // state and the last block to arrive folds them in group order - no block ever waits for another.
 #include "common.cuh"
@@ -25,7 +26,6 @@ constexpr int BN = 64;        // keys a tile
 constexpr int GT = 8;         // tiles a group: one a warp
 constexpr int GK = BN * GT;   // keys a group
 constexpr int TMAX = 32;      // rows a pass at most
-constexpr int GMAX = 8;       // query heads a kv head at most
 #define LOG2E 1.4426950408889634f
 
 __device__ __forceinline__ float ex2(float x) {
@@ -67,25 +67,35 @@ struct AttnArgs {
     long long hs, rs;
 };
 
-template <int D>
-__global__ void __launch_bounds__(GT * 32) attn_decode(const AttnArgs A) {
+constexpr int NWA = 2 * GT;  // warps a block: two a tile, 32 keys each (a lane one key)
+
+// The block's shared memory (dynamic): the token's queries, the half-tiles' maxima and sums, each warp's weights
+// (bf16-rounded) and each warp's partial outputs.
+template <int D, int G>
+struct AttnSmem {
+    float qs[G][D];
+    float hmax[GT][2][G];
+    float hsum[GT][2][G];
+    float ps[NWA][G][32];
+    float ho[NWA][G][D];
+};
+
+template <int D, int G>
+__global__ void __launch_bounds__(NWA * 32) attn_decode(const AttnArgs A) {
     constexpr int E = D / 32;  // dims a lane owns of an output row
     pdl_launch_dependents();
     pdl_wait();
     const int grp = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int Hq = A.Hq, Hk = A.Hk, T = A.T, G = Hq / Hk;
+    const int tile = warp >> 1, half = warp & 1;
+    const int Hq = A.Hq, Hk = A.Hk, T = A.T;
     const int n0 = *A.n0p;
 
     __shared__ int anc[TMAX];  // token t's path, root first
     __shared__ int s_len;
-    __shared__ float tm[GT][GMAX], tl[GT][GMAX];
     __shared__ int s_last_block;
-    // dynamic: the token's G queries, each warp's tile weights (bf16-rounded) and the tiles' outputs
-    extern __shared__ __align__(16) float dsm[];
-    float(*qs)[D] = reinterpret_cast<float(*)[D]>(dsm);                             // [G][D]
-    float(*ps)[BN] = reinterpret_cast<float(*)[BN]>(dsm + G * D);                   // [GT * G][BN]
-    float(*to)[D] = reinterpret_cast<float(*)[D]>(dsm + G * D + GT * G * BN);       // [GT * G][D]
+    extern __shared__ __align__(16) uint8_t dsm_raw[];
+    AttnSmem<D, G>& sm = *reinterpret_cast<AttnSmem<D, G>*>(dsm_raw);
 
     if (threadIdx.x == 0) {
         int len = 0;
@@ -102,139 +112,119 @@ __global__ void __launch_bounds__(GT * 32) attn_decode(const AttnArgs A) {
         if (last >= A.cap && threadIdx.x == 0 && grp == 0) b2_fail(B2_ERR_DOMAIN);
         return;  // the group holds none of the row's keys: nothing stored, nothing counted
     }
-    for (int i = threadIdx.x; i < G * D; i += GT * 32) {
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
         const int hh = i / D, d = i - hh * D;
-        qs[hh][d] = bf2f(A.q[((size_t)t * Hq + g * G + hh) * D + d]);
+        sm.qs[hh][d] = bf2f(A.q[((size_t)t * Hq + g * G + hh) * D + d]);
     }
     __syncthreads();
 
     const float scale2 = __fmul_rn(A.scale, LOG2E);
     const bf16* Kg = A.K + (size_t)g * A.hs;
     const bf16* Vg = A.V + (size_t)g * A.hs;
-    // ---- this warp's tile, a state from nothing ----------------------------------------------------------------
-    const int j0 = lo + warp * BN;
-    const bool tile_live = !(j0 > last || j0 + BN - 1 < first);
-    if (tile_live) {
-        int row[2];
-        float s[2][GMAX];
+    // ---- this warp's half of its tile: one key a lane ------------------------------------------------------------
+    const int j = lo + tile * BN + half * 32 + lane;
+    int row = -1;
+    if (j >= first && j <= last) {
+        int sl = j < n0 ? j : n0 + anc[j - n0];
+        if (A.tbl != nullptr) sl = A.tbl[sl];
+        row = sl;
+    }
+    float s[G];
+    {
+        // the key's whole row in flight at once (D/8 independent 16-byte loads), then the G dot products, each an
+        // f32 chain over the dims in index order
+        uint4 kv[D / 8];
+        const uint4* kr = reinterpret_cast<const uint4*>(Kg + (size_t)(row >= 0 ? row : 0) * A.rs);
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const int j = j0 + k * 32 + lane;
-            row[k] = -1;
-            if (j >= first && j <= last) {
-                int sl = j < n0 ? j : n0 + anc[j - n0];
-                if (A.tbl != nullptr) sl = A.tbl[sl];
-                row[k] = sl;
+        for (int c = 0; c < D / 8; ++c) kv[c] = row >= 0 ? __ldg(kr + c) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) s[hh] = 0.f;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
+                                 bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                float a = s[hh];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a = fmaf(kf[e], sm.qs[hh][c * 8 + e], a);
+                s[hh] = a;
             }
         }
+    }
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            // the key's whole row in flight at once (D/8 independent 16-byte loads), then the G dot products, each
-            // an f32 chain over the dims in index order
-            uint4 kv[D / 8];
-            const uint4* kr = reinterpret_cast<const uint4*>(Kg + (size_t)(row[k] >= 0 ? row[k] : 0) * A.rs);
+    for (int hh = 0; hh < G; ++hh) {
+        s[hh] = row >= 0 ? __fmul_rn(s[hh], scale2) : NEG_INF;
+        float m = s[hh];
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) kv[c] = row[k] >= 0 ? __ldg(kr + c) : make_uint4(0u, 0u, 0u, 0u);
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) sm.hmax[tile][half][hh] = m;
+    }
+    __syncthreads();
+    // the tile's weights against the tile's max (both halves'), this half's sum and its share of P . V
+    {
+        float o[G][E];
 #pragma unroll
-            for (int hh = 0; hh < GMAX; ++hh) s[k][hh] = 0.f;
+        for (int hh = 0; hh < G; ++hh) {
+            const float m = fmaxf(sm.hmax[tile][0][hh], sm.hmax[tile][1][hh]);
+            const float p = (m == NEG_INF || row < 0) ? 0.f : ex2(__fsub_rn(s[hh], m));
+            float l = p;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
-                const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
-                                     bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
-#pragma unroll
-                for (int hh = 0; hh < GMAX; ++hh) {
-                    if (hh < G) {
-                        float a = s[k][hh];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) a = fmaf(kf[e], qs[hh][c * 8 + e], a);
-                        s[k][hh] = a;
-                    }
-                }
-            }
-        }
-#pragma unroll
-        for (int hh = 0; hh < GMAX; ++hh) {
-            if (hh < G) {
-                float s0 = row[0] >= 0 ? __fmul_rn(s[0][hh], scale2) : NEG_INF;
-                float s1 = row[1] >= 0 ? __fmul_rn(s[1][hh], scale2) : NEG_INF;
-                float m = fmaxf(s0, s1);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                const float p0 = (m == NEG_INF || row[0] < 0) ? 0.f : ex2(__fsub_rn(s0, m));
-                const float p1 = (m == NEG_INF || row[1] < 0) ? 0.f : ex2(__fsub_rn(s1, m));
-                float l = __fadd_rn(p0, p1);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, o));
-                ps[warp * G + hh][lane] = bfround(p0);
-                ps[warp * G + hh][32 + lane] = bfround(p1);
-                if (lane == 0) {
-                    tm[warp][hh] = m;
-                    tl[warp][hh] = l;
-                }
-            }
-        }
-        __syncwarp();
-        // P . V: the lane's E dims of every head's output, the tile's keys in order
-        float o[GMAX][E];
-#pragma unroll
-        for (int hh = 0; hh < GMAX; ++hh)
+            for (int k = 16; k > 0; k >>= 1) l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, k));
+            sm.ps[warp][hh][lane] = bfround(p);
+            if (lane == 0) sm.hsum[tile][half][hh] = l;
 #pragma unroll
             for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
-        // sixteen keys' value runs in flight at a time; a key no row sees contributes weight 0 over zeros
+        }
+        __syncwarp();
+        // sixteen keys' value runs in flight at a time; a key the row does not see has weight 0 over zeros
         constexpr int VB = 16;
+#pragma unroll 1
+        for (int i0 = 0; i0 < 32; i0 += VB) {
+            float vf[VB][E];
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-#pragma unroll
-            for (int i0 = 0; i0 < 32; i0 += VB) {
-                float vf[VB][E];
-#pragma unroll
-                for (int u = 0; u < VB; ++u) {
-                    const int rk = __shfl_sync(0xffffffffu, row[k], i0 + u);
-                    const bf16* vr = Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
-                    if (E == 4) {
-                        const uint2 vv = rk >= 0 ? __ldg(reinterpret_cast<const uint2*>(vr)) : make_uint2(0u, 0u);
-                        vf[u][0] = bf_lo(vv.x), vf[u][1] = bf_hi(vv.x), vf[u][2] = bf_lo(vv.y), vf[u][3] = bf_hi(vv.y);
-                    } else {
-                        const uint32_t vv = rk >= 0 ? __ldg(reinterpret_cast<const uint32_t*>(vr)) : 0u;
-                        vf[u][0] = bf_lo(vv), vf[u][E - 1] = bf_hi(vv);
-                    }
+            for (int u = 0; u < VB; ++u) {
+                const int rk = __shfl_sync(0xffffffffu, row, i0 + u);
+                const bf16* vr = Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
+                if (E == 4) {
+                    const uint2 vv = rk >= 0 ? __ldg(reinterpret_cast<const uint2*>(vr)) : make_uint2(0u, 0u);
+                    vf[u][0] = bf_lo(vv.x), vf[u][1] = bf_hi(vv.x), vf[u][2] = bf_lo(vv.y), vf[u][3] = bf_hi(vv.y);
+                } else {
+                    const uint32_t vv = rk >= 0 ? __ldg(reinterpret_cast<const uint32_t*>(vr)) : 0u;
+                    vf[u][0] = bf_lo(vv), vf[u][E - 1] = bf_hi(vv);
                 }
+            }
 #pragma unroll
-                for (int u = 0; u < VB; ++u) {
+            for (int u = 0; u < VB; ++u) {
 #pragma unroll
-                    for (int hh = 0; hh < GMAX; ++hh) {
-                        if (hh < G) {
-                            const float p = ps[warp * G + hh][k * 32 + i0 + u];
+                for (int hh = 0; hh < G; ++hh) {
+                    const float p = sm.ps[warp][hh][i0 + u];
 #pragma unroll
-                            for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[u][e], o[hh][e]);
-                        }
-                    }
+                    for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[u][e], o[hh][e]);
                 }
             }
         }
 #pragma unroll
-        for (int hh = 0; hh < GMAX; ++hh)
-            if (hh < G)
+        for (int hh = 0; hh < G; ++hh)
 #pragma unroll
-                for (int e = 0; e < E; ++e) to[warp * G + hh][lane * E + e] = o[hh][e];
-    } else if (lane < GMAX) {
-        tm[warp][lane] = NEG_INF;
-        tl[warp][lane] = 0.f;
+            for (int e = 0; e < E; ++e) sm.ho[warp][hh][lane * E + e] = o[hh][e];
     }
     __syncthreads();
 
     // ---- the group's state: the tiles folded in tile order, a thread a run of (head, dim) elements -------------
     const int s_first = first / GK, s_last = last / GK;
     const bool single = s_first == s_last;
-    for (int i = threadIdx.x; i < G * D; i += GT * 32) {
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
         const int hh = i / D, d = i - hh * D;
         float M = NEG_INF, L = 0.f, O = 0.f;
         for (int w = 0; w < GT; ++w) {
-            const float m = tm[w][hh];
+            const float m = fmaxf(sm.hmax[w][0][hh], sm.hmax[w][1][hh]);
             if (m == NEG_INF) continue;  // an empty tile changes nothing
+            const float l = __fadd_rn(sm.hsum[w][0][hh], sm.hsum[w][1][hh]);
+            const float o = __fadd_rn(sm.ho[2 * w][hh][d], sm.ho[2 * w + 1][hh][d]);
             float cO, co;
-            fold_ml(M, L, m, tl[w][hh], cO, co);
-            O = fold_e(O, to[w * G + hh][d], cO, co);
+            fold_ml(M, L, m, l, cO, co);
+            O = fold_e(O, o, cO, co);
         }
         const size_t rowi = (size_t)t * Hq + g * G + hh;
         if (single) {
@@ -261,7 +251,7 @@ __global__ void __launch_bounds__(GT * 32) attn_decode(const AttnArgs A) {
     __syncthreads();
     if (!s_last_block) return;
     __threadfence();
-    for (int i = threadIdx.x; i < G * D; i += GT * 32) {
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
         const int hh = i / D, d = i - hh * D;
         const size_t rowi = (size_t)t * Hq + g * G + hh;
         float M = NEG_INF, L = 0.f, O = 0.f;
@@ -281,6 +271,25 @@ __global__ void __launch_bounds__(GT * 32) attn_decode(const AttnArgs A) {
     if (threadIdx.x == 0) A.cnt[(size_t)t * Hk + g] = 0;
 }
 
+template <int D, int G>
+int launch_attn(const AttnArgs& a, dim3 grid, cudaStream_t s) {
+    auto kern = attn_decode<D, G>;
+    static bool allowed[64];
+    int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
+    if (rc) return rc;
+    return b2_launch(reinterpret_cast<const void*>(kern), grid, dim3(NWA * 32), sizeof(AttnSmem<D, G>), s, a);
+}
+template <int D>
+int launch_attn_g(int G, const AttnArgs& a, dim3 grid, cudaStream_t s) {
+    switch (G) {
+        case 1: return launch_attn<D, 1>(a, grid, s);
+        case 2: return launch_attn<D, 2>(a, grid, s);
+        case 4: return launch_attn<D, 4>(a, grid, s);
+        case 8: return launch_attn<D, 8>(a, grid, s);
+        default: return B2_ERR_DOMAIN;
+    }
+}
+
 }  // namespace
 
 extern "C" size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D) {
@@ -292,7 +301,7 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
                                     float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
                                     const void* tbl, const void* sinks, int cap, void* stream) {
     if (!q || !K || !V || !out || !n0p || !par || !part_m || !part_l || !part_acc || !cnt) return B2_ERR_NULL;
-    if (T <= 0 || T > TMAX || Hk <= 0 || Hq <= 0 || Hq % Hk || Hq / Hk > GMAX || cap <= 0 || !(scale == scale))
+    if (T <= 0 || T > TMAX || Hk <= 0 || Hq <= 0 || Hq % Hk || (Hq / Hk != 1 && Hq / Hk != 2 && Hq / Hk != 4 && Hq / Hk != 8) || cap <= 0 || !(scale == scale))
         return B2_ERR_DOMAIN;
     // a key row is read as 16-byte chunks, a value row as D/32-element runs
     if ((hs & 7) || (rs & 7) || (reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15))
@@ -306,13 +315,10 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
     a.scale = scale, a.T = T, a.Hq = Hq, a.Hk = Hk, a.win = win, a.cap = cap, a.hs = hs, a.rs = rs;
     const int S = (cap + GK - 1) / GK;
     const dim3 grid(S, Hk, T);
-    const int G = Hq / Hk;
-    const size_t smem = sizeof(float) * ((size_t)G * D + (size_t)GT * G * BN + (size_t)GT * G * D);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    static bool allowed[2][64];
-    const void* kern = D == 64 ? (const void*)attn_decode<64> : D == 128 ? (const void*)attn_decode<128> : nullptr;
-    if (kern == nullptr) return B2_ERR_DOMAIN;
-    int rc = b2_allow_smem(kern, allowed[D == 128]);
-    if (rc) return rc;
-    return b2_launch(kern, grid, dim3(GT * 32), smem, s, a);
+    switch (D) {
+        case 64: return launch_attn_g<64>(Hq / Hk, a, grid, s);
+        case 128: return launch_attn_g<128>(Hq / Hk, a, grid, s);
+        default: return B2_ERR_DOMAIN;
+    }
 }

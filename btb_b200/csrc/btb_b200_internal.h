@@ -15,6 +15,7 @@ struct B2Tuning {
     int ctas_per_sm;  // GEMV CTAs an SM (the grid is persistent)
     int evict_first;  // weight copies carry an L2 evict-first hint
     int pdl;          // launch with programmatic stream serialization
+    int warps;        // warps a GEMV CTA for passes of one or two rows: 8 or 16
 };
 B2Tuning& b2_tuning();
 int b2_sm_count();

@@ -14,6 +14,7 @@ B2Tuning& b2_tuning() {
         env_int("BTB_B200_RING_BYTES", 96 * 1024), env_int("BTB_B200_SEG_BYTES", 4096),
         env_int("BTB_B200_X_SMEM_MAX", 64 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
         env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 0),
+        env_int("BTB_B200_WARPS", 16),
     };
     return t;
 }
@@ -43,6 +44,7 @@ extern "C" int btb_b200_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "ctas_per_sm")) t.ctas_per_sm = value;
     else if (!strcmp(key, "evict_first")) t.evict_first = value;
     else if (!strcmp(key, "pdl")) t.pdl = value;
+    else if (!strcmp(key, "warps")) t.warps = value == 16 ? 16 : 8;
     else return B2_ERR_DOMAIN;
     return B2_OK;
 }

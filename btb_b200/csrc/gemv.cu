@@ -22,8 +22,7 @@ B2_DEFINE_STATUS(gemv)
 
 namespace {
 
-constexpr int NW = 8;             // warps a CTA, a ring each
-constexpr int THREADS = NW * 32;  // 256
+// warps a CTA, a ring each: 8 or 16 (the tunable `warps`)
 
 enum Fmt { F_BF16 = 0, F_P12 = 1 };
 enum XMode { X_SMEM = 0, X_SMEM_SILU = 1, X_GLOBAL = 2, X_SMEM_NORM = 3 };
@@ -93,29 +92,30 @@ __device__ __noinline__ uint32_t p12_escape(const int32_t* __restrict__ esc_idx,
     return a < e1 ? (uint32_t)__ldg(esc_val + a) : 0u;  // never past the row's run, whatever the list holds
 }
 
-template <int M, int FMT, int XM>
-__global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
+template <int M, int FMT, int XM, int NWT>
+__global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int NT = NWT * 32;
     const int R = A.R, C = A.C, seg = A.seg, S = A.stages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nseg = (C + seg - 1) / seg;
     constexpr bool XS = XM != X_GLOBAL;
 
-    // shared memory: [x: M*C bf16 when staged][rings: NW * S stages][barriers: NW * S]
+    // shared memory: [norm scratch][x: M*C bf16 when staged][rings: NWT * S stages][barriers: NWT * S]
     // (the norm prologue adds one f32 row of h and the 256 partial sums in front)
-    const int nbytes = XM == X_SMEM_NORM ? ((C * 4 + THREADS * 4 + 127) & ~127) : 0;
+    const int nbytes = XM == X_SMEM_NORM ? ((C * 4 + 256 * 4 + 127) & ~127) : 0;
     const int xbytes = (XS ? ((M * C * 2 + 127) & ~127) : 0) + nbytes;
     const int sbytes = (stage_bytes<FMT>(seg) + 127) & ~127;
     bf16* xs = reinterpret_cast<bf16*>(smem + nbytes);
     uint8_t* ring = smem + xbytes + (size_t)warp * S * sbytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + xbytes + (size_t)NW * S * sbytes) + warp * S;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + xbytes + (size_t)NWT * S * sbytes) + warp * S;
 
     // this CTA's rows [r0, r0 + cnt): an even split, the remainder one extra row to the first CTAs
     const int base = R / gridDim.x, rem = R % gridDim.x;
     const int r0 = blockIdx.x * base + min((int)blockIdx.x, rem);
     const int cnt = base + ((int)blockIdx.x < rem ? 1 : 0);
-    // this warp's rows: r0 + warp, + NW, ..; its items are (row, segment) pairs in order
-    const int my_rows = cnt > warp ? (cnt - warp + NW - 1) / NW : 0;
+    // this warp's rows: r0 + warp, + NWT, ..; its items are (row, segment) pairs in order
+    const int my_rows = cnt > warp ? (cnt - warp + NWT - 1) / NWT : 0;
     const int n_items = my_rows * nseg;
 
     if (lane == 0) {
@@ -125,32 +125,42 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
     __syncwarp();
 
     const uint64_t pol = A.evict_first ? l2_evict_first_policy() : 0;
-    auto issue = [&](int i) {  // lane 0 only
-        const int row = r0 + warp + NW * (i / nseg);
-        const int c0 = (i % nseg) * seg;
+    // the producer's cursor: the next item to copy (kept by every lane, issued by lane 0); no division on the way
+    int p_row = r0 + warp, p_seg = 0, p_st = 0, issued = 0;
+    auto issue_next = [&]() {
+        const int c0 = p_seg * seg;
         const int n = min(seg, C - c0);
-        const int st = i % S;
-        const uint32_t bar = smem_u32(bars + st);
-        const uint32_t dst = smem_u32(ring + (size_t)st * sbytes);
-        const size_t e0 = (size_t)row * C + c0;
-        if (FMT == F_BF16) {
-            mbar_expect_tx(bar, n * 2);
-            if (A.evict_first) bulk_g2s_hint(dst, A.w + e0 * 2, n * 2, bar, pol);
-            else bulk_g2s(dst, A.w + e0 * 2, n * 2, bar);
-        } else {
-            mbar_expect_tx(bar, n + n / 2);
-            if (A.evict_first) {
-                bulk_g2s_hint(dst, A.w + e0, n, bar, pol);
-                bulk_g2s_hint(dst + seg, A.hi4 + e0 / 2, n / 2, bar, pol);
+        if (lane == 0) {
+            const uint32_t bar = smem_u32(bars + p_st);
+            const uint32_t dst = smem_u32(ring + (size_t)p_st * sbytes);
+            const size_t e0 = (size_t)p_row * C + c0;
+            if (FMT == F_BF16) {
+                mbar_expect_tx(bar, n * 2);
+                if (A.evict_first) bulk_g2s_hint(dst, A.w + e0 * 2, n * 2, bar, pol);
+                else bulk_g2s(dst, A.w + e0 * 2, n * 2, bar);
             } else {
-                bulk_g2s(dst, A.w + e0, n, bar);
-                bulk_g2s(dst + seg, A.hi4 + e0 / 2, n / 2, bar);
+                mbar_expect_tx(bar, n + n / 2);
+                if (A.evict_first) {
+                    bulk_g2s_hint(dst, A.w + e0, n, bar, pol);
+                    bulk_g2s_hint(dst + seg, A.hi4 + e0 / 2, n / 2, bar, pol);
+                } else {
+                    bulk_g2s(dst, A.w + e0, n, bar);
+                    bulk_g2s(dst + seg, A.hi4 + e0 / 2, n / 2, bar);
+                }
             }
+        }
+        ++issued;
+        if (++p_st == S) p_st = 0;
+        if (++p_seg == nseg) {
+            p_seg = 0;
+            p_row += NWT;
         }
     };
     // fill the ring: weights do not depend on the grids before this one
-    if (lane == 0)
-        for (int i = 0; i < min(S, n_items); ++i) issue(i);
+    {
+        const int first = min(S, n_items);
+        for (int i = 0; i < first; ++i) issue_next();
+    }
 
     pdl_launch_dependents();
     pdl_wait();  // x is the previous kernel's output
@@ -159,12 +169,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
         if (XM == X_SMEM) {
             const uint4* src = reinterpret_cast<const uint4*>(A.x);
             uint4* dst = reinterpret_cast<uint4*>(xs);
-            for (int i = threadIdx.x; i < M * C / 8; i += THREADS) dst[i] = __ldg(src + i);
+            for (int i = threadIdx.x; i < M * C / 8; i += NT) dst[i] = __ldg(src + i);
         } else if (XM == X_SMEM_SILU) {
             // x[m][c] = bf16(bf16(silu(g)) * u), gu [M, 2C] gate then up: the values btb_silu_mul would have written;
             // eight elements a thread a trip (16-byte loads), elementwise so the order is free
             const int cv = C >> 3;
-            for (int i = threadIdx.x; i < M * cv; i += THREADS) {
+            for (int i = threadIdx.x; i < M * cv; i += NT) {
                 const int m = i / cv, c8 = i - m * cv;
                 const uint4 gv = __ldg(reinterpret_cast<const uint4*>(A.x + (size_t)m * 2 * C) + c8);
                 const uint4 uv = __ldg(reinterpret_cast<const uint4*>(A.x + (size_t)m * 2 * C + C) + c8);
@@ -189,11 +199,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
             const int cv = C >> 3, tid = threadIdx.x;
             for (int m = 0; m < M; ++m) {
                 if (m >= A.T) {  // a padding row: zeros
-                    for (int i = tid; i < cv; i += THREADS)
+                    for (int i = tid; i < cv; i += NT)
                         reinterpret_cast<uint4*>(xs + (size_t)m * C)[i] = make_uint4(0u, 0u, 0u, 0u);
                     continue;
                 }
-                for (int i = tid; i < cv; i += THREADS) {
+                for (int i = tid; i < cv; i += NT) {
                     const uint4 hv = __ldg(reinterpret_cast<const uint4*>(A.h_in + (size_t)m * C) + i);
                     uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
                     if (A.y_add != nullptr) {
@@ -215,16 +225,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
                     }
                 }
                 __syncthreads();
-                float ss = 0.f;
-                for (int i = tid; i < C; i += THREADS) ss = fmaf(hsm[i], hsm[i], ss);
-                red[tid] = ss;
+                if (tid < 256) {  // the reference's 256 strided partial sums, whatever the block's width
+                    float ss = 0.f;
+                    for (int i = tid; i < C; i += 256) ss = fmaf(hsm[i], hsm[i], ss);
+                    red[tid] = ss;
+                }
                 __syncthreads();
-                for (int st = THREADS / 2; st > 0; st >>= 1) {
+                for (int st = 128; st > 0; st >>= 1) {
                     if (tid < st) red[tid] += red[tid + st];
                     __syncthreads();
                 }
                 const float rstd = rsqrtf(red[0] / (float)C + A.eps);
-                for (int i = tid; i < C; i += THREADS) {
+                for (int i = tid; i < C; i += NT) {
                     const float wv = bf2f(A.norm_w[i]);
                     xs[(size_t)m * C + i] = f2bf(hsm[i] * rstd * (A.centered ? 1.f + wv : wv));
                 }
@@ -238,25 +250,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.f;
     bool ok = true;
+    // the consumer's cursor
+    int c_row = r0 + warp, c_seg = 0, c_st = 0;
+    uint32_t c_par = 0;
     int i = 0;
     for (; i < n_items; ++i) {
-        const int st = i % S;
-        const uint32_t bar = smem_u32(bars + st);
-        if (!mbar_wait_bounded(bar, (uint32_t)(i / S) & 1u)) {
+        if (!mbar_wait_bounded(smem_u32(bars + c_st), c_par)) {
             ok = false;
             break;
         }
-        const int rr = i / nseg, sg = i - rr * nseg;
-        const int row = r0 + warp + NW * rr;
-        const int c0 = sg * seg;
+        const int row = c_row;
+        const int c0 = c_seg * seg;
         const int nch = min(seg, C - c0) >> 3;  // the segment's chunks; its first chunk is global chunk c0 / 8
-        const uint8_t* stg = ring + (size_t)st * sbytes;
+        const uint8_t* stg = ring + (size_t)c_st * sbytes;
         int e0 = 0, e1 = 0;
         if (FMT == F_P12 && A.esc_row != nullptr) {
             e0 = __ldg(A.esc_row + row);
             e1 = __ldg(A.esc_row + row + 1);
         }
-#pragma unroll 2
+#pragma unroll 4
         for (int lc = lane; lc < nch; lc += 32) {
             uint32_t wp[4];
             if (FMT == F_BF16) {
@@ -266,7 +278,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
                 const uint2 lo = *reinterpret_cast<const uint2*>(stg + lc * 8);
                 const uint32_t codes = *reinterpret_cast<const uint32_t*>(stg + seg + lc * 4);
                 p12_chunk(lo.x, lo.y, codes, A.table, wp);
-                // a code of 15 is an escape: its high byte comes from the row's list (rare: a handful a row)
+                // a code of 15 is an escape: its high byte comes from the row's list
                 const uint32_t f = codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u;
                 if (f != 0u && e1 > e0) {
 #pragma unroll
@@ -297,34 +309,45 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_stream(const GemvArgs A) {
                 acc[m] = a;
             }
         }
-        // the stage is free once every lane has read it: refill it with the item S ahead
+        // the stage is free once every lane has read it (the warp barrier orders their shared loads before the
+        // elected lane's copy, as a consumer's release orders them in any TMA pipeline): refill it with the next item
         __syncwarp();
-        if (lane == 0 && i + S < n_items) {
-            fence_proxy_async();
-            issue(i + S);
-        }
-        if (sg == nseg - 1) {
+        if (issued < n_items) issue_next();
+        if (c_seg == nseg - 1) {
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 const float s = warp_sum(acc[m]);
                 if (lane == 0) A.y[(size_t)m * R + row] = f2bf(s);
                 acc[m] = 0.f;
             }
+            c_seg = 0;
+            c_row += NWT;
+        } else {
+            ++c_seg;
+        }
+        if (++c_st == S) {
+            c_st = 0;
+            c_par ^= 1u;
         }
     }
     if (!ok) {
         // a copy never landed: say so, then let the copies still in flight land (bounded) before the CTA's shared
         // memory goes away
         if (lane == 0) b2_fail(B2_ERR_TIMEOUT);
-        const int last = min(n_items, i + S);
-        for (int j = i + 1; j < last; ++j) mbar_wait_bounded(smem_u32(bars + j % S), (uint32_t)(j / S) & 1u);
+        for (int j = i + 1; j < issued; ++j) {
+            if (++c_st == S) {
+                c_st = 0;
+                c_par ^= 1u;
+            }
+            mbar_wait_bounded(smem_u32(bars + c_st), c_par);
+        }
     }
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------------
 
 struct Plan {
-    int grid, seg, stages, smem;
+    int grid, seg, stages, smem, nw;
     bool xs;
 };
 
@@ -334,7 +357,10 @@ template <int FMT>
 Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     const B2Tuning& t = b2_tuning();
     Plan p;
-    const int xbytes = ((M * C * 2 + 127) & ~127) + (norm ? ((C * 4 + THREADS * 4 + 127) & ~127) : 0);
+    // wide passes keep 8 warps (their accumulators fill the register file); the narrow ones take the tunable
+    const int NW = (M <= 2 && t.warps == 16) ? 16 : 8;
+    p.nw = NW;
+    const int xbytes = ((M * C * 2 + 127) & ~127) + (norm ? ((C * 4 + 256 * 4 + 127) & ~127) : 0);
     p.xs = want_xs && (M * C * 2) <= t.x_smem_max;
     const int ring = t.ring_bytes;
     int per_warp = ring / NW;
@@ -355,13 +381,18 @@ Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     return p;
 }
 
-template <int M, int FMT, int XM>
-int launch_one(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
-    auto kern = gemv_stream<M, FMT, XM>;
+template <int M, int FMT, int XM, int NWT>
+int launch_nw(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
+    auto kern = gemv_stream<M, FMT, XM, NWT>;
     static bool allowed[64];  // the opt-in past 48 KB of dynamic shared memory, once a device
     int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
     if (rc) return rc;
-    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.grid), dim3(THREADS), p.smem, stream, a);
+    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.grid), dim3(NWT * 32), p.smem, stream, a);
+}
+template <int M, int FMT, int XM>
+int launch_one(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
+    if (M <= 2 && p.nw == 16) return launch_nw<M, FMT, XM, (M <= 2 ? 16 : 8)>(a, p, stream);
+    return launch_nw<M, FMT, XM, 8>(a, p, stream);
 }
 
 template <int FMT, int XM>

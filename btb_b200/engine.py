@@ -263,7 +263,7 @@ class CardEngine:
               ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             normed_matvec(L.gu, L.ln2, g["y"], g["gu"], 2 * I)
-            if self.silu_fold and M * I * 2 <= 64 * 1024:
+            if self.silu_fold and M <= 8 and M * I * 2 <= 64 * 1024:
                 if isinstance(L.down, P12Matrix):
                     W = L.down
                     k("btb_b200_gemv_silu_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),
