@@ -14,16 +14,17 @@ struct B2Tuning {
     int x_smem_max;   // x is staged in shared memory when M * C * 2 is at most this
     int ctas_per_sm;  // GEMV CTAs an SM (the grid is persistent)
     int evict_first;  // weight copies carry an L2 evict-first hint
-    int pdl;          // launch with programmatic stream serialization
+    int pdl;          // programmatic stream serialization: bit 0 the GEMV launches, bit 1 the small kernels
     int warps;        // warps a GEMV CTA for passes of one or two rows: 8 or 16
 };
 B2Tuning& b2_tuning();
 int b2_sm_count();
 
 // one launch: `args` is the kernel's single by-value parameter struct
+// `kind`: 1 a GEMV, 2 one of the step's small kernels - the `pdl` tunable is a mask over the kinds
 template <typename Args>
 static inline int b2_launch(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                            const Args& args) {
+                            const Args& args, int kind = 2) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = grid;
@@ -31,7 +32,7 @@ static inline int b2_launch(const void* kern, dim3 grid, dim3 block, size_t smem
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute at[1];
-    if (b2_tuning().pdl) {
+    if (b2_tuning().pdl & kind) {
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;

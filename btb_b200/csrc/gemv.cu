@@ -366,15 +366,25 @@ Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     int per_warp = ring / NW;
     int max_seg_el = t.seg_bytes / (FMT == F_BF16 ? 2 : 1);  // elements
     max_seg_el = max(256, max_seg_el & ~255);
-    const int nseg = (C + max_seg_el - 1) / max_seg_el;
-    int seg = (C + nseg - 1) / nseg;
-    seg = (seg + 255) & ~255;
-    p.seg = seg;
-    const int sb = (stage_bytes<FMT>(seg) + 127) & ~127;
-    p.stages = max(2, min(8, per_warp / sb));
+    int sb = 0;
     auto total = [&](int st) { return (p.xs ? xbytes : 0) + NW * st * sb + NW * st * 8; };
-    while (p.stages > 2 && total(p.stages) > 224 * 1024) --p.stages;
-    if (total(p.stages) > 224 * 1024) p.xs = false;  // a very wide x gives its shared memory back to the ring
+    for (;;) {
+        const int nseg = (C + max_seg_el - 1) / max_seg_el;
+        int seg = (C + nseg - 1) / nseg;
+        seg = (seg + 255) & ~255;
+        p.seg = seg;
+        sb = (stage_bytes<FMT>(seg) + 127) & ~127;
+        p.stages = max(2, min(8, per_warp / sb));
+        while (p.stages > 2 && total(p.stages) > 224 * 1024) --p.stages;
+        if (total(p.stages) <= 224 * 1024) break;
+        if (max_seg_el > 256) {
+            max_seg_el = max(256, (max_seg_el / 2) & ~255);  // two stages of this size do not fit: halve the segment
+        } else if (p.xs) {
+            p.xs = false;  // a very wide x gives its shared memory back to the ring
+        } else {
+            break;
+        }
+    }
     p.smem = total(p.stages);
     const int sms = b2_sm_count();
     p.grid = max(1, min(sms * t.ctas_per_sm, (R + 1) / 2));
@@ -387,7 +397,7 @@ int launch_nw(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
     static bool allowed[64];  // the opt-in past 48 KB of dynamic shared memory, once a device
     int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
     if (rc) return rc;
-    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.grid), dim3(NWT * 32), p.smem, stream, a);
+    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.grid), dim3(NWT * 32), p.smem, stream, a, 1);
 }
 template <int M, int FMT, int XM>
 int launch_one(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
