@@ -57,6 +57,9 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_argmax_bf16": (_I, [_P, _I, _I, _P, _P, _P]),
     "btb_b200_argmax_scratch_bytes": (_SZ, [_I]),
     "btb_b200_publish": (_I, [_P, _P, _P, _P, _P, _I, _P]),
+    "btb_b200_step": (_I, [_P, _I, _I, _I, _P]),
+    "btb_b200_step_op_bytes": (_SZ, []),
+    "btb_b200_step_args_bytes": (_SZ, []),
 }  # fmt: skip
 
 _lib: C.CDLL | None = None

@@ -1,0 +1,332 @@
+// The decode attention's arithmetic and the q/k-norm + RoPE + cache-write arithmetic as device functions, shared by
+// the standalone kernels (attn.cu, layer.cu) and the whole-step kernel (step.cu).
+#pragma once
+
+#include "common.cuh"
+
+
+constexpr int BN = 64;        // keys a tile
+constexpr int GT = 8;         // tiles a group: one a warp
+constexpr int GK = BN * GT;   // keys a group
+constexpr int TMAX = 32;      // rows a pass at most
+#define LOG2E 1.4426950408889634f
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// a state (m, l) folded into the running (M, L): each side scaled to the larger max, the larger side's factor
+// exactly 1; an empty side (max -inf) contributes nothing. Returns the factors for the outputs' fold.
+__device__ __forceinline__ void fold_ml(float& M, float& L, float m, float l, float& cO, float& co) {
+    const bool em = m == NEG_INF, eM = M == NEG_INF;
+    const float hi = fmaxf(M, m), lo = fminf(M, m);
+    const float e = ex2(em || eM ? 0.f : __fsub_rn(lo, hi));
+    cO = em ? 1.f : eM ? 0.f : (M >= m ? 1.f : e);
+    co = em ? 0.f : eM ? 1.f : (M > m ? e : 1.f);
+    L = __fmaf_rn(l, co, __fmul_rn(L, cO));
+    M = hi;
+}
+__device__ __forceinline__ float fold_e(float O, float o, float cO, float co) {
+    return __fmaf_rn(o, co, __fmul_rn(O, cO));
+}
+
+struct AttnArgs {
+    const bf16* q;    // [T, Hq, D]
+    const bf16* K;    // head g, slot j at g * hs + j * rs
+    const bf16* V;
+    bf16* out;        // [T, Hq * D]
+    const int* n0p;   // rows standing before the pass
+    const int* par;   // [T] parents, -1 the root
+    const int* tbl;   // logical slot -> cache row, or null
+    const float* sinks;  // [Hq] a logit joined to the denominator, or null
+    float* part_m;    // [S, T, Hq]
+    float* part_l;
+    float* part_acc;  // [S, T, Hq, D]
+    int* cnt;         // [T, Hk] arrivals, zero between launches
+    float scale;
+    int T, Hq, Hk, win, cap;
+    long long hs, rs;
+};
+
+constexpr int NWA = 2 * GT;  // warps a block: two a tile, 32 keys each (a lane one key)
+
+// The block's shared memory (dynamic): the token's queries, the half-tiles' maxima and sums, each warp's weights
+// (bf16-rounded) and each warp's partial outputs.
+template <int D, int G>
+struct AttnSmem {
+    float qs[G][D];
+    float hmax[GT][2][G];
+    float hsum[GT][2][G];
+    float ps[NWA][G][32];
+    float ho[NWA][G][D];
+};
+
+// one block's work: group grp of kv head g for row t. COHERENT: q and the cache are read with L2-coherent loads
+// (the whole-step kernel, where other SMs wrote them earlier in the same launch).
+template <int D, int G, bool COHERENT>
+__device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int t, uint8_t* dsm_raw) {
+    constexpr int E = D / 32;  // dims a lane owns of an output row
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = warp >> 1, half = warp & 1;
+    const int Hq = A.Hq, Hk = A.Hk, T = A.T;
+    const int n0 = COHERENT ? __ldcg(A.n0p) : *A.n0p;
+
+    __shared__ int anc[TMAX];  // token t's path, root first
+    __shared__ int s_len;
+    __shared__ int s_last_block;
+    AttnSmem<D, G>& sm = *reinterpret_cast<AttnSmem<D, G>*>(dsm_raw);
+
+    __syncthreads();  // the block's previous item is done with the shared state
+    if (threadIdx.x == 0) {
+        int len = 0;
+        for (int p = t; p >= 0 && p < T && len < TMAX; p = A.par[p]) ++len;
+        int k = len;
+        for (int p = t; k > 0; p = A.par[p]) anc[--k] = p;
+        s_len = len;
+    }
+    __syncthreads();
+    const int last = n0 + s_len - 1;
+    const int first = A.win > 0 ? max(last + 1 - A.win, 0) : 0;
+    const int lo = grp * GK, hi = lo + GK - 1;
+    if (lo > last || hi < first || last >= A.cap) {
+        if (last >= A.cap && threadIdx.x == 0 && grp == 0) b2_fail(B2_ERR_DOMAIN);
+        return;  // the group holds none of the row's keys: nothing stored, nothing counted
+    }
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
+        const int hh = i / D, d = i - hh * D;
+        const bf16* qp = A.q + ((size_t)t * Hq + g * G + hh) * D + d;
+        sm.qs[hh][d] = COHERENT ? __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(qp)) << 16) : bf2f(*qp);
+    }
+    __syncthreads();
+
+    const float scale2 = __fmul_rn(A.scale, LOG2E);
+    const bf16* Kg = A.K + (size_t)g * A.hs;
+    const bf16* Vg = A.V + (size_t)g * A.hs;
+    // ---- this warp's half of its tile: one key a lane ------------------------------------------------------------
+    const int j = lo + tile * BN + half * 32 + lane;
+    int row = -1;
+    if (j >= first && j <= last) {
+        int sl = j < n0 ? j : n0 + anc[j - n0];
+        if (A.tbl != nullptr) sl = A.tbl[sl];
+        row = sl;
+    }
+    float s[G];
+    {
+        // the key's whole row in flight at once (D/8 independent 16-byte loads), then the G dot products, each an
+        // f32 chain over the dims in index order
+        uint4 kv[D / 8];
+        const uint4* kr = reinterpret_cast<const uint4*>(Kg + (size_t)(row >= 0 ? row : 0) * A.rs);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) kv[c] = row >= 0 ? (COHERENT ? __ldcg(kr + c) : __ldg(kr + c)) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) s[hh] = 0.f;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
+                                 bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                float a = s[hh];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a = fmaf(kf[e], sm.qs[hh][c * 8 + e], a);
+                s[hh] = a;
+            }
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        s[hh] = row >= 0 ? __fmul_rn(s[hh], scale2) : NEG_INF;
+        float m = s[hh];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) sm.hmax[tile][half][hh] = m;
+    }
+    __syncthreads();
+    // the tile's weights against the tile's max (both halves'), this half's sum and its share of P . V
+    {
+        float o[G][E];
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            const float m = fmaxf(sm.hmax[tile][0][hh], sm.hmax[tile][1][hh]);
+            const float p = (m == NEG_INF || row < 0) ? 0.f : ex2(__fsub_rn(s[hh], m));
+            float l = p;
+#pragma unroll
+            for (int k = 16; k > 0; k >>= 1) l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, k));
+            sm.ps[warp][hh][lane] = bfround(p);
+            if (lane == 0) sm.hsum[tile][half][hh] = l;
+#pragma unroll
+            for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
+        }
+        __syncwarp();
+        // sixteen keys' value runs in flight at a time; a key the row does not see has weight 0 over zeros
+        constexpr int VB = 16;
+#pragma unroll 1
+        for (int i0 = 0; i0 < 32; i0 += VB) {
+            float vf[VB][E];
+#pragma unroll
+            for (int u = 0; u < VB; ++u) {
+                const int rk = __shfl_sync(0xffffffffu, row, i0 + u);
+                const bf16* vr = Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
+                if (E == 4) {
+                    const uint2 vv = rk >= 0 ? (COHERENT ? __ldcg(reinterpret_cast<const uint2*>(vr)) : __ldg(reinterpret_cast<const uint2*>(vr)))
+                                             : make_uint2(0u, 0u);
+                    vf[u][0] = bf_lo(vv.x), vf[u][1] = bf_hi(vv.x), vf[u][2] = bf_lo(vv.y), vf[u][3] = bf_hi(vv.y);
+                } else {
+                    const uint32_t vv = rk >= 0 ? (COHERENT ? __ldcg(reinterpret_cast<const uint32_t*>(vr)) : __ldg(reinterpret_cast<const uint32_t*>(vr)))
+                                            : 0u;
+                    vf[u][0] = bf_lo(vv), vf[u][E - 1] = bf_hi(vv);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < VB; ++u) {
+#pragma unroll
+                for (int hh = 0; hh < G; ++hh) {
+                    const float p = sm.ps[warp][hh][i0 + u];
+#pragma unroll
+                    for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[u][e], o[hh][e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh)
+#pragma unroll
+            for (int e = 0; e < E; ++e) sm.ho[warp][hh][lane * E + e] = o[hh][e];
+    }
+    __syncthreads();
+
+    // ---- the group's state: the tiles folded in tile order, a thread a run of (head, dim) elements -------------
+    const int s_first = first / GK, s_last = last / GK;
+    const bool single = s_first == s_last;
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
+        const int hh = i / D, d = i - hh * D;
+        float M = NEG_INF, L = 0.f, O = 0.f;
+        for (int w = 0; w < GT; ++w) {
+            const float m = fmaxf(sm.hmax[w][0][hh], sm.hmax[w][1][hh]);
+            if (m == NEG_INF) continue;  // an empty tile changes nothing
+            const float l = __fadd_rn(sm.hsum[w][0][hh], sm.hsum[w][1][hh]);
+            const float o = __fadd_rn(sm.ho[2 * w][hh][d], sm.ho[2 * w + 1][hh][d]);
+            float cO, co;
+            fold_ml(M, L, m, l, cO, co);
+            O = fold_e(O, o, cO, co);
+        }
+        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        if (single) {
+            if (A.sinks != nullptr) {
+                float cO, co;
+                fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+                O = __fmul_rn(O, cO);
+            }
+            A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+        } else {
+            const size_t idx = (size_t)grp * T * Hq + rowi;
+            if (d == 0) {
+                A.part_m[idx] = M;
+                A.part_l[idx] = L;
+            }
+            A.part_acc[idx * D + d] = O;
+        }
+    }
+    if (single) return;
+    // ---- several groups: count this block in; the last one folds the row's groups in group order ----------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last_block = atomicAdd(A.cnt + (size_t)t * Hk + g, 1) == s_last - s_first ? 1 : 0;
+    __syncthreads();
+    if (!s_last_block) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
+        const int hh = i / D, d = i - hh * D;
+        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        float M = NEG_INF, L = 0.f, O = 0.f;
+        for (int sp = s_first; sp <= s_last; ++sp) {
+            const size_t iu = (size_t)sp * T * Hq + rowi;
+            float cO, co;
+            fold_ml(M, L, __ldcg(A.part_m + iu), __ldcg(A.part_l + iu), cO, co);
+            O = fold_e(O, __ldcg(A.part_acc + iu * D + d), cO, co);
+        }
+        if (A.sinks != nullptr) {
+            float cO, co;
+            fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+            O = __fmul_rn(O, cO);
+        }
+        A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+    }
+    if (threadIdx.x == 0) A.cnt[(size_t)t * Hk + g] = 0;
+}
+
+// ---- q/k RMSNorm + RoPE + cache write (btb_kernels.cu:261-327) -----------------------------------------------------
+// One warp per (head, row): lane l holds dims l*E .. l*E+E-1, so rotate_half's partner is lane ^ 16.
+struct RopeArgs {
+    const bf16* qkv;
+    const bf16* wq;
+    const bf16* wk;
+    const bf16* cos_t;
+    const bf16* sin_t;
+    const int* n0p;
+    const int* depth;
+    const int* tbl;
+    bf16* K;
+    bf16* V;
+    bf16* qo;
+    float eps;
+    int T, Hq, Hk, centered;
+    long long hs, rs;
+    int cap;  // cache rows: a slot at or past it is refused
+};
+template <int D, bool COHERENT>
+__device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, int lane) {
+    constexpr int E = D / 32;
+    auto ld_bf = [](const bf16* p) -> bf16 {
+        if (!COHERENT) return *p;
+        const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(p));
+        return *reinterpret_cast<const bf16*>(&u);
+    };
+    const int n0 = COHERENT ? __ldcg(A.n0p) : *A.n0p;
+    int slot = n0 + t;
+    const int pos = n0 + A.depth[t];
+    if (slot < 0 || slot >= A.cap || pos < 0 || pos >= A.cap) {
+        if (lane == 0) b2_fail(B2_ERR_DOMAIN);
+        return;
+    }
+    if (A.tbl != nullptr) slot = A.tbl[slot];
+    const int Hq = A.Hq, Hk = A.Hk;
+    const int width = (Hq + 2 * Hk) * D;
+    const bf16* src = A.qkv + (size_t)t * width + (size_t)head * D + lane * E;
+    if (head >= Hq + Hk) {
+        bf16* dst = A.V + (size_t)(head - Hq - Hk) * A.hs + (size_t)slot * A.rs + lane * E;
+#pragma unroll
+        for (int e = 0; e < E; ++e) dst[e] = ld_bf(src + e);
+        return;
+    }
+    const bool is_q = head < Hq;
+    const bf16* wn = is_q ? A.wq : A.wk;
+    float v[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) v[e] = bf2f(ld_bf(src + e));
+    if (wn != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) ss = fmaf(v[e], v[e], ss);
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / (float)D + A.eps);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float wv = bf2f(wn[lane * E + e]);
+            v[e] = bfround(v[e] * rstd * (A.centered ? 1.f + wv : wv));
+        }
+    }
+    const bf16* cp = A.cos_t + (size_t)pos * D + lane * E;
+    const bf16* sp = A.sin_t + (size_t)pos * D + lane * E;
+    const float sgn = lane < 16 ? -1.f : 1.f;
+    bf16* dst = is_q ? (A.qo + ((size_t)t * Hq + head) * D + lane * E)
+                     : (A.K + (size_t)(head - Hq) * A.hs + (size_t)slot * A.rs + lane * E);
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+        const float rot = __shfl_xor_sync(0xffffffffu, v[e], 16);
+        const float qc = bfround(v[e] * bf2f(cp[e]));
+        dst[e] = f2bf(fmaf(sgn * rot, bf2f(sp[e]), qc));
+    }
+}
+

@@ -17,6 +17,7 @@
 // the FMA: no widened copy exists anywhere.
 #include "common.cuh"
 #include "btb_b200_internal.h"
+#include "gemv_core.cuh"
 
 B2_DEFINE_STATUS(gemv)
 
@@ -24,7 +25,6 @@ namespace {
 
 // warps a CTA, a ring each: 8 or 16 (the tunable `warps`)
 
-enum Fmt { F_BF16 = 0, F_P12 = 1 };
 enum XMode { X_SMEM = 0, X_SMEM_SILU = 1, X_GLOBAL = 2, X_SMEM_NORM = 3 };
 
 struct GemvArgs {
@@ -50,47 +50,6 @@ struct GemvArgs {
     int centered;
     int T;               // live rows (rows T..M-1 of x are zeros)
 };
-
-// a stage's bytes for `n` elements of a row
-template <int FMT>
-__host__ __device__ constexpr int stage_bytes(int n) {
-    return FMT == F_BF16 ? n * 2 : n + n / 2;
-}
-
-// the activation of the SwiGLU fold, native/cuda/btb_kernels.cu:159 of the reference: silu in f32 as torch computes it
-__device__ __forceinline__ float act_silu(float g) { return g / (1.f + expf(-g)); }
-
-// ---- pack12: eight weights of a chunk as four bf16 pairs ---------------------------------------------------------
-// lo: the chunk's 8 low bytes (two words), codes: its 8 nibbles (one word, element e in nibble e). The table's 16
-// high bytes sit in four registers; a code picks its byte with two byte-permutes (codes 0-7, 8-15) and a third that
-// chooses between them by the code's top bit. Returns pairs p[k] = (elem 2k low half, elem 2k+1 high half).
-__device__ __forceinline__ void p12_chunk(uint32_t lo0, uint32_t lo1, uint32_t codes, const uint32_t (&t)[4],
-                                          uint32_t (&p)[4]) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint32_t sel = (codes >> (16 * h)) & 0xffffu;  // four codes
-        const uint32_t s7 = sel & 0x7777u;
-        const uint32_t a = __byte_perm(t[0], t[1], s7);
-        const uint32_t b = __byte_perm(t[2], t[3], s7);
-        const uint32_t pick = 0x3210u | ((sel & 0x8888u) >> 1);
-        const uint32_t hi = __byte_perm(a, b, pick);  // the four high bytes
-        const uint32_t lo = h ? lo1 : lo0;
-        p[2 * h] = __byte_perm(lo, hi, 0x5140u);      // lo0 hi0 lo1 hi1
-        p[2 * h + 1] = __byte_perm(lo, hi, 0x7362u);  // lo2 hi2 lo3 hi3
-    }
-}
-
-// an escaped element's high byte: the row's escapes are [e0, e1) of the ascending list; binary search for `gi`
-__device__ __noinline__ uint32_t p12_escape(const int32_t* __restrict__ esc_idx, const uint8_t* __restrict__ esc_val,
-                                            int e0, int e1, int gi) {
-    int a = e0, b = e1;
-    while (a < b) {
-        const int mid = (a + b) >> 1;
-        if (__ldg(esc_idx + mid) < gi) a = mid + 1;
-        else b = mid;
-    }
-    return a < e1 ? (uint32_t)__ldg(esc_val + a) : 0u;  // never past the row's run, whatever the list holds
-}
 
 template <int M, int FMT, int XM, int NWT>
 __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
@@ -166,83 +125,11 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     pdl_wait();  // x is the previous kernel's output
 
     if (XS) {
-        if (XM == X_SMEM) {
-            const uint4* src = reinterpret_cast<const uint4*>(A.x);
-            uint4* dst = reinterpret_cast<uint4*>(xs);
-            for (int i = threadIdx.x; i < M * C / 8; i += NT) dst[i] = __ldg(src + i);
-        } else if (XM == X_SMEM_SILU) {
-            // x[m][c] = bf16(bf16(silu(g)) * u), gu [M, 2C] gate then up: the values btb_silu_mul would have written;
-            // eight elements a thread a trip (16-byte loads), elementwise so the order is free
-            const int cv = C >> 3;
-            for (int i = threadIdx.x; i < M * cv; i += NT) {
-                const int m = i / cv, c8 = i - m * cv;
-                const uint4 gv = __ldg(reinterpret_cast<const uint4*>(A.x + (size_t)m * 2 * C) + c8);
-                const uint4 uv = __ldg(reinterpret_cast<const uint4*>(A.x + (size_t)m * 2 * C + C) + c8);
-                const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
-                uint32_t o[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const float a = bfround(act_silu(bf_lo(gw[k]))) * bf_lo(uw[k]);
-                    const float b = bfround(act_silu(bf_hi(gw[k]))) * bf_hi(uw[k]);
-                    const __nv_bfloat162 pr = __floats2bfloat162_rn(a, b);
-                    o[k] = *reinterpret_cast<const uint32_t*>(&pr);
-                }
-                reinterpret_cast<uint4*>(xs + (size_t)m * C)[c8] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-        } else {
-            // residual + RMSNorm on the way in (the arithmetic of add_rmsnorm, native/cuda/btb_kernels.cu:365-393 of
-            // the reference): hv = bf16(h + y); thread i of 256 sums hv^2 over i, i + 256, .. in order; the fixed
-            // 256 -> 1 tree; x = bf16(hv * rsqrt(ss / H + eps) * w). Every CTA computes the same values; CTA 0
-            // writes the new residual.
-            float* hsm = reinterpret_cast<float*>(smem);
-            float* red = hsm + C;
-            const int cv = C >> 3, tid = threadIdx.x;
-            for (int m = 0; m < M; ++m) {
-                if (m >= A.T) {  // a padding row: zeros
-                    for (int i = tid; i < cv; i += NT)
-                        reinterpret_cast<uint4*>(xs + (size_t)m * C)[i] = make_uint4(0u, 0u, 0u, 0u);
-                    continue;
-                }
-                for (int i = tid; i < cv; i += NT) {
-                    const uint4 hv = __ldg(reinterpret_cast<const uint4*>(A.h_in + (size_t)m * C) + i);
-                    uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
-                    if (A.y_add != nullptr) {
-                        const uint4 yv = __ldg(reinterpret_cast<const uint4*>(A.y_add + (size_t)m * C) + i);
-                        const uint32_t yw[4] = {yv.x, yv.y, yv.z, yv.w};
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const __nv_bfloat162 pr =
-                                __floats2bfloat162_rn(bf_lo(hw[k]) + bf_lo(yw[k]), bf_hi(hw[k]) + bf_hi(yw[k]));
-                            hw[k] = *reinterpret_cast<const uint32_t*>(&pr);
-                        }
-                        if (blockIdx.x == 0)
-                            reinterpret_cast<uint4*>(A.h_out + (size_t)m * C)[i] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                    }
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        hsm[i * 8 + 2 * k] = bf_lo(hw[k]);
-                        hsm[i * 8 + 2 * k + 1] = bf_hi(hw[k]);
-                    }
-                }
-                __syncthreads();
-                if (tid < 256) {  // the reference's 256 strided partial sums, whatever the block's width
-                    float ss = 0.f;
-                    for (int i = tid; i < C; i += 256) ss = fmaf(hsm[i], hsm[i], ss);
-                    red[tid] = ss;
-                }
-                __syncthreads();
-                for (int st = 128; st > 0; st >>= 1) {
-                    if (tid < st) red[tid] += red[tid + st];
-                    __syncthreads();
-                }
-                const float rstd = rsqrtf(red[0] / (float)C + A.eps);
-                for (int i = tid; i < C; i += NT) {
-                    const float wv = bf2f(A.norm_w[i]);
-                    xs[(size_t)m * C + i] = f2bf(hsm[i] * rstd * (A.centered ? 1.f + wv : wv));
-                }
-                __syncthreads();
-            }
-        }
+        if (XM == X_SMEM) stage_x_copy<M, NT>(xs, A.x, C);
+        else if (XM == X_SMEM_SILU) stage_x_silu<M, NT>(xs, A.x, C);
+        else
+            stage_x_norm<M, NT>(xs, reinterpret_cast<float*>(smem), A.h_in, nullptr, A.y_add, A.norm_w, A.h_out, A.eps,
+                                A.centered, A.T, C, blockIdx.x == 0);
         __syncthreads();
     }
 
@@ -268,47 +155,8 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
             e0 = __ldg(A.esc_row + row);
             e1 = __ldg(A.esc_row + row + 1);
         }
-#pragma unroll 4
-        for (int lc = lane; lc < nch; lc += 32) {
-            uint32_t wp[4];
-            if (FMT == F_BF16) {
-                const uint4 wv = *reinterpret_cast<const uint4*>(stg + lc * 16);
-                wp[0] = wv.x, wp[1] = wv.y, wp[2] = wv.z, wp[3] = wv.w;
-            } else {
-                const uint2 lo = *reinterpret_cast<const uint2*>(stg + lc * 8);
-                const uint32_t codes = *reinterpret_cast<const uint32_t*>(stg + seg + lc * 4);
-                p12_chunk(lo.x, lo.y, codes, A.table, wp);
-                // a code of 15 is an escape: its high byte comes from the row's list
-                const uint32_t f = codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u;
-                if (f != 0u && e1 > e0) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        if ((f >> (4 * e)) & 1u) {
-                            const int gi = (int)((size_t)row * C + c0 + lc * 8 + e);
-                            const uint32_t hb = p12_escape(A.esc_idx, A.esc_val, e0, e1, gi);
-                            const int sh = (e & 1) ? 24 : 8;
-                            wp[e >> 1] = (wp[e >> 1] & ~(0xffu << sh)) | (hb << sh);
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-                uint4 xv;
-                if (XS) xv = *reinterpret_cast<const uint4*>(xs + (size_t)m * C + c0 + lc * 8);
-                else xv = __ldg(reinterpret_cast<const uint4*>(A.x + (size_t)m * C + c0 + lc * 8));
-                float a = acc[m];
-                a = fmaf(bf_lo(wp[0]), bf_lo(xv.x), a);
-                a = fmaf(bf_hi(wp[0]), bf_hi(xv.x), a);
-                a = fmaf(bf_lo(wp[1]), bf_lo(xv.y), a);
-                a = fmaf(bf_hi(wp[1]), bf_hi(xv.y), a);
-                a = fmaf(bf_lo(wp[2]), bf_lo(xv.z), a);
-                a = fmaf(bf_hi(wp[2]), bf_hi(xv.z), a);
-                a = fmaf(bf_lo(wp[3]), bf_lo(xv.w), a);
-                a = fmaf(bf_hi(wp[3]), bf_hi(xv.w), a);
-                acc[m] = a;
-            }
-        }
+        consume_stage<M, FMT, XS>(acc, stg, seg, nch, c0, row, C, XS ? xs : A.x, A.esc_idx, A.esc_val, A.table, e0, e1,
+                                  lane);
         // the stage is free once every lane has read it (the warp barrier orders their shared loads before the
         // elected lane's copy, as a consumer's release orders them in any TMA pipeline): refill it with the next item
         __syncwarp();

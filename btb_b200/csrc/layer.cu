@@ -5,6 +5,7 @@
 // (programmatic dependent launch) and nothing traps.
 #include "common.cuh"
 #include "btb_b200_internal.h"
+#include "attn_core.cuh"
 
 B2_DEFINE_STATUS(layer)
 
@@ -90,76 +91,11 @@ __global__ void __launch_bounds__(256) silu_mul(const ActArgs A) {
     }
 }
 
-// ---- q/k RMSNorm + RoPE + cache write (btb_kernels.cu:261-327) -----------------------------------------------------
-// One warp per (head, row): lane l holds dims l*E .. l*E+E-1, so rotate_half's partner is lane ^ 16.
-struct RopeArgs {
-    const bf16* qkv;
-    const bf16* wq;
-    const bf16* wk;
-    const bf16* cos_t;
-    const bf16* sin_t;
-    const int* n0p;
-    const int* depth;
-    const int* tbl;
-    bf16* K;
-    bf16* V;
-    bf16* qo;
-    float eps;
-    int T, Hq, Hk, centered;
-    long long hs, rs;
-    int cap;  // cache rows: a slot at or past it is refused
-};
 template <int D>
 __global__ void __launch_bounds__(32) norm_rope_kv(const RopeArgs A) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int E = D / 32;
-    const int head = blockIdx.x, t = blockIdx.y, lane = threadIdx.x;
-    const int n0 = *A.n0p;
-    int slot = n0 + t;
-    const int pos = n0 + A.depth[t];
-    if (slot < 0 || slot >= A.cap || pos < 0 || pos >= A.cap) {
-        if (lane == 0) b2_fail(B2_ERR_DOMAIN);
-        return;
-    }
-    if (A.tbl != nullptr) slot = A.tbl[slot];
-    const int Hq = A.Hq, Hk = A.Hk;
-    const int width = (Hq + 2 * Hk) * D;
-    const bf16* src = A.qkv + (size_t)t * width + (size_t)head * D + lane * E;
-    if (head >= Hq + Hk) {
-        bf16* dst = A.V + (size_t)(head - Hq - Hk) * A.hs + (size_t)slot * A.rs + lane * E;
-#pragma unroll
-        for (int e = 0; e < E; ++e) dst[e] = src[e];
-        return;
-    }
-    const bool is_q = head < Hq;
-    const bf16* wn = is_q ? A.wq : A.wk;
-    float v[E];
-#pragma unroll
-    for (int e = 0; e < E; ++e) v[e] = bf2f(src[e]);
-    if (wn != nullptr) {
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < E; ++e) ss = fmaf(v[e], v[e], ss);
-        ss = warp_sum(ss);
-        const float rstd = rsqrtf(ss / (float)D + A.eps);
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const float wv = bf2f(wn[lane * E + e]);
-            v[e] = bfround(v[e] * rstd * (A.centered ? 1.f + wv : wv));
-        }
-    }
-    const bf16* cp = A.cos_t + (size_t)pos * D + lane * E;
-    const bf16* sp = A.sin_t + (size_t)pos * D + lane * E;
-    const float sgn = lane < 16 ? -1.f : 1.f;
-    bf16* dst = is_q ? (A.qo + ((size_t)t * Hq + head) * D + lane * E)
-                     : (A.K + (size_t)(head - Hq) * A.hs + (size_t)slot * A.rs + lane * E);
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-        const float rot = __shfl_xor_sync(0xffffffffu, v[e], 16);
-        const float qc = bfround(v[e] * bf2f(cp[e]));
-        dst[e] = f2bf(fmaf(sgn * rot, bf2f(sp[e]), qc));
-    }
+    rope_item<D, false>(A, blockIdx.x, blockIdx.y, threadIdx.x);
 }
 
 // ---- greedy pick: lowest-index argmax over a bf16 logits row (btb/engine/cuda.py:2237; ties as

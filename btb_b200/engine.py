@@ -161,7 +161,7 @@ class CardEngine:
     """one model on one card: its cache arena, pass buffers, step graph and greedy loop"""
 
     def __init__(self, weights: ModelWeights, cap: int = 4096, silu_fold: bool = True, fuse_norm: bool = True,
-                 device: Any = "cuda"):
+                 step_kernel: bool = True, device: Any = "cuda"):
         capi.lib()  # fail here, loudly, when the library is not built
         if not torch.cuda.is_available():
             raise RuntimeError("btb_b200 needs a CUDA device: there is no CPU path")
@@ -178,6 +178,9 @@ class CardEngine:
         self.n0 = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.silu_fold = silu_fold
         self.fuse_norm = fuse_norm
+        # the whole step as one persistent kernel (head dim 128 only); else one launch a kernel
+        self.step_kernel = bool(step_kernel) and weights.cfg.head_dim == 128 and weights.cfg.q_heads // weights.cfg.kv_heads in (2, 4, 8)
+        self._programs: dict[Any, Any] = {}
         self._bufs: dict[int, dict[str, torch.Tensor]] = {}
         self._graphs: dict[Any, Any] = {}
         self.pin_tok = torch.zeros(1, dtype=torch.int64).pin_memory()
@@ -317,8 +320,25 @@ class CardEngine:
         return lg[-1:]
 
     # -- the step graph ------------------------------------------------------------------------------------------
-    def _step_body(self, s: int, publish: bool) -> None:
+    def program(self, M: int, steps: int = 1, pick: bool = True, publish: bool = True) -> Any:
+        """the whole-step kernel's program for a pass width (built once, its records live on the card)"""
+        from .step import StepProgram
+
+        key = (M, steps, pick, publish)
+        if key not in self._programs:
+            self._programs[key] = StepProgram(self, M, steps, pick, publish)
+        return self._programs[key]
+
+    def _step_body(self, s: int, publish: bool, steps: int = 1) -> None:
         """embed(ids) -> layers -> head -> greedy pick into ids -> n0 += 1 (and the handoff to pinned memory)"""
+        if self.step_kernel:
+            self.program(1, steps, True, publish).launch(stream=torch.cuda.current_stream())
+            self.launches_per_step = 1.0 / steps
+            return
+        for _ in range(steps):
+            self._step_body_launches(s, publish)
+
+    def _step_body_launches(self, s: int, publish: bool) -> None:
         g = self.bufs(1)
         self._n = 0
         self._embed(g, 1, s)
@@ -341,16 +361,14 @@ class CardEngine:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            self._step_body(capi.stream_ptr(side), publish)
+            self._step_body(capi.stream_ptr(side), publish, steps)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.n0.copy_(n_keep)
         self.bufs(1)["ids"].copy_(ids_keep)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            s = capi.stream_ptr()
-            for _ in range(steps):
-                self._step_body(s, publish)
+            self._step_body(capi.stream_ptr(), publish, steps)
         self.n0.copy_(n_keep)
         self.bufs(1)["ids"].copy_(ids_keep)
         self._graphs[key] = graph

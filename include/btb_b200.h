@@ -104,6 +104,19 @@ size_t btb_b200_argmax_scratch_bytes(int T);
  * the length last behind a system fence. out_* null: only the advance. */
 int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance, void* stream);
 
+/* ---- the whole step as one launch ---------------------------------------------------------------------------------
+ * btb captures a decode step as a CUDA graph of ~330 kernel nodes (btb/engine/cuda.py:2101-2251 `_card_step_graph`
+ * over `_card_body`, :1601-1837). btb_b200_step runs the same sequence - embed, every layer's kernels, the head, the
+ * greedy pick, the publish (btb_kernels.cu:455-465) - as ONE persistent cooperative kernel that walks a program of
+ * phases, its TMA rings prefetching the next GEMV's weights across the grid barriers. `args`: a HOST image of the
+ * kernel's argument record and, through it, a DEVICE array of phase records (btb_b200/step.py builds both; their
+ * sizes are btb_b200_step_args_bytes / btb_b200_step_op_bytes). M: the pass width (1 or 2), D: head dim (128),
+ * G: query heads a kv head (2, 4, 8). The barrier counter and abort flag the record points at must be zero at launch.
+ * Bit-identical to the separate launches above. */
+int btb_b200_step(const void* args, int M, int D, int G, void* stream);
+size_t btb_b200_step_op_bytes(void);
+size_t btb_b200_step_args_bytes(void);
+
 #ifdef __cplusplus
 }
 #endif
