@@ -82,6 +82,8 @@ struct StepArgs {
     long long* pin_ts;
     int32_t advance;  // n0 += advance after each step
     int32_t pick;     // 1: the program ends with a PICK phase whose result feeds the next step
+    long long* trace;  // null, or [n_ops * 2] device clock (ns) of one CTA: a phase's start, its arrival at the barrier
+    int32_t trace_cta, pad1;
 };
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
@@ -224,6 +226,11 @@ __global__ void __launch_bounds__(NTS, 1) step_kernel(const StepArgs A) {
     };
 #define STEP_BARRIER()                                                \
     do {                                                              \
+        if (tracing) {                                                \
+            unsigned long long ts_;                                   \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ts_));   \
+            A.trace[2 * oi + 1] = (long long)ts_;                     \
+        }                                                             \
         bar_target += gridDim.x;                                      \
         if (!grid_sync(A.bar, bar_target, A.abort_flag, &s_ok)) {     \
             alive = false;                                            \
@@ -233,6 +240,12 @@ __global__ void __launch_bounds__(NTS, 1) step_kernel(const StepArgs A) {
     for (int step = 0; step < A.steps && alive; ++step) {
         for (int oi = 0; oi < A.n_ops && alive; ++oi) {
             const int kind = ops[oi].kind;
+            const bool tracing = A.trace != nullptr && (int)blockIdx.x == A.trace_cta && threadIdx.x == 0;
+            if (tracing) {
+                unsigned long long ts;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ts));
+                A.trace[2 * oi] = (long long)ts;
+            }
             if (kind == OP_GEMV) {
                 const StepOp& op = ops[oi];
                 const int C = op.C, R = op.R, seg = op.seg, fmt = op.fmt;
@@ -383,7 +396,12 @@ __global__ void __launch_bounds__(NTS, 1) step_kernel(const StepArgs A) {
                 *A.pin_n0 = n;
             }
         }
-        if (step + 1 < A.steps) STEP_BARRIER();  // the next step reads ids and n0
+        if (step + 1 < A.steps) {
+            const bool tracing = false;
+            const int oi = 0;
+            (void)oi;
+            STEP_BARRIER();  // the next step reads ids and n0
+        }
     }
     drain();
 #undef STEP_BARRIER

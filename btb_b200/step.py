@@ -47,6 +47,7 @@ class StepArgs(C.Structure):
         ("bar", _P), ("abort_flag", _P), ("logits", _P), ("pick_keys", _P), ("ids", _P), ("tok_out", _P),
         ("pin_tok", _P), ("pin_n0", _P), ("pin_ts", _P),
         ("advance", C.c_int32), ("pick", C.c_int32),
+        ("trace", _P), ("trace_cta", C.c_int32), ("pad1", C.c_int32),
     ]  # fmt: skip
 
 
@@ -162,8 +163,15 @@ class StepProgram:
             a.pin_tok, a.pin_n0, a.pin_ts = ptr(eng.pin_tok), ptr(eng.pin_n0), ptr(eng.pin_ts)
         a.advance, a.pick = M if not pick else 1, 1 if pick else 0
         self.args = a
+        self.kinds = [o.kind for o in ops]
         self.n_phases = len(ops)
         self.smem = front + NWS * S * stage_cap + NWS * S * 8
+
+    def trace(self, cta: int = 0) -> torch.Tensor:
+        """switch on the per-phase device clock of one CTA; returns the [n_phases, 2] buffer the next launches fill"""
+        self._trace = torch.zeros(self.n_phases, 2, dtype=torch.int64, device=self.eng.dev)
+        self.args.trace, self.args.trace_cta = ptr(self._trace), cta
+        return self._trace
 
     def launch(self, T: int | None = None, stream: Any = None) -> None:
         """zero the barrier state, then the one launch; T live rows of the width's M (default: all M)"""
