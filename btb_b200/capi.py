@@ -56,6 +56,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_attn_scratch_floats": (_SZ, [_I, _I, _I, _I]),
     "btb_b200_argmax_bf16": (_I, [_P, _I, _I, _P, _P, _P]),
     "btb_b200_argmax_scratch_bytes": (_SZ, [_I]),
+    "btb_b200_argmax_bf16_static": (_I, [_P, _I, _I, _P, _P]),
     "btb_b200_publish": (_I, [_P, _P, _P, _P, _P, _I, _P]),
     "btb_b200_step": (_I, [_P, _I, _I, _I, _P]),
     "btb_b200_step_op_bytes": (_SZ, []),

@@ -252,6 +252,42 @@ extern "C" int btb_b200_argmax_bf16(const void* logits, int T, int V, void* scra
 
 extern "C" size_t btb_b200_argmax_scratch_bytes(int T) { return (size_t)T * 12 + 4; }
 
+// ---- the greedy pick for callers that cannot allocate -----------------------------------------------------------------
+// Some callers have no way to hand this library a scratch buffer: a host that got its whole device budget granted up
+// front and may not ask the driver for more in the middle of a decode, or code that is already inside a stream capture,
+// where cudaMalloc is not allowed. For them the pick's scratch (one 64-bit key and one arrival counter a row) lives in
+// this array inside the library's own image. It costs every device that loads the library these few hundred bytes
+// until the process exits.
+#define B2_PICK_STATIC_ROWS 32
+static __device__ __align__(256) unsigned char g_pick_static[B2_PICK_STATIC_ROWS * 12 + 4];
+
+extern "C" int btb_b200_argmax_bf16_static(const void* logits, int T, int V, void* out, void* stream) {
+    if (!logits || !out) return B2_ERR_NULL;
+    if (T <= 0 || V <= 0) return B2_ERR_DOMAIN;
+    if (T > B2_PICK_STATIC_ROWS) return B2_ERR_DOMAIN;  // the built-in scratch holds 32 rows, a pass's widest
+    // In host code `g_pick_static` is only a handle: the array's device address has to be asked for, once per device,
+    // with that device current. This happens on the first call on each device - make that call before any stream
+    // capture starts.
+    static void* addr[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_pick_static) != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return B2_ERR_CUDA;
+        }
+        addr[dev] = p;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // every call shares the one array and it keeps what the last call left: the keys and counters must start at zero
+    if (cudaMemsetAsync(addr[dev], 0, (size_t)T * 12 + 4, s) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return B2_ERR_CUDA;
+    }
+    return btb_b200_argmax_bf16(logits, T, V, addr[dev], out, stream);
+}
+
 extern "C" int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance,
                                 void* stream) {
     if (!n0) return B2_ERR_NULL;

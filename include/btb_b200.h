@@ -100,6 +100,14 @@ size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D);
  * out int64 [T]. */
 int btb_b200_argmax_bf16(const void* logits, int T, int V, void* scratch, void* out, void* stream);
 size_t btb_b200_argmax_scratch_bytes(int T);
+/* The same pick with no scratch argument. This entry point has no counterpart in the reference. It is for callers that
+ * cannot allocate device memory when they need the pick - a host whose device budget was fixed at start-up, or code
+ * already inside a stream capture, where cudaMalloc is illegal - the scratch is an array built into the library
+ * (a few hundred bytes on every device that loads it, held until exit). T at most 32 rows (BTB_B200_ERR_DOMAIN
+ * beyond). It allocates nothing and frees nothing. The first call on each device looks the array's address up:
+ * make that call before starting any stream capture. All calls share the one array: two calls whose kernels may
+ * overlap on the device (different streams) race on it - keep them on one stream or order them yourself. */
+int btb_b200_argmax_bf16_static(const void* logits, int T, int V, void* out, void* stream);
 /* btb_publish (btb_kernels.cu:455-465): n0 += advance, then token, device clock (ns) and length to pinned host memory,
  * the length last behind a system fence. out_* null: only the advance. */
 int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance, void* stream);

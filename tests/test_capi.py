@@ -46,7 +46,8 @@ def test_every_declaration_cites_the_reference():
             continue
         at = text.index(name + "(")
         comment = text[text.rfind("/*", 0, at) : at]
-        assert re.search(r"\.(cu|cuh|rs|py):\d+", comment) or "btb_b200_" in comment, name
+        assert (re.search(r"\.(cu|cuh|rs|py):\d+", comment) or "btb_b200_" in comment
+                or "no counterpart in the reference" in comment), name
 
 
 def test_host_side_argument_checks(lib):
