@@ -58,6 +58,14 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_argmax_scratch_bytes": (_SZ, [_I]),
     "btb_b200_argmax_bf16_static": (_I, [_P, _I, _I, _P, _P]),
     "btb_b200_publish": (_I, [_P, _P, _P, _P, _P, _I, _P]),
+    "btb_b200_moe_route": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _I, _P]),
+    "btb_b200_gemv_lane16_f32": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "btb_b200_gemv_lane16_mx4_f32": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "btb_b200_gemv_lane16_fp8_f32": (_I, [_P, _P, _I, _I, _P, _P, _I, _I, _I, _P]),
+    "btb_b200_moe_gemv": (_I, [_I, _P, _P, _LL, _LL, _I, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _P]),
+    "btb_b200_moe_act": (_I, [_P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
+    "btb_b200_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "btb_b200_widen_f32": (_I, [_P, _P, _I, _P]),
     "btb_b200_step": (_I, [_P, _I, _I, _I, _P]),
     "btb_b200_step_op_bytes": (_SZ, []),
     "btb_b200_step_args_bytes": (_SZ, []),

@@ -1,0 +1,431 @@
+// The MoE block's kernels: router top-k, the experts' matvecs over only the picked experts, the gated activation
+// between them and the ordered weighted sum.
+//
+// What the arithmetic follows: on a CUDA device btb multiplies a decode pass's experts with its HOST kernels (or their
+// on-card twins btb_gemv_lane16{,_mx4}_f32, native/cuda/btb_kernels.cu:1635-1766), so an expert's output does not
+// depend on where it is seated: x widened to f32, 16 lane sums a row (column c to lane c mod 16, one fma each in
+// increasing c), the pairwise fold of native/src/gemv.rs:46-58, f32 out. The row's dtype (bf16) comes back between
+// the two matvecs for the gated activation and after the second for the bias, the routing weight and the sum over the
+// picked experts in ascending expert id (btb/engine/host.py:508-569 `_Experts._one_row`). Weights are read as stored:
+// bf16, MXFP4 blocks + e8m0 scales (btb/mxfp4.py:102-124) or FP8 e4m3 + f32 block scales held as bf16
+// (btb/fp8.py:36-100) - widened in registers, no widened copy.
+#include <cuda_fp8.h>
+
+#include "btb_b200_internal.h"
+
+B2_DEFINE_STATUS(moe)
+
+namespace {
+
+// ---- router ---------------------------------------------------------------------------------------------------------
+// mode 0 (native/cuda/btb_kernels.cu:861-948; btb/engine/families/qwen4/router.py:42-50): f32 softmax over the E
+// logits (thread i of 256 sums its strided terms, then the 256 -> 1 tree), top-k by (p desc, index asc), weights
+// p / sum(top k) summed in rank order, rounded to bf16.
+// mode 1 (btb/engine/host.py:187-191, gpt-oss): top-k of the logits themselves, then a softmax over the k.
+#define ROUTE_THREADS 256
+#define ROUTE_MAX_K 32
+struct RouteArgs {
+    const void* logits;
+    int ls, E, k, mode, f32_logits;
+    int* idx;
+    bf16* w;
+};
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
+    extern __shared__ float pr[];  // [E]
+    __shared__ float red[ROUTE_THREADS];
+    __shared__ int redi[ROUTE_THREADS];
+    __shared__ float topv[ROUTE_MAX_K];
+    __shared__ int topi[ROUTE_MAX_K];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, tid = threadIdx.x, E = A.E, k = A.k;
+    auto logit = [&](int e) -> float {
+        if (A.f32_logits) return __ldcg(static_cast<const float*>(A.logits) + (size_t)t * A.ls + e);
+        const unsigned short u = __ldcg(static_cast<const unsigned short*>(A.logits) + (size_t)t * A.ls + e);
+        return __uint_as_float((uint32_t)u << 16);
+    };
+    if (A.mode == 0) {
+        float m = NEG_INF;
+        for (int e = tid; e < E; e += ROUTE_THREADS) m = fmaxf(m, logit(e));
+        red[tid] = m;
+        __syncthreads();
+        for (int s = ROUTE_THREADS / 2; s > 0; s >>= 1) {
+            if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]);
+            __syncthreads();
+        }
+        m = red[0];
+        __syncthreads();
+        float s = 0.f;
+        for (int e = tid; e < E; e += ROUTE_THREADS) {
+            const float p = expf(logit(e) - m);
+            pr[e] = p;
+            s += p;
+        }
+        red[tid] = s;
+        __syncthreads();
+        for (int st = ROUTE_THREADS / 2; st > 0; st >>= 1) {
+            if (tid < st) red[tid] += red[tid + st];
+            __syncthreads();
+        }
+        s = red[0];
+        __syncthreads();
+        for (int e = tid; e < E; e += ROUTE_THREADS) pr[e] = pr[e] / s;
+    } else {
+        for (int e = tid; e < E; e += ROUTE_THREADS) pr[e] = logit(e);
+    }
+    __syncthreads();
+    // k rounds of the total order's maximum; a picked entry leaves the field (a flag array, so any value may be live)
+    constexpr int NONE = 0x7fffffff;
+    for (int j = 0; j < k; ++j) {
+        float bv = 0.f;
+        int bi = NONE;
+        for (int e = tid; e < E; e += ROUTE_THREADS) {
+            bool taken = false;
+            for (int u = 0; u < j; ++u) taken |= topi[u] == e;
+            if (taken) continue;
+            const float v = pr[e];
+            if (bi == NONE || v > bv) {  // e ascends within the thread: a tie keeps the lower index
+                bv = v;
+                bi = e;
+            }
+        }
+        red[tid] = bv;
+        redi[tid] = bi;
+        __syncthreads();
+        for (int st = ROUTE_THREADS / 2; st > 0; st >>= 1) {
+            if (tid < st) {
+                const float ov = red[tid + st];
+                const int oi = redi[tid + st];
+                if (oi != NONE && (redi[tid] == NONE || ov > red[tid] || (ov == red[tid] && oi < redi[tid]))) {
+                    red[tid] = ov;
+                    redi[tid] = oi;
+                }
+            }
+            __syncthreads();
+        }
+        if (tid == 0) {
+            topv[j] = red[0];
+            topi[j] = redi[0];
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        if (A.mode == 0) {
+            float sum = 0.f;
+            for (int j = 0; j < k; ++j) sum += topv[j];
+            for (int j = 0; j < k; ++j) {
+                A.idx[(size_t)t * k + j] = topi[j];
+                A.w[(size_t)t * k + j] = f2bf(topv[j] / sum);
+            }
+        } else {
+            float m = topv[0], sum = 0.f, ex[ROUTE_MAX_K];
+            for (int j = 1; j < k; ++j) m = fmaxf(m, topv[j]);
+            for (int j = 0; j < k; ++j) {
+                ex[j] = expf(topv[j] - m);
+                sum += ex[j];
+            }
+            for (int j = 0; j < k; ++j) {
+                A.idx[(size_t)t * k + j] = topi[j];
+                A.w[(size_t)t * k + j] = f2bf(ex[j] / sum);
+            }
+        }
+    }
+}
+
+// ---- the 16-lane matvec over stored weights ---------------------------------------------------------------------------
+enum L16Fmt { L_BF16 = 0, L_MX4 = 1, L_FP8 = 2 };
+struct L16Args {
+    const uint8_t* w;       // expert 0's weights
+    const uint8_t* scales;  // MX4: e8m0 bytes; FP8: f32 grid
+    long long w_stride, s_stride;  // bytes from an expert to the next
+    const int* idx;         // [n_tasks] the task's expert, or null (expert 0 for all)
+    const float* x;         // [rows_x, C] f32
+    int x_div;              // task i reads x row i / x_div (k: one row a token; 1: a row a task)
+    float* y;               // [n_tasks, R] f32
+    int R, C, sr, sc, E;
+    int ep_rank, ep_size;  // expert e lives on rank e % ep_size as its local expert e / ep_size; others' rows are zeros
+};
+
+__device__ __forceinline__ float mx4_scale(unsigned s) {
+    const float f = __uint_as_float((s == 0u ? 1u : s) << 23);
+    return s == 0u ? __fmul_rn(f, 0.5f) : f;
+}
+__device__ __forceinline__ float fp4_value(unsigned code) {
+    // e2m1: 0, .5, 1, 1.5, 2, 3, 4, 6 and their negatives, built as bf16 bit patterns: exponent field m >> 1 rebased
+    // to 127 and the mantissa bit m & 1 for the normals, 0.5 the one subnormal
+    const unsigned m = code & 7u;
+    const unsigned mag = m >= 2u ? ((((m >> 1) + 126u) << 7) | ((m & 1u) << 6)) : (m ? 0x3F00u : 0u);
+    return __uint_as_float((mag | ((code & 8u) << 12)) << 16);
+}
+// e4m3fn byte -> f32, built from its bits (native/src/gemv.rs:3010-3020)
+__device__ __forceinline__ float f8_value(unsigned b) {
+    const unsigned a = b & 0x7Fu;
+    float mag;
+    if (a == 0x7Fu) mag = __uint_as_float(0x7FC00000u);
+    else if (a < 8u) mag = __fmul_rn((float)a, 1.0f / 512.0f);
+    else mag = __uint_as_float((a << 20) + (120u << 23));
+    return __uint_as_float(__float_as_uint(mag) | ((b & 0x80u) << 24));
+}
+// to the nearest bf16, ties to even, by integer arithmetic as the reference rounds it (gemv.rs:3004-3008)
+__device__ __forceinline__ float round_bf16_int(float f) {
+    const unsigned b = __float_as_uint(f);
+    return __uint_as_float((b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u);
+}
+
+// a half-warp a row: lane j runs the chain of the columns c = j mod 16 in increasing c; the butterfly over xor 1, 2,
+// 4, 8 is reduce16's pairwise fold (each level adds the two partial sums reduce16 adds)
+template <int FMT>
+__global__ void __launch_bounds__(128) gemv_lane16(const L16Args A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int j = threadIdx.x & 15;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 4);
+    const int task = blockIdx.y;
+    int e = 0;
+    if (A.idx != nullptr) {
+        e = __ldcg(A.idx + task);
+        if (e < 0 || e >= A.E) {  // never read outside the experts: record and skip
+            if (threadIdx.x == 0 && blockIdx.x == 0) b2_fail(B2_ERR_DOMAIN);
+            e = -1;
+        }
+    }
+    bool mine = true;
+    if (e >= 0 && A.ep_size > 1) {
+        mine = e % A.ep_size == A.ep_rank;
+        e = e / A.ep_size;
+    }
+    const int R = A.R, C = A.C;
+    const float* x = A.x + (size_t)(task / A.x_div) * C;
+    float acc = 0.f;
+    if (r < R && e >= 0 && mine) {
+        if (FMT == L_BF16) {
+            const unsigned short* wr = reinterpret_cast<const unsigned short*>(A.w + (size_t)e * A.w_stride) + (size_t)r * C;
+            int c = j;
+            for (; c + 48 < C; c += 64) {  // four of the lane's columns in flight, taken in order
+                float wv[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) wv[k] = __uint_as_float((unsigned)__ldcs(wr + c + 16 * k) << 16);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc = fmaf(wv[k], __ldcg(x + c + 16 * k), acc);
+            }
+            for (; c < C; c += 16) acc = fmaf(__uint_as_float((unsigned)__ldcs(wr + c) << 16), __ldcg(x + c), acc);
+        } else if (FMT == L_MX4) {
+            const int G = C >> 5;
+            const unsigned char* br = A.w + (size_t)e * A.w_stride + (size_t)r * G * 16;
+            const unsigned char* sr = A.scales + (size_t)e * A.s_stride + (size_t)r * G;
+            const int sh = (j & 1) << 2;
+#pragma unroll 4
+            for (int g = 0; g < G; ++g) {
+                const float sc = mx4_scale((unsigned)__ldcs(sr + g));
+                const float w0 = __fmul_rn(fp4_value((__ldcs(br + g * 16 + (j >> 1)) >> sh) & 15u), sc);
+                const float w1 = __fmul_rn(fp4_value((__ldcs(br + g * 16 + 8 + (j >> 1)) >> sh) & 15u), sc);
+                const int c = g * 32 + j;
+                acc = fmaf(w0, __ldcg(x + c), acc);
+                acc = fmaf(w1, __ldcg(x + c + 16), acc);
+            }
+        } else {
+            const unsigned char* wr = A.w + (size_t)e * A.w_stride + (size_t)r * C;
+            const float* sg = reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride);
+            const int bm = R / A.sr, bn = C / A.sc;
+            const float* srow = sg + (size_t)(r / bm) * A.sc;
+#pragma unroll 4
+            for (int c = j; c < C; c += 16) {
+                const float w = round_bf16_int(__fmul_rn(f8_value((unsigned)__ldcs(wr + c)), __ldg(srow + c / bn)));
+                acc = fmaf(w, __ldcg(x + c), acc);
+            }
+        }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+    if (r < R && j == 0 && e >= 0) A.y[(size_t)task * R + r] = acc;  // zeros for another rank's expert
+}
+
+// ---- between the two matvecs: the row dtype, the bias, the gated activation, back to f32 -------------------------------
+// kind 0: silu(gate) * up over gate | up halves (btb/engine/host.py:439-441); kind 1: gpt-oss's clamped GLU over
+// interleaved lanes, (up + 1) * gate * sigmoid(alpha * gate) (host.py:444-450) - every torch op's bf16 rounding kept.
+struct ActArgs2 {
+    const float* gu;  // [n, 2I]
+    float* h;         // [n, I]
+    const bf16* bias;  // [E, 2I] or null
+    const int* idx;
+    int n, I, kind;
+    float alpha, limit;
+};
+__global__ void __launch_bounds__(256) moe_act(const ActArgs2 A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total = (size_t)A.n * A.I;
+    for (size_t q = (size_t)blockIdx.x * 256 + threadIdx.x; q < total; q += (size_t)gridDim.x * 256) {
+        const size_t i = q / A.I, c = q - i * A.I;
+        const size_t gi = A.kind == 0 ? c : 2 * c, ui = A.kind == 0 ? A.I + c : 2 * c + 1;
+        float g = bfround(__ldcg(A.gu + i * 2 * A.I + gi)), u = bfround(__ldcg(A.gu + i * 2 * A.I + ui));
+        if (A.bias != nullptr) {
+            const bf16* b = A.bias + (size_t)__ldcg(A.idx + i) * 2 * A.I;
+            g = bfround(g + bf2f(b[gi]));
+            u = bfround(u + bf2f(b[ui]));
+        }
+        float out;
+        if (A.kind == 0) {
+            out = bfround(bfround(g / (1.f + expf(-g))) * u);
+        } else {
+            g = fminf(g, A.limit);
+            u = fminf(fmaxf(u, -A.limit), A.limit);
+            const float t1 = bfround(g * A.alpha);
+            const float t2 = bfround(1.f / (1.f + expf(-t1)));
+            const float glu = bfround(g * t2);
+            out = bfround(bfround(u + 1.f) * glu);
+        }
+        A.h[q] = out;
+    }
+}
+
+// ---- the sum: out_e = bf16(down_e) (+ bias) * w_e, final += out_e one add at a time in ascending expert id ----------
+struct CombineArgs {
+    const float* dn;  // [T, k, H]
+    const int* idx;   // [T, k]
+    const bf16* w;    // [T, k]
+    const bf16* bias;  // [E, H] or null
+    bf16* y;          // [T, H]
+    int T, k, H;
+};
+__global__ void __launch_bounds__(256) moe_combine(const CombineArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y, k = A.k;
+    __shared__ int order[ROUTE_MAX_K];
+    if (threadIdx.x == 0) {  // the row's picks by ascending expert id (a handful: insertion sort)
+        for (int a = 0; a < k; ++a) order[a] = a;
+        for (int a = 1; a < k; ++a) {
+            const int v = order[a];
+            const int ev = __ldcg(A.idx + (size_t)t * k + v);
+            int b = a - 1;
+            while (b >= 0 && __ldcg(A.idx + (size_t)t * k + order[b]) > ev) {
+                order[b + 1] = order[b];
+                --b;
+            }
+            order[b + 1] = v;
+        }
+    }
+    __syncthreads();
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= A.H) return;
+    float fin = 0.f;
+    for (int a = 0; a < k; ++a) {
+        const int s = order[a];
+        const size_t q = (size_t)t * k + s;
+        float o = bfround(__ldcg(A.dn + q * A.H + c));
+        if (A.bias != nullptr) o = bfround(o + bf2f(A.bias[(size_t)__ldcg(A.idx + q) * A.H + c]));
+        const unsigned short wb = __ldcg(reinterpret_cast<const unsigned short*>(A.w) + q);
+        o = bfround(o * __uint_as_float((uint32_t)wb << 16));
+        fin = bfround(fin + o);
+    }
+    A.y[(size_t)t * A.H + c] = f2bf(fin);
+}
+
+// bf16 [n] -> f32 [n] (the experts' and the router's x is the normed row widened)
+struct WidenArgs {
+    const bf16* x;
+    float* y;
+    int n;
+};
+__global__ void __launch_bounds__(256) widen_f32(const WidenArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < A.n; i += gridDim.x * 256) {
+        const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(A.x) + i);
+        A.y[i] = __uint_as_float((uint32_t)u << 16);
+    }
+}
+
+}  // namespace
+
+extern "C" int btb_b200_moe_route(const void* logits, int ls, int E, int k, int mode, int f32_logits, void* idx, void* w,
+                                  int T, void* stream) {
+    if (!logits || !idx || !w) return B2_ERR_NULL;
+    if (T <= 0 || E <= 0 || k <= 0 || k > E || k > ROUTE_MAX_K || ls < E || E > 8192 || (mode != 0 && mode != 1))
+        return B2_ERR_DOMAIN;
+    RouteArgs a{logits, ls, E, k, mode, f32_logits, static_cast<int*>(idx), static_cast<bf16*>(w)};
+    return b2_launch((const void*)moe_route, dim3(T), dim3(ROUTE_THREADS), (size_t)E * 4, static_cast<cudaStream_t>(stream), a);
+}
+
+static int lane16_launch(int fmt, const L16Args& a, int n_tasks, cudaStream_t s) {
+    const dim3 grid((a.R + 7) / 8, n_tasks);
+    switch (fmt) {
+        case L_BF16: return b2_launch((const void*)gemv_lane16<L_BF16>, grid, dim3(128), 0, s, a, 1);
+        case L_MX4: return b2_launch((const void*)gemv_lane16<L_MX4>, grid, dim3(128), 0, s, a, 1);
+        case L_FP8: return b2_launch((const void*)gemv_lane16<L_FP8>, grid, dim3(128), 0, s, a, 1);
+        default: return B2_ERR_DOMAIN;
+    }
+}
+
+extern "C" int btb_b200_gemv_lane16_f32(const void* w, const void* x, void* y, int M, int R, int C, void* stream) {
+    if (!w || !x || !y) return B2_ERR_NULL;
+    if (M <= 0 || R <= 0 || C <= 0) return B2_ERR_DOMAIN;
+    L16Args a{static_cast<const uint8_t*>(w), nullptr, 0, 0, nullptr, static_cast<const float*>(x), 1,
+              static_cast<float*>(y), R, C, 1, 1, 1, 0, 1};
+    return lane16_launch(L_BF16, a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int btb_b200_gemv_lane16_mx4_f32(const void* blocks, const void* scales, const void* x, void* y, int M, int R,
+                                            int C, void* stream) {
+    if (!blocks || !scales || !x || !y) return B2_ERR_NULL;
+    if (M <= 0 || R <= 0 || C <= 0 || (C & 31)) return B2_ERR_DOMAIN;
+    L16Args a{static_cast<const uint8_t*>(blocks), static_cast<const uint8_t*>(scales), 0, 0, nullptr,
+              static_cast<const float*>(x), 1, static_cast<float*>(y), R, C, 1, 1, 1, 0, 1};
+    return lane16_launch(L_MX4, a, M, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int btb_b200_gemv_lane16_fp8_f32(const void* w, const void* scales, int sr, int sc, const void* x, void* y,
+                                            int M, int R, int C, void* stream) {
+    if (!w || !scales || !x || !y) return B2_ERR_NULL;
+    if (M <= 0 || R <= 0 || C <= 0 || sr <= 0 || sc <= 0 || R % sr || C % sc) return B2_ERR_DOMAIN;
+    L16Args a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), 0, 0, nullptr,
+              static_cast<const float*>(x), 1, static_cast<float*>(y), R, C, sr, sc, 1, 0, 1};
+    return lane16_launch(L_FP8, a, M, static_cast<cudaStream_t>(stream));
+}
+
+// the picked experts' matvecs in one launch: task i = (row i / k, pick i % k) multiplies expert idx[i]'s [R, C]
+// matrix with x row (i / x_div). fmt 0 bf16, 1 MXFP4, 2 FP8.
+extern "C" int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride,
+                                 int sr, int sc, const void* idx, int n_tasks, int E, const void* x, int x_div, void* y,
+                                 int R, int C, int ep_rank, int ep_size, void* stream) {
+    if (!w || !idx || !x || !y || (fmt != L_BF16 && !scales)) return B2_ERR_NULL;
+    if (n_tasks <= 0 || R <= 0 || C <= 0 || x_div <= 0 || E <= 0 || ep_size < 1 || ep_rank < 0 || ep_rank >= ep_size)
+        return B2_ERR_DOMAIN;
+    if (fmt == L_MX4 && (C & 31)) return B2_ERR_DOMAIN;
+    if (fmt == L_FP8 && (sr <= 0 || sc <= 0 || R % sr || C % sc)) return B2_ERR_DOMAIN;
+    L16Args a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), w_stride, s_stride,
+              static_cast<const int*>(idx), static_cast<const float*>(x), x_div, static_cast<float*>(y), R, C,
+              sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size};
+    return lane16_launch(fmt, a, n_tasks, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int btb_b200_moe_act(const void* gu, void* h, const void* bias, const void* idx, int n, int I, int kind,
+                                float alpha, float limit, void* stream) {
+    if (!gu || !h || (bias && !idx)) return B2_ERR_NULL;
+    if (n <= 0 || I <= 0 || (kind != 0 && kind != 1)) return B2_ERR_DOMAIN;
+    ActArgs2 a{static_cast<const float*>(gu), static_cast<float*>(h), static_cast<const bf16*>(bias),
+               static_cast<const int*>(idx), n, I, kind, alpha, limit};
+    const long long tot = (long long)n * I;
+    const int grid = (int)((tot + 255) / 256 < 1184 ? (tot + 255) / 256 : 1184);
+    return b2_launch((const void*)moe_act, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" int btb_b200_moe_combine(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T,
+                                    int k, int H, void* stream) {
+    if (!dn || !idx || !w || !y) return B2_ERR_NULL;
+    if (T <= 0 || k <= 0 || k > ROUTE_MAX_K || H <= 0) return B2_ERR_DOMAIN;
+    CombineArgs a{static_cast<const float*>(dn), static_cast<const int*>(idx), static_cast<const bf16*>(w),
+                  static_cast<const bf16*>(bias), static_cast<bf16*>(y), T, k, H};
+    return b2_launch((const void*)moe_combine, dim3((H + 255) / 256, T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" int btb_b200_widen_f32(const void* x, void* y, int n, void* stream) {
+    if (!x || !y) return B2_ERR_NULL;
+    if (n <= 0) return B2_ERR_DOMAIN;
+    WidenArgs a{static_cast<const bf16*>(x), static_cast<float*>(y), n};
+    const int grid = (n + 255) / 256 < 296 ? (n + 255) / 256 : 296;
+    return b2_launch((const void*)widen_f32, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}

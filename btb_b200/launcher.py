@@ -112,7 +112,7 @@ class B200Launcher:
         logits, ls, E, k, idx, w, hidx, hw, cnt, seq, hseq = a
         if _p(hidx) or _p(hseq):
             raise KeyError("btb_moe_route: the host publish is not served (the experts run on the card)")
-        capi.call("btb_b200_moe_route", _p(logits), int(_v(ls)), int(_v(E)), int(_v(k)), 0, _p(idx), _p(w),
+        capi.call("btb_b200_moe_route", _p(logits), int(_v(ls)), int(_v(E)), int(_v(k)), 0, 0, _p(idx), _p(w),
                   int(grid[0]), s)  # fmt: skip
 
     def _gemv_lane16(self, name, m, grid, a, s):

@@ -1,0 +1,220 @@
+"""The MoE decoder on the card: attention as the dense engine's, the MLP a router and the picked experts' matvecs.
+
+What this mirrors: btb serves MoE layers through `_Router` / `Qwen4Router` (btb/engine/host.py:175-191,
+btb/engine/families/qwen4/router.py:24-50) and `_Experts._one_row` (host.py:508-569): the normed row widened to f32,
+the router's logits by the host GEMV, top-k, each picked expert's gate_up and down by the grouped host GEMV over the
+weights as stored (MXFP4 / FP8), the row dtype's gated activation between them, and the weighted sum in ascending
+expert id. btb runs those matvecs on the CPU with two bus hops a layer; here they run on the card, the picks never
+leaving it, with the same arithmetic (the 16-lane order of native/src/gemv.rs).
+
+Expert parallelism (one process a GPU): expert e lives on rank e % ep; a rank multiplies only its own picks and
+writes zeros for the others; one all-reduce of the [T, k, H] f32 products a layer puts every product on every rank
+(x + 0 is exact), and every rank then runs the same ordered bf16 sum - bit-identical to one GPU.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from . import capi
+from .capi import call, ptr
+from .engine import CardEngine, DenseConfig, pad_rows
+
+FMT = {"bf16": 0, "mx4": 1, "fp8": 2}
+
+
+@dataclass
+class MoEConfig(DenseConfig):
+    experts: int = 8
+    top_k: int = 2
+    router_mode: int = 0  # 0: softmax -> top-k -> renormalise (Qwen); 1: top-k -> softmax (gpt-oss)
+    glu_kind: int = 0  # 0: silu(gate) * up over halves; 1: gpt-oss clamped GLU over interleaved lanes
+    expert_fmt: str = "mx4"
+    alpha: float = 1.702
+    limit: float = 7.0
+
+    def expert_bytes(self) -> int:
+        """one expert's stored bytes (gate_up + down)"""
+        n = 3 * self.inter * self.hidden
+        if self.expert_fmt == "mx4":
+            return n // 2 + n // 32
+        if self.expert_fmt == "fp8":
+            return n + 4 * (n // (128 * 128))
+        return 2 * n
+
+    def weight_bytes_per_token(self, storage: str = "bf16") -> int:
+        att = 2 * self.hidden * (self.qkv_rows + self.q_heads * self.head_dim) + 2 * self.experts * self.hidden
+        return self.layers * (att + self.top_k * self.expert_bytes()) + self.vocab * self.hidden * 2
+
+
+GPT_OSS_20B = MoEConfig("gpt-oss-20b", 2880, 24, 64, 8, 64, 2880, 201088, theta=150000.0, eps=1e-5, qk_norm=False,
+                        experts=32, top_k=4, router_mode=1, glu_kind=1, expert_fmt="mx4")  # fmt: skip
+QWEN3_30B_A3B = MoEConfig("qwen3-30b-a3b", 2048, 48, 32, 4, 128, 768, 151936, experts=128, top_k=8, router_mode=0,
+                          glu_kind=0, expert_fmt="fp8")  # fmt: skip
+
+
+@dataclass
+class ExpertStack:
+    """a layer's experts as stored, the locally held ones stacked: w [n_local, R, ...] bytes, scales beside them"""
+
+    fmt: str
+    w: torch.Tensor
+    scales: torch.Tensor | None
+    R: int
+    C: int
+    sr: int = 1
+    sc: int = 1
+
+    @property
+    def w_stride(self) -> int:
+        return int(self.w[0].numel() * self.w.element_size())
+
+    @property
+    def s_stride(self) -> int:
+        return 0 if self.scales is None else int(self.scales[0].numel() * self.scales.element_size())
+
+
+@dataclass
+class MoELayer:
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    qkv: torch.Tensor
+    o: torch.Tensor
+    router: torch.Tensor  # [E, H] bf16
+    gu: ExpertStack
+    dn: ExpertStack
+    wq: torch.Tensor | None = None
+    wk: torch.Tensor | None = None
+
+
+@dataclass
+class MoEWeights:
+    cfg: MoEConfig
+    embed: torch.Tensor
+    norm: torch.Tensor
+    layers: list[MoELayer] = field(default_factory=list)
+    ep_rank: int = 0
+    ep_size: int = 1
+
+
+def synth_expert_stack(cfg: MoEConfig, g: torch.Generator, n: int, R: int, C_: int, device: Any) -> ExpertStack:
+    """seeded stored experts: MXFP4 nibbles uniform over the 16 codes with scales uniform in exponent [-8, 0]; FP8 bytes
+    uniform over the finite codes with bf16 N(0, 0.02) scales per 128 x 128 block; bf16 N(0, 0.02)"""
+    gdev = g.device
+    if cfg.expert_fmt == "mx4":
+        blocks = torch.randint(0, 256, (n, R, C_ // 32, 16), generator=g, device=gdev, dtype=torch.uint8)
+        scales = torch.randint(119, 128, (n, R, C_ // 32), generator=g, device=gdev, dtype=torch.uint8)
+        return ExpertStack("mx4", blocks.to(device), scales.to(device), R, C_)
+    if cfg.expert_fmt == "fp8":
+        w = torch.randint(0, 256, (n, R, C_), generator=g, device=gdev, dtype=torch.uint8)
+        w = torch.where((w & 0x7F) == 0x7F, w & 0xF0, w)  # no NaN codes
+        sr, sc = R // 128, C_ // 128
+        s = (torch.randn(n, sr, sc, generator=g, device=gdev) * 0.02).to(torch.bfloat16).float()
+        return ExpertStack("fp8", w.to(device), s.to(device).contiguous(), R, C_, sr, sc)
+    w = (torch.randn(n, R, C_, generator=g, device=gdev) * 0.02).to(torch.bfloat16)
+    return ExpertStack("bf16", w.to(device), None, R, C_)
+
+
+def synth_moe_weights(cfg: MoEConfig, seed: int = 0, device: Any = "cuda", on_cpu: bool = False, ep_rank: int = 0,
+                      ep_size: int = 1) -> MoEWeights:  # fmt: skip
+    """random-init weights: attention, router, embedding bf16 N(0, 0.02); norm weights 1; experts as
+    `synth_expert_stack`. Under expert parallelism every rank draws the same stream and keeps expert e iff
+    e % ep_size == ep_rank, so the model is the same model at every N."""
+    gdev = "cpu" if on_cpu else device
+    g = torch.Generator(device=gdev).manual_seed(seed)
+
+    def lin(r: int, c: int) -> torch.Tensor:
+        return (torch.randn(r, c, generator=g, device=gdev, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(device)
+
+    def ones(n: int) -> torch.Tensor:
+        return torch.ones(n, dtype=torch.bfloat16, device=device)
+
+    def keep(st: ExpertStack) -> ExpertStack:
+        if ep_size == 1:
+            return st
+        sel = torch.arange(ep_rank, cfg.experts, ep_size, device=st.w.device)
+        st.w = st.w.index_select(0, sel).contiguous()
+        if st.scales is not None:
+            st.scales = st.scales.index_select(0, sel).contiguous()
+        return st
+
+    H, D, I, E = cfg.hidden, cfg.head_dim, cfg.inter, cfg.experts
+    mw = MoEWeights(cfg, lin(cfg.vocab, H), ones(H), ep_rank=ep_rank, ep_size=ep_size)
+    for _ in range(cfg.layers):
+        qkv = torch.cat([lin(cfg.q_heads * D, H), lin(cfg.kv_heads * D, H), lin(cfg.kv_heads * D, H)])
+        o = lin(H, cfg.q_heads * D)
+        router = lin(E, H)
+        gu = keep(synth_expert_stack(cfg, g, E, 2 * I, H, device))
+        dn = keep(synth_expert_stack(cfg, g, E, H, I, device))
+        mw.layers.append(MoELayer(ones(H), ones(H), qkv, o, router, gu, dn,
+                                  ones(D) if cfg.qk_norm else None, ones(D) if cfg.qk_norm else None))  # fmt: skip
+    return mw
+
+
+class MoEEngine(CardEngine):
+    """the MoE model on one card (or one rank of an expert-parallel group)"""
+
+    def __init__(self, weights: MoEWeights, cap: int = 4096, device: Any = "cuda", group: Any = None):
+        super().__init__(weights, cap=cap, step_kernel=False, device=device)  # type: ignore[arg-type]
+        self.group = group
+        self.ep_rank, self.ep_size = weights.ep_rank, weights.ep_size
+
+    def bufs(self, M: int) -> dict[str, torch.Tensor]:
+        g = super().bufs(M)
+        if "xf" not in g:
+            c, dev = self.cfg, self.dev
+            f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)  # noqa: E731
+            k = c.top_k
+            g.update({
+                "xf": f32(M, c.hidden), "rl": f32(M, c.experts), "idx": torch.zeros(M, k, dtype=torch.int32, device=dev),
+                "rw": torch.zeros(M, k, dtype=torch.bfloat16, device=dev), "egu": f32(M * k, 2 * c.inter),
+                "eh": f32(M * k, c.inter), "edn": f32(M * k, c.hidden),
+            })  # fmt: skip
+        return g
+
+    def _expert_gemv(self, st: ExpertStack, idx: torch.Tensor, n_tasks: int, x: torch.Tensor, x_div: int,
+                     y: torch.Tensor, s: int) -> None:  # fmt: skip
+        self._k("btb_b200_moe_gemv", FMT[st.fmt], ptr(st.w), ptr(st.scales), st.w_stride, st.s_stride, st.sr, st.sc,
+                ptr(idx), n_tasks, self.cfg.experts, ptr(x), x_div, ptr(y), st.R, st.C, self.ep_rank, self.ep_size, s)
+
+    def body(self, T: int, tail: bool = True, stream_ptr: int | None = None) -> None:
+        c = self.cfg
+        M = pad_rows(T)
+        g = self.bufs(M)
+        s = capi.stream_ptr() if stream_ptr is None else stream_ptr
+        H, Hq, Hk, D, I, E, k = c.hidden, c.q_heads, c.kv_heads, c.head_dim, c.inter, c.experts, c.top_k
+        K_ = self._k
+        y_prev = None
+        for i, L in enumerate(self.w.layers):
+            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(g["x"]), T, H, 0, s)
+            self._matvec(L.qkv, g["x"], g["qkv"], M, c.qkv_rows, H, s)
+            K_("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
+               ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
+               self.rs, 0, 0, self.cap, s)  # fmt: skip
+            K_("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["att"]), ptr(self.n0),
+               ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
+               ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
+            self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
+            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
+            # the MoE block: x.float(), the router's logits by the host-order GEMV, the picks, the experts, the sum
+            K_("btb_b200_widen_f32", ptr(g["x"]), ptr(g["xf"]), T * H, s)
+            K_("btb_b200_gemv_lane16_f32", ptr(L.router), ptr(g["xf"]), ptr(g["rl"]), T, E, H, s)
+            K_("btb_b200_moe_route", ptr(g["rl"]), E, E, k, c.router_mode, 1, ptr(g["idx"]), ptr(g["rw"]), T, s)
+            self._expert_gemv(L.gu, g["idx"], T * k, g["xf"], k, g["egu"], s)
+            K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
+            self._expert_gemv(L.dn, g["idx"], T * k, g["eh"], 1, g["edn"], s)
+            if self.ep_size > 1:
+                import torch.distributed as dist
+
+                dist.all_reduce(g["edn"][: T * k], group=self.group)
+            K_("btb_b200_moe_combine", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, s)
+            y_prev = g["y"]
+        if tail:
+            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(self.w.norm), c.eps, ptr(g["x"]), T, H, 0, s)
+            self._matvec(self.w.embed, g["x"], g["logits"], M, c.vocab, H, s)
+
+    def weight_bytes(self) -> int:
+        return self.cfg.weight_bytes_per_token()

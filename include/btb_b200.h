@@ -112,6 +112,45 @@ int btb_b200_argmax_bf16_static(const void* logits, int T, int V, void* out, voi
  * the length last behind a system fence. out_* null: only the advance. */
 int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance, void* stream);
 
+/* ---- the MoE block ------------------------------------------------------------------------------------------------
+ * btb_moe_route (btb_kernels.cu:861-948) and the host routers it mirrors. mode 0: f32 softmax over the E logits ->
+ * top-k by (p desc, index asc) -> p / sum(top k) (btb/engine/families/qwen4/router.py:42-50); mode 1: top-k of the
+ * logits -> softmax over the k (gpt-oss, btb/engine/host.py:187-191). logits [T, ls] bf16, or f32 when f32_logits;
+ * idx i32 [T,k], w bf16 [T,k]. */
+int btb_b200_moe_route(const void* logits, int ls, int E, int k, int mode, int f32_logits, void* idx, void* w, int T,
+                       void* stream);
+/* btb_gemv_lane16_f32_m{M} (btb_kernels.cu:1635-1682): the host's bf16 GEMV order on the card (16 lane sums a row,
+ * column c to lane c mod 16, reduce16's fold: native/src/gemv.rs:46-58,85-123). w [R,C] bf16, x [M,C] f32, y [M,R]
+ * f32; bit-equal to btb_gemv_bf16_rows. */
+int btb_b200_gemv_lane16_f32(const void* w, const void* x, void* y, int M, int R, int C, void* stream);
+/* btb_gemv_lane16_mx4_f32_m{M} (btb_kernels.cu:1684-1766): the same over MXFP4 as stored (blocks [R,C/32,16],
+ * scales [R,C/32] e8m0); bit-equal to btb_gemv_mxfp4_rows (native/src/lib.rs:137-160). */
+int btb_b200_gemv_lane16_mx4_f32(const void* blocks, const void* scales, const void* x, void* y, int M, int R, int C,
+                                 void* stream);
+/* the same over FP8 e4m3 + f32 [sr,sc] block scales, each weight bf16(e4m3 * scale); bit-equal to btb_gemv_fp8_rows
+ * (native/src/lib.rs:501-552, gemv.rs:2996-3085). */
+int btb_b200_gemv_lane16_fp8_f32(const void* w, const void* scales, int sr, int sc, const void* x, void* y, int M,
+                                 int R, int C, void* stream);
+/* `_Experts._one_row`'s grouped matvec (btb/engine/host.py:508-569; btb_gemv_*_group, native/src/lib.rs:86-104,
+ * 162-243) with the picks read on the card: task i multiplies expert idx[i]'s [R,C] matrix (fmt 0 bf16, 1 MXFP4,
+ * 2 FP8; w_stride/s_stride bytes between experts) with x row i / x_div; y f32 [n_tasks, R]. An index outside
+ * [0, E) is refused (status word). Expert parallelism: `w` holds this rank's experts only, expert e being local expert
+ * e / ep_size of rank e % ep_size; a task of another rank's expert writes a row of zeros (ep_size 1: everything). */
+int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr,
+                      int sc, const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C,
+                      int ep_rank, int ep_size, void* stream);
+/* the experts' middle (host.py:414-419): gu f32 [n,2I] to the row dtype (+ bias [E,2I] bf16 by idx), kind 0
+ * silu(gate) * up over halves (host.py:439-441), kind 1 gpt-oss's clamped GLU over interleaved lanes
+ * (host.py:444-450; btb/mxfp4_torch.py:146-153), every bf16 rounding of the torch ops kept; h f32 [n,I]. */
+int btb_b200_moe_act(const void* gu, void* h, const void* bias, const void* idx, int n, int I, int kind, float alpha,
+                     float limit, void* stream);
+/* host.py:426-431,565-569: out_e = bf16(down_e) (+ bias [E,H]) * w_e, summed one bf16 add at a time in ascending
+ * expert id from zero. dn f32 [T,k,H], y bf16 [T,H]. */
+int btb_b200_moe_combine(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T, int k, int H,
+                         void* stream);
+/* x.float() (host.py:525): bf16 [n] -> f32 [n] */
+int btb_b200_widen_f32(const void* x, void* y, int n, void* stream);
+
 /* ---- the whole step as one launch ---------------------------------------------------------------------------------
  * btb captures a decode step as a CUDA graph of ~330 kernel nodes (btb/engine/cuda.py:2101-2251 `_card_step_graph`
  * over `_card_body`, :1601-1837). btb_b200_step runs the same sequence - embed, every layer's kernels, the head, the

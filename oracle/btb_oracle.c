@@ -433,23 +433,26 @@ int orc_attn_decode(const uint16_t* q, const uint16_t* K, const uint16_t* V, uin
 /* router, argmax                                                                                          */
 /* ------------------------------------------------------------------------------------------------------- */
 
-int orc_moe_route(const uint16_t* logits, int ls, int E, int k, int mode, int32_t* idx, uint16_t* w, int T) {
+int orc_moe_route(const void* logits, int ls, int E, int k, int mode, int f32_logits, int32_t* idx, uint16_t* w,
+                  int T) {
     if (!logits || !idx || !w) return BTB_ERR_NULL;
     if (E <= 0 || k <= 0 || k > E || k > 32 || E > 4096) return BTB_ERR_DOMAIN;
     float* pr = (float*)malloc((size_t)E * sizeof(float));
+    float* lg = (float*)malloc((size_t)E * sizeof(float));
     for (int t = 0; t < T; ++t) {
-        const uint16_t* lr = logits + (size_t)t * ls;
+        for (int e = 0; e < E; ++e)
+            lg[e] = f32_logits ? ((const float*)logits)[(size_t)t * ls + e] : bf2f(((const uint16_t*)logits)[(size_t)t * ls + e]);
         float topv[32];
         int topi[32];
         if (mode == 0) {
             float m = NEG_INF;
-            for (int e = 0; e < E; ++e) m = fmaxf(m, bf2f(lr[e]));
+            for (int e = 0; e < E; ++e) m = fmaxf(m, lg[e]);
             /* thread tid of 256 sums its strided elements, then the 256 -> 1 tree */
             float red[256];
             for (int tid = 0; tid < 256; ++tid) {
                 float s = 0.f;
                 for (int e = tid; e < E; e += 256) {
-                    const float p = expf(bf2f(lr[e]) - m);
+                    const float p = expf(lg[e] - m);
                     pr[e] = p;
                     s += p;
                 }
@@ -459,7 +462,7 @@ int orc_moe_route(const uint16_t* logits, int ls, int E, int k, int mode, int32_
                 for (int tid = 0; tid < s; ++tid) red[tid] += red[tid + s];
             for (int e = 0; e < E; ++e) pr[e] = pr[e] / red[0];
         } else {
-            for (int e = 0; e < E; ++e) pr[e] = bf2f(lr[e]);
+            for (int e = 0; e < E; ++e) pr[e] = lg[e];
         }
         /* k rounds of the total order's maximum (value desc, index asc); a picked one leaves the field */
         unsigned char taken[4096];
@@ -496,6 +499,7 @@ int orc_moe_route(const uint16_t* logits, int ls, int E, int k, int mode, int32_
         }
     }
     free(pr);
+    free(lg);
     return BTB_OK;
 }
 

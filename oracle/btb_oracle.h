@@ -71,8 +71,9 @@ int orc_attn_decode(const uint16_t* q, const uint16_t* K, const uint16_t* V, uin
                     const int32_t* par, int T, int Hq, int Hk, int D, long hs, long rs, float scale, int win,
                     const int32_t* tbl, const float* sinks);
 /* native/cuda/btb_kernels.cu:861-948 (mode 0: softmax -> top-k -> renormalise) and btb/engine/host.py:187-191
- * (mode 1: top-k of the logits -> softmax over the k). idx [T,k] int32, w [T,k] bf16 bits. */
-int orc_moe_route(const uint16_t* logits, int ls, int E, int k, int mode, int32_t* idx, uint16_t* w, int T);
+ * (mode 1: top-k of the logits -> softmax over the k). logits [T, ls] bf16 bits, or f32 when f32_logits. idx [T,k]
+ * int32, w [T,k] bf16 bits. */
+int orc_moe_route(const void* logits, int ls, int E, int k, int mode, int f32_logits, int32_t* idx, uint16_t* w, int T);
 /* lowest-index argmax over bf16 logits rows, btb/engine/cuda.py:2237, native/src/sample.rs:57-67 */
 int orc_argmax_bf16(const uint16_t* logits, int T, int V, int64_t* out);
 

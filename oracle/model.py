@@ -226,3 +226,89 @@ class CardPath:
             lg = self.forward([toks[-1]])
             toks.append(int(O.argmax_bf16(lg)[0]))
         return toks
+
+
+# --------------------------------------------------------------------------------------------------------------
+# the MoE decoder: the card path's attention, the host's router and experts (btb/engine/host.py:175-191, 508-569)
+# --------------------------------------------------------------------------------------------------------------
+
+
+@dataclass
+class MoECfg(DenseCfg):
+    experts: int = 8
+    top_k: int = 2
+    router_mode: int = 0
+    glu_kind: int = 0
+    expert_fmt: str = "mx4"
+    alpha: float = 1.702
+    limit: float = 7.0
+
+
+class MoECardPath:
+    """layers: dicts with ln1, ln2, qkv, o, router (bf16 bits), wq, wk (or None), gu / dn: (fmt, w, scales) stacked
+    over ALL experts as stored. embed, norm: bf16 bits."""
+
+    def __init__(self, cfg: MoECfg, embed, norm, layers, cap: int = 512, tables=None):
+        self.cfg, self.embed, self.norm, self.layers = cfg, embed, norm, layers
+        self.cos, self.sin = rope_tables_bf16(cfg, cap) if tables is None else tables
+        self.K = np.zeros((cfg.layers, cap, cfg.kv_heads, cfg.head_dim), np.uint16)
+        self.V = np.zeros_like(self.K)
+        self.n = 0
+
+    @staticmethod
+    def expert_gemv(stack, e: int, x: np.ndarray) -> np.ndarray:
+        fmt, w, sc = stack
+        if fmt == "mx4":
+            R, G = w.shape[1], w.shape[2]
+            return O.cpu_gemv_mxfp4(w[e], sc[e], R, G * 32, x)
+        if fmt == "fp8":
+            R, C_ = w.shape[1], w.shape[2]
+            return O.cpu_gemv_fp8(w[e], sc[e], R, C_, x)
+        return O.cpu_gemv_bf16(w[e], x)
+
+    def moe_block(self, L, x_bits: np.ndarray) -> np.ndarray:
+        c = self.cfg
+        xf = O.bits_to_f32(x_bits)
+        logits = O.cpu_gemv_bf16(L["router"], xf)
+        idx, w = O.moe_route(logits, c.experts, c.top_k, c.router_mode)
+        T = xf.shape[0]
+        dn = np.zeros((T, c.top_k, c.hidden), np.float32)
+        for t in range(T):
+            for s in range(c.top_k):
+                e = int(idx[t, s])
+                gu = self.expert_gemv(L["gu"], e, xf[t : t + 1])
+                hmid = O.moe_act(gu, c.glu_kind, None, c.alpha, c.limit)
+                dn[t, s] = self.expert_gemv(L["dn"], e, hmid)[0]
+        return O.moe_combine(dn, idx, w)
+
+    def forward(self, ids, depth=None, parents=None) -> np.ndarray:
+        c = self.cfg
+        T, n0 = len(ids), self.n
+        depth = np.arange(T, dtype=np.int32) if depth is None else np.asarray(depth, np.int32)
+        par = np.arange(-1, T - 1, dtype=np.int32) if parents is None else np.asarray(parents, np.int32)
+        D, Hq, Hk = c.head_dim, c.q_heads, c.kv_heads
+        hs, rs = D, Hk * D
+        h = self.embed[np.asarray(ids)].copy()
+        y_prev = None
+        for i, L in enumerate(self.layers):
+            h, x = O.add_rmsnorm(h, y_prev, L["ln1"], c.eps)
+            qkv = O.gemv_card_bf16(L["qkv"], x)
+            q = O.norm_rope_kv(qkv, L.get("wq"), L.get("wk"), c.eps, self.cos, self.sin, n0, depth, self.K[i], self.V[i],
+                               Hq, Hk, D, hs, rs)
+            att = O.attn_decode(q, self.K[i], self.V[i], n0, par, Hq, Hk, D, hs, rs, float(D**-0.5))
+            y = O.gemv_card_bf16(L["o"], att)
+            h, x = O.add_rmsnorm(h, y, L["ln2"], c.eps)
+            y_prev = self.moe_block(L, x)
+        h, x = O.add_rmsnorm(h, y_prev, self.norm, c.eps)
+        self.n = n0 + T
+        return O.gemv_card_bf16(self.embed, x)
+
+    def greedy(self, prompt, n_new: int) -> list[int]:
+        lg = None
+        for a in range(0, len(prompt), 32):
+            lg = self.forward(prompt[a : a + 32])
+        toks = [int(O.argmax_bf16(lg[-1:])[0])]
+        while len(toks) < n_new:
+            lg = self.forward([toks[-1]])
+            toks.append(int(O.argmax_bf16(lg)[0]))
+        return toks

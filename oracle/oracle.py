@@ -231,12 +231,57 @@ def attn_decode(q, K, V, n0, par, Hq, Hk, D, hs, rs, scale, win=0, tbl=None, sin
 
 
 def moe_route(logits, E: int, k: int, mode: int):
-    logits = _u16(logits)
+    """logits [T, ls]: uint16 (bf16 bits) or float32"""
+    logits = np.ascontiguousarray(logits)
+    f32 = logits.dtype == np.float32
+    assert f32 or logits.dtype == np.uint16
     T, ls = logits.shape
     idx = np.empty((T, k), np.int32)
     w = np.empty((T, k), np.uint16)
-    _ck(lib().orc_moe_route(_p(logits), ls, E, k, mode, _p(idx), _p(w), T), "orc_moe_route")
+    _ck(lib().orc_moe_route(_p(logits), ls, E, k, mode, int(f32), _p(idx), _p(w), T), "orc_moe_route")
     return idx, w
+
+
+def bfround(f: np.ndarray) -> np.ndarray:
+    """f32 values rounded to the nearest bf16 (ties to even), still as f32"""
+    return bits_to_f32(f32_to_bits(np.asarray(f, np.float32)))
+
+
+def moe_act(gu: np.ndarray, kind: int, bias=None, alpha: float = 1.702, limit: float = 7.0) -> np.ndarray:
+    """the experts' middle (btb/engine/host.py:414-450): gu f32 [n, 2I] to the row dtype, the gated activation with
+    every torch op's bf16 rounding, back to f32 [n, I]. kind 0: silu(gate) * up over halves; kind 1: gpt-oss"""
+    gu = bfround(gu)
+    if bias is not None:
+        gu = bfround(gu + bits_to_f32(bias))
+    I = gu.shape[1] // 2
+    if kind == 0:
+        g, u = gu[:, :I], gu[:, I:]
+        with np.errstate(over="ignore"):
+            act = bfround((g / (np.float32(1) + np.exp(-g, dtype=np.float32))).astype(np.float32))
+        return bfround(act * u)
+    g, u = gu[:, 0::2], gu[:, 1::2]
+    g = np.minimum(g, np.float32(limit))
+    u = np.clip(u, np.float32(-limit), np.float32(limit))
+    t1 = bfround(g * np.float32(alpha))
+    with np.errstate(over="ignore"):
+        t2 = bfround((np.float32(1) / (np.float32(1) + np.exp(-t1, dtype=np.float32))).astype(np.float32))
+    glu = bfround(g * t2)
+    return bfround(bfround(u + np.float32(1)) * glu)
+
+
+def moe_combine(dn: np.ndarray, idx: np.ndarray, w_bits: np.ndarray, bias=None) -> np.ndarray:
+    """host.py:426-431,565-569: dn f32 [T, k, H]; out_e = bf16(dn_e) (+ bias) * w_e; the sum one bf16 add at a time in
+    ascending expert id from zero. Returns bf16 bits [T, H]."""
+    T, k, H = dn.shape
+    y = np.zeros((T, H), np.float32)
+    for t in range(T):
+        for s in np.argsort(idx[t], kind="stable"):
+            o = bfround(dn[t, s])
+            if bias is not None:
+                o = bfround(o + bits_to_f32(bias[idx[t, s]]))
+            o = bfround(o * bits_to_f32(w_bits[t, s : s + 1]))
+            y[t] = bfround(y[t] + o)
+    return f32_to_bits(y)
 
 
 def argmax_bf16(logits) -> np.ndarray:

@@ -1,0 +1,190 @@
+"""The MoE block on the card against the oracle: router (both orders), the 16-lane matvecs over bf16 / MXFP4 / FP8 as
+stored (bit-equal to the CPU tier's GEMV), the gated activations, the ordered sum, and small MoE models end to end."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import model as OM
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+from btb_b200 import capi  # noqa: E402
+from btb_b200 import moe as MO  # noqa: E402
+from btb_b200.capi import call, ptr  # noqa: E402
+
+DEV = "cuda"
+
+
+def s():
+    return capi.stream_ptr()
+
+
+def bits(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.fixture(autouse=True)
+def clean_status():
+    yield
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+
+
+@pytest.mark.parametrize("E,k,mode", [(32, 4, 1), (128, 8, 0), (8, 2, 0), (300, 5, 1)])
+@pytest.mark.parametrize("f32", [True, False])
+def test_router(E, k, mode, f32):
+    rng = np.random.default_rng(E + k)
+    T = 5
+    lg = rng.standard_normal((T, E)).astype(np.float32) * 2
+    lg[0, 3] = lg[0, 7]  # a tie: the lower index first
+    if not f32:
+        lgb = O.f32_to_bits(lg)
+        want_idx, want_w = O.moe_route(lgb, E, k, mode)
+        lt = torch.from_numpy(lgb.view(np.int16)).view(torch.bfloat16).to(DEV)
+    else:
+        want_idx, want_w = O.moe_route(lg, E, k, mode)
+        lt = torch.from_numpy(lg).to(DEV)
+    idx = torch.zeros(T, k, dtype=torch.int32, device=DEV)
+    w = torch.zeros(T, k, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_moe_route", ptr(lt), E, E, k, mode, int(f32), ptr(idx), ptr(w), T, s())
+    assert np.array_equal(idx.cpu().numpy(), want_idx)  # the picks are integers: exact
+    d = bits(w).astype(np.int32) - want_w.astype(np.int32)
+    assert np.max(np.abs(d)) <= 1  # expf on the card against libm: at most one bf16 step
+
+
+def _mx4(rng, n, R, C_):
+    return (rng.integers(0, 256, size=(n, R, C_ // 32, 16), dtype=np.uint8),
+            rng.integers(117, 130, size=(n, R, C_ // 32), dtype=np.uint8))
+
+
+def _fp8(rng, n, R, C_, sr, sc):
+    w = rng.integers(0, 256, size=(n, R, C_), dtype=np.uint8)
+    w[(w & 0x7F) == 0x7F] = 0x33
+    sc_ = O.bits_to_f32(O.f32_to_bits(rng.standard_normal((n, sr, sc)).astype(np.float32) * 0.02))
+    return w, sc_
+
+
+@pytest.mark.parametrize("R,C_", [(64, 128), (300, 2880), (5, 96)])
+def test_lane16_gemvs_equal_the_cpu_tier_bits(R, C_):
+    rng = np.random.default_rng(R + C_)
+    M = 3
+    x = rng.standard_normal((M, C_)).astype(np.float32)
+    xt = torch.from_numpy(x).to(DEV)
+    y = torch.zeros(M, R, dtype=torch.float32, device=DEV)
+    wb = O.f32_to_bits(rng.standard_normal((R, C_)).astype(np.float32) * 0.02)
+    wt = torch.from_numpy(wb.view(np.int16)).to(DEV)
+    call("btb_b200_gemv_lane16_f32", ptr(wt), ptr(xt), ptr(y), M, R, C_, s())
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), O.cpu_gemv_bf16(wb, x).view(np.uint32))
+    blocks, scales = _mx4(rng, 1, R, C_)
+    bt, st = torch.from_numpy(blocks[0]).to(DEV), torch.from_numpy(scales[0]).to(DEV)
+    call("btb_b200_gemv_lane16_mx4_f32", ptr(bt), ptr(st), ptr(xt), ptr(y), M, R, C_, s())
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), O.cpu_gemv_mxfp4(blocks[0], scales[0], R, C_, x).view(np.uint32))
+    if R % 1 == 0 and C_ % 32 == 0:
+        sr, sc = (2 if R % 2 == 0 else 1), (C_ // 32)
+        w8, s8 = _fp8(rng, 1, R, C_, sr, sc)
+        w8t, s8t = torch.from_numpy(w8[0]).to(DEV), torch.from_numpy(s8[0]).to(DEV)
+        call("btb_b200_gemv_lane16_fp8_f32", ptr(w8t), ptr(s8t), sr, sc, ptr(xt), ptr(y), M, R, C_, s())
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), O.cpu_gemv_fp8(w8[0], s8[0], R, C_, x).view(np.uint32))
+
+
+def test_mx4_lane16_every_byte_every_scale():
+    """all 256 bytes under all 256 scales through the card's widen (x = 1 at one column a row isolates a weight)"""
+    blocks = np.broadcast_to(np.arange(256, dtype=np.uint8)[None, :, None], (256, 256, 16)).copy().reshape(256 * 256, 1, 16)
+    scales = np.broadcast_to(np.arange(256, dtype=np.uint8)[:, None], (256, 256)).copy().reshape(256 * 256, 1)
+    R = 256 * 256
+    want = O.widen_mxfp4(blocks.reshape(R, 16), scales.reshape(R), R, 32)
+    bt, st = torch.from_numpy(blocks).to(DEV), torch.from_numpy(scales).to(DEV)
+    for col in (0, 1, 17):
+        x = np.zeros((1, 32), np.float32)
+        x[0, col] = 1.0
+        xt = torch.from_numpy(x).to(DEV)
+        y = torch.zeros(1, R, dtype=torch.float32, device=DEV)
+        call("btb_b200_gemv_lane16_mx4_f32", ptr(bt), ptr(st), ptr(xt), ptr(y), 1, R, 32, s())
+        got, ref = y.cpu().numpy()[0], want[:, col]
+        fin = np.isfinite(ref)
+        assert np.array_equal(got[fin].view(np.uint32) & 0x7FFFFFFF, (ref[fin] + np.float32(0)).view(np.uint32) & 0x7FFFFFFF)
+        assert np.array_equal(np.isnan(got), np.isnan(ref + np.float32(0)) | (~fin & np.isnan(got)))
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_act_and_combine(kind):
+    rng = np.random.default_rng(kind)
+    n, I, H, k, T = 8, 96, 160, 4, 2
+    gu = (rng.standard_normal((n, 2 * I)) * 3).astype(np.float32)
+    gt, ht = torch.from_numpy(gu).to(DEV), torch.zeros(n, I, dtype=torch.float32, device=DEV)
+    call("btb_b200_moe_act", ptr(gt), ptr(ht), 0, 0, n, I, kind, 1.702, 7.0, s())
+    want = O.moe_act(gu, kind)
+    got = ht.cpu().numpy()
+    d = O.f32_to_bits(got).astype(np.int32) - O.f32_to_bits(want).astype(np.int32)
+    assert np.max(np.abs(d)) <= (1 if kind == 0 else 2) and np.mean(d != 0) < 5e-3
+    dn = rng.standard_normal((T, k, H)).astype(np.float32)
+    idx = np.array([[5, 1, 7, 3], [0, 9, 2, 4]], np.int32)
+    w = O.f32_to_bits(rng.uniform(0.1, 0.4, size=(T, k)).astype(np.float32))
+    y = torch.zeros(T, H, dtype=torch.bfloat16, device=DEV)
+    keep = [torch.from_numpy(dn).to(DEV), torch.from_numpy(idx).to(DEV), torch.from_numpy(w.view(np.int16)).to(DEV)]
+    call("btb_b200_moe_combine", ptr(keep[0]), ptr(keep[1]), ptr(keep[2]), 0, ptr(y), T, k, H, s())
+    assert np.array_equal(bits(y), O.moe_combine(dn, idx, w))  # bf16 adds and multiplies are exact arithmetic
+
+
+def _oracle_of(mw: MO.MoEWeights, eng) -> OM.MoECardPath:
+    c = mw.cfg
+    oc = OM.MoECfg(c.hidden, c.layers, c.q_heads, c.kv_heads, c.head_dim, c.inter, c.vocab, c.theta, c.eps, c.qk_norm,
+                   c.experts, c.top_k, c.router_mode, c.glu_kind, c.expert_fmt, c.alpha, c.limit)
+    layers = []
+    for L in mw.layers:
+        def stack(st):
+            return (st.fmt, st.w.cpu().numpy() if st.fmt != "bf16" else bits(st.w),
+                    None if st.scales is None else st.scales.cpu().numpy())
+        layers.append({"ln1": bits(L.ln1), "ln2": bits(L.ln2), "qkv": bits(L.qkv), "o": bits(L.o), "router": bits(L.router),
+                       "wq": None if L.wq is None else bits(L.wq), "wk": None if L.wk is None else bits(L.wk),
+                       "gu": stack(L.gu), "dn": stack(L.dn)})
+    return OM.MoECardPath(oc, bits(mw.embed), bits(mw.norm), layers, cap=eng.cap, tables=(bits(eng.cos), bits(eng.sin)))
+
+
+SMALL = {
+    "gpt-oss-like": MO.MoEConfig("m1", 256, 2, 8, 2, 64, 128, 512, theta=150000.0, eps=1e-5, qk_norm=False, experts=8,
+                                 top_k=2, router_mode=1, glu_kind=1, expert_fmt="mx4"),
+    "qwen-moe-like": MO.MoEConfig("m2", 256, 2, 8, 2, 128, 128, 512, experts=16, top_k=4, router_mode=0, glu_kind=0,
+                                  expert_fmt="fp8"),
+}
+
+
+@pytest.mark.parametrize("name", list(SMALL))
+def test_moe_model_tracks_the_oracle(name):
+    cfg = SMALL[name]
+    mw = MO.synth_moe_weights(cfg, seed=1, on_cpu=True)
+    eng = MO.MoEEngine(mw, cap=512)
+    orc = _oracle_of(mw, eng)
+    rng = np.random.default_rng(0)
+    prompt = rng.integers(0, cfg.vocab, size=20)
+    lg = eng.forward(torch.from_numpy(prompt))
+    want = orc.forward(prompt.tolist())
+    got_f, want_f = O.bits_to_f32(bits(lg)), O.bits_to_f32(want)
+    assert np.max(np.abs(got_f - want_f)) <= 2.0**-6 * max(1.0, float(np.max(np.abs(want_f))))
+    # one more row: the step after the prompt
+    lg1 = eng.forward(torch.tensor([7]))
+    w1 = orc.forward([7])
+    assert np.max(np.abs(O.bits_to_f32(bits(lg1)) - O.bits_to_f32(w1))) <= 2.0**-6 * max(1.0, float(np.max(np.abs(O.bits_to_f32(w1)))))
+    assert eng.generate_greedy(prompt.tolist(), 6) == _oracle_of(mw, eng).greedy(prompt.tolist(), 6)
+
+
+def test_verify_rows_equal_steps_in_a_moe_model():
+    cfg = SMALL["qwen-moe-like"]
+    eng = MO.MoEEngine(MO.synth_moe_weights(cfg, seed=2, on_cpu=True), cap=512)
+    prompt = torch.arange(5, 30)
+    toks = eng.generate_greedy(prompt, 6)
+    eng.reset()
+    eng.prefill(prompt)
+    steps = []
+    for t in toks[:5]:
+        steps.append(bits(eng.forward(torch.tensor([t])))[0].copy())
+    eng.reset()
+    eng.prefill(prompt)
+    lg = bits(eng.forward(torch.tensor(toks[:5]), advance=False))
+    for t in range(5):
+        assert np.array_equal(lg[t], steps[t]), t
