@@ -49,6 +49,8 @@ struct GemvArgs {
     float eps;
     int centered;
     int T;               // live rows (rows T..M-1 of x are zeros)
+    const float* fscales;  // FP8: the [sr, sc] f32 grid
+    int fsc, fbm, fbn;     // its columns, a block's rows and columns
 };
 
 template <int M, int FMT, int XM, int NWT>
@@ -93,10 +95,11 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
             const uint32_t bar = smem_u32(bars + p_st);
             const uint32_t dst = smem_u32(ring + (size_t)p_st * sbytes);
             const size_t e0 = (size_t)p_row * C + c0;
-            if (FMT == F_BF16) {
-                mbar_expect_tx(bar, n * 2);
-                if (A.evict_first) bulk_g2s_hint(dst, A.w + e0 * 2, n * 2, bar, pol);
-                else bulk_g2s(dst, A.w + e0 * 2, n * 2, bar);
+            if (FMT == F_BF16 || FMT == F_FP8) {
+                const uint32_t nb = FMT == F_BF16 ? n * 2 : n;
+                mbar_expect_tx(bar, nb);
+                if (A.evict_first) bulk_g2s_hint(dst, A.w + e0 * (FMT == F_BF16 ? 2 : 1), nb, bar, pol);
+                else bulk_g2s(dst, A.w + e0 * (FMT == F_BF16 ? 2 : 1), nb, bar);
             } else {
                 mbar_expect_tx(bar, n + n / 2);
                 if (A.evict_first) {
@@ -150,13 +153,15 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
         const int c0 = c_seg * seg;
         const int nch = min(seg, C - c0) >> 3;  // the segment's chunks; its first chunk is global chunk c0 / 8
         const uint8_t* stg = ring + (size_t)c_st * sbytes;
-        int e0 = 0, e1 = 0;
+        WidenCtx wc;
+        wc.esc_idx = A.esc_idx, wc.esc_val = A.esc_val, wc.e0 = 0, wc.e1 = 0, wc.srow = nullptr, wc.bn = 8;
+        wc.table[0] = A.table[0], wc.table[1] = A.table[1], wc.table[2] = A.table[2], wc.table[3] = A.table[3];
         if (FMT == F_P12 && A.esc_row != nullptr) {
-            e0 = __ldg(A.esc_row + row);
-            e1 = __ldg(A.esc_row + row + 1);
+            wc.e0 = __ldg(A.esc_row + row);
+            wc.e1 = __ldg(A.esc_row + row + 1);
         }
-        consume_stage<M, FMT, XS>(acc, stg, seg, nch, c0, row, C, XS ? xs : A.x, A.esc_idx, A.esc_val, A.table, e0, e1,
-                                  lane);
+        if (FMT == F_FP8) wc.srow = A.fscales + (size_t)(row / A.fbm) * A.fsc, wc.bn = A.fbn;
+        consume_stage<M, FMT, XS>(acc, stg, seg, nch, c0, row, C, XS ? xs : A.x, wc, lane);
         // the stage is free once every lane has read it (the warp barrier orders their shared loads before the
         // elected lane's copy, as a consumer's release orders them in any TMA pipeline): refill it with the next item
         __syncwarp();
@@ -212,7 +217,7 @@ Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     p.xs = want_xs && (M * C * 2) <= t.x_smem_max;
     const int ring = t.ring_bytes;
     int per_warp = ring / NW;
-    int max_seg_el = t.seg_bytes / (FMT == F_BF16 ? 2 : 1);  // elements
+    int max_seg_el = t.seg_bytes / (FMT == F_BF16 ? 2 : 1);  // elements (pack12 and FP8: a byte and a bit each)
     max_seg_el = max(256, max_seg_el & ~255);
     int sb = 0;
     auto total = [&](int st) { return (p.xs ? xbytes : 0) + NW * st * sb + NW * st * 8; };
@@ -358,6 +363,28 @@ extern "C" int btb_b200_gemv_norm(const void* w, const void* hi4, const void* ta
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return p12 ? launch_m<F_P12, X_SMEM_NORM>(M, a, p, s) : launch_m<F_BF16, X_SMEM_NORM>(M, a, p, s);
+}
+
+// FP8 e4m3 weights with an f32 [sr, sc] block-scale grid, each weight the bf16 btb holds for it, widened in registers
+extern "C" int btb_b200_gemv_fp8(const void* w, const void* scales, int sr, int sc, const void* x, void* y, int M, int R,
+                                 int C, void* stream) {
+    int rc = check_dims(w, x, y, M, R, C);
+    if (rc) return rc;
+    if (scales == nullptr) return B2_ERR_NULL;
+    // a row's bytes are bulk-copied from its own offset (16-byte aligned: C a multiple of 16) and a chunk of eight
+    // columns lies in one scale block
+    if (sr <= 0 || sc <= 0 || R % sr || C % sc || (C & 15) || ((C / sc) & 7)) return B2_ERR_DOMAIN;
+    GemvArgs a{};
+    a.w = static_cast<const uint8_t*>(w);
+    a.fscales = static_cast<const float*>(scales);
+    a.fsc = sc, a.fbm = R / sr, a.fbn = C / sc;
+    a.x = static_cast<const bf16*>(x);
+    a.y = static_cast<bf16*>(y);
+    a.R = R, a.C = C;
+    Plan p = make_plan<F_FP8>(M, R, C, M <= 8);
+    a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return p.xs ? launch_m<F_FP8, X_SMEM>(M, a, p, s) : launch_m_global<F_FP8>(M, a, p, s);
 }
 
 extern "C" int btb_b200_gemv_silu_bf16(const void* w, const void* gu, void* y, int M, int R, int C, void* stream) {

@@ -6,14 +6,37 @@
 
 #include "common.cuh"
 
-enum Fmt { F_BF16 = 0, F_P12 = 1 };
+enum Fmt { F_BF16 = 0, F_P12 = 1, F_FP8 = 2 };
+
+// what a stage's widen needs beside the bytes: pack12's table and the row's escapes, FP8's scale row
+struct WidenCtx {
+    const int32_t* esc_idx;
+    const uint8_t* esc_val;
+    uint32_t table[4];
+    int e0, e1;         // the row's escapes are [e0, e1) of the ascending list
+    const float* srow;  // FP8: the row's scales, one per `bn` columns
+    int bn;
+};
 
 __device__ __forceinline__ uint4 ldcg16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
 // a stage's bytes for `n` elements of a row
 template <int FMT>
 __host__ __device__ constexpr int stage_bytes(int n) {
-    return FMT == F_BF16 ? n * 2 : n + n / 2;
+    return FMT == F_BF16 ? n * 2 : (FMT == F_P12 ? n + n / 2 : n);
+}
+
+// e4m3fn byte -> f32 from its bits, times the block's scale, to the nearest bf16 (ties to even) by integer arithmetic:
+// the value btb holds for an FP8 weight (native/src/gemv.rs:2996-3020, 3081; btb/fp8.py:97-100), as an f32
+__device__ __forceinline__ float fp8_held(uint32_t b, float scale) {
+    const uint32_t a = b & 0x7Fu;
+    float mag;
+    if (a == 0x7Fu) mag = __uint_as_float(0x7FC00000u);
+    else if (a < 8u) mag = __fmul_rn((float)a, 1.0f / 512.0f);
+    else mag = __uint_as_float((a << 20) + (120u << 23));
+    const float v = __fmul_rn(__uint_as_float(__float_as_uint(mag) | ((b & 0x80u) << 24)), scale);
+    const uint32_t u = __float_as_uint(v);
+    return __uint_as_float((u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u);
 }
 
 // the activation of the SwiGLU fold, native/cuda/btb_kernels.cu:159 of the reference: silu in f32 as torch computes it
@@ -149,30 +172,45 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
 // xv: x in shared memory [M, C] (XS) or in global memory (read-only path: the standalone kernels' wide passes only).
 template <int M, int FMT, bool XS>
 __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* stg, int seg, int nch, int c0, int row,
-                                              int C, const bf16* xv, const int32_t* esc_idx, const uint8_t* esc_val,
-                                              const uint32_t (&table)[4], int e0, int e1, int lane) {
+                                              int C, const bf16* xv, const WidenCtx& W, int lane) {
 #pragma unroll 4
     for (int lc = lane; lc < nch; lc += 32) {
-        uint32_t wp[4];
-        if (FMT == F_BF16) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(stg + lc * 16);
-            wp[0] = wv.x, wp[1] = wv.y, wp[2] = wv.z, wp[3] = wv.w;
-        } else {
-            const uint2 lo = *reinterpret_cast<const uint2*>(stg + lc * 8);
-            const uint32_t codes = *reinterpret_cast<const uint32_t*>(stg + seg + lc * 4);
-            p12_chunk(lo.x, lo.y, codes, table, wp);
-            // a code of 15 is an escape: its high byte comes from the row's list
-            const uint32_t f = codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u;
-            if (f != 0u && e1 > e0) {
+        float wf[8];
+        if (FMT == F_FP8) {
+            const uint2 wb = *reinterpret_cast<const uint2*>(stg + lc * 8);
+            const float sc = __ldg(W.srow + (c0 + lc * 8) / W.bn);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    if ((f >> (4 * e)) & 1u) {
-                        const int gi = (int)((size_t)row * C + c0 + lc * 8 + e);
-                        const uint32_t hb = p12_escape(esc_idx, esc_val, e0, e1, gi);
-                        const int sh = (e & 1) ? 24 : 8;
-                        wp[e >> 1] = (wp[e >> 1] & ~(0xffu << sh)) | (hb << sh);
+            for (int e = 0; e < 4; ++e) {
+                wf[e] = fp8_held((wb.x >> (8 * e)) & 0xffu, sc);
+                wf[4 + e] = fp8_held((wb.y >> (8 * e)) & 0xffu, sc);
+            }
+        } else {
+            uint32_t wp[4];
+            if (FMT == F_BF16) {
+                const uint4 wv = *reinterpret_cast<const uint4*>(stg + lc * 16);
+                wp[0] = wv.x, wp[1] = wv.y, wp[2] = wv.z, wp[3] = wv.w;
+            } else {
+                const uint2 lo = *reinterpret_cast<const uint2*>(stg + lc * 8);
+                const uint32_t codes = *reinterpret_cast<const uint32_t*>(stg + seg + lc * 4);
+                p12_chunk(lo.x, lo.y, codes, W.table, wp);
+                // a code of 15 is an escape: its high byte comes from the row's list
+                const uint32_t f = codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u;
+                if (f != 0u && W.e1 > W.e0) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        if ((f >> (4 * e)) & 1u) {
+                            const int gi = (int)((size_t)row * C + c0 + lc * 8 + e);
+                            const uint32_t hb = p12_escape(W.esc_idx, W.esc_val, W.e0, W.e1, gi);
+                            const int sh = (e & 1) ? 24 : 8;
+                            wp[e >> 1] = (wp[e >> 1] & ~(0xffu << sh)) | (hb << sh);
+                        }
                     }
                 }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                wf[2 * e] = bf_lo(wp[e]);
+                wf[2 * e + 1] = bf_hi(wp[e]);
             }
         }
 #pragma unroll
@@ -181,14 +219,14 @@ __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* st
             if (XS) x4 = *reinterpret_cast<const uint4*>(xv + (size_t)m * C + c0 + lc * 8);
             else x4 = __ldg(reinterpret_cast<const uint4*>(xv + (size_t)m * C + c0 + lc * 8));  // standalone wide passes
             float a = acc[m];
-            a = fmaf(bf_lo(wp[0]), bf_lo(x4.x), a);
-            a = fmaf(bf_hi(wp[0]), bf_hi(x4.x), a);
-            a = fmaf(bf_lo(wp[1]), bf_lo(x4.y), a);
-            a = fmaf(bf_hi(wp[1]), bf_hi(x4.y), a);
-            a = fmaf(bf_lo(wp[2]), bf_lo(x4.z), a);
-            a = fmaf(bf_hi(wp[2]), bf_hi(x4.z), a);
-            a = fmaf(bf_lo(wp[3]), bf_lo(x4.w), a);
-            a = fmaf(bf_hi(wp[3]), bf_hi(x4.w), a);
+            a = fmaf(wf[0], bf_lo(x4.x), a);
+            a = fmaf(wf[1], bf_hi(x4.x), a);
+            a = fmaf(wf[2], bf_lo(x4.y), a);
+            a = fmaf(wf[3], bf_hi(x4.y), a);
+            a = fmaf(wf[4], bf_lo(x4.z), a);
+            a = fmaf(wf[5], bf_hi(x4.z), a);
+            a = fmaf(wf[6], bf_lo(x4.w), a);
+            a = fmaf(wf[7], bf_hi(x4.w), a);
             acc[m] = a;
         }
     }

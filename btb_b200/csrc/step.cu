@@ -277,17 +277,17 @@ __global__ void __launch_bounds__(NTS, 1) step_kernel(const StepArgs A) {
                     const int c0 = c_seg * seg;
                     const int nch = min(seg, C - c0) >> 3;
                     const uint8_t* stg = ring + (size_t)c_st * cap_b;
+                    WidenCtx wc;
+                    wc.esc_idx = op.esc_idx, wc.esc_val = op.esc_val, wc.e0 = 0, wc.e1 = 0, wc.srow = nullptr, wc.bn = 8;
+                    wc.table[0] = table[0], wc.table[1] = table[1], wc.table[2] = table[2], wc.table[3] = table[3];
                     if (fmt == F_BF16) {
-                        consume_stage<M, F_BF16, true>(acc, stg, seg, nch, c0, c_row, C, xs, nullptr, nullptr, table, 0, 0,
-                                                       lane);
+                        consume_stage<M, F_BF16, true>(acc, stg, seg, nch, c0, c_row, C, xs, wc, lane);
                     } else {
-                        int e0 = 0, e1 = 0;
                         if (op.esc_row != nullptr) {
-                            e0 = __ldg(op.esc_row + c_row);
-                            e1 = __ldg(op.esc_row + c_row + 1);
+                            wc.e0 = __ldg(op.esc_row + c_row);
+                            wc.e1 = __ldg(op.esc_row + c_row + 1);
                         }
-                        consume_stage<M, F_P12, true>(acc, stg, seg, nch, c0, c_row, C, xs, op.esc_idx, op.esc_val, table,
-                                                      e0, e1, lane);
+                        consume_stage<M, F_P12, true>(acc, stg, seg, nch, c0, c_row, C, xs, wc, lane);
                     }
                     __syncwarp();
                     --inflight;

@@ -93,6 +93,20 @@ class P12Matrix:
         return self.lo.numel() + self.hi4.numel() + 5 * self.n_esc
 
 
+class FP8Matrix:
+    """one FP8 matrix on the card as stored (btb/fp8.py:65-94 `F8Weight`): e4m3 bytes [R, C] and an f32 [sr, sc] grid"""
+
+    def __init__(self, w: torch.Tensor, scales: torch.Tensor):
+        self.w = w.contiguous().view(torch.uint8)
+        self.scales = scales.float().contiguous()
+        self.rows, self.cols = int(w.shape[0]), int(w.shape[1])
+        self.sr, self.sc = int(scales.shape[0]), int(scales.shape[1])
+
+    @property
+    def nbytes(self) -> int:
+        return self.w.numel() + 4 * self.scales.numel()
+
+
 @dataclass
 class LayerWeights:
     ln1: torch.Tensor
@@ -225,6 +239,8 @@ class CardEngine:
         if isinstance(W, P12Matrix):
             self._k("btb_b200_gemv_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),
                     ptr(W.esc_row), ptr(x), ptr(y), M, R, C_, s)  # fmt: skip
+        elif isinstance(W, FP8Matrix):
+            self._k("btb_b200_gemv_fp8", ptr(W.w), ptr(W.scales), W.sr, W.sc, ptr(x), ptr(y), M, R, C_, s)
         else:
             self._k("btb_b200_gemv_bf16", ptr(W), ptr(x), ptr(y), M, R, C_, s)
 

@@ -21,7 +21,7 @@ import torch
 
 from . import capi
 from .capi import call, ptr
-from .engine import CardEngine, DenseConfig, pad_rows
+from .engine import CardEngine, DenseConfig, FP8Matrix, pad_rows
 
 FMT = {"bf16": 0, "mx4": 1, "fp8": 2}
 
@@ -35,6 +35,7 @@ class MoEConfig(DenseConfig):
     expert_fmt: str = "mx4"
     alpha: float = 1.702
     limit: float = 7.0
+    dense_fmt: str = "bf16"  # the attention linears: bf16, or FP8 e4m3 with 128 x 128 block scales ("fp8")
 
     def expert_bytes(self) -> int:
         """one expert's stored bytes (gate_up + down)"""
@@ -46,14 +47,15 @@ class MoEConfig(DenseConfig):
         return 2 * n
 
     def weight_bytes_per_token(self, storage: str = "bf16") -> int:
-        att = 2 * self.hidden * (self.qkv_rows + self.q_heads * self.head_dim) + 2 * self.experts * self.hidden
+        att = (2 if self.dense_fmt == "bf16" else 1) * self.hidden * (self.qkv_rows + self.q_heads * self.head_dim)
+        att += 2 * self.experts * self.hidden
         return self.layers * (att + self.top_k * self.expert_bytes()) + self.vocab * self.hidden * 2
 
 
 GPT_OSS_20B = MoEConfig("gpt-oss-20b", 2880, 24, 64, 8, 64, 2880, 201088, theta=150000.0, eps=1e-5, qk_norm=False,
                         experts=32, top_k=4, router_mode=1, glu_kind=1, expert_fmt="mx4")  # fmt: skip
 QWEN3_30B_A3B = MoEConfig("qwen3-30b-a3b", 2048, 48, 32, 4, 128, 768, 151936, experts=128, top_k=8, router_mode=0,
-                          glu_kind=0, expert_fmt="fp8")  # fmt: skip
+                          glu_kind=0, expert_fmt="fp8", dense_fmt="fp8")  # fmt: skip
 
 
 @dataclass
@@ -81,8 +83,8 @@ class ExpertStack:
 class MoELayer:
     ln1: torch.Tensor
     ln2: torch.Tensor
-    qkv: torch.Tensor
-    o: torch.Tensor
+    qkv: Any  # bf16 [rows, H] or FP8Matrix
+    o: Any
     router: torch.Tensor  # [E, H] bf16
     gu: ExpertStack
     dn: ExpertStack
@@ -141,11 +143,22 @@ def synth_moe_weights(cfg: MoEConfig, seed: int = 0, device: Any = "cuda", on_cp
             st.scales = st.scales.index_select(0, sel).contiguous()
         return st
 
+    def dense(r: int, c: int) -> Any:
+        if cfg.dense_fmt == "bf16":
+            return lin(r, c)
+        w = torch.randint(0, 256, (r, c), generator=g, device=gdev, dtype=torch.uint8)
+        w = torch.where((w & 0x7F) == 0x7F, w & 0xF0, w)
+        sc = (torch.randn(r // 128, c // 128, generator=g, device=gdev) * 0.02).to(torch.bfloat16).float()
+        return FP8Matrix(w.to(device), sc.to(device))
+
     H, D, I, E = cfg.hidden, cfg.head_dim, cfg.inter, cfg.experts
     mw = MoEWeights(cfg, lin(cfg.vocab, H), ones(H), ep_rank=ep_rank, ep_size=ep_size)
     for _ in range(cfg.layers):
-        qkv = torch.cat([lin(cfg.q_heads * D, H), lin(cfg.kv_heads * D, H), lin(cfg.kv_heads * D, H)])
-        o = lin(H, cfg.q_heads * D)
+        if cfg.dense_fmt == "bf16":
+            qkv = torch.cat([lin(cfg.q_heads * D, H), lin(cfg.kv_heads * D, H), lin(cfg.kv_heads * D, H)])
+        else:
+            qkv = dense(cfg.qkv_rows, H)
+        o = dense(H, cfg.q_heads * D)
         router = lin(E, H)
         gu = keep(synth_expert_stack(cfg, g, E, 2 * I, H, device))
         dn = keep(synth_expert_stack(cfg, g, E, H, I, device))

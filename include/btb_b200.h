@@ -53,6 +53,12 @@ int btb_b200_gemv_silu_bf16(const void* w, const void* gu, void* y, int M, int R
  * or past its start (btb_b200_p12_rows builds it; null when there are no escapes). C a multiple of 32. */
 int btb_b200_gemv_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
                       const void* esc_row, const void* x, void* y, int M, int R, int C, void* stream);
+/* FP8 e4m3 weights + f32 [sr, sc] block scales (btb/fp8.py:36-100; the CPU form is btb_gemv_fp8_rows,
+ * native/src/lib.rs:501-552): on a card the reference widens them to a bf16 copy at load (fp8.held) and runs
+ * btb_gemv_bf16 - the output here is that output to the bit, each weight bf16(e4m3 * scale) made in registers.
+ * C a multiple of 16, a scale block's columns a multiple of 8. */
+int btb_b200_gemv_fp8(const void* w, const void* scales, int sr, int sc, const void* x, void* y, int M, int R, int C,
+                      void* stream);
 /* btb_gemv_silu over pack12 weights: the fold of btb_b200_gemv_silu_bf16 with the widen of btb_b200_gemv_p12. */
 int btb_b200_gemv_silu_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx,
                            const void* esc_val, const void* esc_row, const void* gu, void* y, int M, int R, int C,

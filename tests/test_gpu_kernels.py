@@ -217,6 +217,23 @@ def test_gemv_p12_equals_bf16_gemv_bits(R, Cc, dense, M):
         assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
 
 
+@pytest.mark.parametrize("R,Cc,sr,sc", [(256, 256, 2, 2), (384, 2048, 3, 16), (128, 768, 1, 6), (40, 64, 5, 1)])
+@pytest.mark.parametrize("M", [1, 8, 16])
+def test_gemv_fp8_equals_bf16_gemv_over_held_weights(R, Cc, sr, sc, M):
+    rng = np.random.default_rng(R + Cc + M)
+    w8 = rng.integers(0, 256, size=(R, Cc), dtype=np.uint8)
+    w8[(w8 & 0x7F) == 0x7F] = 0x2A
+    scales = O.bits_to_f32(O.f32_to_bits(rng.standard_normal((sr, sc)).astype(np.float32) * 0.02))
+    x = rand_bf(rng, (M, Cc))
+    held = O.widen_fp8(w8, scales, R, Cc)
+    want = O.gemv_card_bf16(held, x)
+    assert np.array_equal(want, O.gemv_card_fp8(w8, scales, x, R, Cc))
+    wt, st, xt = torch.from_numpy(w8).to(DEV), torch.from_numpy(scales).to(DEV), bf(x)
+    y = torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_gemv_fp8", ptr(wt), ptr(st), sr, sc, ptr(xt), ptr(y), M, R, Cc, s())
+    assert np.array_equal(bits(y), want)
+
+
 # ---- the small kernels -------------------------------------------------------------------------------------------
 
 
