@@ -210,6 +210,44 @@ def run_reference(args, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def tp_synth_shard(cfg, rank: int, world: int):
+    """this rank's share of a seeded dense model, drawn shard by shard on the card (the whole model may not fit one
+    GPU): every rank draws the same per-tensor streams and keeps its rows"""
+    import torch
+
+    from btb_b200 import engine as E
+    from btb_b200 import parallel as P
+
+    def lin(seed: int, r: int, c: int, lo: int, hi: int):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        out = torch.empty(hi - lo, c, dtype=torch.bfloat16, device="cuda")
+        step = 4096
+        for a in range(0, r, step):  # draw in row blocks, keep the overlap with [lo, hi)
+            b = min(r, a + step)
+            blk = (torch.randn(b - a, c, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+            x, y = max(a, lo), min(b, hi)
+            if x < y:
+                out[x - lo : y - lo] = blk[x - a : y - a]
+        return out
+
+    H, D, I = cfg.hidden, cfg.head_dim, cfg.inter
+    ones = lambda n: torch.ones(n, dtype=torch.bfloat16, device="cuda")  # noqa: E731
+    vl, vh = P.row_shard(cfg.vocab, rank, world)
+    hl, hh = P.row_shard(H, rank, world)
+    il, ih = P.row_shard(I, rank, world)
+    ql, qh = P.row_shard(cfg.q_heads * D, rank, world)
+    kl, kh = P.row_shard(cfg.kv_heads * D, rank, world)
+    mw = E.ModelWeights(cfg, lin(1, cfg.vocab, H, vl, vh), ones(H))
+    for i in range(cfg.layers):
+        s0 = 100 + 10 * i
+        qkv = torch.cat([lin(s0, cfg.q_heads * D, H, ql, qh), lin(s0 + 1, cfg.kv_heads * D, H, kl, kh),
+                         lin(s0 + 2, cfg.kv_heads * D, H, kl, kh)])
+        gu = torch.cat([lin(s0 + 4, I, H, il, ih), lin(s0 + 5, I, H, il, ih)])
+        mw.layers.append(E.LayerWeights(ones(H), ones(H), qkv, lin(s0 + 3, H, cfg.q_heads * D, hl, hh), gu,
+                                        lin(s0 + 6, H, I, hl, hh), None, None))
+    return mw
+
+
 def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     import torch
 
@@ -222,20 +260,55 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         import torch.distributed as dist  # noqa: PLC0415
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    cfg = E.QWEN3_4B
-    storage = "p12" if args.workload.endswith("p12") else "bf16"
-    if args.pdl is not None:
-        capi.set_tuning(pdl=args.pdl)
+    import dataclasses
+
     K, W = args.steps, max(args.warmup, 3)
     cap = ((PROMPT + 2 * (K + W) + 64 + 511) // 512) * 512
-    mw = E.synth_weights(cfg, seed=0, storage=storage)
-    eng = E.CardEngine(mw, cap=cap)
+    storage, parallelism = "bf16", ("replicas only" if world > 1 else "1 gpu")
+    if args.pdl is not None:
+        capi.set_tuning(pdl=args.pdl)
+    if args.workload.startswith("qwen3-4b"):
+        cfg = E.QWEN3_4B if not args.layers else dataclasses.replace(E.QWEN3_4B, layers=args.layers)
+        storage = "p12" if args.workload.endswith("p12") else "bf16"
+        mw = E.synth_weights(cfg, seed=0, storage=storage)
+        eng = E.CardEngine(mw, cap=cap, step_kernel=bool(args.step_kernel))
+    elif args.workload in ("gpt-oss-20b", "qwen3-30b-a3b"):
+        from btb_b200 import moe as MO
+
+        cfg = MO.GPT_OSS_20B if args.workload == "gpt-oss-20b" else MO.QWEN3_30B_A3B
+        if args.layers:
+            cfg = dataclasses.replace(cfg, layers=args.layers)
+        storage = cfg.expert_fmt
+        mw = MO.synth_moe_weights(cfg, seed=0, ep_rank=rank, ep_size=world)
+        eng = MO.MoEEngine(mw, cap=cap)
+        parallelism = f"ep{world}" if world > 1 else "1 gpu"
+    else:
+        from btb_b200 import parallel as P
+
+        cfg = E.LLAMA31_70B if not args.layers else dataclasses.replace(E.LLAMA31_70B, layers=args.layers)
+        ctx = args.context or 32768
+        cap = ((ctx + 2 * (K + W) + 64 + 511) // 512) * 512
+        shard = tp_synth_shard(cfg, rank, world)
+        eng = P.TPEngine(cfg, shard, rank, world, cap=cap)
+        mw = shard
+        parallelism = f"tp{world}" if world > 1 else "1 gpu"
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (PROMPT,), generator=g)
     eng.reset()
-    last = eng.prefill(prompt)
-    first = int(last.float().argmax(-1))
-    eng.bufs(1)["ids"][0] = first
+    if args.workload == "llama-70b":
+        # the metric excludes prefill: the 32768-row context is seeded synthetic cache rows (bf16 N(0, 1)), not a
+        # prefilled prompt - a chain-pass prefill of that length through the decode kernels would take minutes
+        ctx = args.context or 32768
+        gk = torch.Generator(device="cuda").manual_seed(1)
+        for i in range(cfg.layers):
+            eng.K[i][:ctx].normal_(generator=gk)
+            eng.V[i][:ctx].normal_(generator=gk)
+        eng.n0.fill_(ctx)
+        eng.bufs(1)["ids"][0] = 1
+    else:
+        last = eng.prefill(prompt)
+        first = int(last.float().argmax(-1)) if not hasattr(eng, "tp_bufs") else 1
+        eng.bufs(1)["ids"][0] = first
     graph = eng.step_graph(args.graph_steps, publish=True)
     reps = lambda n: -(-n // args.graph_steps)  # noqa: E731
 
@@ -283,8 +356,12 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     g1 = eng.bufs(1)
     s = capi.stream_ptr()
 
+    dense_model = args.workload.startswith("qwen3-4b")
+
     def gemvs():
         H, D, I = cfg.hidden, cfg.head_dim, cfg.inter
+        if not dense_model:
+            return
         for L in mw.layers:
             eng._matvec(L.qkv, g1["x"], g1["qkv"], 1, cfg.qkv_rows, H, s)
             eng._matvec(L.o, g1["att"], g1["y"], 1, H, cfg.q_heads * D, s)
@@ -293,7 +370,7 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         eng._matvec(mw.embed, g1["x"], g1["logits"], 1, cfg.vocab, H, s)
 
     n_gemv = 4 * cfg.layers + 1
-    for _ in range(3):
+    for _ in range(3 if dense_model else 0):
         gemvs()
     torch.cuda.synchronize()
     e0.record()
@@ -302,8 +379,8 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         gemvs()
     e1.record()
     torch.cuda.synchronize()
-    gemv_ms = e0.elapsed_time(e1) / ROUNDS
-    wbytes = eng.weight_bytes()
+    gemv_ms = max(e0.elapsed_time(e1) / ROUNDS, 1e-6)
+    wbytes = eng.weight_bytes() if dense_model else 0
     # algorithmic bytes of one token's GEMVs: the weights as stored, plus each launch's x and y vectors
     H_, A_, I_ = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.inter
     abytes = wbytes + cfg.layers * 2 * (3 * H_ + cfg.qkv_rows + A_ + 3 * I_ + H_) + 2 * (H_ + cfg.vocab)
@@ -317,8 +394,10 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": world, "steps": steps_done, "warmup": W,
         "ms_per_step": ms / steps_done, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if storage == "bf16" else "bf16 (pack12 weights widened in registers)", "data": "synthetic",
-        "config": {"workload": f"qwen3-4b-shape {storage}, batch 1, greedy decode after a 128-token prompt",
-                   "parallelism": "replicas only" if world > 1 else "1 gpu", "graph_steps": args.graph_steps,
+        "config": {"workload": f"{cfg.name}-shape {storage}, batch 1, greedy decode after a 128-token prompt"
+                   if args.workload != "llama-70b" else f"{cfg.name}-shape bf16, batch 1, greedy decode over a "
+                   f"{args.context or 32768}-row synthetic cache",
+                   "parallelism": parallelism, "graph_steps": args.graph_steps, "step_kernel": args.step_kernel,
                    "l2": "weights per step 8.0 GB > L2 126 MB (inputs larger than L2)", "pdl": args.pdl,
                    "bytes_per_token": cfg.weight_bytes_per_token(storage)},
         "clocks": clk.summary(),
@@ -327,7 +406,17 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         "roofline": roof,
         "token_roofline_frac": (cfg.weight_bytes_per_token(storage) * tps / world / 1e9) / peak,
     }  # fmt: skip
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if not dense_model:
+        line["roofline"] = None
+        line["metric"] = f"decode tok/s @bs1 ({cfg.name} shape)"
+    if args.workload != "qwen3-4b-bf16" and args.workload.startswith("qwen3-4b"):
+        line["metric"] = "decode tok/s @bs1 (Qwen3-4B shape, pack12 weights)"
+    if world > 1 and parallelism != "replicas only":
+        line["value"] = tps / world  # one model over all ranks: the job decodes one stream
+        line["e2e"]["value"] = e2e / world
+        line["scaling"] = "strong"
+        line["token_roofline_frac"] = None
+    if rank == 0 and world == 1 and not args.no_cpu and args.workload == "qwen3-4b-bf16":
         hw = host_weights_from_engine(mw) if storage == "bf16" else host_weights_synth(cfg)
         from oracle import oracle as O
 
@@ -337,7 +426,11 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
-        dist.destroy_process_group()
+        # every rank is past its last collective: leave without a collective teardown
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 # per-launch DRAM traffic of the dominant kernel from the committed ncu summary (profiles/), filled once captured
@@ -350,7 +443,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="qwen3-4b-bf16", choices=["qwen3-4b-bf16", "qwen3-4b-p12"])
+    ap.add_argument("--workload", default="qwen3-4b-bf16",
+                    choices=["qwen3-4b-bf16", "qwen3-4b-p12", "gpt-oss-20b", "qwen3-30b-a3b", "llama-70b"])
+    ap.add_argument("--step-kernel", type=int, default=0, help="1: the whole step as one persistent kernel")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0: the config's)")
+    ap.add_argument("--context", type=int, default=0, help="llama-70b: rows of synthetic cache standing before the step")
     ap.add_argument("--graph-steps", type=int, default=1)
     ap.add_argument("--pdl", type=int, default=None)
     ap.add_argument("--cpu-steps", type=int, default=4)

@@ -175,7 +175,7 @@ class CardEngine:
     """one model on one card: its cache arena, pass buffers, step graph and greedy loop"""
 
     def __init__(self, weights: ModelWeights, cap: int = 4096, silu_fold: bool = True, fuse_norm: bool = True,
-                 step_kernel: bool = True, device: Any = "cuda"):
+                 step_kernel: bool = False, device: Any = "cuda"):
         capi.lib()  # fail here, loudly, when the library is not built
         if not torch.cuda.is_available():
             raise RuntimeError("btb_b200 needs a CUDA device: there is no CPU path")

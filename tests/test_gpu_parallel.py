@@ -39,5 +39,5 @@ def test_two_ranks_equal_one_gpu():
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
            "--master-port", "29611", os.path.join(HERE, "mp_gpu_check.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0 and "multi-gpu ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
