@@ -189,6 +189,41 @@ __global__ void publish_step(const PublishArgs A) {
     }
 }
 
+// ---- the accepted branch's rows gathered to the cache's front (btb/engine/cuda.py:3563-3575 `ad`) -------------------
+// A verify pass wrote its T rows at slots n0 .. n0 + T - 1; the kept path's node path[j] moves to slot n0 + j. Nodes
+// are numbered parents first, so path[j] >= j and the moves run in ascending j: a row is read before its slot is
+// written. One block per (layer, K or V); the block's threads copy a row, then the next.
+struct CommitArgs {
+    bf16* K;
+    bf16* V;
+    const int* n0p;
+    const int* path;
+    const int* tbl;
+    long long layer_stride, rs;
+    int len, row_el, cap;
+};
+__global__ void __launch_bounds__(256) kv_commit(const CommitArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    bf16* base = (blockIdx.y == 0 ? A.K : A.V) + (size_t)blockIdx.x * A.layer_stride;
+    const int n0 = *A.n0p;
+    for (int j = 0; j < A.len; ++j) {
+        const int p = A.path[j];
+        if (p < j || n0 + p >= A.cap) {  // not a parents-first path, or past the cache: refuse, move nothing more
+            if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) b2_fail(B2_ERR_DOMAIN);
+            return;
+        }
+        if (p != j) {
+            int src = n0 + p, dst = n0 + j;
+            if (A.tbl != nullptr) src = A.tbl[src], dst = A.tbl[dst];
+            const uint4* s4 = reinterpret_cast<const uint4*>(base + (size_t)src * A.rs);
+            uint4* d4 = reinterpret_cast<uint4*>(base + (size_t)dst * A.rs);
+            for (int i = threadIdx.x; i < A.row_el / 8; i += 256) d4[i] = s4[i];
+        }
+        __syncthreads();
+    }
+}
+
 }  // namespace
 
 // ---- C-ABI ------------------------------------------------------------------------------------------------------------
@@ -286,6 +321,17 @@ extern "C" int btb_b200_argmax_bf16_static(const void* logits, int T, int V, voi
         return B2_ERR_CUDA;
     }
     return btb_b200_argmax_bf16(logits, T, V, addr[dev], out, stream);
+}
+
+extern "C" int btb_b200_kv_commit(void* K, void* V, long long layer_stride, int layers, const void* n0p, const void* path,
+                                  int len, int row_el, long long rs, const void* tbl, int cap, void* stream) {
+    if (!K || !V || !n0p || !path) return B2_ERR_NULL;
+    if (layers <= 0 || len <= 0 || len > 32 || row_el <= 0 || (row_el & 7) || (rs & 7) || rs < row_el || cap <= 0 ||
+        (reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15) || (layer_stride & 7))
+        return B2_ERR_DOMAIN;
+    CommitArgs a{static_cast<bf16*>(K), static_cast<bf16*>(V), static_cast<const int*>(n0p), static_cast<const int*>(path),
+                 static_cast<const int*>(tbl), layer_stride, rs, len, row_el, cap};
+    return b2_launch((const void*)kv_commit, dim3(layers, 2), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
 }
 
 extern "C" int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance,

@@ -407,6 +407,13 @@ class CardEngine:
             toks.append(int(self.pin_tok[0]))
         return toks
 
+    def generate_speculative(self, prompt: Any, max_new: int, budget: int = 8, v_max: int = 8) -> tuple[list[int], dict]:
+        """greedy decode with n-gram tree drafts verified a tree a pass (btb/engine/generate.py:682-795); the tokens
+        are generate_greedy's"""
+        from .draft import generate_speculative
+
+        return generate_speculative(self, prompt, max_new, budget, v_max)
+
     def step(self, token: int) -> int:
         """the public one-token call: the token from pinned host memory to the card, one step, the next token back"""
         g = self.bufs(1)

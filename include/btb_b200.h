@@ -114,6 +114,12 @@ size_t btb_b200_argmax_scratch_bytes(int T);
  * make that call before starting any stream capture. All calls share the one array: two calls whose kernels may
  * overlap on the device (different streams) race on it - keep them on one stream or order them yourself. */
 int btb_b200_argmax_bf16_static(const void* logits, int T, int V, void* out, void* stream);
+/* the tree commit (btb/engine/cuda.py:3535-3575 `ad`): a verify pass's accepted path gathered in place - node path[j]'s
+ * row (slot n0 + path[j]) moves to slot n0 + j in every layer's K and V. K, V: layer 0's arenas, `layer_stride`
+ * elements to the next layer's, a row `row_el` elements at stride `rs`. path i32 [len] on the card, parents first
+ * (path[j] >= j; else refused through the status word). n0 is not advanced here (btb_b200_publish does). */
+int btb_b200_kv_commit(void* K, void* V, long long layer_stride, int layers, const void* n0p, const void* path, int len,
+                       int row_el, long long rs, const void* tbl, int cap, void* stream);
 /* btb_publish (btb_kernels.cu:455-465): n0 += advance, then token, device clock (ns) and length to pinned host memory,
  * the length last behind a system fence. out_* null: only the advance. */
 int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance, void* stream);

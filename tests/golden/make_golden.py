@@ -2,7 +2,7 @@
 
 Run once where the reference is mounted (``python tests/golden/make_golden.py /root/reference``); the outputs are
 committed and the tests read only them. Everything here is produced by IMPORTING the reference's own Python codecs
-(``btb.pack12``, ``btb.mxfp4``, ``btb.fp8``, ``btb.sampling``) or by reading its banked test
+(``btb.pack12``, ``btb.mxfp4``, ``btb.fp8``, ``btb.sampling``, ``btb.draft``) or by reading its banked test
 fixtures (``tests/fixtures/tiny_qwen3*``, ``tests/fixtures/receipts_qwen3.pt``), never by re-deriving a value.
 
 Outputs
@@ -11,6 +11,7 @@ Outputs
   tiny_qwen3.npz   the tiny Qwen3 fixture's weights (bf16 bits), its pack12 and FP8 stores' parts, and the receipts
                    banked by the reference's CPU path (prompt/tree/next logits, per-layer K/V, greedy tokens)
   sampling.npz     key_for() values for seeded (seed, position) pairs
+  drafts.json      n-gram chains and merged trees from the reference's proposer over seeded token streams
 """
 
 from __future__ import annotations
@@ -146,6 +147,44 @@ def sampling(ref: str, out: dict) -> None:
     out["uniform"] = S._hash_uniform(key, idx).numpy()
 
 
+def drafts(ref: str) -> dict:
+    """seeded token streams through the reference's n-gram proposer and its chain merge: the chains proposed after
+    every few tokens and the trees built from them"""
+    import random
+
+    import ast
+
+    from btb.draft import NGramProposer
+
+    # btb.engine.generate imports a transformers class this image's version lacks; its tree builder is a plain
+    # function, so it is taken from the module's source and run on its own
+    src = open(os.path.join(ref, "btb", "engine", "generate.py")).read()
+    fn = next(n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef) and n.name == "_chains_tree")
+    ns: dict = {}
+    exec("from __future__ import annotations\n" + ast.get_source_segment(src, fn), ns)  # noqa: S102
+    _chains_tree = ns["_chains_tree"]
+
+    cases = []
+    for seed, vocab, n, kw in ((0, 6, 160, {}), (1, 3, 120, {"n_max": 3, "n_min": 1, "followers": 2}),
+                               (2, 40, 200, {"n_max": 5, "n_min": 2, "followers": 4})):  # fmt: skip
+        rng = random.Random(seed)
+        pattern = [rng.randrange(vocab) for _ in range(17)]
+        toks = [pattern[i % 17] if rng.random() < 0.8 else rng.randrange(vocab) for i in range(n)]
+        prop = NGramProposer(toks[:8], **kw)
+        steps = []
+        for i, t in enumerate(toks[8:]):
+            prop.extend(t)
+            if i % 5 == 0:
+                for v, budget in ((4, 8), (8, 5), (3, 31)):
+                    chains = prop.propose_chains(v)
+                    g, par, dep, ch, _tags = _chains_tree(chains, budget)
+                    steps.append({"at": i, "v": v, "budget": budget, "chains": [[list(c), tag] for c, tag in chains],
+                                  "guesses": list(g), "parents": list(par), "depth": list(dep),
+                                  "children": {str(k): list(x) for k, x in ch.items()}})  # fmt: skip
+        cases.append({"kw": kw, "head": toks[:8], "tail": toks[8:], "steps": steps})
+    return {"cases": cases}
+
+
 def main() -> None:
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     sys.path.insert(0, ref)
@@ -158,7 +197,9 @@ def main() -> None:
     c: dict = {}
     sampling(ref, c)
     np.savez_compressed(os.path.join(HERE, "sampling.npz"), **c)
-    for f in ("codecs.npz", "tiny_qwen3.npz", "sampling.npz"):
+    with open(os.path.join(HERE, "drafts.json"), "w") as f:
+        json.dump(drafts(ref), f, separators=(",", ":"))
+    for f in ("codecs.npz", "tiny_qwen3.npz", "sampling.npz", "drafts.json"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
