@@ -1,0 +1,283 @@
+// The sampled pick: temperature, top-k, top-p and a hashed Gumbel-max draw over a row of logits, one launch.
+//
+// What it computes is btb's card sampler (native/cuda/btb_kernels.cu:1865-2124: btb_sample_max / _hist / _bin / _draw /
+// _out / _keys) and, to the kept set, its CPU kernel (native/src/sample.rs:385-405): s = x / T; the top-k threshold is
+// the k-th largest s found by a three-level radix select (11 + 11 + 10 of a float's 32 ordered bits) over integer
+// counts; the top-p threshold the same select over masses exp(s - max) in 2^30 fixed point (exact u64 sums, so no
+// order of summation changes it); the token is argmax(s + gumbel(key, i)) over the kept tokens, lowest index first.
+//
+// How it runs here: the reference spreads a row over the grid as up to fifteen launches with its histograms in global
+// memory. Here a row belongs to one thread-block cluster of 8 CTAs. Each CTA keeps an eighth of the scaled row in its
+// shared memory (read from global memory once), builds its private histogram there, and the eight histograms are
+// summed through distributed shared memory after one cluster barrier a level; every CTA does the same scan of the same
+// sums, so nothing is broadcast. Nine cluster barriers a pick, no global scratch, no atomics on global memory.
+#include <cooperative_groups.h>
+
+#include "btb_b200_internal.h"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int SMP_CTAS = 8;       // CTAs a cluster (the portable maximum)
+constexpr int SMP_THREADS = 1024;
+constexpr int SMP_BINS = 2048;
+constexpr float SMP_MASS = 1073741824.0f;  // 2^30 a unit of mass
+constexpr float SMP_FLOOR = -21.0f;        // this far under the top a token carries less than 2^-30
+
+__device__ __forceinline__ unsigned smp_ordered(float f) {
+    const unsigned u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float smp_unordered(unsigned o) {
+    return __uint_as_float((o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o);
+}
+// exp(t), t <= 0: t = n ln2 + r with ln2 split in two, e^r a degree-7 series, 0 below -87 (sample.rs `fast_exp`).
+// Every product and sum is rounded on its own (no contraction), as the host's scalar code rounds them.
+__device__ __forceinline__ float smp_exp(float t) {
+    if (t < -87.0f) return 0.0f;
+    const float n = roundf(__fmul_rn(t, 1.4426950408889634f));
+    const float r = __fsub_rn(__fsub_rn(t, __fmul_rn(n, 0.69314575f)), __fmul_rn(n, 1.4286068e-6f));
+    float p = __fmul_rn(r, 0.0001984127f);
+    p = __fmul_rn(r, __fadd_rn(0.001388889f, p));
+    p = __fmul_rn(r, __fadd_rn(0.008333334f, p));
+    p = __fmul_rn(r, __fadd_rn(0.041666668f, p));
+    p = __fmul_rn(r, __fadd_rn(0.16666667f, p));
+    p = __fmul_rn(r, __fadd_rn(0.5f, p));
+    p = __fmul_rn(r, __fadd_rn(1.0f, p));
+    p = __fadd_rn(1.0f, p);
+    int e = (int)n + 127;
+    e = e < 1 ? 1 : (e > 254 ? 254 : e);
+    return __fmul_rn(__int_as_float((unsigned)e << 23), p);
+}
+__device__ __forceinline__ float smp_uniform(unsigned long long key, unsigned i) {
+    unsigned long long h = key ^ ((unsigned long long)i * 0x9E3779B97F4A7C15ull);
+    h ^= h >> 32;
+    h *= 0xBF58476D1CE4E5B9ull;
+    h ^= h >> 29;
+    h *= 0x94D049BB133111EBull;
+    h ^= h >> 32;
+    return __fmul_rn(__fadd_rn((float)(unsigned)(h >> 41), 0.5f), 1.0f / 8388608.0f);  // 23 bits: never 1.0
+}
+__device__ __forceinline__ unsigned long long smp_mix_step(unsigned long long x, unsigned long long p) {
+    x = (x ^ p) + 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return x;
+}
+// btb/sampling.py `_mix` / `key_for`
+__device__ __forceinline__ unsigned long long smp_key(unsigned long long seed, unsigned long long pos, unsigned salt) {
+    unsigned long long x = smp_mix_step(smp_mix_step(0ull, seed), pos);
+    if (salt) x = smp_mix_step(x, (unsigned long long)salt);
+    return x & 0x7FFFFFFFFFFFFFFFull;
+}
+__device__ __forceinline__ unsigned long long smp_pack(float v, unsigned i) {
+    return ((unsigned long long)smp_ordered(v) << 32) | (unsigned long long)(~i);
+}
+
+struct SampleArgs {
+    const void* logits;
+    long long ls;  // elements between rows
+    int V, f32, top_k;
+    unsigned salt;
+    const float* fp;                 // [1/T, top_p] on the card
+    const unsigned long long* keys;  // [R], or null: derived from seed and position
+    const unsigned long long* seed;
+    const int* n0p;
+    const int* depth;
+    long long* out;
+    unsigned* floors;  // [R, 2] the top-k and top-p thresholds (ordered bits), or null
+    int per;           // a CTA's slice of the row
+};
+
+struct Shared {
+    unsigned long long hist[2][SMP_BINS];  // this CTA's histogram of the level (two, so a level needs one barrier)
+    unsigned long long tot[SMP_BINS];      // the cluster's
+    unsigned long long cs[64];
+    unsigned long long best;
+    unsigned long long carry;
+    unsigned vmax, pre;
+};
+
+// One radix select over the cluster's row slices: mode 0 by count (target top_k), mode 1 by mass (target top_p of the
+// mass at or above `floor`). Returns the threshold's ordered bits; every thread of every CTA returns the same value.
+__device__ unsigned smp_select(cg::cluster_group& cl, Shared* S, const float* sv, int n, int mode, unsigned floor,
+                               float M, unsigned top_k, float top_p, int& gen) {
+    const unsigned tid = threadIdx.x;
+    for (int level = 0; level < 3; ++level, ++gen) {
+        unsigned long long* mine = S->hist[gen & 1];
+        const unsigned bits = level < 2 ? 11u : 10u;
+        const unsigned shift = level == 0 ? 21u : (level == 1 ? 10u : 0u), hi = shift + bits;
+        const unsigned prefix = level == 0 ? 0u : S->pre;
+        for (unsigned b = tid; b < SMP_BINS; b += SMP_THREADS) mine[b] = 0ull;
+        __syncthreads();
+        for (int i = tid; i < n; i += SMP_THREADS) {
+            const float s = sv[i];
+            const unsigned u = smp_ordered(s);
+            if (u < floor) continue;
+            if (hi < 32u && (u >> hi) != (prefix >> hi)) continue;
+            if (mode == 0) {
+                atomicAdd(&mine[(u >> shift) & (SMP_BINS - 1)], 1ull);
+            } else if (s - M >= SMP_FLOOR) {
+                const unsigned long long w = (unsigned long long)__fmul_rn(smp_exp(__fsub_rn(s, M)), SMP_MASS);
+                if (w) atomicAdd(&mine[(u >> shift) & (SMP_BINS - 1)], w);
+            }
+        }
+        cl.sync();  // every CTA's histogram of this level is whole
+        for (unsigned b = tid; b < SMP_BINS; b += SMP_THREADS) {
+            unsigned long long a = 0ull;
+#pragma unroll
+            for (int c = 0; c < SMP_CTAS; ++c) a += cl.map_shared_rank(mine, c)[b];
+            S->tot[b] = a;
+        }
+        __syncthreads();
+        if (tid < 64) {
+            unsigned long long c = 0ull;
+            for (unsigned j = 0; j < 32; ++j) c += S->tot[tid * 32 + j];
+            S->cs[tid] = c;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long target;
+            if (level != 0) {
+                target = S->carry;
+            } else if (mode == 0) {
+                target = (unsigned long long)top_k;
+            } else {
+                unsigned long long z = 0ull;
+                for (int c = 0; c < 64; ++c) z += S->cs[c];
+                target = (unsigned long long)__fmul_rn((float)z, top_p);
+                if (!target) target = 1ull;  // at least the top token
+            }
+            // from the top: the chunk of 32 bins the running total first reaches the target in, then the bin
+            unsigned long long acc = 0ull;
+            int chunk = -1;
+            for (int c = 63; c >= 0; --c) {
+                acc += S->cs[c];
+                if (acc >= target) {
+                    chunk = c;
+                    break;
+                }
+            }
+            unsigned pick = 0;
+            unsigned long long rem = target;
+            if (chunk >= 0) {  // else fewer tokens (less mass) than asked for: the threshold stays at the bottom
+                rem = target - (acc - S->cs[chunk]);
+                unsigned long long a = 0ull;
+                for (int b = chunk * 32 + 31; b >= chunk * 32; --b) {
+                    const unsigned long long c = S->tot[b];
+                    a += c;
+                    if (a >= rem) {
+                        pick = (unsigned)b;
+                        rem -= a - c;
+                        break;
+                    }
+                }
+            }
+            S->pre = prefix | (pick << shift);
+            S->carry = rem;
+        }
+        __syncthreads();
+    }
+    return S->pre;
+}
+
+__global__ void __cluster_dims__(SMP_CTAS, 1, 1) __launch_bounds__(SMP_THREADS) sample_pick(const SampleArgs A) {
+    cg::cluster_group cl = cg::this_cluster();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Shared* S = reinterpret_cast<Shared*>(smem_raw);
+    float* sv = reinterpret_cast<float*>(smem_raw + sizeof(Shared));
+    const unsigned tid = threadIdx.x, rank = blockIdx.x, r = blockIdx.y;
+    const int lo = (int)rank * A.per;
+    const int n = max(0, min(A.per, A.V - lo));
+    const float invT = A.fp[0], top_p = A.fp[1];
+
+    // the slice, scaled, into shared memory; the row's max
+    if (tid == 0) {
+        S->vmax = 0u;
+        S->best = 0ull;
+    }
+    __syncthreads();
+    float m = NEG_INF;
+    if (A.f32) {
+        const float* row = static_cast<const float*>(A.logits) + (size_t)r * A.ls + lo;
+        for (int i = tid; i < n; i += SMP_THREADS) {
+            const float s = __fmul_rn(row[i], invT);
+            sv[i] = s;
+            m = fmaxf(m, s);
+        }
+    } else {
+        const bf16* row = static_cast<const bf16*>(A.logits) + (size_t)r * A.ls + lo;
+        for (int i = tid; i < n; i += SMP_THREADS) {
+            const float s = __fmul_rn(bf2f(row[i]), invT);
+            sv[i] = s;
+            m = fmaxf(m, s);
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((tid & 31u) == 0) atomicMax(&S->vmax, smp_ordered(m));
+    cl.sync();
+    unsigned om = 0u;
+    for (int c = 0; c < SMP_CTAS; ++c) om = max(om, *cl.map_shared_rank(&S->vmax, c));
+    const float M = smp_unordered(om);
+
+    int gen = 0;
+    unsigned floorK = 0u, floorP = 0u;
+    if (A.top_k > 0) floorK = smp_select(cl, S, sv, n, 0, 0u, M, (unsigned)A.top_k, top_p, gen);
+    if (top_p < 1.0f) floorP = smp_select(cl, S, sv, n, 1, floorK, M, 0u, top_p, gen);
+    const unsigned floor = max(floorK, floorP);
+
+    // the draw
+    unsigned long long key;
+    if (A.keys != nullptr) {
+        key = A.keys[r];
+    } else {
+        const long long pos = (long long)*A.n0p + (A.depth != nullptr ? A.depth[r] : 0);
+        key = smp_key(*A.seed, (unsigned long long)pos, A.salt);
+    }
+    unsigned long long best = 0ull;
+    for (int i = tid; i < n; i += SMP_THREADS) {
+        const float s = sv[i];
+        if (smp_ordered(s) < floor || !(s - M >= SMP_FLOOR)) continue;
+        const unsigned tok = (unsigned)(lo + i);
+        const float v = __fsub_rn(s, logf(-logf(smp_uniform(key, tok))));
+        if (v > NEG_INF) best = max(best, smp_pack(v, tok));
+    }
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if ((tid & 31u) == 0 && best) atomicMax(&S->best, best);
+    cl.sync();
+    if (rank == 0 && tid == 0) {
+        unsigned long long b = 0ull;
+        for (int c = 0; c < SMP_CTAS; ++c) b = max(b, *cl.map_shared_rank(&S->best, c));
+        A.out[r] = b ? (long long)(~(unsigned)(b & 0xFFFFFFFFull)) : 0ll;  // nothing in the race: token 0, as the host's
+        if (A.floors != nullptr) {
+            A.floors[2 * r] = floorK;
+            A.floors[2 * r + 1] = floorP;
+        }
+    }
+    cl.sync();  // no CTA leaves while a peer may still read its shared memory
+}
+
+}  // namespace
+
+B2_DEFINE_STATUS(sample)
+
+extern "C" int btb_b200_sample_pick(const void* logits, int f32_logits, int R, int V, long long ls, const void* fp,
+                                    int top_k, const void* keys, const void* seed, const void* n0p, const void* depth,
+                                    unsigned salt, void* out, void* floors, void* stream) {
+    if (!logits || !fp || !out) return B2_ERR_NULL;
+    if (!keys && (!seed || !n0p)) return B2_ERR_NULL;
+    if (R <= 0 || R > 65535 || V <= 0 || ls < V || top_k < 0) return B2_ERR_DOMAIN;
+    const int per = (V + SMP_CTAS - 1) / SMP_CTAS;
+    const size_t smem = sizeof(Shared) + (size_t)per * sizeof(float);
+    if (smem > 227 * 1024) return B2_ERR_DOMAIN;  // a row's eighth must fit a CTA's shared memory
+    static bool allowed[64] = {};
+    if (const int rc = b2_allow_smem((const void*)sample_pick, allowed)) return rc;
+    SampleArgs a{logits, ls, V, f32_logits, top_k, salt, static_cast<const float*>(fp),
+                 static_cast<const unsigned long long*>(keys), static_cast<const unsigned long long*>(seed),
+                 static_cast<const int*>(n0p), static_cast<const int*>(depth), static_cast<long long*>(out),
+                 static_cast<unsigned*>(floors), per};
+    // the cluster shape is the kernel's own (__cluster_dims__); the grid is whole clusters
+    return b2_launch((const void*)sample_pick, dim3(SMP_CTAS, R), dim3(SMP_THREADS), smem, static_cast<cudaStream_t>(stream), a, 0);
+}

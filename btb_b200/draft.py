@@ -109,7 +109,7 @@ def generate_speculative(eng: Any, prompt: Any, max_new: int, budget: int = 8, v
     last = eng.prefill(torch.tensor(prompt))
     g1 = eng.bufs(1)
     s = capi.stream_ptr()
-    eng._pick({"logits": last.contiguous(), "pick": g1["pick"]}, 1, s, g1["tok"])
+    eng._pick({"logits": last.contiguous(), "pick": g1["pick"], "depth": eng._before}, 1, s, g1["tok"])
     cur = int(g1["tok"][0].item())
     toks = [cur]
     prop = NGramProposer(prompt + [cur])

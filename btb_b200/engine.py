@@ -203,6 +203,10 @@ class CardEngine:
         self.pin_in = torch.zeros(CARD_ROWS[-1], dtype=torch.int64).pin_memory()
         self.launches_per_step = 0
         self._n = 0
+        from .sampling import CardSampler
+
+        self.sampler = CardSampler(self.dev)
+        self._before = torch.full((1,), -1, dtype=torch.int32, device=self.dev)  # "the row before n0" as a depth
 
     # -- buffers -------------------------------------------------------------------------------------------------
     def bufs(self, M: int) -> dict[str, torch.Tensor]:
@@ -302,7 +306,17 @@ class CardEngine:
         self._k("btb_b200_embed", ptr(self.w.embed), ptr(g["ids"]), ptr(g["h"]), T, self.cfg.hidden, self.cfg.vocab, s)
 
     def _pick(self, g: dict, T: int, s: int, out: torch.Tensor) -> None:
-        self._k("btb_b200_argmax_bf16", ptr(g["logits"]), T, self.cfg.vocab, ptr(g["pick"]), ptr(out), s)
+        """the pass's tokens: the lowest-index argmax, or the sampler's draw keyed by each row's cache position"""
+        if self.sampler.sampling.greedy:
+            self._k("btb_b200_argmax_bf16", ptr(g["logits"]), T, self.cfg.vocab, ptr(g["pick"]), ptr(out), s)
+        else:
+            self.sampler.pick(g["logits"], T, self.n0, g.get("depth"), out, s)
+            self._n += 1
+
+    def set_sampling(self, sampling: Any) -> None:
+        """greedy or sampled picks from here on (btb/sampling.py:34-61); temperature, top-p and seed are data to a
+        captured step graph, greedy/sampled and top-k are part of its shape"""
+        self.sampler.set(sampling)
 
     # -- passes --------------------------------------------------------------------------------------------------
     def reset(self) -> None:
@@ -347,7 +361,7 @@ class CardEngine:
 
     def _step_body(self, s: int, publish: bool, steps: int = 1) -> None:
         """embed(ids) -> layers -> head -> greedy pick into ids -> n0 += 1 (and the handoff to pinned memory)"""
-        if self.step_kernel:
+        if self.step_kernel and self.sampler.sampling.greedy:
             self.program(1, steps, True, publish).launch(stream=torch.cuda.current_stream())
             self.launches_per_step = 1.0 / steps
             return
@@ -369,7 +383,7 @@ class CardEngine:
 
     def step_graph(self, steps: int = 1, publish: bool = True) -> Any:
         """`steps` self-advancing decode steps as one CUDA graph (btb/engine/cuda.py:2101-2251)"""
-        key = ("step", steps, publish)
+        key = ("step", steps, publish, self.sampler.sampling.greedy, self.sampler.top_k)
         if key in self._graphs:
             return self._graphs[key]
         # run once eagerly on a side stream (allocations, shared-memory opt-ins), with the state put back after
@@ -390,6 +404,12 @@ class CardEngine:
         self._graphs[key] = graph
         return graph
 
+    def generate(self, prompt: Any, max_new: int, sampling: Any = None) -> list[int]:
+        """`generate_greedy`'s loop under a sampling: every pick is keyed by (seed, the cache row that decides it)"""
+        if sampling is not None:
+            self.set_sampling(sampling)
+        return self.generate_greedy(prompt, max_new)
+
     def generate_greedy(self, prompt: Any, max_new: int, graph_steps: int = 1) -> list[int]:
         """prefill, the first token from the prompt's last logits, then the step graph replayed; tokens come back
         through pinned host memory (btb/engine/cuda.py:2253-2459)"""
@@ -398,7 +418,7 @@ class CardEngine:
         last = self.prefill(prompt)
         g = self.bufs(1)
         s = capi.stream_ptr()
-        self._pick({"logits": last.contiguous(), "pick": g["pick"]}, 1, s, g["ids"])
+        self._pick({"logits": last.contiguous(), "pick": g["pick"], "depth": self._before}, 1, s, g["ids"])
         toks = [int(g["ids"][0].item())]
         graph = self.step_graph(1, publish=True)
         while len(toks) < max_new:

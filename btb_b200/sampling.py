@@ -1,0 +1,79 @@
+"""How a token is picked: greedy, or temperature / top-k / top-p with a Gumbel-max draw keyed by (seed, cache row).
+
+Mirrors btb's `Sampling` (btb/sampling.py:34-61: the fields, `greedy`, `masked`, `key_for`) and the card sampler's
+device-side configuration (btb/engine/cuda.py:2131-2143: ``fp = [1/T, top_p]`` and the seed live in device buffers
+filled before a replay, so one captured graph serves every temperature, top-p and seed; top-k is a launch parameter).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from .capi import call, ptr
+
+_M64 = 0xFFFFFFFFFFFFFFFF
+
+
+def _mix(*parts: int) -> int:
+    """splitmix64 folded over the parts, 63 bits (btb/sampling.py:22-31)"""
+    x = 0
+    for p in parts:
+        x = ((x ^ (int(p) & _M64)) + 0x9E3779B97F4A7C15) & _M64
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _M64
+        x ^= x >> 31
+    return x & 0x7FFFFFFFFFFFFFFF
+
+
+@dataclass(frozen=True)
+class Sampling:
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    seed: int | None = None
+
+    def __post_init__(self) -> None:
+        if not (self.temperature >= 0.0) or not (0.0 <= self.top_p <= 1.0) or self.top_k < 0:
+            raise ValueError(f"sampling out of range: {self}")
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+    @property
+    def masked(self) -> bool:
+        return self.top_k > 0 or self.top_p < 1.0
+
+    def key_for(self, pos: int, salt: int = 0) -> int:
+        """the noise key of the pick decided at cache row `pos`"""
+        return _mix(self.seed or 0, pos, salt) if salt else _mix(self.seed or 0, pos)
+
+
+class CardSampler:
+    """a `Sampling` on the card: its parameters in device buffers and the one-launch pick over a pass's logits"""
+
+    def __init__(self, device: Any):
+        self.dev = torch.device(device)
+        self.fp = torch.ones(2, dtype=torch.float32, device=self.dev)
+        self.seed = torch.zeros(1, dtype=torch.int64, device=self.dev)
+        self.top_k = 0
+        self.sampling = Sampling()
+
+    def set(self, s: Sampling) -> None:
+        """new parameters; temperature, top-p and seed reach a captured graph as data, top-k needs a new capture"""
+        self.sampling = s
+        if not s.greedy:
+            self.fp.copy_(torch.tensor([1.0 / s.temperature, s.top_p], dtype=torch.float32))
+            self.seed.copy_(torch.tensor([(s.seed or 0) & 0x7FFFFFFFFFFFFFFF], dtype=torch.int64))
+            self.top_k = int(s.top_k)
+
+    def pick(self, logits: torch.Tensor, T: int, n0: torch.Tensor, depth: torch.Tensor | None, out: torch.Tensor,
+             stream: int, keys: torch.Tensor | None = None, floors: torch.Tensor | None = None) -> None:  # fmt: skip
+        """out[:T] = the draw of each of the T rows of `logits` (bf16 or f32, row-major); row r keyed by
+        key_for(n0 + depth[r]) unless `keys` (int64 [T]) gives them"""
+        V = int(logits.shape[-1])
+        call("btb_b200_sample_pick", ptr(logits), int(logits.dtype == torch.float32), T, V, int(logits.stride(0)),
+             ptr(self.fp), self.top_k, ptr(keys), ptr(self.seed), ptr(n0), ptr(depth), 0, ptr(out), ptr(floors), stream)

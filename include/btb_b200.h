@@ -114,6 +114,16 @@ size_t btb_b200_argmax_scratch_bytes(int T);
  * make that call before starting any stream capture. All calls share the one array: two calls whose kernels may
  * overlap on the device (different streams) race on it - keep them on one stream or order them yourself. */
 int btb_b200_argmax_bf16_static(const void* logits, int T, int V, void* out, void* stream);
+/* the sampled pick: btb_sample_keys / _max / _hist / _bin / _draw / _out (native/cuda/btb_kernels.cu:1865-2124) and
+ * btb_sample_pick (native/src/sample.rs:385-405) as one launch - a cluster of 8 CTAs a row. logits [R, V] at stride
+ * `ls`, bf16 (or f32 when f32_logits); fp f32 [2] ON THE CARD = {1 / temperature, top_p} (top_p >= 1 switches the
+ * nucleus off); top_k 0 = off. The row's key is keys[r] (u64 on the card), or with keys null
+ * key_for(seed, *n0p + depth[r], salt) (btb/sampling.py:57-61; seed u64 and n0p i32 on the card, depth i32 [R] or
+ * null). out i64 [R]. floors u32 [R, 2] or null: the top-k and top-p thresholds as ordered float bits. The kept set is
+ * the reference's to the token; V is limited by a CTA's shared memory (an eighth of the row as f32: V <= ~360k). */
+int btb_b200_sample_pick(const void* logits, int f32_logits, int R, int V, long long ls, const void* fp, int top_k,
+                         const void* keys, const void* seed, const void* n0p, const void* depth, unsigned salt,
+                         void* out, void* floors, void* stream);
 /* the tree commit (btb/engine/cuda.py:3535-3575 `ad`): a verify pass's accepted path gathered in place - node path[j]'s
  * row (slot n0 + path[j]) moves to slot n0 + j in every layer's K and V. K, V: layer 0's arenas, `layer_stride`
  * elements to the next layer's, a row `row_el` elements at stride `rs`. path i32 [len] on the card, parents first

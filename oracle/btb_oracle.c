@@ -521,6 +521,133 @@ int orc_argmax_bf16(const uint16_t* logits, int T, int V, int64_t* out) {
     return BTB_OK;
 }
 
+/* ---- the sampled pick: native/src/sample.rs:17-155,255-384 (and native/cuda/btb_kernels.cu:1865-2124) ---------- */
+
+static uint32_t smp_ordered(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+/* exp(t), t <= 0: t = n ln2 + r, e^r a degree-7 series, 0 below -87; each operation rounded on its own */
+static float smp_exp(float t) {
+    if (t < -87.0f) return 0.0f;
+    const float n = roundf(t * 1.4426950408889634f);
+    const float r = t - n * 0.69314575f - n * 1.4286068e-6f;
+    const float p = 1.0f + r * (1.0f + r * (0.5f + r * (0.16666667f + r * (0.041666668f + r * (0.008333334f +
+                    r * (0.001388889f + r * 0.0001984127f))))));
+    int e = (int)n + 127;
+    e = e < 1 ? 1 : (e > 254 ? 254 : e);
+    const uint32_t eb = (uint32_t)e << 23;
+    float sc;
+    memcpy(&sc, &eb, 4);
+    return sc * p;
+}
+float orc_sample_uniform(uint64_t key, uint32_t i) {
+    uint64_t h = key ^ ((uint64_t)i * 0x9E3779B97F4A7C15ull);
+    h ^= h >> 32;
+    h *= 0xBF58476D1CE4E5B9ull;
+    h ^= h >> 29;
+    h *= 0x94D049BB133111EBull;
+    h ^= h >> 32;
+    return ((float)(uint32_t)(h >> 41) + 0.5f) * (1.0f / 8388608.0f);
+}
+static uint64_t smp_mix_step(uint64_t x, uint64_t p) {
+    x = (x ^ p) + 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return x;
+}
+uint64_t orc_sample_key(uint64_t seed, uint64_t pos, uint32_t salt) {
+    uint64_t x = smp_mix_step(smp_mix_step(0ull, seed), pos);
+    if (salt) x = smp_mix_step(x, salt);
+    return x & 0x7FFFFFFFFFFFFFFFull;
+}
+float orc_sample_exp(float t) { return smp_exp(t); }
+
+static uint64_t smp_mass(float a, float m, uint32_t floor) {
+    return (smp_ordered(a) >= floor && a - m >= -21.0f) ? (uint64_t)(smp_exp(a - m) * 1073741824.0f) : 0;
+}
+/* the threshold at which the count (w == NULL) or the mass of tokens with u' >= u first reaches the target, by three
+ * radix levels of 11 + 11 + 10 bits over the tokens with u' >= floor */
+static uint32_t smp_select(const float* s, const uint64_t* w, int V, uint64_t need, float top_p, uint32_t floor) {
+    uint32_t prefix = 0, shift = 32;
+    uint64_t* bin = (uint64_t*)malloc(2048 * sizeof(uint64_t));
+    for (int level = 0; level < 3; ++level) {
+        const uint32_t bits = level < 2 ? 11 : 10;
+        shift -= bits;
+        const uint32_t hi = shift + bits;
+        memset(bin, 0, 2048 * sizeof(uint64_t));
+        for (int i = 0; i < V; ++i) {
+            const uint32_t u = smp_ordered(s[i]);
+            if (u >= floor && (hi >= 32 || (u >> hi) == (prefix >> hi))) bin[(u >> shift) & 2047] += w ? w[i] : 1;
+        }
+        if (level == 0 && w) {
+            uint64_t z = 0;
+            for (int b = 0; b < 2048; ++b) z += bin[b];
+            need = (uint64_t)((float)z * top_p);
+            if (!need) need = 1; /* at least the top token */
+        }
+        uint64_t acc = 0;
+        uint32_t pick = 0;
+        for (int b = 2047; b >= 0; --b) {
+            acc += bin[b];
+            if (acc >= need) {
+                pick = (uint32_t)b;
+                need -= acc - bin[b];
+                break;
+            }
+        }
+        prefix |= pick << shift;
+    }
+    free(bin);
+    return prefix;
+}
+
+/* x [R, V] f32 logits, keys [R]; out [R] tokens; floors [R, 2] (may be null) the top-k and top-p thresholds as ordered
+ * bits; margin [R] (may be null) the winner's lead over the runner-up in the Gumbel race */
+int orc_sample_pick(const float* x, int R, int V, const uint64_t* keys, float inv_t, uint32_t top_k, float top_p,
+                    uint32_t* out, uint32_t* floors, float* margin) {
+    if (!x || !keys || !out) return BTB_ERR_NULL;
+    if (R <= 0 || V <= 0 || !(inv_t > 0.0f)) return BTB_ERR_DOMAIN;
+    float* s = (float*)malloc((size_t)V * sizeof(float));
+    uint64_t* w = (uint64_t*)malloc((size_t)V * sizeof(uint64_t));
+    for (int r = 0; r < R; ++r) {
+        const float* row = x + (size_t)r * V;
+        float m = -INFINITY;
+        for (int i = 0; i < V; ++i) {
+            s[i] = row[i] * inv_t;
+            m = fmaxf(m, s[i]);
+        }
+        uint32_t fk = 0, fp = 0;
+        if (top_k > 0) fk = smp_select(s, NULL, V, top_k, 0.0f, 0);
+        if (top_p < 1.0f) {
+            for (int i = 0; i < V; ++i) w[i] = smp_mass(s[i], m, fk);
+            fp = smp_select(s, w, V, 0, top_p, fk);
+        }
+        const uint32_t floor = fk > fp ? fk : fp;
+        float best = -INFINITY, second = -INFINITY;
+        uint32_t bi = 0;
+        for (int i = 0; i < V; ++i) {
+            if (smp_ordered(s[i]) < floor || !(s[i] - m >= -21.0f)) continue;
+            const float v = s[i] - logf(-logf(orc_sample_uniform(keys[r], (uint32_t)i)));
+            if (v > best) {
+                second = best;
+                best = v;
+                bi = (uint32_t)i;
+            } else if (v > second) {
+                second = v;
+            }
+        }
+        out[r] = bi;
+        if (floors) floors[2 * r] = fk, floors[2 * r + 1] = fp;
+        if (margin) margin[r] = best - second;
+    }
+    free(s);
+    free(w);
+    return BTB_OK;
+}
+
 /* ------------------------------------------------------------------------------------------------------- */
 /* CPU tier: 16-lane GEMV over bf16 / pack12 / MXFP4 / FP8                                                 */
 /* ------------------------------------------------------------------------------------------------------- */

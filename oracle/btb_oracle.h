@@ -77,6 +77,17 @@ int orc_moe_route(const void* logits, int ls, int E, int k, int mode, int f32_lo
 /* lowest-index argmax over bf16 logits rows, btb/engine/cuda.py:2237, native/src/sample.rs:57-67 */
 int orc_argmax_bf16(const uint16_t* logits, int T, int V, int64_t* out);
 
+/* the sampled pick, native/src/sample.rs:17-155,255-405 (whose kept set the card's kernels,
+ * native/cuda/btb_kernels.cu:1865-2124, share): s = x * inv_t; top-k and top-p thresholds by radix select over exact
+ * integer counts and 2^30 fixed-point masses; token = argmax(s + gumbel(key, i)) over the kept, lowest index first.
+ * floors [R, 2] and margin [R] (the winner's lead in the race) may be null. */
+int orc_sample_pick(const float* x, int R, int V, const uint64_t* keys, float inv_t, uint32_t top_k, float top_p,
+                    uint32_t* out, uint32_t* floors, float* margin);
+/* btb/sampling.py:22-31,59-61 `_mix` / `key_for`; :394-398 `_hash_uniform`; sample.rs:28-45 `fast_exp` */
+uint64_t orc_sample_key(uint64_t seed, uint64_t pos, uint32_t salt);
+float orc_sample_uniform(uint64_t key, uint32_t i);
+float orc_sample_exp(float t);
+
 /* ---- CPU tier C-ABI (reference names) ------------------------------------------------------------------ */
 
 const char* btb_isa(void);

@@ -292,6 +292,38 @@ def argmax_bf16(logits) -> np.ndarray:
     return out
 
 
+def sample_pick(x, keys, temperature: float, top_k: int = 0, top_p: float = 1.0):
+    """(tokens [R], floors [R, 2] ordered bits, margin [R]) of the sampled pick over f32 logits [R, V]"""
+    x = np.ascontiguousarray(x, np.float32)
+    keys = np.ascontiguousarray(keys, np.uint64)
+    R, V = x.shape
+    out, floors, margin = np.empty(R, np.uint32), np.empty((R, 2), np.uint32), np.empty(R, np.float32)
+    L = lib()
+    L.orc_sample_pick.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_float, C.c_uint32, C.c_float,
+                                  C.c_void_p, C.c_void_p, C.c_void_p]  # fmt: skip
+    _ck(L.orc_sample_pick(_p(x), R, V, _p(keys), np.float32(1.0) / np.float32(temperature), int(top_k), float(top_p),
+                          _p(out), _p(floors), _p(margin)), "orc_sample_pick")  # fmt: skip
+    return out, floors, margin
+
+
+def sample_key(seed: int, pos: int, salt: int = 0) -> int:
+    L = lib()
+    L.orc_sample_key.restype, L.orc_sample_key.argtypes = C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint32]
+    return int(L.orc_sample_key(seed, pos, salt))
+
+
+def sample_uniform(key: int, idx) -> np.ndarray:
+    L = lib()
+    L.orc_sample_uniform.restype, L.orc_sample_uniform.argtypes = C.c_float, [C.c_uint64, C.c_uint32]
+    return np.asarray([L.orc_sample_uniform(key, int(i)) for i in idx], np.float32)
+
+
+def sample_exp(t) -> np.ndarray:
+    L = lib()
+    L.orc_sample_exp.restype, L.orc_sample_exp.argtypes = C.c_float, [C.c_float]
+    return np.asarray([L.orc_sample_exp(float(v)) for v in t], np.float32)
+
+
 # ---- CPU tier C-ABI -----------------------------------------------------------------------------------------
 
 

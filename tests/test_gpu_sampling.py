@@ -1,0 +1,131 @@
+"""The one-launch sampled pick against the oracle: thresholds to the bit, the drawn token wherever the Gumbel race is
+not decided inside the last ulps of logf, keys derived on the card, and the engine's sampled loop."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+from btb_b200 import capi  # noqa: E402
+from btb_b200 import engine as E  # noqa: E402
+from btb_b200.capi import call, ptr  # noqa: E402
+from btb_b200.sampling import CardSampler, Sampling  # noqa: E402
+
+TIE = 2e-5  # a race closer than this (relative) may go either way between the host's logf and the card's
+
+
+def _run(x: torch.Tensor, keys, T, k, p, f32=True):
+    R, V = x.shape
+    smp = CardSampler("cuda")
+    smp.set(Sampling(temperature=T, top_k=k, top_p=p, seed=0))
+    out = torch.zeros(R, dtype=torch.int64, device="cuda")
+    floors = torch.zeros(R, 2, dtype=torch.int32, device="cuda")
+    kd = torch.from_numpy(np.asarray(keys, np.uint64).view(np.int64)).cuda()
+    n0 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    smp.pick(x, R, n0, None, out, capi.stream_ptr(), keys=kd, floors=floors)
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    return out.cpu().numpy(), floors.cpu().numpy().view(np.uint32)
+
+
+CASES = [(1000, 0.8, 40, 0.9), (151936, 0.7, 50, 0.95), (201088, 1.0, 0, 0.8), (128256, 1.3, 8, 1.0), (257, 1.5, 3, 0.5),
+         (70, 0.3, 0, 0.99), (7, 1.0, 20, 1.0), (32000, 1.0, 0, 1.0), (50257, 0.05, 0, 0.3)]  # fmt: skip
+
+
+@pytest.mark.parametrize("V,T,k,p", CASES)
+def test_pick_equals_the_oracle(V, T, k, p):
+    rng = np.random.default_rng(V)
+    R = 5
+    x = (rng.standard_normal((R, V)) * 3).astype(np.float32)
+    x[1, : V // 2] = x[1, V // 2 : 2 * (V // 2)]  # a row with every value twice: ties at the thresholds
+    keys = rng.integers(0, 2**63, size=R, dtype=np.uint64)
+    want, wfl, margin = O.sample_pick(x, keys, T, k, p)
+    got, gfl = _run(torch.from_numpy(x).cuda(), keys, T, k, p)
+    assert np.array_equal(gfl, wfl)
+    for r in range(R):
+        assert got[r] == want[r] or margin[r] <= TIE * max(1.0, abs(float(x[r].max()) / T)), (r, got[r], want[r], margin[r])
+    # bf16 logits are the same pick as their f32 widening
+    xb = torch.from_numpy(x).cuda().bfloat16()
+    want_b, wfl_b, margin_b = O.sample_pick(xb.float().cpu().numpy(), keys, T, k, p)
+    got_b, gfl_b = _run(xb, keys, T, k, p)
+    assert np.array_equal(gfl_b, wfl_b)
+    assert all(got_b[r] == want_b[r] or margin_b[r] <= TIE * 40 for r in range(R))
+
+
+def test_special_values_and_strided_rows():
+    V = 4096
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((4, V)) * 2).astype(np.float32)
+    x[0, ::7] = -np.inf
+    x[1, 5] = np.inf
+    x[2] = 0.0
+    x[2, ::2] = -0.0
+    x[3, 100:200] = x[3].max()
+    keys = np.arange(4, dtype=np.uint64) + 11
+    for T, k, p in ((1.0, 0, 0.9), (0.5, 10, 1.0), (2.0, 64, 0.5)):
+        want, wfl, margin = O.sample_pick(x, keys, T, k, p)
+        wide = torch.zeros(4, V + 24, device="cuda")
+        wide[:, :V] = torch.from_numpy(x).cuda()
+        got, gfl = _run(wide[:, :V], keys, T, k, p)  # rows at a stride longer than V
+        assert np.array_equal(gfl, wfl), (T, k, p)
+        assert all(got[r] == want[r] or margin[r] <= 1e-4 for r in range(4)), (T, k, p, got, want)
+
+
+def test_key_derived_on_the_card_is_key_for():
+    V = 5000
+    rng = np.random.default_rng(9)
+    x = torch.from_numpy((rng.standard_normal((3, V)) * 3).astype(np.float32)).cuda()
+    s = Sampling(temperature=0.9, top_k=0, top_p=1.0, seed=123456789)
+    smp = CardSampler("cuda")
+    smp.set(s)
+    n0 = torch.tensor([4095], dtype=torch.int32, device="cuda")
+    depth = torch.tensor([0, 1, 5], dtype=torch.int32, device="cuda")
+    out = torch.zeros(3, dtype=torch.int64, device="cuda")
+    smp.pick(x, 3, n0, depth, out, capi.stream_ptr())
+    keys = np.asarray([s.key_for(4095 + d) for d in (0, 1, 5)], np.uint64)
+    assert [int(k) for k in keys] == [O.sample_key(123456789, 4095 + d) for d in (0, 1, 5)]
+    want, _, margin = O.sample_pick(x.cpu().numpy(), keys, 0.9)
+    got = out.cpu().numpy()
+    assert all(got[r] == want[r] or margin[r] <= 1e-4 for r in range(3))
+
+
+def test_refusals():
+    x = torch.zeros(1, 64, device="cuda")
+    fp = torch.ones(2, device="cuda")
+    out = torch.zeros(1, dtype=torch.int64, device="cuda")
+    with pytest.raises(capi.NativeError):  # no keys and no seed
+        call("btb_b200_sample_pick", ptr(x), 1, 1, 64, 64, ptr(fp), 0, 0, 0, 0, 0, 0, ptr(out), 0, 0)
+    with pytest.raises(capi.NativeError):  # a row too long for a cluster's shared memory
+        call("btb_b200_sample_pick", ptr(x), 1, 1, 1 << 20, 1 << 20, ptr(fp), 0, ptr(out), 0, 0, 0, 0, ptr(out), 0, 0)
+
+
+SMALL = E.DenseConfig("small", hidden=256, layers=3, q_heads=8, kv_heads=2, head_dim=128, inter=512, vocab=1000)
+
+
+def test_engine_sampled_loop_draws_what_the_sequential_keys_draw():
+    eng = E.CardEngine(E.synth_weights(SMALL, seed=0, on_cpu=True), cap=512)
+    s = Sampling(temperature=0.8, top_k=40, top_p=0.9, seed=7)
+    prompt = list(range(3, 23))
+    toks = eng.generate(prompt, 24, s)
+    assert toks == eng.generate(prompt, 24, s)  # a seed repeats
+    assert toks != eng.generate(prompt, 24, Sampling(temperature=0.8, top_k=40, top_p=0.9, seed=8))
+    # teacher-forced: each step's logits through the oracle's pick under key_for(the deciding row)
+    eng.set_sampling(Sampling())
+    eng.reset()
+    lg = eng.prefill(torch.tensor(prompt))
+    pos = len(prompt) - 1
+    for t in toks:
+        want, _, margin = O.sample_pick(lg.float().cpu().numpy(), np.asarray([s.key_for(pos)], np.uint64), 0.8, 40, 0.9)
+        assert t == want[0] or margin[0] <= 1e-3, (pos, t, want[0], margin[0])
+        lg = eng.forward(torch.tensor([t]))
+        pos += 1
+    # temperature, top-p and seed are data to the captured graph; greedy comes back as the argmax loop
+    hot = eng.generate(prompt, 12, Sampling(temperature=5.0, top_k=40, top_p=1.0, seed=7))
+    assert hot != toks[:12]
+    assert eng.generate(prompt, 12, Sampling()) == eng.generate_greedy(prompt, 12)
