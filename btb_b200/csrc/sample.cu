@@ -88,6 +88,7 @@ struct SampleArgs {
     const int* depth;
     long long* out;
     unsigned* floors;  // [R, 2] the top-k and top-p thresholds (ordered bits), or null
+    unsigned long long* packed;  // [R] the winner as (ordered value << 32 | ~index), or null
     int per;           // a CTA's slice of the row
 };
 
@@ -250,7 +251,9 @@ __global__ void __cluster_dims__(SMP_CTAS, 1, 1) __launch_bounds__(SMP_THREADS) 
     if (rank == 0 && tid == 0) {
         unsigned long long b = 0ull;
         for (int c = 0; c < SMP_CTAS; ++c) b = max(b, *cl.map_shared_rank(&S->best, c));
-        A.out[r] = b ? (long long)(~(unsigned)(b & 0xFFFFFFFFull)) : 0ll;  // nothing in the race: token 0, as the host's
+        // nothing in the race: token 0, as the host's
+        if (A.out != nullptr) A.out[r] = b ? (long long)(~(unsigned)(b & 0xFFFFFFFFull)) : 0ll;
+        if (A.packed != nullptr) A.packed[r] = b;
         if (A.floors != nullptr) {
             A.floors[2 * r] = floorK;
             A.floors[2 * r + 1] = floorP;
@@ -259,14 +262,53 @@ __global__ void __cluster_dims__(SMP_CTAS, 1, 1) __launch_bounds__(SMP_THREADS) 
     cl.sync();  // no CTA leaves while a peer may still read its shared memory
 }
 
+// btb_sample_out (native/cuda/btb_kernels.cu:2110-2114): the token of a packed winner
+struct OutArgs {
+    const unsigned long long* packed;
+    unsigned* out;
+    int R;
+};
+__global__ void sample_out_k(const OutArgs A) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < A.R) A.out[r] = ~(unsigned)(A.packed[r] & 0xFFFFFFFFull);
+}
+
+// btb_sample_keys (native/cuda/btb_kernels.cu:2116-2124): keys[0..1] = key_for(seed, pos[0], salt) as (lo, hi)
+struct KeysArgs {
+    const unsigned* seed;
+    const int* pos;
+    unsigned salt;
+    unsigned* keys;
+};
+__global__ void sample_keys_k(const KeysArgs A) {
+    if (blockIdx.x || threadIdx.x) return;
+    const unsigned long long sd = ((unsigned long long)A.seed[1] << 32) | (unsigned long long)A.seed[0];
+    const unsigned long long k = smp_key(sd, (unsigned long long)(unsigned)A.pos[0], A.salt);
+    A.keys[0] = (unsigned)(k & 0xFFFFFFFFull);
+    A.keys[1] = (unsigned)(k >> 32);
+}
+
 }  // namespace
 
 B2_DEFINE_STATUS(sample)
 
+extern "C" int btb_b200_sample_keys(const void* seed, const void* pos, unsigned salt, void* keys, void* stream) {
+    if (!seed || !pos || !keys) return B2_ERR_NULL;
+    KeysArgs a{static_cast<const unsigned*>(seed), static_cast<const int*>(pos), salt, static_cast<unsigned*>(keys)};
+    return b2_launch((const void*)sample_keys_k, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), a, 0);
+}
+
+extern "C" int btb_b200_sample_out(const void* packed, void* out, int R, void* stream) {
+    if (!packed || !out) return B2_ERR_NULL;
+    if (R <= 0) return B2_ERR_DOMAIN;
+    OutArgs a{static_cast<const unsigned long long*>(packed), static_cast<unsigned*>(out), R};
+    return b2_launch((const void*)sample_out_k, dim3((R + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream), a, 0);
+}
+
 extern "C" int btb_b200_sample_pick(const void* logits, int f32_logits, int R, int V, long long ls, const void* fp,
                                     int top_k, const void* keys, const void* seed, const void* n0p, const void* depth,
-                                    unsigned salt, void* out, void* floors, void* stream) {
-    if (!logits || !fp || !out) return B2_ERR_NULL;
+                                    unsigned salt, void* out, void* floors, void* packed, void* stream) {
+    if (!logits || !fp || (!out && !packed)) return B2_ERR_NULL;
     if (!keys && (!seed || !n0p)) return B2_ERR_NULL;
     if (R <= 0 || R > 65535 || V <= 0 || ls < V || top_k < 0) return B2_ERR_DOMAIN;
     const int per = (V + SMP_CTAS - 1) / SMP_CTAS;
@@ -277,7 +319,7 @@ extern "C" int btb_b200_sample_pick(const void* logits, int f32_logits, int R, i
     SampleArgs a{logits, ls, V, f32_logits, top_k, salt, static_cast<const float*>(fp),
                  static_cast<const unsigned long long*>(keys), static_cast<const unsigned long long*>(seed),
                  static_cast<const int*>(n0p), static_cast<const int*>(depth), static_cast<long long*>(out),
-                 static_cast<unsigned*>(floors), per};
+                 static_cast<unsigned*>(floors), static_cast<unsigned long long*>(packed), per};
     // the cluster shape is the kernel's own (__cluster_dims__); the grid is whole clusters
     return b2_launch((const void*)sample_pick, dim3(SMP_CTAS, R), dim3(SMP_THREADS), smem, static_cast<cudaStream_t>(stream), a, 0);
 }

@@ -54,10 +54,17 @@ class B200Launcher:
         (r"btb_moe_route$", "_moe_route"),
         (r"btb_gemv_lane16_f32_m(\d+)$", "_gemv_lane16"),
         (r"btb_gemv_lane16_mx4_f32_m(\d+)$", "_gemv_lane16_mx4"),
+        (r"btb_sample_keys$", "_sample_keys"),
+        (r"btb_sample_max$", "_sample_max"),
+        (r"btb_sample_hist$", "_sample_level"),
+        (r"btb_sample_bin$", "_sample_bin"),
+        (r"btb_sample_draw$", "_sample_draw"),
+        (r"btb_sample_out$", "_sample_out"),
     )
 
     def __init__(self) -> None:
         self.lib = capi.lib()
+        self._top_k = 0  # the pick being assembled: the reference launches it as a pipeline of kernels
         self._families = [(re.compile(rx), getattr(self, h)) for rx, h in self.FAMILIES if hasattr(self, h)]
 
     def serves(self, name: str) -> bool:
@@ -125,6 +132,38 @@ class B200Launcher:
                   int(_v(Cc)), s)  # fmt: skip
 
 
+    # the sampled pick (native/cuda/btb_kernels.cu:1865-2124). The reference runs max -> three radix levels for top-k
+    # -> three for top-p -> draw as separate launches sharing global scratch; the library does all of it inside the
+    # draw's launch. The earlier stages only tell this launcher the pick's shape: max opens a pick, a count-mode bin
+    # carries top_k; whether the nucleus applies is read from fp[1] on the card (top_p < 1), which is what decides
+    # whether the reference's host launches the mass-mode levels at all.
+    def _sample_keys(self, name, m, grid, a, s):
+        seed, pos, salt, keys = a
+        capi.call("btb_b200_sample_keys", _p(seed), _p(pos), int(_v(salt)), _p(keys), s)
+
+    def _sample_max(self, name, m, grid, a, s):
+        self._top_k = 0
+
+    def _sample_level(self, name, m, grid, a, s):
+        pass
+
+    def _sample_bin(self, name, m, grid, a, s):
+        level, mode, top_k = (int(_v(v)) for v in a[:3])
+        if mode == 0:
+            self._top_k = top_k
+
+    def _sample_draw(self, name, m, grid, a, s):
+        x, keys, V, fp, gM, gpreK, gpreP, gbest = a
+        R = int(grid[1])
+        capi.call("btb_b200_sample_pick", _p(x), 1, R, int(_v(V)), int(_v(V)), _p(fp), self._top_k, _p(keys), 0, 0, 0,
+                  0, 0, 0, _p(gbest), s)  # fmt: skip
+        self._top_k = 0
+
+    def _sample_out(self, name, m, grid, a, s):
+        gbest, out, R = a
+        capi.call("btb_b200_sample_out", _p(gbest), _p(out), int(_v(R)), s)
+
+
 # -- typed launchers, the reference's names and argument order (btb/engine/card_launch.py) --------------------------
 _P, _I, _F = C.c_void_p, C.c_int, C.c_float
 
@@ -179,3 +218,30 @@ def btb_attn_flash(launcher, D, grid, block, q, K, V, out, n0p, par, T, Hq, Hk, 
 
 def btb_publish(launcher, grid, block, n0, ids, out_tok, out_n0, out_ts, *, stream=None, shared=0):
     launcher.launch("btb_publish", grid, block, [_P(n0), _P(ids), _P(out_tok), _P(out_n0), _P(out_ts)], stream, shared)
+
+
+def btb_sample_keys(launcher, grid, block, seed, pos, salt, keys, *, stream=None, shared=0):
+    launcher.launch("btb_sample_keys", grid, block, [_P(seed), _P(pos), _I(salt), _P(keys)], stream, shared)
+
+
+def btb_sample_max(launcher, grid, block, x, V, fp, gM, *, stream=None, shared=0):
+    launcher.launch("btb_sample_max", grid, block, [_P(x), _I(V), _P(fp), _P(gM)], stream, shared)
+
+
+def btb_sample_hist(launcher, grid, block, x, V, fp, level, mode, gM, gpre, gfloor, ghist, *, stream=None, shared=0):
+    launcher.launch("btb_sample_hist", grid, block,
+                    [_P(x), _I(V), _P(fp), _I(level), _I(mode), _P(gM), _P(gpre), _P(gfloor), _P(ghist)], stream, shared)  # fmt: skip
+
+
+def btb_sample_bin(launcher, grid, block, level, mode, top_k, fp, ghist, gpre, gcarry, *, stream=None, shared=0):
+    launcher.launch("btb_sample_bin", grid, block,
+                    [_I(level), _I(mode), _I(top_k), _P(fp), _P(ghist), _P(gpre), _P(gcarry)], stream, shared)  # fmt: skip
+
+
+def btb_sample_draw(launcher, grid, block, x, keys, V, fp, gM, gpreK, gpreP, gbest, *, stream=None, shared=0):
+    launcher.launch("btb_sample_draw", grid, block,
+                    [_P(x), _P(keys), _I(V), _P(fp), _P(gM), _P(gpreK), _P(gpreP), _P(gbest)], stream, shared)  # fmt: skip
+
+
+def btb_sample_out(launcher, grid, block, gbest, out, R, *, stream=None, shared=0):
+    launcher.launch("btb_sample_out", grid, block, [_P(gbest), _P(out), _I(R)], stream, shared)

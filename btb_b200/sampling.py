@@ -76,4 +76,4 @@ class CardSampler:
         key_for(n0 + depth[r]) unless `keys` (int64 [T]) gives them"""
         V = int(logits.shape[-1])
         call("btb_b200_sample_pick", ptr(logits), int(logits.dtype == torch.float32), T, V, int(logits.stride(0)),
-             ptr(self.fp), self.top_k, ptr(keys), ptr(self.seed), ptr(n0), ptr(depth), 0, ptr(out), ptr(floors), stream)
+             ptr(self.fp), self.top_k, ptr(keys), ptr(self.seed), ptr(n0), ptr(depth), 0, ptr(out), ptr(floors), 0, stream)

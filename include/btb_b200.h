@@ -119,11 +119,17 @@ int btb_b200_argmax_bf16_static(const void* logits, int T, int V, void* out, voi
  * `ls`, bf16 (or f32 when f32_logits); fp f32 [2] ON THE CARD = {1 / temperature, top_p} (top_p >= 1 switches the
  * nucleus off); top_k 0 = off. The row's key is keys[r] (u64 on the card), or with keys null
  * key_for(seed, *n0p + depth[r], salt) (btb/sampling.py:57-61; seed u64 and n0p i32 on the card, depth i32 [R] or
- * null). out i64 [R]. floors u32 [R, 2] or null: the top-k and top-p thresholds as ordered float bits. The kept set is
- * the reference's to the token; V is limited by a CTA's shared memory (an eighth of the row as f32: V <= ~360k). */
+ * null). out i64 [R] (or null). floors u32 [R, 2] or null: the top-k and top-p thresholds as ordered float bits.
+ * packed u64 [R] or null: the winner as btb_sample_draw leaves it in `gbest` (ordered value << 32 | ~index). The kept
+ * set is the reference's to the token; V is limited by a CTA's shared memory (an eighth of the row as f32: V <= ~360k). */
 int btb_b200_sample_pick(const void* logits, int f32_logits, int R, int V, long long ls, const void* fp, int top_k,
                          const void* keys, const void* seed, const void* n0p, const void* depth, unsigned salt,
-                         void* out, void* floors, void* stream);
+                         void* out, void* floors, void* packed, void* stream);
+/* btb_sample_out (native/cuda/btb_kernels.cu:2110-2114): out u32 [R] = the token of each packed winner */
+int btb_b200_sample_out(const void* packed, void* out, int R, void* stream);
+/* btb_sample_keys (native/cuda/btb_kernels.cu:2116-2124): keys u32 [2] = key_for(seed u32 [2] (lo, hi), pos i32 [1],
+ * salt) as (lo, hi), for callers that keep the reference's separate key buffer */
+int btb_b200_sample_keys(const void* seed, const void* pos, unsigned salt, void* keys, void* stream);
 /* the tree commit (btb/engine/cuda.py:3535-3575 `ad`): a verify pass's accepted path gathered in place - node path[j]'s
  * row (slot n0 + path[j]) moves to slot n0 + j in every layer's K and V. K, V: layer 0's arenas, `layer_stride`
  * elements to the next layer's, a row `row_el` elements at stride `rs`. path i32 [len] on the card, parents first

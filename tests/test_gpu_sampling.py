@@ -100,9 +100,9 @@ def test_refusals():
     fp = torch.ones(2, device="cuda")
     out = torch.zeros(1, dtype=torch.int64, device="cuda")
     with pytest.raises(capi.NativeError):  # no keys and no seed
-        call("btb_b200_sample_pick", ptr(x), 1, 1, 64, 64, ptr(fp), 0, 0, 0, 0, 0, 0, ptr(out), 0, 0)
+        call("btb_b200_sample_pick", ptr(x), 1, 1, 64, 64, ptr(fp), 0, 0, 0, 0, 0, 0, ptr(out), 0, 0, 0)
     with pytest.raises(capi.NativeError):  # a row too long for a cluster's shared memory
-        call("btb_b200_sample_pick", ptr(x), 1, 1, 1 << 20, 1 << 20, ptr(fp), 0, ptr(out), 0, 0, 0, 0, ptr(out), 0, 0)
+        call("btb_b200_sample_pick", ptr(x), 1, 1, 1 << 20, 1 << 20, ptr(fp), 0, ptr(out), 0, 0, 0, 0, ptr(out), 0, 0, 0)
 
 
 SMALL = E.DenseConfig("small", hidden=256, layers=3, q_heads=8, kv_heads=2, head_dim=128, inter=512, vocab=1000)
@@ -129,3 +129,63 @@ def test_engine_sampled_loop_draws_what_the_sequential_keys_draw():
     hot = eng.generate(prompt, 12, Sampling(temperature=5.0, top_k=40, top_p=1.0, seed=7))
     assert hot != toks[:12]
     assert eng.generate(prompt, 12, Sampling()) == eng.generate_greedy(prompt, 12)
+
+
+# ---- the reference's own pipeline, launch by launch, through both launchers --------------------------------------
+
+
+def _pipeline(launcher, x, seed, n0, T, top_k, top_p):
+    """btb's card pick as its host issues it (btb/engine/cuda.py:2158-2220): keys -> max -> radix levels -> draw -> out"""
+    import ctypes as C
+
+    from btb_b200 import launcher as L
+
+    R, V = x.shape
+    dev = x.device
+    z = lambda n, dt: torch.zeros(n, dtype=dt, device=dev)  # noqa: E731
+    fp = torch.tensor([1.0 / T, top_p], dtype=torch.float32, device=dev)
+    seedt = torch.tensor([seed & 0xFFFFFFFF, seed >> 32], dtype=torch.int64).to(torch.int32).to(dev)
+    pos = torch.tensor([n0], dtype=torch.int32, device=dev)
+    keys, gM, ghist = z(2, torch.int32), z(R, torch.int32), z(R * 2048, torch.int64)
+    gpreK, gpreP, gcarry, gbest = z(R, torch.int32), z(R, torch.int32), z(R, torch.int64), z(R, torch.int64)
+    out = z(R, torch.int32)
+    nb = min(max(1, (V + 1023) // 1024), 4 * 148)
+    p = lambda t: t.data_ptr()  # noqa: E731
+    L.btb_sample_keys(launcher, (1, 1, 1), (1, 1, 1), p(seedt), p(pos), 0, p(keys))
+    L.btb_sample_max(launcher, (nb, R, 1), (1024, 1, 1), p(x), V, p(fp), p(gM))
+    for mode, pre, flo, run in ((0, gpreK, gpreP, top_k > 0), (1, gpreP, gpreK, top_p < 1.0)):
+        if not run:
+            continue
+        for lvl in (0, 1, 2):
+            ghist.zero_()
+            L.btb_sample_hist(launcher, (nb, R, 1), (1024, 1, 1), p(x), V, p(fp), lvl, mode, p(gM), p(pre), p(flo), p(ghist))
+            L.btb_sample_bin(launcher, (R, 1, 1), (1024, 1, 1), lvl, mode, top_k, p(fp), p(ghist), p(pre), p(gcarry))
+    L.btb_sample_draw(launcher, (nb, R, 1), (1024, 1, 1), p(x), p(keys), V, p(fp), p(gM), p(gpreK), p(gpreP), p(gbest))
+    L.btb_sample_out(launcher, ((R + 255) // 256, 1, 1), (256, 1, 1), p(gbest), p(out), R)
+    torch.cuda.synchronize()
+    del C
+    return out.cpu().numpy().view(np.uint32), keys.cpu().numpy().view(np.uint32), gbest.cpu().numpy()
+
+
+@pytest.mark.parametrize("V,T,k,p", [(151936, 0.7, 50, 0.95), (32000, 1.0, 0, 0.8), (5000, 1.2, 8, 1.0), (1000, 1.0, 0, 1.0)])
+def test_launcher_serves_the_reference_pipeline_and_equals_its_kernels(V, T, k, p):
+    from . import refkernels
+    from btb_b200 import launcher as L
+
+    rng = np.random.default_rng(V + k)
+    x = torch.from_numpy((rng.standard_normal((1, V)) * 3).astype(np.float32)).cuda()
+    mine = _pipeline(L.B200Launcher(), x, 0x1234567 << 8, 77, T, k, p)
+    key = Sampling(temperature=T, seed=0x1234567 << 8).key_for(77)
+    assert int(mine[1][0]) | (int(mine[1][1]) << 32) == key
+    want, _, margin = O.sample_pick(x.cpu().numpy(), np.asarray([key], np.uint64), T, k, p)
+    assert mine[0][0] == want[0] or margin[0] <= 1e-4
+    if not refkernels.available():
+        pytest.skip("the reference's kernels are not built (oracle/build_ref.sh)")
+    theirs = _pipeline(refkernels.RefLauncher(), x, 0x1234567 << 8, 77, T, k, p)
+    assert np.array_equal(mine[1], theirs[1])  # the key
+    assert mine[0][0] == theirs[0][0] or margin[0] <= 1e-4  # the token
+    if mine[0][0] == theirs[0][0]:
+        # the packed winner: the same token, and its raced value to a few ulps (logf is not the same routine)
+        a = np.uint64(mine[2][0]).item() >> 32
+        b = np.uint64(theirs[2][0]).item() >> 32
+        assert abs(a - b) <= 64
