@@ -39,6 +39,37 @@ int launch_attn(const AttnArgs& a, dim3 grid, cudaStream_t s) {
     if (rc) return rc;
     return b2_launch(reinterpret_cast<const void*>(kern), grid, dim3(NWA * 32), sizeof(AttnSmem<D, G>), s, a);
 }
+// the step's row: norm + RoPE + cache write + attention, one launch (T = 1)
+struct StepAttnArgs {
+    AttnArgs a;
+    RopeArgs r;
+};
+template <int D, int G>
+__global__ void __launch_bounds__(NWA * 32) attn_step(const StepAttnArgs A) {
+    extern __shared__ __align__(16) uint8_t dsm_raw[];
+    pdl_launch_dependents();
+    pdl_wait();
+    attn_step_item<D, G>(A.a, A.r, blockIdx.x, blockIdx.y, dsm_raw);
+}
+template <int D, int G>
+int launch_attn_step(const StepAttnArgs& a, dim3 grid, cudaStream_t s) {
+    auto kern = attn_step<D, G>;
+    static bool allowed[64];
+    int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
+    if (rc) return rc;
+    return b2_launch(reinterpret_cast<const void*>(kern), grid, dim3(NWA * 32), sizeof(AttnSmem<D, G>), s, a);
+}
+template <int D>
+int launch_attn_step_g(int G, const StepAttnArgs& a, dim3 grid, cudaStream_t s) {
+    switch (G) {
+        case 1: return launch_attn_step<D, 1>(a, grid, s);
+        case 2: return launch_attn_step<D, 2>(a, grid, s);
+        case 4: return launch_attn_step<D, 4>(a, grid, s);
+        case 8: return launch_attn_step<D, 8>(a, grid, s);
+        default: return B2_ERR_DOMAIN;
+    }
+}
+
 template <int D>
 int launch_attn_g(int G, const AttnArgs& a, dim3 grid, cudaStream_t s) {
     switch (G) {
@@ -79,6 +110,40 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
     switch (D) {
         case 64: return launch_attn_g<64>(Hq / Hk, a, grid, s);
         case 128: return launch_attn_g<128>(Hq / Hk, a, grid, s);
+        default: return B2_ERR_DOMAIN;
+    }
+}
+
+extern "C" int btb_b200_attn_step(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                  const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
+                                  void* out, int Hq, int Hk, int D, long long hs, long long rs, int centered,
+                                  float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
+                                  const void* tbl, const void* sinks, int cap, void* stream) {
+    if (!qkv || !cos_t || !sin_t || !n0p || !depth || !K || !V || !q || !out || !part_m || !part_l || !part_acc || !cnt)
+        return B2_ERR_NULL;
+    if (Hk <= 0 || Hq <= 0 || Hq % Hk || (Hq / Hk != 1 && Hq / Hk != 2 && Hq / Hk != 4 && Hq / Hk != 8) || cap <= 0 ||
+        !(scale == scale))
+        return B2_ERR_DOMAIN;
+    if ((hs & 7) || (rs & 7) || (reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15))
+        return B2_ERR_DOMAIN;
+    StepAttnArgs sa{};
+    AttnArgs& a = sa.a;
+    a.q = static_cast<const bf16*>(q), a.K = static_cast<const bf16*>(K), a.V = static_cast<const bf16*>(V);
+    a.out = static_cast<bf16*>(out), a.n0p = static_cast<const int*>(n0p), a.par = nullptr;
+    a.tbl = static_cast<const int*>(tbl), a.sinks = static_cast<const float*>(sinks);
+    a.part_m = static_cast<float*>(part_m), a.part_l = static_cast<float*>(part_l);
+    a.part_acc = static_cast<float*>(part_acc), a.cnt = static_cast<int*>(cnt);
+    a.scale = scale, a.T = 1, a.Hq = Hq, a.Hk = Hk, a.win = win, a.cap = cap, a.hs = hs, a.rs = rs;
+    sa.r = RopeArgs{static_cast<const bf16*>(qkv), static_cast<const bf16*>(wq), static_cast<const bf16*>(wk),
+                    static_cast<const bf16*>(cos_t), static_cast<const bf16*>(sin_t), static_cast<const int*>(n0p),
+                    static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),
+                    static_cast<bf16*>(V), static_cast<bf16*>(q), eps, 1, Hq, Hk, centered, hs, rs, cap};
+    const int S = (cap + GK - 1) / GK;
+    const dim3 grid(S, Hk, 1);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (D) {
+        case 64: return launch_attn_step_g<64>(Hq / Hk, sa, grid, s);
+        case 128: return launch_attn_step_g<128>(Hq / Hk, sa, grid, s);
         default: return B2_ERR_DOMAIN;
     }
 }

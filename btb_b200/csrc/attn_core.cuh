@@ -63,6 +63,74 @@ struct AttnSmem {
     float ho[NWA][G][D];
 };
 
+// ---- a block's tiles folded into its group's state, and a row's groups into the row -------------------------------
+// `sm` holds the tiles' maxima, sums and partial outputs; [first, last] the row's keys. A row inside one group is
+// written out at once; else the group's state is stored and the last block to arrive folds the groups in order.
+template <int D, int G>
+__device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& sm, int grp, int g, int t, int first,
+                                            int last, int* s_last_block_p) {
+    const int Hq = A.Hq, Hk = A.Hk, T = A.T;
+    int& s_last_block = *s_last_block_p;
+    // ---- the group's state: the tiles folded in tile order, a thread a run of (head, dim) elements -------------
+    const int s_first = first / GK, s_last = last / GK;
+    const bool single = s_first == s_last;
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
+        const int hh = i / D, d = i - hh * D;
+        float M = NEG_INF, L = 0.f, O = 0.f;
+        for (int w = 0; w < GT; ++w) {
+            const float m = fmaxf(sm.hmax[w][0][hh], sm.hmax[w][1][hh]);
+            if (m == NEG_INF) continue;  // an empty tile changes nothing
+            const float l = __fadd_rn(sm.hsum[w][0][hh], sm.hsum[w][1][hh]);
+            const float o = __fadd_rn(sm.ho[2 * w][hh][d], sm.ho[2 * w + 1][hh][d]);
+            float cO, co;
+            fold_ml(M, L, m, l, cO, co);
+            O = fold_e(O, o, cO, co);
+        }
+        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        if (single) {
+            if (A.sinks != nullptr) {
+                float cO, co;
+                fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+                O = __fmul_rn(O, cO);
+            }
+            A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+        } else {
+            const size_t idx = (size_t)grp * T * Hq + rowi;
+            if (d == 0) {
+                A.part_m[idx] = M;
+                A.part_l[idx] = L;
+            }
+            A.part_acc[idx * D + d] = O;
+        }
+    }
+    if (single) return;
+    // ---- several groups: count this block in; the last one folds the row's groups in group order ----------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last_block = atomicAdd(A.cnt + (size_t)t * Hk + g, 1) == s_last - s_first ? 1 : 0;
+    __syncthreads();
+    if (!s_last_block) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
+        const int hh = i / D, d = i - hh * D;
+        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        float M = NEG_INF, L = 0.f, O = 0.f;
+        for (int sp = s_first; sp <= s_last; ++sp) {
+            const size_t iu = (size_t)sp * T * Hq + rowi;
+            float cO, co;
+            fold_ml(M, L, __ldcg(A.part_m + iu), __ldcg(A.part_l + iu), cO, co);
+            O = fold_e(O, __ldcg(A.part_acc + iu * D + d), cO, co);
+        }
+        if (A.sinks != nullptr) {
+            float cO, co;
+            fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+            O = __fmul_rn(O, cO);
+        }
+        A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+    }
+    if (threadIdx.x == 0) A.cnt[(size_t)t * Hk + g] = 0;
+}
+
 // one block's work: group grp of kv head g for row t. COHERENT: q and the cache are read with L2-coherent loads
 // (the whole-step kernel, where other SMs wrote them earlier in the same launch).
 template <int D, int G, bool COHERENT>
@@ -196,64 +264,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
     }
     __syncthreads();
 
-    // ---- the group's state: the tiles folded in tile order, a thread a run of (head, dim) elements -------------
-    const int s_first = first / GK, s_last = last / GK;
-    const bool single = s_first == s_last;
-    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
-        const int hh = i / D, d = i - hh * D;
-        float M = NEG_INF, L = 0.f, O = 0.f;
-        for (int w = 0; w < GT; ++w) {
-            const float m = fmaxf(sm.hmax[w][0][hh], sm.hmax[w][1][hh]);
-            if (m == NEG_INF) continue;  // an empty tile changes nothing
-            const float l = __fadd_rn(sm.hsum[w][0][hh], sm.hsum[w][1][hh]);
-            const float o = __fadd_rn(sm.ho[2 * w][hh][d], sm.ho[2 * w + 1][hh][d]);
-            float cO, co;
-            fold_ml(M, L, m, l, cO, co);
-            O = fold_e(O, o, cO, co);
-        }
-        const size_t rowi = (size_t)t * Hq + g * G + hh;
-        if (single) {
-            if (A.sinks != nullptr) {
-                float cO, co;
-                fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
-                O = __fmul_rn(O, cO);
-            }
-            A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
-        } else {
-            const size_t idx = (size_t)grp * T * Hq + rowi;
-            if (d == 0) {
-                A.part_m[idx] = M;
-                A.part_l[idx] = L;
-            }
-            A.part_acc[idx * D + d] = O;
-        }
-    }
-    if (single) return;
-    // ---- several groups: count this block in; the last one folds the row's groups in group order ----------------
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last_block = atomicAdd(A.cnt + (size_t)t * Hk + g, 1) == s_last - s_first ? 1 : 0;
-    __syncthreads();
-    if (!s_last_block) return;
-    __threadfence();
-    for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
-        const int hh = i / D, d = i - hh * D;
-        const size_t rowi = (size_t)t * Hq + g * G + hh;
-        float M = NEG_INF, L = 0.f, O = 0.f;
-        for (int sp = s_first; sp <= s_last; ++sp) {
-            const size_t iu = (size_t)sp * T * Hq + rowi;
-            float cO, co;
-            fold_ml(M, L, __ldcg(A.part_m + iu), __ldcg(A.part_l + iu), cO, co);
-            O = fold_e(O, __ldcg(A.part_acc + iu * D + d), cO, co);
-        }
-        if (A.sinks != nullptr) {
-            float cO, co;
-            fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
-            O = __fmul_rn(O, cO);
-        }
-        A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
-    }
-    if (threadIdx.x == 0) A.cnt[(size_t)t * Hk + g] = 0;
+    attn_finish<D, G>(A, sm, grp, g, t, first, last, &s_last_block);
 }
 
 // ---- q/k RMSNorm + RoPE + cache write (btb_kernels.cu:261-327) -----------------------------------------------------
@@ -275,33 +286,25 @@ struct RopeArgs {
     long long hs, rs;
     int cap;  // cache rows: a slot at or past it is refused
 };
+// the E values lane `lane` owns of `head` for row t at position `pos`: q and k heads normalised and rotated, a v head
+// as it stands - the bf16 values the cache and the query buffer hold
 template <int D, bool COHERENT>
-__device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, int lane) {
+__device__ __forceinline__ void rope_values(const RopeArgs& A, int head, int t, int lane, int pos, bf16* out) {
     constexpr int E = D / 32;
     auto ld_bf = [](const bf16* p) -> bf16 {
         if (!COHERENT) return *p;
         const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(p));
         return *reinterpret_cast<const bf16*>(&u);
     };
-    const int n0 = COHERENT ? __ldcg(A.n0p) : *A.n0p;
-    int slot = n0 + t;
-    const int pos = n0 + A.depth[t];
-    if (slot < 0 || slot >= A.cap || pos < 0 || pos >= A.cap) {
-        if (lane == 0) b2_fail(B2_ERR_DOMAIN);
-        return;
-    }
-    if (A.tbl != nullptr) slot = A.tbl[slot];
     const int Hq = A.Hq, Hk = A.Hk;
     const int width = (Hq + 2 * Hk) * D;
     const bf16* src = A.qkv + (size_t)t * width + (size_t)head * D + lane * E;
     if (head >= Hq + Hk) {
-        bf16* dst = A.V + (size_t)(head - Hq - Hk) * A.hs + (size_t)slot * A.rs + lane * E;
 #pragma unroll
-        for (int e = 0; e < E; ++e) dst[e] = ld_bf(src + e);
+        for (int e = 0; e < E; ++e) out[e] = ld_bf(src + e);
         return;
     }
-    const bool is_q = head < Hq;
-    const bf16* wn = is_q ? A.wq : A.wk;
+    const bf16* wn = head < Hq ? A.wq : A.wk;
     float v[E];
 #pragma unroll
     for (int e = 0; e < E; ++e) v[e] = bf2f(ld_bf(src + e));
@@ -320,13 +323,181 @@ __device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, in
     const bf16* cp = A.cos_t + (size_t)pos * D + lane * E;
     const bf16* sp = A.sin_t + (size_t)pos * D + lane * E;
     const float sgn = lane < 16 ? -1.f : 1.f;
-    bf16* dst = is_q ? (A.qo + ((size_t)t * Hq + head) * D + lane * E)
-                     : (A.K + (size_t)(head - Hq) * A.hs + (size_t)slot * A.rs + lane * E);
 #pragma unroll
     for (int e = 0; e < E; ++e) {
         const float rot = __shfl_xor_sync(0xffffffffu, v[e], 16);
         const float qc = bfround(v[e] * bf2f(cp[e]));
-        dst[e] = f2bf(fmaf(sgn * rot, bf2f(sp[e]), qc));
+        out[e] = f2bf(fmaf(sgn * rot, bf2f(sp[e]), qc));
     }
 }
 
+template <int D, bool COHERENT>
+__device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, int lane) {
+    constexpr int E = D / 32;
+    const int n0 = COHERENT ? __ldcg(A.n0p) : *A.n0p;
+    int slot = n0 + t;
+    const int pos = n0 + A.depth[t];
+    if (slot < 0 || slot >= A.cap || pos < 0 || pos >= A.cap) {
+        if (lane == 0) b2_fail(B2_ERR_DOMAIN);
+        return;
+    }
+    if (A.tbl != nullptr) slot = A.tbl[slot];
+    const int Hq = A.Hq, Hk = A.Hk;
+    bf16 o[E];
+    rope_values<D, COHERENT>(A, head, t, lane, pos, o);
+    bf16* dst = head >= Hq + Hk ? (A.V + (size_t)(head - Hq - Hk) * A.hs + (size_t)slot * A.rs + lane * E)
+                : head < Hq     ? (A.qo + ((size_t)t * Hq + head) * D + lane * E)
+                                : (A.K + (size_t)(head - Hq) * A.hs + (size_t)slot * A.rs + lane * E);
+#pragma unroll
+    for (int e = 0; e < E; ++e) dst[e] = o[e];
+}
+
+// ---- the step's row: q/k-norm + RoPE + cache write and the attention in one block -------------------------------------
+// One row (T = 1) at slot n0. Every block of kv head g rotates the head's G queries itself (into shared memory); the
+// block whose group holds slot n0 also makes the new key and value, writes them to the cache and keeps them in shared
+// memory, since it is the only block that reads them. The old keys' loads are issued before any of that, so the two
+// latencies overlap. The arithmetic is rope_values' and attn_item's: the row's bits are the two kernels' bits.
+template <int D, int G>
+__device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs& RA, int grp, int g, uint8_t* dsm_raw) {
+    constexpr int E = D / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = warp >> 1, half = warp & 1;
+    const int Hq = A.Hq, Hk = A.Hk;
+    __shared__ int s_last_block;
+    __shared__ __align__(16) bf16 knew[D];
+    __shared__ __align__(16) bf16 vnew[D];
+    AttnSmem<D, G>& sm = *reinterpret_cast<AttnSmem<D, G>*>(dsm_raw);
+
+    const int n0 = *A.n0p;
+    const int pos = n0 + RA.depth[0];
+    const int last = n0;
+    const int first = A.win > 0 ? max(last + 1 - A.win, 0) : 0;
+    const int lo = grp * GK, hi = lo + GK - 1;
+    if (lo > last || hi < first) return;
+    if (n0 < 0 || last >= A.cap || pos < 0 || pos >= A.cap) {
+        if (threadIdx.x == 0) b2_fail(B2_ERR_DOMAIN);
+        return;
+    }
+    const bool owner = lo <= n0 && n0 <= hi;  // this block's group holds the new row
+    const bf16* Kg = A.K + (size_t)g * A.hs;
+    const bf16* Vg = A.V + (size_t)g * A.hs;
+    // ---- this lane's key; an old key's row starts its way here now ----------------------------------------------
+    const int wbase = lo + tile * BN + half * 32;
+    const int j = wbase + lane;
+    const int new_lane = owner ? n0 - wbase : -1;  // the lane of this warp that holds the new key (if in 0..31)
+    int row = -1;
+    if (j >= first && j <= last) row = A.tbl != nullptr ? A.tbl[j] : j;
+    uint4 kv[D / 8];
+    {
+        const bool fetch = row >= 0 && lane != new_lane;
+        const uint4* kr = reinterpret_cast<const uint4*>(Kg + (size_t)(fetch ? row : 0) * A.rs);
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) kv[c] = fetch ? __ldg(kr + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    // ---- the head's queries (every block), the new key and value (the owner) -----------------------------------
+    if (warp < G) {
+        bf16 o[E];
+        rope_values<D, false>(RA, g * G + warp, 0, lane, pos, o);
+#pragma unroll
+        for (int e = 0; e < E; ++e) sm.qs[warp][lane * E + e] = bf2f(o[e]);
+        if (owner) {
+            bf16* dst = RA.qo + (size_t)(g * G + warp) * D + lane * E;
+#pragma unroll
+            for (int e = 0; e < E; ++e) dst[e] = o[e];
+        }
+    } else if (warp < G + 2 && owner) {
+        const bool is_k = warp == G;
+        bf16 o[E];
+        rope_values<D, false>(RA, is_k ? Hq + g : Hq + Hk + g, 0, lane, pos, o);
+        const int slot = A.tbl != nullptr ? A.tbl[n0] : n0;
+        bf16* dst = (is_k ? RA.K : RA.V) + (size_t)g * A.hs + (size_t)slot * A.rs + lane * E;
+        bf16* keep = (is_k ? knew : vnew) + lane * E;
+#pragma unroll
+        for (int e = 0; e < E; ++e) dst[e] = o[e], keep[e] = o[e];
+    }
+    __syncthreads();
+    if (lane == new_lane && row >= 0) {
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) kv[c] = reinterpret_cast<const uint4*>(knew)[c];
+    }
+    const float scale2 = __fmul_rn(A.scale, LOG2E);
+    float s[G];
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) s[hh] = 0.f;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+        const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
+                             bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            float a = s[hh];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a = fmaf(kf[e], sm.qs[hh][c * 8 + e], a);
+            s[hh] = a;
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh < G; ++hh) {
+        s[hh] = row >= 0 ? __fmul_rn(s[hh], scale2) : NEG_INF;
+        float m = s[hh];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) sm.hmax[tile][half][hh] = m;
+    }
+    __syncthreads();
+    {
+        float o[G][E];
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh) {
+            const float m = fmaxf(sm.hmax[tile][0][hh], sm.hmax[tile][1][hh]);
+            const float p = (m == NEG_INF || row < 0) ? 0.f : ex2(__fsub_rn(s[hh], m));
+            float l = p;
+#pragma unroll
+            for (int k = 16; k > 0; k >>= 1) l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, k));
+            sm.ps[warp][hh][lane] = bfround(p);
+            if (lane == 0) sm.hsum[tile][half][hh] = l;
+#pragma unroll
+            for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
+        }
+        __syncwarp();
+        // a warp none of whose keys the row sees adds nothing (its weights are all zero): skip its value loads
+        const bool any = __ballot_sync(0xffffffffu, row >= 0) != 0u;
+        constexpr int VB = 16;
+#pragma unroll 1
+        for (int i0 = 0; any && i0 < 32; i0 += VB) {
+            float vf[VB][E];
+#pragma unroll
+            for (int u = 0; u < VB; ++u) {
+                const int rk = __shfl_sync(0xffffffffu, row, i0 + u);
+                const bool from_smem = i0 + u == new_lane;
+                const bf16* vr = from_smem ? vnew + lane * E : Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
+                if (E == 4) {
+                    const uint2 vv = rk < 0 ? make_uint2(0u, 0u)
+                                     : from_smem ? *reinterpret_cast<const uint2*>(vr)
+                                                 : __ldg(reinterpret_cast<const uint2*>(vr));
+                    vf[u][0] = bf_lo(vv.x), vf[u][1] = bf_hi(vv.x), vf[u][2] = bf_lo(vv.y), vf[u][3] = bf_hi(vv.y);
+                } else {
+                    const uint32_t vv = rk < 0 ? 0u
+                                        : from_smem ? *reinterpret_cast<const uint32_t*>(vr)
+                                                    : __ldg(reinterpret_cast<const uint32_t*>(vr));
+                    vf[u][0] = bf_lo(vv), vf[u][E - 1] = bf_hi(vv);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < VB; ++u) {
+#pragma unroll
+                for (int hh = 0; hh < G; ++hh) {
+                    const float p = sm.ps[warp][hh][i0 + u];
+#pragma unroll
+                    for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[u][e], o[hh][e]);
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < G; ++hh)
+#pragma unroll
+            for (int e = 0; e < E; ++e) sm.ho[warp][hh][lane * E + e] = o[hh][e];
+    }
+    __syncthreads();
+    attn_finish<D, G>(A, sm, grp, g, 0, first, last, &s_last_block);
+}

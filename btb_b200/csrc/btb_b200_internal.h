@@ -16,6 +16,8 @@ struct B2Tuning {
     int evict_first;  // weight copies carry an L2 evict-first hint
     int pdl;          // programmatic stream serialization: bit 0 the GEMV launches, bit 1 the small kernels
     int warps;        // warps a GEMV CTA for passes of one or two rows: 8 or 16
+    int solo;         // under PDL a GEMV CTA claims an SM's shared memory for itself
+    int balance;      // pick the GEMV grid and warps a CTA so that the rows divide evenly over the warps
 };
 B2Tuning& b2_tuning();
 int b2_sm_count();

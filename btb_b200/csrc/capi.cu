@@ -13,8 +13,9 @@ B2Tuning& b2_tuning() {
     static B2Tuning t = {
         env_int("BTB_B200_RING_BYTES", 96 * 1024), env_int("BTB_B200_SEG_BYTES", 4096),
         env_int("BTB_B200_X_SMEM_MAX", 64 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
-        env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 0),
-        env_int("BTB_B200_WARPS", 16),
+        env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 1),
+        env_int("BTB_B200_WARPS", 16),             env_int("BTB_B200_SOLO", 1),
+        env_int("BTB_B200_BALANCE", 1),
     };
     return t;
 }
@@ -45,6 +46,8 @@ extern "C" int btb_b200_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "evict_first")) t.evict_first = value;
     else if (!strcmp(key, "pdl")) t.pdl = value;
     else if (!strcmp(key, "warps")) t.warps = value == 16 ? 16 : 8;
+    else if (!strcmp(key, "balance")) t.balance = value != 0;
+    else if (!strcmp(key, "solo")) t.solo = value != 0;
     else return B2_ERR_DOMAIN;
     return B2_OK;
 }

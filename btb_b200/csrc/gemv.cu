@@ -53,10 +53,12 @@ struct GemvArgs {
     int fsc, fbm, fbn;     // its columns, a block's rows and columns
 };
 
+// NWT: the most warps a CTA of this instance is launched with (its register budget); the launch picks how many
 template <int M, int FMT, int XM, int NWT>
 __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int NT = NWT * 32;
+    constexpr int NT = 0;  // the staging loops stride by the block's own width
+    const int nw = blockDim.x >> 5;
     const int R = A.R, C = A.C, seg = A.seg, S = A.stages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nseg = (C + seg - 1) / seg;
@@ -69,14 +71,14 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     const int sbytes = (stage_bytes<FMT>(seg) + 127) & ~127;
     bf16* xs = reinterpret_cast<bf16*>(smem + nbytes);
     uint8_t* ring = smem + xbytes + (size_t)warp * S * sbytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + xbytes + (size_t)NWT * S * sbytes) + warp * S;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + xbytes + (size_t)nw * S * sbytes) + warp * S;
 
     // this CTA's rows [r0, r0 + cnt): an even split, the remainder one extra row to the first CTAs
     const int base = R / gridDim.x, rem = R % gridDim.x;
     const int r0 = blockIdx.x * base + min((int)blockIdx.x, rem);
     const int cnt = base + ((int)blockIdx.x < rem ? 1 : 0);
-    // this warp's rows: r0 + warp, + NWT, ..; its items are (row, segment) pairs in order
-    const int my_rows = cnt > warp ? (cnt - warp + NWT - 1) / NWT : 0;
+    // this warp's rows: r0 + warp, + nw, ..; its items are (row, segment) pairs in order
+    const int my_rows = cnt > warp ? (cnt - warp + nw - 1) / nw : 0;
     const int n_items = my_rows * nseg;
 
     if (lane == 0) {
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
         if (++p_st == S) p_st = 0;
         if (++p_seg == nseg) {
             p_seg = 0;
-            p_row += NWT;
+            p_row += nw;
         }
     };
     // fill the ring: weights do not depend on the grids before this one
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
                 acc[m] = 0.f;
             }
             c_seg = 0;
-            c_row += NWT;
+            c_row += nw;
         } else {
             ++c_seg;
         }
@@ -210,8 +212,26 @@ template <int FMT>
 Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     const B2Tuning& t = b2_tuning();
     Plan p;
-    // wide passes keep 8 warps (their accumulators fill the register file); the narrow ones take the tunable
-    const int NW = (M <= 2 && t.warps == 16) ? 16 : 8;
+    const int sms = b2_sm_count();
+    // The unit of work is a row on a warp (the chain order allows no finer cut), so the pass takes as long as the
+    // warp with the most rows: pick the grid and the CTA's warps so that the rows divide evenly. R = 2560 over 148
+    // CTAs of 16 warps leaves most warps one row and some two - half the card idles through the second; 128 CTAs of
+    // 20 warps take one row each. Wide passes keep 8 warps (their accumulators fill the register file).
+    const int w_max = M <= 2 ? 32 : (M <= 8 ? 16 : 8);
+    int NW = (M <= 2 && t.warps >= 16) ? 16 : 8;
+    p.grid = max(1, min(sms * t.ctas_per_sm, (R + 1) / 2));
+    if (t.balance && t.ctas_per_sm == 1 && R >= sms) {
+        double best = 0.0;
+        for (int g = sms; g >= (sms * 3) / 4; --g) {
+            const int per_cta = (R + g - 1) / g;
+            for (int w = 8; w <= w_max; ++w) {
+                const int per_warp = (per_cta + w - 1) / w;
+                // rows done a unit of time, with a mild preference for more SMs and for the usual 16 warps
+                const double eff = (double)R / ((double)per_warp * g * w) * (0.9 + 0.1 * g / sms) - 0.002 * abs(w - 16);
+                if (eff > best + 1e-9) best = eff, p.grid = g, NW = w;
+            }
+        }
+    }
     p.nw = NW;
     const int xbytes = ((M * C * 2 + 127) & ~127) + (norm ? ((C * 4 + 256 * 4 + 127) & ~127) : 0);
     p.xs = want_xs && (M * C * 2) <= t.x_smem_max;
@@ -239,8 +259,9 @@ Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
         }
     }
     p.smem = total(p.stages);
-    const int sms = b2_sm_count();
-    p.grid = max(1, min(sms * t.ctas_per_sm, (R + 1) / 2));
+    // Under programmatic dependent launch the next GEMV's CTAs arrive while this one's are still resident. Two CTAs
+    // of one grid on an SM would make that SM the pass's slowest, so a CTA claims more than half an SM's shared memory.
+    if ((t.pdl & 1) && t.solo) p.smem = max(p.smem, 116 * 1024);
     return p;
 }
 
@@ -250,11 +271,14 @@ int launch_nw(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
     static bool allowed[64];  // the opt-in past 48 KB of dynamic shared memory, once a device
     int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
     if (rc) return rc;
-    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.grid), dim3(NWT * 32), p.smem, stream, a, 1);
+    if (p.nw > NWT) return B2_ERR_DOMAIN;
+    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.grid), dim3(p.nw * 32), p.smem, stream, a, 1);
 }
 template <int M, int FMT, int XM>
 int launch_one(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
-    if (M <= 2 && p.nw == 16) return launch_nw<M, FMT, XM, (M <= 2 ? 16 : 8)>(a, p, stream);
+    // one instance a register budget: up to 16 warps (128 registers a thread) and, for one- and two-row passes, up to 32
+    if (M <= 2 && p.nw > 16) return launch_nw<M, FMT, XM, (M <= 2 ? 32 : 8)>(a, p, stream);
+    if (M <= 8 && p.nw > 8) return launch_nw<M, FMT, XM, (M <= 8 ? 16 : 8)>(a, p, stream);
     return launch_nw<M, FMT, XM, 8>(a, p, stream);
 }
 

@@ -81,7 +81,8 @@ static __device__ __noinline__ uint32_t p12_escape(const int32_t* __restrict__ e
 template <int M, int NT>
 __device__ __forceinline__ void stage_x_copy(bf16* xs, const bf16* x, int C) {
     uint4* dst = reinterpret_cast<uint4*>(xs);
-    for (int i = threadIdx.x; i < M * C / 8; i += NT) dst[i] = ldcg16(reinterpret_cast<const uint4*>(x) + i);
+    const int nt = NT > 0 ? NT : (int)blockDim.x;  // NT 0: the block's width is a launch parameter
+    for (int i = threadIdx.x; i < M * C / 8; i += nt) dst[i] = ldcg16(reinterpret_cast<const uint4*>(x) + i);
 }
 
 // x[m][c] = bf16(bf16(silu(g)) * u), gu [M, 2C] gate then up: the values btb_silu_mul would have written
@@ -89,7 +90,8 @@ __device__ __forceinline__ void stage_x_copy(bf16* xs, const bf16* x, int C) {
 template <int M, int NT>
 __device__ __forceinline__ void stage_x_silu(bf16* xs, const bf16* gu, int C) {
     const int cv = C >> 3;
-    for (int i = threadIdx.x; i < M * cv; i += NT) {
+    const int nt = NT > 0 ? NT : (int)blockDim.x;
+    for (int i = threadIdx.x; i < M * cv; i += nt) {
         const int m = i / cv, c8 = i - m * cv;
         const uint4 gv = ldcg16(reinterpret_cast<const uint4*>(gu + (size_t)m * 2 * C) + c8);
         const uint4 uv = ldcg16(reinterpret_cast<const uint4*>(gu + (size_t)m * 2 * C + C) + c8);
@@ -118,13 +120,14 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
     float* hsm = scratch;
     float* red = hsm + C;
     const int cv = C >> 3, tid = threadIdx.x;
+    const int nt = NT > 0 ? NT : (int)blockDim.x;
     for (int m = 0; m < M; ++m) {
         if (m >= T) {  // a padding row: zeros
-            for (int i = tid; i < cv; i += NT) reinterpret_cast<uint4*>(xs + (size_t)m * C)[i] = make_uint4(0u, 0u, 0u, 0u);
+            for (int i = tid; i < cv; i += nt) reinterpret_cast<uint4*>(xs + (size_t)m * C)[i] = make_uint4(0u, 0u, 0u, 0u);
             continue;
         }
         const bf16* hrow = rows != nullptr ? h_in + (size_t)__ldcg(rows + m) * C : h_in + (size_t)m * C;
-        for (int i = tid; i < cv; i += NT) {
+        for (int i = tid; i < cv; i += nt) {
             const uint4 hv = ldcg16(reinterpret_cast<const uint4*>(hrow) + i);
             uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
             if (y_add != nullptr) {
@@ -157,7 +160,7 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
             __syncthreads();
         }
         const float rstd = rsqrtf(red[0] / (float)C + eps);
-        for (int i = tid; i < C; i += NT) {
+        for (int i = tid; i < C; i += nt) {
             const float wv = bf2f(norm_w[i]);
             xs[(size_t)m * C + i] = f2bf(hsm[i] * rstd * (centered ? 1.f + wv : wv));
         }

@@ -192,6 +192,7 @@ class CardEngine:
         self.n0 = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.silu_fold = silu_fold
         self.fuse_norm = fuse_norm
+        self.fuse_attn = True  # the step's row: norm + RoPE + cache write + attention as one launch
         # the whole step as one persistent kernel (head dim 128 only); else one launch a kernel
         self.step_kernel = bool(step_kernel) and weights.cfg.head_dim == 128 and weights.cfg.q_heads // weights.cfg.kv_heads in (2, 4, 8)
         self._programs: dict[Any, Any] = {}
@@ -278,12 +279,7 @@ class CardEngine:
         y_prev = None
         for i, L in enumerate(self.w.layers):
             normed_matvec(L.qkv, L.ln1, y_prev, g["qkv"], c.qkv_rows)
-            k("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
-              ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
-              self.rs, 0, 0, self.cap, s)  # fmt: skip
-            k("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["att"]), ptr(self.n0),
-              ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
-              ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
+            self._attention(g, i, L.wq, L.wk, T, s)
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             normed_matvec(L.gu, L.ln2, g["y"], g["gu"], 2 * I)
             if self.silu_fold and M <= 8 and M * I * 2 <= 64 * 1024:
@@ -301,6 +297,24 @@ class CardEngine:
             normed_matvec(self.w.embed, self.w.norm, y_prev, g["logits"], c.vocab)
         if hcur is not g["h"]:  # an odd number of folded adds (a pass without its tail): bring the residual home
             g["h"].copy_(hcur)
+
+    def _attention(self, g: dict, i: int, wq: Any, wk: Any, T: int, s: int, win: int = 0, sinks: Any = None) -> None:
+        """q/k-norm + RoPE + cache write, then the attention over the cache: one fused launch for the step's single
+        row, the two kernels for a pass of several rows (the same bits either way)"""
+        c = self.cfg
+        Hq, Hk, D = c.q_heads, c.kv_heads, c.head_dim
+        if T == 1 and self.fuse_attn and D in (64, 128):
+            self._k("btb_b200_attn_step", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
+                    ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), ptr(g["att"]), Hq, Hk,
+                    D, self.hs, self.rs, 0, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]), ptr(g["part_acc"]),
+                    ptr(g["cnt"]), win, 0, ptr(sinks), self.cap, s)  # fmt: skip
+            return
+        self._k("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
+                ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
+                self.rs, 0, 0, self.cap, s)  # fmt: skip
+        self._k("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["att"]), ptr(self.n0),
+                ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
+                ptr(g["part_acc"]), ptr(g["cnt"]), win, 0, ptr(sinks), self.cap, s)  # fmt: skip
 
     def _embed(self, g: dict, T: int, s: int) -> None:
         self._k("btb_b200_embed", ptr(self.w.embed), ptr(g["ids"]), ptr(g["h"]), T, self.cfg.hidden, self.cfg.vocab, s)

@@ -204,12 +204,7 @@ class MoEEngine(CardEngine):
         for i, L in enumerate(self.w.layers):
             K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(g["x"]), T, H, 0, s)
             self._matvec(L.qkv, g["x"], g["qkv"], M, c.qkv_rows, H, s)
-            K_("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
-               ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
-               self.rs, 0, 0, self.cap, s)  # fmt: skip
-            K_("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["att"]), ptr(self.n0),
-               ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
-               ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
+            self._attention(g, i, L.wq, L.wk, T, s)
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
             # the MoE block: x.float(), the router's logits by the host-order GEMV, the picks, the experts, the sum

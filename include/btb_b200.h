@@ -32,7 +32,7 @@ extern "C" {
 
 int btb_b200_version(void);
 int btb_b200_sm_count(void);
-/* tunables: "ring_bytes", "seg_bytes", "x_smem_max", "ctas_per_sm", "evict_first", "pdl" (host string) */
+/* tunables: "ring_bytes", "seg_bytes", "x_smem_max", "ctas_per_sm", "evict_first", "pdl", "warps", "balance" (host string) */
 int btb_b200_set_tuning(const char* key, int value);
 /* reads the device status word into *code (host pointer) and clears it; synchronises the default stream's copy */
 int btb_b200_status(int* code);
@@ -100,6 +100,16 @@ int btb_b200_attn_decode(const void* q, const void* K, const void* V, void* out,
                          int T, int Hq, int Hk, int D, long long hs, long long rs, float scale, void* part_m,
                          void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
                          void* stream);
+/* the decode step's row (T = 1) in one launch: btb_norm_rope_kv_d* (btb_kernels.cu:261-358) and btb_attn_flash_d*
+ * (btb_attn_flash.cuh:372-675) back to back in the reference. Every block rotates its kv head's queries itself; the
+ * block whose key group holds slot n0 makes the new key and value, writes them to the cache and uses them from shared
+ * memory. Arguments as the two functions above (qkv [1, (Hq+2Hk) D]; q [1, Hq, D] is still written); the cache, the
+ * query buffer and `out` hold the bits the two launches would have left. D 64 or 128. */
+int btb_b200_attn_step(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                       const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, void* out,
+                       int Hq, int Hk, int D, long long hs, long long rs, int centered, float scale, void* part_m,
+                       void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
+                       void* stream);
 size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D);
 /* the greedy pick: lowest-index argmax of each bf16 logits row (torch.argmax in btb/engine/cuda.py:2237; tie rule
  * native/src/sample.rs:57-67). scratch: btb_b200_argmax_scratch_bytes(T) bytes, 8-byte aligned, zeroed once.
