@@ -40,6 +40,7 @@ int launch_attn(const AttnArgs& a, dim3 grid, cudaStream_t s) {
     return b2_launch(reinterpret_cast<const void*>(kern), grid, dim3(NWA * 32), sizeof(AttnSmem<D, G>), s, a);
 }
 // the step's row: norm + RoPE + cache write + attention, one launch (T = 1)
+constexpr int SPLIT_ROWS = 4096;
 struct StepAttnArgs {
     AttnArgs a;
     RopeArgs r;
@@ -47,9 +48,14 @@ struct StepAttnArgs {
 template <int D, int G>
 __global__ void __launch_bounds__(NWA * 32) attn_step(const StepAttnArgs A) {
     extern __shared__ __align__(16) uint8_t dsm_raw[];
-    pdl_launch_dependents();
-    pdl_wait();
-    attn_step_item<D, G>(A.a, A.r, blockIdx.x, blockIdx.y, dsm_raw);
+    pdl_wait();  // the trigger for the next kernel is inside, after the values are read
+    // Below this many cached rows the group's heads take a block each (grid z); above, block z = 0 takes them all -
+    // a long cache has blocks enough, and each key row is then read once.
+    if (G > 1 && *A.a.n0p < SPLIT_ROWS) {
+        attn_step_item<D, 1, G>(A.a, A.r, blockIdx.x, blockIdx.y, blockIdx.z, dsm_raw);
+    } else if (blockIdx.z == 0) {
+        attn_step_item<D, G, G>(A.a, A.r, blockIdx.x, blockIdx.y, 0, dsm_raw);
+    }
 }
 template <int D, int G>
 int launch_attn_step(const StepAttnArgs& a, dim3 grid, cudaStream_t s) {
@@ -126,6 +132,10 @@ extern "C" int btb_b200_attn_step(const void* qkv, const void* wq, const void* w
         return B2_ERR_DOMAIN;
     if ((hs & 7) || (rs & 7) || (reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15))
         return B2_ERR_DOMAIN;
+    // a lane reads its D/32 elements of a head, a norm weight or a table row as one load
+    if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk) |
+         reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t) | reinterpret_cast<uintptr_t>(q)) & 15)
+        return B2_ERR_DOMAIN;
     StepAttnArgs sa{};
     AttnArgs& a = sa.a;
     a.q = static_cast<const bf16*>(q), a.K = static_cast<const bf16*>(K), a.V = static_cast<const bf16*>(V);
@@ -139,7 +149,7 @@ extern "C" int btb_b200_attn_step(const void* qkv, const void* wq, const void* w
                     static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),
                     static_cast<bf16*>(V), static_cast<bf16*>(q), eps, 1, Hq, Hk, centered, hs, rs, cap};
     const int S = (cap + GK - 1) / GK;
-    const dim3 grid(S, Hk, 1);
+    const dim3 grid(S, Hk, Hq / Hk);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (D) {
         case 64: return launch_attn_step_g<64>(Hq / Hk, sa, grid, s);

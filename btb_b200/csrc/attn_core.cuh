@@ -67,9 +67,11 @@ struct AttnSmem {
 // `sm` holds the tiles' maxima, sums and partial outputs; [first, last] the row's keys. A row inside one group is
 // written out at once; else the group's state is stored and the last block to arrive folds the groups in order.
 template <int D, int G>
-__device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& sm, int grp, int g, int t, int first,
-                                            int last, int* s_last_block_p) {
-    const int Hq = A.Hq, Hk = A.Hk, T = A.T;
+__device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& sm, int grp, int hbase, int ci, int t,
+                                            int first, int last, int* s_last_block_p) {
+    // hbase: the first of the block's G query heads; ci: the block's arrival counter (one a set of blocks that share
+    // a row's groups)
+    const int Hq = A.Hq, T = A.T;
     int& s_last_block = *s_last_block_p;
     // ---- the group's state: the tiles folded in tile order, a thread a run of (head, dim) elements -------------
     const int s_first = first / GK, s_last = last / GK;
@@ -86,11 +88,11 @@ __device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& s
             fold_ml(M, L, m, l, cO, co);
             O = fold_e(O, o, cO, co);
         }
-        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        const size_t rowi = (size_t)t * Hq + hbase + hh;
         if (single) {
             if (A.sinks != nullptr) {
                 float cO, co;
-                fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+                fold_ml(M, L, __fmul_rn(A.sinks[hbase + hh], LOG2E), 1.f, cO, co);
                 O = __fmul_rn(O, cO);
             }
             A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
@@ -107,13 +109,13 @@ __device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& s
     // ---- several groups: count this block in; the last one folds the row's groups in group order ----------------
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) s_last_block = atomicAdd(A.cnt + (size_t)t * Hk + g, 1) == s_last - s_first ? 1 : 0;
+    if (threadIdx.x == 0) s_last_block = atomicAdd(A.cnt + ci, 1) == s_last - s_first ? 1 : 0;
     __syncthreads();
     if (!s_last_block) return;
     __threadfence();
     for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
         const int hh = i / D, d = i - hh * D;
-        const size_t rowi = (size_t)t * Hq + g * G + hh;
+        const size_t rowi = (size_t)t * Hq + hbase + hh;
         float M = NEG_INF, L = 0.f, O = 0.f;
         for (int sp = s_first; sp <= s_last; ++sp) {
             const size_t iu = (size_t)sp * T * Hq + rowi;
@@ -123,12 +125,12 @@ __device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& s
         }
         if (A.sinks != nullptr) {
             float cO, co;
-            fold_ml(M, L, __fmul_rn(A.sinks[g * G + hh], LOG2E), 1.f, cO, co);
+            fold_ml(M, L, __fmul_rn(A.sinks[hbase + hh], LOG2E), 1.f, cO, co);
             O = __fmul_rn(O, cO);
         }
         A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
     }
-    if (threadIdx.x == 0) A.cnt[(size_t)t * Hk + g] = 0;
+    if (threadIdx.x == 0) A.cnt[ci] = 0;
 }
 
 // one block's work: group grp of kv head g for row t. COHERENT: q and the cache are read with L2-coherent loads
@@ -264,7 +266,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
     }
     __syncthreads();
 
-    attn_finish<D, G>(A, sm, grp, g, t, first, last, &s_last_block);
+    attn_finish<D, G>(A, sm, grp, g * G, t * Hk + g, t, first, last, &s_last_block);
 }
 
 // ---- q/k RMSNorm + RoPE + cache write (btb_kernels.cu:261-327) -----------------------------------------------------
@@ -288,26 +290,43 @@ struct RopeArgs {
 };
 // the E values lane `lane` owns of `head` for row t at position `pos`: q and k heads normalised and rotated, a v head
 // as it stands - the bf16 values the cache and the query buffer hold
+// E consecutive bf16 (E = 2, 4 or 8; the address a multiple of 2 E bytes) as one load
+template <int E, bool COHERENT>
+__device__ __forceinline__ void ld_run(const bf16* p, bf16* out) {
+    if (E == 4) {
+        const uint2 v = COHERENT ? __ldcg(reinterpret_cast<const uint2*>(p)) : *reinterpret_cast<const uint2*>(p);
+        *reinterpret_cast<uint2*>(out) = v;
+    } else if (E == 2) {
+        const uint32_t v = COHERENT ? __ldcg(reinterpret_cast<const uint32_t*>(p)) : *reinterpret_cast<const uint32_t*>(p);
+        *reinterpret_cast<uint32_t*>(out) = v;
+    } else {
+        const uint4 v = COHERENT ? __ldcg(reinterpret_cast<const uint4*>(p)) : *reinterpret_cast<const uint4*>(p);
+        *reinterpret_cast<uint4*>(out) = v;
+    }
+}
+
 template <int D, bool COHERENT>
 __device__ __forceinline__ void rope_values(const RopeArgs& A, int head, int t, int lane, int pos, bf16* out) {
     constexpr int E = D / 32;
-    auto ld_bf = [](const bf16* p) -> bf16 {
-        if (!COHERENT) return *p;
-        const unsigned short u = __ldcg(reinterpret_cast<const unsigned short*>(p));
-        return *reinterpret_cast<const bf16*>(&u);
-    };
     const int Hq = A.Hq, Hk = A.Hk;
     const int width = (Hq + 2 * Hk) * D;
     const bf16* src = A.qkv + (size_t)t * width + (size_t)head * D + lane * E;
+    __align__(16) bf16 raw[E];
+    ld_run<E, COHERENT>(src, raw);
     if (head >= Hq + Hk) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) out[e] = ld_bf(src + e);
+        for (int e = 0; e < E; ++e) out[e] = raw[e];
         return;
     }
     const bf16* wn = head < Hq ? A.wq : A.wk;
+    // every load the head needs is issued before the first is used
+    __align__(16) bf16 wr[E], cr[E], sr[E];
+    if (wn != nullptr) ld_run<E, false>(wn + lane * E, wr);
+    ld_run<E, false>(A.cos_t + (size_t)pos * D + lane * E, cr);
+    ld_run<E, false>(A.sin_t + (size_t)pos * D + lane * E, sr);
     float v[E];
 #pragma unroll
-    for (int e = 0; e < E; ++e) v[e] = bf2f(ld_bf(src + e));
+    for (int e = 0; e < E; ++e) v[e] = bf2f(raw[e]);
     if (wn != nullptr) {
         float ss = 0.f;
 #pragma unroll
@@ -316,18 +335,16 @@ __device__ __forceinline__ void rope_values(const RopeArgs& A, int head, int t, 
         const float rstd = rsqrtf(ss / (float)D + A.eps);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-            const float wv = bf2f(wn[lane * E + e]);
+            const float wv = bf2f(wr[e]);
             v[e] = bfround(v[e] * rstd * (A.centered ? 1.f + wv : wv));
         }
     }
-    const bf16* cp = A.cos_t + (size_t)pos * D + lane * E;
-    const bf16* sp = A.sin_t + (size_t)pos * D + lane * E;
     const float sgn = lane < 16 ? -1.f : 1.f;
 #pragma unroll
     for (int e = 0; e < E; ++e) {
         const float rot = __shfl_xor_sync(0xffffffffu, v[e], 16);
-        const float qc = bfround(v[e] * bf2f(cp[e]));
-        out[e] = f2bf(fmaf(sgn * rot, bf2f(sp[e]), qc));
+        const float qc = bfround(v[e] * bf2f(cr[e]));
+        out[e] = f2bf(fmaf(sgn * rot, bf2f(sr[e]), qc));
     }
 }
 
@@ -357,8 +374,14 @@ __device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, in
 // block whose group holds slot n0 also makes the new key and value, writes them to the cache and keeps them in shared
 // memory, since it is the only block that reads them. The old keys' loads are issued before any of that, so the two
 // latencies overlap. The arithmetic is rope_values' and attn_item's: the row's bits are the two kernels' bits.
-template <int D, int G>
-__device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs& RA, int grp, int g, uint8_t* dsm_raw) {
+// G: the query heads this block takes, GQ the heads a kv head serves. G == GQ: the kv head's whole group (z = 0).
+// G == 1: head z of the group - a short cache leaves most of the card idle and the per-key arithmetic is what takes
+// the time, so the group's heads spread over GQ blocks (each reads the kv head's rows: they are few). Only block z = 0
+// writes the cache.
+template <int D, int G, int GQ>
+__device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs& RA, int grp, int g, int z,
+                                               uint8_t* dsm_raw) {
+    const int hbase = g * GQ + z;
     constexpr int E = D / 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = warp >> 1, half = warp & 1;
@@ -381,12 +404,42 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
     const bool owner = lo <= n0 && n0 <= hi;  // this block's group holds the new row
     const bf16* Kg = A.K + (size_t)g * A.hs;
     const bf16* Vg = A.V + (size_t)g * A.hs;
-    // ---- this lane's key; an old key's row starts its way here now ----------------------------------------------
+    // ---- this lane's key ------------------------------------------------------------------------------------------
     const int wbase = lo + tile * BN + half * 32;
     const int j = wbase + lane;
     const int new_lane = owner ? n0 - wbase : -1;  // the lane of this warp that holds the new key (if in 0..31)
     int row = -1;
     if (j >= first && j <= last) row = A.tbl != nullptr ? A.tbl[j] : j;
+    // a warp none of whose keys the row sees leaves its tile's half empty and stays out of the arithmetic
+    const bool any = __ballot_sync(0xffffffffu, row >= 0) != 0u;
+    // ---- the head's queries (every block), the new key and value (the owner): the block's LAST warps take them, the
+    // ones whose tiles a short cache leaves empty, and before their own keys - the rotation is what the block waits for
+    const int rw = NWA - 1 - warp;
+    if (rw < G) {
+        bf16 o[E];
+        rope_values<D, false>(RA, hbase + rw, 0, lane, pos, o);
+#pragma unroll
+        for (int e = 0; e < E; ++e) sm.qs[rw][lane * E + e] = bf2f(o[e]);
+        if (owner) {
+            bf16* dst = RA.qo + (size_t)(hbase + rw) * D + lane * E;
+#pragma unroll
+            for (int e = 0; e < E; ++e) dst[e] = o[e];
+        }
+    } else if (rw < G + 2 && owner) {
+        const bool is_k = rw == G;
+        bf16 o[E];
+        rope_values<D, false>(RA, is_k ? Hq + g : Hq + Hk + g, 0, lane, pos, o);
+        const int slot = A.tbl != nullptr ? A.tbl[n0] : n0;
+        bf16* dst = (is_k ? RA.K : RA.V) + (size_t)g * A.hs + (size_t)slot * A.rs + lane * E;
+        bf16* keep = (is_k ? knew : vnew) + lane * E;
+#pragma unroll
+        for (int e = 0; e < E; ++e) keep[e] = o[e];
+        if (z == 0) {
+#pragma unroll
+            for (int e = 0; e < E; ++e) dst[e] = o[e];
+        }
+    }
+    // an old key's row: D/8 independent 16-byte loads in flight
     uint4 kv[D / 8];
     {
         const bool fetch = row >= 0 && lane != new_lane;
@@ -394,58 +447,43 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) kv[c] = fetch ? __ldg(kr + c) : make_uint4(0u, 0u, 0u, 0u);
     }
-    // ---- the head's queries (every block), the new key and value (the owner) -----------------------------------
-    if (warp < G) {
-        bf16 o[E];
-        rope_values<D, false>(RA, g * G + warp, 0, lane, pos, o);
-#pragma unroll
-        for (int e = 0; e < E; ++e) sm.qs[warp][lane * E + e] = bf2f(o[e]);
-        if (owner) {
-            bf16* dst = RA.qo + (size_t)(g * G + warp) * D + lane * E;
-#pragma unroll
-            for (int e = 0; e < E; ++e) dst[e] = o[e];
-        }
-    } else if (warp < G + 2 && owner) {
-        const bool is_k = warp == G;
-        bf16 o[E];
-        rope_values<D, false>(RA, is_k ? Hq + g : Hq + Hk + g, 0, lane, pos, o);
-        const int slot = A.tbl != nullptr ? A.tbl[n0] : n0;
-        bf16* dst = (is_k ? RA.K : RA.V) + (size_t)g * A.hs + (size_t)slot * A.rs + lane * E;
-        bf16* keep = (is_k ? knew : vnew) + lane * E;
-#pragma unroll
-        for (int e = 0; e < E; ++e) dst[e] = o[e], keep[e] = o[e];
-    }
     __syncthreads();
-    if (lane == new_lane && row >= 0) {
-#pragma unroll
-        for (int c = 0; c < D / 8; ++c) kv[c] = reinterpret_cast<const uint4*>(knew)[c];
-    }
-    const float scale2 = __fmul_rn(A.scale, LOG2E);
     float s[G];
+    if (any) {
+        if (lane == new_lane && row >= 0) {
 #pragma unroll
-    for (int hh = 0; hh < G; ++hh) s[hh] = 0.f;
+            for (int c = 0; c < D / 8; ++c) kv[c] = reinterpret_cast<const uint4*>(knew)[c];
+        }
+        const float scale2 = __fmul_rn(A.scale, LOG2E);
 #pragma unroll
-    for (int c = 0; c < D / 8; ++c) {
-        const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
-                             bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
+        for (int hh = 0; hh < G; ++hh) s[hh] = 0.f;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
+                                 bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
+#pragma unroll
+            for (int hh = 0; hh < G; ++hh) {
+                float a = s[hh];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a = fmaf(kf[e], sm.qs[hh][c * 8 + e], a);
+                s[hh] = a;
+            }
+        }
 #pragma unroll
         for (int hh = 0; hh < G; ++hh) {
-            float a = s[hh];
+            s[hh] = row >= 0 ? __fmul_rn(s[hh], scale2) : NEG_INF;
+            float m = s[hh];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) a = fmaf(kf[e], sm.qs[hh][c * 8 + e], a);
-            s[hh] = a;
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) sm.hmax[tile][half][hh] = m;
         }
-    }
-#pragma unroll
-    for (int hh = 0; hh < G; ++hh) {
-        s[hh] = row >= 0 ? __fmul_rn(s[hh], scale2) : NEG_INF;
-        float m = s[hh];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) sm.hmax[tile][half][hh] = m;
+    } else {
+        // what the arithmetic would have left for a half with no key: max -inf, sum 0, outputs 0
+        if (lane < G) sm.hmax[tile][half][lane] = NEG_INF, sm.hsum[tile][half][lane] = 0.f;
+        for (int i = lane; i < G * D; i += 32) sm.ho[warp][i / D][i % D] = 0.f;
     }
     __syncthreads();
-    {
+    if (any) {
         float o[G][E];
 #pragma unroll
         for (int hh = 0; hh < G; ++hh) {
@@ -460,37 +498,35 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
             for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
         }
         __syncwarp();
-        // a warp none of whose keys the row sees adds nothing (its weights are all zero): skip its value loads
-        const bool any = __ballot_sync(0xffffffffu, row >= 0) != 0u;
-        constexpr int VB = 16;
-#pragma unroll 1
-        for (int i0 = 0; any && i0 < 32; i0 += VB) {
-            float vf[VB][E];
+        // all thirty-two keys' value runs in flight at once (raw, in the registers the key row has left); a key the
+        // row does not see has weight 0 over zeros
+        uint32_t vraw[32][E / 2];
 #pragma unroll
-            for (int u = 0; u < VB; ++u) {
-                const int rk = __shfl_sync(0xffffffffu, row, i0 + u);
-                const bool from_smem = i0 + u == new_lane;
-                const bf16* vr = from_smem ? vnew + lane * E : Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
-                if (E == 4) {
-                    const uint2 vv = rk < 0 ? make_uint2(0u, 0u)
-                                     : from_smem ? *reinterpret_cast<const uint2*>(vr)
-                                                 : __ldg(reinterpret_cast<const uint2*>(vr));
-                    vf[u][0] = bf_lo(vv.x), vf[u][1] = bf_hi(vv.x), vf[u][2] = bf_lo(vv.y), vf[u][3] = bf_hi(vv.y);
-                } else {
-                    const uint32_t vv = rk < 0 ? 0u
-                                        : from_smem ? *reinterpret_cast<const uint32_t*>(vr)
-                                                    : __ldg(reinterpret_cast<const uint32_t*>(vr));
-                    vf[u][0] = bf_lo(vv), vf[u][E - 1] = bf_hi(vv);
-                }
+        for (int u = 0; u < 32; ++u) {
+            const int rk = __shfl_sync(0xffffffffu, row, u);
+            const bool from_smem = u == new_lane;
+            const bf16* vr = from_smem ? vnew + lane * E : Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
+            if (E == 4) {
+                const uint2 vv = rk < 0 ? make_uint2(0u, 0u)
+                                 : from_smem ? *reinterpret_cast<const uint2*>(vr)
+                                             : __ldg(reinterpret_cast<const uint2*>(vr));
+                vraw[u][0] = vv.x, vraw[u][E / 2 - 1] = vv.y;
+            } else {
+                vraw[u][0] = rk < 0 ? 0u
+                             : from_smem ? *reinterpret_cast<const uint32_t*>(vr)
+                                         : __ldg(reinterpret_cast<const uint32_t*>(vr));
             }
+        }
 #pragma unroll
-            for (int u = 0; u < VB; ++u) {
+        for (int u = 0; u < 32; ++u) {
+            float vf[E];
 #pragma unroll
-                for (int hh = 0; hh < G; ++hh) {
-                    const float p = sm.ps[warp][hh][i0 + u];
+            for (int e = 0; e < E / 2; ++e) vf[2 * e] = bf_lo(vraw[u][e]), vf[2 * e + 1] = bf_hi(vraw[u][e]);
 #pragma unroll
-                    for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[u][e], o[hh][e]);
-                }
+            for (int hh = 0; hh < G; ++hh) {
+                const float p = sm.ps[warp][hh][u];
+#pragma unroll
+                for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[e], o[hh][e]);
             }
         }
 #pragma unroll
@@ -499,5 +535,8 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
             for (int e = 0; e < E; ++e) sm.ho[warp][hh][lane * E + e] = o[hh][e];
     }
     __syncthreads();
-    attn_finish<D, G>(A, sm, grp, g, 0, first, last, &s_last_block);
+    // The next kernel's blocks may come in now, not earlier: a GEMV's blocks open with a burst of weight copies into
+    // every SM, and a key or value row of this block queued behind that burst arrives microseconds late.
+    pdl_launch_dependents();
+    attn_finish<D, G>(A, sm, grp, hbase, G == GQ ? g : hbase, 0, first, last, &s_last_block);
 }

@@ -260,6 +260,12 @@ extern "C" int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void
                                      const void* tbl, int cap, void* stream) {
     if (!qkv || !cos_t || !sin_t || !n0p || !depth || !K || !V || !q) return B2_ERR_NULL;
     if (T <= 0 || Hq <= 0 || Hk <= 0 || cap <= 0) return B2_ERR_DOMAIN;
+    // a lane reads its D/32 elements of a head, a norm weight or a table row as one load
+    if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk) |
+         reinterpret_cast<uintptr_t>(cos_t) | reinterpret_cast<uintptr_t>(sin_t) | reinterpret_cast<uintptr_t>(q) |
+         reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V)) & 15)
+        return B2_ERR_DOMAIN;
+    if ((hs & 7) || (rs & 7)) return B2_ERR_DOMAIN;
     RopeArgs a{static_cast<const bf16*>(qkv), static_cast<const bf16*>(wq), static_cast<const bf16*>(wk),
                static_cast<const bf16*>(cos_t), static_cast<const bf16*>(sin_t), static_cast<const int*>(n0p),
                static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),

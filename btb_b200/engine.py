@@ -227,7 +227,7 @@ class CardEngine:
             "part_m": torch.zeros(self.S * M * Hq, dtype=torch.float32, device=dev),
             "part_l": torch.zeros(self.S * M * Hq, dtype=torch.float32, device=dev),
             "part_acc": torch.zeros(self.S * M * Hq * D, dtype=torch.float32, device=dev),
-            "cnt": torch.zeros(M * c.kv_heads, dtype=torch.int32, device=dev),
+            "cnt": torch.zeros(M * c.q_heads, dtype=torch.int32, device=dev),
             "pick": torch.zeros((int(capi.lib().btb_b200_argmax_scratch_bytes(M)) + 7) // 8, dtype=torch.int64,
                                 device=dev),
         }  # fmt: skip

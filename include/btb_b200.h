@@ -104,7 +104,8 @@ int btb_b200_attn_decode(const void* q, const void* K, const void* V, void* out,
  * (btb_attn_flash.cuh:372-675) back to back in the reference. Every block rotates its kv head's queries itself; the
  * block whose key group holds slot n0 makes the new key and value, writes them to the cache and uses them from shared
  * memory. Arguments as the two functions above (qkv [1, (Hq+2Hk) D]; q [1, Hq, D] is still written); the cache, the
- * query buffer and `out` hold the bits the two launches would have left. D 64 or 128. */
+ * query buffer and `out` hold the bits the two launches would have left. D 64 or 128. cnt: i32 [Hq] here (under 4096
+ * cached rows a kv head's query heads take a block each, and each counts its own groups in). */
 int btb_b200_attn_step(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
                        const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, void* out,
                        int Hq, int Hk, int D, long long hs, long long rs, int centered, float scale, void* part_m,

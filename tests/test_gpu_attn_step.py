@@ -39,7 +39,7 @@ def _case(Hq, Hk, D, n0, cap, win=0, tbl=False, sinks=False, qk_norm=True, seed=
         d.update(q=torch.zeros(1, Hq, D, dtype=torch.bfloat16, device=DEV),
                  att=torch.zeros(1, Hq * D, dtype=torch.bfloat16, device=DEV),
                  pm=torch.zeros(S * Hq, device=DEV), pl=torch.zeros(S * Hq, device=DEV),
-                 pa=torch.zeros(S * Hq * D, device=DEV), cnt=torch.zeros(Hk, dtype=torch.int32, device=DEV))  # fmt: skip
+                 pa=torch.zeros(S * Hq * D, device=DEV), cnt=torch.zeros(Hq, dtype=torch.int32, device=DEV))  # fmt: skip
         return d
 
     s = capi.stream_ptr()
@@ -67,6 +67,13 @@ def test_fused_row_equals_the_two_kernels(Hq, Hk, D, n0):
     _case(Hq, Hk, D, n0, cap=2048, seed=n0 + Hq)
 
 
+@pytest.mark.parametrize("Hq,Hk,D", [(32, 8, 128), (64, 8, 64), (8, 8, 128)])
+@pytest.mark.parametrize("n0", [4095, 4096, 4097, 6000])
+def test_fused_row_past_the_head_split(Hq, Hk, D, n0):
+    """at 4096 cached rows the kernel goes from a block a query head to a block a kv head"""
+    _case(Hq, Hk, D, n0, cap=6144, seed=n0 + Hq)
+
+
 @pytest.mark.parametrize("n0", [5, 200, 700, 1100])
 def test_fused_row_with_window_row_map_sinks_and_no_qk_norm(n0):
     _case(64, 8, 64, n0, cap=1536, win=128, sinks=True, qk_norm=False, seed=n0)
@@ -83,6 +90,6 @@ def test_fused_row_refuses_a_full_cache():
     call("btb_b200_attn_step", ptr(z(1, (Hq + 2 * Hk) * D)), 0, 0, 1e-6, ptr(z(cap, D)), ptr(z(cap, D)), ptr(n0),
          ptr(z(1, dt=torch.int32)), ptr(z(cap, Hk, D)), ptr(z(cap, Hk, D)), ptr(z(1, Hq, D)), ptr(z(1, Hq * D)), Hq, Hk, D,
          D, Hk * D, 0, 0.1, ptr(z(S * Hq, dt=torch.float32)), ptr(z(S * Hq, dt=torch.float32)),
-         ptr(z(S * Hq * D, dt=torch.float32)), ptr(z(Hk, dt=torch.int32)), 0, 0, 0, cap, capi.stream_ptr())  # fmt: skip
+         ptr(z(S * Hq * D, dt=torch.float32)), ptr(z(Hq, dt=torch.int32)), 0, 0, 0, cap, capi.stream_ptr())  # fmt: skip
     torch.cuda.synchronize()
     assert capi.status() == capi.ERR_DOMAIN
