@@ -87,24 +87,39 @@ __device__ __forceinline__ void stage_x_copy(bf16* xs, const bf16* x, int C) {
 
 // x[m][c] = bf16(bf16(silu(g)) * u), gu [M, 2C] gate then up: the values btb_silu_mul would have written
 // (native/cuda/btb_kernels.cu:171-209 of the reference); eight elements a thread a trip, elementwise so the order is free
-template <int M, int NT>
+// U: trips whose loads are in flight together
+template <int M, int NT, int U = 4>
 __device__ __forceinline__ void stage_x_silu(bf16* xs, const bf16* gu, int C) {
     const int cv = C >> 3;
     const int nt = NT > 0 ? NT : (int)blockDim.x;
-    for (int i = threadIdx.x; i < M * cv; i += nt) {
-        const int m = i / cv, c8 = i - m * cv;
-        const uint4 gv = ldcg16(reinterpret_cast<const uint4*>(gu + (size_t)m * 2 * C) + c8);
-        const uint4 uv = ldcg16(reinterpret_cast<const uint4*>(gu + (size_t)m * 2 * C + C) + c8);
-        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
-        uint32_t o[4];
+    for (int i0 = threadIdx.x; i0 < M * cv; i0 += U * nt) {
+        uint4 gv[U], uv[U];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float a = bfround(act_silu(bf_lo(gw[k]))) * bf_lo(uw[k]);
-            const float b = bfround(act_silu(bf_hi(gw[k]))) * bf_hi(uw[k]);
-            const __nv_bfloat162 pr = __floats2bfloat162_rn(a, b);
-            o[k] = *reinterpret_cast<const uint32_t*>(&pr);
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * nt;
+            if (i < M * cv) {
+                const int m = i / cv, c8 = i - m * cv;
+                gv[u] = ldcg16(reinterpret_cast<const uint4*>(gu + (size_t)m * 2 * C) + c8);
+                uv[u] = ldcg16(reinterpret_cast<const uint4*>(gu + (size_t)m * 2 * C + C) + c8);
+            }
         }
-        reinterpret_cast<uint4*>(xs + (size_t)m * C)[c8] = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * nt;
+            if (i < M * cv) {
+                const int m = i / cv, c8 = i - m * cv;
+                const uint32_t gw[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w}, uw[4] = {uv[u].x, uv[u].y, uv[u].z, uv[u].w};
+                uint32_t o[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float a = bfround(act_silu(bf_lo(gw[k]))) * bf_lo(uw[k]);
+                    const float b = bfround(act_silu(bf_hi(gw[k]))) * bf_hi(uw[k]);
+                    const __nv_bfloat162 pr = __floats2bfloat162_rn(a, b);
+                    o[k] = *reinterpret_cast<const uint32_t*>(&pr);
+                }
+                reinterpret_cast<uint4*>(xs + (size_t)m * C)[c8] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
     }
 }
 
@@ -113,7 +128,7 @@ __device__ __forceinline__ void stage_x_silu(bf16* xs, const bf16* gu, int C) {
 // x = bf16(hv * rsqrt(ss / H + eps) * w). Every CTA computes the same values; the one with `writer` set stores the
 // new residual to h_out (never the buffer h_in points into). `rows`: when not null, row m of the input is
 // h_in + rows[m] * C (an embedding table's row: the gather folded in). scratch: C + 256 floats.
-template <int M, int NT>
+template <int M, int NT, bool PRE = true>
 __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf16* h_in, const long long* rows,
                                              const bf16* y_add, const bf16* norm_w, bf16* h_out, float eps,
                                              int centered, int T, int C, bool writer) {
@@ -121,6 +136,13 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
     float* red = hsm + C;
     const int cv = C >> 3, tid = threadIdx.x;
     const int nt = NT > 0 ? NT : (int)blockDim.x;
+    // the norm's weights are on their way before the first barrier (they do not depend on the row)
+    // (PRE false: a caller short of registers reads them where they are used)
+    constexpr int UW = PRE ? 4 : 1;
+    uint4 wpre[UW];
+#pragma unroll
+    for (int u = 0; u < UW; ++u)
+        if (PRE && tid + u * nt < cv) wpre[u] = __ldg(reinterpret_cast<const uint4*>(norm_w) + tid + u * nt);
     for (int m = 0; m < M; ++m) {
         if (m >= T) {  // a padding row: zeros
             for (int i = tid; i < cv; i += nt) reinterpret_cast<uint4*>(xs + (size_t)m * C)[i] = make_uint4(0u, 0u, 0u, 0u);
@@ -142,11 +164,8 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
             }
             if (writer && h_out != nullptr)
                 reinterpret_cast<uint4*>(h_out + (size_t)m * C)[i] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                hsm[i * 8 + 2 * k] = bf_lo(hw[k]);
-                hsm[i * 8 + 2 * k + 1] = bf_hi(hw[k]);
-            }
+            reinterpret_cast<float4*>(hsm)[2 * i] = make_float4(bf_lo(hw[0]), bf_hi(hw[0]), bf_lo(hw[1]), bf_hi(hw[1]));
+            reinterpret_cast<float4*>(hsm)[2 * i + 1] = make_float4(bf_lo(hw[2]), bf_hi(hw[2]), bf_lo(hw[3]), bf_hi(hw[3]));
         }
         __syncthreads();
         if (tid < 256) {  // the reference's 256 strided partial sums, whatever the block's width
@@ -155,14 +174,44 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
             red[tid] = ss;
         }
         __syncthreads();
-        for (int st = 128; st > 0; st >>= 1) {
-            if (tid < st) red[tid] += red[tid + st];
-            __syncthreads();
+        // the reference's tree red[t] += red[t + st], st = 128 .. 1, with the same pairs in the same order on one warp:
+        // lane l holds red[l + 32 k]; st >= 32 pairs registers of one lane, st < 32 pairs lanes
+        if (tid < 32) {
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = red[tid + 32 * k];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] += v[k + 4];
+            v[0] += v[2];
+            v[1] += v[3];
+            v[0] += v[1];
+#pragma unroll
+            for (int st = 16; st > 0; st >>= 1) v[0] += __shfl_down_sync(0xffffffffu, v[0], st);
+            if (tid == 0) red[0] = v[0];
         }
+        __syncthreads();
         const float rstd = rsqrtf(red[0] / (float)C + eps);
-        for (int i = tid; i < C; i += nt) {
-            const float wv = bf2f(norm_w[i]);
-            xs[(size_t)m * C + i] = f2bf(hsm[i] * rstd * (centered ? 1.f + wv : wv));
+        for (int i = tid, u = 0; i < cv; i += nt, ++u) {
+            uint4 wv4;
+            switch (PRE ? u : 99) {  // a constant index keeps the prefetched vectors in registers
+                case 0: wv4 = wpre[0]; break;
+                case 1: wv4 = wpre[UW > 1 ? 1 : 0]; break;
+                case 2: wv4 = wpre[UW > 2 ? 2 : 0]; break;
+                case 3: wv4 = wpre[UW > 3 ? 3 : 0]; break;
+                default: wv4 = __ldg(reinterpret_cast<const uint4*>(norm_w) + i); break;
+            }
+            const uint32_t ww[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+            const float4 ha = reinterpret_cast<const float4*>(hsm)[2 * i], hb = reinterpret_cast<const float4*>(hsm)[2 * i + 1];
+            const float hv8[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float w0 = bf_lo(ww[k]), w1 = bf_hi(ww[k]);
+                const bf16 a = f2bf(hv8[2 * k] * rstd * (centered ? 1.f + w0 : w0));
+                const bf16 b = f2bf(hv8[2 * k + 1] * rstd * (centered ? 1.f + w1 : w1));
+                o[k] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+            }
+            reinterpret_cast<uint4*>(xs + (size_t)m * C)[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
         __syncthreads();
     }

@@ -251,9 +251,9 @@ __global__ void __launch_bounds__(NTS, 1) step_kernel(const StepArgs A) {
                 const int C = op.C, R = op.R, seg = op.seg, fmt = op.fmt;
                 // x on the way in (the previous phase's output, visible after the barrier)
                 if (op.xkind == XK_COPY) stage_x_copy<M, NTS>(xs, op.x, C);
-                else if (op.xkind == XK_SILU) stage_x_silu<M, NTS>(xs, op.x, C);
+                else if (op.xkind == XK_SILU) stage_x_silu<M, NTS, 1>(xs, op.x, C);
                 else
-                    stage_x_norm<M, NTS>(xs, norm_scratch, op.h_in, op.rows, op.y_add, op.norm_w, op.h_out, op.eps,
+                    stage_x_norm<M, NTS, false>(xs, norm_scratch, op.h_in, op.rows, op.y_add, op.norm_w, op.h_out, op.eps,
                                          op.centered, A.T, C, blockIdx.x == 0);
                 __syncthreads();
                 const int nseg = (C + seg - 1) / seg;
