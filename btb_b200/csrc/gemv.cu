@@ -51,6 +51,10 @@ struct GemvArgs {
     int T;               // live rows (rows T..M-1 of x are zeros)
     const float* fscales;  // FP8: the [sr, sc] f32 grid
     int fsc, fbm, fbn;     // its columns, a block's rows and columns
+    // SwiGLU epilogue: w is [2 * pair, C] (gate rows, then up rows); a warp takes gate row p and up row p + pair one
+    // after the other and writes y[m][p] = bf16(bf16(silu(bf16 g)) * bf16 u) - what btb_silu_mul makes of the two
+    // outputs. 0: off. R counts pairs then.
+    int pair;
 };
 
 // NWT: the most warps a CTA of this instance is launched with (its register budget); the launch picks how many
@@ -79,7 +83,7 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     const int cnt = base + ((int)blockIdx.x < rem ? 1 : 0);
     // this warp's rows: r0 + warp, + nw, ..; its items are (row, segment) pairs in order
     const int my_rows = cnt > warp ? (cnt - warp + nw - 1) / nw : 0;
-    const int n_items = my_rows * nseg;
+    const int n_items = my_rows * nseg * (A.pair != 0 ? 2 : 1);
 
     if (lane == 0) {
         for (int s = 0; s < S; ++s) mbar_init(smem_u32(bars + s), 1);
@@ -89,14 +93,15 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
 
     const uint64_t pol = A.evict_first ? l2_evict_first_policy() : 0;
     // the producer's cursor: the next item to copy (kept by every lane, issued by lane 0); no division on the way
-    int p_row = r0 + warp, p_seg = 0, p_st = 0, issued = 0;
+    int p_row = r0 + warp, p_seg = 0, p_st = 0, issued = 0, p_sub = 0;
+    const int pair = A.pair;
     auto issue_next = [&]() {
         const int c0 = p_seg * seg;
         const int n = min(seg, C - c0);
         if (lane == 0) {
             const uint32_t bar = smem_u32(bars + p_st);
             const uint32_t dst = smem_u32(ring + (size_t)p_st * sbytes);
-            const size_t e0 = (size_t)p_row * C + c0;
+            const size_t e0 = (size_t)(p_row + p_sub * pair) * C + c0;
             if (FMT == F_BF16 || FMT == F_FP8) {
                 const uint32_t nb = FMT == F_BF16 ? n * 2 : n;
                 mbar_expect_tx(bar, nb);
@@ -117,7 +122,12 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
         if (++p_st == S) p_st = 0;
         if (++p_seg == nseg) {
             p_seg = 0;
-            p_row += nw;
+            if (pair != 0 && p_sub == 0) {
+                p_sub = 1;  // the pair's up row next
+            } else {
+                p_sub = 0;
+                p_row += nw;
+            }
         }
     };
     // fill the ring: weights do not depend on the grids before this one
@@ -143,15 +153,16 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     for (int m = 0; m < M; ++m) acc[m] = 0.f;
     bool ok = true;
     // the consumer's cursor
-    int c_row = r0 + warp, c_seg = 0, c_st = 0;
+    int c_row = r0 + warp, c_seg = 0, c_st = 0, c_sub = 0;
     uint32_t c_par = 0;
+    float gate[M];  // a pair's gate outputs (bf16 values) while its up row streams
     int i = 0;
     for (; i < n_items; ++i) {
         if (!mbar_wait_bounded(smem_u32(bars + c_st), c_par)) {
             ok = false;
             break;
         }
-        const int row = c_row;
+        const int row = c_row + c_sub * pair;
         const int c0 = c_seg * seg;
         const int nch = min(seg, C - c0) >> 3;  // the segment's chunks; its first chunk is global chunk c0 / 8
         const uint8_t* stg = ring + (size_t)c_st * sbytes;
@@ -172,11 +183,22 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 const float s = warp_sum(acc[m]);
-                if (lane == 0) A.y[(size_t)m * R + row] = f2bf(s);
+                if (pair == 0) {
+                    if (lane == 0) A.y[(size_t)m * R + row] = f2bf(s);
+                } else if (c_sub == 0) {
+                    gate[m] = bfround(s);
+                } else if (lane == 0) {
+                    A.y[(size_t)m * R + c_row] = f2bf(bfround(act_silu(gate[m])) * bfround(s));
+                }
                 acc[m] = 0.f;
             }
             c_seg = 0;
-            c_row += nw;
+            if (pair != 0 && c_sub == 0) {
+                c_sub = 1;
+            } else {
+                c_sub = 0;
+                c_row += nw;
+            }
         } else {
             ++c_seg;
         }
@@ -359,15 +381,17 @@ extern "C" int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, 
     return p.xs ? launch_m<F_BF16, X_SMEM>(M, a, p, s) : launch_m_global<F_BF16>(M, a, p, s);
 }
 
-// x = rmsnorm(h_in + y) * w computed inside the GEMV (bf16 weights, or pack12 when hi4 is not null)
-extern "C" int btb_b200_gemv_norm(const void* w, const void* hi4, const void* table, const void* esc_idx,
-                                  const void* esc_val, const void* esc_row, const void* h_in, const void* y_add,
-                                  const void* norm_w, float eps, int centered, void* h_out, void* y, int T, int M, int R,
-                                  int C, void* stream) {
+// x = rmsnorm(h_in + y) * w computed inside the GEMV (bf16 weights, or pack12 when hi4 is not null); swiglu: the rows are
+// gate then up and the output is the activated product of each pair
+static int gemv_norm_impl(const void* w, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
+                          const void* esc_row, const void* h_in, const void* y_add, const void* norm_w, float eps,
+                          int centered, void* h_out, void* y, int T, int M, int R, int C, bool swiglu, void* stream) {
     int rc = check_dims(w, h_in, y, M, R, C);
     if (rc) return rc;
     if (norm_w == nullptr || (y_add != nullptr && h_out == nullptr)) return B2_ERR_NULL;
     if (T <= 0 || T > M || M > 8 || !(eps == eps) || h_out == h_in) return B2_ERR_DOMAIN;
+    if (swiglu && (R & 1)) return B2_ERR_DOMAIN;
+    if (reinterpret_cast<uintptr_t>(norm_w) & 15) return B2_ERR_DOMAIN;  // read as 16-byte vectors
     const bool p12 = hi4 != nullptr;
     if (p12 && (table == nullptr || (C & 31) != 0 || (reinterpret_cast<uintptr_t>(hi4) & 15))) return B2_ERR_DOMAIN;
     GemvArgs a{};
@@ -378,15 +402,32 @@ extern "C" int btb_b200_gemv_norm(const void* w, const void* hi4, const void* ta
     a.esc_row = static_cast<const int32_t*>(esc_row);
     if (p12) memcpy(a.table, table, 16);
     a.y = static_cast<bf16*>(y);
-    a.R = R, a.C = C;
+    a.R = swiglu ? R / 2 : R, a.C = C;
+    a.pair = swiglu ? R / 2 : 0;
     a.h_in = static_cast<const bf16*>(h_in), a.y_add = static_cast<const bf16*>(y_add);
     a.norm_w = static_cast<const bf16*>(norm_w), a.h_out = static_cast<bf16*>(h_out);
     a.eps = eps, a.centered = centered, a.T = T;
-    Plan p = p12 ? make_plan<F_P12>(M, R, C, true, true) : make_plan<F_BF16>(M, R, C, true, true);
+    Plan p = p12 ? make_plan<F_P12>(M, a.R, C, true, true) : make_plan<F_BF16>(M, a.R, C, true, true);
     if (!p.xs) return B2_ERR_DOMAIN;  // too wide to stage: the caller runs btb_b200_add_rmsnorm and the plain GEMV
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return p12 ? launch_m<F_P12, X_SMEM_NORM>(M, a, p, s) : launch_m<F_BF16, X_SMEM_NORM>(M, a, p, s);
+}
+
+extern "C" int btb_b200_gemv_norm(const void* w, const void* hi4, const void* table, const void* esc_idx,
+                                  const void* esc_val, const void* esc_row, const void* h_in, const void* y_add,
+                                  const void* norm_w, float eps, int centered, void* h_out, void* y, int T, int M, int R,
+                                  int C, void* stream) {
+    return gemv_norm_impl(w, hi4, table, esc_idx, esc_val, esc_row, h_in, y_add, norm_w, eps, centered, h_out, y, T, M, R,
+                          C, false, stream);
+}
+
+extern "C" int btb_b200_gemv_norm_swiglu(const void* w, const void* hi4, const void* table, const void* esc_idx,
+                                         const void* esc_val, const void* esc_row, const void* h_in, const void* y_add,
+                                         const void* norm_w, float eps, int centered, void* h_out, void* m_out, int T,
+                                         int M, int R, int C, void* stream) {
+    return gemv_norm_impl(w, hi4, table, esc_idx, esc_val, esc_row, h_in, y_add, norm_w, eps, centered, h_out, m_out, T, M,
+                          R, C, true, stream);
 }
 
 // FP8 e4m3 weights with an f32 [sr, sc] block-scale grid, each weight the bf16 btb holds for it, widened in registers

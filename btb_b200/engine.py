@@ -192,6 +192,7 @@ class CardEngine:
         self.n0 = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.silu_fold = silu_fold
         self.fuse_norm = fuse_norm
+        self.swiglu_epilogue = True  # SwiGLU in the gate/up GEMV's epilogue (passes of up to 8 rows)
         self.fuse_attn = True  # the step's row: norm + RoPE + cache write + attention as one launch
         # the whole step as one persistent kernel (head dim 128 only); else one launch a kernel
         self.step_kernel = bool(step_kernel) and weights.cfg.head_dim == 128 and weights.cfg.q_heads // weights.cfg.kv_heads in (2, 4, 8)
@@ -262,14 +263,15 @@ class CardEngine:
         fuse = self.fuse_norm and M <= 8 and M * max(H, 1) * 2 <= 64 * 1024
         hcur, halt = g["h"], g["h2"]
 
-        def normed_matvec(W: Any, norm_w: torch.Tensor, y_add: Any, out: torch.Tensor, R: int) -> None:
+        def normed_matvec(W: Any, norm_w: torch.Tensor, y_add: Any, out: torch.Tensor, R: int,
+                          swiglu: bool = False) -> None:
             nonlocal hcur, halt
             if fuse:
                 p12 = isinstance(W, P12Matrix)
                 parts = ((ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val), ptr(W.esc_row)) if p12
                          else (ptr(W), 0, 0, 0, 0, 0))  # fmt: skip
-                k("btb_b200_gemv_norm", *parts, ptr(hcur), ptr(y_add), ptr(norm_w), c.eps, 0,
-                  ptr(halt) if y_add is not None else 0, ptr(out), T, M, R, H, s)
+                k("btb_b200_gemv_norm_swiglu" if swiglu else "btb_b200_gemv_norm", *parts, ptr(hcur), ptr(y_add),
+                  ptr(norm_w), c.eps, 0, ptr(halt) if y_add is not None else 0, ptr(out), T, M, R, H, s)
                 if y_add is not None:
                     hcur, halt = halt, hcur
             else:
@@ -281,6 +283,12 @@ class CardEngine:
             normed_matvec(L.qkv, L.ln1, y_prev, g["qkv"], c.qkv_rows)
             self._attention(g, i, L.wq, L.wk, T, s)
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
+            if fuse and self.swiglu_epilogue and not isinstance(L.gu, FP8Matrix):
+                # the gate/up GEMV activates each pair itself: g["gu"] is never written, the down GEMV reads g["m"]
+                normed_matvec(L.gu, L.ln2, g["y"], g["m"], 2 * I, swiglu=True)
+                self._matvec(L.down, g["m"], g["y"], M, H, I, s)
+                y_prev = g["y"]
+                continue
             normed_matvec(L.gu, L.ln2, g["y"], g["gu"], 2 * I)
             if self.silu_fold and M <= 8 and M * I * 2 <= 64 * 1024:
                 if isinstance(L.down, P12Matrix):

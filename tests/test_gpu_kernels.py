@@ -517,3 +517,44 @@ def test_launcher_refuses_unknown_kernels(b200):
         b200.launch("btb_delta_nodes", (1, 1, 1), (32, 1, 1), [])
     assert b200.serves("btb_gemv_bf16_m8") and not b200.serves("btb_gemv_q4k_bf16_m1")
     assert isinstance(C.c_void_p(0), C._SimpleCData) and os.path.exists(capi.LIB_PATH)
+
+
+# ---- SwiGLU in the gate/up GEMV's epilogue -----------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("M,T", [(1, 1), (2, 2), (4, 3), (8, 8)])
+@pytest.mark.parametrize("I,H", [(9728, 2560), (512, 256), (300, 264), (37, 1024)])
+def test_gemv_norm_swiglu_equals_gemv_norm_then_silu_mul(M, T, I, H):
+    rng = np.random.default_rng(I + H + M)
+    w = bf(rand_bf(rng, (2 * I, H), 0.05))
+    h, yadd, nw = bf(rand_bf(rng, (M, H))), bf(rand_bf(rng, (M, H))), bf(rand_bf(rng, (H,)))
+    h2a, h2b = torch.zeros_like(h), torch.zeros_like(h)
+    gu = torch.zeros(M, 2 * I, dtype=torch.bfloat16, device=DEV)
+    want = torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    got = torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_gemv_norm", ptr(w), 0, 0, 0, 0, 0, ptr(h), ptr(yadd), ptr(nw), 1e-6, 0, ptr(h2a), ptr(gu), T, M, 2 * I,
+         H, s())  # fmt: skip
+    call("btb_b200_silu_mul", ptr(gu), ptr(want), M, I, s())
+    call("btb_b200_gemv_norm_swiglu", ptr(w), 0, 0, 0, 0, 0, ptr(h), ptr(yadd), ptr(nw), 1e-6, 0, ptr(h2b), ptr(got), T,
+         M, 2 * I, H, s())  # fmt: skip
+    assert np.array_equal(bits(got)[:T], bits(want)[:T])
+    assert np.array_equal(bits(h2a)[:T], bits(h2b)[:T])
+
+
+def test_gemv_norm_swiglu_over_pack12_weights():
+    from btb_b200.engine import P12Matrix
+
+    rng = np.random.default_rng(5)
+    I, H, M = 384, 512, 2
+    wbits, parts = _p12_case(rng, 2 * I, H, True)
+    w = bf(wbits)
+    P = P12Matrix(parts, 2 * I, H, DEV)
+    h, yadd, nw = bf(rand_bf(rng, (M, H))), bf(rand_bf(rng, (M, H))), bf(rand_bf(rng, (H,)))
+    h2a, h2b = torch.zeros_like(h), torch.zeros_like(h)
+    want = torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    got = torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_gemv_norm_swiglu", ptr(w), 0, 0, 0, 0, 0, ptr(h), ptr(yadd), ptr(nw), 1e-6, 0, ptr(h2a), ptr(want), M, M,
+         2 * I, H, s())  # fmt: skip
+    call("btb_b200_gemv_norm_swiglu", ptr(P.lo), ptr(P.hi4), P.table, ptr(P.esc_idx), ptr(P.esc_val), ptr(P.esc_row),
+         ptr(h), ptr(yadd), ptr(nw), 1e-6, 0, ptr(h2b), ptr(got), M, M, 2 * I, H, s())  # fmt: skip
+    assert np.array_equal(bits(got), bits(want))
