@@ -295,6 +295,9 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (PROMPT,), generator=g)
     eng.reset()
+    if args.speculative:
+        run_speculative(args, eng, cfg, storage, parallelism, rank, world, dist)
+        return
     if args.workload == "llama-70b":
         # the metric excludes prefill: the 32768-row context is seeded synthetic cache rows (bf16 N(0, 1)), not a
         # prefilled prompt - a chain-pass prefill of that length through the decode kernels would take minutes
@@ -388,12 +391,15 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     achieved = abytes / (gemv_ms / 1000.0) / 1e9
     roof = {"bound": "hbm", "kernel": "gemv_stream (all of a token's GEMVs)", "achieved": achieved, "peak": peak,
             "unit": "GB/s", "frac": achieved / peak, "peak_source": which, "frac_of_8tbs": achieved / 8000.0,
-            "launches": n_gemv, "avg_launch_us": gemv_ms * 1000.0 / n_gemv, "traffic": TRAFFIC.get(storage)}  # fmt: skip
+            "launches": n_gemv, "avg_launch_us": gemv_ms * 1000.0 / n_gemv,
+            # DRAM bytes a launch: the ncu capture's read+write over algorithmic bytes, scaled to the average launch
+            "traffic": TRAFFIC[storage] * abytes / n_gemv if TRAFFIC.get(storage) else None}  # fmt: skip
 
     line = {
         "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": world, "steps": steps_done, "warmup": W,
         "ms_per_step": ms / steps_done, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16" if storage == "bf16" else "bf16 (pack12 weights widened in registers)", "data": "synthetic",
+        "dtype": "bf16" if storage == "bf16" else f"bf16 ({STORED.get(storage, storage)} weights widened in registers)",
+        "data": "synthetic",
         "config": {"workload": f"{cfg.name}-shape {storage}, batch 1, greedy decode after a 128-token prompt"
                    if args.workload != "llama-70b" else f"{cfg.name}-shape bf16, batch 1, greedy decode over a "
                    f"{args.context or 32768}-row synthetic cache",
@@ -433,8 +439,140 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         os._exit(0)
 
 
+STORED = {"p12": "pack12", "mx4": "MXFP4 expert", "fp8": "FP8 block-scaled"}
+
+def run_case(args) -> None:
+    """one kernel on a small case, for a profiler capture or a quick look: `gemv:RxC[:M[:fmt]]` rotates over enough
+    seeded matrices to stay out of L2 (fmt bf16 | p12); `attn:N` is the step's fused attention row over N cached rows
+    at the Qwen3-4B head shape. Prints us a launch (CUDA events) and, for a GEMV, the weight-streaming rate."""
+    import torch
+
+    from btb_b200 import capi
+    from btb_b200 import engine as E
+    from btb_b200.capi import call, ptr
+
+    kind, _, rest = args.case.partition(":")
+    sp = capi.stream_ptr()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    out: dict = {"case": args.case}
+    if kind == "gemv":
+        parts = rest.split(":")
+        R, C_ = (int(v) for v in parts[0].split("x"))
+        M = int(parts[1]) if len(parts) > 1 else 1
+        fmt = parts[2] if len(parts) > 2 else "bf16"
+        per = R * C_ * (2 if fmt == "bf16" else 1.5)
+        nmat = max(2, int(400e6 // per) + 1)
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        ws = []
+        for _ in range(nmat):
+            w = torch.randn(R, C_, device="cuda", generator=gen).mul_(0.02).to(torch.bfloat16)
+            if fmt == "p12":
+                from btb_b200 import pack12
+
+                w = E.P12Matrix(pack12.pack_bf16(w.cpu()), R, C_, "cuda")
+            ws.append(w)
+        x = torch.randn(M, C_, device="cuda", generator=gen).to(torch.bfloat16)
+        y = torch.zeros(M, R, device="cuda", dtype=torch.bfloat16)
+
+        def one(w):
+            if fmt == "p12":
+                call("btb_b200_gemv_p12", ptr(w.lo), ptr(w.hi4), w.table, ptr(w.esc_idx), ptr(w.esc_val), ptr(w.esc_row),
+                     ptr(x), ptr(y), M, R, C_, sp)  # fmt: skip
+            else:
+                call("btb_b200_gemv_bf16", ptr(w), ptr(x), ptr(y), M, R, C_, sp)
+
+        for it in range(3):
+            e0.record()
+            for w in ws:
+                one(w)
+            e1.record()
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1000 / nmat
+        out.update(us_per_launch=us, gbs=per / us / 1e3, matrices=nmat, bytes_per_launch=per + 2 * M * (R + C_))
+    elif kind == "attn":
+        n0v = int(rest)
+        c = E.QWEN3_4B
+        Hq, Hk, D, cap = c.q_heads, c.kv_heads, c.head_dim, ((n0v + 64 + 511) // 512) * 512
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        rnd = lambda *sh: torch.randn(*sh, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
+        qkv, K_, V_ = rnd(1, (Hq + 2 * Hk) * D), rnd(cap, Hk, D), rnd(cap, Hk, D)
+        wq, wk, cos, sin = rnd(D), rnd(D), rnd(cap, D), rnd(cap, D)
+        q, att = torch.zeros(1, Hq, D, device="cuda", dtype=torch.bfloat16), torch.zeros(1, Hq * D, device="cuda", dtype=torch.bfloat16)
+        S = cap // 512
+        pm, pl, pa = torch.zeros(S * Hq, device="cuda"), torch.zeros(S * Hq, device="cuda"), torch.zeros(S * Hq * D, device="cuda")
+        cnt = torch.zeros(Hq, dtype=torch.int32, device="cuda")
+        n0 = torch.tensor([n0v], dtype=torch.int32, device="cuda")
+        depth = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for it in range(3):
+            e0.record()
+            for _ in range(20):
+                call("btb_b200_attn_step", ptr(qkv), ptr(wq), ptr(wk), 1e-6, ptr(cos), ptr(sin), ptr(n0), ptr(depth),
+                     ptr(K_), ptr(V_), ptr(q), ptr(att), Hq, Hk, D, D, Hk * D, 0, float(D**-0.5), ptr(pm), ptr(pl), ptr(pa),
+                     ptr(cnt), 0, 0, 0, cap, sp)  # fmt: skip
+            e1.record()
+            torch.cuda.synchronize()
+        out.update(us_per_launch=e0.elapsed_time(e1) * 1000 / 20, cached_rows=n0v)
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    assert capi.status() == 0
+    print(json.dumps(out), flush=True)
+
+
+def run_speculative(args, eng, cfg, storage, parallelism, rank, world, dist) -> None:
+    """greedy decode with an n-gram tree of `--speculative` drafts verified a pass: the prompt is a seeded 64-token
+    pattern repeated to 512 tokens so that the n-grams have something to propose"""
+    import torch
+
+    from btb_b200 import capi
+    from btb_b200.draft import generate_speculative
+
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (64,), generator=g).repeat(8)
+    K, W = args.steps, max(args.warmup, 3)
+    generate_speculative(eng, prompt, W, budget=args.speculative)
+    ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with Clocks(int(os.environ.get("LOCAL_RANK", "0"))) as clk:
+        t0 = time.perf_counter()
+        toks, stats = generate_speculative(eng, prompt, K + 1, budget=args.speculative, events=ev)
+        wall = time.perf_counter() - t0
+    ms = ev[0].elapsed_time(ev[1])
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    assert capi.status() == 0, "a kernel recorded a device-side refusal"
+    tps = K / (ms / 1000.0)
+    line = {
+        "metric": f"decode tok/s @bs1 ({cfg.name} shape, n-gram tree of {args.speculative} drafts a pass)", "value": tps,
+        "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "bf16" if storage == "bf16" else f"bf16 ({STORED.get(storage, storage)} weights widened in registers)",
+        "data": "synthetic",
+        "config": {"workload": f"{cfg.name}-shape {storage}, batch 1, speculative greedy decode after a 512-token prompt "
+                   "(a seeded 64-token pattern repeated)", "parallelism": parallelism, "passes": stats["passes"],
+                   "tokens_per_pass": stats["tokens_per_pass"], "l2": "weights per pass > L2 126 MB"},
+        "clocks": clk.summary(),
+        # the loop is the public call: every pass reads its picks back and sends the next tree's ids
+        "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 8 * (1 + args.speculative) * stats["passes"] / K,
+                "d2h_bytes_per_step": 8 * (1 + args.speculative) * stats["passes"] / K, "wall_s": wall},
+        "gpu_launches": None, "roofline": None,
+    }  # fmt: skip
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
 # per-launch DRAM traffic of the dominant kernel from the committed ncu summary (profiles/), filled once captured
-TRAFFIC: dict[str, float | None] = {"bf16": None, "p12": None}
+# (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes of the captured launch: 103.03 MB over 99.66 MB for
+# the 19456 x 2560 bf16 GEMV (profiles/gemv_stream_bf16_m1.md); traffic grows in proportion to the rows streamed
+TRAFFIC: dict[str, float | None] = {"bf16": 1.034, "p12": None}
 
 
 def main() -> None:
@@ -452,11 +590,15 @@ def main() -> None:
     ap.add_argument("--pdl", type=int, default=None)
     ap.add_argument("--cpu-steps", type=int, default=4)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--case", default="", help="one kernel on a small case: gemv:RxC[:M[:fmt]] or attn:N")
+    ap.add_argument("--speculative", type=int, default=0, help="verify an n-gram tree of this many drafts a pass")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args, rank)
     else:
         run_b200(args, rank, world, local_rank)

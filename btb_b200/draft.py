@@ -102,8 +102,10 @@ def walk(picks: Sequence[int], guesses: Sequence[int], children: dict[int, list[
         path.append(nxt)
 
 
-def generate_speculative(eng: Any, prompt: Any, max_new: int, budget: int = 8, v_max: int = 8) -> tuple[list[int], dict]:
-    """greedy decode with n-gram tree drafts; returns (tokens, stats). The tokens are the plain greedy loop's."""
+def generate_speculative(eng: Any, prompt: Any, max_new: int, budget: int = 8, v_max: int = 8,
+                         events: Any = None) -> tuple[list[int], dict]:
+    """greedy decode with n-gram tree drafts; returns (tokens, stats). The tokens are the plain greedy loop's.
+    events: a pair of CUDA events recorded after the prefill's pick and after the last commit (the decode alone)."""
     prompt = [int(t) for t in torch.as_tensor(prompt).tolist()]
     eng.reset()
     last = eng.prefill(torch.tensor(prompt))
@@ -114,6 +116,8 @@ def generate_speculative(eng: Any, prompt: Any, max_new: int, budget: int = 8, v
     toks = [cur]
     prop = NGramProposer(prompt + [cur])
     passes = 0
+    if events is not None:
+        events[0].record()
     c = eng.cfg
     row_el = c.kv_heads * c.head_dim
     while len(toks) < max_new:
@@ -134,6 +138,8 @@ def generate_speculative(eng: Any, prompt: Any, max_new: int, budget: int = 8, v
         toks += new
         cur = new[-1]
         passes += 1
+    if events is not None:
+        events[1].record()
     torch.cuda.synchronize()
     return toks[:max_new], {"passes": passes, "tokens_per_pass": (len(toks) - 1) / max(1, passes)}
 
