@@ -17,6 +17,7 @@ struct B2Tuning {
     int pdl;          // programmatic stream serialization: bit 0 the GEMV launches, bit 1 the small kernels
     int warps;        // warps a GEMV CTA for passes of one or two rows: 8 or 16
     int solo;         // under PDL a GEMV CTA claims an SM's shared memory for itself
+    int moe_stream;   // the picked experts' matvecs through the streaming kernel (0: the plain 16-lane kernel)
     int balance;      // pick the GEMV grid and warps a CTA so that the rows divide evenly over the warps
 };
 B2Tuning& b2_tuning();

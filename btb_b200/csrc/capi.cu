@@ -15,6 +15,7 @@ B2Tuning& b2_tuning() {
         env_int("BTB_B200_X_SMEM_MAX", 64 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
         env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 1),
         env_int("BTB_B200_WARPS", 16),             env_int("BTB_B200_SOLO", 1),
+        env_int("BTB_B200_MOE_STREAM", 1),
         env_int("BTB_B200_BALANCE", 1),
     };
     return t;
@@ -48,6 +49,7 @@ extern "C" int btb_b200_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "warps")) t.warps = value == 16 ? 16 : 8;
     else if (!strcmp(key, "balance")) t.balance = value != 0;
     else if (!strcmp(key, "solo")) t.solo = value != 0;
+    else if (!strcmp(key, "moe_stream")) t.moe_stream = value != 0;
     else return B2_ERR_DOMAIN;
     return B2_OK;
 }
@@ -58,11 +60,12 @@ int b2_status_take_attn(int*);
 int b2_status_take_step(int*);
 int b2_status_take_moe(int*);
 int b2_status_take_sample(int*);
+int b2_status_take_moes(int*);
 
 extern "C" int btb_b200_status(int* code) {
     if (code == nullptr) return B2_ERR_NULL;
     int (*const take[])(int*) = {b2_status_take_gemv, b2_status_take_layer, b2_status_take_attn, b2_status_take_step,
-                                 b2_status_take_moe, b2_status_take_sample};
+                                 b2_status_take_moe, b2_status_take_sample, b2_status_take_moes};
     *code = 0;
     for (auto f : take) {
         int v = 0;

@@ -15,6 +15,12 @@
 
 B2_DEFINE_STATUS(moe)
 
+bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, const void* x,
+                      int R, int C, int sr, int sc);
+int b2_moe_stream_launch(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
+                         const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C, int ep_rank,
+                         int ep_size, cudaStream_t s);
+
 namespace {
 
 // ---- router ---------------------------------------------------------------------------------------------------------
@@ -396,6 +402,10 @@ extern "C" int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, lon
         return B2_ERR_DOMAIN;
     if (fmt == L_MX4 && (C & 31)) return B2_ERR_DOMAIN;
     if (fmt == L_FP8 && (sr <= 0 || sc <= 0 || R % sr || C % sc)) return B2_ERR_DOMAIN;
+    // the streaming kernel takes every shape whose rows start on 16 bytes; the rest keep the plain 16-lane kernel
+    if (b2_tuning().moe_stream && n_tasks <= 65535 && b2_moe_stream_ok(fmt, w, scales, w_stride, s_stride, x, R, C, sr, sc))
+        return b2_moe_stream_launch(fmt, w, scales, w_stride, s_stride, sr, sc, idx, n_tasks, E, x, x_div, y, R, C, ep_rank,
+                                    ep_size, static_cast<cudaStream_t>(stream));
     L16Args a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), w_stride, s_stride,
               static_cast<const int*>(idx), static_cast<const float*>(x), x_div, static_cast<float*>(y), R, C,
               sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size};

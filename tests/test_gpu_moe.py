@@ -196,3 +196,59 @@ def test_verify_rows_equal_steps_in_a_moe_model():
     lg = bits(eng.forward(torch.tensor(toks[:5]), advance=False))
     for t in range(5):
         assert np.array_equal(lg[t], steps[t]), t
+
+
+# ---- the picked experts' matvecs through the streaming kernel ------------------------------------------------------
+
+
+@pytest.mark.parametrize("R,C_,n,k", [(1536, 2048, 8, 8), (2048, 768, 8, 1), (5760, 2880, 4, 4), (2880, 2880, 4, 1),
+                                      (300, 2880, 5, 1), (13, 96, 3, 3), (64, 128, 40, 8), (8, 32, 1, 1)])  # fmt: skip
+@pytest.mark.parametrize("fmt", ["bf16", "mx4", "fp8"])
+def test_expert_gemv_stream_equals_the_cpu_tier_bits(R, C_, n, k, fmt):
+    """task i multiplies expert idx[i] with x row i // x_div: every output the oracle's 16-lane sum to the bit"""
+    rng = np.random.default_rng(R + C_ + n)
+    E = 6
+    idx = rng.integers(0, E, size=n).astype(np.int32)
+    x = rng.standard_normal(((n + k - 1) // k, C_)).astype(np.float32)
+    xt, it = torch.from_numpy(x).to(DEV), torch.from_numpy(idx).to(DEV)
+    y = torch.full((n, R), 7.0, dtype=torch.float32, device=DEV)
+    if fmt == "bf16":
+        wb = O.f32_to_bits(rng.standard_normal((E, R, C_)).astype(np.float32) * 0.02)
+        wt = torch.from_numpy(wb.view(np.int16)).to(DEV)
+        args = (0, ptr(wt), 0, R * C_ * 2, 0, 1, 1)
+        want = [O.cpu_gemv_bf16(wb[idx[i]], x[i // k : i // k + 1])[0] for i in range(n)]
+    elif fmt == "mx4":
+        blocks, scales = _mx4(rng, E, R, C_)
+        bt, st = torch.from_numpy(blocks).to(DEV), torch.from_numpy(scales).to(DEV)
+        args = (1, ptr(bt), ptr(st), R * C_ // 2, R * C_ // 32, 1, 1)
+        want = [O.cpu_gemv_mxfp4(blocks[idx[i]], scales[idx[i]], R, C_, x[i // k : i // k + 1])[0] for i in range(n)]
+    else:
+        sr = next(d for d in (12, 8, 4, 2, 1) if R % d == 0)
+        sc = C_ // 128 if C_ % 128 == 0 else C_ // 32
+        w8, s8 = _fp8(rng, E, R, C_, sr, sc)
+        wt, st = torch.from_numpy(w8).to(DEV), torch.from_numpy(s8).to(DEV)
+        args = (2, ptr(wt), ptr(st), R * C_, sr * sc * 4, sr, sc)
+        want = [O.cpu_gemv_fp8(w8[idx[i]], s8[idx[i]], R, C_, x[i // k : i // k + 1])[0] for i in range(n)]
+    f, w, sc_, ws, ss, sr_, scn = args
+    call("btb_b200_moe_gemv", f, w, sc_, ws, ss, sr_, scn, ptr(it), n, E, ptr(xt), k, ptr(y), R, C_, 0, 1, s())
+    got = y.cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), np.stack(want).view(np.uint32))
+    # the plain 16-lane kernel gives the same bits
+    capi.set_tuning(moe_stream=0)
+    try:
+        y2 = torch.zeros_like(y)
+        call("btb_b200_moe_gemv", f, w, sc_, ws, ss, sr_, scn, ptr(it), n, E, ptr(xt), k, ptr(y2), R, C_, 0, 1, s())
+        assert torch.equal(y2.view(torch.int32), y.view(torch.int32))
+    finally:
+        capi.set_tuning(moe_stream=1)
+    # expert parallel: a rank's own experts, zeros for the others'; the ranks' sum is the whole
+    parts = []
+    for rank in range(2):
+        yp = torch.full((n, R), 3.0, dtype=torch.float32, device=DEV)
+        Wl = w  # expert e of rank r is global expert 2 e + r: the test hands each rank a strided view
+        call("btb_b200_moe_gemv", f, Wl + rank * ws, (sc_ + rank * ss) if sc_ else 0, 2 * ws, 2 * ss, sr_, scn, ptr(it), n, E,
+             ptr(xt), k, ptr(yp), R, C_, rank, 2, s())  # fmt: skip
+        parts.append(yp)
+    tot = parts[0] + parts[1]
+    assert torch.equal(tot.view(torch.int32), y.view(torch.int32))
+    assert all(bool((parts[int(idx[i]) % 2 ^ 1][i] == 0).all()) for i in range(n))
