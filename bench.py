@@ -263,7 +263,7 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     import dataclasses
 
     K, W = args.steps, max(args.warmup, 3)
-    cap = ((PROMPT + 2 * (K + W) + 64 + 511) // 512) * 512
+    cap = (((512 if args.speculative else PROMPT) + 2 * (K + W) + 96 + 511) // 512) * 512
     storage, parallelism = "bf16", ("replicas only" if world > 1 else "1 gpu")
     if args.pdl is not None:
         capi.set_tuning(pdl=args.pdl)

@@ -50,6 +50,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_p12_rows": (_I, [_P, _I, _I, _I, _P, _P]),
     "btb_b200_embed": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_add_rmsnorm": (_I, [_P, _P, _P, _F, _P, _I, _I, _I, _P]),
+    "btb_b200_add_rmsnorm_wide": (_I, [_P, _P, _P, _F, _P, _P, _I, _I, _I, _P]),
     "btb_b200_silu_mul": (_I, [_P, _P, _I, _I, _P]),
     "btb_b200_norm_rope_kv": (_I, [_P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _I, _P, _I, _P]),
     "btb_b200_attn_decode": (

@@ -18,6 +18,8 @@ struct B2Tuning {
     int warps;        // warps a GEMV CTA for passes of one or two rows: 8 or 16
     int solo;         // under PDL a GEMV CTA claims an SM's shared memory for itself
     int moe_stream;   // the picked experts' matvecs through the streaming kernel (0: the plain 16-lane kernel)
+    int ms_tpr;       // threads that share an expert row: 4, 8 or 16
+    int ms_seg, ms_warps;  // the expert kernel's columns a stage and warps a CTA (0: its own choice)
     int balance;      // pick the GEMV grid and warps a CTA so that the rows divide evenly over the warps
 };
 B2Tuning& b2_tuning();

@@ -15,7 +15,9 @@ B2Tuning& b2_tuning() {
         env_int("BTB_B200_X_SMEM_MAX", 64 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
         env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 1),
         env_int("BTB_B200_WARPS", 16),             env_int("BTB_B200_SOLO", 1),
-        env_int("BTB_B200_MOE_STREAM", 1),
+        env_int("BTB_B200_MOE_STREAM", 1),         env_int("BTB_B200_MS_TPR", 0),
+        env_int("BTB_B200_MS_SEG", 0),
+        env_int("BTB_B200_MS_WARPS", 0),
         env_int("BTB_B200_BALANCE", 1),
     };
     return t;

@@ -4,6 +4,8 @@
 // the whole-step kernel re-reads buffers that other SMs rewrote earlier in the same launch.
 #pragma once
 
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 enum Fmt { F_BF16 = 0, F_P12 = 1, F_FP8 = 2 };
@@ -37,6 +39,14 @@ __device__ __forceinline__ float fp8_held(uint32_t b, float scale) {
     const float v = __fmul_rn(__uint_as_float(__float_as_uint(mag) | ((b & 0x80u) << 24)), scale);
     const uint32_t u = __float_as_uint(v);
     return __uint_as_float((u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u);
+}
+
+// two e4m3 bytes (the low 16 bits of `two`) the same way through the conversion unit: e4m3 -> f16 is exact, f16 -> f32 is
+// exact, so the product and its rounding to bf16 (nearest, ties to even) are fp8_held's for every finite weight
+__device__ __forceinline__ void fp8x2_held(uint32_t two, float scale, float& a, float& b) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(two & 0xffffu), __NV_E4M3);
+    a = bfround(__fmul_rn(__half2float(__ushort_as_half(h.x)), scale));
+    b = bfround(__fmul_rn(__half2float(__ushort_as_half(h.y)), scale));
 }
 
 // the activation of the SwiGLU fold, native/cuda/btb_kernels.cu:159 of the reference: silu in f32 as torch computes it
@@ -231,11 +241,10 @@ __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* st
         if (FMT == F_FP8) {
             const uint2 wb = *reinterpret_cast<const uint2*>(stg + lc * 8);
             const float sc = __ldg(W.srow + (c0 + lc * 8) / W.bn);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                wf[e] = fp8_held((wb.x >> (8 * e)) & 0xffu, sc);
-                wf[4 + e] = fp8_held((wb.y >> (8 * e)) & 0xffu, sc);
-            }
+            fp8x2_held(wb.x, sc, wf[0], wf[1]);
+            fp8x2_held(wb.x >> 16, sc, wf[2], wf[3]);
+            fp8x2_held(wb.y, sc, wf[4], wf[5]);
+            fp8x2_held(wb.y >> 16, sc, wf[6], wf[7]);
         } else {
             uint32_t wp[4];
             if (FMT == F_BF16) {

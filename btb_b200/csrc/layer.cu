@@ -39,36 +39,104 @@ struct NormArgs {
     const bf16* y;
     const bf16* w;
     bf16* x;
+    float* xf;  // the same values as f32, or null (the MoE block's router and experts read x widened)
     float eps;
     int H, centered;
 };
+// One block a row. The arithmetic is the reference's: hv = bf16(h + y); thread i of 256 sums hv^2 over i, i + 256, ..;
+// the 256 -> 1 tree red[t] += red[t + st], st = 128 .. 1 (here with the same pairs in the same order on one warp);
+// x = bf16(hv * rsqrt(ss / H + eps) * w). The row is read once, as 16-byte runs when H allows, and kept in shared
+// memory (dynamic: H floats) between the two passes; the norm's weights are on their way before the reduction.
 __global__ void __launch_bounds__(256) add_rmsnorm(const NormArgs A) {
+    extern __shared__ __align__(16) float hsm[];
+    __shared__ float red[256];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, tid = threadIdx.x, H = A.H;
     bf16* hr = A.h + (size_t)t * H;
     const bf16* yr = A.y == nullptr ? nullptr : A.y + (size_t)t * H;
     bf16* xr = A.x + (size_t)t * H;
-    float ss = 0.f;
-    for (int i = tid; i < H; i += 256) {
-        float hv = bf2f(hr[i]);
-        if (yr != nullptr) {
-            hv = bfround(hv + bf2f(yr[i]));
-            hr[i] = f2bf(hv);
+    const bool vec = (H & 7) == 0 && ((reinterpret_cast<uintptr_t>(A.h) | reinterpret_cast<uintptr_t>(A.y) |
+                                       reinterpret_cast<uintptr_t>(A.w) | reinterpret_cast<uintptr_t>(A.x)) & 15) == 0;
+    if (vec) {
+        const int cv = H >> 3;
+        for (int i = tid; i < cv; i += 256) {
+            const uint4 hv = *(reinterpret_cast<const uint4*>(hr) + i);
+            uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+            if (yr != nullptr) {
+                const uint4 yv = *(reinterpret_cast<const uint4*>(yr) + i);
+                const uint32_t yw[4] = {yv.x, yv.y, yv.z, yv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const __nv_bfloat162 pr = __floats2bfloat162_rn(bf_lo(hw[k]) + bf_lo(yw[k]), bf_hi(hw[k]) + bf_hi(yw[k]));
+                    hw[k] = *reinterpret_cast<const uint32_t*>(&pr);
+                }
+                *(reinterpret_cast<uint4*>(hr) + i) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            }
+            reinterpret_cast<float4*>(hsm)[2 * i] = make_float4(bf_lo(hw[0]), bf_hi(hw[0]), bf_lo(hw[1]), bf_hi(hw[1]));
+            reinterpret_cast<float4*>(hsm)[2 * i + 1] = make_float4(bf_lo(hw[2]), bf_hi(hw[2]), bf_lo(hw[3]), bf_hi(hw[3]));
         }
-        ss = fmaf(hv, hv, ss);
+    } else {
+        for (int i = tid; i < H; i += 256) {
+            float hv = bf2f(hr[i]);
+            if (yr != nullptr) {
+                hv = bfround(hv + bf2f(yr[i]));
+                hr[i] = f2bf(hv);
+            }
+            hsm[i] = hv;
+        }
     }
-    __shared__ float red[256];
+    __syncthreads();
+    float ss = 0.f;
+    for (int i = tid; i < H; i += 256) ss = fmaf(hsm[i], hsm[i], ss);
     red[tid] = ss;
     __syncthreads();
-    for (int s = 128; s > 0; s >>= 1) {
-        if (tid < s) red[tid] += red[tid + s];
-        __syncthreads();
+    if (tid < 32) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = red[tid + 32 * k];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] += v[k + 4];
+        v[0] += v[2];
+        v[1] += v[3];
+        v[0] += v[1];
+#pragma unroll
+        for (int st = 16; st > 0; st >>= 1) v[0] += __shfl_down_sync(0xffffffffu, v[0], st);
+        if (tid == 0) red[0] = v[0];
     }
+    __syncthreads();
     const float rstd = rsqrtf(red[0] / (float)H + A.eps);
-    for (int i = tid; i < H; i += 256) {
-        const float wv = bf2f(A.w[i]);
-        xr[i] = f2bf(bf2f(hr[i]) * rstd * (A.centered ? 1.f + wv : wv));
+    float* xfr = A.xf == nullptr ? nullptr : A.xf + (size_t)t * H;
+    if (vec) {
+        const int cv = H >> 3;
+        for (int i = tid; i < cv; i += 256) {
+            const uint4 wv4 = __ldg(reinterpret_cast<const uint4*>(A.w) + i);
+            const uint32_t ww[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+            const float4 ha = reinterpret_cast<const float4*>(hsm)[2 * i], hb = reinterpret_cast<const float4*>(hsm)[2 * i + 1];
+            const float hv8[8] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+            uint32_t o[4];
+            float of[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float w0 = bf_lo(ww[k]), w1 = bf_hi(ww[k]);
+                const bf16 a = f2bf(hv8[2 * k] * rstd * (A.centered ? 1.f + w0 : w0));
+                const bf16 b = f2bf(hv8[2 * k + 1] * rstd * (A.centered ? 1.f + w1 : w1));
+                o[k] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
+                of[2 * k] = bf2f(a), of[2 * k + 1] = bf2f(b);
+            }
+            *(reinterpret_cast<uint4*>(xr) + i) = make_uint4(o[0], o[1], o[2], o[3]);
+            if (xfr != nullptr) {
+                reinterpret_cast<float4*>(xfr)[2 * i] = make_float4(of[0], of[1], of[2], of[3]);
+                reinterpret_cast<float4*>(xfr)[2 * i + 1] = make_float4(of[4], of[5], of[6], of[7]);
+            }
+        }
+    } else {
+        for (int i = tid; i < H; i += 256) {
+            const float wv = bf2f(A.w[i]);
+            const bf16 o = f2bf(hsm[i] * rstd * (A.centered ? 1.f + wv : wv));
+            xr[i] = o;
+            if (xfr != nullptr) xfr[i] = bf2f(o);
+        }
     }
 }
 
@@ -236,13 +304,28 @@ extern "C" int btb_b200_embed(const void* table, const void* ids, void* h, int T
     return b2_launch((const void*)embed_rows, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
 }
 
-extern "C" int btb_b200_add_rmsnorm(void* h, const void* y, const void* w, float eps, void* x, int T, int H,
-                                    int centered, void* stream) {
+static int add_rmsnorm_launch(void* h, const void* y, const void* w, float eps, void* x, void* xf, int T, int H,
+                              int centered, void* stream) {
     if (!h || !w || !x) return B2_ERR_NULL;
     if (T <= 0 || H <= 0 || !(eps == eps)) return B2_ERR_DOMAIN;
+    if ((size_t)H * 4 > 200 * 1024) return B2_ERR_DOMAIN;  // the row is held in shared memory as f32
+    if (xf != nullptr && (reinterpret_cast<uintptr_t>(xf) & 15)) return B2_ERR_DOMAIN;
     NormArgs a{static_cast<bf16*>(h), static_cast<const bf16*>(y), static_cast<const bf16*>(w), static_cast<bf16*>(x),
-               eps, H, centered};
-    return b2_launch((const void*)add_rmsnorm, dim3(T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+               static_cast<float*>(xf), eps, H, centered};
+    static bool allowed[64];
+    if (const int rc = b2_allow_smem((const void*)add_rmsnorm, allowed)) return rc;
+    return b2_launch((const void*)add_rmsnorm, dim3(T), dim3(256), (size_t)H * 4, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" int btb_b200_add_rmsnorm(void* h, const void* y, const void* w, float eps, void* x, int T, int H,
+                                    int centered, void* stream) {
+    return add_rmsnorm_launch(h, y, w, eps, x, nullptr, T, H, centered, stream);
+}
+
+extern "C" int btb_b200_add_rmsnorm_wide(void* h, const void* y, const void* w, float eps, void* x, void* xf, int T, int H,
+                                         int centered, void* stream) {
+    if (!xf) return B2_ERR_NULL;
+    return add_rmsnorm_launch(h, y, w, eps, x, xf, T, H, centered, stream);
 }
 
 extern "C" int btb_b200_silu_mul(const void* gu, void* m, int T, int I, void* stream) {

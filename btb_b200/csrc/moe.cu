@@ -51,16 +51,19 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
         return __uint_as_float((uint32_t)u << 16);
     };
     if (A.mode == 0) {
+        // the row's max (any order gives the same value)
         float m = NEG_INF;
         for (int e = tid; e < E; e += ROUTE_THREADS) m = fmaxf(m, logit(e));
-        red[tid] = m;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if ((tid & 31) == 0) red[tid >> 5] = m;
         __syncthreads();
-        for (int s = ROUTE_THREADS / 2; s > 0; s >>= 1) {
-            if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]);
-            __syncthreads();
-        }
         m = red[0];
+#pragma unroll
+        for (int w = 1; w < ROUTE_THREADS / 32; ++w) m = fmaxf(m, red[w]);
         __syncthreads();
+        // the sum: thread i's strided terms, then the reference's 256 -> 1 tree (red[t] += red[t + st], st = 128 .. 1)
+        // with the same pairs in the same order on one warp: lane l holds red[l + 32 k]
         float s = 0.f;
         for (int e = tid; e < E; e += ROUTE_THREADS) {
             const float p = expf(logit(e) - m);
@@ -69,10 +72,20 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
         }
         red[tid] = s;
         __syncthreads();
-        for (int st = ROUTE_THREADS / 2; st > 0; st >>= 1) {
-            if (tid < st) red[tid] += red[tid + st];
-            __syncthreads();
+        if (tid < 32) {
+            float v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = red[tid + 32 * q];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) v[q] += v[q + 4];
+            v[0] += v[2];
+            v[1] += v[3];
+            v[0] += v[1];
+#pragma unroll
+            for (int st = 16; st > 0; st >>= 1) v[0] += __shfl_down_sync(0xffffffffu, v[0], st);
+            if (tid == 0) red[0] = v[0];
         }
+        __syncthreads();
         s = red[0];
         __syncthreads();
         for (int e = tid; e < E; e += ROUTE_THREADS) pr[e] = pr[e] / s;
@@ -80,40 +93,65 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
         for (int e = tid; e < E; e += ROUTE_THREADS) pr[e] = logit(e);
     }
     __syncthreads();
-    // k rounds of the total order's maximum; a picked entry leaves the field (a flag array, so any value may be live)
+    // k rounds of the total order's maximum (value descending, index ascending); a picked entry leaves the field
     constexpr int NONE = 0x7fffffff;
-    for (int j = 0; j < k; ++j) {
-        float bv = 0.f;
-        int bi = NONE;
-        for (int e = tid; e < E; e += ROUTE_THREADS) {
-            bool taken = false;
-            for (int u = 0; u < j; ++u) taken |= topi[u] == e;
-            if (taken) continue;
-            const float v = pr[e];
-            if (bi == NONE || v > bv) {  // e ascends within the thread: a tie keeps the lower index
-                bv = v;
-                bi = e;
+    if (E <= 1024) {
+        // one warp, no block barriers: lane l owns entries l, l + 32, .. (a bit a taken entry)
+        if (tid < 32) {
+            unsigned taken = 0u;
+            for (int j = 0; j < k; ++j) {
+                float bv = 0.f;
+                int bi = NONE;
+                for (int e = tid, i = 0; e < E; e += 32, ++i) {
+                    if ((taken >> i) & 1u) continue;
+                    const float v = pr[e];
+                    if (bi == NONE || v > bv) bv = v, bi = e;  // e ascends: a tie keeps the lower index
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (oi != NONE && (bi == NONE || ov > bv || (ov == bv && oi < bi))) bv = ov, bi = oi;
+                }
+                if (bi != NONE && (bi & 31) == tid) taken |= 1u << (bi >> 5);
+                if (tid == 0) topv[j] = bv, topi[j] = bi;
             }
         }
-        red[tid] = bv;
-        redi[tid] = bi;
         __syncthreads();
-        for (int st = ROUTE_THREADS / 2; st > 0; st >>= 1) {
-            if (tid < st) {
-                const float ov = red[tid + st];
-                const int oi = redi[tid + st];
-                if (oi != NONE && (redi[tid] == NONE || ov > red[tid] || (ov == red[tid] && oi < redi[tid]))) {
-                    red[tid] = ov;
-                    redi[tid] = oi;
+    } else {
+        for (int j = 0; j < k; ++j) {
+            float bv = 0.f;
+            int bi = NONE;
+            for (int e = tid; e < E; e += ROUTE_THREADS) {
+                bool taken = false;
+                for (int u = 0; u < j; ++u) taken |= topi[u] == e;
+                if (taken) continue;
+                const float v = pr[e];
+                if (bi == NONE || v > bv) {  // e ascends within the thread: a tie keeps the lower index
+                    bv = v;
+                    bi = e;
                 }
+            }
+            red[tid] = bv;
+            redi[tid] = bi;
+            __syncthreads();
+            for (int st = ROUTE_THREADS / 2; st > 0; st >>= 1) {
+                if (tid < st) {
+                    const float ov = red[tid + st];
+                    const int oi = redi[tid + st];
+                    if (oi != NONE && (redi[tid] == NONE || ov > red[tid] || (ov == red[tid] && oi < redi[tid]))) {
+                        red[tid] = ov;
+                        redi[tid] = oi;
+                    }
+                }
+                __syncthreads();
+            }
+            if (tid == 0) {
+                topv[j] = red[0];
+                topi[j] = redi[0];
             }
             __syncthreads();
         }
-        if (tid == 0) {
-            topv[j] = red[0];
-            topi[j] = redi[0];
-        }
-        __syncthreads();
     }
     if (tid == 0) {
         if (A.mode == 0) {
@@ -301,13 +339,16 @@ __global__ void __launch_bounds__(256) moe_combine(const CombineArgs A) {
     pdl_wait();
     const int t = blockIdx.y, k = A.k;
     __shared__ int order[ROUTE_MAX_K];
+    __shared__ int eid[ROUTE_MAX_K];
+    if (threadIdx.x < k) eid[threadIdx.x] = __ldcg(A.idx + (size_t)t * k + threadIdx.x);  // one round trip for all
+    __syncthreads();
     if (threadIdx.x == 0) {  // the row's picks by ascending expert id (a handful: insertion sort)
         for (int a = 0; a < k; ++a) order[a] = a;
         for (int a = 1; a < k; ++a) {
             const int v = order[a];
-            const int ev = __ldcg(A.idx + (size_t)t * k + v);
+            const int ev = eid[v];
             int b = a - 1;
-            while (b >= 0 && __ldcg(A.idx + (size_t)t * k + order[b]) > ev) {
+            while (b >= 0 && eid[order[b]] > ev) {
                 order[b + 1] = order[b];
                 --b;
             }
@@ -397,7 +438,7 @@ extern "C" int btb_b200_gemv_lane16_fp8_f32(const void* w, const void* scales, i
 extern "C" int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride,
                                  int sr, int sc, const void* idx, int n_tasks, int E, const void* x, int x_div, void* y,
                                  int R, int C, int ep_rank, int ep_size, void* stream) {
-    if (!w || !idx || !x || !y || (fmt != L_BF16 && !scales)) return B2_ERR_NULL;
+    if (!w || !x || !y || (fmt != L_BF16 && !scales)) return B2_ERR_NULL;  // idx null: every task is matrix 0
     if (n_tasks <= 0 || R <= 0 || C <= 0 || x_div <= 0 || E <= 0 || ep_size < 1 || ep_rank < 0 || ep_rank >= ep_size)
         return B2_ERR_DOMAIN;
     if (fmt == L_MX4 && (C & 31)) return B2_ERR_DOMAIN;

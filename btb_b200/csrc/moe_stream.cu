@@ -19,7 +19,6 @@ B2_DEFINE_STATUS(moes)
 namespace {
 
 enum { S_BF16 = 0, S_MX4 = 1, S_FP8 = 2 };
-constexpr int RB = 8;       // rows a warp takes at a time
 constexpr int PAD = 16;     // bytes between the rows of a stage
 constexpr int MAXW = 16;    // warps a CTA at most
 
@@ -37,6 +36,20 @@ struct MSArgs {
     int stages;
 };
 
+// four e2m1 codes (the nibbles of `codes`, lowest first) as two bf16 pairs: p01 = (value 0 | value 1 << 16), p23 alike.
+// A value's bf16 pattern is two table bytes: the high byte out of eight by the code's low three bits, from the
+// positive or the negative table by its top bit, the low byte out of eight - byte permutes, no arithmetic.
+__device__ __forceinline__ void fp4x4_bf16(uint32_t codes, uint32_t& p01, uint32_t& p23) {
+    const uint32_t s7 = codes & 0x7777u;
+    const uint32_t pick = 0x3210u | ((codes & 0x8888u) >> 1);
+    const uint32_t hp = __byte_perm(0x3F3F3F00u, 0x40404040u, s7);  // 0, .5, 1, 1.5 | 2, 3, 4, 6: high bytes
+    const uint32_t hn = __byte_perm(0xBFBFBF80u, 0xC0C0C0C0u, s7);  // the same with the sign
+    const uint32_t hb = __byte_perm(hp, hn, pick);
+    const uint32_t lb = __byte_perm(0xC0800000u, 0xC0804000u, s7);  // low bytes
+    p01 = __byte_perm(lb, hb, 0x5140u);
+    p23 = __byte_perm(lb, hb, 0x7362u);
+}
+
 template <int FMT>
 __host__ __device__ constexpr int col_bytes2() { return FMT == S_BF16 ? 4 : FMT == S_FP8 ? 2 : 1; }  // twice a column's bytes
 
@@ -50,11 +63,13 @@ __device__ __forceinline__ float fp4_value_s(unsigned code) {
     return __uint_as_float((mag | ((code & 8u) << 12)) << 16);
 }
 
-template <int FMT>
-__global__ void __launch_bounds__(MAXW * 32, 1) moe_gemv_stream(const MSArgs A) {
+// TPR threads share a row, each running CPT = 16 / TPR adjacent chains; a warp takes RB = 32 / TPR rows at a time
+template <int FMT, int TPR>
+__global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(const MSArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int CPT = 16 / TPR, RB = 32 / TPR;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int ri = lane >> 2, q = lane & 3;  // the thread's row of the warp's eight, its four chains 4q .. 4q + 3
+    const int ri = lane / TPR, q = lane % TPR;  // the thread's row of the warp's RB, its chains q CPT .. q CPT + CPT - 1
     const int task = blockIdx.y;
     const int R = A.R, C = A.C, seg = A.seg, S = A.stages;
     constexpr int CB2 = col_bytes2<FMT>();
@@ -135,7 +150,9 @@ __global__ void __launch_bounds__(MAXW * 32, 1) moe_gemv_stream(const MSArgs A) 
     }
     __syncthreads();
 
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[CPT];
+#pragma unroll
+    for (int u = 0; u < CPT; ++u) acc[u] = 0.f;
     int c_grp = g0 + warp, c_seg = 0, c_st = 0;
     uint32_t c_par = 0;
     bool ok = true;
@@ -160,9 +177,10 @@ __global__ void __launch_bounds__(MAXW * 32, 1) moe_gemv_stream(const MSArgs A) 
             // a row's scale bytes of this stage (one a block of 32 columns): four a thread, shared by shuffle below
             const uint8_t* sr = A.scales + (size_t)e * A.s_stride + (size_t)(live ? r : 0) * (C >> 5) + (c0 >> 5);
             const int nb = n >> 5;
+            constexpr int SPT = TPR >= 16 ? 1 : 16 / TPR >= 4 ? 4 : 16 / TPR;  // scale bytes a thread fetches: 4, 2 or 1
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int b = q * 4 + u;
+            for (int u = 0; u < SPT; ++u) {
+                const int b = q * SPT + u;
                 mxs |= (b < nb ? (unsigned)__ldg(sr + b) : 127u) << (8 * u);
             }
         }
@@ -177,65 +195,108 @@ __global__ void __launch_bounds__(MAXW * 32, 1) moe_gemv_stream(const MSArgs A) 
             const int steps = n >> 4;
 #pragma unroll 4
             for (int s = 0; s < steps; ++s) {
-                const uint32_t wb = *reinterpret_cast<const uint32_t*>(srowp + s * 16 + q * 4);
-                const float4 xv = *reinterpret_cast<const float4*>(xp + s * 16 + q * 4);
                 // the block scale of these columns: the stage starts on a multiple of 128 columns when bn is 128
-                const float sc = (bn == 128 && (seg & 127) == 0) ? fsc[(s * 16) >> 7]
-                                                                 : __ldg(reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride) +
-                                                                         (size_t)((live ? r : 0) / (R / A.sr)) * A.sc + (c0 + s * 16) / bn);
-                const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb & 0xffffu), __NV_E4M3);
-                const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb >> 16), __NV_E4M3);
-                const float w0 = bfround(__fmul_rn(__half2float(__ushort_as_half(h01.x)), sc));
-                const float w1 = bfround(__fmul_rn(__half2float(__ushort_as_half(h01.y)), sc));
-                const float w2 = bfround(__fmul_rn(__half2float(__ushort_as_half(h23.x)), sc));
-                const float w3 = bfround(__fmul_rn(__half2float(__ushort_as_half(h23.y)), sc));
-                acc[0] = fmaf(w0, xv.x, acc[0]);
-                acc[1] = fmaf(w1, xv.y, acc[1]);
-                acc[2] = fmaf(w2, xv.z, acc[2]);
-                acc[3] = fmaf(w3, xv.w, acc[3]);
+                const float sc = (bn == 128 && (seg & 127) == 0 && seg <= 512)
+                                     ? fsc[(s * 16) >> 7]
+                                     : __ldg(reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride) +
+                                             (size_t)((live ? r : 0) / (R / A.sr)) * A.sc + (c0 + s * 16) / bn);
+                const uint8_t* wp = srowp + s * 16 + q * CPT;
+                const float* xq = xp + s * 16 + q * CPT;
+                if (CPT == 4) {
+                    const uint32_t wb = *reinterpret_cast<const uint32_t*>(wp);
+                    const float4 xv = *reinterpret_cast<const float4*>(xq);
+                    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb & 0xffffu), __NV_E4M3);
+                    const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb >> 16), __NV_E4M3);
+                    acc[0] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.x)), sc)), xv.x, acc[0]);
+                    acc[1 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.y)), sc)), xv.y, acc[1 % CPT]);
+                    acc[2 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h23.x)), sc)), xv.z, acc[2 % CPT]);
+                    acc[3 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h23.y)), sc)), xv.w, acc[3 % CPT]);
+                } else if (CPT == 2) {
+                    const uint32_t wb = *reinterpret_cast<const unsigned short*>(wp);
+                    const float2 xv = *reinterpret_cast<const float2*>(xq);
+                    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)wb, __NV_E4M3);
+                    acc[0] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.x)), sc)), xv.x, acc[0]);
+                    acc[1 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.y)), sc)), xv.y, acc[1 % CPT]);
+                } else {
+                    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)*wp, __NV_E4M3);
+                    acc[0] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.x)), sc)), *xq, acc[0]);
+                }
             }
         } else if (FMT == S_MX4) {
             const int nb = n >> 5;
+            constexpr int SPT = TPR >= 16 ? 1 : 16 / TPR >= 4 ? 4 : 16 / TPR;
 #pragma unroll 4
             for (int b = 0; b < nb; ++b) {
-                const unsigned pk = __shfl_sync(0xffffffffu, mxs, (lane & ~3) | (b >> 2));
-                const float sc = mx4_scale_s((pk >> ((b & 3) * 8)) & 255u);
+                const unsigned pk = __shfl_sync(0xffffffffu, mxs, (lane / TPR) * TPR + b / SPT);
+                const float sc = mx4_scale_s((pk >> ((b % SPT) * 8)) & 255u);
                 // the block's 16 bytes: byte i holds columns 2i (low nibble) and 2i + 1 of its first 16 columns,
                 // byte 8 + i the same of its last 16
-                const unsigned lo = *reinterpret_cast<const unsigned short*>(srowp + b * 16 + q * 2);
-                const unsigned hi = *reinterpret_cast<const unsigned short*>(srowp + b * 16 + 8 + q * 2);
-                const float4 xa = *reinterpret_cast<const float4*>(xp + b * 32 + q * 4);
-                const float4 xb = *reinterpret_cast<const float4*>(xp + b * 32 + 16 + q * 4);
-                acc[0] = fmaf(__fmul_rn(fp4_value_s(lo & 15u), sc), xa.x, acc[0]);
-                acc[1] = fmaf(__fmul_rn(fp4_value_s((lo >> 4) & 15u), sc), xa.y, acc[1]);
-                acc[2] = fmaf(__fmul_rn(fp4_value_s((lo >> 8) & 15u), sc), xa.z, acc[2]);
-                acc[3] = fmaf(__fmul_rn(fp4_value_s((lo >> 12) & 15u), sc), xa.w, acc[3]);
-                acc[0] = fmaf(__fmul_rn(fp4_value_s(hi & 15u), sc), xb.x, acc[0]);
-                acc[1] = fmaf(__fmul_rn(fp4_value_s((hi >> 4) & 15u), sc), xb.y, acc[1]);
-                acc[2] = fmaf(__fmul_rn(fp4_value_s((hi >> 8) & 15u), sc), xb.z, acc[2]);
-                acc[3] = fmaf(__fmul_rn(fp4_value_s((hi >> 12) & 15u), sc), xb.w, acc[3]);
+                const uint8_t* bp = srowp + b * 16;
+                const float* xa = xp + b * 32 + q * CPT;
+                const float* xb = xa + 16;
+                if (CPT == 4) {
+                    const unsigned lo = *reinterpret_cast<const unsigned short*>(bp + q * 2);
+                    const unsigned hi = *reinterpret_cast<const unsigned short*>(bp + 8 + q * 2);
+                    const float4 va = *reinterpret_cast<const float4*>(xa), vb = *reinterpret_cast<const float4*>(xb);
+                    uint32_t a01, a23, b01, b23;
+                    fp4x4_bf16(lo, a01, a23);
+                    fp4x4_bf16(hi, b01, b23);
+                    acc[0] = fmaf(__fmul_rn(bf_lo(a01), sc), va.x, acc[0]);
+                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(a01), sc), va.y, acc[1 % CPT]);
+                    acc[2 % CPT] = fmaf(__fmul_rn(bf_lo(a23), sc), va.z, acc[2 % CPT]);
+                    acc[3 % CPT] = fmaf(__fmul_rn(bf_hi(a23), sc), va.w, acc[3 % CPT]);
+                    acc[0] = fmaf(__fmul_rn(bf_lo(b01), sc), vb.x, acc[0]);
+                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(b01), sc), vb.y, acc[1 % CPT]);
+                    acc[2 % CPT] = fmaf(__fmul_rn(bf_lo(b23), sc), vb.z, acc[2 % CPT]);
+                    acc[3 % CPT] = fmaf(__fmul_rn(bf_hi(b23), sc), vb.w, acc[3 % CPT]);
+                } else if (CPT == 2) {
+                    const unsigned codes = (unsigned)bp[q] | ((unsigned)bp[8 + q] << 8);
+                    const float2 va = *reinterpret_cast<const float2*>(xa), vb = *reinterpret_cast<const float2*>(xb);
+                    uint32_t a01, b01;
+                    fp4x4_bf16(codes, a01, b01);  // the first half's two columns, then the second half's
+                    acc[0] = fmaf(__fmul_rn(bf_lo(a01), sc), va.x, acc[0]);
+                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(a01), sc), va.y, acc[1 % CPT]);
+                    acc[0] = fmaf(__fmul_rn(bf_lo(b01), sc), vb.x, acc[0]);
+                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(b01), sc), vb.y, acc[1 % CPT]);
+                } else {
+                    const int sh = (q & 1) << 2;
+                    acc[0] = fmaf(__fmul_rn(fp4_value_s((bp[q >> 1] >> sh) & 15u), sc), *xa, acc[0]);
+                    acc[0] = fmaf(__fmul_rn(fp4_value_s((bp[8 + (q >> 1)] >> sh) & 15u), sc), *xb, acc[0]);
+                }
             }
         } else {
             const int steps = n >> 4;
 #pragma unroll 4
             for (int s = 0; s < steps; ++s) {
-                const uint2 wb = *reinterpret_cast<const uint2*>(srowp + s * 32 + q * 8);
-                const float4 xv = *reinterpret_cast<const float4*>(xp + s * 16 + q * 4);
-                acc[0] = fmaf(bf_lo(wb.x), xv.x, acc[0]);
-                acc[1] = fmaf(bf_hi(wb.x), xv.y, acc[1]);
-                acc[2] = fmaf(bf_lo(wb.y), xv.z, acc[2]);
-                acc[3] = fmaf(bf_hi(wb.y), xv.w, acc[3]);
+                const uint8_t* wp = srowp + s * 32 + q * CPT * 2;
+                const float* xq = xp + s * 16 + q * CPT;
+                if (CPT == 4) {
+                    const uint2 wb = *reinterpret_cast<const uint2*>(wp);
+                    const float4 xv = *reinterpret_cast<const float4*>(xq);
+                    acc[0] = fmaf(bf_lo(wb.x), xv.x, acc[0]);
+                    acc[1 % CPT] = fmaf(bf_hi(wb.x), xv.y, acc[1 % CPT]);
+                    acc[2 % CPT] = fmaf(bf_lo(wb.y), xv.z, acc[2 % CPT]);
+                    acc[3 % CPT] = fmaf(bf_hi(wb.y), xv.w, acc[3 % CPT]);
+                } else if (CPT == 2) {
+                    const uint32_t wb = *reinterpret_cast<const uint32_t*>(wp);
+                    const float2 xv = *reinterpret_cast<const float2*>(xq);
+                    acc[0] = fmaf(bf_lo(wb), xv.x, acc[0]);
+                    acc[1 % CPT] = fmaf(bf_hi(wb), xv.y, acc[1 % CPT]);
+                } else {
+                    acc[0] = fmaf(__uint_as_float((uint32_t)*reinterpret_cast<const unsigned short*>(wp) << 16), *xq, acc[0]);
+                }
             }
         }
         __syncwarp();
         if (issued < n_items) issue_next();
         if (c_seg == nseg - 1) {
             // reduce16's pairwise fold: chains 1 apart, 2 apart (both in this thread), 4 and 8 apart (the row's threads)
-            float s = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            float s = CPT == 4 ? (acc[0] + acc[1 % CPT]) + (acc[2 % CPT] + acc[3 % CPT]) : CPT == 2 ? acc[0] + acc[1 % CPT] : acc[0];
+#pragma unroll
+            for (int o = 1; o < TPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             if (live && q == 0) A.y[(size_t)task * R + r] = s;
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll
+            for (int u = 0; u < CPT; ++u) acc[u] = 0.f;
             c_seg = 0;
             c_grp += nw;
         } else {
@@ -263,11 +324,13 @@ struct MSPlan {
     int ctas, warps, seg, stages, smem;
 };
 
-template <int FMT>
+template <int FMT, int TPR>
 bool plan_stream(int n_tasks, int R, int C, MSPlan& p) {
+    constexpr int RB = 32 / TPR;
+    const int per_sm = TPR == 4 ? 1 : 2;  // CTAs an SM holds
     const int sms = b2_sm_count();
     const int groups = (R + RB - 1) / RB;
-    p.ctas = max(1, min(groups, sms / max(1, n_tasks)));  // CTAs that share a task
+    p.ctas = max(1, min(groups, per_sm * sms / max(1, n_tasks)));  // CTAs that share a task
     const int per_cta = (groups + p.ctas - 1) / p.ctas;
     p.warps = max(4, min(MAXW, per_cta));
     // even the rows out: with per_cta groups over the warps, fewer warps may idle less (the last round is fuller)
@@ -276,28 +339,43 @@ bool plan_stream(int n_tasks, int R, int C, MSPlan& p) {
         p.warps = max(4, (per_cta + rounds - 1) / rounds);
     }
     const int xbytes = (C * 4 + 127) & ~127;
-    const int budget = 200 * 1024 - xbytes;
-    for (p.seg = min(512, (C + 31) & ~31);; p.seg = max(32, (p.seg / 2) & ~31)) {
+    const int budget = (per_sm == 1 ? 200 : 104) * 1024 - xbytes;
+    const B2Tuning& t = b2_tuning();
+    if (t.ms_warps > 0) p.warps = min(MAXW, t.ms_warps);
+    // (an MXFP4 stage holds at most 16 blocks of a row: the scale bytes its threads fetch ahead)
+    for (p.seg = min(t.ms_seg > 0 && (FMT != S_MX4 || t.ms_seg <= 512) ? t.ms_seg : 512, (C + 31) & ~31);; p.seg = max(32, (p.seg / 2) & ~31)) {
         const int stride = p.seg * col_bytes2<FMT>() / 2 + PAD;
         const int sbytes = RB * stride;
         p.stages = max(2, min(6, budget / (p.warps * (sbytes + 8))));
         p.smem = xbytes + p.warps * p.stages * (sbytes + 8);
-        if (p.smem <= 220 * 1024 || p.seg == 32) break;  // two stages must fit: a narrower segment
+        if (p.smem <= (per_sm == 1 ? 220 : 110) * 1024 || p.seg == 32) break;  // two stages must fit: a narrower segment
     }
-    return p.smem <= 220 * 1024;
+    return p.smem <= (per_sm == 1 ? 220 : 110) * 1024;
 }
 
-template <int FMT>
-int launch_stream(const MSArgs& a0, int n_tasks, cudaStream_t s) {
+template <int FMT, int TPR>
+int launch_stream_t(const MSArgs& a0, int n_tasks, cudaStream_t s) {
     MSPlan p;
     MSArgs a = a0;
-    if (!plan_stream<FMT>(n_tasks, a.R, a.C, p)) return B2_ERR_DOMAIN;
+    if (!plan_stream<FMT, TPR>(n_tasks, a.R, a.C, p)) return B2_ERR_DOMAIN;
     a.seg = p.seg, a.stages = p.stages;
-    auto kern = moe_gemv_stream<FMT>;
+    auto kern = moe_gemv_stream<FMT, TPR>;
     static bool allowed[64];
     int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
     if (rc) return rc;
     return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.ctas, n_tasks), dim3(p.warps * 32), p.smem, s, a, 2);
+}
+
+template <int FMT>
+int launch_stream(const MSArgs& a, int n_tasks, cudaStream_t s) {
+    // threads a row: four measured best for every format (the conversion units bound the kernel, not latency)
+    int tpr = b2_tuning().ms_tpr;
+    if (tpr != 4 && tpr != 8 && tpr != 16) tpr = 4;
+    switch (tpr) {
+        case 4: return launch_stream_t<FMT, 4>(a, n_tasks, s);
+        case 16: return launch_stream_t<FMT, 16>(a, n_tasks, s);
+        default: return launch_stream_t<FMT, 8>(a, n_tasks, s);
+    }
 }
 
 }  // namespace

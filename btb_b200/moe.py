@@ -206,10 +206,11 @@ class MoEEngine(CardEngine):
             self._matvec(L.qkv, g["x"], g["qkv"], M, c.qkv_rows, H, s)
             self._attention(g, i, L.wq, L.wk, T, s)
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
-            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
-            # the MoE block: x.float(), the router's logits by the host-order GEMV, the picks, the experts, the sum
-            K_("btb_b200_widen_f32", ptr(g["x"]), ptr(g["xf"]), T * H, s)
-            K_("btb_b200_gemv_lane16_f32", ptr(L.router), ptr(g["xf"]), ptr(g["rl"]), T, E, H, s)
+            # the MoE block: x.float() (made by the norm's own launch), the router's logits by the host-order GEMV,
+            # the picks, the experts, the sum
+            K_("btb_b200_add_rmsnorm_wide", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), ptr(g["xf"]), T, H, 0,
+               s)  # fmt: skip
+            K_("btb_b200_moe_gemv", 0, ptr(L.router), 0, 0, 0, 1, 1, 0, T, 1, ptr(g["xf"]), 1, ptr(g["rl"]), E, H, 0, 1, s)
             K_("btb_b200_moe_route", ptr(g["rl"]), E, E, k, c.router_mode, 1, ptr(g["idx"]), ptr(g["rw"]), T, s)
             self._expert_gemv(L.gu, g["idx"], T * k, g["xf"], k, g["egu"], s)
             K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)

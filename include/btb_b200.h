@@ -91,6 +91,10 @@ int btb_b200_embed(const void* table, const void* ids, void* h, int T, int H, in
 /* btb_add_rmsnorm (btb_kernels.cu:365-393): h += y (y may be null), x = bf16(h * rstd * w) or * (1 + w). */
 int btb_b200_add_rmsnorm(void* h, const void* y, const void* w, float eps, void* x, int T, int H, int centered,
                          void* stream);
+/* the same, and xf f32 [T, H] = x widened (the value the MoE block's router and experts read,
+ * btb/engine/host.py:180-186): one launch for the norm and the widen */
+int btb_b200_add_rmsnorm_wide(void* h, const void* y, const void* w, float eps, void* x, void* xf, int T, int H,
+                              int centered, void* stream);
 /* btb_silu_mul (btb_kernels.cu:481-484): m[T,I] = bf16(bf16(silu(g)) * u) over gu [T,2I]. */
 int btb_b200_silu_mul(const void* gu, void* m, int T, int I, void* stream);
 /* btb_norm_rope_kv{,_tbl}_d{64,128,256} (btb_kernels.cu:261-358): q/k RMSNorm (null weights: none), RoPE from bf16

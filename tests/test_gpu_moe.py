@@ -35,7 +35,7 @@ def clean_status():
     assert capi.status() == 0
 
 
-@pytest.mark.parametrize("E,k,mode", [(32, 4, 1), (128, 8, 0), (8, 2, 0), (300, 5, 1)])
+@pytest.mark.parametrize("E,k,mode", [(32, 4, 1), (128, 8, 0), (8, 2, 0), (300, 5, 1), (1024, 8, 0), (2048, 6, 0), (1500, 3, 1)])
 @pytest.mark.parametrize("f32", [True, False])
 def test_router(E, k, mode, f32):
     rng = np.random.default_rng(E + k)
