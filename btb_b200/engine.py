@@ -306,21 +306,23 @@ class CardEngine:
         if hcur is not g["h"]:  # an odd number of folded adds (a pass without its tail): bring the residual home
             g["h"].copy_(hcur)
 
-    def _attention(self, g: dict, i: int, wq: Any, wk: Any, T: int, s: int, win: int = 0, sinks: Any = None) -> None:
+    def _attention(self, g: dict, i: int, wq: Any, wk: Any, T: int, s: int, win: int = 0, sinks: Any = None,
+                   out: Any = None) -> None:
         """q/k-norm + RoPE + cache write, then the attention over the cache: one fused launch for the step's single
         row, the two kernels for a pass of several rows (the same bits either way)"""
         c = self.cfg
         Hq, Hk, D = c.q_heads, c.kv_heads, c.head_dim
+        out = g["att"] if out is None else out
         if T == 1 and self.fuse_attn and D in (64, 128):
             self._k("btb_b200_attn_step", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
-                    ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), ptr(g["att"]), Hq, Hk,
+                    ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), ptr(out), Hq, Hk,
                     D, self.hs, self.rs, 0, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]), ptr(g["part_acc"]),
                     ptr(g["cnt"]), win, 0, ptr(sinks), self.cap, s)  # fmt: skip
             return
         self._k("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
                 ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
                 self.rs, 0, 0, self.cap, s)  # fmt: skip
-        self._k("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["att"]), ptr(self.n0),
+        self._k("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(out), ptr(self.n0),
                 ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
                 ptr(g["part_acc"]), ptr(g["cnt"]), win, 0, ptr(sinks), self.cap, s)  # fmt: skip
 

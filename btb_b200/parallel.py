@@ -125,18 +125,12 @@ class TPEngine(CardEngine):
         g, t = self.bufs(M), self.tp_bufs(M)
         s = capi.stream_ptr() if stream_ptr is None else stream_ptr
         H, D, I = c.hidden, c.head_dim, c.inter
-        Hq, Hk = lc.q_heads, lc.kv_heads  # this rank's heads
         K_ = self._k
         y_prev = None
         for i, L in enumerate(self.w.layers):
             K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(g["x"]), T, H, 0, s)
             self._matvec(L.qkv, g["x"], g["qkv"], M, lc.qkv_rows, H, s)
-            K_("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
-               ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
-               self.rs, 0, 0, self.cap, s)  # fmt: skip
-            K_("btb_b200_attn_decode", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(t["att_l"]), ptr(self.n0),
-               ptr(g["par"]), T, Hq, Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]),
-               ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
+            self._attention(g, i, L.wq, L.wk, T, s, out=t["att_l"])  # this rank's heads
             self._gather(t["att_l"], t["att_g"], t["att"])
             self._matvec(L.o, t["att"], t["y_l"], M, H // w, c.q_heads * D, s)
             self._gather(t["y_l"], t["y_g"], t["y"])
