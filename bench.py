@@ -271,6 +271,9 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         cfg = E.QWEN3_4B if not args.layers else dataclasses.replace(E.QWEN3_4B, layers=args.layers)
         storage = "p12" if args.workload.endswith("p12") else "bf16"
         mw = E.synth_weights(cfg, seed=0, storage=storage)
+        if args.batch > 1:
+            run_batch(args, mw, cfg, storage, cap, rank, world, dist)
+            return
         eng = E.CardEngine(mw, cap=cap, step_kernel=bool(args.step_kernel))
     elif args.workload in ("gpt-oss-20b", "qwen3-30b-a3b"):
         from btb_b200 import moe as MO
@@ -518,6 +521,68 @@ def run_case(args) -> None:
     print(json.dumps(out), flush=True)
 
 
+def run_batch(args, mw, cfg, storage, cap, rank, world, dist) -> None:
+    """small-batch decode: --batch sequences with independent seeded prompts decoded side by side, a pass of B rows a
+    step (every weight streamed once for all of them)"""
+    import torch
+
+    from btb_b200 import capi
+    from btb_b200.batch import BatchEngine
+
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    eng = BatchEngine(mw, B, cap=cap)
+    prompts = [torch.randint(0, cfg.vocab, (PROMPT,), generator=torch.Generator().manual_seed(100 + b)) for b in range(B)]
+    eng.prefill_all(prompts)
+    graph = eng.batch_graph()
+    for _ in range(W):
+        graph.replay()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with Clocks(int(os.environ.get("LOCAL_RANK", "0"))) as clk:
+        e0.record()
+        for _ in range(K):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    t0 = time.perf_counter()
+    for _ in range(K):  # the public loop: every step's B tokens read back before the next
+        graph.replay()
+        torch.cuda.current_stream().synchronize()
+        _ = eng.pin_toks.tolist()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([ms, e2e_s * 1000.0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0]), float(t[1]) / 1000.0
+    assert capi.status() == 0, "a kernel recorded a device-side refusal"
+    peak, _ = measured_hbm_peak()
+    tps = world * B * K / (ms / 1000.0)
+    line = {
+        "metric": f"decode tok/s @bs{B} ({cfg.name} shape" + (", pack12 weights)" if storage == "p12" else ")"),
+        "value": tps, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if storage == "bf16" else f"bf16 ({STORED.get(storage, storage)} weights widened in registers)",
+        "data": "synthetic",
+        "config": {"workload": f"{cfg.name}-shape {storage}, batch {B} (independent seeded prompts of {PROMPT} tokens), "
+                   "greedy decode", "parallelism": "replicas only" if world > 1 else "1 gpu", "batch": B,
+                   "l2": "weights per step > L2 126 MB", "bytes_per_step": cfg.weight_bytes_per_token(storage)},
+        "clocks": clk.summary(),
+        "e2e": {"value": world * B * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8 * B},
+        "gpu_launches": eng.launches_per_step * K, "roofline": None,
+        "step_roofline_frac": (cfg.weight_bytes_per_token(storage) * K / (ms / 1000.0) / 1e9) / peak,
+    }  # fmt: skip
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def run_speculative(args, eng, cfg, storage, parallelism, rank, world, dist) -> None:
     """greedy decode with an n-gram tree of `--speculative` drafts verified a pass: the prompt is a seeded 64-token
     pattern repeated to 512 tokens so that the n-grams have something to propose"""
@@ -590,6 +655,7 @@ def main() -> None:
     ap.add_argument("--pdl", type=int, default=None)
     ap.add_argument("--cpu-steps", type=int, default=4)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--batch", type=int, default=1, help="qwen3-4b workloads: sequences decoded side by side")
     ap.add_argument("--case", default="", help="one kernel on a small case: gemv:RxC[:M[:fmt]] or attn:N")
     ap.add_argument("--speculative", type=int, default=0, help="verify an n-gram tree of this many drafts a pass")
     args = ap.parse_args()

@@ -44,11 +44,31 @@ constexpr int SPLIT_ROWS = 4096;
 struct StepAttnArgs {
     AttnArgs a;
     RopeArgs r;
+    int B;                   // sequences decoded side by side (row b of the pass belongs to sequence b), 1 for a step
+    long long seq_stride;    // elements from a sequence's cache to the next one's
 };
 template <int D, int G>
 __global__ void __launch_bounds__(NWA * 32) attn_step(const StepAttnArgs A) {
     extern __shared__ __align__(16) uint8_t dsm_raw[];
     pdl_wait();  // the trigger for the next kernel is inside, after the values are read
+    if (A.B > 1) {
+        // sequence b's row: its slice of qkv, its own cache, length, partials and counters
+        const int b = blockIdx.y / A.a.Hk, g = blockIdx.y - b * A.a.Hk;
+        AttnArgs a = A.a;
+        RopeArgs r = A.r;
+        const int Hq = a.Hq, Hk = a.Hk;
+        const size_t S = gridDim.x;
+        r.qkv += (size_t)b * (Hq + 2 * Hk) * D, r.n0p += b, r.depth += b, r.K += (size_t)b * A.seq_stride;
+        r.V += (size_t)b * A.seq_stride, r.qo += (size_t)b * Hq * D;
+        a.q = r.qo, a.K = r.K, a.V = r.V, a.out += (size_t)b * Hq * D, a.n0p = r.n0p;
+        a.part_m += (size_t)b * S * Hq, a.part_l += (size_t)b * S * Hq, a.part_acc += (size_t)b * S * Hq * D, a.cnt += (size_t)b * Hq;
+        if (G > 1 && *a.n0p < SPLIT_ROWS) {
+            attn_step_item<D, 1, G>(a, r, blockIdx.x, g, blockIdx.z, dsm_raw);
+        } else if (blockIdx.z == 0) {
+            attn_step_item<D, G, G>(a, r, blockIdx.x, g, 0, dsm_raw);
+        }
+        return;
+    }
     // Below this many cached rows the group's heads take a block each (grid z); above, block z = 0 takes them all -
     // a long cache has blocks enough, and each key row is then read once.
     if (G > 1 && *A.a.n0p < SPLIT_ROWS) {
@@ -120,11 +140,11 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
     }
 }
 
-extern "C" int btb_b200_attn_step(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
-                                  const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
-                                  void* out, int Hq, int Hk, int D, long long hs, long long rs, int centered,
-                                  float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
-                                  const void* tbl, const void* sinks, int cap, void* stream) {
+static int attn_step_launch(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                            const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, void* out,
+                            int Hq, int Hk, int D, long long hs, long long rs, int centered, float scale, void* part_m,
+                            void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
+                            int B, long long seq_stride, void* stream) {
     if (!qkv || !cos_t || !sin_t || !n0p || !depth || !K || !V || !q || !out || !part_m || !part_l || !part_acc || !cnt)
         return B2_ERR_NULL;
     if (Hk <= 0 || Hq <= 0 || Hq % Hk || (Hq / Hk != 1 && Hq / Hk != 2 && Hq / Hk != 4 && Hq / Hk != 8) || cap <= 0 ||
@@ -149,11 +169,31 @@ extern "C" int btb_b200_attn_step(const void* qkv, const void* wq, const void* w
                     static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),
                     static_cast<bf16*>(V), static_cast<bf16*>(q), eps, 1, Hq, Hk, centered, hs, rs, cap};
     const int S = (cap + GK - 1) / GK;
-    const dim3 grid(S, Hk, Hq / Hk);
+    sa.B = B, sa.seq_stride = seq_stride;
+    const dim3 grid(S, Hk * B, Hq / Hk);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (D) {
         case 64: return launch_attn_step_g<64>(Hq / Hk, sa, grid, s);
         case 128: return launch_attn_step_g<128>(Hq / Hk, sa, grid, s);
         default: return B2_ERR_DOMAIN;
     }
+}
+
+extern "C" int btb_b200_attn_step(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                  const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
+                                  void* out, int Hq, int Hk, int D, long long hs, long long rs, int centered,
+                                  float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
+                                  const void* tbl, const void* sinks, int cap, void* stream) {
+    return attn_step_launch(qkv, wq, wk, eps, cos_t, sin_t, n0p, depth, K, V, q, out, Hq, Hk, D, hs, rs, centered, scale,
+                            part_m, part_l, part_acc, cnt, win, tbl, sinks, cap, 1, 0, stream);
+}
+
+extern "C" int btb_b200_attn_step_batch(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                        const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
+                                        void* out, int B, long long seq_stride, int Hq, int Hk, int D, long long hs,
+                                        long long rs, int centered, float scale, void* part_m, void* part_l,
+                                        void* part_acc, void* cnt, int win, const void* sinks, int cap, void* stream) {
+    if (B <= 0 || B > 32 || (long long)Hk * B > 65535 || seq_stride <= 0 || (seq_stride & 7)) return B2_ERR_DOMAIN;
+    return attn_step_launch(qkv, wq, wk, eps, cos_t, sin_t, n0p, depth, K, V, q, out, Hq, Hk, D, hs, rs, centered, scale,
+                            part_m, part_l, part_acc, cnt, win, nullptr, sinks, cap, B, seq_stride, stream);
 }

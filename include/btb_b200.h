@@ -123,6 +123,16 @@ int btb_b200_attn_step(const void* qkv, const void* wq, const void* wk, float ep
                        int Hq, int Hk, int D, long long hs, long long rs, int centered, float scale, void* part_m,
                        void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
                        void* stream);
+/* the same for B sequences decoded side by side (btb's batched greedy loop, btb/engine/generate.py:985-1046, over a
+ * cache of B rows each at its own length, btb/engine/cache.py:334-337: the GEMVs run one pass of B rows, row b is
+ * sequence b's token): qkv [B, (Hq+2Hk) D], n0p i32 [B] and depth i32 [B] (each sequence's length and 0), K / V
+ * sequence 0's cache with `seq_stride` elements to the next sequence's, q [B, Hq, D], out [B, Hq D], partials
+ * [B, S, Hq(, D)], cnt i32 [B, Hq]. Row b's bits are the one-sequence call's. */
+int btb_b200_attn_step_batch(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                             const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, void* out,
+                             int B, long long seq_stride, int Hq, int Hk, int D, long long hs, long long rs,
+                             int centered, float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
+                             const void* sinks, int cap, void* stream);
 size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D);
 /* the greedy pick: lowest-index argmax of each bf16 logits row (torch.argmax in btb/engine/cuda.py:2237; tie rule
  * native/src/sample.rs:57-67). scratch: btb_b200_argmax_scratch_bytes(T) bytes, 8-byte aligned, zeroed once.
