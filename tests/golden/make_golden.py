@@ -1,6 +1,6 @@
 """Generates the golden fixtures of this folder from the reference checkout.
 
-Run once where the reference is mounted (``python tests/golden/make_golden.py /root/reference``); the outputs are
+Run once where the reference is mounted (``python tests/golden/make_golden.py <reference checkout>``); the outputs are
 committed and the tests read only them. Everything here is produced by IMPORTING the reference's own Python codecs
 (``btb.pack12``, ``btb.mxfp4``, ``btb.fp8``, ``btb.sampling``, ``btb.draft``) or by reading its banked test
 fixtures (``tests/fixtures/tiny_qwen3*``, ``tests/fixtures/receipts_qwen3.pt``), never by re-deriving a value.
