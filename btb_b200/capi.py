@@ -64,6 +64,10 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
         _I, [_P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _LL, _I, _I, _I, _LL, _LL, _I, _F, _P, _P, _P, _P, _I,
              _P, _I, _P],
     ),
+    "btb_b200_attn_o_step": (
+        _I, [_P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _LL, _LL, _I, _F, _P, _P, _P, _P, _I, _P, _I,
+             _P, _P, _I, _P, _P],
+    ),
     "btb_b200_attn_scratch_floats": (_SZ, [_I, _I, _I, _I]),
     "btb_b200_argmax_bf16": (_I, [_P, _I, _I, _P, _P, _P]),
     "btb_b200_argmax_scratch_bytes": (_SZ, [_I]),

@@ -378,7 +378,7 @@ __device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, in
 // G == 1: head z of the group - a short cache leaves most of the card idle and the per-key arithmetic is what takes
 // the time, so the group's heads spread over GQ blocks (each reads the kv head's rows: they are few). Only block z = 0
 // writes the cache.
-template <int D, int G, int GQ>
+template <int D, int G, int GQ, bool TRIGGER = true>
 __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs& RA, int grp, int g, int z,
                                                uint8_t* dsm_raw) {
     const int hbase = g * GQ + z;
@@ -537,6 +537,6 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
     __syncthreads();
     // The next kernel's blocks may come in now, not earlier: a GEMV's blocks open with a burst of weight copies into
     // every SM, and a key or value row of this block queued behind that burst arrives microseconds late.
-    pdl_launch_dependents();
+    if (TRIGGER) pdl_launch_dependents();
     attn_finish<D, G>(A, sm, grp, hbase, G == GQ ? g : hbase, 0, first, last, &s_last_block);
 }

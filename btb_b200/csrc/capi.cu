@@ -63,11 +63,12 @@ int b2_status_take_step(int*);
 int b2_status_take_moe(int*);
 int b2_status_take_sample(int*);
 int b2_status_take_moes(int*);
+int b2_status_take_attno(int*);
 
 extern "C" int btb_b200_status(int* code) {
     if (code == nullptr) return B2_ERR_NULL;
     int (*const take[])(int*) = {b2_status_take_gemv, b2_status_take_layer, b2_status_take_attn, b2_status_take_step,
-                                 b2_status_take_moe, b2_status_take_sample, b2_status_take_moes};
+                                 b2_status_take_moe, b2_status_take_sample, b2_status_take_moes, b2_status_take_attno};
     *code = 0;
     for (auto f : take) {
         int v = 0;

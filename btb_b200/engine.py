@@ -13,6 +13,8 @@ raises at construction.
 
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass, field
 from typing import Any
@@ -193,6 +195,9 @@ class CardEngine:
         self.silu_fold = silu_fold
         self.fuse_norm = fuse_norm
         self.swiglu_epilogue = True  # SwiGLU in the gate/up GEMV's epilogue (passes of up to 8 rows)
+        # ... and the output projection in the same (cooperative) launch
+        self.fuse_attn_o = os.environ.get("BTB_B200_FUSE_ATTN_O", "0") == "1"
+        self._bar = torch.zeros(2, dtype=torch.int32, device=self.dev)
         self.fuse_attn = True  # the step's row: norm + RoPE + cache write + attention as one launch
         # the whole step as one persistent kernel (head dim 128 only); else one launch a kernel
         self.step_kernel = bool(step_kernel) and weights.cfg.head_dim == 128 and weights.cfg.q_heads // weights.cfg.kv_heads in (2, 4, 8)
@@ -281,8 +286,15 @@ class CardEngine:
         y_prev = None
         for i, L in enumerate(self.w.layers):
             normed_matvec(L.qkv, L.ln1, y_prev, g["qkv"], c.qkv_rows)
-            self._attention(g, i, L.wq, L.wk, T, s)
-            self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
+            if T == 1 and self.fuse_attn_o and self.fuse_attn and D in (64, 128) and isinstance(L.o, torch.Tensor):
+                # the step's attention row and its output projection in one cooperative launch
+                k("btb_b200_attn_o_step", ptr(g["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
+                  ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), ptr(g["att"]), Hq, Hk, D,
+                  self.hs, self.rs, 0, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]), ptr(g["part_acc"]),
+                  ptr(g["cnt"]), 0, 0, self.cap, ptr(L.o), ptr(g["y"]), H, ptr(self._bar), s)  # fmt: skip
+            else:
+                self._attention(g, i, L.wq, L.wk, T, s)
+                self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             if fuse and self.swiglu_epilogue and not isinstance(L.gu, FP8Matrix):
                 # the gate/up GEMV activates each pair itself: g["gu"] is never written, the down GEMV reads g["m"]
                 normed_matvec(L.gu, L.ln2, g["y"], g["m"], 2 * I, swiglu=True)

@@ -133,6 +133,17 @@ int btb_b200_attn_step_batch(const void* qkv, const void* wq, const void* wk, fl
                              int B, long long seq_stride, int Hq, int Hk, int D, long long hs, long long rs,
                              int centered, float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
                              const void* sinks, int cap, void* stream);
+/* btb_b200_attn_step and the output projection that reads its row (btb_gemv_bf16_m1 over o_proj, btb_kernels.cu:89-155)
+ * as one cooperative launch: every CTA fills its ring with its rows of w_o [R, Hq D] first, the grid's CTAs share out
+ * the attention's blocks, meet at one bounded grid barrier and multiply. att [1, Hq D] is still written; y [1, R] bf16.
+ * bar: u32 [2] on the card, zero before the first launch, used by no other stream at the same time. The bits are the
+ * two launches' bits. No row map. The device must hold the whole grid at once (one CTA an SM): the launch is refused
+ * (ERR_CUDA) where it cannot. */
+int btb_b200_attn_o_step(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                         const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, void* att,
+                         int Hq, int Hk, int D, long long hs, long long rs, int centered, float scale, void* part_m,
+                         void* part_l, void* part_acc, void* cnt, int win, const void* sinks, int cap, const void* w_o,
+                         void* y, int R, void* bar, void* stream);
 size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D);
 /* the greedy pick: lowest-index argmax of each bf16 logits row (torch.argmax in btb/engine/cuda.py:2237; tie rule
  * native/src/sample.rs:57-67). scratch: btb_b200_argmax_scratch_bytes(T) bytes, 8-byte aligned, zeroed once.

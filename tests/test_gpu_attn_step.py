@@ -93,3 +93,44 @@ def test_fused_row_refuses_a_full_cache():
          ptr(z(S * Hq * D, dt=torch.float32)), ptr(z(Hq, dt=torch.int32)), 0, 0, 0, cap, capi.stream_ptr())  # fmt: skip
     torch.cuda.synchronize()
     assert capi.status() == capi.ERR_DOMAIN
+
+
+@pytest.mark.parametrize("Hq,Hk,D,H", [(32, 8, 128, 2560), (64, 8, 64, 2880), (8, 8, 128, 512)])
+@pytest.mark.parametrize("n0", [0, 63, 160, 512, 1500, 4096, 5000])
+def test_attention_and_projection_in_one_launch(Hq, Hk, D, H, n0):
+    """btb_b200_attn_o_step leaves what btb_b200_attn_step then btb_b200_gemv_bf16 leave: cache, q, att and y"""
+    cap = 6144
+    gen = torch.Generator(device=DEV).manual_seed(n0 + Hq)
+    rnd = lambda *s: torch.randn(*s, generator=gen, device=DEV)  # noqa: E731
+    S = cap // 512
+    qkv = rnd(1, (Hq + 2 * Hk) * D).bfloat16()
+    wq, wk = (1 + 0.1 * rnd(D)).bfloat16(), (1 + 0.1 * rnd(D)).bfloat16()
+    cos, sin = torch.cos(rnd(cap, D)).bfloat16(), torch.sin(rnd(cap, D)).bfloat16()
+    K0, V0 = rnd(cap, Hk, D).bfloat16(), rnd(cap, Hk, D).bfloat16()
+    wo = (rnd(H, Hq * D) * 0.05).bfloat16()
+    n0t = torch.tensor([n0], dtype=torch.int32, device=DEV)
+    depth = torch.zeros(1, dtype=torch.int32, device=DEV)
+    bar = torch.zeros(2, dtype=torch.int32, device=DEV)
+
+    def bufs():
+        return dict(K=K0.clone(), V=V0.clone(), q=torch.zeros(1, Hq, D, dtype=torch.bfloat16, device=DEV),
+                    att=torch.zeros(1, Hq * D, dtype=torch.bfloat16, device=DEV), y=torch.zeros(1, H, dtype=torch.bfloat16, device=DEV),
+                    pm=torch.zeros(S * Hq, device=DEV), pl=torch.zeros(S * Hq, device=DEV), pa=torch.zeros(S * Hq * D, device=DEV),
+                    cnt=torch.zeros(Hq, dtype=torch.int32, device=DEV))  # fmt: skip
+
+    a, b = bufs(), bufs()
+    s = capi.stream_ptr()
+    scale = float(D**-0.5)
+    call("btb_b200_attn_step", ptr(qkv), ptr(wq), ptr(wk), 1e-6, ptr(cos), ptr(sin), ptr(n0t), ptr(depth), ptr(a["K"]),
+         ptr(a["V"]), ptr(a["q"]), ptr(a["att"]), Hq, Hk, D, D, Hk * D, 0, scale, ptr(a["pm"]), ptr(a["pl"]), ptr(a["pa"]),
+         ptr(a["cnt"]), 0, 0, 0, cap, s)  # fmt: skip
+    call("btb_b200_gemv_bf16", ptr(wo), ptr(a["att"]), ptr(a["y"]), 1, H, Hq * D, s)
+    for _ in range(3):  # the barrier's generation carries over from launch to launch
+        call("btb_b200_attn_o_step", ptr(qkv), ptr(wq), ptr(wk), 1e-6, ptr(cos), ptr(sin), ptr(n0t), ptr(depth),
+             ptr(b["K"]), ptr(b["V"]), ptr(b["q"]), ptr(b["att"]), Hq, Hk, D, D, Hk * D, 0, scale, ptr(b["pm"]),
+             ptr(b["pl"]), ptr(b["pa"]), ptr(b["cnt"]), 0, 0, cap, ptr(wo), ptr(b["y"]), H, ptr(bar), s)  # fmt: skip
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    for name in ("K", "V", "q", "att", "y"):
+        assert torch.equal(a[name].view(torch.int16), b[name].view(torch.int16)), name
+    assert bar.tolist() == [0, 3]
