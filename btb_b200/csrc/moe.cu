@@ -19,7 +19,7 @@ bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_st
                       int R, int C, int sr, int sc);
 int b2_moe_stream_launch(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
                          const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C, int ep_rank,
-                         int ep_size, cudaStream_t s);
+                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s);
 
 namespace {
 
@@ -371,6 +371,91 @@ __global__ void __launch_bounds__(256) moe_combine(const CombineArgs A) {
     A.y[(size_t)t * A.H + c] = f2bf(fin);
 }
 
+// ---- the sum and the next norm in one launch -----------------------------------------------------------------------
+// y = moe_combine's row (kept in `y` for nobody: written only when y is not null), h = bf16(h + y), x = rmsnorm(h) * w
+// and xf = x widened when asked: moe_combine followed by add_rmsnorm, with their arithmetic (the ordered bf16 sum; the
+// 256 strided partial sums and the 256 -> 1 tree with the reference's pairs).
+struct CombineNormArgs {
+    const float* dn;
+    const int* idx;
+    const bf16* rw;
+    bf16* h;
+    const bf16* nw;
+    bf16* x;
+    float* xf;
+    bf16* y;
+    float eps;
+    int k, H, centered;
+};
+__global__ void __launch_bounds__(256) moe_combine_norm(const CombineNormArgs A) {
+    extern __shared__ __align__(16) float hsm[];
+    __shared__ float red[256];
+    __shared__ int order[ROUTE_MAX_K];
+    __shared__ int eid[ROUTE_MAX_K];
+    __shared__ float wts[ROUTE_MAX_K];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, tid = threadIdx.x, k = A.k, H = A.H;
+    if (tid < k) {
+        eid[tid] = __ldcg(A.idx + (size_t)t * k + tid);
+        const unsigned short wb = __ldcg(reinterpret_cast<const unsigned short*>(A.rw) + (size_t)t * k + tid);
+        wts[tid] = __uint_as_float((uint32_t)wb << 16);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int a = 0; a < k; ++a) order[a] = a;
+        for (int a = 1; a < k; ++a) {
+            const int v = order[a], ev = eid[v];
+            int b = a - 1;
+            while (b >= 0 && eid[order[b]] > ev) {
+                order[b + 1] = order[b];
+                --b;
+            }
+            order[b + 1] = v;
+        }
+    }
+    __syncthreads();
+    bf16* hr = A.h + (size_t)t * H;
+    float ss = 0.f;
+    for (int c = tid; c < H; c += 256) {
+        float fin = 0.f;
+        for (int a = 0; a < k; ++a) {
+            const int sl = order[a];
+            float o = bfround(__ldcg(A.dn + ((size_t)t * k + sl) * H + c));
+            o = bfround(o * wts[sl]);
+            fin = bfround(fin + o);
+        }
+        if (A.y != nullptr) A.y[(size_t)t * H + c] = f2bf(fin);
+        const float hv = bfround(bf2f(hr[c]) + fin);
+        hr[c] = f2bf(hv);
+        hsm[c] = hv;
+        ss = fmaf(hv, hv, ss);  // thread i's strided terms i, i + 256, .. in order: the reference's partial sums
+    }
+    red[tid] = ss;
+    __syncthreads();
+    if (tid < 32) {
+        float v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] = red[tid + 32 * q];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) v[q] += v[q + 4];
+        v[0] += v[2];
+        v[1] += v[3];
+        v[0] += v[1];
+#pragma unroll
+        for (int st = 16; st > 0; st >>= 1) v[0] += __shfl_down_sync(0xffffffffu, v[0], st);
+        if (tid == 0) red[0] = v[0];
+    }
+    __syncthreads();
+    const float rstd = rsqrtf(red[0] / (float)H + A.eps);
+    for (int c = tid; c < H; c += 256) {
+        const float wv = bf2f(A.nw[c]);
+        const bf16 o = f2bf(hsm[c] * rstd * (A.centered ? 1.f + wv : wv));
+        A.x[(size_t)t * H + c] = o;
+        if (A.xf != nullptr) A.xf[(size_t)t * H + c] = bf2f(o);
+    }
+}
+
 // bf16 [n] -> f32 [n] (the experts' and the router's x is the normed row widened)
 struct WidenArgs {
     const bf16* x;
@@ -446,11 +531,27 @@ extern "C" int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, lon
     // the streaming kernel takes every shape whose rows start on 16 bytes; the rest keep the plain 16-lane kernel
     if (b2_tuning().moe_stream && n_tasks <= 65535 && b2_moe_stream_ok(fmt, w, scales, w_stride, s_stride, x, R, C, sr, sc))
         return b2_moe_stream_launch(fmt, w, scales, w_stride, s_stride, sr, sc, idx, n_tasks, E, x, x_div, y, R, C, ep_rank,
-                                    ep_size, static_cast<cudaStream_t>(stream));
+                                    ep_size, -1, 0.f, 0.f, static_cast<cudaStream_t>(stream));
     L16Args a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), w_stride, s_stride,
               static_cast<const int*>(idx), static_cast<const float*>(x), x_div, static_cast<float*>(y), R, C,
               sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size};
     return lane16_launch(fmt, a, n_tasks, static_cast<cudaStream_t>(stream));
+}
+
+// the picked experts' DOWN matvecs with the gated activation made on the way in: x row of task i = act(gu row i).
+// btb_b200_moe_act followed by btb_b200_moe_gemv (x_div 1), one launch and no [n, I] buffer. No bias.
+extern "C" int btb_b200_moe_gemv_act(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride,
+                                     int sr, int sc, const void* idx, int n_tasks, int E, const void* gu, int kind,
+                                     float alpha, float limit, void* y, int R, int C, int ep_rank, int ep_size,
+                                     void* stream) {
+    if (!w || !gu || !y || (fmt != L_BF16 && !scales)) return B2_ERR_NULL;
+    if (n_tasks <= 0 || n_tasks > 65535 || R <= 0 || C <= 0 || E <= 0 || ep_size < 1 || ep_rank < 0 || ep_rank >= ep_size ||
+        (kind != 0 && kind != 1))
+        return B2_ERR_DOMAIN;
+    if (fmt == L_FP8 && (sr <= 0 || sc <= 0 || R % sr || C % sc)) return B2_ERR_DOMAIN;
+    if (!b2_moe_stream_ok(fmt, w, scales, w_stride, s_stride, gu, R, C, sr, sc)) return B2_ERR_DOMAIN;
+    return b2_moe_stream_launch(fmt, w, scales, w_stride, s_stride, sr, sc, idx, n_tasks, E, gu, 1, y, R, C, ep_rank,
+                                ep_size, kind, alpha, limit, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int btb_b200_moe_act(const void* gu, void* h, const void* bias, const void* idx, int n, int I, int kind,
@@ -479,4 +580,16 @@ extern "C" int btb_b200_widen_f32(const void* x, void* y, int n, void* stream) {
     WidenArgs a{static_cast<const bf16*>(x), static_cast<float*>(y), n};
     const int grid = (n + 255) / 256 < 296 ? (n + 255) / 256 : 296;
     return b2_launch((const void*)widen_f32, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+}
+
+extern "C" int btb_b200_moe_combine_norm(const void* dn, const void* idx, const void* w, int k, void* h, const void* norm_w,
+                                         float eps, void* x, void* xf, void* y, int T, int H, int centered, void* stream) {
+    if (!dn || !idx || !w || !h || !norm_w || !x) return B2_ERR_NULL;
+    if (T <= 0 || k <= 0 || k > ROUTE_MAX_K || H <= 0 || (size_t)H * 4 > 200 * 1024 || !(eps == eps)) return B2_ERR_DOMAIN;
+    CombineNormArgs a{static_cast<const float*>(dn), static_cast<const int*>(idx), static_cast<const bf16*>(w),
+                      static_cast<bf16*>(h), static_cast<const bf16*>(norm_w), static_cast<bf16*>(x),
+                      static_cast<float*>(xf), static_cast<bf16*>(y), eps, k, H, centered};
+    static bool allowed[64];
+    if (const int rc = b2_allow_smem((const void*)moe_combine_norm, allowed)) return rc;
+    return b2_launch((const void*)moe_combine_norm, dim3(T), dim3(256), (size_t)H * 4, static_cast<cudaStream_t>(stream), a);
 }

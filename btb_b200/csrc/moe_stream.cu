@@ -34,7 +34,24 @@ struct MSArgs {
     int ep_rank, ep_size;
     int seg;                // columns a stage holds of each row (a multiple of 32)
     int stages;
+    // x made on the way in from the gate/up outputs (btb/engine/host.py:439-450): x row of task i is the gated
+    // activation of gu row i [2C]. act_kind -1: x as given; 0: silu(gate) * up over halves; 1: gpt-oss's clamped GLU
+    // over interleaved lanes - every bf16 rounding of the host's torch ops kept
+    int act_kind;
+    float alpha, limit;
 };
+
+__device__ __forceinline__ float moe_act_value(const float* gu, int c, int I, int kind, float alpha, float limit) {
+    const int gi = kind == 0 ? c : 2 * c, ui = kind == 0 ? I + c : 2 * c + 1;
+    float g = bfround(__ldcg(gu + gi)), u = bfround(__ldcg(gu + ui));
+    if (kind == 0) return bfround(bfround(g / (1.f + expf(-g))) * u);
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    const float t1 = bfround(g * alpha);
+    const float t2 = bfround(1.f / (1.f + expf(-t1)));
+    const float glu = bfround(g * t2);
+    return bfround(bfround(u + 1.f) * glu);
+}
 
 // four e2m1 codes (the nibbles of `codes`, lowest first) as two bf16 pairs: p01 = (value 0 | value 1 << 16), p23 alike.
 // A value's bf16 pattern is two table bytes: the high byte out of eight by the code's low three bits, from the
@@ -144,9 +161,12 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
         for (int i = 0; i < first; ++i) issue_next();
     }
     // x as f32 in shared memory, once a CTA
-    {
+    if (A.act_kind < 0) {
         const float4* xg = reinterpret_cast<const float4*>(A.x + (size_t)(task / A.x_div) * C);
         for (int i = threadIdx.x; i < C / 4; i += blockDim.x) reinterpret_cast<float4*>(xs)[i] = __ldcg(xg + i);
+    } else {
+        const float* gu = A.x + (size_t)task * 2 * C;
+        for (int i = threadIdx.x; i < C; i += blockDim.x) xs[i] = moe_act_value(gu, i, C, A.act_kind, A.alpha, A.limit);
     }
     __syncthreads();
 
@@ -390,10 +410,10 @@ bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_st
 
 int b2_moe_stream_launch(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
                          const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C, int ep_rank,
-                         int ep_size, cudaStream_t s) {
+                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s) {
     MSArgs a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), w_stride, s_stride,
              static_cast<const int*>(idx), static_cast<const float*>(x), x_div, static_cast<float*>(y), R, C,
-             sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size, 0, 0};
+             sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size, 0, 0, act_kind, alpha, limit};
     switch (fmt) {
         case S_BF16: return launch_stream<S_BF16>(a, n_tasks, s);
         case S_MX4: return launch_stream<S_MX4>(a, n_tasks, s);

@@ -174,6 +174,7 @@ class MoEEngine(CardEngine):
         super().__init__(weights, cap=cap, step_kernel=False, device=device)  # type: ignore[arg-type]
         self.group = group
         self.ep_rank, self.ep_size = weights.ep_rank, weights.ep_size
+        self.fold = True  # the activation inside the down matvecs' launch, the picks' sum inside the next norm's
 
     def bufs(self, M: int) -> dict[str, torch.Tensor]:
         g = super().bufs(M)
@@ -200,9 +201,21 @@ class MoEEngine(CardEngine):
         s = capi.stream_ptr() if stream_ptr is None else stream_ptr
         H, Hq, Hk, D, I, E, k = c.hidden, c.q_heads, c.kv_heads, c.head_dim, c.inter, c.experts, c.top_k
         K_ = self._k
+        fold = self.fold
+        pending = False  # the previous layer's picks are summed by the norm that reads them
         y_prev = None
+
+        def norm_in(norm_w: torch.Tensor) -> None:
+            nonlocal pending
+            if pending:
+                K_("btb_b200_moe_combine_norm", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), k, ptr(g["h"]), ptr(norm_w),
+                   c.eps, ptr(g["x"]), 0, 0, T, H, 0, s)
+                pending = False
+            else:
+                K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
+
         for i, L in enumerate(self.w.layers):
-            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(g["x"]), T, H, 0, s)
+            norm_in(L.ln1)
             self._matvec(L.qkv, g["x"], g["qkv"], M, c.qkv_rows, H, s)
             self._attention(g, i, L.wq, L.wk, T, s)
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
@@ -213,17 +226,29 @@ class MoEEngine(CardEngine):
             K_("btb_b200_moe_gemv", 0, ptr(L.router), 0, 0, 0, 1, 1, 0, T, 1, ptr(g["xf"]), 1, ptr(g["rl"]), E, H, 0, 1, s)
             K_("btb_b200_moe_route", ptr(g["rl"]), E, E, k, c.router_mode, 1, ptr(g["idx"]), ptr(g["rw"]), T, s)
             self._expert_gemv(L.gu, g["idx"], T * k, g["xf"], k, g["egu"], s)
-            K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
-            self._expert_gemv(L.dn, g["idx"], T * k, g["eh"], 1, g["edn"], s)
+            st = L.dn
+            if fold and I % 32 == 0:
+                # the gated activation is made inside the down matvecs' launch
+                K_("btb_b200_moe_gemv_act", FMT[st.fmt], ptr(st.w), ptr(st.scales), st.w_stride, st.s_stride, st.sr, st.sc,
+                   ptr(g["idx"]), T * k, E, ptr(g["egu"]), c.glu_kind, c.alpha, c.limit, ptr(g["edn"]), st.R, st.C,
+                   self.ep_rank, self.ep_size, s)  # fmt: skip
+            else:
+                K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
+                self._expert_gemv(L.dn, g["idx"], T * k, g["eh"], 1, g["edn"], s)
             if self.ep_size > 1:
                 import torch.distributed as dist
 
                 dist.all_reduce(g["edn"][: T * k], group=self.group)
-            K_("btb_b200_moe_combine", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, s)
+            if fold:
+                pending = True
+            else:
+                K_("btb_b200_moe_combine", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, s)
             y_prev = g["y"]
         if tail:
-            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(self.w.norm), c.eps, ptr(g["x"]), T, H, 0, s)
+            norm_in(self.w.norm)
             self._matvec(self.w.embed, g["x"], g["logits"], M, c.vocab, H, s)
+        elif pending:  # a pass without its head leaves the last layer's sum in y, as the unfolded pass does
+            K_("btb_b200_moe_combine", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, s)
 
     def weight_bytes(self) -> int:
         return self.cfg.weight_bytes_per_token()

@@ -216,10 +216,22 @@ int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, long long w_st
  * (host.py:444-450; btb/mxfp4_torch.py:146-153), every bf16 rounding of the torch ops kept; h f32 [n,I]. */
 int btb_b200_moe_act(const void* gu, void* h, const void* bias, const void* idx, int n, int I, int kind, float alpha,
                      float limit, void* stream);
+/* btb_b200_moe_act then btb_b200_moe_gemv as one launch: task i's x row is the gated activation of gu row i
+ * (f32 [n_tasks, 2C]; kind, alpha, limit as btb_b200_moe_act; no bias), made while the expert's rows are on their
+ * way. y f32 [n_tasks, R]. Shapes the streaming kernel does not take (C not a multiple of 32, unaligned rows) are
+ * refused: use the two calls. */
+int btb_b200_moe_gemv_act(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr,
+                          int sc, const void* idx, int n_tasks, int E, const void* gu, int kind, float alpha,
+                          float limit, void* y, int R, int C, int ep_rank, int ep_size, void* stream);
 /* host.py:426-431,565-569: out_e = bf16(down_e) (+ bias [E,H]) * w_e, summed one bf16 add at a time in ascending
  * expert id from zero. dn f32 [T,k,H], y bf16 [T,H]. */
 int btb_b200_moe_combine(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T, int k, int H,
                          void* stream);
+/* btb_b200_moe_combine (no bias) and the btb_b200_add_rmsnorm that reads its row, one launch: the ordered bf16 sum of
+ * the k picks, h = bf16(h + sum), x = bf16(h * rstd * norm_w); xf (f32, may be null) = x widened; y (may be null)
+ * receives the sum itself. The bits are the two launches'. */
+int btb_b200_moe_combine_norm(const void* dn, const void* idx, const void* w, int k, void* h, const void* norm_w,
+                              float eps, void* x, void* xf, void* y, int T, int H, int centered, void* stream);
 /* x.float() (host.py:525): bf16 [n] -> f32 [n] */
 int btb_b200_widen_f32(const void* x, void* y, int n, void* stream);
 

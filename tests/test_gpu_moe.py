@@ -252,3 +252,19 @@ def test_expert_gemv_stream_equals_the_cpu_tier_bits(R, C_, n, k, fmt):
     tot = parts[0] + parts[1]
     assert torch.equal(tot.view(torch.int32), y.view(torch.int32))
     assert all(bool((parts[int(idx[i]) % 2 ^ 1][i] == 0).all()) for i in range(n))
+
+
+@pytest.mark.parametrize("name", list(SMALL))
+def test_folded_moe_pass_equals_the_unfolded_pass(name):
+    """the activation inside the down matvecs' launch and the picks' sum inside the next norm's change no bit"""
+    cfg = SMALL[name]
+    mw = MO.synth_moe_weights(cfg, seed=3, on_cpu=True)
+    a, b = MO.MoEEngine(mw, cap=512), MO.MoEEngine(mw, cap=512)
+    b.fold = False
+    prompt = torch.arange(7, 40)
+    la, lb = a.forward(prompt[:20]), b.forward(prompt[:20])
+    assert torch.equal(la.view(torch.int16), lb.view(torch.int16))
+    la, lb = a.forward(prompt[20:21]), b.forward(prompt[20:21])
+    assert torch.equal(la.view(torch.int16), lb.view(torch.int16))
+    assert torch.equal(a.K.view(torch.int16), b.K.view(torch.int16))
+    assert a.generate_greedy(prompt, 8) == b.generate_greedy(prompt, 8)
