@@ -446,7 +446,7 @@ STORED = {"p12": "pack12", "mx4": "MXFP4 expert", "fp8": "FP8 block-scaled"}
 
 def run_case(args) -> None:
     """one kernel on a small case, for a profiler capture or a quick look: `gemv:RxC[:M[:fmt]]` rotates over enough
-    seeded matrices to stay out of L2 (fmt bf16 | p12); `attn:N` is the step's fused attention row over N cached rows
+    seeded matrices to stay out of L2 (fmt bf16 | p12 | tc: the tensor-core matvec); `attn:N` is the step's fused attention row over N cached rows
     at the Qwen3-4B head shape. Prints us a launch (CUDA events) and, for a GEMV, the weight-streaming rate."""
     import torch
 
@@ -463,7 +463,7 @@ def run_case(args) -> None:
         R, C_ = (int(v) for v in parts[0].split("x"))
         M = int(parts[1]) if len(parts) > 1 else 1
         fmt = parts[2] if len(parts) > 2 else "bf16"
-        per = R * C_ * (2 if fmt == "bf16" else 1.5)
+        per = R * C_ * (1.5 if fmt == "p12" else 2)
         nmat = max(2, int(400e6 // per) + 1)
         gen = torch.Generator(device="cuda").manual_seed(0)
         ws = []
@@ -477,8 +477,14 @@ def run_case(args) -> None:
         x = torch.randn(M, C_, device="cuda", generator=gen).to(torch.bfloat16)
         y = torch.zeros(M, R, device="cuda", dtype=torch.bfloat16)
 
+        ws_tc = None
+        if fmt == "tc":
+            ws_tc = torch.zeros(max(int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, C_)) // 4, 4), device="cuda")
+
         def one(w):
-            if fmt == "p12":
+            if fmt == "tc":
+                call("btb_b200_gemv_tc_bf16", ptr(w), ptr(x), ptr(y), M, R, C_, ptr(ws_tc), sp)
+            elif fmt == "p12":
                 call("btb_b200_gemv_p12", ptr(w.lo), ptr(w.hi4), w.table, ptr(w.esc_idx), ptr(w.esc_val), ptr(w.esc_row),
                      ptr(x), ptr(y), M, R, C_, sp)  # fmt: skip
             else:
@@ -531,6 +537,7 @@ def run_batch(args, mw, cfg, storage, cap, rank, world, dist) -> None:
 
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     eng = BatchEngine(mw, B, cap=cap)
+    eng.wide_tc = bool(args.wide_tc) and storage == "bf16"
     prompts = [torch.randint(0, cfg.vocab, (PROMPT,), generator=torch.Generator().manual_seed(100 + b)) for b in range(B)]
     eng.prefill_all(prompts)
     graph = eng.batch_graph()
@@ -568,6 +575,7 @@ def run_batch(args, mw, cfg, storage, cap, rank, world, dist) -> None:
         "data": "synthetic",
         "config": {"workload": f"{cfg.name}-shape {storage}, batch {B} (independent seeded prompts of {PROMPT} tokens), "
                    "greedy decode", "parallelism": "replicas only" if world > 1 else "1 gpu", "batch": B,
+                   "matvec": "tensor cores (tcgen05)" if eng.wide_tc else "fp32 chains",
                    "l2": "weights per step > L2 126 MB", "bytes_per_step": cfg.weight_bytes_per_token(storage)},
         "clocks": clk.summary(),
         "e2e": {"value": world * B * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8 * B},
@@ -656,6 +664,7 @@ def main() -> None:
     ap.add_argument("--cpu-steps", type=int, default=4)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--batch", type=int, default=1, help="qwen3-4b workloads: sequences decoded side by side")
+    ap.add_argument("--wide-tc", type=int, default=1, help="--batch: the tensor-core matvec for the pass of B rows")
     ap.add_argument("--case", default="", help="one kernel on a small case: gemv:RxC[:M[:fmt]] or attn:N")
     ap.add_argument("--speculative", type=int, default=0, help="verify an n-gram tree of this many drafts a pass")
     args = ap.parse_args()

@@ -12,7 +12,7 @@ static int env_int(const char* name, int dflt) {
 B2Tuning& b2_tuning() {
     static B2Tuning t = {
         env_int("BTB_B200_RING_BYTES", 96 * 1024), env_int("BTB_B200_SEG_BYTES", 4096),
-        env_int("BTB_B200_X_SMEM_MAX", 64 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
+        env_int("BTB_B200_X_SMEM_MAX", 160 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
         env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 1),
         env_int("BTB_B200_WARPS", 16),             env_int("BTB_B200_SOLO", 1),
         env_int("BTB_B200_MOE_STREAM", 1),         env_int("BTB_B200_MS_TPR", 0),
@@ -64,11 +64,12 @@ int b2_status_take_moe(int*);
 int b2_status_take_sample(int*);
 int b2_status_take_moes(int*);
 int b2_status_take_attno(int*);
+int b2_status_take_tc(int*);
 
 extern "C" int btb_b200_status(int* code) {
     if (code == nullptr) return B2_ERR_NULL;
     int (*const take[])(int*) = {b2_status_take_gemv, b2_status_take_layer, b2_status_take_attn, b2_status_take_step,
-                                 b2_status_take_moe, b2_status_take_sample, b2_status_take_moes, b2_status_take_attno};
+                                 b2_status_take_moe, b2_status_take_sample, b2_status_take_moes, b2_status_take_attno, b2_status_take_tc};
     *code = 0;
     for (auto f : take) {
         int v = 0;

@@ -194,6 +194,12 @@ class CardEngine:
         self.n0 = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.silu_fold = silu_fold
         self.fuse_norm = fuse_norm
+        # passes of 4..32 rows over bf16 weights through the tensor cores (btb_b200_gemv_tc_bf16). Off: every pass runs
+        # the fp32-chain kernels, whose row r equals the one-row step's row r to the bit - what a speculative verify
+        # pass compares. On: prefill chunks and small batches run several times faster; their rows agree with the
+        # step's to rounding.
+        self.wide_tc = False
+        self._tc_ws: Any = None
         self.swiglu_epilogue = True  # SwiGLU in the gate/up GEMV's epilogue (passes of up to 8 rows)
         # ... and the output projection in the same (cooperative) launch
         self.fuse_attn_o = os.environ.get("BTB_B200_FUSE_ATTN_O", "0") == "1"
@@ -247,6 +253,15 @@ class CardEngine:
         self._n += 1
 
     def _matvec(self, W: Any, x: torch.Tensor, y: torch.Tensor, M: int, R: int, C_: int, s: int) -> None:
+        if self.wide_tc and M >= 4 and isinstance(W, torch.Tensor):
+            # a pass of several rows over bf16 weights: the tensor-core matvec (its own summation order)
+            need = int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, C_))
+            if self._tc_ws is None or self._tc_ws.numel() * 4 < need:
+                self._tc_ws = torch.zeros(max(need // 4, 4), dtype=torch.float32, device=self.dev)
+            self._k("btb_b200_gemv_tc_bf16", ptr(W), ptr(x), ptr(y), M, R, C_, ptr(self._tc_ws), s)
+            if need:
+                self._n += 1  # the ordered sum of the K ranges is a launch of its own
+            return
         if isinstance(W, P12Matrix):
             self._k("btb_b200_gemv_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),
                     ptr(W.esc_row), ptr(x), ptr(y), M, R, C_, s)  # fmt: skip
@@ -265,7 +280,8 @@ class CardEngine:
         k = self._k
         # the residual ping-pongs between two buffers when the norm is folded into the GEMV that reads it (a CTA must
         # not read a row another CTA is updating); the pass starts and ends on g["h"]
-        fuse = self.fuse_norm and M <= 8 and M * max(H, 1) * 2 <= 64 * 1024
+        tc = self.wide_tc and M >= 4 and isinstance(self.w.layers[0].qkv, torch.Tensor)
+        fuse = self.fuse_norm and M <= 8 and M * max(H, 1) * 2 <= 64 * 1024 and not tc
         hcur, halt = g["h"], g["h2"]
 
         def normed_matvec(W: Any, norm_w: torch.Tensor, y_add: Any, out: torch.Tensor, R: int,
@@ -302,7 +318,7 @@ class CardEngine:
                 y_prev = g["y"]
                 continue
             normed_matvec(L.gu, L.ln2, g["y"], g["gu"], 2 * I)
-            if self.silu_fold and M <= 8 and M * I * 2 <= 64 * 1024:
+            if self.silu_fold and M <= 8 and M * I * 2 <= 160 * 1024 and not tc:
                 if isinstance(L.down, P12Matrix):
                     W = L.down
                     k("btb_b200_gemv_silu_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),

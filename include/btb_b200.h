@@ -42,6 +42,14 @@ int btb_b200_status(int* code);
 
 /* btb_gemv_bf16_m{M} (btb_kernels.cu:89-155). w [R,C] bf16, x [M,C] bf16, y [M,R] bf16. */
 int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* stream);
+/* btb_gemv_mma_bf16 (native/cuda/btb_gemv_mma.cuh:123-315): the tensor-core matvec for passes of 1..32 rows - tcgen05.mma
+ * with the accumulator in tensor memory, operand tiles by TMA tensor maps. One kernel for every pass width (x is read
+ * as 32 rows, the rest zeros), so a row's bits do not depend on the width; its summation order is its own (as the
+ * reference's is): it agrees with btb_b200_gemv_bf16 to rounding, not to the bit. workspace: f32,
+ * btb_b200_gemv_tc_workspace_bytes(R, C) bytes (0 for matrices of many rows), 16-byte aligned, for the K ranges'
+ * partial sums of matrices with few rows. */
+int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* workspace, void* stream);
+size_t btb_b200_gemv_tc_workspace_bytes(int R, int C);
 /* btb_gemv_silu_bf16_m{M} (btb_kernels.cu:171-227): gu [M,2C] (gate then up), x = bf16(bf16(silu(g)) * u)
  * computed on the way in. M <= 8 and M*C*2 <= the x staging budget, else BTB_B200_ERR_DOMAIN (use
  * btb_b200_silu_mul + btb_b200_gemv_bf16: the same bits). */

@@ -96,7 +96,7 @@ def test_gemv_bits_do_not_depend_on_the_ring_geometry(tune):
     w, x = rand_bf(rng, (R, Cc), 0.02), rand_bf(rng, (M, Cc))
     wt, xt = bf(w), bf(x)
     want = O.gemv_card_bf16(w, x)
-    dflt = dict(ring_bytes=96 * 1024, seg_bytes=4096, x_smem_max=64 * 1024, ctas_per_sm=1, evict_first=1)
+    dflt = dict(ring_bytes=96 * 1024, seg_bytes=4096, x_smem_max=160 * 1024, ctas_per_sm=1, evict_first=1)
     try:
         capi.set_tuning(**tune)
         y = torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
@@ -126,7 +126,7 @@ def test_gemv_silu_fold_equals_two_kernels(M, R, Cc):
     w, gu = rand_bf(rng, (R, Cc), 0.02), rand_bf(rng, (M, 2 * Cc), 1.5)
     wt, gt = bf(w), bf(gu)
     y = torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
-    if M * Cc * 2 > 64 * 1024:  # the activated x does not fit its shared-memory budget: refused, by contract
+    if M * Cc * 2 > 160 * 1024:  # the activated x does not fit its shared-memory budget: refused, by contract
         with pytest.raises(capi.NativeError) as e:
             call("btb_b200_gemv_silu_bf16", ptr(wt), ptr(gt), ptr(y), M, R, Cc, s())
         assert e.value.rc == capi.ERR_DOMAIN

@@ -1,0 +1,87 @@
+"""The tensor-core matvec (tcgen05, accumulator in tensor memory) for passes of up to 32 rows: right to bf16 rounding
+against an exact reference, a row's bits independent of the pass width, the same bits every launch."""
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+from btb_b200 import capi  # noqa: E402
+from btb_b200.capi import call, ptr  # noqa: E402
+
+DEV = "cuda"
+
+
+def _run(w, x, M=None):
+    M = x.shape[0] if M is None else M
+    R, C_ = w.shape
+    y = torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
+    nbytes = int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, C_))
+    ws = torch.zeros(max(nbytes // 4, 4), dtype=torch.float32, device=DEV)
+    call("btb_b200_gemv_tc_bf16", ptr(w), ptr(x), ptr(y), M, R, C_, ptr(ws), capi.stream_ptr())
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    return y
+
+
+SHAPES = [(128, 64), (256, 512), (300, 2560), (2560, 4096), (2560, 9728), (6144, 2560), (19456, 2560), (5, 72), (129, 8),
+          (1000, 2880)]  # fmt: skip
+
+
+@pytest.mark.parametrize("R,C_", SHAPES)
+@pytest.mark.parametrize("M", [1, 3, 8, 32])
+def test_tc_gemv_is_right_to_bf16_rounding(R, C_, M):
+    g = torch.Generator(device=DEV).manual_seed(R + C_ + M)
+    w = (torch.randn(R, C_, generator=g, device=DEV) * 0.05).bfloat16()
+    x = torch.randn(M, C_, generator=g, device=DEV).bfloat16()
+    y = _run(w, x)
+    ref = x.double() @ w.double().t()
+    # the products are exact in f32 and the sums are f32 over at most C terms: the error is the final rounding to bf16
+    # (2^-9 relative) plus the f32 accumulation's (C * 2^-24 of the row's absolute sum)
+    bound = ref.abs() * 2.0**-8 + (x.double().abs() @ w.double().abs().t()) * (C_ * 2.0**-24) + 1e-30
+    assert bool(((y.double() - ref).abs() <= bound).all())
+
+
+@pytest.mark.parametrize("R,C_", [(300, 2560), (2560, 4096), (19456, 2560)])
+def test_a_rows_bits_do_not_depend_on_the_pass_width(R, C_):
+    g = torch.Generator(device=DEV).manual_seed(R)
+    w = (torch.randn(R, C_, generator=g, device=DEV) * 0.05).bfloat16()
+    x = torch.randn(32, C_, generator=g, device=DEV).bfloat16()
+    wide = _run(w, x)
+    again = _run(w, x)
+    assert torch.equal(wide.view(torch.int16), again.view(torch.int16))  # the same bits every launch
+    for m in (0, 7, 31):
+        one = _run(w, x[m : m + 1].contiguous())
+        assert torch.equal(one.view(torch.int16)[0], wide.view(torch.int16)[m])
+    eight = _run(w, x[:8].contiguous())
+    assert torch.equal(eight.view(torch.int16), wide.view(torch.int16)[:8])
+
+
+def test_tc_gemv_agrees_with_the_chain_gemv_to_rounding():
+    g = torch.Generator(device=DEV).manual_seed(1)
+    R, C_, M = 2560, 2560, 8
+    w = (torch.randn(R, C_, generator=g, device=DEV) * 0.02).bfloat16()
+    x = torch.randn(M, C_, generator=g, device=DEV).bfloat16()
+    y = _run(w, x)
+    y2 = torch.zeros_like(y)
+    call("btb_b200_gemv_bf16", ptr(w), ptr(x), ptr(y2), M, R, C_, capi.stream_ptr())
+    d = (y.float() - y2.float()).abs()
+    assert float(d.max()) <= 2.0**-7 * float(y2.float().abs().max())
+    assert float((d > 0).float().mean()) < 0.5  # most outputs round to the same bf16
+
+
+def test_tc_gemv_refuses_bad_arguments():
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
+    for M, R, C_ in ((0, 128, 64), (33, 128, 64), (1, 0, 64), (1, 128, 60)):
+        with pytest.raises(capi.NativeError) as e:
+            call("btb_b200_gemv_tc_bf16", ptr(w), ptr(w), ptr(w), M, R, C_, 0, 0)
+        assert e.value.rc == capi.ERR_DOMAIN
+    with pytest.raises(capi.NativeError):
+        call("btb_b200_gemv_tc_bf16", 0, ptr(w), ptr(w), 1, 128, 64, 0, 0)
+    big = torch.zeros(2560, 4096, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(capi.NativeError):  # a matrix of few tiles needs the partial sums' workspace
+        call("btb_b200_gemv_tc_bf16", ptr(big), ptr(big), ptr(big), 1, 2560, 4096, 0, 0)
