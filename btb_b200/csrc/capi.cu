@@ -17,7 +17,8 @@ B2Tuning& b2_tuning() {
         env_int("BTB_B200_WARPS", 16),             env_int("BTB_B200_SOLO", 1),
         env_int("BTB_B200_MOE_STREAM", 1),         env_int("BTB_B200_MS_TPR", 0),
         env_int("BTB_B200_MS_SEG", 0),
-        env_int("BTB_B200_MS_WARPS", 0),
+        env_int("BTB_B200_MS_WARPS", 0),           env_int("BTB_B200_TC_STAGES", 0),
+        env_int("BTB_B200_TC_CTAS", 0),
         env_int("BTB_B200_BALANCE", 1),
     };
     return t;

@@ -26,7 +26,7 @@ namespace {
 constexpr int TC_BM = 128;  // weight rows a tile (the MMA's M)
 constexpr int TC_BN = 32;   // x rows, padded (the MMA's N)
 constexpr int TC_BK = 64;   // columns a stage: one 128-byte swizzle span of bf16
-constexpr int TC_STAGES = 4;
+constexpr int TC_STAGES_MAX = 10;  // ring depth at most; the launch picks (four stages let two CTAs share an SM)
 constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TC_BN * TC_BK * 2, ST_BYTES = A_BYTES + B_BYTES;
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
@@ -58,13 +58,14 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 struct TcArgs {
     bf16* y;      // [M, R]
     float* part;  // [splits, 32, R] partial sums when splits > 1
-    int R, C, M, kblocks_per_split, splits;
+    int R, C, M, kblocks_per_split, splits, stages;
 };
 
 __global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtensorMap tmW,
                                                   const __grid_constant__ CUtensorMap tmX, const TcArgs A) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t full[TC_STAGES], empty[TC_STAGES], done;
+    __shared__ __align__(8) uint64_t full[TC_STAGES_MAX], empty[TC_STAGES_MAX], done;
+    const int TC_STAGES = A.stages;
     __shared__ uint32_t tmem_slot;
     __shared__ int s_fail;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,7 +213,8 @@ int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, ui
 // matrix's shape alone, so every pass width sums in the same order
 int tc_splits(int R, int C) {
     const int tiles = (R + TC_BM - 1) / TC_BM, kb = (C + TC_BK - 1) / TC_BK;
-    const int want = max(1, (2 * b2_sm_count()) / tiles);
+    const int per_sm = b2_tuning().tc_ctas > 0 ? b2_tuning().tc_ctas : 2;
+    const int want = max(1, (per_sm * b2_sm_count()) / tiles);
     return max(1, min(min(want, 16), kb / 4));
 }
 
@@ -234,13 +236,14 @@ extern "C" int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int 
     CUtensorMap tw, tx;
     if (make_map(&tw, w, (uint64_t)R, (uint64_t)C, TC_BM) || make_map(&tx, x, (uint64_t)M, (uint64_t)C, TC_BN)) return B2_ERR_CUDA;
     const int total_kb = (C + TC_BK - 1) / TC_BK;
-    TcArgs a{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, (total_kb + splits - 1) / splits, splits};
-    const int smem = TC_STAGES * ST_BYTES + 1024;
+    const int stages = b2_tuning().tc_stages > 0 ? min(TC_STAGES_MAX, b2_tuning().tc_stages) : 4;
+    TcArgs a{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, (total_kb + splits - 1) / splits, splits, stages};
+    const int smem = stages * ST_BYTES + 1024;
     static bool allowed[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
     if (!allowed[dev]) {
-        if (cudaFuncSetAttribute(gemv_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        if (cudaFuncSetAttribute(gemv_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_STAGES_MAX * ST_BYTES + 1024) != cudaSuccess) {
             (void)cudaGetLastError();
             return B2_ERR_CUDA;
         }
