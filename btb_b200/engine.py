@@ -15,7 +15,6 @@ from __future__ import annotations
 
 import os
 
-import math
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -508,4 +507,4 @@ def ceil_div(a: int, b: int) -> int:
 
 
 __all__ = ["CardEngine", "DenseConfig", "ModelWeights", "LayerWeights", "P12Matrix", "QWEN3_4B", "LLAMA31_70B",
-           "synth_weights", "rope_tables", "pad_rows", "math"]  # fmt: skip
+           "synth_weights", "rope_tables", "pad_rows"]  # fmt: skip

@@ -45,6 +45,7 @@ class B200Launcher:
     FAMILIES = (
         (r"btb_gemv_bf16_m(\d+)$", "_gemv_bf16"),
         (r"btb_gemv_silu_bf16_m(\d+)$", "_gemv_silu"),
+        (r"btb_gemv_mma_bf16$", "_gemv_mma"),
         (r"btb_add_rmsnorm$", "_add_rmsnorm"),
         (r"btb_silu_mul$", "_silu_mul"),
         (r"btb_norm_rope_kv_d(\d+)$", "_norm_rope_kv"),
@@ -64,6 +65,7 @@ class B200Launcher:
 
     def __init__(self) -> None:
         self.lib = capi.lib()
+        self._tc_ws: Any = None  # the tensor-core matvec's partial sums (matrices of few rows)
         self._top_k = 0  # the pick being assembled: the reference launches it as a pipeline of kernels
         self._families = [(re.compile(rx), getattr(self, h)) for rx, h in self.FAMILIES if hasattr(self, h)]
 
@@ -88,6 +90,18 @@ class B200Launcher:
     def _gemv_silu(self, name, m, grid, a, s):
         w, gu, y, R, Cc = a
         capi.call("btb_b200_gemv_silu_bf16", _p(w), _p(gu), _p(y), int(m.group(1)), int(_v(R)), int(_v(Cc)), s)
+
+    def _gemv_mma(self, name, m, grid, a, s):
+        # btb_gemv_mma_bf16(w [R, C], x [32, C], y [32, R], R, C, M): the tensor-core matvec, M live rows
+        import torch
+
+        w, x, y, R, Cc, M = a
+        R, Cc = int(_v(R)), int(_v(Cc))
+        need = int(self.lib.btb_b200_gemv_tc_workspace_bytes(R, Cc))
+        if need and (self._tc_ws is None or self._tc_ws.numel() * 4 < need):
+            self._tc_ws = torch.zeros(need // 4, dtype=torch.float32, device="cuda")
+        ws = 0 if not need else int(self._tc_ws.data_ptr())
+        capi.call("btb_b200_gemv_tc_bf16", _p(w), _p(x), _p(y), int(_v(M)), R, Cc, ws, s)
 
     def _add_rmsnorm(self, name, m, grid, a, s):
         h, y, w, eps, x, H, cen = a
@@ -245,3 +259,7 @@ def btb_sample_draw(launcher, grid, block, x, keys, V, fp, gM, gpreK, gpreP, gbe
 
 def btb_sample_out(launcher, grid, block, gbest, out, R, *, stream=None, shared=0):
     launcher.launch("btb_sample_out", grid, block, [_P(gbest), _P(out), _I(R)], stream, shared)
+
+
+def btb_gemv_mma_bf16(launcher, grid, block, w, x, y, R, C_, M, *, stream=None, shared=0):
+    launcher.launch("btb_gemv_mma_bf16", grid, block, [_P(w), _P(x), _P(y), _I(R), _I(C_), _I(M)], stream, shared)

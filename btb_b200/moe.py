@@ -20,7 +20,7 @@ from typing import Any
 import torch
 
 from . import capi
-from .capi import call, ptr
+from .capi import ptr
 from .engine import CardEngine, DenseConfig, FP8Matrix, pad_rows
 
 FMT = {"bf16": 0, "mx4": 1, "fp8": 2}

@@ -85,3 +85,30 @@ def test_tc_gemv_refuses_bad_arguments():
     big = torch.zeros(2560, 4096, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(capi.NativeError):  # a matrix of few tiles needs the partial sums' workspace
         call("btb_b200_gemv_tc_bf16", ptr(big), ptr(big), ptr(big), 1, 2560, 4096, 0, 0)
+
+
+def test_launcher_serves_the_reference_mma_matvec():
+    """btb_gemv_mma_bf16 by the reference's name and parameter list: the library's tensor-core kernel and - where the
+    reference's kernels are built - the reference's own mma.sync kernel agree to rounding (two summation orders)"""
+    from btb_b200 import launcher as L
+
+    from . import refkernels
+
+    R, C_, M = 2560, 4096, 5
+    g = torch.Generator(device=DEV).manual_seed(3)
+    w = (torch.randn(R, C_, generator=g, device=DEV) * 0.05).bfloat16()
+    x = torch.zeros(32, C_, dtype=torch.bfloat16, device=DEV)
+    x[:M] = torch.randn(M, C_, generator=g, device=DEV).bfloat16()
+    y = torch.zeros(32, R, dtype=torch.bfloat16, device=DEV)
+    L.btb_gemv_mma_bf16(L.B200Launcher(), ((R + 63) // 64, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(), y.data_ptr(), R, C_, M)
+    torch.cuda.synchronize()
+    ref = x[:M].double() @ w.double().t()
+    assert float((y[:M].double() - ref).abs().max()) <= 2.0**-7 * float(ref.abs().max())
+    assert float(y[M:].float().abs().max()) == 0.0  # rows past M are not written
+    if not refkernels.available():
+        return
+    y2 = torch.zeros(32, R, dtype=torch.bfloat16, device=DEV)
+    L.btb_gemv_mma_bf16(refkernels.RefLauncher(), ((R + 63) // 64, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(),
+                        y2.data_ptr(), R, C_, M)  # fmt: skip
+    torch.cuda.synchronize()
+    assert float((y[:M].float() - y2[:M].float()).abs().max()) <= 2.0**-7 * float(ref.abs().max())
