@@ -42,3 +42,25 @@ def test_tree_is_parents_first_and_walk_follows_picks():
     assert walk([9, 0, 0, 0, 0, 3], g, ch) == [0, 5]
     assert chains_tree(chains, 2)[0] == [5, 6]
     assert chains_tree([], 8) == ([], [-1], [0], {})
+
+
+def test_host_sampling_keys_are_the_reference_keys():
+    """btb_b200.sampling.Sampling.key_for against key_for() values banked from the reference (sampling.npz)"""
+    import numpy as np
+
+    from btb_b200.sampling import Sampling
+
+    g = np.load(os.path.join(HERE, "golden", "sampling.npz"))
+    for a, seed in enumerate(g["key_seeds"]):
+        for b, pos in enumerate(g["key_pos"]):
+            s = Sampling(temperature=1.0, seed=int(seed))
+            assert s.key_for(int(pos)) == int(g["keys"][a][b])
+            assert s.key_for(int(pos), 3) == int(g["keys_salt3"][a][b])
+    assert Sampling().greedy and not Sampling(temperature=0.7).greedy
+    assert Sampling(temperature=1.0, top_k=5).masked and Sampling(temperature=1.0, top_p=0.9).masked
+    import pytest
+
+    with pytest.raises(ValueError):
+        Sampling(temperature=-1.0)
+    with pytest.raises(ValueError):
+        Sampling(temperature=1.0, top_p=1.5)
