@@ -258,6 +258,8 @@ class CardEngine:
             if self._tc_ws is None or self._tc_ws.numel() * 4 < need:
                 self._tc_ws = torch.zeros(max(need // 4, 4), dtype=torch.float32, device=self.dev)
             self._k("btb_b200_gemv_tc_bf16", ptr(W), ptr(x), ptr(y), M, R, C_, ptr(self._tc_ws), s)
+            if need:
+                self._n += 1  # the ordered sum of the K ranges is a launch of its own
             return
         if isinstance(W, P12Matrix):
             self._k("btb_b200_gemv_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),
