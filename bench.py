@@ -407,7 +407,8 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
                    if args.workload != "llama-70b" else f"{cfg.name}-shape bf16, batch 1, greedy decode over a "
                    f"{args.context or 32768}-row synthetic cache",
                    "parallelism": parallelism, "graph_steps": args.graph_steps, "step_kernel": args.step_kernel,
-                   "l2": "weights per step 8.0 GB > L2 126 MB (inputs larger than L2)", "pdl": args.pdl,
+                   "l2": f"weights per step {cfg.weight_bytes_per_token(storage) / 1e9:.1f} GB > L2 126 MB (inputs larger "
+                         "than L2)", "pdl": args.pdl,
                    "bytes_per_token": cfg.weight_bytes_per_token(storage)},
         "clocks": clk.summary(),
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
