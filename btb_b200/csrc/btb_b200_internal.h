@@ -14,7 +14,8 @@ struct B2Tuning {
     int x_smem_max;   // x is staged in shared memory when M * C * 2 is at most this
     int ctas_per_sm;  // GEMV CTAs an SM (the grid is persistent)
     int evict_first;  // weight copies carry an L2 evict-first hint
-    int pdl;          // programmatic stream serialization: bit 0 the GEMV launches, bit 1 the small kernels
+    int pdl;          // programmatic stream serialization: bit 0 the GEMV launches, bit 1 the step's small kernels,
+                      // bit 2 the MoE block's kernels (router, picked experts, activation, sum)
     int warps;        // warps a GEMV CTA for passes of one or two rows: 8 or 16
     int solo;         // under PDL a GEMV CTA claims an SM's shared memory for itself
     int moe_stream;   // the picked experts' matvecs through the streaming kernel (0: the plain 16-lane kernel)
@@ -27,7 +28,8 @@ B2Tuning& b2_tuning();
 int b2_sm_count();
 
 // one launch: `args` is the kernel's single by-value parameter struct
-// `kind`: 1 a GEMV, 2 one of the step's small kernels - the `pdl` tunable is a mask over the kinds
+// `kind`: 1 a GEMV, 2 one of the step's small kernels, 4 one of the MoE block's - the `pdl` tunable is a mask over the
+// kinds (0 never launches early)
 template <typename Args>
 static inline int b2_launch(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                             const Args& args, int kind = 2) {

@@ -479,15 +479,15 @@ extern "C" int btb_b200_moe_route(const void* logits, int ls, int E, int k, int 
     if (T <= 0 || E <= 0 || k <= 0 || k > E || k > ROUTE_MAX_K || ls < E || E > 8192 || (mode != 0 && mode != 1))
         return B2_ERR_DOMAIN;
     RouteArgs a{logits, ls, E, k, mode, f32_logits, static_cast<int*>(idx), static_cast<bf16*>(w)};
-    return b2_launch((const void*)moe_route, dim3(T), dim3(ROUTE_THREADS), (size_t)E * 4, static_cast<cudaStream_t>(stream), a);
+    return b2_launch((const void*)moe_route, dim3(T), dim3(ROUTE_THREADS), (size_t)E * 4, static_cast<cudaStream_t>(stream), a, 4);
 }
 
 static int lane16_launch(int fmt, const L16Args& a, int n_tasks, cudaStream_t s) {
     const dim3 grid((a.R + 7) / 8, n_tasks);
     switch (fmt) {
-        case L_BF16: return b2_launch((const void*)gemv_lane16<L_BF16>, grid, dim3(128), 0, s, a, 1);
-        case L_MX4: return b2_launch((const void*)gemv_lane16<L_MX4>, grid, dim3(128), 0, s, a, 1);
-        case L_FP8: return b2_launch((const void*)gemv_lane16<L_FP8>, grid, dim3(128), 0, s, a, 1);
+        case L_BF16: return b2_launch((const void*)gemv_lane16<L_BF16>, grid, dim3(128), 0, s, a, 4);
+        case L_MX4: return b2_launch((const void*)gemv_lane16<L_MX4>, grid, dim3(128), 0, s, a, 4);
+        case L_FP8: return b2_launch((const void*)gemv_lane16<L_FP8>, grid, dim3(128), 0, s, a, 4);
         default: return B2_ERR_DOMAIN;
     }
 }
@@ -562,7 +562,7 @@ extern "C" int btb_b200_moe_act(const void* gu, void* h, const void* bias, const
                static_cast<const int*>(idx), n, I, kind, alpha, limit};
     const long long tot = (long long)n * I;
     const int grid = (int)((tot + 255) / 256 < 1184 ? (tot + 255) / 256 : 1184);
-    return b2_launch((const void*)moe_act, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+    return b2_launch((const void*)moe_act, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a, 4);
 }
 
 extern "C" int btb_b200_moe_combine(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T,
@@ -571,7 +571,7 @@ extern "C" int btb_b200_moe_combine(const void* dn, const void* idx, const void*
     if (T <= 0 || k <= 0 || k > ROUTE_MAX_K || H <= 0) return B2_ERR_DOMAIN;
     CombineArgs a{static_cast<const float*>(dn), static_cast<const int*>(idx), static_cast<const bf16*>(w),
                   static_cast<const bf16*>(bias), static_cast<bf16*>(y), T, k, H};
-    return b2_launch((const void*)moe_combine, dim3((H + 255) / 256, T), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+    return b2_launch((const void*)moe_combine, dim3((H + 255) / 256, T), dim3(256), 0, static_cast<cudaStream_t>(stream), a, 4);
 }
 
 extern "C" int btb_b200_widen_f32(const void* x, void* y, int n, void* stream) {
@@ -579,7 +579,7 @@ extern "C" int btb_b200_widen_f32(const void* x, void* y, int n, void* stream) {
     if (n <= 0) return B2_ERR_DOMAIN;
     WidenArgs a{static_cast<const bf16*>(x), static_cast<float*>(y), n};
     const int grid = (n + 255) / 256 < 296 ? (n + 255) / 256 : 296;
-    return b2_launch((const void*)widen_f32, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
+    return b2_launch((const void*)widen_f32, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a, 4);
 }
 
 extern "C" int btb_b200_moe_combine_norm(const void* dn, const void* idx, const void* w, int k, void* h, const void* norm_w,
@@ -591,5 +591,5 @@ extern "C" int btb_b200_moe_combine_norm(const void* dn, const void* idx, const 
                       static_cast<float*>(xf), static_cast<bf16*>(y), eps, k, H, centered};
     static bool allowed[64];
     if (const int rc = b2_allow_smem((const void*)moe_combine_norm, allowed)) return rc;
-    return b2_launch((const void*)moe_combine_norm, dim3(T), dim3(256), (size_t)H * 4, static_cast<cudaStream_t>(stream), a);
+    return b2_launch((const void*)moe_combine_norm, dim3(T), dim3(256), (size_t)H * 4, static_cast<cudaStream_t>(stream), a, 4);
 }

@@ -383,7 +383,7 @@ int launch_stream_t(const MSArgs& a0, int n_tasks, cudaStream_t s) {
     static bool allowed[64];
     int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
     if (rc) return rc;
-    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.ctas, n_tasks), dim3(p.warps * 32), p.smem, s, a, 2);
+    return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.ctas, n_tasks), dim3(p.warps * 32), p.smem, s, a, 4);
 }
 
 template <int FMT>

@@ -14,6 +14,8 @@ writes zeros for the others; one all-reduce of the [T, k, H] f32 products a laye
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -174,7 +176,10 @@ class MoEEngine(CardEngine):
         super().__init__(weights, cap=cap, step_kernel=False, device=device)  # type: ignore[arg-type]
         self.group = group
         self.ep_rank, self.ep_size = weights.ep_rank, weights.ep_size
-        self.fold = True  # the activation inside the down matvecs' launch, the picks' sum inside the next norm's
+        # the activation inside the down matvecs' launch, the picks' sum inside the next norm's: fewer launches, the
+        # same bits, but measured slower than the separate kernels (one block a token sums the picks; every CTA of the
+        # down matvecs repeats the activation) - off unless asked for
+        self.fold = os.environ.get("BTB_B200_MOE_FOLD", "0") != "0"
 
     def bufs(self, M: int) -> dict[str, torch.Tensor]:
         g = super().bufs(M)

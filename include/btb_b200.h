@@ -32,7 +32,9 @@ extern "C" {
 
 int btb_b200_version(void);
 int btb_b200_sm_count(void);
-/* tunables: "ring_bytes", "seg_bytes", "x_smem_max", "ctas_per_sm", "evict_first", "pdl", "warps", "balance" (host string) */
+/* tunables: "ring_bytes", "seg_bytes", "x_smem_max", "ctas_per_sm", "evict_first", "pdl" (a mask: 1 the GEMV launches,
+ * 2 the step's small kernels, 4 the MoE block's kernels start under programmatic dependent launch; default 5), "warps",
+ * "balance", "solo", "moe_stream" (host string) */
 int btb_b200_set_tuning(const char* key, int value);
 /* reads the device status word into *code (host pointer) and clears it; synchronises the default stream's copy */
 int btb_b200_status(int* code);

@@ -260,7 +260,7 @@ def test_folded_moe_pass_equals_the_unfolded_pass(name):
     cfg = SMALL[name]
     mw = MO.synth_moe_weights(cfg, seed=3, on_cpu=True)
     a, b = MO.MoEEngine(mw, cap=512), MO.MoEEngine(mw, cap=512)
-    b.fold = False
+    a.fold, b.fold = True, False
     prompt = torch.arange(7, 40)
     la, lb = a.forward(prompt[:20]), b.forward(prompt[:20])
     assert torch.equal(la.view(torch.int16), lb.view(torch.int16))
