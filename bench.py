@@ -522,6 +522,44 @@ def run_case(args) -> None:
             e1.record()
             torch.cuda.synchronize()
         out.update(us_per_launch=e0.elapsed_time(e1) * 1000 / 20, cached_rows=n0v)
+    elif kind == "moe":
+        # the picked experts' gate/up matvecs of one MoE layer: moe:fp8 (Qwen3-30B-A3B shape, 8 picks of 128 experts)
+        # or moe:mx4 (gpt-oss-20b shape, 4 picks of 32); the picks rotate so that the rows come from DRAM
+        from btb_b200 import moe as MO
+
+        cfg = MO.QWEN3_30B_A3B if rest == "fp8" else MO.GPT_OSS_20B
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        st = MO.synth_expert_stack(cfg, gen, cfg.experts, 2 * cfg.inter, cfg.hidden, "cuda")
+        k, E = cfg.top_k, cfg.experts
+        rounds = max(2, E // k)
+        picks = [torch.arange(i * k, (i + 1) * k, dtype=torch.int32, device="cuda") % E for i in range(rounds)]
+        xf = torch.randn(1, cfg.hidden, device="cuda", generator=gen)
+        yv = torch.zeros(k, 2 * cfg.inter, device="cuda")
+        per = k * 2 * cfg.inter * cfg.hidden * {"fp8": 1.0, "mx4": 17 / 32, "bf16": 2.0}[st.fmt]
+        for it in range(3):
+            e0.record()
+            for idx in picks:
+                call("btb_b200_moe_gemv", MO.FMT[st.fmt], ptr(st.w), ptr(st.scales), st.w_stride, st.s_stride, st.sr, st.sc,
+                     ptr(idx), k, E, ptr(xf), k, ptr(yv), st.R, st.C, 0, 1, sp)  # fmt: skip
+            e1.record()
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1000 / rounds
+        out.update(us_per_launch=us, gbs=per / us / 1e3, bytes_per_launch=per, picks=k, experts=E)
+    elif kind == "sample":
+        V = int(rest)
+        from btb_b200.sampling import CardSampler, Sampling
+
+        smp = CardSampler("cuda")
+        smp.set(Sampling(temperature=0.8, top_k=40, top_p=0.9, seed=7))
+        lg = torch.randn(1, V, device="cuda").to(torch.bfloat16)
+        n0, tok = torch.zeros(1, dtype=torch.int32, device="cuda"), torch.zeros(1, dtype=torch.int64, device="cuda")
+        for it in range(3):
+            e0.record()
+            for _ in range(20):
+                smp.pick(lg, 1, n0, None, tok, sp)
+            e1.record()
+            torch.cuda.synchronize()
+        out.update(us_per_launch=e0.elapsed_time(e1) * 1000 / 20, vocab=V)
     else:
         raise SystemExit(f"unknown case {args.case}")
     assert capi.status() == 0
@@ -666,7 +704,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--batch", type=int, default=1, help="qwen3-4b workloads: sequences decoded side by side")
     ap.add_argument("--wide-tc", type=int, default=1, help="--batch: the tensor-core matvec for the pass of B rows")
-    ap.add_argument("--case", default="", help="one kernel on a small case: gemv:RxC[:M[:fmt]] or attn:N")
+    ap.add_argument("--case", default="", help="one kernel on a small case: gemv:RxC[:M[:fmt]], attn:N, moe:fp8|mx4, sample:V")
     ap.add_argument("--speculative", type=int, default=0, help="verify an n-gram tree of this many drafts a pass")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -93,7 +93,11 @@ struct SampleArgs {
 };
 
 struct Shared {
-    unsigned long long hist[2][SMP_BINS];  // this CTA's histogram of the level (two, so a level needs one barrier)
+    // this CTA's histogram of the level (two, so a level needs one barrier): a bin's 64-bit sum kept as two 32-bit words
+    // - the masses' low 16 bits and the rest - because 32-bit shared atomics are native and 64-bit ones are not, and
+    // a level's values crowd into a few bins (a CTA's eighth of a row cannot overflow either word)
+    unsigned lo[2][SMP_BINS];
+    unsigned hi[2][SMP_BINS];
     unsigned long long tot[SMP_BINS];      // the cluster's
     unsigned long long cs[64];
     unsigned long long best;
@@ -107,29 +111,35 @@ __device__ unsigned smp_select(cg::cluster_group& cl, Shared* S, const float* sv
                                float M, unsigned top_k, float top_p, int& gen) {
     const unsigned tid = threadIdx.x;
     for (int level = 0; level < 3; ++level, ++gen) {
-        unsigned long long* mine = S->hist[gen & 1];
+        unsigned* mine_lo = S->lo[gen & 1];
+        unsigned* mine_hi = S->hi[gen & 1];
         const unsigned bits = level < 2 ? 11u : 10u;
         const unsigned shift = level == 0 ? 21u : (level == 1 ? 10u : 0u), hi = shift + bits;
         const unsigned prefix = level == 0 ? 0u : S->pre;
-        for (unsigned b = tid; b < SMP_BINS; b += SMP_THREADS) mine[b] = 0ull;
+        for (unsigned b = tid; b < SMP_BINS; b += SMP_THREADS) mine_lo[b] = 0u, mine_hi[b] = 0u;
         __syncthreads();
         for (int i = tid; i < n; i += SMP_THREADS) {
             const float s = sv[i];
             const unsigned u = smp_ordered(s);
             if (u < floor) continue;
             if (hi < 32u && (u >> hi) != (prefix >> hi)) continue;
+            const unsigned bin = (u >> shift) & (SMP_BINS - 1);
             if (mode == 0) {
-                atomicAdd(&mine[(u >> shift) & (SMP_BINS - 1)], 1ull);
+                atomicAdd(&mine_lo[bin], 1u);
             } else if (s - M >= SMP_FLOOR) {
-                const unsigned long long w = (unsigned long long)__fmul_rn(smp_exp(__fsub_rn(s, M)), SMP_MASS);
-                if (w) atomicAdd(&mine[(u >> shift) & (SMP_BINS - 1)], w);
+                const unsigned w = (unsigned)__fmul_rn(smp_exp(__fsub_rn(s, M)), SMP_MASS);  // at most 2^30
+                if (w) {
+                    atomicAdd(&mine_lo[bin], w & 0xFFFFu);
+                    atomicAdd(&mine_hi[bin], w >> 16);
+                }
             }
         }
         cl.sync();  // every CTA's histogram of this level is whole
         for (unsigned b = tid; b < SMP_BINS; b += SMP_THREADS) {
             unsigned long long a = 0ull;
 #pragma unroll
-            for (int c = 0; c < SMP_CTAS; ++c) a += cl.map_shared_rank(mine, c)[b];
+            for (int c = 0; c < SMP_CTAS; ++c)
+                a += (unsigned long long)cl.map_shared_rank(mine_lo, c)[b] + ((unsigned long long)cl.map_shared_rank(mine_hi, c)[b] << 16);
             S->tot[b] = a;
         }
         __syncthreads();
