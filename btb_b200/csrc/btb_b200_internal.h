@@ -20,6 +20,7 @@ struct B2Tuning {
     int solo;         // under PDL a GEMV CTA claims an SM's shared memory for itself
     int moe_stream;   // the picked experts' matvecs through the streaming kernel (0: the plain 16-lane kernel)
     int ms_tpr;       // threads that share an expert row: 4, 8 or 16
+    int ms_ctas;      // CTAs of the expert kernel an SM holds (0: one for four threads a row, else two)
     int ms_seg, ms_warps;  // the expert kernel's columns a stage and warps a CTA (0: its own choice)
     int tc_stages, tc_ctas;  // the tensor-core matvec's ring depth and CTAs an SM its K split aims at (0: 4 and 2)
     int balance;      // pick the GEMV grid and warps a CTA so that the rows divide evenly over the warps

@@ -15,7 +15,7 @@ B2Tuning& b2_tuning() {
         env_int("BTB_B200_X_SMEM_MAX", 160 * 1024), env_int("BTB_B200_CTAS_PER_SM", 1),
         env_int("BTB_B200_EVICT_FIRST", 1),        env_int("BTB_B200_PDL", 5),
         env_int("BTB_B200_WARPS", 16),             env_int("BTB_B200_SOLO", 1),
-        env_int("BTB_B200_MOE_STREAM", 1),         env_int("BTB_B200_MS_TPR", 0),
+        env_int("BTB_B200_MOE_STREAM", 1),         env_int("BTB_B200_MS_TPR", 0),             env_int("BTB_B200_MS_CTAS", 0),
         env_int("BTB_B200_MS_SEG", 0),
         env_int("BTB_B200_MS_WARPS", 0),           env_int("BTB_B200_TC_STAGES", 0),
         env_int("BTB_B200_TC_CTAS", 0),

@@ -347,7 +347,9 @@ struct MSPlan {
 template <int FMT, int TPR>
 bool plan_stream(int n_tasks, int R, int C, MSPlan& p) {
     constexpr int RB = 32 / TPR;
-    const int per_sm = TPR == 4 ? 1 : 2;  // CTAs an SM holds
+    // CTAs an SM holds: two measured best for MXFP4 rows (half the bytes a column, so twice the arithmetic a byte), one
+    // for FP8 and bf16 rows at four threads a row
+    const int per_sm = b2_tuning().ms_ctas > 0 ? b2_tuning().ms_ctas : (TPR == 4 && FMT != S_MX4 ? 1 : 2);
     const int sms = b2_sm_count();
     const int groups = (R + RB - 1) / RB;
     p.ctas = max(1, min(groups, per_sm * sms / max(1, n_tasks)));  // CTAs that share a task
