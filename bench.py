@@ -202,7 +202,8 @@ def run_reference(args, rank: int) -> None:
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": min(args.warmup, 2), "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 activations over bf16 weights", "data": "synthetic",
-        "config": {"workload": "qwen3-4b-shape bf16, batch 1, greedy decode after a 128-token prompt (CPU tier)"},
+        "config": {"workload": f"{cfg.name}-shape bf16, batch 1, greedy decode after a 128-token prompt",
+                   "parallelism": "cpu tier, all host cores", "bytes_per_token": cfg.weight_bytes_per_token("bf16")},
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "port",
                          "sample": f"{steps} full decode steps, isa {O.isa()}"},
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
