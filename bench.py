@@ -1,6 +1,8 @@
 """Decode benchmark of the B200 hot path.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload qwen3-4b-bf16|qwen3-4b-p12]
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+                    [--workload qwen3-4b-bf16|qwen3-4b-p12|gpt-oss-20b|qwen3-30b-a3b|llama-70b]
+                    [--batch B [--wide-tc 0|1]] [--speculative N] [--case gemv:RxC[:M[:fmt]]|attn:N|moe:fp8|moe:mx4|sample:V]
 
 A step is one greedy decode step (one token) at batch 1 of the Qwen3-4B-shaped model with seeded random bf16 weights
 (N(0, 0.02), norm weights 1) after a 128-token uniform-random prompt: the configuration the metric is quoted on.
