@@ -80,6 +80,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_kv_commit": (_I, [_P, _P, _LL, _I, _P, _P, _I, _I, _LL, _P, _I, _P]),
     "btb_b200_publish": (_I, [_P, _P, _P, _P, _P, _I, _P]),
     "btb_b200_moe_route": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _I, _P]),
+    "btb_b200_moe_router": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
     "btb_b200_gemv_lane16_f32": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_lane16_mx4_f32": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_lane16_fp8_f32": (_I, [_P, _P, _I, _I, _P, _P, _I, _I, _I, _P]),

@@ -11,9 +11,13 @@
 // (btb/fp8.py:36-100) - widened in registers, no widened copy.
 #include <cuda_fp8.h>
 
+#include <cooperative_groups.h>
+
 #include "btb_b200_internal.h"
 
 B2_DEFINE_STATUS(moe)
+
+namespace cg = cooperative_groups;
 
 bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, const void* x,
                       int R, int C, int sr, int sc);
@@ -36,21 +40,15 @@ struct RouteArgs {
     int* idx;
     bf16* w;
 };
-__global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
-    extern __shared__ float pr[];  // [E]
+// the picks of one row from its E logits (`logit(e)`), by a block of ROUTE_THREADS threads; pr: E floats of shared memory
+template <typename Logit>
+__device__ __forceinline__ void route_row(Logit logit, int t, int E, int k, int mode, int* idx_out, bf16* w_out, float* pr) {
     __shared__ float red[ROUTE_THREADS];
     __shared__ int redi[ROUTE_THREADS];
     __shared__ float topv[ROUTE_MAX_K];
     __shared__ int topi[ROUTE_MAX_K];
-    pdl_launch_dependents();
-    pdl_wait();
-    const int t = blockIdx.x, tid = threadIdx.x, E = A.E, k = A.k;
-    auto logit = [&](int e) -> float {
-        if (A.f32_logits) return __ldcg(static_cast<const float*>(A.logits) + (size_t)t * A.ls + e);
-        const unsigned short u = __ldcg(static_cast<const unsigned short*>(A.logits) + (size_t)t * A.ls + e);
-        return __uint_as_float((uint32_t)u << 16);
-    };
-    if (A.mode == 0) {
+    const int tid = threadIdx.x;
+    if (mode == 0) {
         // the row's max (any order gives the same value)
         float m = NEG_INF;
         for (int e = tid; e < E; e += ROUTE_THREADS) m = fmaxf(m, logit(e));
@@ -154,12 +152,12 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
         }
     }
     if (tid == 0) {
-        if (A.mode == 0) {
+        if (mode == 0) {
             float sum = 0.f;
             for (int j = 0; j < k; ++j) sum += topv[j];
             for (int j = 0; j < k; ++j) {
-                A.idx[(size_t)t * k + j] = topi[j];
-                A.w[(size_t)t * k + j] = f2bf(topv[j] / sum);
+                idx_out[(size_t)t * k + j] = topi[j];
+                w_out[(size_t)t * k + j] = f2bf(topv[j] / sum);
             }
         } else {
             float m = topv[0], sum = 0.f, ex[ROUTE_MAX_K];
@@ -169,11 +167,90 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
                 sum += ex[j];
             }
             for (int j = 0; j < k; ++j) {
-                A.idx[(size_t)t * k + j] = topi[j];
-                A.w[(size_t)t * k + j] = f2bf(ex[j] / sum);
+                idx_out[(size_t)t * k + j] = topi[j];
+                w_out[(size_t)t * k + j] = f2bf(ex[j] / sum);
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
+    extern __shared__ float pr[];  // [E]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    auto logit = [&](int e) -> float {
+        if (A.f32_logits) return __ldcg(static_cast<const float*>(A.logits) + (size_t)t * A.ls + e);
+        const unsigned short u = __ldcg(static_cast<const unsigned short*>(A.logits) + (size_t)t * A.ls + e);
+        return __uint_as_float((uint32_t)u << 16);
+    };
+    route_row(logit, t, A.E, A.k, A.mode, A.idx, A.w, pr);
+}
+
+// ---- the router's matvec and the picks in one launch: a cluster of 8 CTAs a row ----------------------------------------
+// The router is a small matrix ([E, H] bf16: 0.5 MB for 128 experts) whose matvec and top-k were two dependent launches
+// of a few microseconds each, mostly launch latency. Here each CTA of the cluster takes an eighth of the experts' rows
+// (staged in shared memory by wide loads, multiplied in the host's 16-lane order: column c on lane c mod 16, pairwise
+// fold), writes its logits into the leader's shared memory through the cluster's distributed shared memory, and after
+// one cluster barrier the leader picks. The logits are btb_b200_gemv_lane16_f32's and the picks btb_b200_moe_route's.
+constexpr int RR_CTAS = 8;
+struct RouterArgs {
+    const bf16* w;   // [E, H]
+    const float* x;  // [T, H] f32
+    float* rl;       // [T, E] the logits, or null
+    int* idx;
+    bf16* wout;
+    int E, H, k, mode;
+};
+__global__ void __cluster_dims__(RR_CTAS, 1, 1) __launch_bounds__(ROUTE_THREADS) moe_router_route(const RouterArgs A) {
+    cg::cluster_group cl = cg::this_cluster();
+    extern __shared__ __align__(16) unsigned char rsm[];
+    const int E = A.E, H = A.H, tid = threadIdx.x;
+    const int rank = blockIdx.x, t = blockIdx.y;
+    float* xs = reinterpret_cast<float*>(rsm);                                  // [H]
+    float* lg = xs + H;                                                          // [E] (the leader's is the one read)
+    float* pr = lg + E;                                                          // [E]
+    const int wstride = H + 8;                                                   // bf16 elements: rows 16 bytes apart in banks
+    bf16* wrows = reinterpret_cast<bf16*>(rsm + ((((size_t)H + 2 * (size_t)E) * 4 + 15) & ~(size_t)15));  // [16][H + 8]
+    pdl_launch_dependents();
+    pdl_wait();
+    {
+        const float4* xg = reinterpret_cast<const float4*>(A.x + (size_t)t * H);
+        for (int i = tid; i < H / 4; i += ROUTE_THREADS) reinterpret_cast<float4*>(xs)[i] = __ldcg(xg + i);
+    }
+    const int per = (E + RR_CTAS - 1) / RR_CTAS;
+    const int r_lo = rank * per, r_hi = min(E, r_lo + per);
+    float* lg0 = cl.map_shared_rank(lg, 0);
+    for (int g0 = r_lo; g0 < r_hi; g0 += 16) {
+        const int nrow = min(16, r_hi - g0);
+        const int hv = H >> 3;
+        for (int i = tid; i < nrow * hv; i += ROUTE_THREADS) {
+            const int ri = i / hv, c8 = i - ri * hv;
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(A.w + (size_t)(g0 + ri) * H) + c8);
+            *reinterpret_cast<uint4*>(wrows + (size_t)ri * wstride + c8 * 8) = v;
+        }
+        __syncthreads();
+        const int ri = tid >> 4, j = tid & 15;
+        float acc = 0.f;
+        if (ri < nrow) {
+            const unsigned short* wr = reinterpret_cast<const unsigned short*>(wrows + (size_t)ri * wstride);
+#pragma unroll 8
+            for (int c = j; c < H; c += 16) acc = fmaf(__uint_as_float((unsigned)wr[c] << 16), xs[c], acc);
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+        if (ri < nrow && j == 0) {
+            lg0[g0 + ri] = acc;
+            if (A.rl != nullptr) A.rl[(size_t)t * E + g0 + ri] = acc;
+        }
+        __syncthreads();
+    }
+    cl.sync();  // every CTA's logits stand in the leader's shared memory
+    if (rank != 0) return;
+    auto logit = [&](int e) -> float { return lg[e]; };
+    route_row(logit, t, E, A.k, A.mode, A.idx, A.wout, pr);
 }
 
 // ---- the 16-lane matvec over stored weights ---------------------------------------------------------------------------
@@ -592,4 +669,23 @@ extern "C" int btb_b200_moe_combine_norm(const void* dn, const void* idx, const 
     static bool allowed[64];
     if (const int rc = b2_allow_smem((const void*)moe_combine_norm, allowed)) return rc;
     return b2_launch((const void*)moe_combine_norm, dim3(T), dim3(256), (size_t)H * 4, static_cast<cudaStream_t>(stream), a, 4);
+}
+
+// the router's matvec and the picks as one cluster launch; shapes it does not take (H not a multiple of 8, more than 1024
+// experts, unaligned pointers) are refused: use btb_b200_gemv_lane16_f32 and btb_b200_moe_route
+extern "C" int btb_b200_moe_router(const void* w, const void* x, void* logits, int E, int H, int k, int mode, void* idx,
+                                   void* wout, int T, void* stream) {
+    if (!w || !x || !idx || !wout) return B2_ERR_NULL;
+    if (T <= 0 || T > 65535 || E <= 0 || E > 1024 || k <= 0 || k > E || k > ROUTE_MAX_K || H <= 0 || (H & 7) ||
+        (mode != 0 && mode != 1))
+        return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return B2_ERR_DOMAIN;
+    const size_t smem = ((((size_t)H + 2 * (size_t)E) * 4 + 15) & ~(size_t)15) + 16 * ((size_t)H + 8) * 2;
+    if (smem > 200 * 1024) return B2_ERR_DOMAIN;
+    RouterArgs a{static_cast<const bf16*>(w), static_cast<const float*>(x), static_cast<float*>(logits),
+                 static_cast<int*>(idx), static_cast<bf16*>(wout), E, H, k, mode};
+    static bool allowed[64];
+    if (const int rc = b2_allow_smem((const void*)moe_router_route, allowed)) return rc;
+    return b2_launch((const void*)moe_router_route, dim3(RR_CTAS, T), dim3(ROUTE_THREADS), smem,
+                     static_cast<cudaStream_t>(stream), a, 4);
 }

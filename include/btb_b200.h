@@ -201,6 +201,12 @@ int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, voi
  * idx i32 [T,k], w bf16 [T,k]. */
 int btb_b200_moe_route(const void* logits, int ls, int E, int k, int mode, int f32_logits, void* idx, void* w, int T,
                        void* stream);
+/* the router's matvec (btb_gemv_lane16_f32_m*, btb_kernels.cu:1635-1700; the host's _Router, btb/engine/host.py:175-191)
+ * and btb_moe_route's picks as one launch: a cluster of 8 CTAs a row, the logits handed to the leader through
+ * distributed shared memory. w bf16 [E, H], x f32 [T, H], logits f32 [T, E] or null (written when given), idx i32 [T, k],
+ * wout bf16 [T, k]. The logits and the picks are the two calls' to the bit. H a multiple of 8, E <= 1024. */
+int btb_b200_moe_router(const void* w, const void* x, void* logits, int E, int H, int k, int mode, void* idx, void* wout,
+                        int T, void* stream);
 /* btb_gemv_lane16_f32_m{M} (btb_kernels.cu:1635-1682): the host's bf16 GEMV order on the card (16 lane sums a row,
  * column c to lane c mod 16, reduce16's fold: native/src/gemv.rs:46-58,85-123). w [R,C] bf16, x [M,C] f32, y [M,R]
  * f32; bit-equal to btb_gemv_bf16_rows. */

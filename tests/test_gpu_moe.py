@@ -268,3 +268,29 @@ def test_folded_moe_pass_equals_the_unfolded_pass(name):
     assert torch.equal(la.view(torch.int16), lb.view(torch.int16))
     assert torch.equal(a.K.view(torch.int16), b.K.view(torch.int16))
     assert a.generate_greedy(prompt, 8) == b.generate_greedy(prompt, 8)
+
+
+@pytest.mark.parametrize("E,H,k,mode", [(128, 2048, 8, 0), (32, 2880, 4, 1), (8, 256, 2, 0), (300, 512, 5, 1), (1024, 264, 8, 0),
+                                        (7, 64, 3, 1)])  # fmt: skip
+def test_router_cluster_launch_equals_matvec_then_route(E, H, k, mode):
+    """btb_b200_moe_router: the logits are the 16-lane matvec's bits, the picks and weights btb_b200_moe_route's"""
+    rng = np.random.default_rng(E + H)
+    T = 3
+    wb = O.f32_to_bits(rng.standard_normal((E, H)).astype(np.float32) * 0.05)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    wt = torch.from_numpy(wb.view(np.int16)).to(DEV)
+    xt = torch.from_numpy(x).to(DEV)
+    rl_a = torch.zeros(T, E, dtype=torch.float32, device=DEV)
+    idx_a, w_a = torch.zeros(T, k, dtype=torch.int32, device=DEV), torch.zeros(T, k, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_gemv_lane16_f32", ptr(wt), ptr(xt), ptr(rl_a), T, E, H, s())
+    call("btb_b200_moe_route", ptr(rl_a), E, E, k, mode, 1, ptr(idx_a), ptr(w_a), T, s())
+    rl_b = torch.zeros_like(rl_a)
+    idx_b, w_b = torch.zeros_like(idx_a), torch.zeros_like(w_a)
+    call("btb_b200_moe_router", ptr(wt), ptr(xt), ptr(rl_b), E, H, k, mode, ptr(idx_b), ptr(w_b), T, s())
+    torch.cuda.synchronize()
+    assert np.array_equal(rl_b.cpu().numpy().view(np.uint32), O.cpu_gemv_bf16(wb, x).view(np.uint32))
+    assert torch.equal(rl_a.view(torch.int32), rl_b.view(torch.int32))
+    assert torch.equal(idx_a, idx_b) and torch.equal(w_a.view(torch.int16), w_b.view(torch.int16))
+    idx_c, w_c = torch.zeros_like(idx_a), torch.zeros_like(w_a)
+    call("btb_b200_moe_router", ptr(wt), ptr(xt), 0, E, H, k, mode, ptr(idx_c), ptr(w_c), T, s())  # without the logits
+    assert torch.equal(idx_a, idx_c) and torch.equal(w_a.view(torch.int16), w_c.view(torch.int16))
