@@ -476,7 +476,7 @@ def run_case(args) -> None:
             if fmt == "p12":
                 from btb_b200 import pack12
 
-                w = E.P12Matrix(pack12.pack_bf16(w.cpu()), R, C_, "cuda")
+                w = E.P12Matrix(pack12.pack_bf16(w), R, C_, "cuda")
             ws.append(w)
         x = torch.randn(M, C_, device="cuda", generator=gen).to(torch.bfloat16)
         y = torch.zeros(M, R, device="cuda", dtype=torch.bfloat16)

@@ -50,6 +50,11 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_gemv_norm": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _P]),
     "btb_b200_gemv_norm_swiglu": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _P]),
     "btb_b200_p12_rows": (_I, [_P, _I, _I, _I, _P, _P]),
+    "btb_b200_p12_tiles": (_SZ, [_LL]),
+    "btb_b200_p12_hist": (_I, [_P, _LL, _P, _P]),
+    "btb_b200_p12_table": (_I, [C.POINTER(C.c_uint), C.POINTER(C.c_ubyte), C.POINTER(C.c_int)]),
+    "btb_b200_p12_encode": (_I, [_P, _LL, C.POINTER(C.c_ubyte), _I, _P, _P, _P, _P]),
+    "btb_b200_p12_escapes": (_I, [_P, _LL, C.POINTER(C.c_ubyte), _I, _P, _P, _P, _P]),
     "btb_b200_embed": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_add_rmsnorm": (_I, [_P, _P, _P, _F, _P, _I, _I, _I, _P]),
     "btb_b200_add_rmsnorm_wide": (_I, [_P, _P, _P, _F, _P, _P, _I, _I, _I, _P]),
@@ -92,6 +97,18 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_moe_act": (_I, [_P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
     "btb_b200_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_widen_f32": (_I, [_P, _P, _I, _P]),
+    "btb_b200_ngram_new": (_P, [_I, _I, _I]),
+    "btb_b200_ngram_free": (None, [_P]),
+    "btb_b200_ngram_extend": (_I, [_P, C.POINTER(C.c_longlong), _I]),
+    "btb_b200_ngram_length": (_I, [_P]),
+    "btb_b200_ngram_chains": (_I, [_P, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                   C.POINTER(C.c_int)]),
+    "btb_b200_chains_tree": (_I, [C.POINTER(C.c_int), C.POINTER(C.c_int), _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                  C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "btb_b200_ngram_tree": (_I, [_P, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                 C.POINTER(C.c_int)]),
+    "btb_b200_tree_walk": (_I, [C.POINTER(C.c_longlong), C.POINTER(C.c_int), C.POINTER(C.c_int), _I, C.POINTER(C.c_int),
+                                C.POINTER(C.c_int)]),
     "btb_b200_step": (_I, [_P, _I, _I, _I, _P]),
     "btb_b200_step_op_bytes": (_SZ, []),
     "btb_b200_step_args_bytes": (_SZ, []),

@@ -394,6 +394,7 @@ static int gemv_norm_impl(const void* w, const void* hi4, const void* table, con
     if (reinterpret_cast<uintptr_t>(norm_w) & 15) return B2_ERR_DOMAIN;  // read as 16-byte vectors
     const bool p12 = hi4 != nullptr;
     if (p12 && (table == nullptr || (C & 31) != 0 || (reinterpret_cast<uintptr_t>(hi4) & 15))) return B2_ERR_DOMAIN;
+    if (p12 && esc_row != nullptr && (esc_idx == nullptr || esc_val == nullptr)) return B2_ERR_NULL;
     GemvArgs a{};
     a.w = static_cast<const uint8_t*>(w);
     a.hi4 = static_cast<const uint8_t*>(hi4);

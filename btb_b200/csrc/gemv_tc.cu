@@ -211,11 +211,17 @@ int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, ui
 
 // K ranges a matrix is cut into: enough CTAs for two an SM, a whole number of K blocks each; a function of the
 // matrix's shape alone, so every pass width sums in the same order
-int tc_splits(int R, int C) {
+// `kps`: the K blocks a range holds. The count is recomputed from the rounded-up range length, so the last range is
+// never empty (14 wanted ranges over 64 blocks are 5 blocks each, which 13 ranges already cover): every slice of the
+// workspace that the ordered sum reads has been written by this launch.
+int tc_splits(int R, int C, int* kps = nullptr) {
     const int tiles = (R + TC_BM - 1) / TC_BM, kb = (C + TC_BK - 1) / TC_BK;
     const int per_sm = b2_tuning().tc_ctas > 0 ? b2_tuning().tc_ctas : 2;
     const int want = max(1, (per_sm * b2_sm_count()) / tiles);
-    return max(1, min(min(want, 16), kb / 4));
+    const int aim = max(1, min(min(want, 16), kb / 4));
+    const int per = (kb + aim - 1) / aim;
+    if (kps != nullptr) *kps = per;
+    return (kb + per - 1) / per;
 }
 
 }  // namespace
@@ -231,13 +237,13 @@ extern "C" int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int 
     if (!w || !x || !y) return B2_ERR_NULL;
     if (M < 1 || M > 32 || R <= 0 || C <= 0 || (C & 7)) return B2_ERR_DOMAIN;
     if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return B2_ERR_DOMAIN;
-    const int splits = tc_splits(R, C);
+    int kps = 0;
+    const int splits = tc_splits(R, C, &kps);
     if (splits > 1 && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15))) return B2_ERR_NULL;
     CUtensorMap tw, tx;
     if (make_map(&tw, w, (uint64_t)R, (uint64_t)C, TC_BM) || make_map(&tx, x, (uint64_t)M, (uint64_t)C, TC_BN)) return B2_ERR_CUDA;
-    const int total_kb = (C + TC_BK - 1) / TC_BK;
     const int stages = b2_tuning().tc_stages > 0 ? min(TC_STAGES_MAX, b2_tuning().tc_stages) : 4;
-    TcArgs a{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, (total_kb + splits - 1) / splits, splits, stages};
+    TcArgs a{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, kps, splits, stages};
     const int smem = stages * ST_BYTES + 1024;
     static bool allowed[64];
     int dev = 0;

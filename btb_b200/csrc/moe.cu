@@ -14,6 +14,7 @@
 #include <cooperative_groups.h>
 
 #include "btb_b200_internal.h"
+#include "moe_widen.cuh"
 
 B2_DEFINE_STATUS(moe)
 
@@ -44,7 +45,6 @@ struct RouteArgs {
 template <typename Logit>
 __device__ __forceinline__ void route_row(Logit logit, int t, int E, int k, int mode, int* idx_out, bf16* w_out, float* pr) {
     __shared__ float red[ROUTE_THREADS];
-    __shared__ int redi[ROUTE_THREADS];
     __shared__ float topv[ROUTE_MAX_K];
     __shared__ int topi[ROUTE_MAX_K];
     const int tid = threadIdx.x;
@@ -91,66 +91,34 @@ __device__ __forceinline__ void route_row(Logit logit, int t, int E, int k, int 
         for (int e = tid; e < E; e += ROUTE_THREADS) pr[e] = logit(e);
     }
     __syncthreads();
-    // k rounds of the total order's maximum (value descending, index ascending); a picked entry leaves the field
+    // k rounds of the total order's maximum (value descending, index ascending) on one warp, no block barriers: lane l
+    // scans entries l, l + 32, ..; a picked entry leaves the field by having its slot overwritten with a marker (a NaN
+    // payload no softmax produces), so any number of experts the shared row holds is served by the same loop
     constexpr int NONE = 0x7fffffff;
-    if (E <= 1024) {
-        // one warp, no block barriers: lane l owns entries l, l + 32, .. (a bit a taken entry)
-        if (tid < 32) {
-            unsigned taken = 0u;
-            for (int j = 0; j < k; ++j) {
-                float bv = 0.f;
-                int bi = NONE;
-                for (int e = tid, i = 0; e < E; e += 32, ++i) {
-                    if ((taken >> i) & 1u) continue;
-                    const float v = pr[e];
-                    if (bi == NONE || v > bv) bv = v, bi = e;  // e ascends: a tie keeps the lower index
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                    if (oi != NONE && (bi == NONE || ov > bv || (ov == bv && oi < bi))) bv = ov, bi = oi;
-                }
-                if (bi != NONE && (bi & 31) == tid) taken |= 1u << (bi >> 5);
-                if (tid == 0) topv[j] = bv, topi[j] = bi;
-            }
-        }
-        __syncthreads();
-    } else {
+    constexpr uint32_t PICKED = 0x7fc0b200u;
+    if (tid < 32) {
         for (int j = 0; j < k; ++j) {
             float bv = 0.f;
             int bi = NONE;
-            for (int e = tid; e < E; e += ROUTE_THREADS) {
-                bool taken = false;
-                for (int u = 0; u < j; ++u) taken |= topi[u] == e;
-                if (taken) continue;
+            for (int e = tid; e < E; e += 32) {
                 const float v = pr[e];
-                if (bi == NONE || v > bv) {  // e ascends within the thread: a tie keeps the lower index
-                    bv = v;
-                    bi = e;
-                }
+                if (__float_as_uint(v) == PICKED) continue;
+                if (bi == NONE || v > bv) bv = v, bi = e;  // e ascends: a tie keeps the lower index
             }
-            red[tid] = bv;
-            redi[tid] = bi;
-            __syncthreads();
-            for (int st = ROUTE_THREADS / 2; st > 0; st >>= 1) {
-                if (tid < st) {
-                    const float ov = red[tid + st];
-                    const int oi = redi[tid + st];
-                    if (oi != NONE && (redi[tid] == NONE || ov > red[tid] || (ov == red[tid] && oi < redi[tid]))) {
-                        red[tid] = ov;
-                        redi[tid] = oi;
-                    }
-                }
-                __syncthreads();
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != NONE && (bi == NONE || ov > bv || (ov == bv && oi < bi))) bv = ov, bi = oi;
             }
             if (tid == 0) {
-                topv[j] = red[0];
-                topi[j] = redi[0];
+                topv[j] = bv, topi[j] = bi;
+                if (bi != NONE) pr[bi] = __uint_as_float(PICKED);
             }
-            __syncthreads();
+            __syncwarp();
         }
     }
+    __syncthreads();
     if (tid == 0) {
         if (mode == 0) {
             float sum = 0.f;
@@ -267,40 +235,30 @@ struct L16Args {
     int ep_rank, ep_size;  // expert e lives on rank e % ep_size as its local expert e / ep_size; others' rows are zeros
 };
 
-__device__ __forceinline__ float mx4_scale(unsigned s) {
-    const float f = __uint_as_float((s == 0u ? 1u : s) << 23);
-    return s == 0u ? __fmul_rn(f, 0.5f) : f;
-}
-__device__ __forceinline__ float fp4_value(unsigned code) {
-    // e2m1: 0, .5, 1, 1.5, 2, 3, 4, 6 and their negatives, built as bf16 bit patterns: exponent field m >> 1 rebased
-    // to 127 and the mantissa bit m & 1 for the normals, 0.5 the one subnormal
-    const unsigned m = code & 7u;
-    const unsigned mag = m >= 2u ? ((((m >> 1) + 126u) << 7) | ((m & 1u) << 6)) : (m ? 0x3F00u : 0u);
-    return __uint_as_float((mag | ((code & 8u) << 12)) << 16);
-}
-// e4m3fn byte -> f32, built from its bits (native/src/gemv.rs:3010-3020)
-__device__ __forceinline__ float f8_value(unsigned b) {
-    const unsigned a = b & 0x7Fu;
-    float mag;
-    if (a == 0x7Fu) mag = __uint_as_float(0x7FC00000u);
-    else if (a < 8u) mag = __fmul_rn((float)a, 1.0f / 512.0f);
-    else mag = __uint_as_float((a << 20) + (120u << 23));
-    return __uint_as_float(__float_as_uint(mag) | ((b & 0x80u) << 24));
-}
-// to the nearest bf16, ties to even, by integer arithmetic as the reference rounds it (gemv.rs:3004-3008)
-__device__ __forceinline__ float round_bf16_int(float f) {
-    const unsigned b = __float_as_uint(f);
-    return __uint_as_float((b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u);
-}
-
-// a half-warp a row: lane j runs the chain of the columns c = j mod 16 in increasing c; the butterfly over xor 1, 2,
-// 4, 8 is reduce16's pairwise fold (each level adds the two partial sums reduce16 adds)
+// The matvec for the shapes the streaming kernel does not take (columns not a multiple of 32, rows that do not start on
+// 16 bytes): the same sixteen chains a row, four adjacent chains a thread and four threads a row as there, but every
+// weight fetched where it lies with an element-sized load and widened by `stored_weight`. A fallback for odd shapes,
+// not a fast path: the benchmark's shapes all stream.
 template <int FMT>
-__global__ void __launch_bounds__(128) gemv_lane16(const L16Args A) {
+__device__ __forceinline__ float stored_weight(const L16Args& A, const uint8_t* wbase, const uint8_t* sbase, int r, int c) {
+    if (FMT == L_BF16) {
+        return __uint_as_float((uint32_t)__ldg(reinterpret_cast<const unsigned short*>(wbase) + (size_t)r * A.C + c) << 16);
+    } else if (FMT == L_MX4) {
+        const int G = A.C >> 5, g = c >> 5, i = c & 31;
+        const uint32_t byte = __ldg(wbase + ((size_t)r * G + g) * 16 + (i >> 1));
+        return __fmul_rn(fp4_to_f32((byte >> ((i & 1) * 4)) & 15u), e8m0_to_f32(__ldg(sbase + (size_t)r * G + g)));
+    } else {
+        const int bm = A.R / A.sr, bn = A.C / A.sc;
+        const float sc = __ldg(reinterpret_cast<const float*>(sbase) + (size_t)(r / bm) * A.sc + c / bn);
+        return e4m3_held(__ldg(wbase + (size_t)r * A.C + c), sc);
+    }
+}
+template <int FMT>
+__global__ void __launch_bounds__(128) gemv_chains16(const L16Args A) {
     pdl_launch_dependents();
     pdl_wait();
-    const int j = threadIdx.x & 15;
-    const int r = blockIdx.x * 8 + (threadIdx.x >> 4);
+    const int q = threadIdx.x & 3;                       // the thread's chains 4 q .. 4 q + 3
+    const int r = blockIdx.x * 32 + (threadIdx.x >> 2);  // its row
     const int task = blockIdx.y;
     int e = 0;
     if (A.idx != nullptr) {
@@ -310,57 +268,28 @@ __global__ void __launch_bounds__(128) gemv_lane16(const L16Args A) {
             e = -1;
         }
     }
-    bool mine = true;
-    if (e >= 0 && A.ep_size > 1) {
+    bool mine = e >= 0;
+    if (mine && A.ep_size > 1) {
         mine = e % A.ep_size == A.ep_rank;
-        e = e / A.ep_size;
+        e /= A.ep_size;
     }
-    const int R = A.R, C = A.C;
-    const float* x = A.x + (size_t)(task / A.x_div) * C;
-    float acc = 0.f;
-    if (r < R && e >= 0 && mine) {
-        if (FMT == L_BF16) {
-            const unsigned short* wr = reinterpret_cast<const unsigned short*>(A.w + (size_t)e * A.w_stride) + (size_t)r * C;
-            int c = j;
-            for (; c + 48 < C; c += 64) {  // four of the lane's columns in flight, taken in order
-                float wv[4];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (r < A.R && mine) {
+        const uint8_t* wbase = A.w + (size_t)e * A.w_stride;
+        const uint8_t* sbase = A.scales != nullptr ? A.scales + (size_t)e * A.s_stride : nullptr;
+        const float* x = A.x + (size_t)(task / A.x_div) * A.C;
+        for (int c0 = 4 * q; c0 < A.C; c0 += 16) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) wv[k] = __uint_as_float((unsigned)__ldcs(wr + c + 16 * k) << 16);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) acc = fmaf(wv[k], __ldcg(x + c + 16 * k), acc);
-            }
-            for (; c < C; c += 16) acc = fmaf(__uint_as_float((unsigned)__ldcs(wr + c) << 16), __ldcg(x + c), acc);
-        } else if (FMT == L_MX4) {
-            const int G = C >> 5;
-            const unsigned char* br = A.w + (size_t)e * A.w_stride + (size_t)r * G * 16;
-            const unsigned char* sr = A.scales + (size_t)e * A.s_stride + (size_t)r * G;
-            const int sh = (j & 1) << 2;
-#pragma unroll 4
-            for (int g = 0; g < G; ++g) {
-                const float sc = mx4_scale((unsigned)__ldcs(sr + g));
-                const float w0 = __fmul_rn(fp4_value((__ldcs(br + g * 16 + (j >> 1)) >> sh) & 15u), sc);
-                const float w1 = __fmul_rn(fp4_value((__ldcs(br + g * 16 + 8 + (j >> 1)) >> sh) & 15u), sc);
-                const int c = g * 32 + j;
-                acc = fmaf(w0, __ldcg(x + c), acc);
-                acc = fmaf(w1, __ldcg(x + c + 16), acc);
-            }
-        } else {
-            const unsigned char* wr = A.w + (size_t)e * A.w_stride + (size_t)r * C;
-            const float* sg = reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride);
-            const int bm = R / A.sr, bn = C / A.sc;
-            const float* srow = sg + (size_t)(r / bm) * A.sc;
-#pragma unroll 4
-            for (int c = j; c < C; c += 16) {
-                const float w = round_bf16_int(__fmul_rn(f8_value((unsigned)__ldcs(wr + c)), __ldg(srow + c / bn)));
-                acc = fmaf(w, __ldcg(x + c), acc);
-            }
+            for (int u = 0; u < 4; ++u)
+                if (c0 + u < A.C) acc[u] = fmaf(stored_weight<FMT>(A, wbase, sbase, r, c0 + u), __ldcg(x + c0 + u), acc[u]);
         }
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-    if (r < R && j == 0 && e >= 0) A.y[(size_t)task * R + r] = acc;  // zeros for another rank's expert
+    // the pairwise fold of the sixteen sums: neighbours, pairs of neighbours (both inside the thread), then across the
+    // row's four threads
+    float s = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if (r < A.R && q == 0 && e >= 0) A.y[(size_t)task * A.R + r] = s;  // zeros for another rank's expert
 }
 
 // ---- between the two matvecs: the row dtype, the bias, the gated activation, back to f32 -------------------------------
@@ -560,11 +489,16 @@ extern "C" int btb_b200_moe_route(const void* logits, int ls, int E, int k, int 
 }
 
 static int lane16_launch(int fmt, const L16Args& a, int n_tasks, cudaStream_t s) {
-    const dim3 grid((a.R + 7) / 8, n_tasks);
+    if (n_tasks > 65535) return B2_ERR_DOMAIN;
+    // every shape the streaming kernel takes goes there (one task a pass row for the plain matvec entry points)
+    if (b2_tuning().moe_stream && b2_moe_stream_ok(fmt, a.w, a.scales, a.w_stride, a.s_stride, a.x, a.R, a.C, a.sr, a.sc))
+        return b2_moe_stream_launch(fmt, a.w, a.scales, a.w_stride, a.s_stride, a.sr, a.sc, a.idx, n_tasks, a.E, a.x, a.x_div,
+                                    a.y, a.R, a.C, a.ep_rank, a.ep_size, -1, 0.f, 0.f, s);
+    const dim3 grid((a.R + 31) / 32, n_tasks);
     switch (fmt) {
-        case L_BF16: return b2_launch((const void*)gemv_lane16<L_BF16>, grid, dim3(128), 0, s, a, 4);
-        case L_MX4: return b2_launch((const void*)gemv_lane16<L_MX4>, grid, dim3(128), 0, s, a, 4);
-        case L_FP8: return b2_launch((const void*)gemv_lane16<L_FP8>, grid, dim3(128), 0, s, a, 4);
+        case L_BF16: return b2_launch((const void*)gemv_chains16<L_BF16>, grid, dim3(128), 0, s, a, 4);
+        case L_MX4: return b2_launch((const void*)gemv_chains16<L_MX4>, grid, dim3(128), 0, s, a, 4);
+        case L_FP8: return b2_launch((const void*)gemv_chains16<L_FP8>, grid, dim3(128), 0, s, a, 4);
         default: return B2_ERR_DOMAIN;
     }
 }
@@ -605,10 +539,7 @@ extern "C" int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, lon
         return B2_ERR_DOMAIN;
     if (fmt == L_MX4 && (C & 31)) return B2_ERR_DOMAIN;
     if (fmt == L_FP8 && (sr <= 0 || sc <= 0 || R % sr || C % sc)) return B2_ERR_DOMAIN;
-    // the streaming kernel takes every shape whose rows start on 16 bytes; the rest keep the plain 16-lane kernel
-    if (b2_tuning().moe_stream && n_tasks <= 65535 && b2_moe_stream_ok(fmt, w, scales, w_stride, s_stride, x, R, C, sr, sc))
-        return b2_moe_stream_launch(fmt, w, scales, w_stride, s_stride, sr, sc, idx, n_tasks, E, x, x_div, y, R, C, ep_rank,
-                                    ep_size, -1, 0.f, 0.f, static_cast<cudaStream_t>(stream));
+    // the streaming kernel takes every shape whose rows start on 16 bytes; the rest take the element-load kernel
     L16Args a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), w_stride, s_stride,
               static_cast<const int*>(idx), static_cast<const float*>(x), x_div, static_cast<float*>(y), R, C,
               sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size};

@@ -13,6 +13,7 @@
 #include <cuda_fp8.h>
 
 #include "btb_b200_internal.h"
+#include "moe_widen.cuh"
 
 B2_DEFINE_STATUS(moes)
 
@@ -69,16 +70,6 @@ __device__ __forceinline__ void fp4x4_bf16(uint32_t codes, uint32_t& p01, uint32
 
 template <int FMT>
 __host__ __device__ constexpr int col_bytes2() { return FMT == S_BF16 ? 4 : FMT == S_FP8 ? 2 : 1; }  // twice a column's bytes
-
-__device__ __forceinline__ float mx4_scale_s(unsigned s) {
-    const float f = __uint_as_float((s == 0u ? 1u : s) << 23);
-    return s == 0u ? __fmul_rn(f, 0.5f) : f;
-}
-__device__ __forceinline__ float fp4_value_s(unsigned code) {
-    const unsigned m = code & 7u;
-    const unsigned mag = m >= 2u ? ((((m >> 1) + 126u) << 7) | ((m & 1u) << 6)) : (m ? 0x3F00u : 0u);
-    return __uint_as_float((mag | ((code & 8u) << 12)) << 16);
-}
 
 // TPR threads share a row, each running CPT = 16 / TPR adjacent chains; a warp takes RB = 32 / TPR rows at a time
 template <int FMT, int TPR>
@@ -248,7 +239,7 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
 #pragma unroll 4
             for (int b = 0; b < nb; ++b) {
                 const unsigned pk = __shfl_sync(0xffffffffu, mxs, (lane / TPR) * TPR + b / SPT);
-                const float sc = mx4_scale_s((pk >> ((b % SPT) * 8)) & 255u);
+                const float sc = e8m0_to_f32((pk >> ((b % SPT) * 8)) & 255u);
                 // the block's 16 bytes: byte i holds columns 2i (low nibble) and 2i + 1 of its first 16 columns,
                 // byte 8 + i the same of its last 16
                 const uint8_t* bp = srowp + b * 16;
@@ -280,8 +271,8 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
                     acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(b01), sc), vb.y, acc[1 % CPT]);
                 } else {
                     const int sh = (q & 1) << 2;
-                    acc[0] = fmaf(__fmul_rn(fp4_value_s((bp[q >> 1] >> sh) & 15u), sc), *xa, acc[0]);
-                    acc[0] = fmaf(__fmul_rn(fp4_value_s((bp[8 + (q >> 1)] >> sh) & 15u), sc), *xb, acc[0]);
+                    acc[0] = fmaf(__fmul_rn(fp4_to_f32((bp[q >> 1] >> sh) & 15u), sc), *xa, acc[0]);
+                    acc[0] = fmaf(__fmul_rn(fp4_to_f32((bp[8 + (q >> 1)] >> sh) & 15u), sc), *xb, acc[0]);
                 }
             }
         } else {

@@ -9,6 +9,7 @@ gathered to the front. The tokens are therefore exactly the greedy loop's; only 
 
 from __future__ import annotations
 
+import ctypes as C
 from collections.abc import Iterable, Sequence
 from typing import Any
 
@@ -19,93 +20,95 @@ from .capi import call, ptr
 
 
 class NGramProposer:
-    """per order n in [n_min, n_max]: each n-gram's followers with their count and the position after the latest
-    occurrence (btb/draft.py:8-74)"""
+    """the library's n-gram index behind btb's proposer interface (btb/draft.py:8-113): `extend(token)` and
+    `propose_chains(v)` -> [(tokens, "ngram<order>"), ...]"""
 
     def __init__(self, corpus_ids: Iterable[int], n_max: int = 4, n_min: int = 2, followers: int = 4) -> None:
-        self.corpus: list[int] = []
+        L = capi.lib()
+        self._h = L.btb_b200_ngram_new(int(n_max), int(n_min), int(followers))
+        if not self._h:
+            raise ValueError(f"n-gram orders {n_min}..{n_max} are not served")
+        self._free = L.btb_b200_ngram_free
         self.n_max, self.n_min, self.followers = n_max, n_min, max(1, int(followers))
-        self.maps: dict[int, dict[tuple[int, ...], dict[int, list[int]]]] = {n: {} for n in range(n_min, n_max + 1)}
-        for t in corpus_ids:
-            self.extend(int(t))
+        ids = [int(t) for t in corpus_ids]
+        if ids:
+            call("btb_b200_ngram_extend", self._h, (C.c_longlong * len(ids))(*ids), len(ids))
+
+    def __del__(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._free(h)
+
+    def __len__(self) -> int:
+        return int(capi.lib().btb_b200_ngram_length(self._h))
 
     def extend(self, tok: int) -> None:
-        self.corpus.append(tok)
-        hi = len(self.corpus)
-        for n in range(self.n_min, self.n_max + 1):
-            i = hi - n - 1
-            if i >= 0:
-                key = tuple(self.corpus[i : i + n])
-                slot = self.maps[n].setdefault(key, {})
-                e = slot.get(tok)
-                if e is None:
-                    slot[tok] = [1, i + n]
-                else:
-                    e[0] += 1
-                    e[1] = i + n
-
-    def _followers(self, n: int, key: tuple[int, ...]) -> list[tuple[int, int]]:
-        d = self.maps[n].get(key)
-        if not d:
-            return []
-        return sorted(((c, p) for c, p in d.values()), reverse=True)[: self.followers]
+        call("btb_b200_ngram_extend", self._h, (C.c_longlong * 1)(int(tok)), 1)
 
     def propose_chains(self, v: int) -> list[tuple[list[int], str]]:
-        """distinct continuations of up to v tokens: longest order first, most frequent follower first; a chain equal
-        to or a prefix of an earlier one is dropped (btb/draft.py:76-97)"""
-        out: list[tuple[list[int], str]] = []
+        """distinct continuations of the text's tail, up to v tokens each: longest order first, most frequent follower
+        first; a chain equal to or a prefix of an earlier one is dropped"""
+        most = (self.n_max - self.n_min + 1) * self.followers
         if v <= 0:
-            return out
-        for n in range(self.n_max, self.n_min - 1, -1):
-            if len(self.corpus) < n:
-                continue
-            key = tuple(self.corpus[-n:])
-            for _c, at in self._followers(n, key):
-                c = self.corpus[at : at + v]
-                if c and not any(o[: len(c)] == c for o, _ in out):
-                    out.append((list(c), f"ngram{n}"))
-        return out
+            return []
+        toks, offs, order = (C.c_int * (most * v))(), (C.c_int * (most + 1))(), (C.c_int * most)()
+        n = C.c_int(0)
+        call("btb_b200_ngram_chains", self._h, int(v), most, toks, offs, order, C.byref(n))
+        return [(list(toks[offs[c] : offs[c + 1]]), f"ngram{order[c]}") for c in range(n.value)]
+
+    def tree(self, v: int, budget: int) -> tuple[list[int], list[int], list[int]]:
+        """`propose_chains(v)` merged into a tree of at most `budget` guesses, in one call: (guesses, parents, depth)"""
+        g, par, dep = (C.c_int * max(budget, 1))(), (C.c_int * (budget + 1))(), (C.c_int * (budget + 1))()
+        n = C.c_int(0)
+        call("btb_b200_ngram_tree", self._h, int(v), int(budget), g, par, dep, C.byref(n))
+        return list(g[: n.value]), list(par[: n.value + 1]), list(dep[: n.value + 1])
 
 
 def chains_tree(chains: Sequence[tuple[Sequence[int], str]], budget: int):
-    """chains merged by shared prefix: node 0 the root, node j > 0 carrying guesses[j - 1]; (guesses, parents, depth,
-    children), at most `budget` guesses (btb/engine/generate.py:94-117)"""
-    guesses: list[int] = []
-    parents, depth = [-1], [0]
-    children: dict[int, list[int]] = {}
+    """chains merged by shared prefix (btb/engine/generate.py:94-117): node 0 the root, node j > 0 carrying
+    guesses[j - 1]; (guesses, parents, depth, children), at most `budget` guesses. Takes any proposer's chains - the
+    reference's own `NGramProposer.propose_chains` output included."""
+    flat = [int(t) for toks, _tag in chains for t in toks]
+    offs = [0]
     for toks, _tag in chains:
-        node = 0
-        for d, t in enumerate(toks):
-            t = int(t)
-            nxt = next((c for c in children.get(node, []) if guesses[c - 1] == t), None)
-            if nxt is None:
-                if len(guesses) >= budget:
-                    break
-                nxt = len(guesses) + 1
-                guesses.append(t)
-                parents.append(node)
-                depth.append(d + 1)
-                children.setdefault(node, []).append(nxt)
-            node = nxt
-    return guesses, parents, depth, children
+        offs.append(offs[-1] + len(toks))
+    g, par, dep = (C.c_int * max(budget, 1))(), (C.c_int * (budget + 1))(), (C.c_int * (budget + 1))()
+    n = C.c_int(0)
+    call("btb_b200_chains_tree", (C.c_int * max(len(flat), 1))(*flat), (C.c_int * len(offs))(*offs), len(chains),
+         int(budget), g, par, dep, C.byref(n))  # fmt: skip
+    guesses, parents, depth = list(g[: n.value]), list(par[: n.value + 1]), list(dep[: n.value + 1])
+    return guesses, parents, depth, children_of(parents)
+
+
+def children_of(parents: Sequence[int]) -> dict[int, list[int]]:
+    """each node's children in node order, from the parents list"""
+    children: dict[int, list[int]] = {}
+    for j, p in enumerate(parents):
+        if p >= 0:
+            children.setdefault(p, []).append(j)
+    return children
 
 
 def walk(picks: Sequence[int], guesses: Sequence[int], children: dict[int, list[int]]) -> list[int]:
-    """the accepted branch: from the root, the child whose guess is the node's own pick, as long as there is one
-    (btb/engine/generate.py:765-795)"""
-    node, path = 0, [0]
-    while True:
-        nxt = next((c for c in children.get(node, []) if guesses[c - 1] == picks[node]), None)
-        if nxt is None:
-            return path
-        node = nxt
-        path.append(nxt)
+    """the accepted branch (btb/engine/generate.py:765-795): from the root, the child whose guess is the node's own pick,
+    as long as there is one"""
+    n = 1 + len(guesses)
+    parents = [-1] * n
+    for p, cs in children.items():
+        for c in cs:
+            parents[c] = int(p)
+    path, m = (C.c_int * n)(), C.c_int(0)
+    call("btb_b200_tree_walk", (C.c_longlong * n)(*[int(t) for t in picks[:n]]), (C.c_int * max(n - 1, 1))(*guesses),
+         (C.c_int * n)(*parents), n, path, C.byref(m))  # fmt: skip
+    return list(path[: m.value])
 
 
 def generate_speculative(eng: Any, prompt: Any, max_new: int, budget: int = 8, v_max: int = 8,
-                         events: Any = None) -> tuple[list[int], dict]:
+                         events: Any = None, proposer: Any = None) -> tuple[list[int], dict]:
     """greedy decode with n-gram tree drafts; returns (tokens, stats). The tokens are the plain greedy loop's.
-    events: a pair of CUDA events recorded after the prefill's pick and after the last commit (the decode alone)."""
+    events: a pair of CUDA events recorded after the prefill's pick and after the last commit (the decode alone).
+    proposer: a factory `proposer(ids) -> object with extend(token) and propose_chains(v)` - btb's own
+    `btb.draft.NGramProposer` fits as it is; None: the library's native index."""
     prompt = [int(t) for t in torch.as_tensor(prompt).tolist()]
     eng.reset()
     last = eng.prefill(torch.tensor(prompt))
@@ -114,7 +117,7 @@ def generate_speculative(eng: Any, prompt: Any, max_new: int, budget: int = 8, v
     eng._pick({"logits": last.contiguous(), "pick": g1["pick"], "depth": eng._before}, 1, s, g1["tok"])
     cur = int(g1["tok"][0].item())
     toks = [cur]
-    prop = NGramProposer(prompt + [cur])
+    prop = (proposer or NGramProposer)(prompt + [cur])
     passes = 0
     if events is not None:
         events[0].record()

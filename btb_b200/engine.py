@@ -80,7 +80,8 @@ class P12Matrix:
         self.rows, self.cols = rows, cols
         as_t = lambda a, dt: torch.as_tensor(a, dtype=dt).to(device).contiguous()  # noqa: E731
         self.lo, self.hi4 = as_t(lo, torch.uint8), as_t(hi4, torch.uint8)
-        self.table = bytes(bytearray(int(v) for v in table))  # 16 bytes, host: it travels in the launch's arguments
+        # 16 bytes, host: it travels in the launch's arguments
+        self.table = bytes(table) if isinstance(table, (bytes, bytearray)) else bytes(bytearray(int(v) for v in table))
         self.n_esc = int(len(esc_idx))
         self.esc_idx = as_t(esc_idx, torch.int32) if self.n_esc else None
         self.esc_val = as_t(esc_val, torch.uint8) if self.n_esc else None
@@ -129,17 +130,21 @@ class ModelWeights:
 
 
 def synth_weights(cfg: DenseConfig, seed: int = 0, device: Any = "cuda", storage: str = "bf16",
-                  on_cpu: bool = False) -> ModelWeights:  # fmt: skip
+                  on_cpu: bool = False, layer_std: float = 0.02) -> ModelWeights:  # fmt: skip
     """random-init weights of the config's shapes: linears bf16 N(0, 0.02), norm weights 1.0, in a fixed tensor order
     (embed; per layer q, k, v, o, gate, up, down). `on_cpu` draws with the CPU generator (small configs whose weights
-    the CPU oracle must share); otherwise on the device. storage "p12" encodes every layer linear with pack12."""
+    the CPU oracle must share); otherwise on the device. storage "p12" encodes every layer linear with pack12.
+    `layer_std` is the layers' linears' deviation (the embedding keeps 0.02): a few narrow layers drawn at 0.02 leave
+    the residual stream the embedding plus noise and greedy decoding repeats one token, so small test models draw
+    theirs wider."""
     from . import pack12
 
     gdev = "cpu" if on_cpu else device
     g = torch.Generator(device=gdev).manual_seed(seed)
+    std = [0.02]
 
     def lin(r: int, c: int) -> torch.Tensor:
-        return (torch.randn(r, c, generator=g, device=gdev, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(device)
+        return (torch.randn(r, c, generator=g, device=gdev, dtype=torch.float32) * std[0]).to(torch.bfloat16).to(device)
 
     def ones(n: int) -> torch.Tensor:
         return torch.ones(n, dtype=torch.bfloat16, device=device)
@@ -151,6 +156,7 @@ def synth_weights(cfg: DenseConfig, seed: int = 0, device: Any = "cuda", storage
 
     H, D = cfg.hidden, cfg.head_dim
     mw = ModelWeights(cfg, lin(cfg.vocab, H), ones(H))
+    std[0] = layer_std
     for _ in range(cfg.layers):
         q, k, v = lin(cfg.q_heads * D, H), lin(cfg.kv_heads * D, H), lin(cfg.kv_heads * D, H)
         o = lin(H, cfg.q_heads * D)

@@ -123,15 +123,17 @@ def synth_expert_stack(cfg: MoEConfig, g: torch.Generator, n: int, R: int, C_: i
 
 
 def synth_moe_weights(cfg: MoEConfig, seed: int = 0, device: Any = "cuda", on_cpu: bool = False, ep_rank: int = 0,
-                      ep_size: int = 1) -> MoEWeights:  # fmt: skip
+                      ep_size: int = 1, layer_std: float = 0.02) -> MoEWeights:  # fmt: skip
     """random-init weights: attention, router, embedding bf16 N(0, 0.02); norm weights 1; experts as
     `synth_expert_stack`. Under expert parallelism every rank draws the same stream and keeps expert e iff
-    e % ep_size == ep_rank, so the model is the same model at every N."""
+    e % ep_size == ep_rank, so the model is the same model at every N. `layer_std`: the deviation of the
+    layers' bf16 linears (attention, router), as in `engine.synth_weights`."""
     gdev = "cpu" if on_cpu else device
     g = torch.Generator(device=gdev).manual_seed(seed)
+    std = [0.02]
 
     def lin(r: int, c: int) -> torch.Tensor:
-        return (torch.randn(r, c, generator=g, device=gdev, dtype=torch.float32) * 0.02).to(torch.bfloat16).to(device)
+        return (torch.randn(r, c, generator=g, device=gdev, dtype=torch.float32) * std[0]).to(torch.bfloat16).to(device)
 
     def ones(n: int) -> torch.Tensor:
         return torch.ones(n, dtype=torch.bfloat16, device=device)
@@ -155,6 +157,7 @@ def synth_moe_weights(cfg: MoEConfig, seed: int = 0, device: Any = "cuda", on_cp
 
     H, D, I, E = cfg.hidden, cfg.head_dim, cfg.inter, cfg.experts
     mw = MoEWeights(cfg, lin(cfg.vocab, H), ones(H), ep_rank=ep_rank, ep_size=ep_size)
+    std[0] = layer_std
     for _ in range(cfg.layers):
         if cfg.dense_fmt == "bf16":
             qkv = torch.cat([lin(cfg.q_heads * D, H), lin(cfg.kv_heads * D, H), lin(cfg.kv_heads * D, H)])

@@ -93,6 +93,22 @@ int btb_b200_gemv_norm_swiglu(const void* w, const void* hi4, const void* table,
 /* esc_row[r] = lower_bound(esc_idx, r * C) for r in 0..R (the CPU kernel's per-row cursor, native/src/gemv.rs:720-735,
  * computed once at load instead of per call) */
 int btb_b200_p12_rows(const void* esc_idx, int n_esc, int R, int C, void* esc_row, void* stream);
+/* pack12's encoder (btb/pack12.py:48-68 `pack_bf16`) on the card, for a bf16 tensor [n] that already lies in device
+ * memory; the parts are byte-identical to that encoder's. Four calls:
+ *   _hist    counts the high bytes into hist (u32 [256], device; cleared by the call);
+ *   _table   (host only, no device work) picks the table from the counts copied to the host: the 15 most frequent high
+ *            bytes, by count descending and byte value ascending, unused slots 0; *n_codes = slots in use;
+ *   _encode  writes lo [n] and hi4 [ceil(n/2)] (even element in the low nibble, an odd count's pad nibble 0) and leaves
+ *            in tile_esc (i32 [btb_b200_p12_tiles(n) + 1]) each tile's first escape's position in the list, the total last;
+ *   _escapes writes the escapes' ascending indices (i32) and high bytes from those offsets.
+ * n at most 2^31 - 1 (escape indices are int32). */
+size_t btb_b200_p12_tiles(long long n);
+int btb_b200_p12_hist(const void* src, long long n, void* hist, void* stream);
+int btb_b200_p12_table(const unsigned* hist_host, unsigned char* table16_host, int* n_codes);
+int btb_b200_p12_encode(const void* src, long long n, const unsigned char* table16_host, int n_codes, void* lo, void* hi4,
+                        void* tile_esc, void* stream);
+int btb_b200_p12_escapes(const void* src, long long n, const unsigned char* table16_host, int n_codes,
+                         const void* tile_off, void* esc_idx, void* esc_val, void* stream);
 
 /* ---- the step's small kernels ------------------------------------------------------------------------------------ */
 
@@ -190,6 +206,28 @@ int btb_b200_sample_keys(const void* seed, const void* pos, unsigned salt, void*
  * (path[j] >= j; else refused through the status word). n0 is not advanced here (btb_b200_publish does). */
 int btb_b200_kv_commit(void* K, void* V, long long layer_stride, int layers, const void* n0p, const void* path, int len,
                        int row_el, long long rs, const void* tbl, int cap, void* stream);
+/* ---- drafting, host side (no device work, no stream) ----------------------------------------------------------------
+ * btb's n-gram proposer (btb/draft.py:8-113 `NGramProposer`): for each order n in [n_min, n_max] every n-gram of the
+ * text remembers its followers, how often and where last. _new returns a handle (null: orders not served), _extend
+ * appends tokens, _free releases. */
+void* btb_b200_ngram_new(int n_max, int n_min, int followers);
+void btb_b200_ngram_free(void* proposer);
+int btb_b200_ngram_extend(void* proposer, const long long* toks, int n);
+int btb_b200_ngram_length(void* proposer);
+/* `propose_chains(v)` (btb/draft.py:76-97): continuations of the text's tail of up to v tokens, longest order first, most
+ * frequent then most recent follower first, a chain that is a prefix of an earlier one dropped. Chain c is
+ * toks[offs[c] .. offs[c + 1]) found at order[c]; toks holds max_chains * v, offs max_chains + 1, order max_chains. */
+int btb_b200_ngram_chains(void* proposer, int v, int max_chains, int* toks, int* offs, int* order, int* n_chains);
+/* `_chains_tree` (btb/engine/generate.py:94-117): chains merged by shared prefix into a tree of at most `budget` guesses;
+ * node 0 is the root, node j > 0 carries guesses[j - 1]; parents and depth hold budget + 1, parents first. */
+int btb_b200_chains_tree(const int* toks, const int* offs, int n_chains, int budget, int* guesses, int* parents, int* depth,
+                         int* n_guesses);
+/* btb_b200_ngram_chains then btb_b200_chains_tree in one call */
+int btb_b200_ngram_tree(void* proposer, int v, int budget, int* guesses, int* parents, int* depth, int* n_guesses);
+/* the accept walk of a verify pass (btb/engine/generate.py:765-795): from the root, the child whose guess is its parent's
+ * own pick, while there is one. picks i64 [n_nodes], guesses [n_nodes - 1], parents [n_nodes]; path holds n_nodes. */
+int btb_b200_tree_walk(const long long* picks, const int* guesses, const int* parents, int n_nodes, int* path, int* n_path);
+
 /* btb_publish (btb_kernels.cu:455-465): n0 += advance, then token, device clock (ns) and length to pinned host memory,
  * the length last behind a system fence. out_* null: only the advance. */
 int btb_b200_publish(void* n0, const void* ids, void* out_tok, void* out_n0, void* out_ts, int advance, void* stream);

@@ -97,6 +97,25 @@ def f32_to_bits(f: np.ndarray) -> np.ndarray:
 # ---- widens -------------------------------------------------------------------------------------------------
 
 
+def pack_p12(bits16) -> tuple[np.ndarray, np.ndarray, np.ndarray, np.ndarray, np.ndarray]:
+    """the reference's encoder (btb/pack12.py:48-68 `pack_bf16`) restated over bf16 bit patterns: (lo, hi4, table,
+    esc_idx, esc_val). What the card's encoder is checked against where no reference-made fixture exists."""
+    bits = np.ascontiguousarray(bits16, np.uint16).reshape(-1)
+    lo, hi = (bits & 0xFF).astype(np.uint8), (bits >> 8).astype(np.uint8)
+    hist = np.bincount(hi, minlength=256)
+    top = np.argsort(-hist, kind="stable")[:15]  # count descending, byte value ascending among equals
+    top = top[hist[top] > 0]
+    code_of = np.full(256, 15, np.uint8)
+    code_of[top] = np.arange(top.size, dtype=np.uint8)
+    codes = code_of[hi]
+    where = np.flatnonzero(codes == 15)
+    if codes.size & 1:
+        codes = np.append(codes, np.uint8(0))
+    table = np.zeros(16, np.uint8)
+    table[: top.size] = top
+    return lo, (codes[0::2] | (codes[1::2] << 4)).astype(np.uint8), table, where.astype(np.int32), hi[where]
+
+
 def widen_p12(lo, hi4, table, esc_idx, esc_val, n: int) -> np.ndarray:
     out = np.empty(n, np.uint16)
     esc_idx = np.ascontiguousarray(esc_idx, np.int32)

@@ -10,6 +10,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from btb_b200 import engine as E  # noqa: E402
+from tests.util import LAYER_STD, lively  # noqa: E402
 from btb_b200 import moe as MO  # noqa: E402
 from btb_b200 import parallel as P  # noqa: E402
 
@@ -21,16 +22,18 @@ def main() -> None:
     prompt = torch.arange(3, 48)
     cfg = E.DenseConfig("tp-check", hidden=256 * world, layers=2, q_heads=4 * world, kv_heads=world, head_dim=128,
                         inter=512 * world, vocab=512 * world)
-    full = E.synth_weights(cfg, seed=4, on_cpu=True)
-    want = E.CardEngine(full, cap=512, step_kernel=False).generate_greedy(prompt, 8)
-    tp = P.TPEngine(cfg, P.shard_dense(E.synth_weights(cfg, seed=4, on_cpu=True), rank, world), rank, world, cap=512)
-    got = tp.generate_greedy(prompt, 8)
+    full = E.synth_weights(cfg, seed=4, on_cpu=True, layer_std=LAYER_STD)
+    want = E.CardEngine(full, cap=512, step_kernel=False).generate_greedy(prompt, 16)
+    lively(want)
+    tp = P.TPEngine(cfg, P.shard_dense(E.synth_weights(cfg, seed=4, on_cpu=True, layer_std=LAYER_STD), rank, world), rank, world, cap=512)
+    got = tp.generate_greedy(prompt, 16)
     assert got == want, (rank, got, want)
     mcfg = MO.MoEConfig("ep-check", 256, 2, 8, 2, 128, 128, 512, experts=8 * world, top_k=4, router_mode=0, glu_kind=0,
                         expert_fmt="fp8")
-    want = MO.MoEEngine(MO.synth_moe_weights(mcfg, seed=6, on_cpu=True), cap=512).generate_greedy(prompt, 8)
-    ep = MO.MoEEngine(MO.synth_moe_weights(mcfg, seed=6, on_cpu=True, ep_rank=rank, ep_size=world), cap=512)
-    got = ep.generate_greedy(prompt, 8)
+    want = MO.MoEEngine(MO.synth_moe_weights(mcfg, seed=6, on_cpu=True, layer_std=LAYER_STD), cap=512).generate_greedy(prompt, 16)
+    lively(want)
+    ep = MO.MoEEngine(MO.synth_moe_weights(mcfg, seed=6, on_cpu=True, layer_std=LAYER_STD, ep_rank=rank, ep_size=world), cap=512)
+    got = ep.generate_greedy(prompt, 16)
     assert got == want, (rank, got, want)
     dist.barrier()
     torch.cuda.synchronize()

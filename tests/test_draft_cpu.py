@@ -1,5 +1,5 @@
-"""The n-gram proposer, the chain merge and the accept walk against fixtures made by the reference's own code
-(tests/golden/make_golden.py: btb/draft.py NGramProposer, btb/engine/generate.py _chains_tree)."""
+"""The library's native n-gram index, chain merge and accept walk (host code behind the C-ABI) against fixtures made by
+the reference's own code (tests/golden/make_golden.py: btb/draft.py NGramProposer, btb/engine/generate.py _chains_tree)."""
 
 import json
 import os
@@ -25,6 +25,7 @@ def test_proposer_and_tree_match_reference():
                 assert (g, par, dep) == (cur["guesses"], cur["parents"], cur["depth"])
                 assert {str(k): v for k, v in ch.items()} == cur["children"]
                 assert len(g) <= cur["budget"]
+                assert prop.tree(cur["v"], cur["budget"]) == (g, par, dep)  # the one-call form
                 n += 1
                 cur = next(steps, None)
     assert n > 100

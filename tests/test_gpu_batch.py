@@ -12,6 +12,7 @@ if not torch.cuda.is_available():
 
 from btb_b200 import capi  # noqa: E402
 from btb_b200 import engine as E  # noqa: E402
+from .util import LAYER_STD, lively  # noqa: E402
 from btb_b200.batch import BatchEngine  # noqa: E402
 
 SMALL = E.DenseConfig("small", hidden=256, layers=3, q_heads=8, kv_heads=2, head_dim=128, inter=512, vocab=1000)
@@ -19,11 +20,13 @@ SMALL = E.DenseConfig("small", hidden=256, layers=3, q_heads=8, kv_heads=2, head
 
 @pytest.mark.parametrize("B,storage", [(8, "bf16"), (3, "bf16"), (8, "p12"), (1, "bf16")])
 def test_batch_tokens_equal_each_sequences_own_greedy_tokens(B, storage):
-    mw = E.synth_weights(SMALL, seed=0, on_cpu=True, storage=storage)
+    mw = E.synth_weights(SMALL, seed=0, on_cpu=True, layer_std=LAYER_STD, storage=storage)
     rng = np.random.default_rng(B)
     prompts = [rng.integers(0, SMALL.vocab, size=int(n)).tolist() for n in rng.integers(5, 70, size=B)]
     one = E.CardEngine(mw, cap=512)
     want = [one.generate_greedy(p, 12) for p in prompts]
+    for w in want:
+        lively(w)
     be = BatchEngine(mw, B, cap=512)
     got = be.generate_batch(prompts, 12)
     assert got == want
@@ -35,7 +38,7 @@ def test_batch_tokens_equal_each_sequences_own_greedy_tokens(B, storage):
 def test_tensor_core_passes_agree_with_the_chain_passes_to_rounding():
     """with wide_tc a pass of several rows takes the tensor-core matvec: its logits agree with the fp32-chain pass's
     to bf16 rounding carried through the layers, and a one-row step is untouched"""
-    mw = E.synth_weights(SMALL, seed=1, on_cpu=True)
+    mw = E.synth_weights(SMALL, seed=1, on_cpu=True, layer_std=LAYER_STD)
     a, b = E.CardEngine(mw, cap=512), E.CardEngine(mw, cap=512)
     b.wide_tc = True
     ids = torch.arange(9, 41)
@@ -48,7 +51,7 @@ def test_tensor_core_passes_agree_with_the_chain_passes_to_rounding():
 
 
 def test_batch_engine_on_tensor_cores():
-    mw = E.synth_weights(SMALL, seed=0, on_cpu=True)
+    mw = E.synth_weights(SMALL, seed=0, on_cpu=True, layer_std=LAYER_STD)
     rng = np.random.default_rng(8)
     prompts = [rng.integers(0, SMALL.vocab, size=int(n)).tolist() for n in rng.integers(5, 70, size=8)]
     be = BatchEngine(mw, 8, cap=512)

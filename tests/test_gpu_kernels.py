@@ -173,6 +173,32 @@ def test_gemv_with_norm_prologue_equals_two_kernels(M, T, R, H, add):
 # ---- pack12 ------------------------------------------------------------------------------------------------------
 
 
+def test_card_pack12_encoder_writes_the_reference_encoders_bytes(golden_dir):
+    """the library's on-card encoder against the parts the reference's own encoder wrote for the same tensors (golden
+    fixtures), and against the oracle's restatement on larger seeded tensors whose escapes span many tiles"""
+    import os
+
+    from btb_b200 import pack12
+
+    g = np.load(os.path.join(golden_dir, "codecs.npz"))
+    cases = [(f"golden {c}", g[f"p12_{c}_src"], [g[f"p12_{c}_{n}"] for n in ("lo", "hi4", "tbl", "esc_idx", "esc_val")])
+             for c in "abcd"]  # fmt: skip
+    rng = np.random.default_rng(12)
+    for R, Cc, dense in ((300, 2560, False), (129, 4097, True), (1, 1, False), (64, 9728, True)):
+        f = rng.standard_normal((R, Cc)).astype(np.float32) * 0.02
+        if dense:
+            f *= np.logspace(-9, 3, Cc, dtype=np.float32)[None, :]
+        src = O.f32_to_bits(f)
+        cases.append((f"seeded {R}x{Cc}", src, list(O.pack_p12(src))))
+    for what, src, want in cases:
+        t = torch.from_numpy(src.view(np.int16)).view(torch.bfloat16).to(DEV)
+        lo, hi4, table, ei, ev = pack12.pack_bf16(t)
+        got = [lo.cpu().numpy(), hi4.cpu().numpy(), np.frombuffer(table, np.uint8), ei.cpu().numpy(), ev.cpu().numpy()]
+        for mine, theirs, name in zip(got, want, ("lo", "hi4", "table", "esc_idx", "esc_val")):
+            assert np.array_equal(mine, theirs), (what, name)
+        assert np.array_equal(O.widen_p12(*got, src.size), src.reshape(-1)), what
+
+
 def _p12_case(rng, R, Cc, scale_cols=False):
     from btb_b200 import pack12
 
@@ -181,7 +207,8 @@ def _p12_case(rng, R, Cc, scale_cols=False):
         f *= np.logspace(-9, 3, Cc, dtype=np.float32)[None, :]
     wb = O.f32_to_bits(f)
     t = torch.from_numpy(wb.view(np.int16)).view(torch.bfloat16)
-    return wb, pack12.pack_bf16(t)
+    lo, hi4, table, ei, ev = pack12.pack_bf16(t)  # the card's encoder; numpy copies for the oracle's arguments
+    return wb, (lo.cpu().numpy(), hi4.cpu().numpy(), np.frombuffer(table, np.uint8).copy(), ei.cpu().numpy(), ev.cpu().numpy())
 
 
 @pytest.mark.parametrize("R,Cc,dense", [(40, 256, False), (300, 2560, False), (64, 9728, False), (33, 512, True),

@@ -12,6 +12,7 @@ if not torch.cuda.is_available():
 
 from btb_b200 import capi  # noqa: E402
 from btb_b200 import engine as E  # noqa: E402
+from .util import LAYER_STD, lively  # noqa: E402
 from btb_b200 import moe as MO  # noqa: E402
 from btb_b200.capi import call, ptr  # noqa: E402
 from btb_b200.draft import generate_speculative  # noqa: E402
@@ -64,9 +65,10 @@ def _pattern_prompt(vocab, n=48, period=12, seed=0):
 
 @pytest.mark.parametrize("budget", [1, 4, 8, 31])
 def test_speculative_tokens_are_the_greedy_tokens(budget):
-    eng = E.CardEngine(E.synth_weights(SMALL, seed=0, on_cpu=True), cap=1024)
+    eng = E.CardEngine(E.synth_weights(SMALL, seed=0, on_cpu=True, layer_std=LAYER_STD), cap=1024)
     prompt = _pattern_prompt(SMALL.vocab)
     want = eng.generate_greedy(prompt, 80)
+    lively(want)
     got, stats = generate_speculative(eng, prompt, 80, budget=budget)
     assert got == want
     assert stats["passes"] <= 79
@@ -77,9 +79,10 @@ def test_speculative_tokens_are_the_greedy_tokens(budget):
 
 
 def test_speculative_accepts_drafts_on_text_that_repeats():
-    eng = E.CardEngine(E.synth_weights(SMALL, seed=3, on_cpu=True), cap=1024)
+    eng = E.CardEngine(E.synth_weights(SMALL, seed=3, on_cpu=True, layer_std=LAYER_STD), cap=1024)
     prompt = _pattern_prompt(SMALL.vocab, seed=5)
     want = eng.generate_greedy(prompt, 120)
+    lively(want)
     # feed the model its own continuation as the prompt's tail: the n-grams now predict what it will say
     got, stats = generate_speculative(eng, prompt + want[:60], 60, budget=8)
     assert got == eng.generate_greedy(prompt + want[:60], 60)
@@ -89,8 +92,9 @@ def test_speculative_accepts_drafts_on_text_that_repeats():
 def test_speculative_equals_greedy_in_a_moe_model():
     cfg = MO.MoEConfig("m2", 256, 2, 8, 2, 128, 128, 512, experts=16, top_k=4, router_mode=0, glu_kind=0,
                        expert_fmt="fp8")  # fmt: skip
-    eng = MO.MoEEngine(MO.synth_moe_weights(cfg, seed=2, on_cpu=True), cap=512)
+    eng = MO.MoEEngine(MO.synth_moe_weights(cfg, seed=2, on_cpu=True, layer_std=LAYER_STD), cap=512)
     prompt = _pattern_prompt(cfg.vocab, seed=2)
     want = eng.generate_greedy(prompt, 48)
+    lively(want)
     got, _ = generate_speculative(eng, prompt, 48, budget=8)
     assert got == want
