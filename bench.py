@@ -240,14 +240,16 @@ def tp_synth_shard(cfg, rank: int, world: int):
     il, ih = P.row_shard(I, rank, world)
     ql, qh = P.row_shard(cfg.q_heads * D, rank, world)
     kl, kh = P.row_shard(cfg.kv_heads * D, rank, world)
-    mw = E.ModelWeights(cfg, lin(1, cfg.vocab, H, vl, vh), ones(H))
+    table = lin(1, cfg.vocab, H, 0, cfg.vocab)  # the embedding table whole on every rank; the head is this rank's rows of it
+    mw = E.ModelWeights(cfg, table, ones(H), head=table[vl:vh])
     for i in range(cfg.layers):
         s0 = 100 + 10 * i
         qkv = torch.cat([lin(s0, cfg.q_heads * D, H, ql, qh), lin(s0 + 1, cfg.kv_heads * D, H, kl, kh),
                          lin(s0 + 2, cfg.kv_heads * D, H, kl, kh)])
         gu = torch.cat([lin(s0 + 4, I, H, il, ih), lin(s0 + 5, I, H, il, ih)])
         mw.layers.append(E.LayerWeights(ones(H), ones(H), qkv, lin(s0 + 3, H, cfg.q_heads * D, hl, hh), gu,
-                                        lin(s0 + 6, H, I, hl, hh), None, None))
+                                        lin(s0 + 6, H, I, hl, hh), ones(D) if cfg.qk_norm else None,
+                                        ones(D) if cfg.qk_norm else None))
     return mw
 
 
@@ -270,7 +272,15 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     storage, parallelism = "bf16", ("replicas only" if world > 1 else "1 gpu")
     if args.pdl is not None:
         capi.set_tuning(pdl=args.pdl)
-    if args.workload.startswith("qwen3-4b"):
+    if args.workload == "qwen3-4b-bf16" and world > 1 and args.batch == 1 and not args.replicas:
+        # one model over the ranks: every linear cut by output rows, one token stream (strong scaling)
+        from btb_b200 import parallel as P
+
+        cfg = E.QWEN3_4B if not args.layers else dataclasses.replace(E.QWEN3_4B, layers=args.layers)
+        mw = tp_synth_shard(cfg, rank, world)
+        eng = P.TPEngine(cfg, mw, rank, world, cap=cap)
+        parallelism = f"tp{world}"
+    elif args.workload.startswith("qwen3-4b"):
         cfg = E.QWEN3_4B if not args.layers else dataclasses.replace(E.QWEN3_4B, layers=args.layers)
         storage = "p12" if args.workload.endswith("p12") else "bf16"
         mw = E.synth_weights(cfg, seed=0, storage=storage)
@@ -365,7 +375,7 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     g1 = eng.bufs(1)
     s = capi.stream_ptr()
 
-    dense_model = args.workload.startswith("qwen3-4b")
+    dense_model = args.workload.startswith("qwen3-4b") and not hasattr(eng, "tp_bufs")
 
     def gemvs():
         H, D, I = cfg.hidden, cfg.head_dim, cfg.inter
@@ -428,7 +438,11 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         line["value"] = tps / world  # one model over all ranks: the job decodes one stream
         line["e2e"]["value"] = e2e / world
         line["scaling"] = "strong"
-        line["token_roofline_frac"] = None
+        line["token_roofline_frac"] = (cfg.weight_bytes_per_token(storage) / world * (tps / world) / 1e9) / peak
+        if hasattr(eng, "tp_bufs"):
+            line["roofline"] = None
+            line["metric"] = METRIC
+            line["collective"] = tp_collective(eng, cfg, world, dist)
     if rank == 0 and world == 1 and not args.no_cpu and args.workload == "qwen3-4b-bf16":
         hw = host_weights_from_engine(mw) if storage == "bf16" else host_weights_synth(cfg)
         from oracle import oracle as O
@@ -447,6 +461,57 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
 
 
 STORED = {"p12": "pack12", "mx4": "MXFP4 expert", "fp8": "FP8 block-scaled"}
+
+
+def tp_collective(eng, cfg, world, dist) -> dict:
+    """what the tensor-parallel step exchanges, and one hop of it timed on its own: every rank sends its slice of a
+    hidden-size vector to every rank and waits for everyone's (CUDA events around 200 hops in a row, max over ranks)"""
+    import ctypes as C
+
+    import torch
+
+    from btb_b200 import capi
+    from btb_b200.capi import call, ptr
+
+    t = eng.tp_bufs(1)
+    H, A, I = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.inter
+    src = torch.zeros(1, H // world, dtype=torch.bfloat16, device="cuda")
+    n = C.c_int(0)
+    s = capi.stream_ptr()
+    hops = 200
+    # the probe uses the last layer's `yd` vector and its counter; one pass of the probe = one hop, then a tick
+    send = t["send_yd"][cfg.layers - 1]
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    flag_off = eng.flag_off(1, cfg.layers - 1, "yd")
+    # the counter has seen the decode's passes: start the probe's own count from where it stands
+    base = eng.heap.tensor(flag_off, (1,), torch.int32)
+    probe_pass = torch.zeros(1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    dist.barrier()
+    start = int(base[0].item())
+    assert start % world == 0
+    probe_pass[0] = start // world
+    w = capi.Wait(eng.heap.local + flag_off, ptr(probe_pass), world)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record()
+    for _ in range(hops):
+        call("btb_b200_xchg_send", ptr(src), 1, H // world, 2, None, send, C.byref(n), s)
+        call("btb_b200_xchg_wait", w, s)
+        call("btb_b200_xchg_tick", ptr(probe_pass), s)
+    e1.record()
+    torch.cuda.synchronize()
+    us = torch.tensor([e0.elapsed_time(e1) * 1000.0 / hops], device="cuda")
+    dist.all_reduce(us, op=dist.ReduceOp.MAX)
+    assert capi.status() == 0, "the exchange probe timed out"
+    per_step = cfg.layers * 2 * (A + 2 * H + I)  # bytes of activation vectors a step assembles on every rank
+    return {"kind": "peer stores into every rank's copy + arrival counters (NVLink writes, no collective call, no "
+                    "reduction), folded into the producing kernels' epilogues",
+            "hops_per_step": 4 * cfg.layers + 1, "bytes_per_step_per_rank_received": per_step * (world - 1) // world,
+            "us_per_hop_alone": float(us[0]), "note": "a hop alone = 3 launches (send, wait, tick) on an idle stream; "
+            "inside the step the send and the wait are parts of the GEMV kernels"}
 
 def run_case(args) -> None:
     """one kernel on a small case, for a profiler capture or a quick look: `gemv:RxC[:M[:fmt]]` rotates over enough
@@ -709,6 +774,7 @@ def main() -> None:
     ap.add_argument("--wide-tc", type=int, default=1, help="--batch: the tensor-core matvec for the pass of B rows")
     ap.add_argument("--case", default="", help="one kernel on a small case: gemv:RxC[:M[:fmt]], attn:N, moe:fp8|mx4, sample:V")
     ap.add_argument("--speculative", type=int, default=0, help="verify an n-gram tree of this many drafts a pass")
+    ap.add_argument("--replicas", action="store_true", help="--gpus N: N independent copies instead of one model over N ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

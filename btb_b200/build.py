@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libbtb_b200.so")
-SOURCES = ["capi.cu", "gemv.cu", "p12_encode.cu", "gemv_tc.cu", "layer.cu", "attn.cu", "attn_o.cu", "step.cu", "moe.cu", "moe_stream.cu", "sample.cu", "draft_host.cu"]
+SOURCES = ["capi.cu", "gemv.cu", "p12_encode.cu", "gemv_tc.cu", "layer.cu", "attn.cu", "attn_o.cu", "step.cu", "moe.cu", "moe_stream.cu", "sample.cu", "draft_host.cu", "tp.cu"]
 FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC",
     "-Xcompiler", "-fvisibility=default",

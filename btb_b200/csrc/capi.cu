@@ -66,11 +66,12 @@ int b2_status_take_sample(int*);
 int b2_status_take_moes(int*);
 int b2_status_take_attno(int*);
 int b2_status_take_tc(int*);
+int b2_status_take_tp(int*);
 
 extern "C" int btb_b200_status(int* code) {
     if (code == nullptr) return B2_ERR_NULL;
     int (*const take[])(int*) = {b2_status_take_gemv, b2_status_take_layer, b2_status_take_attn, b2_status_take_step,
-                                 b2_status_take_moe, b2_status_take_sample, b2_status_take_moes, b2_status_take_attno, b2_status_take_tc};
+                                 b2_status_take_moe, b2_status_take_sample, b2_status_take_moes, b2_status_take_attno, b2_status_take_tc, b2_status_take_tp};
     *code = 0;
     for (auto f : take) {
         int v = 0;

@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "btb_b200_internal.h"
 #include "gemv_core.cuh"
+#include "tp.cuh"
+#include "../../include/btb_b200.h"
 
 B2_DEFINE_STATUS(gemv)
 
@@ -55,6 +57,11 @@ struct GemvArgs {
     // after the other and writes y[m][p] = bf16(bf16(silu(bf16 g)) * bf16 u) - what btb_silu_mul makes of the two
     // outputs. 0: off. R counts pairs then.
     int pair;
+    // a model cut over ranks by output rows (tp.cuh): `wait` holds back the read of x (or of y_add) until every rank's
+    // slice of it has arrived; with `send.n > 0` every output element goes to each rank's copy of the full vector at
+    // [m][send.offset + row] instead of y, and the CTA adds its arrival to each rank's counter when its rows are done
+    B2Wait wait;
+    B2Send send;
 };
 
 // NWT: the most warps a CTA of this instance is launched with (its register budget); the launch picks how many
@@ -138,6 +145,10 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
 
     pdl_launch_dependents();
     pdl_wait();  // x is the previous kernel's output
+    if (A.wait.flag != nullptr) {  // ... or, in a model cut over ranks, every rank's: wait for the last slice
+        if (threadIdx.x == 0) b2_wait_arrivals(A.wait);
+        __syncthreads();
+    }
 
     if (XS) {
         if (XM == X_SMEM) stage_x_copy<M, NT>(xs, A.x, C);
@@ -183,12 +194,17 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 const float s = warp_sum(acc[m]);
-                if (pair == 0) {
-                    if (lane == 0) A.y[(size_t)m * R + row] = f2bf(s);
-                } else if (c_sub == 0) {
+                if (pair != 0 && c_sub == 0) {
                     gate[m] = bfround(s);
                 } else if (lane == 0) {
-                    A.y[(size_t)m * R + c_row] = f2bf(bfround(act_silu(gate[m])) * bfround(s));
+                    const bf16 v = pair == 0 ? f2bf(s) : f2bf(bfround(act_silu(gate[m])) * bfround(s));
+                    if (A.send.n == 0) {
+                        A.y[(size_t)m * R + c_row] = v;
+                    } else {
+                        const size_t at = (size_t)m * A.send.stride + A.send.offset + c_row;
+#pragma unroll 1
+                        for (int p = 0; p < A.send.n; ++p) static_cast<bf16*>(A.send.out[p])[at] = v;
+                    }
                 }
                 acc[m] = 0.f;
             }
@@ -218,6 +234,10 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
             }
             mbar_wait_bounded(smem_u32(bars + c_st), c_par);
         }
+    }
+    if (A.send.n != 0) {  // every warp's rows are stored: publish them and arrive at every rank
+        __syncthreads();
+        b2_signal_arrival(A.send);
     }
 }
 
@@ -367,26 +387,60 @@ extern "C" int btb_b200_p12_rows(const void* esc_idx, int n_esc, int R, int C, v
                      a);
 }
 
-extern "C" int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* stream) {
-    int rc = check_dims(w, x, y, M, R, C);
+// the exchange descriptors of the C-ABI (include/btb_b200.h) into the kernels' own; refuses what a kernel could fault on
+static int take_exchange(const btb_b200_wait* wait, const btb_b200_send* send, GemvArgs& a) {
+    if (wait != nullptr && wait->flag != nullptr) {
+        if (wait->pass == nullptr) return B2_ERR_NULL;
+        a.wait = B2Wait{static_cast<const unsigned*>(wait->flag), static_cast<const unsigned*>(wait->pass), wait->per_pass};
+    }
+    if (send != nullptr && send->n != 0) {
+        if (send->n < 0 || send->n > B2_MAX_RANKS || send->stride <= 0 || send->offset < 0 ||
+            send->offset + a.R > send->stride)
+            return B2_ERR_DOMAIN;
+        a.send.n = send->n, a.send.stride = send->stride, a.send.offset = send->offset;
+        for (int p = 0; p < send->n; ++p) {
+            if (send->out[p] == nullptr || send->flag[p] == nullptr) return B2_ERR_NULL;
+            a.send.out[p] = send->out[p], a.send.flag[p] = static_cast<unsigned*>(send->flag[p]);
+        }
+    }
+    return B2_OK;
+}
+
+static int gemv_bf16_impl(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_wait* wait,
+                          const btb_b200_send* send, int* ctas, void* stream) {
+    const bool sends = send != nullptr && send->n != 0;
+    int rc = check_dims(w, x, sends ? w : y, M, R, C);  // a sending launch has no local y
     if (rc) return rc;
     GemvArgs a{};
     a.w = static_cast<const uint8_t*>(w);
     a.x = static_cast<const bf16*>(x);
     a.y = static_cast<bf16*>(y);
     a.R = R, a.C = C;
+    if ((rc = take_exchange(wait, send, a)) != B2_OK) return rc;
     Plan p = make_plan<F_BF16>(M, R, C, M <= 8);
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
+    if (ctas != nullptr) *ctas = p.grid;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return p.xs ? launch_m<F_BF16, X_SMEM>(M, a, p, s) : launch_m_global<F_BF16>(M, a, p, s);
+}
+
+extern "C" int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* stream) {
+    return gemv_bf16_impl(w, x, y, M, R, C, nullptr, nullptr, nullptr, stream);
+}
+
+extern "C" int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_wait* wait,
+                                    const btb_b200_send* send, int* ctas, void* stream) {
+    return gemv_bf16_impl(w, x, y, M, R, C, wait, send, ctas, stream);
 }
 
 // x = rmsnorm(h_in + y) * w computed inside the GEMV (bf16 weights, or pack12 when hi4 is not null); swiglu: the rows are
 // gate then up and the output is the activated product of each pair
 static int gemv_norm_impl(const void* w, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
                           const void* esc_row, const void* h_in, const void* y_add, const void* norm_w, float eps,
-                          int centered, void* h_out, void* y, int T, int M, int R, int C, bool swiglu, void* stream) {
-    int rc = check_dims(w, h_in, y, M, R, C);
+                          int centered, void* h_out, void* y, int T, int M, int R, int C, bool swiglu, void* stream,
+                          const btb_b200_wait* wait = nullptr, const btb_b200_send* send = nullptr, int* ctas = nullptr) {
+    const bool sends = send != nullptr && send->n != 0;
+    int rc = check_dims(w, h_in, sends ? w : y, M, R, C);
     if (rc) return rc;
     if (norm_w == nullptr || (y_add != nullptr && h_out == nullptr)) return B2_ERR_NULL;
     if (T <= 0 || T > M || M > 8 || !(eps == eps) || h_out == h_in) return B2_ERR_DOMAIN;
@@ -408,9 +462,11 @@ static int gemv_norm_impl(const void* w, const void* hi4, const void* table, con
     a.h_in = static_cast<const bf16*>(h_in), a.y_add = static_cast<const bf16*>(y_add);
     a.norm_w = static_cast<const bf16*>(norm_w), a.h_out = static_cast<bf16*>(h_out);
     a.eps = eps, a.centered = centered, a.T = T;
+    if ((rc = take_exchange(wait, send, a)) != B2_OK) return rc;
     Plan p = p12 ? make_plan<F_P12>(M, a.R, C, true, true) : make_plan<F_BF16>(M, a.R, C, true, true);
     if (!p.xs) return B2_ERR_DOMAIN;  // too wide to stage: the caller runs btb_b200_add_rmsnorm and the plain GEMV
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
+    if (ctas != nullptr) *ctas = p.grid;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return p12 ? launch_m<F_P12, X_SMEM_NORM>(M, a, p, s) : launch_m<F_BF16, X_SMEM_NORM>(M, a, p, s);
 }
@@ -429,6 +485,15 @@ extern "C" int btb_b200_gemv_norm_swiglu(const void* w, const void* hi4, const v
                                          int M, int R, int C, void* stream) {
     return gemv_norm_impl(w, hi4, table, esc_idx, esc_val, esc_row, h_in, y_add, norm_w, eps, centered, h_out, m_out, T, M,
                           R, C, true, stream);
+}
+
+// btb_b200_gemv_norm / _norm_swiglu over bf16 weights in a model cut over ranks: the wait holds back the read of y_add
+// (every rank's slice of the previous block's output), the outputs go to every rank's copy of the next vector
+extern "C" int btb_b200_gemv_norm_x(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps,
+                                    int centered, void* h_out, void* y, int T, int M, int R, int C, int swiglu,
+                                    const btb_b200_wait* wait, const btb_b200_send* send, int* ctas, void* stream) {
+    return gemv_norm_impl(w, nullptr, nullptr, nullptr, nullptr, nullptr, h_in, y_add, norm_w, eps, centered, h_out, y, T, M,
+                          R, C, swiglu != 0, stream, wait, send, ctas);
 }
 
 // FP8 e4m3 weights with an f32 [sr, sc] block-scale grid, each weight the bf16 btb holds for it, widened in registers

@@ -127,6 +127,7 @@ class ModelWeights:
     embed: torch.Tensor  # [V, H] bf16, the tied head
     norm: torch.Tensor
     layers: list[LayerWeights] = field(default_factory=list)
+    head: torch.Tensor | None = None  # a rank's vocabulary rows of `embed` (a view) when the model is cut over ranks
 
 
 def synth_weights(cfg: DenseConfig, seed: int = 0, device: Any = "cuda", storage: str = "bf16",

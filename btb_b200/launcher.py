@@ -263,3 +263,18 @@ def btb_sample_out(launcher, grid, block, gbest, out, R, *, stream=None, shared=
 
 def btb_gemv_mma_bf16(launcher, grid, block, w, x, y, R, C_, M, *, stream=None, shared=0):
     launcher.launch("btb_gemv_mma_bf16", grid, block, [_P(w), _P(x), _P(y), _I(R), _I(C_), _I(M)], stream, shared)
+
+
+def btb_moe_route(launcher, grid, block, logits, ls, E, k, idx, w, hidx, hw, cnt, seq, hseq, *, stream=None, shared=0):
+    launcher.launch("btb_moe_route", grid, block,
+                    [_P(logits), _I(ls), _I(E), _I(k), _P(idx), _P(w), _P(hidx), _P(hw), _P(cnt), _P(seq), _P(hseq)],
+                    stream, shared)  # fmt: skip
+
+
+def btb_gemv_lane16_f32(launcher, M, grid, block, w, x, y, R, C_, *, stream=None, shared=0):
+    launcher.launch(f"btb_gemv_lane16_f32_m{M}", grid, block, [_P(w), _P(x), _P(y), _I(R), _I(C_)], stream, shared)
+
+
+def btb_gemv_lane16_mx4_f32(launcher, M, grid, block, blocks, scales, x, y, R, C_, *, stream=None, shared=0):
+    launcher.launch(f"btb_gemv_lane16_mx4_f32_m{M}", grid, block,
+                    [_P(blocks), _P(scales), _P(x), _P(y), _I(R), _I(C_)], stream, shared)  # fmt: skip

@@ -4,12 +4,14 @@ btb has no multi-GPU path, so the contract here is bit-identity with the one-GPU
 
 * dense layers (tensor parallel): every linear is cut by OUTPUT rows - q/k/v by kv-head group, o and down by rows of
   the hidden size, gate and up by the same rows of the intermediate size (paired), the head by vocabulary rows - so
-  each output element's whole K-sum stays on one GPU in the one-GPU order. What a rank lacks of an activation vector it
-  gets by all-gather (16-57 KB a hop at batch 1). Attention is cut by kv head; a rank holds only its heads' cache.
-* MoE layers (expert parallel): expert e lives on rank e % N (`btb_b200.moe`); products are exchanged by one all-reduce
-  of zeros-elsewhere f32 rows and every rank runs the same ordered sum.
-* the greedy pick over a vocabulary cut by rows: each rank's (value, index) best, gathered, the largest value and on
-  ties the lowest index - the one-GPU rule.
+  each output element's whole K-sum stays on one GPU in the one-GPU order. Attention is cut by kv head; a rank holds
+  only its heads' cache. What a rank lacks of an activation vector its peers write into its memory: the producing
+  kernel's epilogue stores every finished element into every rank's copy and counts its CTAs' arrivals, the consuming
+  kernel's prologue waits on its local counter (csrc/tp.cuh) - four such hops a layer, no collective call, no reduction
+  (hence no change of summation order), and the whole step stays one captured CUDA graph.
+* the greedy pick over a vocabulary cut by rows: each rank's (value, index) best goes to every rank, which takes the
+  largest value and on ties the lowest index - the one-GPU rule.
+* MoE layers (expert parallel): expert e lives on rank e % N (`btb_b200.moe`).
 
 The host-side pieces (who owns what, how gathered slices are laid out, how picks merge) are plain functions so the
 CPU tests can run them over gloo; `TPEngine` is the card engine over them.
@@ -21,9 +23,12 @@ from typing import Any
 
 import torch
 
+import ctypes as C
+
 from . import capi
 from .capi import ptr
-from .engine import CardEngine, DenseConfig, LayerWeights, ModelWeights, pad_rows
+from .engine import CARD_ROWS, CardEngine, DenseConfig, LayerWeights, ModelWeights, pad_rows
+from .exchange import FLAG_BYTES, PeerHeap
 
 
 def row_shard(rows: int, rank: int, world: int) -> tuple[int, int]:
@@ -54,7 +59,8 @@ def shard_gate_up(gu: torch.Tensor, inter: int, rank: int, world: int) -> torch.
 def shard_dense(mw: ModelWeights, rank: int, world: int) -> ModelWeights:
     """a rank's share of a dense model: every linear by output rows, norms and rope replicated"""
     c = mw.cfg
-    out = ModelWeights(c, mw.embed[slice(*row_shard(c.vocab, rank, world))].contiguous(), mw.norm)
+    # the embedding table stays whole on every rank (a step reads one row of it); the head is this rank's rows of it
+    out = ModelWeights(c, mw.embed, mw.norm, head=mw.embed[slice(*row_shard(c.vocab, rank, world))])
     for L in mw.layers:
         out.layers.append(LayerWeights(
             L.ln1, L.ln2, shard_qkv(L.qkv, c, rank, world), L.o[slice(*row_shard(c.hidden, rank, world))].contiguous(),
@@ -80,133 +86,177 @@ def merge_picks(values: torch.Tensor, indices: torch.Tensor, shard: int) -> torc
 
 
 class TPEngine(CardEngine):
-    """a dense model tensor-parallel over a process group: this rank's row shards, its kv heads' cache"""
+    """a dense model tensor-parallel over the ranks of one box: this rank's row shards, its kv heads' cache, and the
+    peer-store exchange (module docstring). `heap`: a `PeerHeap` already connected to the other ranks' (the lockstep
+    emulation hands engines of one process each other's); None: one is made and connected through `group`."""
+
+    XCHG = ("att", "yo", "m", "yd")  # the four vectors a layer exchanges, in order
 
     def __init__(self, full_cfg: DenseConfig, shard: ModelWeights, rank: int, world: int, group: Any = None,
-                 cap: int = 4096, device: Any = "cuda"):  # fmt: skip
+                 cap: int = 4096, device: Any = "cuda", heap: PeerHeap | None = None):  # fmt: skip
         import dataclasses
 
-        if world < 1 or full_cfg.q_heads % world or full_cfg.kv_heads % world or full_cfg.hidden % (8 * world) \
-                or full_cfg.inter % (8 * world) or full_cfg.vocab % world:
+        if world < 1 or world > 8 or full_cfg.q_heads % world or full_cfg.kv_heads % world \
+                or full_cfg.hidden % (8 * world) or full_cfg.inter % (8 * world) or full_cfg.vocab % world:
             raise ValueError(f"{full_cfg.name} does not cut into {world} ranks")
         self.full, self.rank, self.world, self.group = full_cfg, rank, world, group
         # the local view: this rank's heads; hidden and intermediate stay whole as GEMV input widths
         local = dataclasses.replace(full_cfg, q_heads=full_cfg.q_heads // world, kv_heads=full_cfg.kv_heads // world)
         shard.cfg = local
+        if shard.head is None:
+            shard.head = shard.embed[slice(*row_shard(full_cfg.vocab, rank, world))]
         super().__init__(shard, cap=cap, step_kernel=False, device=device)
-        self._tp: dict[int, dict[str, torch.Tensor]] = {}
+        c = full_cfg
+        self.widths = {"att": c.q_heads * c.head_dim, "yo": c.hidden, "m": c.inter, "yd": c.hidden}
+        self.heap = heap if heap is not None else PeerHeap(self.heap_bytes(c), rank, world)
+        self._layout()
+        if heap is None:
+            self.heap.connect_processes(group)
+        self._tp: dict[int, dict[str, Any]] = {}
+        # passes made so far at each width, on the card: the layers' exchanges and the picks count their own
+        self.passes = torch.zeros(len(CARD_ROWS), 2, dtype=torch.int32, device=self.dev)
 
-    def tp_bufs(self, M: int) -> dict[str, torch.Tensor]:
+    # -- the heap: the same layout on every rank -------------------------------------------------------------------------
+    @classmethod
+    def heap_bytes(cls, c: DenseConfig) -> int:
+        per_row = 2 * (c.q_heads * c.head_dim + 2 * c.hidden + c.inter)
+        flags = (4 * c.layers + 1) * FLAG_BYTES
+        return sum(M * per_row + 4 * 256 + flags + 8 * 32 * 8 + 512 for M in CARD_ROWS) + 4096
+
+    def _layout(self) -> None:
+        self.off: dict[int, dict[str, int]] = {}
+        for M in CARD_ROWS:
+            o = {k: self.heap.carve(M * w * 2) for k, w in self.widths.items()}
+            o["flags"] = self.heap.carve((4 * self.full.layers + 1) * FLAG_BYTES)
+            o["picks"] = self.heap.carve(8 * 32 * 8)
+            self.off[M] = o
+
+    def flag_off(self, M: int, layer: int, which: str) -> int:
+        return self.off[M]["flags"] + (4 * layer + self.XCHG.index(which)) * FLAG_BYTES
+
+    def tp_bufs(self, M: int) -> dict[str, Any]:
+        """width M's local buffers and its exchange descriptors"""
         if M not in self._tp:
-            c, w, dev = self.full, self.world, self.dev
+            c, w, dev, hp = self.full, self.world, self.dev, self.heap
             bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)  # noqa: E731
-            self._tp[M] = {
-                "att_l": bf(M, c.q_heads * c.head_dim // w), "att_g": bf(w, M, c.q_heads * c.head_dim // w),
-                "y_l": bf(M, c.hidden // w), "y_g": bf(w, M, c.hidden // w), "att": bf(M, c.q_heads * c.head_dim),
-                "y": bf(M, c.hidden), "gu_l": bf(M, 2 * c.inter // w), "m_l": bf(M, c.inter // w),
-                "m_g": bf(w, M, c.inter // w), "m": bf(M, c.inter), "lg_l": bf(M, c.vocab // w),
-                "pv": torch.zeros(w, M, dtype=torch.float32, device=dev),
-                "pi": torch.zeros(w, M, dtype=torch.int64, device=dev),
+            wi = CARD_ROWS.index(M)
+            t: dict[str, Any] = {
+                "att_l": bf(M, c.q_heads * c.head_dim // w), "gu_l": bf(M, 2 * c.inter // w), "m_l": bf(M, c.inter // w),
+                "lg_l": bf(M, c.vocab // w), "tok_l": torch.zeros(M, dtype=torch.int64, device=dev),
+                "pass": int(self.passes[wi, 0:1].data_ptr()), "pick_pass": int(self.passes[wi, 1:2].data_ptr()),
             }  # fmt: skip
+            for k, width in self.widths.items():
+                t[k] = hp.local + self.off[M][k]  # this rank's copy of the full vector
+                t[k + "_t"] = hp.tensor(self.off[M][k], (M, width), torch.bfloat16)
+                t["send_" + k] = [hp.send_desc(self.off[M][k], self.flag_off(M, i, k), width, self.rank * (width // w))
+                                  for i in range(c.layers)]  # fmt: skip
+            pick_flag = self.off[M]["flags"] + 4 * c.layers * FLAG_BYTES
+            t["send_pick"] = hp.send_desc(self.off[M]["picks"], pick_flag, 8 * 32, 0)
+            t["wait_pick"] = hp.wait_desc(pick_flag, t["pick_pass"], w)
+            self._tp[M] = t
         return self._tp[M]
 
-    def _gather(self, local: torch.Tensor, parts: torch.Tensor, full: torch.Tensor) -> None:
-        if self.world == 1:
-            full.copy_(local)
-            return
-        import torch.distributed as dist
+    def _wait(self, M: int, layer: int, which: str, ctas: int) -> Any:
+        return self.heap.wait_desc(self.flag_off(M, layer, which), self.tp_bufs(M)["pass"], ctas * self.world)
 
-        dist.all_gather_into_tensor(parts.view(-1, local.shape[-1]), local, group=self.group)
-        full.copy_(gathered_rows(parts))
-
-    def body(self, T: int, tail: bool = True, stream_ptr: int | None = None) -> None:
+    # -- the pass, one exchange-delimited piece at a time ---------------------------------------------------------------
+    def ops(self, T: int, tail: bool = True, stream_ptr: int | None = None):
+        """the pass's launches; yields after each piece that ends in an exchange, so that engines standing in for the
+        ranks on ONE GPU can take turns (every producer launched before any consumer of its vector)"""
         c, lc, w = self.full, self.cfg, self.world
         M = pad_rows(T)
         g, t = self.bufs(M), self.tp_bufs(M)
         s = capi.stream_ptr() if stream_ptr is None else stream_ptr
         H, D, I = c.hidden, c.head_dim, c.inter
+        A = c.q_heads * D
         K_ = self._k
-        y_prev = None
-        for i, L in enumerate(self.w.layers):
-            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(g["x"]), T, H, 0, s)
-            self._matvec(L.qkv, g["x"], g["qkv"], M, lc.qkv_rows, H, s)
-            self._attention(g, i, L.wq, L.wk, T, s, out=t["att_l"])  # this rank's heads
-            self._gather(t["att_l"], t["att_g"], t["att"])
-            self._matvec(L.o, t["att"], t["y_l"], M, H // w, c.q_heads * D, s)
-            self._gather(t["y_l"], t["y_g"], t["y"])
-            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(t["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
-            self._matvec(L.gu, g["x"], t["gu_l"], M, 2 * I // w, H, s)
+        n = C.c_int(0)
+        fuse = self.fuse_norm and M <= 8 and M * H * 2 <= 64 * 1024
+        hcur, halt = g["h"], g["h2"]
+        y_prev, wait_prev = 0, None  # the previous layer's output (every rank's slices, in this rank's copy)
+
+        def normed(W: torch.Tensor, norm_w: torch.Tensor, R: int, out: Any, swiglu: bool, send: Any) -> int:
+            """x = rmsnorm(h + y_prev) folded into the GEMV over W where the row fits, else the separate kernels"""
+            nonlocal hcur, halt
+            if fuse:
+                K_("btb_b200_gemv_norm_x", ptr(W), ptr(hcur), y_prev, ptr(norm_w), c.eps, 0, ptr(halt) if y_prev else 0,
+                   ptr(out) if send is None else 0, T, M, R, H, int(swiglu), wait_prev, send, C.byref(n), s)  # fmt: skip
+                if y_prev:
+                    hcur, halt = halt, hcur
+                return n.value
+            if wait_prev is not None:
+                K_("btb_b200_xchg_wait", wait_prev, s)
+            K_("btb_b200_add_rmsnorm", ptr(hcur), y_prev, ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
+            if not swiglu:
+                K_("btb_b200_gemv_bf16_x", ptr(W), ptr(g["x"]), ptr(out) if send is None else 0, M, R, H, None, send,
+                   C.byref(n), s)  # fmt: skip
+                return n.value
+            K_("btb_b200_gemv_bf16", ptr(W), ptr(g["x"]), ptr(t["gu_l"]), M, R, H, s)
             K_("btb_b200_silu_mul", ptr(t["gu_l"]), ptr(t["m_l"]), M, I // w, s)
-            self._gather(t["m_l"], t["m_g"], t["m"])
-            self._matvec(L.down, t["m"], t["y_l"], M, H // w, I, s)
-            self._gather(t["y_l"], t["y_g"], t["y"])
-            y_prev = t["y"]
+            K_("btb_b200_xchg_send", ptr(t["m_l"]), M, I // w, 2, None, send, C.byref(n), s)
+            return n.value
+
+        for i, L in enumerate(self.w.layers):
+            normed(L.qkv, L.ln1, lc.qkv_rows, g["qkv"], False, None)
+            self._attention(g, i, L.wq, L.wk, T, s, out=t["att_l"])  # this rank's heads
+            K_("btb_b200_xchg_send", ptr(t["att_l"]), M, A // w, 2, None, t["send_att"][i], C.byref(n), s)
+            wait_prev = self._wait(M, i, "att", n.value)
+            yield
+            K_("btb_b200_gemv_bf16_x", ptr(L.o), t["att"], 0, M, H // w, A, wait_prev, t["send_yo"][i], C.byref(n), s)
+            y_prev, wait_prev = t["yo"], self._wait(M, i, "yo", n.value)
+            yield
+            ctas = normed(L.gu, L.ln2, 2 * I // w, None, True, t["send_m"][i])
+            wait_prev = self._wait(M, i, "m", ctas)
+            yield
+            K_("btb_b200_gemv_bf16_x", ptr(L.down), t["m"], 0, M, H // w, I, wait_prev, t["send_yd"][i], C.byref(n), s)
+            y_prev, wait_prev = t["yd"], self._wait(M, i, "yd", n.value)
+            yield
         if tail:
-            K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(self.w.norm), c.eps, ptr(g["x"]), T, H, 0, s)
-            self._matvec(self.w.embed, g["x"], t["lg_l"], M, c.vocab // w, H, s)
+            normed(self.w.head, self.w.norm, c.vocab // w, t["lg_l"], False, None)
+        elif wait_prev is not None:  # the last layer's output must have landed before the pass count moves on
+            K_("btb_b200_xchg_wait", wait_prev, s)
+        if hcur is not g["h"]:
+            g["h"].copy_(hcur)
 
-    def _embed(self, g: dict, T: int, s: int) -> None:
-        """the embedding table is the head, cut by vocabulary rows: the owner of a token's row supplies it, the
-        others zeros, and an all-reduce (x + 0, exact) gives every rank the row"""
-        V = self.full.vocab // self.world
-        ids = g["ids"][:T]
-        local = ids - self.rank * V
-        mine = (local >= 0) & (local < V)
-        rows = self.w.embed[local.clamp(0, V - 1)] * mine[:, None].to(torch.bfloat16)
-        if self.world > 1:
-            import torch.distributed as dist
+    def body(self, T: int, tail: bool = True, stream_ptr: int | None = None) -> None:
+        for _ in self.ops(T, tail, stream_ptr):
+            pass
 
-            rows = rows.float()
-            dist.all_reduce(rows, group=self.group)
-        g["h"][:T].copy_(rows.to(torch.bfloat16))
-        self._n += 1
+    def tick(self, M: int, s: int) -> None:
+        """a pass that ends without a pick advances the layers' pass count by a launch of its own"""
+        self._k("btb_b200_xchg_tick", self.tp_bufs(M)["pass"], s)
 
-    def _pick(self, g: dict, T: int, s: int, out: torch.Tensor) -> None:
+    def _pick(self, g: dict, T: int, s: int, out: torch.Tensor, phase: int = 0, body_pass: bool = True) -> None:
+        """the step's pick: this rank's lowest-index argmax of its vocabulary rows, then the merge over the ranks (which
+        also closes the pass: the layers' pass count advances there)"""
         M = pad_rows(T)
         t = self.tp_bufs(M)
-        lg = t["lg_l"][:T].float()
-        val, idx = lg.max(dim=-1)  # torch's max/argmax return the first of equal maxima: the lowest local index
-        if self.world > 1:
-            import torch.distributed as dist
-
-            vp = torch.full((M,), float("-inf"), dtype=torch.float32, device=self.dev)
-            ip = torch.zeros(M, dtype=torch.int64, device=self.dev)
-            vp[:T], ip[:T] = val, idx
-            dist.all_gather_into_tensor(t["pv"].view(-1), vp, group=self.group)
-            dist.all_gather_into_tensor(t["pi"].view(-1), ip, group=self.group)
-            out[:T].copy_(merge_picks(t["pv"][:, :T], t["pi"][:, :T], self.full.vocab // self.world))
-        else:
-            out[:T].copy_(idx)
-        self._n += 1
+        lg = g.get("logits_l", t["lg_l"])
+        Vl = self.full.vocab // self.world
+        if phase != 2:
+            self._k("btb_b200_argmax_bf16", ptr(lg), T, Vl, ptr(self.bufs(M)["pick"]), ptr(t["tok_l"]), s)
+        self._k("btb_b200_xchg_pick", ptr(lg), T, Vl, self.rank * Vl, ptr(t["tok_l"]), self.rank, t["wait_pick"],
+                t["send_pick"], ptr(out), t["pass"] if body_pass else 0, phase, s)  # fmt: skip
 
     def forward(self, ids: torch.Tensor, depth: Any = None, parents: Any = None, advance: bool = True) -> torch.Tensor:
         """a pass; returns THIS RANK'S logits slice [T, V / world]"""
         super().forward(ids, depth, parents, advance)
-        return self.tp_bufs(pad_rows(int(ids.numel())))["lg_l"][: int(ids.numel())]
-
-    def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
-        lg = None
-        for a in range(0, int(prompt.numel()), 32):
-            lg = self.forward(prompt[a : a + 32])
-        assert lg is not None
-        return lg[-1:]
+        M = pad_rows(int(ids.numel()))
+        self.tick(M, capi.stream_ptr())
+        return self.tp_bufs(M)["lg_l"][: int(ids.numel())]
 
     def generate_greedy(self, prompt: Any, max_new: int, graph_steps: int = 1) -> list[int]:
+        """prefill, the first token from the prompt's last row, then the captured step graph replayed"""
         prompt = torch.as_tensor(prompt, dtype=torch.int64)
         self.reset()
-        self.prefill(prompt)
+        last = self.prefill(prompt)
         g = self.bufs(1)
         s = capi.stream_ptr()
-        n = int(prompt.numel())
-        last_M = pad_rows(n - (n - 1) // 32 * 32)
-        # the last prompt row's slice sits in the last pass's buffer
-        t = self.tp_bufs(last_M)
-        keep = t["lg_l"][(n - 1) % 32 : (n - 1) % 32 + 1].clone()
-        self.tp_bufs(1)["lg_l"][:1].copy_(keep)
-        self._pick(g, 1, s, g["ids"])
+        self._pick({"logits_l": last.contiguous()}, 1, s, g["ids"], body_pass=False)
         toks = [int(g["ids"][0].item())]
+        graph = self.step_graph(1, publish=True)
         while len(toks) < max_new:
-            self._step_body_launches(s, publish=False)
+            graph.replay()
             torch.cuda.current_stream().synchronize()
-            toks.append(int(g["ids"][0].item()))
+            toks.append(int(self.pin_tok[0]))
         return toks

@@ -312,3 +312,135 @@ class MoECardPath:
             lg = self.forward([toks[-1]])
             toks.append(int(O.argmax_bf16(lg)[0]))
         return toks
+
+
+# --------------------------------------------------------------------------------------------------------------
+# gpt-oss in f32: what the reference's banked receipts for its tiny gpt-oss fixture were computed with
+# (tests/make_fixtures.py:1331-1366 `bank_gpt_oss`: transformers' GptOssForCausalLM in float32, eager attention,
+# experts dequantized from the stored MXFP4). The pieces are the oracle's own: the 16-lane GEMVs over the weights as
+# stored (native/src/gemv.rs:46-58, 1038-1119), the router's top-k then softmax (btb/engine/host.py:187-191), the
+# clamped GLU over interleaved lanes (host.py:444-450) and the sum in ascending expert id (host.py:565-569) - here
+# without the row dtype's roundings, since the receipts' activations are f32.
+# --------------------------------------------------------------------------------------------------------------
+
+
+class GptOssF32:
+    def __init__(self, cfg: dict, w: dict, cap: int = 128):
+        self.c, self.w = cfg, w
+        self.L, self.H, self.D = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["head_dim"]
+        self.Hq, self.Hk = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+        self.E, self.k = cfg["num_local_experts"], cfg["num_experts_per_tok"]
+        self.eps, self.win = np.float32(cfg["rms_norm_eps"]), int(cfg["sliding_window"])
+        self.limit, self.alpha = np.float32(cfg.get("swiglu_limit", 7.0)), np.float32(1.702)
+        self.inv_freq, self.att_scale = self._yarn(cfg)
+        self.K = np.zeros((self.L, cap, self.Hk, self.D), np.float32)
+        self.V = np.zeros_like(self.K)
+        self.n = 0
+
+    @classmethod
+    def from_fixture(cls, npz) -> "GptOssF32":
+        import json
+
+        cfg = json.loads(npz["config"].tobytes())
+        return cls(cfg, {k[2:]: npz[k] for k in npz.files if k.startswith("w/")})
+
+    @staticmethod
+    def _yarn(cfg: dict):
+        """the YaRN inverse frequencies and the attention factor applied to cos and sin (transformers'
+        `_compute_yarn_parameters`: interpolated and extrapolated frequencies blended by a linear ramp between the
+        dimensions that make beta_fast and beta_slow rotations over the original context)"""
+        import math
+
+        rs = cfg["rope_scaling"]
+        base, dim, factor = float(cfg["rope_theta"]), int(cfg["head_dim"]), float(rs["factor"])
+        orig = int(rs["original_max_position_embeddings"])
+
+        def corr(rot: float) -> float:
+            return (dim * math.log(orig / (rot * 2 * math.pi))) / (2 * math.log(base))
+
+        low, high = corr(float(rs["beta_fast"])), corr(float(rs["beta_slow"]))
+        if rs.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = np.clip((np.arange(dim // 2, dtype=np.float32) - np.float32(low)) / np.float32(high - low), 0, 1)
+        pos_freqs = np.float32(base) ** (np.arange(0, dim, 2, dtype=np.float32) / np.float32(dim))
+        extra, inter = np.float32(1) / pos_freqs, np.float32(1) / (np.float32(factor) * pos_freqs)
+        keep = (np.float32(1) - ramp).astype(np.float32)
+        inv = (inter * (np.float32(1) - keep) + extra * keep).astype(np.float32)
+        return inv, np.float32(0.1 * math.log(factor) + 1.0)
+
+    def _lin(self, name: str, x: np.ndarray) -> np.ndarray:
+        y = O.cpu_gemv_bf16(self.w[name + ".weight"], np.ascontiguousarray(x, np.float32))
+        b = self.w.get(name + ".bias")
+        return y if b is None else (y + O.bits_to_f32(b)[None, :]).astype(np.float32)
+
+    def _norm(self, name: str, h: np.ndarray) -> np.ndarray:
+        var = np.mean(h * h, axis=-1, keepdims=True, dtype=np.float32)
+        return (O.bits_to_f32(self.w[name + ".weight"])[None, :] * (h * (np.float32(1) / np.sqrt(var + self.eps)))).astype(np.float32)
+
+    def _rope(self, x: np.ndarray, pos: np.ndarray) -> np.ndarray:
+        ang = pos[:, None].astype(np.float32) * self.inv_freq[None, :]
+        cos, sin = (np.cos(ang) * self.att_scale)[:, None, :], (np.sin(ang) * self.att_scale)[:, None, :]
+        a, b = x[..., : self.D // 2], x[..., self.D // 2 :]
+        return np.concatenate([a * cos - b * sin, b * cos + a * sin], -1).astype(np.float32)
+
+    def _experts(self, p: str, x: np.ndarray) -> np.ndarray:
+        T = x.shape[0]
+        logits = self._lin(p + "router", x)
+        idx, _w = O.moe_route(logits, self.E, self.k, 1)  # the picks: top-k by value, lower index first among equals
+        out = np.zeros((T, self.H), np.float32)
+        gb, gs = self.w[p + "experts.gate_up_proj_blocks"], self.w[p + "experts.gate_up_proj_scales"]
+        db, ds = self.w[p + "experts.down_proj_blocks"], self.w[p + "experts.down_proj_scales"]
+        gbias, dbias = O.bits_to_f32(self.w[p + "experts.gate_up_proj_bias"]), O.bits_to_f32(self.w[p + "experts.down_proj_bias"])
+        for t in range(T):
+            top = logits[t, idx[t]]
+            ex = np.exp(top - top.max(), dtype=np.float32)
+            wts = ex / ex.sum(dtype=np.float32)
+            for s in np.argsort(idx[t], kind="stable"):  # ascending expert id
+                e = int(idx[t, s])
+                gu = O.cpu_gemv_mxfp4(gb[e], gs[e], gb.shape[1], gb.shape[2] * 32, x[t : t + 1])[0] + gbias[e]
+                g, u = np.minimum(gu[0::2], self.limit), np.clip(gu[1::2], -self.limit, self.limit)
+                hmid = ((u + np.float32(1)) * (g * (np.float32(1) / (np.float32(1) + np.exp(-g * self.alpha, dtype=np.float32))))).astype(np.float32)
+                y = O.cpu_gemv_mxfp4(db[e], ds[e], db.shape[1], db.shape[2] * 32, hmid[None, :])[0] + dbias[e]
+                out[t] += (y * wts[s]).astype(np.float32)
+        return out
+
+    def forward(self, ids) -> np.ndarray:
+        """a chain of rows after the cache's; f32 logits [T, V]"""
+        T, n0 = len(ids), self.n
+        pos = np.arange(n0, n0 + T)
+        G = self.Hq // self.Hk
+        h = O.bits_to_f32(self.w["model.embed_tokens.weight"][np.asarray(ids)])
+        sliding = [t == "sliding_attention" for t in self.c["layer_types"]]
+        for i in range(self.L):
+            p = f"model.layers.{i}."
+            x = self._norm(p + "input_layernorm", h)
+            q = self._rope(self._lin(p + "self_attn.q_proj", x).reshape(T, self.Hq, self.D), pos)
+            k = self._rope(self._lin(p + "self_attn.k_proj", x).reshape(T, self.Hk, self.D), pos)
+            v = self._lin(p + "self_attn.v_proj", x).reshape(T, self.Hk, self.D)
+            self.K[i, n0 : n0 + T], self.V[i, n0 : n0 + T] = k, v
+            sinks = O.bits_to_f32(self.w[p + "self_attn.sinks"])
+            att = np.zeros((T, self.Hq, self.D), np.float32)
+            for t in range(T):
+                last = n0 + t
+                first = max(0, last + 1 - self.win) if sliding[i] else 0
+                for hq in range(self.Hq):
+                    kk, vv = self.K[i, first : last + 1, hq // G], self.V[i, first : last + 1, hq // G]
+                    s = np.append((kk @ q[t, hq]) * np.float32(self.D**-0.5), sinks[hq]).astype(np.float32)
+                    pr = np.exp(s - s.max(), dtype=np.float32)
+                    pr = pr / pr.sum(dtype=np.float32)
+                    att[t, hq] = pr[:-1] @ vv  # the sink takes its share of the mass and contributes no value
+            h = h + self._lin(p + "self_attn.o_proj", att.reshape(T, -1))
+            x = self._norm(p + "post_attention_layernorm", h)
+            h = h + self._experts(p + "mlp.", x)
+        self.n = n0 + T
+        return self._lin("lm_head", self._norm("model.norm", h))
+
+    def greedy(self, prompt, n_new: int) -> list[int]:
+        lg = self.forward(list(prompt))
+        toks = [int(np.argmax(lg[-1]))]
+        while len(toks) < n_new:
+            toks.append(int(np.argmax(self.forward([toks[-1]])[-1])))
+        return toks

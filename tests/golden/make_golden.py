@@ -12,6 +12,9 @@ Outputs
                    banked by the reference's CPU path (prompt/tree/next logits, per-layer K/V, greedy tokens)
   sampling.npz     key_for() values for seeded (seed, position) pairs
   drafts.json      n-gram chains and merged trees from the reference's proposer over seeded token streams
+  moe.npz          the MoE block's host pieces run from the reference's own source: both routers' picks and weights, both
+                   gated activations in the row dtype, the down product's rounding, bias and ordered sum
+  tiny_gpt_oss.npz the tiny gpt-oss fixture's tensors as stored (MXFP4 experts) and its banked receipts
 """
 
 from __future__ import annotations
@@ -40,6 +43,7 @@ def codecs(ref: str, out: dict) -> None:
         "b": torch.randn(7, 24, generator=g) * torch.logspace(-12, 6, 24),  # many high bytes: dense escapes
         "c": torch.randn(5, 9, generator=g),  # odd element count
         "d": torch.zeros(4, 8),  # one high byte only
+        "e": torch.randn(96, 160, generator=g) * torch.logspace(-10, 4, 160),  # escapes across many 2048-element tiles
     }
     for name, t in cases.items():
         t = t.to(torch.bfloat16)
@@ -185,8 +189,101 @@ def drafts(ref: str) -> dict:
     return {"cases": cases}
 
 
+def _method(ref: str, rel: str, cls: str, name: str):
+    """a method of a class in a reference module that this image cannot import whole (it needs a newer transformers),
+    taken from the module's source and run on its own as a plain function of (self, ...)"""
+    import ast
+    from typing import Any
+
+    src = open(os.path.join(ref, rel)).read()
+    c = next(n for n in ast.parse(src).body if isinstance(n, ast.ClassDef) and n.name == cls)
+    fn = next(n for n in c.body if isinstance(n, ast.FunctionDef) and n.name == name)
+    fn.decorator_list = []
+    ns: dict = {"torch": torch, "Any": Any}
+    exec("from __future__ import annotations\n" + ast.unparse(fn), ns)  # noqa: S102
+    return ns[name]
+
+
+def moe(ref: str, out: dict) -> None:
+    """the host's MoE pieces (btb/engine/host.py `_Router`, `_Experts`; families/qwen4/router.py `Qwen4Router`) executed
+    from the reference's source on seeded rows"""
+    from types import SimpleNamespace as NS
+
+    g = torch.Generator().manual_seed(4321)
+    # routers: f32 logits in (what the host GEMV hands them), bf16 rows
+    for tag, E, k in (("a", 32, 4), ("b", 128, 8), ("c", 8, 2)):
+        lg = torch.randn(6, E, generator=g) * 2.0
+        hidden = torch.zeros(6, 4, dtype=torch.bfloat16)
+        lin = lambda x, lg=lg: lg  # noqa: E731  the router's matvec is pinned elsewhere; the picks are what is banked here
+        r1 = _method(ref, "btb/engine/host.py", "_Router", "forward")
+        _lg, scores, idx = r1(NS(lin=lin, top_k=k), hidden)
+        out[f"route_{tag}_logits"] = lg.numpy()
+        out[f"route_{tag}_m1_idx"], out[f"route_{tag}_m1_w"] = idx.numpy().astype(np.int32), bits(scores)
+        r0 = _method(ref, "btb/engine/families/qwen4/router.py", "Qwen4Router", "forward")
+        _l, wts, ex = r0(NS(lin=lin, top_k=k, hidden_dim=4, norm_topk_prob=True), hidden)
+        out[f"route_{tag}_m0_idx"], out[f"route_{tag}_m0_w"] = ex.numpy().astype(np.int32), bits(wts)
+    # the gated activations in the row dtype, with and without the bias
+    gate1 = _method(ref, "btb/engine/host.py", "_Experts", "gpt_oss_gate")
+    silu_gate = _method(ref, "btb/engine/host.py", "_Experts", "_silu_gate")
+    act = _method(ref, "btb/engine/host.py", "_Experts", "_act")
+    bias_of = _method(ref, "btb/engine/host.py", "_Experts", "_bias")
+    down = _method(ref, "btb/engine/host.py", "_Experts", "_down")
+    n, I, H, E = 8, 48, 40, 6
+    gu = torch.randn(n, 2 * I, generator=g) * 3.0  # past the clamp at 7 on both sides
+    rows = torch.randint(0, E, (n,), generator=g)
+    b_gu = (torch.randn(E, 2 * I, generator=g) * 0.5).to(torch.bfloat16)
+    b_dn = (torch.randn(E, H, generator=g) * 0.5).to(torch.bfloat16)
+    out["act_gu"], out["act_rows"] = gu.numpy(), rows.numpy().astype(np.int32)
+    out["act_bias_gu"], out["act_bias_dn"] = bits(b_gu), bits(b_dn)
+    for kind, gate in ((0, None), (1, gate1)):
+        for biased in (False, True):
+            me = NS(biased=biased, gate=gate, alpha=1.702, limit=7.0, gate_up_proj_bias=b_gu, _bias=bias_of,
+                    act_fn=torch.nn.functional.silu)  # fmt: skip
+            me._silu_gate = lambda x, me=me: silu_gate(me, x)
+            got = act(me, gu.to(torch.bfloat16), rows)
+            assert got.dtype == torch.bfloat16
+            out[f"act_k{kind}_b{int(biased)}"] = bits(got)
+    # the down product's rounding and bias, the routing weight, and the sum one expert at a time in ascending id
+    # (host.py `_one_row`: out[i] = _down(dn_buf[i], hit[i], dt) * weights[slot]; final[0] += out[i], hit ascending)
+    T, k = 5, 4
+    dn = torch.randn(T, k, H, generator=g) * 2.0
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])  # the router's order, not sorted
+    w = torch.softmax(torch.randn(T, k, generator=g), -1).to(torch.bfloat16)
+    out["comb_dn"], out["comb_idx"], out["comb_w"] = dn.numpy(), idx.numpy().astype(np.int32), bits(w)
+    for biased in (False, True):
+        me = NS(biased=biased, down_proj_bias=b_dn, _bias=bias_of)
+        fin = torch.zeros(T, H, dtype=torch.bfloat16)
+        for t in range(T):
+            hit = sorted(int(e) for e in idx[t])
+            slot = {e: idx[t].tolist().index(e) for e in hit}
+            for e in hit:
+                fin[t] += down(me, dn[t, slot[e]], e, torch.bfloat16) * w[t][slot[e]]
+        out[f"comb_b{int(biased)}"] = bits(fin)
+
+
+def tiny_moe(ref: str, out: dict) -> None:
+    """the reference's tiny gpt-oss fixture as stored, and its banked receipts (transformers' f32 forward)"""
+    from safetensors import safe_open
+
+    fx = os.path.join(ref, "tests", "fixtures")
+    d = os.path.join(fx, "tiny_gpt_oss")
+    idx = json.load(open(os.path.join(d, "model.safetensors.index.json")))
+    out["config"] = np.frombuffer(open(os.path.join(d, "config.json"), "rb").read(), np.uint8)
+    for shard in sorted(set(idx["weight_map"].values())):
+        with safe_open(os.path.join(d, shard), "pt") as f:
+            for k in f.keys():
+                v = f.get_tensor(k)
+                out["w/" + k] = v.numpy() if v.dtype == torch.uint8 else bits(v)
+    rc = torch.load(os.path.join(fx, "receipts_gpt_oss.pt"), weights_only=False)["host"]
+    out["rc/prompt"], out["rc/cont"] = np.asarray(rc["prompt"][0], np.int64), np.asarray(rc["cont"][0], np.int64)
+    out["rc/prompt_logits"], out["rc/next"] = rc["prompt_logits"].numpy(), rc["next"].numpy()
+    out["rc/greedy"] = np.asarray(rc["greedy"], np.int64)
+
+
 def main() -> None:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 and not os.environ.get("BTB_REFERENCE"):
+        raise SystemExit("usage: make_golden.py <reference checkout> (or BTB_REFERENCE=<checkout>)")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ["BTB_REFERENCE"]
     sys.path.insert(0, ref)
     a: dict = {}
     codecs(ref, a)
@@ -199,7 +296,13 @@ def main() -> None:
     np.savez_compressed(os.path.join(HERE, "sampling.npz"), **c)
     with open(os.path.join(HERE, "drafts.json"), "w") as f:
         json.dump(drafts(ref), f, separators=(",", ":"))
-    for f in ("codecs.npz", "tiny_qwen3.npz", "sampling.npz", "drafts.json"):
+    d: dict = {}
+    moe(ref, d)
+    np.savez_compressed(os.path.join(HERE, "moe.npz"), **d)
+    e: dict = {}
+    tiny_moe(ref, e)
+    np.savez_compressed(os.path.join(HERE, "tiny_gpt_oss.npz"), **e)
+    for f in ("codecs.npz", "tiny_qwen3.npz", "sampling.npz", "drafts.json", "moe.npz", "tiny_gpt_oss.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 

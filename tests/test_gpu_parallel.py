@@ -1,6 +1,8 @@
-"""Tensor-parallel and expert-parallel engines on the card: one rank equals the plain engine; two or more ranks (when
-the box has them) equal one GPU's tokens."""
+"""The tensor-parallel engine and its peer-store exchange on the card: one rank equals the plain engine; N ranks taking
+turns on ONE GPU (tests/lockstep.py) equal it too - slices, offsets, arrival counts and the merged pick all at work;
+a wait nobody answers gives up with ERR_TIMEOUT instead of hanging; and, when the box has them, two real GPUs equal one."""
 
+import ctypes as C
 import os
 import subprocess
 import sys
@@ -13,9 +15,13 @@ pytestmark = pytest.mark.gpu
 if not torch.cuda.is_available():
     pytest.skip("needs a CUDA device", allow_module_level=True)
 
+from btb_b200 import capi  # noqa: E402
 from btb_b200 import engine as E  # noqa: E402
-from .util import LAYER_STD, lively  # noqa: E402
 from btb_b200 import parallel as P  # noqa: E402
+from btb_b200.capi import call, ptr  # noqa: E402
+
+from . import lockstep  # noqa: E402
+from .util import LAYER_STD, lively  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -27,12 +33,65 @@ def test_one_rank_tensor_parallel_engine_equals_the_plain_engine():
     want = plain.generate_greedy(prompt, 12)
     lively(want)
     tp = P.TPEngine(cfg, P.shard_dense(E.synth_weights(cfg, seed=9, on_cpu=True, layer_std=LAYER_STD), 0, 1), 0, 1, cap=512)
-    assert tp.generate_greedy(prompt, 12) == want
+    assert tp.generate_greedy(prompt, 12) == want  # prefill passes, then the captured step graph with its exchanges
     # the pass's logits too, bit for bit
     plain.reset()
     tp.reset()
     a, b = plain.forward(prompt[:20]), tp.forward(prompt[:20])
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert capi.status() == 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_taking_turns_on_one_gpu_equal_the_plain_engine(world):
+    cfg = E.DenseConfig("tpN", hidden=256 * world, layers=3, q_heads=4 * world, kv_heads=world, head_dim=128,
+                        inter=256 * world, vocab=160 * world)  # fmt: skip
+    draw = lambda: E.synth_weights(cfg, seed=4, on_cpu=True, layer_std=LAYER_STD)  # noqa: E731
+    plain = E.CardEngine(draw(), cap=512, step_kernel=False)
+    prompt = torch.arange(3, 48) % cfg.vocab
+    want = plain.generate_greedy(prompt, 16)
+    lively(want)
+    engs = lockstep.make(cfg, draw, world)
+    got = lockstep.greedy(engs, prompt, 16)
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    assert all(g == want for g in got), (got, want)
+    # a wide pass (the separate norm kernels, waits as launches of their own) and a narrow one: every rank's slice of
+    # the logits is the plain engine's columns, bit for bit
+    for T in (20, 3, 1):
+        plain.reset()
+        for e in engs:
+            e.reset()
+        full = plain.forward(prompt[:T])
+        parts = lockstep.forward(engs, prompt[:T])
+        assert torch.equal(torch.cat(parts, dim=1).view(torch.int16), full.view(torch.int16)), T
+    # each rank's copy of an exchanged vector holds every rank's slice: the copies are equal
+    for k in ("att_t", "yo_t", "m_t", "yd_t"):
+        for e in engs[1:]:
+            assert torch.equal(e.tp_bufs(1)[k].view(torch.int16), engs[0].tp_bufs(1)[k].view(torch.int16)), k
+    assert capi.status() == 0
+
+
+def test_a_wait_nobody_answers_gives_up():
+    """a consumer whose producers never arrive (a peer that died between steps) returns after about a second with
+    ERR_TIMEOUT in the status word; the context stays usable"""
+    flag = torch.zeros(16, dtype=torch.int32, device="cuda")
+    pas = torch.zeros(1, dtype=torch.int32, device="cuda")
+    w = capi.Wait(ptr(flag), ptr(pas), 3)
+    call("btb_b200_xchg_wait", w, capi.stream_ptr())
+    torch.cuda.synchronize()
+    assert capi.status() == capi.ERR_TIMEOUT
+    # the arrivals in: the same wait returns at once
+    flag[0] = 3
+    call("btb_b200_xchg_wait", w, capi.stream_ptr())
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    n = C.c_int(0)
+    x = torch.ones(1, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(capi.NativeError):  # a slice that does not fit its vector is refused on the host
+        s = capi.Send()
+        s.out[0], s.flag[0], s.n, s.stride, s.offset = ptr(x), ptr(flag), 1, 64, 32
+        call("btb_b200_xchg_send", ptr(x), 1, 64, 2, None, s, C.byref(n), capi.stream_ptr())
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

@@ -129,9 +129,10 @@ def test_engine_sampled_loop_draws_what_the_sequential_keys_draw():
     # temperature, top-p and seed are data to the captured graph; greedy comes back as the argmax loop
     hot = eng.generate(prompt, 12, Sampling(temperature=5.0, top_k=40, top_p=1.0, seed=7))
     assert hot != toks[:12]
+    got = eng.generate(prompt, 12, Sampling())  # the sampling set back to greedy
     want = eng.generate_greedy(prompt, 12)
     lively(want)
-    assert eng.generate(prompt, 12, Sampling()) == want
+    assert got == want
 
 
 # ---- the reference's own pipeline, launch by launch, through both launchers --------------------------------------
