@@ -465,9 +465,7 @@ STORED = {"p12": "pack12", "mx4": "MXFP4 expert", "fp8": "FP8 block-scaled"}
 
 def tp_collective(eng, cfg, world, dist) -> dict:
     """what the tensor-parallel step exchanges, and one hop of it timed on its own: every rank sends its slice of a
-    hidden-size vector to every rank and waits for everyone's (CUDA events around 200 hops in a row, max over ranks)"""
-    import ctypes as C
-
+    hidden-size vector to every rank and takes everyone's (CUDA events around 200 hops in a row, max over ranks)"""
     import torch
 
     from btb_b200 import capi
@@ -476,42 +474,36 @@ def tp_collective(eng, cfg, world, dist) -> dict:
     t = eng.tp_bufs(1)
     H, A, I = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.inter
     src = torch.zeros(1, H // world, dtype=torch.bfloat16, device="cuda")
-    n = C.c_int(0)
+    dst = torch.zeros(1, H, dtype=torch.bfloat16, device="cuda")
     s = capi.stream_ptr()
     hops = 200
-    # the probe uses the last layer's `yd` vector and its counter; one pass of the probe = one hop, then a tick
-    send = t["send_yd"][cfg.layers - 1]
+    # the probe borrows the `yd` vector of width 1 with a pass count of its own, started well past the marks the decode
+    # left in it (every rank has made the same passes, so every rank starts the probe at the same number)
     torch.cuda.synchronize()
-    dist.barrier()
+    start = int(eng.passes[0, 0].item()) * 4 * cfg.layers + 4 * cfg.layers + 1000
+    probe = torch.full((1,), start, dtype=torch.int32, device="cuda")
+    send = eng.heap.send_desc(eng.off[1]["yd"], H, eng.rank * (H // world), ptr(probe), 1, 1)
+    recv = capi.Recv(ptr(probe), 1, 1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    flag_off = eng.flag_off(1, cfg.layers - 1, "yd")
-    # the counter has seen the decode's passes: start the probe's own count from where it stands
-    base = eng.heap.tensor(flag_off, (1,), torch.int32)
-    probe_pass = torch.zeros(1, dtype=torch.int32, device="cuda")
-    torch.cuda.synchronize()
-    dist.barrier()
-    start = int(base[0].item())
-    assert start % world == 0
-    probe_pass[0] = start // world
-    w = capi.Wait(eng.heap.local + flag_off, ptr(probe_pass), world)
     torch.cuda.synchronize()
     dist.barrier()
     e0.record()
     for _ in range(hops):
-        call("btb_b200_xchg_send", ptr(src), 1, H // world, 2, None, send, C.byref(n), s)
-        call("btb_b200_xchg_wait", w, s)
-        call("btb_b200_xchg_tick", ptr(probe_pass), s)
+        call("btb_b200_xchg_send", ptr(src), 1, H // world, send, s)
+        call("btb_b200_xchg_unpack", t["yd"], ptr(dst), 1, H, recv, s)
+        call("btb_b200_xchg_tick", ptr(probe), s)
     e1.record()
     torch.cuda.synchronize()
     us = torch.tensor([e0.elapsed_time(e1) * 1000.0 / hops], device="cuda")
     dist.all_reduce(us, op=dist.ReduceOp.MAX)
     assert capi.status() == 0, "the exchange probe timed out"
-    per_step = cfg.layers * 2 * (A + 2 * H + I)  # bytes of activation vectors a step assembles on every rank
-    return {"kind": "peer stores into every rank's copy + arrival counters (NVLink writes, no collective call, no "
-                    "reduction), folded into the producing kernels' epilogues",
-            "hops_per_step": 4 * cfg.layers + 1, "bytes_per_step_per_rank_received": per_step * (world - 1) // world,
-            "us_per_hop_alone": float(us[0]), "note": "a hop alone = 3 launches (send, wait, tick) on an idle stream; "
-            "inside the step the send and the wait are parts of the GEMV kernels"}
+    per_step = cfg.layers * 4 * (A + 2 * H + I)  # bytes of marked words a step assembles in every rank's copies
+    return {"kind": "peer stores of marked words into every rank's copy (NVLink writes; no collective call, no fence or "
+                    "flag, no reduction), folded into the producing kernels' epilogues and the consuming kernels' prologues",
+            "hops_per_step": 4 * cfg.layers + 1, "bytes_per_step_received_per_rank": per_step * (world - 1) // world,
+            "us_per_hop_alone": float(us[0]), "note": "a hop alone = 3 launches (send, take, tick) on an idle stream; "
+            "inside the step the send and the take are parts of the GEMV kernels"}
+
 
 def run_case(args) -> None:
     """one kernel on a small case, for a profiler capture or a quick look: `gemv:RxC[:M[:fmt]]` rotates over enough

@@ -116,30 +116,31 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
 
 
 
-class Wait(C.Structure):
-    """`btb_b200_wait` of the header: what a consumer of an exchanged vector waits on"""
+class Recv(C.Structure):
+    """`btb_b200_recv` of the header: how a consumer knows a word of its hop"""
 
-    _fields_ = [("flag", C.c_void_p), ("pass_", C.c_void_p), ("per_pass", C.c_uint)]
+    _fields_ = [("pass_", C.c_void_p), ("per_pass", C.c_uint), ("base", C.c_uint)]
 
 
 class Send(C.Structure):
-    """`btb_b200_send` of the header: every rank's copy of a vector and its arrival counter"""
+    """`btb_b200_send` of the header: every rank's copy of a vector and the hop's number"""
 
-    _fields_ = [("out", C.c_void_p * 8), ("flag", C.c_void_p * 8), ("n", C.c_int), ("stride", C.c_int), ("offset", C.c_int)]
+    _fields_ = [("out", C.c_void_p * 8), ("n", C.c_int), ("stride", C.c_int), ("offset", C.c_int), ("pass_", C.c_void_p),
+                ("per_pass", C.c_uint), ("base", C.c_uint)]  # fmt: skip
 
 
-_WP, _SP, _IP = C.POINTER(Wait), C.POINTER(Send), C.POINTER(C.c_int)
+_RP, _SP = C.POINTER(Recv), C.POINTER(Send)
 SIGNATURES.update({
     "btb_b200_peer_alloc": (_I, [_SZ, C.POINTER(C.c_void_p)]),
     "btb_b200_peer_free": (_I, [_P]),
     "btb_b200_peer_handle": (_I, [_P, C.POINTER(C.c_ubyte)]),
     "btb_b200_peer_open": (_I, [C.POINTER(C.c_ubyte), C.POINTER(C.c_void_p)]),
     "btb_b200_peer_close": (_I, [_P]),
-    "btb_b200_gemv_bf16_x": (_I, [_P, _P, _P, _I, _I, _I, _WP, _SP, _IP, _P]),
-    "btb_b200_gemv_norm_x": (_I, [_P, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _I, _WP, _SP, _IP, _P]),
-    "btb_b200_xchg_send": (_I, [_P, _I, _I, _I, _WP, _SP, _IP, _P]),
-    "btb_b200_xchg_pick": (_I, [_P, _I, _I, _I, _P, _I, _WP, _SP, _P, _P, _I, _P]),
-    "btb_b200_xchg_wait": (_I, [_WP, _P]),
+    "btb_b200_gemv_bf16_x": (_I, [_P, _P, _P, _I, _I, _I, _RP, _SP, _P]),
+    "btb_b200_gemv_norm_x": (_I, [_P, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _I, _RP, _SP, _P]),
+    "btb_b200_xchg_send": (_I, [_P, _I, _I, _SP, _P]),
+    "btb_b200_xchg_unpack": (_I, [_P, _P, _I, _I, _RP, _P]),
+    "btb_b200_xchg_pick": (_I, [_P, _I, _I, _I, _P, _I, _I, C.POINTER(C.c_void_p), _P, _P, _P, _I, _P]),
     "btb_b200_xchg_tick": (_I, [_P, _P]),
 })  # fmt: skip
 

@@ -18,7 +18,6 @@
 #include "common.cuh"
 #include "btb_b200_internal.h"
 #include "gemv_core.cuh"
-#include "tp.cuh"
 #include "../../include/btb_b200.h"
 
 B2_DEFINE_STATUS(gemv)
@@ -57,10 +56,10 @@ struct GemvArgs {
     // after the other and writes y[m][p] = bf16(bf16(silu(bf16 g)) * bf16 u) - what btb_silu_mul makes of the two
     // outputs. 0: off. R counts pairs then.
     int pair;
-    // a model cut over ranks by output rows (tp.cuh): `wait` holds back the read of x (or of y_add) until every rank's
-    // slice of it has arrived; with `send.n > 0` every output element goes to each rank's copy of the full vector at
-    // [m][send.offset + row] instead of y, and the CTA adds its arrival to each rank's counter when its rows are done
-    B2Wait wait;
+    // a model cut over ranks by output rows (tp.cuh): with `recv.pass` set, x (or y_add under the norm prologue) is this
+    // rank's copy of an exchanged vector, read word by word as the words arrive; with `send.n > 0` every output element
+    // goes, marked, to each rank's copy of the full vector at [m][send.offset + row] instead of y
+    B2Recv recv;
     B2Send send;
 };
 
@@ -145,17 +144,17 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
 
     pdl_launch_dependents();
     pdl_wait();  // x is the previous kernel's output
-    if (A.wait.flag != nullptr) {  // ... or, in a model cut over ranks, every rank's: wait for the last slice
-        if (threadIdx.x == 0) b2_wait_arrivals(A.wait);
-        __syncthreads();
-    }
+    // ... or, in a model cut over ranks, every rank's: the words are taken as they arrive
+    const bool marked = A.recv.pass != nullptr;
+    const uint32_t mark_in = marked ? b2_hop_mark(A.recv.pass, A.recv.per_pass, A.recv.base) : 0u;
+    const uint32_t mark_out = A.send.n != 0 ? b2_hop_mark(A.send.pass, A.send.per_pass, A.send.base) : 0u;
 
     if (XS) {
-        if (XM == X_SMEM) stage_x_copy<M, NT>(xs, A.x, C);
+        if (XM == X_SMEM) stage_x_copy<M, NT>(xs, A.x, C, marked, mark_in);
         else if (XM == X_SMEM_SILU) stage_x_silu<M, NT>(xs, A.x, C);
         else
             stage_x_norm<M, NT>(xs, reinterpret_cast<float*>(smem), A.h_in, nullptr, A.y_add, A.norm_w, A.h_out, A.eps,
-                                A.centered, A.T, C, blockIdx.x == 0);
+                                A.centered, A.T, C, blockIdx.x == 0, marked, mark_in);
         __syncthreads();
     }
 
@@ -202,8 +201,9 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
                         A.y[(size_t)m * R + c_row] = v;
                     } else {
                         const size_t at = (size_t)m * A.send.stride + A.send.offset + c_row;
+                        const uint32_t word = b2_word(v, mark_out);
 #pragma unroll 1
-                        for (int p = 0; p < A.send.n; ++p) static_cast<bf16*>(A.send.out[p])[at] = v;
+                        for (int p = 0; p < A.send.n; ++p) A.send.out[p][at] = word;
                     }
                 }
                 acc[m] = 0.f;
@@ -234,10 +234,6 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
             }
             mbar_wait_bounded(smem_u32(bars + c_st), c_par);
         }
-    }
-    if (A.send.n != 0) {  // every warp's rows are stored: publish them and arrive at every rank
-        __syncthreads();
-        b2_signal_arrival(A.send);
     }
 }
 
@@ -388,26 +384,26 @@ extern "C" int btb_b200_p12_rows(const void* esc_idx, int n_esc, int R, int C, v
 }
 
 // the exchange descriptors of the C-ABI (include/btb_b200.h) into the kernels' own; refuses what a kernel could fault on
-static int take_exchange(const btb_b200_wait* wait, const btb_b200_send* send, GemvArgs& a) {
-    if (wait != nullptr && wait->flag != nullptr) {
-        if (wait->pass == nullptr) return B2_ERR_NULL;
-        a.wait = B2Wait{static_cast<const unsigned*>(wait->flag), static_cast<const unsigned*>(wait->pass), wait->per_pass};
-    }
+static int take_exchange(const btb_b200_recv* recv, const btb_b200_send* send, GemvArgs& a) {
+    if (recv != nullptr && recv->pass != nullptr)
+        a.recv = B2Recv{static_cast<const unsigned*>(recv->pass), recv->per_pass, recv->base};
     if (send != nullptr && send->n != 0) {
         if (send->n < 0 || send->n > B2_MAX_RANKS || send->stride <= 0 || send->offset < 0 ||
             send->offset + a.R > send->stride)
             return B2_ERR_DOMAIN;
+        if (send->pass == nullptr) return B2_ERR_NULL;
         a.send.n = send->n, a.send.stride = send->stride, a.send.offset = send->offset;
+        a.send.pass = static_cast<const unsigned*>(send->pass), a.send.per_pass = send->per_pass, a.send.base = send->base;
         for (int p = 0; p < send->n; ++p) {
-            if (send->out[p] == nullptr || send->flag[p] == nullptr) return B2_ERR_NULL;
-            a.send.out[p] = send->out[p], a.send.flag[p] = static_cast<unsigned*>(send->flag[p]);
+            if (send->out[p] == nullptr || (reinterpret_cast<uintptr_t>(send->out[p]) & 15)) return B2_ERR_NULL;
+            a.send.out[p] = static_cast<uint32_t*>(send->out[p]);
         }
     }
     return B2_OK;
 }
 
-static int gemv_bf16_impl(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_wait* wait,
-                          const btb_b200_send* send, int* ctas, void* stream) {
+static int gemv_bf16_impl(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_recv* recv,
+                          const btb_b200_send* send, void* stream) {
     const bool sends = send != nullptr && send->n != 0;
     int rc = check_dims(w, x, sends ? w : y, M, R, C);  // a sending launch has no local y
     if (rc) return rc;
@@ -416,21 +412,22 @@ static int gemv_bf16_impl(const void* w, const void* x, void* y, int M, int R, i
     a.x = static_cast<const bf16*>(x);
     a.y = static_cast<bf16*>(y);
     a.R = R, a.C = C;
-    if ((rc = take_exchange(wait, send, a)) != B2_OK) return rc;
+    if ((rc = take_exchange(recv, send, a)) != B2_OK) return rc;
     Plan p = make_plan<F_BF16>(M, R, C, M <= 8);
+    // an exchanged x is decoded on its way into shared memory: a pass too wide to stage x takes btb_b200_xchg_unpack first
+    if (a.recv.pass != nullptr && !p.xs) return B2_ERR_DOMAIN;
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
-    if (ctas != nullptr) *ctas = p.grid;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return p.xs ? launch_m<F_BF16, X_SMEM>(M, a, p, s) : launch_m_global<F_BF16>(M, a, p, s);
 }
 
 extern "C" int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* stream) {
-    return gemv_bf16_impl(w, x, y, M, R, C, nullptr, nullptr, nullptr, stream);
+    return gemv_bf16_impl(w, x, y, M, R, C, nullptr, nullptr, stream);
 }
 
-extern "C" int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_wait* wait,
-                                    const btb_b200_send* send, int* ctas, void* stream) {
-    return gemv_bf16_impl(w, x, y, M, R, C, wait, send, ctas, stream);
+extern "C" int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_recv* recv,
+                                    const btb_b200_send* send, void* stream) {
+    return gemv_bf16_impl(w, x, y, M, R, C, recv, send, stream);
 }
 
 // x = rmsnorm(h_in + y) * w computed inside the GEMV (bf16 weights, or pack12 when hi4 is not null); swiglu: the rows are
@@ -438,7 +435,7 @@ extern "C" int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M
 static int gemv_norm_impl(const void* w, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
                           const void* esc_row, const void* h_in, const void* y_add, const void* norm_w, float eps,
                           int centered, void* h_out, void* y, int T, int M, int R, int C, bool swiglu, void* stream,
-                          const btb_b200_wait* wait = nullptr, const btb_b200_send* send = nullptr, int* ctas = nullptr) {
+                          const btb_b200_recv* recv = nullptr, const btb_b200_send* send = nullptr) {
     const bool sends = send != nullptr && send->n != 0;
     int rc = check_dims(w, h_in, sends ? w : y, M, R, C);
     if (rc) return rc;
@@ -462,11 +459,11 @@ static int gemv_norm_impl(const void* w, const void* hi4, const void* table, con
     a.h_in = static_cast<const bf16*>(h_in), a.y_add = static_cast<const bf16*>(y_add);
     a.norm_w = static_cast<const bf16*>(norm_w), a.h_out = static_cast<bf16*>(h_out);
     a.eps = eps, a.centered = centered, a.T = T;
-    if ((rc = take_exchange(wait, send, a)) != B2_OK) return rc;
+    if ((rc = take_exchange(recv, send, a)) != B2_OK) return rc;
+    if (a.recv.pass != nullptr && y_add == nullptr) return B2_ERR_NULL;  // the exchanged input of this form is y_add
     Plan p = p12 ? make_plan<F_P12>(M, a.R, C, true, true) : make_plan<F_BF16>(M, a.R, C, true, true);
     if (!p.xs) return B2_ERR_DOMAIN;  // too wide to stage: the caller runs btb_b200_add_rmsnorm and the plain GEMV
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
-    if (ctas != nullptr) *ctas = p.grid;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return p12 ? launch_m<F_P12, X_SMEM_NORM>(M, a, p, s) : launch_m<F_BF16, X_SMEM_NORM>(M, a, p, s);
 }
@@ -487,13 +484,13 @@ extern "C" int btb_b200_gemv_norm_swiglu(const void* w, const void* hi4, const v
                           R, C, true, stream);
 }
 
-// btb_b200_gemv_norm / _norm_swiglu over bf16 weights in a model cut over ranks: the wait holds back the read of y_add
-// (every rank's slice of the previous block's output), the outputs go to every rank's copy of the next vector
+// btb_b200_gemv_norm / _norm_swiglu over bf16 weights in a model cut over ranks: with `recv`, y_add is this rank's copy
+// of the previous block's exchanged output (marked words); with `send`, the outputs go to every rank's copy of the next
 extern "C" int btb_b200_gemv_norm_x(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps,
                                     int centered, void* h_out, void* y, int T, int M, int R, int C, int swiglu,
-                                    const btb_b200_wait* wait, const btb_b200_send* send, int* ctas, void* stream) {
+                                    const btb_b200_recv* recv, const btb_b200_send* send, void* stream) {
     return gemv_norm_impl(w, nullptr, nullptr, nullptr, nullptr, nullptr, h_in, y_add, norm_w, eps, centered, h_out, y, T, M,
-                          R, C, swiglu != 0, stream, wait, send, ctas);
+                          R, C, swiglu != 0, stream, recv, send);
 }
 
 // FP8 e4m3 weights with an f32 [sr, sc] block-scale grid, each weight the bf16 btb holds for it, widened in registers

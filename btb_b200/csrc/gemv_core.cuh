@@ -7,6 +7,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "tp.cuh"
 
 enum Fmt { F_BF16 = 0, F_P12 = 1, F_FP8 = 2 };
 
@@ -87,11 +88,16 @@ static __device__ __noinline__ uint32_t p12_escape(const int32_t* __restrict__ e
 
 // ---- x into shared memory ------------------------------------------------------------------------------------------
 
-// x [M, C] bf16 as is
+// x [M, C] bf16 as is; `marked`: x is this rank's copy of an exchanged vector (u32 words [M, C], tp.cuh), each element
+// taken once it carries this hop's `mark`
 template <int M, int NT>
-__device__ __forceinline__ void stage_x_copy(bf16* xs, const bf16* x, int C) {
+__device__ __forceinline__ void stage_x_copy(bf16* xs, const bf16* x, int C, bool marked = false, uint32_t mark = 0u) {
     uint4* dst = reinterpret_cast<uint4*>(xs);
     const int nt = NT > 0 ? NT : (int)blockDim.x;  // NT 0: the block's width is a launch parameter
+    if (marked) {
+        for (int i = threadIdx.x; i < M * C / 8; i += nt) dst[i] = b2_take8(reinterpret_cast<const uint32_t*>(x) + (size_t)i * 8, mark);
+        return;
+    }
     for (int i = threadIdx.x; i < M * C / 8; i += nt) dst[i] = ldcg16(reinterpret_cast<const uint4*>(x) + i);
 }
 
@@ -141,7 +147,8 @@ __device__ __forceinline__ void stage_x_silu(bf16* xs, const bf16* gu, int C) {
 template <int M, int NT, bool PRE = true>
 __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf16* h_in, const long long* rows,
                                              const bf16* y_add, const bf16* norm_w, bf16* h_out, float eps,
-                                             int centered, int T, int C, bool writer) {
+                                             int centered, int T, int C, bool writer, bool marked = false,
+                                             uint32_t mark = 0u) {
     float* hsm = scratch;
     float* red = hsm + C;
     const int cv = C >> 3, tid = threadIdx.x;
@@ -163,7 +170,9 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
             const uint4 hv = ldcg16(reinterpret_cast<const uint4*>(hrow) + i);
             uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
             if (y_add != nullptr) {
-                const uint4 yv = ldcg16(reinterpret_cast<const uint4*>(y_add + (size_t)m * C) + i);
+                // (in a model cut over ranks y_add is this rank's copy of an exchanged vector: words with marks)
+                const uint4 yv = marked ? b2_take8(reinterpret_cast<const uint32_t*>(y_add) + (size_t)m * C + (size_t)i * 8, mark)
+                                        : ldcg16(reinterpret_cast<const uint4*>(y_add + (size_t)m * C) + i);
                 const uint32_t yw[4] = {yv.x, yv.y, yv.z, yv.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {

@@ -1,11 +1,11 @@
 """Peer-mapped memory and the exchange descriptors of a model cut over the GPUs of one box (one process a GPU).
 
-The exchange itself is device code (csrc/tp.cuh): producers store finished elements into every rank's copy of an
-activation vector and count their CTAs' arrivals into every rank's counters; consumers wait on their local counter and
-read their local copy. This module sets that up: a `PeerHeap` is one allocation of the same size and layout on every
+The exchange itself is device code (csrc/tp.cuh): producers store every finished element, marked with its hop's
+sequence number, into every rank's copy of an activation vector; consumers read their local copy and take each word
+once it carries the mark. This module sets that up: a `PeerHeap` is one allocation of the same size and layout on every
 rank, each rank's mapped into every process (CUDA IPC handles handed round through the process group at set-up; plain
 pointers when the "ranks" are engines of one process, which is how a single GPU exercises the N-rank data path in
-lockstep); `carve` hands out equal offsets on every rank; `send_desc` / `wait_desc` build the C-ABI's descriptors.
+lockstep); `carve` hands out equal offsets on every rank; `send_desc` builds the C-ABI's descriptor.
 """
 
 from __future__ import annotations
@@ -16,7 +16,7 @@ from typing import Any
 import torch
 
 from . import capi
-from .capi import Send, Wait, call
+from .capi import Send, call
 
 
 class PeerHeap:
@@ -89,16 +89,10 @@ class PeerHeap:
         return torch.as_tensor(_Mem(), device="cuda").view(dtype).reshape(shape)
 
     # -- descriptors ---------------------------------------------------------------------------------------------------
-    def send_desc(self, buf_off: int, flag_off: int, stride: int, offset: int) -> Send:
+    def send_desc(self, buf_off: int, stride: int, offset: int, pass_ptr: int, per_pass: int, base: int) -> Send:
         s = Send()
         for r in range(self.world):
             s.out[r] = self.base[r] + buf_off
-            s.flag[r] = self.base[r] + flag_off
         s.n, s.stride, s.offset = self.world, int(stride), int(offset)
+        s.pass_, s.per_pass, s.base = pass_ptr, int(per_pass), int(base)
         return s
-
-    def wait_desc(self, flag_off: int, pass_ptr: int, per_pass: int) -> Wait:
-        return Wait(self.local + flag_off, pass_ptr, int(per_pass))
-
-
-FLAG_BYTES = 64  # a counter a 64-byte line: arrivals for different vectors never share a sector

@@ -6,9 +6,10 @@ btb has no multi-GPU path, so the contract here is bit-identity with the one-GPU
   the hidden size, gate and up by the same rows of the intermediate size (paired), the head by vocabulary rows - so
   each output element's whole K-sum stays on one GPU in the one-GPU order. Attention is cut by kv head; a rank holds
   only its heads' cache. What a rank lacks of an activation vector its peers write into its memory: the producing
-  kernel's epilogue stores every finished element into every rank's copy and counts its CTAs' arrivals, the consuming
-  kernel's prologue waits on its local counter (csrc/tp.cuh) - four such hops a layer, no collective call, no reduction
-  (hence no change of summation order), and the whole step stays one captured CUDA graph.
+  kernel's epilogue stores every finished element, marked with the hop's sequence number, into every rank's copy, and
+  the consuming kernel's prologue takes each word of its local copy once it carries the mark (csrc/tp.cuh) - four such
+  hops a layer, no collective call, no fence or flag, no reduction (hence no change of summation order), and the whole
+  step stays one captured CUDA graph.
 * the greedy pick over a vocabulary cut by rows: each rank's (value, index) best goes to every rank, which takes the
   largest value and on ties the lowest index - the one-GPU rule.
 * MoE layers (expert parallel): expert e lives on rank e % N (`btb_b200.moe`).
@@ -28,7 +29,7 @@ import ctypes as C
 from . import capi
 from .capi import ptr
 from .engine import CARD_ROWS, CardEngine, DenseConfig, LayerWeights, ModelWeights, pad_rows
-from .exchange import FLAG_BYTES, PeerHeap
+from .exchange import PeerHeap
 
 
 def row_shard(rows: int, rank: int, world: int) -> tuple[int, int]:
@@ -115,27 +116,25 @@ class TPEngine(CardEngine):
         self._tp: dict[int, dict[str, Any]] = {}
         # passes made so far at each width, on the card: the layers' exchanges and the picks count their own
         self.passes = torch.zeros(len(CARD_ROWS), 2, dtype=torch.int32, device=self.dev)
+        self.x_stage_max = 96 * 1024  # an exchanged x is decoded on its way into shared memory up to this size
 
     # -- the heap: the same layout on every rank -------------------------------------------------------------------------
+    PICK_TABLE = 8 * 32 * 2 * 8
+
     @classmethod
     def heap_bytes(cls, c: DenseConfig) -> int:
-        per_row = 2 * (c.q_heads * c.head_dim + 2 * c.hidden + c.inter)
-        flags = (4 * c.layers + 1) * FLAG_BYTES
-        return sum(M * per_row + 4 * 256 + flags + 8 * 32 * 8 + 512 for M in CARD_ROWS) + 4096
+        per_row = 4 * (c.q_heads * c.head_dim + 2 * c.hidden + c.inter)  # a word an element
+        return sum(M * per_row + 5 * 256 + cls.PICK_TABLE for M in CARD_ROWS) + 4096
 
     def _layout(self) -> None:
         self.off: dict[int, dict[str, int]] = {}
         for M in CARD_ROWS:
-            o = {k: self.heap.carve(M * w * 2) for k, w in self.widths.items()}
-            o["flags"] = self.heap.carve((4 * self.full.layers + 1) * FLAG_BYTES)
-            o["picks"] = self.heap.carve(8 * 32 * 8)
+            o = {k: self.heap.carve(M * w * 4) for k, w in self.widths.items()}
+            o["picks"] = self.heap.carve(self.PICK_TABLE)
             self.off[M] = o
 
-    def flag_off(self, M: int, layer: int, which: str) -> int:
-        return self.off[M]["flags"] + (4 * layer + self.XCHG.index(which)) * FLAG_BYTES
-
     def tp_bufs(self, M: int) -> dict[str, Any]:
-        """width M's local buffers and its exchange descriptors"""
+        """width M's local buffers and its exchange descriptors: hop 4 i + j + 1 of a pass carries layer i's vector j"""
         if M not in self._tp:
             c, w, dev, hp = self.full, self.world, self.dev, self.heap
             bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)  # noqa: E731
@@ -143,21 +142,19 @@ class TPEngine(CardEngine):
             t: dict[str, Any] = {
                 "att_l": bf(M, c.q_heads * c.head_dim // w), "gu_l": bf(M, 2 * c.inter // w), "m_l": bf(M, c.inter // w),
                 "lg_l": bf(M, c.vocab // w), "tok_l": torch.zeros(M, dtype=torch.int64, device=dev),
+                "plain": bf(M, max(self.widths.values())),  # an exchanged vector decoded for a kernel that reads plain bf16
                 "pass": int(self.passes[wi, 0:1].data_ptr()), "pick_pass": int(self.passes[wi, 1:2].data_ptr()),
             }  # fmt: skip
-            for k, width in self.widths.items():
-                t[k] = hp.local + self.off[M][k]  # this rank's copy of the full vector
-                t[k + "_t"] = hp.tensor(self.off[M][k], (M, width), torch.bfloat16)
-                t["send_" + k] = [hp.send_desc(self.off[M][k], self.flag_off(M, i, k), width, self.rank * (width // w))
+            per_pass = 4 * c.layers
+            for j, (k, width) in enumerate(self.widths.items()):
+                t[k] = hp.local + self.off[M][k]  # this rank's copy of the full vector (words)
+                t[k + "_t"] = hp.tensor(self.off[M][k], (M, width), torch.int32)
+                t["send_" + k] = [hp.send_desc(self.off[M][k], width, self.rank * (width // w), t["pass"], per_pass, 4 * i + j + 1)
                                   for i in range(c.layers)]  # fmt: skip
-            pick_flag = self.off[M]["flags"] + 4 * c.layers * FLAG_BYTES
-            t["send_pick"] = hp.send_desc(self.off[M]["picks"], pick_flag, 8 * 32, 0)
-            t["wait_pick"] = hp.wait_desc(pick_flag, t["pick_pass"], w)
+                t["recv_" + k] = [capi.Recv(t["pass"], per_pass, 4 * i + j + 1) for i in range(c.layers)]
+            t["tables"] = (C.c_void_p * w)(*[hp.base[r] + self.off[M]["picks"] for r in range(w)])
             self._tp[M] = t
         return self._tp[M]
-
-    def _wait(self, M: int, layer: int, which: str, ctas: int) -> Any:
-        return self.heap.wait_desc(self.flag_off(M, layer, which), self.tp_bufs(M)["pass"], ctas * self.world)
 
     # -- the pass, one exchange-delimited piece at a time ---------------------------------------------------------------
     def ops(self, T: int, tail: bool = True, stream_ptr: int | None = None):
@@ -170,51 +167,56 @@ class TPEngine(CardEngine):
         H, D, I = c.hidden, c.head_dim, c.inter
         A = c.q_heads * D
         K_ = self._k
-        n = C.c_int(0)
         fuse = self.fuse_norm and M <= 8 and M * H * 2 <= 64 * 1024
         hcur, halt = g["h"], g["h2"]
-        y_prev, wait_prev = 0, None  # the previous layer's output (every rank's slices, in this rank's copy)
+        y_prev, recv_prev = 0, None  # the previous block's output: every rank's slices, in this rank's copy
 
-        def normed(W: torch.Tensor, norm_w: torch.Tensor, R: int, out: Any, swiglu: bool, send: Any) -> int:
+        def normed(W: torch.Tensor, norm_w: torch.Tensor, R: int, out: Any, swiglu: bool, send: Any) -> None:
             """x = rmsnorm(h + y_prev) folded into the GEMV over W where the row fits, else the separate kernels"""
             nonlocal hcur, halt
             if fuse:
                 K_("btb_b200_gemv_norm_x", ptr(W), ptr(hcur), y_prev, ptr(norm_w), c.eps, 0, ptr(halt) if y_prev else 0,
-                   ptr(out) if send is None else 0, T, M, R, H, int(swiglu), wait_prev, send, C.byref(n), s)  # fmt: skip
+                   ptr(out) if send is None else 0, T, M, R, H, int(swiglu), recv_prev, send, s)  # fmt: skip
                 if y_prev:
                     hcur, halt = halt, hcur
-                return n.value
-            if wait_prev is not None:
-                K_("btb_b200_xchg_wait", wait_prev, s)
-            K_("btb_b200_add_rmsnorm", ptr(hcur), y_prev, ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
+                return
+            y_plain = 0
+            if y_prev:
+                K_("btb_b200_xchg_unpack", y_prev, ptr(t["plain"]), M, H, recv_prev, s)
+                y_plain = ptr(t["plain"])
+            K_("btb_b200_add_rmsnorm", ptr(hcur), y_plain, ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
             if not swiglu:
-                K_("btb_b200_gemv_bf16_x", ptr(W), ptr(g["x"]), ptr(out) if send is None else 0, M, R, H, None, send,
-                   C.byref(n), s)  # fmt: skip
-                return n.value
+                K_("btb_b200_gemv_bf16_x", ptr(W), ptr(g["x"]), ptr(out) if send is None else 0, M, R, H, None, send, s)
+                return
             K_("btb_b200_gemv_bf16", ptr(W), ptr(g["x"]), ptr(t["gu_l"]), M, R, H, s)
             K_("btb_b200_silu_mul", ptr(t["gu_l"]), ptr(t["m_l"]), M, I // w, s)
-            K_("btb_b200_xchg_send", ptr(t["m_l"]), M, I // w, 2, None, send, C.byref(n), s)
-            return n.value
+            K_("btb_b200_xchg_send", ptr(t["m_l"]), M, I // w, send, s)
+
+        def over_exchanged(W: torch.Tensor, which: str, i: int, R: int, C_: int, send: Any) -> None:
+            """a GEMV whose x is an exchanged vector: decoded inside the GEMV where x is staged, else beforehand"""
+            if M <= 8 and M * C_ * 2 <= self.x_stage_max:
+                K_("btb_b200_gemv_bf16_x", ptr(W), t[which], 0, M, R, C_, t["recv_" + which][i], send, s)
+                return
+            K_("btb_b200_xchg_unpack", t[which], ptr(t["plain"]), M, C_, t["recv_" + which][i], s)
+            K_("btb_b200_gemv_bf16_x", ptr(W), ptr(t["plain"]), 0, M, R, C_, None, send, s)
 
         for i, L in enumerate(self.w.layers):
             normed(L.qkv, L.ln1, lc.qkv_rows, g["qkv"], False, None)
             self._attention(g, i, L.wq, L.wk, T, s, out=t["att_l"])  # this rank's heads
-            K_("btb_b200_xchg_send", ptr(t["att_l"]), M, A // w, 2, None, t["send_att"][i], C.byref(n), s)
-            wait_prev = self._wait(M, i, "att", n.value)
+            K_("btb_b200_xchg_send", ptr(t["att_l"]), M, A // w, t["send_att"][i], s)
             yield
-            K_("btb_b200_gemv_bf16_x", ptr(L.o), t["att"], 0, M, H // w, A, wait_prev, t["send_yo"][i], C.byref(n), s)
-            y_prev, wait_prev = t["yo"], self._wait(M, i, "yo", n.value)
+            over_exchanged(L.o, "att", i, H // w, A, t["send_yo"][i])
+            y_prev, recv_prev = t["yo"], t["recv_yo"][i]
             yield
-            ctas = normed(L.gu, L.ln2, 2 * I // w, None, True, t["send_m"][i])
-            wait_prev = self._wait(M, i, "m", ctas)
+            normed(L.gu, L.ln2, 2 * I // w, None, True, t["send_m"][i])
             yield
-            K_("btb_b200_gemv_bf16_x", ptr(L.down), t["m"], 0, M, H // w, I, wait_prev, t["send_yd"][i], C.byref(n), s)
-            y_prev, wait_prev = t["yd"], self._wait(M, i, "yd", n.value)
+            over_exchanged(L.down, "m", i, H // w, I, t["send_yd"][i])
+            y_prev, recv_prev = t["yd"], t["recv_yd"][i]
             yield
         if tail:
             normed(self.w.head, self.w.norm, c.vocab // w, t["lg_l"], False, None)
-        elif wait_prev is not None:  # the last layer's output must have landed before the pass count moves on
-            K_("btb_b200_xchg_wait", wait_prev, s)
+        elif y_prev:  # a pass without its head: the last block's output decoded into y, as the plain engine leaves it
+            K_("btb_b200_xchg_unpack", y_prev, ptr(g["y"]), M, H, recv_prev, s)
         if hcur is not g["h"]:
             g["h"].copy_(hcur)
 
@@ -235,8 +237,8 @@ class TPEngine(CardEngine):
         Vl = self.full.vocab // self.world
         if phase != 2:
             self._k("btb_b200_argmax_bf16", ptr(lg), T, Vl, ptr(self.bufs(M)["pick"]), ptr(t["tok_l"]), s)
-        self._k("btb_b200_xchg_pick", ptr(lg), T, Vl, self.rank * Vl, ptr(t["tok_l"]), self.rank, t["wait_pick"],
-                t["send_pick"], ptr(out), t["pass"] if body_pass else 0, phase, s)  # fmt: skip
+        self._k("btb_b200_xchg_pick", ptr(lg), T, Vl, self.rank * Vl, ptr(t["tok_l"]), self.rank, self.world, t["tables"],
+                ptr(out), t["pick_pass"], t["pass"] if body_pass else 0, phase, s)  # fmt: skip
 
     def forward(self, ids: torch.Tensor, depth: Any = None, parents: Any = None, advance: bool = True) -> torch.Tensor:
         """a pass; returns THIS RANK'S logits slice [T, V / world]"""

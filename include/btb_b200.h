@@ -291,57 +291,63 @@ int btb_b200_widen_f32(const void* x, void* y, int n, void* stream);
 
 /* ---- one model over the GPUs of a box (one process a GPU): the exchange ---------------------------------------------
  * btb has no multi-GPU path (no counterpart in the reference); these serve `north_star`'s sharded configurations with the
- * one-GPU bits. Every linear is cut by OUTPUT rows, so ranks exchange finished elements, never partial sums: a producer
- * kernel stores each element into every rank's copy of the activation vector (plain stores to peer-mapped memory) and
- * each of its CTAs then adds one arrival to a counter in every rank's memory; a consumer waits (about a second at
- * most, then BTB_B200_ERR_TIMEOUT in the status word) until (pass + 1) * per_pass arrivals are in and reads its local
- * copy. `pass` is a device-side count of the passes made so far, advanced once a pass (btb_b200_xchg_pick or
- * btb_b200_xchg_tick), so a captured graph replays without new arguments. Counters are u32 and only grow. */
-typedef struct btb_b200_wait {
-    const void* flag; /* this rank's arrival counter (device, u32); null: nothing to wait for */
-    const void* pass; /* the pass count (device, u32) */
-    unsigned per_pass; /* arrivals a pass brings: the producer's CTAs times the ranks */
-} btb_b200_wait;
+ * one-GPU bits. Every linear is cut by OUTPUT rows, so ranks exchange finished bf16 elements, never partial sums. An
+ * exchanged vector lives in every rank's memory as u32 WORDS [M, stride]: a word is the element's bf16 in its low half
+ * and, in its high half, the low 16 bits of the hop's sequence number pass * per_pass + base. A producer stores each
+ * finished element's word into every rank's copy (plain 4-byte stores to peer-mapped memory: atomic, no fence, no flag);
+ * a consumer reads its local copy and takes a word once it carries the hop's mark (re-reading until then: about a second
+ * at most, then BTB_B200_ERR_TIMEOUT in the status word, and the kernel goes on). `pass` is a device-side u32 count of
+ * the passes made so far, advanced once a pass (btb_b200_xchg_pick or btb_b200_xchg_tick), so a captured graph replays
+ * without new arguments; `base` numbers the hop within the pass (1 ..per_pass). */
+typedef struct btb_b200_recv {
+    const void* pass;  /* the pass count (device, u32) */
+    unsigned per_pass; /* hops a pass makes */
+    unsigned base;     /* this hop's number within the pass */
+} btb_b200_recv;
 typedef struct btb_b200_send {
-    void* out[8];  /* every rank's copy of the full vector, this rank's own included (peer-mapped device pointers) */
-    void* flag[8]; /* every rank's arrival counter for it */
-    int n;         /* ranks; 0: no exchange */
-    int stride;    /* elements a row of the full vector holds */
-    int offset;    /* where this rank's slice starts in a row */
+    void* out[8]; /* every rank's copy of the full vector (u32 words), this rank's own included; peer-mapped, 16-byte aligned */
+    int n;        /* ranks; 0: no exchange */
+    int stride;   /* elements a row of the full vector holds */
+    int offset;   /* where this rank's slice starts in a row */
+    const void* pass;
+    unsigned per_pass, base;
 } btb_b200_send;
-/* peer-mapped memory for one-process-a-GPU jobs (no counterpart in the reference). SET-UP calls: _alloc is cudaMalloc (zeroed) and the others open and
- * close CUDA IPC handles; none belongs in a decode loop or a stream capture. handle64: 64 host bytes to hand to the
- * other processes of the box (any channel), which _open them into pointers valid in their own address space. */
+/* peer-mapped memory for one-process-a-GPU jobs (no counterpart in the reference). SET-UP calls: _alloc is cudaMalloc
+ * (zeroed) and the others open and close CUDA IPC handles; none belongs in a decode loop or a stream capture. handle64:
+ * 64 host bytes to hand to the other processes of the box (any channel), which _open them into pointers valid in their
+ * own address space. */
 int btb_b200_peer_alloc(size_t bytes, void** ptr);
 int btb_b200_peer_free(void* ptr);
 int btb_b200_peer_handle(void* ptr, unsigned char* handle64);
 int btb_b200_peer_open(const unsigned char* handle64, void** ptr);
 int btb_b200_peer_close(void* ptr);
-/* btb_b200_gemv_bf16 with the exchange folded in: `wait` holds back the read of x; with send->n > 0 the outputs go to
- * every rank's [M, stride] vector at [m][offset + r] (y may be null) and the CTAs arrive. *ctas (host, may be null)
- * receives the CTAs launched - the consumer's per_pass is that times the ranks. */
-int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_wait* wait,
-                         const btb_b200_send* send, int* ctas, void* stream);
+/* btb_b200_gemv_bf16 with the exchange folded in: with `recv`, x is this rank's copy of an exchanged vector (words
+ * [M, C]), taken word by word on its way into shared memory (M <= 8 and M*C*2 within the x staging budget, else
+ * BTB_B200_ERR_DOMAIN: btb_b200_xchg_unpack first); with send->n > 0 the outputs go, marked, to every rank's copy at
+ * [m][offset + r] (y may be null). */
+int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_recv* recv,
+                         const btb_b200_send* send, void* stream);
 /* btb_b200_gemv_norm (swiglu 0) / btb_b200_gemv_norm_swiglu (swiglu 1) over bf16 weights with the exchange folded in:
- * `wait` holds back the read of y_add */
+ * with `recv`, y_add is this rank's copy of an exchanged vector */
 int btb_b200_gemv_norm_x(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps, int centered,
-                         void* h_out, void* y, int T, int M, int R, int C, int swiglu, const btb_b200_wait* wait,
-                         const btb_b200_send* send, int* ctas, void* stream);
-/* (no counterpart in the reference) a finished local slice src [M, n] (elements of elem_bytes; rows, stride and offset multiples of 16 bytes) into every
- * rank's copy: for kernels that do not send themselves */
-int btb_b200_xchg_send(const void* src, int M, int n, int elem_bytes, const btb_b200_wait* wait, const btb_b200_send* send,
-                       int* ctas, void* stream);
+                         void* h_out, void* y, int T, int M, int R, int C, int swiglu, const btb_b200_recv* recv,
+                         const btb_b200_send* send, void* stream);
+/* (no counterpart in the reference) a finished local slice src bf16 [M, n] into every rank's copy, marked: for kernels
+ * that do not send themselves. n, stride and offset multiples of 4. */
+int btb_b200_xchg_send(const void* src, int M, int n, const btb_b200_send* send, void* stream);
+/* (no counterpart in the reference) this rank's copy of an exchanged vector (words [M, C]) as plain bf16 dst [M, C] once
+ * every word carries the hop's mark: for consumers that read plain vectors (wide passes), and where a wait on its own
+ * is wanted. C a multiple of 8. */
+int btb_b200_xchg_unpack(const void* words, void* dst, int M, int C, const btb_b200_recv* recv, void* stream);
 /* the greedy pick over a vocabulary cut by rows: local_idx i64 [T] is this rank's lowest-index argmax within its slice
  * logits [T, Vl] (btb_b200_argmax_bf16); every rank receives every rank's (value, v_offset + index) and takes the largest
- * value, the lowest index among equals - the one-GPU pick (btb/engine/cuda.py:2237). send->out[p]: rank p's table of
- * u64 [ranks, 32]; wait->per_pass = ranks, wait->pass the picks' own pass count (advanced here). ids i64 [T]. body_pass
- * (may be null): the layers' pass count, advanced by one at the end too. phase 0: the whole pick; 1: send only; 2: wait and
- * merge only (for ranks that share one GPU and take turns). T <= 32. */
-int btb_b200_xchg_pick(const void* logits, int T, int Vl, int v_offset, const void* local_idx, int rank,
-                       const btb_b200_wait* wait, const btb_b200_send* send, void* ids, void* body_pass, int phase,
-                       void* stream);
-/* a wait and a pass-count advance as launches of their own (no counterpart in the reference) */
-int btb_b200_xchg_wait(const btb_b200_wait* wait, void* stream);
+ * value, the lowest index among equals - the one-GPU pick (btb/engine/cuda.py:2237). tables (host array of `ranks` device
+ * pointers): rank p's table, u64 [ranks, 32, 2], zero at first. pick_pass: the picks' own pass count (device u32,
+ * advanced here); body_pass (may be null): the layers' pass count, advanced by one at the end too. ids i64 [T]. phase 0:
+ * the whole pick; 1: send only; 2: take and merge only (for ranks that share one GPU and take turns). T <= 32. */
+int btb_b200_xchg_pick(const void* logits, int T, int Vl, int v_offset, const void* local_idx, int rank, int ranks,
+                       void* const* tables, void* ids, void* pick_pass, void* body_pass, int phase, void* stream);
+/* a pass-count advance as a launch of its own (no counterpart in the reference) */
 int btb_b200_xchg_tick(void* pass, void* stream);
 
 /* ---- the whole step as one launch ---------------------------------------------------------------------------------

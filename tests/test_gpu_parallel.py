@@ -2,7 +2,6 @@
 turns on ONE GPU (tests/lockstep.py) equal it too - slices, offsets, arrival counts and the merged pick all at work;
 a wait nobody answers gives up with ERR_TIMEOUT instead of hanging; and, when the box has them, two real GPUs equal one."""
 
-import ctypes as C
 import os
 import subprocess
 import sys
@@ -72,26 +71,28 @@ def test_ranks_taking_turns_on_one_gpu_equal_the_plain_engine(world):
     assert capi.status() == 0
 
 
-def test_a_wait_nobody_answers_gives_up():
-    """a consumer whose producers never arrive (a peer that died between steps) returns after about a second with
+def test_a_vector_nobody_sends_gives_up():
+    """a consumer whose producers never write (a peer that died between steps) returns after about a second with
     ERR_TIMEOUT in the status word; the context stays usable"""
-    flag = torch.zeros(16, dtype=torch.int32, device="cuda")
+    words = torch.zeros(1, 64, dtype=torch.int32, device="cuda")
+    dst = torch.zeros(1, 64, dtype=torch.bfloat16, device="cuda")
     pas = torch.zeros(1, dtype=torch.int32, device="cuda")
-    w = capi.Wait(ptr(flag), ptr(pas), 3)
-    call("btb_b200_xchg_wait", w, capi.stream_ptr())
+    r = capi.Recv(ptr(pas), 4, 3)  # awaits words marked 0 * 4 + 3
+    call("btb_b200_xchg_unpack", ptr(words), ptr(dst), 1, 64, r, capi.stream_ptr())
     torch.cuda.synchronize()
     assert capi.status() == capi.ERR_TIMEOUT
-    # the arrivals in: the same wait returns at once
-    flag[0] = 3
-    call("btb_b200_xchg_wait", w, capi.stream_ptr())
+    # the words in (one rank sending to itself): the same take returns at once with the elements
+    src = torch.arange(64, dtype=torch.float32, device="cuda").to(torch.bfloat16).reshape(1, 64)
+    s = capi.Send()
+    s.out[0], s.n, s.stride, s.offset, s.pass_, s.per_pass, s.base = ptr(words), 1, 64, 0, ptr(pas), 4, 3
+    call("btb_b200_xchg_send", ptr(src), 1, 64, s, capi.stream_ptr())
+    call("btb_b200_xchg_unpack", ptr(words), ptr(dst), 1, 64, r, capi.stream_ptr())
     torch.cuda.synchronize()
-    assert capi.status() == 0
-    n = C.c_int(0)
-    x = torch.ones(1, 64, dtype=torch.bfloat16, device="cuda")
+    assert capi.status() == 0 and torch.equal(dst, src)
+    assert int(words[0, 5]) == (3 << 16) | int(src.view(torch.int16)[0, 5])
     with pytest.raises(capi.NativeError):  # a slice that does not fit its vector is refused on the host
-        s = capi.Send()
-        s.out[0], s.flag[0], s.n, s.stride, s.offset = ptr(x), ptr(flag), 1, 64, 32
-        call("btb_b200_xchg_send", ptr(x), 1, 64, 2, None, s, C.byref(n), capi.stream_ptr())
+        s.offset = 32
+        call("btb_b200_xchg_send", ptr(src), 1, 64, s, capi.stream_ptr())
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
