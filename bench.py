@@ -272,6 +272,10 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     storage, parallelism = "bf16", ("replicas only" if world > 1 else "1 gpu")
     if args.pdl is not None:
         capi.set_tuning(pdl=args.pdl)
+    if args.l2_warm_kb is not None:
+        capi.set_tuning(l2_warm_kb=args.l2_warm_kb)
+    if args.l2_warm_ctas is not None:
+        capi.set_tuning(l2_warm_ctas=args.l2_warm_ctas)
     if args.workload == "qwen3-4b-bf16" and world > 1 and args.batch == 1 and not args.replicas:
         # one model over the ranks: every linear cut by output rows, one token stream (strong scaling)
         from btb_b200 import parallel as P
@@ -477,20 +481,21 @@ def tp_collective(eng, cfg, world, dist) -> dict:
     dst = torch.zeros(1, H, dtype=torch.bfloat16, device="cuda")
     s = capi.stream_ptr()
     hops = 200
-    # the probe borrows the `yd` vector of width 1 with a pass count of its own, started well past the marks the decode
-    # left in it (every rank has made the same passes, so every rank starts the probe at the same number)
+    # the probe borrows the `yd` and `yo` vectors of width 1 in turn (a rank may send hop k + 1 while another still takes
+    # hop k: two buffers keep them apart, as the step's own order of hops does) with a pass count of its own, started well
+    # past the marks the decode left (every rank has made the same passes, so every rank starts at the same number)
     torch.cuda.synchronize()
     start = int(eng.passes[0, 0].item()) * 4 * cfg.layers + 4 * cfg.layers + 1000
     probe = torch.full((1,), start, dtype=torch.int32, device="cuda")
-    send = eng.heap.send_desc(eng.off[1]["yd"], H, eng.rank * (H // world), ptr(probe), 1, 1)
+    sends = [eng.heap.send_desc(eng.off[1][k], H, eng.rank * (H // world), ptr(probe), 1, 1) for k in ("yd", "yo")]
     recv = capi.Recv(ptr(probe), 1, 1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     dist.barrier()
     e0.record()
-    for _ in range(hops):
-        call("btb_b200_xchg_send", ptr(src), 1, H // world, send, s)
-        call("btb_b200_xchg_unpack", t["yd"], ptr(dst), 1, H, recv, s)
+    for k in range(hops):
+        call("btb_b200_xchg_send", ptr(src), 1, H // world, sends[k & 1], s)
+        call("btb_b200_xchg_unpack", t[("yd", "yo")[k & 1]], ptr(dst), 1, H, recv, s)
         call("btb_b200_xchg_tick", ptr(probe), s)
     e1.record()
     torch.cuda.synchronize()
@@ -760,6 +765,8 @@ def main() -> None:
     ap.add_argument("--context", type=int, default=0, help="llama-70b: rows of synthetic cache standing before the step")
     ap.add_argument("--graph-steps", type=int, default=1)
     ap.add_argument("--pdl", type=int, default=None)
+    ap.add_argument("--l2-warm-kb", type=int, default=None, help="weights the attention launch pulls into L2 ahead (KB)")
+    ap.add_argument("--l2-warm-ctas", type=int, default=None)
     ap.add_argument("--cpu-steps", type=int, default=4)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--batch", type=int, default=1, help="qwen3-4b workloads: sequences decoded side by side")

@@ -136,8 +136,19 @@ SIGNATURES.update({
     "btb_b200_peer_handle": (_I, [_P, C.POINTER(C.c_ubyte)]),
     "btb_b200_peer_open": (_I, [C.POINTER(C.c_ubyte), C.POINTER(C.c_void_p)]),
     "btb_b200_peer_close": (_I, [_P]),
-    "btb_b200_gemv_bf16_x": (_I, [_P, _P, _P, _I, _I, _I, _RP, _SP, _P]),
+    "btb_b200_gemv_bf16_x": (_I, [_P, _P, _P, _I, _I, _I, _I, _RP, _SP, _P]),
     "btb_b200_gemv_norm_x": (_I, [_P, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _I, _RP, _SP, _P]),
+    "btb_b200_attn_step_x": (
+        _I, [_P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _LL, _LL, _I, _F, _P, _P, _P, _P, _I, _P, _P, _I, _SP,
+             _P],
+    ),
+    "btb_b200_attn_step_w": (
+        _I, [_P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _LL, _LL, _I, _F, _P, _P, _P, _P, _I, _P, _P, _I, _SP,
+             _P, _LL, _P, _LL, _P],
+    ),
+    "btb_b200_attn_decode_x": (
+        _I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _F, _P, _P, _P, _P, _I, _P, _P, _I, _SP, _P],
+    ),
     "btb_b200_xchg_send": (_I, [_P, _I, _I, _SP, _P]),
     "btb_b200_xchg_unpack": (_I, [_P, _P, _I, _I, _RP, _P]),
     "btb_b200_xchg_pick": (_I, [_P, _I, _I, _I, _P, _I, _I, C.POINTER(C.c_void_p), _P, _P, _P, _I, _P]),

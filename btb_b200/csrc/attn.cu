@@ -21,6 +21,8 @@
 
 B2_DEFINE_STATUS(attn)
 
+#include "../../include/btb_b200.h"
+
 namespace {
 
 template <int D, int G>
@@ -46,10 +48,33 @@ struct StepAttnArgs {
     RopeArgs r;
     int B;                   // sequences decoded side by side (row b of the pass belongs to sequence b), 1 for a step
     long long seq_stride;    // elements from a sequence's cache to the next one's
+    // The step's attention row moves a few hundred KB and is a chain of dependent latencies; the memory system idles
+    // under it. Blocks past the attention's own (grid x >= S) spend that time pulling the NEXT kernels' weights into
+    // L2 (the output projection's, then the start of gate/up's): `warm` ranges of 16-byte-aligned bytes.
+    const uint8_t* warm[2];
+    long long warm_bytes[2];
+    int S;                   // the attention's own extent of grid x
 };
+// a range of global memory into L2, 4 KB a request (the bulk-copy unit's prefetch form: no destination, no barrier)
+__device__ __forceinline__ void l2_prefetch(const uint8_t* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
 template <int D, int G>
 __global__ void __launch_bounds__(NWA * 32) attn_step(const StepAttnArgs A) {
     extern __shared__ __align__(16) uint8_t dsm_raw[];
+    if ((int)blockIdx.x >= A.S) {  // a warming block: weights do not depend on the kernels before this one
+        const long long nblk = (long long)(gridDim.x - A.S) * gridDim.y * gridDim.z;
+        const long long me = ((long long)(blockIdx.x - A.S) * gridDim.y + blockIdx.y) * gridDim.z + blockIdx.z;
+        constexpr long long CH = 4096;
+        for (int k = 0; k < 2; ++k) {
+            const long long n = (A.warm_bytes[k] + CH - 1) / CH;
+            for (long long c = me * blockDim.x + threadIdx.x; c < n; c += nblk * blockDim.x) {
+                const long long left = A.warm_bytes[k] - c * CH;
+                l2_prefetch(A.warm[k] + c * CH, (uint32_t)(left < CH ? left : CH));
+            }
+        }
+        return;
+    }
     pdl_wait();  // the trigger for the next kernel is inside, after the values are read
     if (A.B > 1) {
         // sequence b's row: its slice of qkv, its own cache, length, partials and counters
@@ -57,7 +82,7 @@ __global__ void __launch_bounds__(NWA * 32) attn_step(const StepAttnArgs A) {
         AttnArgs a = A.a;
         RopeArgs r = A.r;
         const int Hq = a.Hq, Hk = a.Hk;
-        const size_t S = gridDim.x;
+        const size_t S = A.S;
         r.qkv += (size_t)b * (Hq + 2 * Hk) * D, r.n0p += b, r.depth += b, r.K += (size_t)b * A.seq_stride;
         r.V += (size_t)b * A.seq_stride, r.qo += (size_t)b * Hq * D;
         a.q = r.qo, a.K = r.K, a.V = r.V, a.out += (size_t)b * Hq * D, a.n0p = r.n0p;
@@ -109,15 +134,31 @@ int launch_attn_g(int G, const AttnArgs& a, dim3 grid, cudaStream_t s) {
 
 }  // namespace
 
+// the C-ABI's send descriptor into the kernels' own (a slice of T rows of Hq * D elements)
+static int take_send(const btb_b200_send* send, int Hq, int D, B2Send& out) {
+    if (send == nullptr || send->n == 0) return B2_OK;
+    if (send->n < 0 || send->n > B2_MAX_RANKS || send->stride <= 0 || send->offset < 0 || send->offset + Hq * D > send->stride)
+        return B2_ERR_DOMAIN;
+    if (send->pass == nullptr) return B2_ERR_NULL;
+    out.n = send->n, out.stride = send->stride, out.offset = send->offset;
+    out.pass = static_cast<const unsigned*>(send->pass), out.per_pass = send->per_pass, out.base = send->base;
+    for (int p = 0; p < send->n; ++p) {
+        if (send->out[p] == nullptr) return B2_ERR_NULL;
+        out.out[p] = static_cast<uint32_t*>(send->out[p]);
+    }
+    return B2_OK;
+}
+
 extern "C" size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D) {
     return (size_t)S * T * Hq * (D + 2);
 }
 
-extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V, void* out, const void* n0p,
+static int attn_decode_impl(const void* q, const void* K, const void* V, void* out, const void* n0p,
                                     const void* par, int T, int Hq, int Hk, int D, long long hs, long long rs,
                                     float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
-                                    const void* tbl, const void* sinks, int cap, void* stream) {
-    if (!q || !K || !V || !out || !n0p || !par || !part_m || !part_l || !part_acc || !cnt) return B2_ERR_NULL;
+                                    const void* tbl, const void* sinks, int cap, const btb_b200_send* send, void* stream) {
+    const bool sends = send != nullptr && send->n != 0;
+    if (!q || !K || !V || (!out && !sends) || !n0p || !par || !part_m || !part_l || !part_acc || !cnt) return B2_ERR_NULL;
     if (T <= 0 || T > TMAX || Hk <= 0 || Hq <= 0 || Hq % Hk || (Hq / Hk != 1 && Hq / Hk != 2 && Hq / Hk != 4 && Hq / Hk != 8) || cap <= 0 || !(scale == scale))
         return B2_ERR_DOMAIN;
     // a key row is read as 16-byte chunks, a value row as D/32-element runs
@@ -130,6 +171,7 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
     a.part_m = static_cast<float*>(part_m), a.part_l = static_cast<float*>(part_l);
     a.part_acc = static_cast<float*>(part_acc), a.cnt = static_cast<int*>(cnt);
     a.scale = scale, a.T = T, a.Hq = Hq, a.Hk = Hk, a.win = win, a.cap = cap, a.hs = hs, a.rs = rs;
+    if (const int rc = take_send(send, Hq, D, a.send)) return rc;
     const int S = (cap + GK - 1) / GK;
     const dim3 grid(S, Hk, T);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -140,12 +182,33 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
     }
 }
 
+extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V, void* out, const void* n0p,
+                                    const void* par, int T, int Hq, int Hk, int D, long long hs, long long rs,
+                                    float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
+                                    const void* tbl, const void* sinks, int cap, void* stream) {
+    return attn_decode_impl(q, K, V, out, n0p, par, T, Hq, Hk, D, hs, rs, scale, part_m, part_l, part_acc, cnt, win, tbl,
+                            sinks, cap, nullptr, stream);
+}
+
+// btb_b200_attn_decode in a model cut over ranks by kv head: the output rows go, marked, to every rank's copy
+extern "C" int btb_b200_attn_decode_x(const void* q, const void* K, const void* V, const void* n0p, const void* par, int T,
+                                      int Hq, int Hk, int D, long long hs, long long rs, float scale, void* part_m,
+                                      void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks,
+                                      int cap, const btb_b200_send* send, void* stream) {
+    if (send == nullptr || send->n == 0) return B2_ERR_NULL;
+    return attn_decode_impl(q, K, V, nullptr, n0p, par, T, Hq, Hk, D, hs, rs, scale, part_m, part_l, part_acc, cnt, win,
+                            tbl, sinks, cap, send, stream);
+}
+
 static int attn_step_launch(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
                             const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, void* out,
                             int Hq, int Hk, int D, long long hs, long long rs, int centered, float scale, void* part_m,
                             void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
-                            int B, long long seq_stride, void* stream) {
-    if (!qkv || !cos_t || !sin_t || !n0p || !depth || !K || !V || !q || !out || !part_m || !part_l || !part_acc || !cnt)
+                            int B, long long seq_stride, void* stream, const btb_b200_send* send = nullptr,
+                            const void* warm_a = nullptr, long long bytes_a = 0, const void* warm_b = nullptr,
+                            long long bytes_b = 0) {
+    const bool sends = send != nullptr && send->n != 0;
+    if (!qkv || !cos_t || !sin_t || !n0p || !depth || !K || !V || !q || (!out && !sends) || !part_m || !part_l || !part_acc || !cnt)
         return B2_ERR_NULL;
     if (Hk <= 0 || Hq <= 0 || Hq % Hk || (Hq / Hk != 1 && Hq / Hk != 2 && Hq / Hk != 4 && Hq / Hk != 8) || cap <= 0 ||
         !(scale == scale))
@@ -168,9 +231,29 @@ static int attn_step_launch(const void* qkv, const void* wq, const void* wk, flo
                     static_cast<const bf16*>(cos_t), static_cast<const bf16*>(sin_t), static_cast<const int*>(n0p),
                     static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),
                     static_cast<bf16*>(V), static_cast<bf16*>(q), eps, 1, Hq, Hk, centered, hs, rs, cap};
+    if (const int rc = take_send(send, Hq, D, a.send)) return rc;
     const int S = (cap + GK - 1) / GK;
-    sa.B = B, sa.seq_stride = seq_stride;
-    const dim3 grid(S, Hk * B, Hq / Hk);
+    sa.B = B, sa.seq_stride = seq_stride, sa.S = S;
+    // warming blocks: as many as fill the card beside the attention's, for at most `l2_warm_kb` of the next weights
+    int extra = 0;
+    {
+        long long budget = (long long)b2_tuning().l2_warm_kb * 1024;
+        const void* wp[2] = {warm_a, warm_b};
+        const long long wb[2] = {bytes_a, bytes_b};
+        for (int k = 0; k < 2; ++k) {
+            if (wp[k] == nullptr || wb[k] <= 0 || budget <= 0) continue;
+            if ((reinterpret_cast<uintptr_t>(wp[k]) & 15) || (wb[k] & 15)) return B2_ERR_DOMAIN;
+            sa.warm[k] = static_cast<const uint8_t*>(wp[k]);
+            sa.warm_bytes[k] = wb[k] < budget ? wb[k] : (budget & ~15LL);
+            budget -= sa.warm_bytes[k];
+        }
+        if (sa.warm_bytes[0] + sa.warm_bytes[1] > 0) {
+            const int per_x = Hk * B * (Hq / Hk);
+            const int want = b2_tuning().l2_warm_ctas > 0 ? b2_tuning().l2_warm_ctas : b2_sm_count() - S * per_x;
+            extra = want > 0 ? (want + per_x - 1) / per_x : 0;
+        }
+    }
+    const dim3 grid(S + extra, Hk * B, Hq / Hk);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (D) {
         case 64: return launch_attn_step_g<64>(Hq / Hk, sa, grid, s);
@@ -186,6 +269,29 @@ extern "C" int btb_b200_attn_step(const void* qkv, const void* wq, const void* w
                                   const void* tbl, const void* sinks, int cap, void* stream) {
     return attn_step_launch(qkv, wq, wk, eps, cos_t, sin_t, n0p, depth, K, V, q, out, Hq, Hk, D, hs, rs, centered, scale,
                             part_m, part_l, part_acc, cnt, win, tbl, sinks, cap, 1, 0, stream);
+}
+
+// btb_b200_attn_step with idle SMs pulling the next kernels' weights into L2 while the row's latencies run their course
+extern "C" int btb_b200_attn_step_w(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                    const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
+                                    void* out, int Hq, int Hk, int D, long long hs, long long rs, int centered, float scale,
+                                    void* part_m, void* part_l, void* part_acc, void* cnt, int win, const void* tbl,
+                                    const void* sinks, int cap, const btb_b200_send* send, const void* warm_a,
+                                    long long bytes_a, const void* warm_b, long long bytes_b, void* stream) {
+    return attn_step_launch(qkv, wq, wk, eps, cos_t, sin_t, n0p, depth, K, V, q, out, Hq, Hk, D, hs, rs, centered, scale,
+                            part_m, part_l, part_acc, cnt, win, tbl, sinks, cap, 1, 0, stream, send, warm_a, bytes_a, warm_b,
+                            bytes_b);
+}
+
+// btb_b200_attn_step in a model cut over ranks by kv head: the step's output row goes, marked, to every rank's copy
+extern "C" int btb_b200_attn_step_x(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                    const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, int Hq,
+                                    int Hk, int D, long long hs, long long rs, int centered, float scale, void* part_m,
+                                    void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks,
+                                    int cap, const btb_b200_send* send, void* stream) {
+    if (send == nullptr || send->n == 0) return B2_ERR_NULL;
+    return attn_step_launch(qkv, wq, wk, eps, cos_t, sin_t, n0p, depth, K, V, q, nullptr, Hq, Hk, D, hs, rs, centered, scale,
+                            part_m, part_l, part_acc, cnt, win, tbl, sinks, cap, 1, 0, stream, send);
 }
 
 extern "C" int btb_b200_attn_step_batch(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,

@@ -3,6 +3,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "tp.cuh"
 
 
 constexpr int BN = 64;        // keys a tile
@@ -48,7 +49,22 @@ struct AttnArgs {
     float scale;
     int T, Hq, Hk, win, cap;
     long long hs, rs;
+    // a model cut over ranks by kv head (tp.cuh): with send.n > 0 a finished output element goes, marked, to every rank's
+    // copy of the full [T, stride] vector at [t][send.offset + head * D + d] instead of `out`
+    B2Send send{};
 };
+
+// a finished output element: the local row, or every rank's copy of the exchanged vector
+__device__ __forceinline__ void attn_store(const AttnArgs& A, int t, int head, int d, int D, bf16 v, uint32_t mark) {
+    if (A.send.n == 0) {
+        A.out[((size_t)t * A.Hq + head) * D + d] = v;
+        return;
+    }
+    const size_t at = (size_t)t * A.send.stride + A.send.offset + (size_t)head * D + d;
+    const uint32_t word = b2_word(v, mark);
+#pragma unroll 1
+    for (int p = 0; p < A.send.n; ++p) A.send.out[p][at] = word;
+}
 
 constexpr int NWA = 2 * GT;  // warps a block: two a tile, 32 keys each (a lane one key)
 
@@ -73,6 +89,7 @@ __device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& s
     // a row's groups)
     const int Hq = A.Hq, T = A.T;
     int& s_last_block = *s_last_block_p;
+    const uint32_t mark = A.send.n != 0 ? b2_hop_mark(A.send.pass, A.send.per_pass, A.send.base) : 0u;
     // ---- the group's state: the tiles folded in tile order, a thread a run of (head, dim) elements -------------
     const int s_first = first / GK, s_last = last / GK;
     const bool single = s_first == s_last;
@@ -95,7 +112,7 @@ __device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& s
                 fold_ml(M, L, __fmul_rn(A.sinks[hbase + hh], LOG2E), 1.f, cO, co);
                 O = __fmul_rn(O, cO);
             }
-            A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+            attn_store(A, t, hbase + hh, d, D, f2bf(__fmul_rn(O, __fdiv_rn(1.f, L))), mark);
         } else {
             const size_t idx = (size_t)grp * T * Hq + rowi;
             if (d == 0) {
@@ -128,7 +145,7 @@ __device__ __forceinline__ void attn_finish(const AttnArgs& A, AttnSmem<D, G>& s
             fold_ml(M, L, __fmul_rn(A.sinks[hbase + hh], LOG2E), 1.f, cO, co);
             O = __fmul_rn(O, cO);
         }
-        A.out[rowi * D + d] = f2bf(__fmul_rn(O, __fdiv_rn(1.f, L)));
+        attn_store(A, t, hbase + hh, d, D, f2bf(__fmul_rn(O, __fdiv_rn(1.f, L))), mark);
     }
     if (threadIdx.x == 0) A.cnt[ci] = 0;
 }

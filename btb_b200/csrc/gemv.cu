@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     const uint32_t mark_out = A.send.n != 0 ? b2_hop_mark(A.send.pass, A.send.per_pass, A.send.base) : 0u;
 
     if (XS) {
-        if (XM == X_SMEM) stage_x_copy<M, NT>(xs, A.x, C, marked, mark_in);
+        if (XM == X_SMEM) stage_x_copy<M, NT>(xs, A.x, C, marked, mark_in, A.T);
         else if (XM == X_SMEM_SILU) stage_x_silu<M, NT>(xs, A.x, C);
         else
             stage_x_norm<M, NT>(xs, reinterpret_cast<float*>(smem), A.h_in, nullptr, A.y_add, A.norm_w, A.h_out, A.eps,
@@ -402,7 +402,7 @@ static int take_exchange(const btb_b200_recv* recv, const btb_b200_send* send, G
     return B2_OK;
 }
 
-static int gemv_bf16_impl(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_recv* recv,
+static int gemv_bf16_impl(const void* w, const void* x, void* y, int T, int M, int R, int C, const btb_b200_recv* recv,
                           const btb_b200_send* send, void* stream) {
     const bool sends = send != nullptr && send->n != 0;
     int rc = check_dims(w, x, sends ? w : y, M, R, C);  // a sending launch has no local y
@@ -411,7 +411,8 @@ static int gemv_bf16_impl(const void* w, const void* x, void* y, int M, int R, i
     a.w = static_cast<const uint8_t*>(w);
     a.x = static_cast<const bf16*>(x);
     a.y = static_cast<bf16*>(y);
-    a.R = R, a.C = C;
+    a.R = R, a.C = C, a.T = T;
+    if (T < 1 || T > M) return B2_ERR_DOMAIN;
     if ((rc = take_exchange(recv, send, a)) != B2_OK) return rc;
     Plan p = make_plan<F_BF16>(M, R, C, M <= 8);
     // an exchanged x is decoded on its way into shared memory: a pass too wide to stage x takes btb_b200_xchg_unpack first
@@ -422,12 +423,12 @@ static int gemv_bf16_impl(const void* w, const void* x, void* y, int M, int R, i
 }
 
 extern "C" int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* stream) {
-    return gemv_bf16_impl(w, x, y, M, R, C, nullptr, nullptr, stream);
+    return gemv_bf16_impl(w, x, y, M, M, R, C, nullptr, nullptr, stream);
 }
 
-extern "C" int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_recv* recv,
-                                    const btb_b200_send* send, void* stream) {
-    return gemv_bf16_impl(w, x, y, M, R, C, recv, send, stream);
+extern "C" int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int T, int M, int R, int C,
+                                    const btb_b200_recv* recv, const btb_b200_send* send, void* stream) {
+    return gemv_bf16_impl(w, x, y, T, M, R, C, recv, send, stream);
 }
 
 // x = rmsnorm(h_in + y) * w computed inside the GEMV (bf16 weights, or pack12 when hi4 is not null); swiglu: the rows are

@@ -90,12 +90,16 @@ static __device__ __noinline__ uint32_t p12_escape(const int32_t* __restrict__ e
 
 // x [M, C] bf16 as is; `marked`: x is this rank's copy of an exchanged vector (u32 words [M, C], tp.cuh), each element
 // taken once it carries this hop's `mark`
+// (only the pass's `live` rows are awaited - a producer may have none to send for the padding rows - the rest are zeros)
 template <int M, int NT>
-__device__ __forceinline__ void stage_x_copy(bf16* xs, const bf16* x, int C, bool marked = false, uint32_t mark = 0u) {
+__device__ __forceinline__ void stage_x_copy(bf16* xs, const bf16* x, int C, bool marked = false, uint32_t mark = 0u,
+                                             int live = M) {
     uint4* dst = reinterpret_cast<uint4*>(xs);
     const int nt = NT > 0 ? NT : (int)blockDim.x;  // NT 0: the block's width is a launch parameter
     if (marked) {
-        for (int i = threadIdx.x; i < M * C / 8; i += nt) dst[i] = b2_take8(reinterpret_cast<const uint32_t*>(x) + (size_t)i * 8, mark);
+        const int n_live = live * (C / 8);
+        for (int i = threadIdx.x; i < M * C / 8; i += nt)
+            dst[i] = i < n_live ? b2_take8(reinterpret_cast<const uint32_t*>(x) + (size_t)i * 8, mark) : make_uint4(0u, 0u, 0u, 0u);
         return;
     }
     for (int i = threadIdx.x; i < M * C / 8; i += nt) dst[i] = ldcg16(reinterpret_cast<const uint4*>(x) + i);

@@ -315,7 +315,7 @@ class CardEngine:
                   self.hs, self.rs, 0, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]), ptr(g["part_acc"]),
                   ptr(g["cnt"]), 0, 0, self.cap, ptr(L.o), ptr(g["y"]), H, ptr(self._bar), s)  # fmt: skip
             else:
-                self._attention(g, i, L.wq, L.wk, T, s)
+                self._attention(g, i, L.wq, L.wk, T, s, warm=(L.o, L.gu))
                 self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             if fuse and self.swiglu_epilogue and not isinstance(L.gu, FP8Matrix):
                 # the gate/up GEMV activates each pair itself: g["gu"] is never written, the down GEMV reads g["m"]
@@ -340,18 +340,27 @@ class CardEngine:
         if hcur is not g["h"]:  # an odd number of folded adds (a pass without its tail): bring the residual home
             g["h"].copy_(hcur)
 
+    @staticmethod
+    def _warm(W: Any) -> tuple[int, int]:
+        """(address, bytes) of a bf16 matrix for the attention launch's L2 warming, nothing for packed stores"""
+        if isinstance(W, torch.Tensor):
+            return ptr(W), (W.numel() * W.element_size()) & ~15
+        return 0, 0
+
     def _attention(self, g: dict, i: int, wq: Any, wk: Any, T: int, s: int, win: int = 0, sinks: Any = None,
-                   out: Any = None) -> None:
+                   out: Any = None, warm: tuple = ()) -> None:
         """q/k-norm + RoPE + cache write, then the attention over the cache: one fused launch for the step's single
-        row, the two kernels for a pass of several rows (the same bits either way)"""
+        row, the two kernels for a pass of several rows (the same bits either way). `warm`: the matrices the next
+        kernels stream, pulled into L2 by the SMs the step's row leaves idle (the `l2_warm_kb` tunable bounds it)"""
         c = self.cfg
         Hq, Hk, D = c.q_heads, c.kv_heads, c.head_dim
         out = g["att"] if out is None else out
         if T == 1 and self.fuse_attn and D in (64, 128):
-            self._k("btb_b200_attn_step", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
+            (wa, na), (wb, nb) = (self._warm(warm[0]) if len(warm) > 0 else (0, 0)), (self._warm(warm[1]) if len(warm) > 1 else (0, 0))
+            self._k("btb_b200_attn_step_w", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
                     ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), ptr(out), Hq, Hk,
                     D, self.hs, self.rs, 0, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]), ptr(g["part_acc"]),
-                    ptr(g["cnt"]), win, 0, ptr(sinks), self.cap, s)  # fmt: skip
+                    ptr(g["cnt"]), win, 0, ptr(sinks), self.cap, None, wa, na, wb, nb, s)  # fmt: skip
             return
         self._k("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
                 ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,

@@ -182,11 +182,11 @@ class TPEngine(CardEngine):
                 return
             y_plain = 0
             if y_prev:
-                K_("btb_b200_xchg_unpack", y_prev, ptr(t["plain"]), M, H, recv_prev, s)
+                K_("btb_b200_xchg_unpack", y_prev, ptr(t["plain"]), T, H, recv_prev, s)
                 y_plain = ptr(t["plain"])
             K_("btb_b200_add_rmsnorm", ptr(hcur), y_plain, ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
             if not swiglu:
-                K_("btb_b200_gemv_bf16_x", ptr(W), ptr(g["x"]), ptr(out) if send is None else 0, M, R, H, None, send, s)
+                K_("btb_b200_gemv_bf16_x", ptr(W), ptr(g["x"]), ptr(out) if send is None else 0, T, M, R, H, None, send, s)
                 return
             K_("btb_b200_gemv_bf16", ptr(W), ptr(g["x"]), ptr(t["gu_l"]), M, R, H, s)
             K_("btb_b200_silu_mul", ptr(t["gu_l"]), ptr(t["m_l"]), M, I // w, s)
@@ -195,15 +195,14 @@ class TPEngine(CardEngine):
         def over_exchanged(W: torch.Tensor, which: str, i: int, R: int, C_: int, send: Any) -> None:
             """a GEMV whose x is an exchanged vector: decoded inside the GEMV where x is staged, else beforehand"""
             if M <= 8 and M * C_ * 2 <= self.x_stage_max:
-                K_("btb_b200_gemv_bf16_x", ptr(W), t[which], 0, M, R, C_, t["recv_" + which][i], send, s)
+                K_("btb_b200_gemv_bf16_x", ptr(W), t[which], 0, T, M, R, C_, t["recv_" + which][i], send, s)
                 return
-            K_("btb_b200_xchg_unpack", t[which], ptr(t["plain"]), M, C_, t["recv_" + which][i], s)
-            K_("btb_b200_gemv_bf16_x", ptr(W), ptr(t["plain"]), 0, M, R, C_, None, send, s)
+            K_("btb_b200_xchg_unpack", t[which], ptr(t["plain"]), T, C_, t["recv_" + which][i], s)
+            K_("btb_b200_gemv_bf16_x", ptr(W), ptr(t["plain"]), 0, T, M, R, C_, None, send, s)
 
         for i, L in enumerate(self.w.layers):
             normed(L.qkv, L.ln1, lc.qkv_rows, g["qkv"], False, None)
-            self._attention(g, i, L.wq, L.wk, T, s, out=t["att_l"])  # this rank's heads
-            K_("btb_b200_xchg_send", ptr(t["att_l"]), M, A // w, t["send_att"][i], s)
+            self._attention_send(g, i, L.wq, L.wk, T, s, t["send_att"][i], (L.o, L.gu))  # this rank's heads, to every rank
             yield
             over_exchanged(L.o, "att", i, H // w, A, t["send_yo"][i])
             y_prev, recv_prev = t["yo"], t["recv_yo"][i]
@@ -216,9 +215,28 @@ class TPEngine(CardEngine):
         if tail:
             normed(self.w.head, self.w.norm, c.vocab // w, t["lg_l"], False, None)
         elif y_prev:  # a pass without its head: the last block's output decoded into y, as the plain engine leaves it
-            K_("btb_b200_xchg_unpack", y_prev, ptr(g["y"]), M, H, recv_prev, s)
+            K_("btb_b200_xchg_unpack", y_prev, ptr(g["y"]), T, H, recv_prev, s)
         if hcur is not g["h"]:
             g["h"].copy_(hcur)
+
+    def _attention_send(self, g: dict, i: int, wq: Any, wk: Any, T: int, s: int, send: Any, warm: tuple = ()) -> None:
+        """`CardEngine._attention` over this rank's heads, its output rows stored into every rank's copy by the
+        attention kernel itself"""
+        c = self.cfg
+        Hq, Hk, D = c.q_heads, c.kv_heads, c.head_dim
+        if T == 1 and self.fuse_attn and D in (64, 128):
+            (wa, na), (wb, nb) = self._warm(warm[0]) if warm else (0, 0), self._warm(warm[1]) if len(warm) > 1 else (0, 0)
+            self._k("btb_b200_attn_step_w", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
+                    ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), 0, Hq, Hk, D, self.hs,
+                    self.rs, 0, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]), ptr(g["part_acc"]), ptr(g["cnt"]), 0, 0,
+                    0, self.cap, send, wa, na, wb, nb, s)  # fmt: skip
+            return
+        self._k("btb_b200_norm_rope_kv", ptr(g["qkv"]), ptr(wq), ptr(wk), c.eps, ptr(self.cos), ptr(self.sin),
+                ptr(self.n0), ptr(g["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(g["q"]), T, Hq, Hk, D, self.hs,
+                self.rs, 0, 0, self.cap, s)  # fmt: skip
+        self._k("btb_b200_attn_decode_x", ptr(g["q"]), ptr(self.K[i]), ptr(self.V[i]), ptr(self.n0), ptr(g["par"]), T, Hq,
+                Hk, D, self.hs, self.rs, float(D**-0.5), ptr(g["part_m"]), ptr(g["part_l"]), ptr(g["part_acc"]),
+                ptr(g["cnt"]), 0, 0, 0, self.cap, send, s)  # fmt: skip
 
     def body(self, T: int, tail: bool = True, stream_ptr: int | None = None) -> None:
         for _ in self.ops(T, tail, stream_ptr):

@@ -322,22 +322,41 @@ int btb_b200_peer_handle(void* ptr, unsigned char* handle64);
 int btb_b200_peer_open(const unsigned char* handle64, void** ptr);
 int btb_b200_peer_close(void* ptr);
 /* btb_b200_gemv_bf16 with the exchange folded in: with `recv`, x is this rank's copy of an exchanged vector (words
- * [M, C]), taken word by word on its way into shared memory (M <= 8 and M*C*2 within the x staging budget, else
- * BTB_B200_ERR_DOMAIN: btb_b200_xchg_unpack first); with send->n > 0 the outputs go, marked, to every rank's copy at
- * [m][offset + r] (y may be null). */
-int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int M, int R, int C, const btb_b200_recv* recv,
+ * [M, C]), its T live rows taken word by word on their way into shared memory, the padding rows read as zeros (M <= 8 and
+ * M*C*2 within the x staging budget, else BTB_B200_ERR_DOMAIN: btb_b200_xchg_unpack first); with send->n > 0 the
+ * outputs go, marked, to every rank's copy at [m][offset + r] (y may be null). */
+int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int T, int M, int R, int C, const btb_b200_recv* recv,
                          const btb_b200_send* send, void* stream);
 /* btb_b200_gemv_norm (swiglu 0) / btb_b200_gemv_norm_swiglu (swiglu 1) over bf16 weights with the exchange folded in:
  * with `recv`, y_add is this rank's copy of an exchanged vector */
 int btb_b200_gemv_norm_x(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps, int centered,
                          void* h_out, void* y, int T, int M, int R, int C, int swiglu, const btb_b200_recv* recv,
                          const btb_b200_send* send, void* stream);
+/* btb_b200_attn_step / btb_b200_attn_decode in a model cut over ranks by kv head (this rank's Hq query and Hk kv heads):
+ * the output rows go, marked, to every rank's copy of the full [T, stride] vector at [t][offset + head * D + d] */
+int btb_b200_attn_step_x(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t, const void* sin_t,
+                         const void* n0p, const void* depth, void* K, void* V, void* q, int Hq, int Hk, int D, long long hs,
+                         long long rs, int centered, float scale, void* part_m, void* part_l, void* part_acc, void* cnt,
+                         int win, const void* tbl, const void* sinks, int cap, const btb_b200_send* send, void* stream);
+int btb_b200_attn_decode_x(const void* q, const void* K, const void* V, const void* n0p, const void* par, int T, int Hq,
+                           int Hk, int D, long long hs, long long rs, float scale, void* part_m, void* part_l,
+                           void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
+                           const btb_b200_send* send, void* stream);
+/* btb_b200_attn_step (send null or n 0; out the local row) or btb_b200_attn_step_x (send set; out may be null) with the
+ * SMs the row leaves idle pulling up to the `l2_warm_kb` tunable of the next kernels' weights into L2 meanwhile - warm_a
+ * first, then warm_b (device pointers and byte counts, 16-byte aligned; null or 0: none). The reference warms L2 ahead of
+ * its tensor-core matvec with a kernel of its own (btb_l2_warm, native/cuda/btb_gemv_mma.cuh:317-357). */
+int btb_b200_attn_step_w(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t, const void* sin_t,
+                         const void* n0p, const void* depth, void* K, void* V, void* q, void* out, int Hq, int Hk, int D,
+                         long long hs, long long rs, int centered, float scale, void* part_m, void* part_l, void* part_acc,
+                         void* cnt, int win, const void* tbl, const void* sinks, int cap, const btb_b200_send* send,
+                         const void* warm_a, long long bytes_a, const void* warm_b, long long bytes_b, void* stream);
 /* (no counterpart in the reference) a finished local slice src bf16 [M, n] into every rank's copy, marked: for kernels
  * that do not send themselves. n, stride and offset multiples of 4. */
 int btb_b200_xchg_send(const void* src, int M, int n, const btb_b200_send* send, void* stream);
 /* (no counterpart in the reference) this rank's copy of an exchanged vector (words [M, C]) as plain bf16 dst [M, C] once
  * every word carries the hop's mark: for consumers that read plain vectors (wide passes), and where a wait on its own
- * is wanted. C a multiple of 8. */
+ * is wanted. M: the rows to take (a pass's live rows - a producer may send none for its padding rows). C a multiple of 8. */
 int btb_b200_xchg_unpack(const void* words, void* dst, int M, int C, const btb_b200_recv* recv, void* stream);
 /* the greedy pick over a vocabulary cut by rows: local_idx i64 [T] is this rank's lowest-index argmax within its slice
  * logits [T, Vl] (btb_b200_argmax_bf16); every rank receives every rank's (value, v_offset + index) and takes the largest
