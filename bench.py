@@ -30,6 +30,8 @@ sys.path.insert(0, ROOT)
 
 METRIC = "bf16 decode tok/s @bs1 (Qwen3-4B shape)"
 PROMPT = 128
+# each configuration's own prompt length (config 5's 32768 rows stand in the cache as seeded synthetic rows)
+PROMPTS = {"qwen3-4b-bf16": 128, "qwen3-4b-p12": 2048, "gpt-oss-20b": 1024, "qwen3-30b-a3b": 512, "llama-70b": 128}
 
 
 def measured_hbm_peak() -> tuple[float, str]:
@@ -197,15 +199,18 @@ def run_reference(args, rank: int) -> None:
         return
     hw = host_weights_synth(cfg)
     steps = max(1, min(args.steps, 64))
-    tps, cores = time_cpu_tier(cfg, hw, steps, warmup=min(args.warmup, 2))
+    tps, cores = time_cpu_tier(cfg, hw, steps, warmup=args.warmup)
     from oracle import oracle as O
 
     line = {
         "impl": "reference", "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 2), "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1000.0 / tps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 activations over bf16 weights", "data": "synthetic",
+        # the same workload record as the GPU arm's: what differs (the CPU tier, its cores) is in cpu_baseline
         "config": {"workload": f"{cfg.name}-shape bf16, batch 1, greedy decode after a 128-token prompt",
-                   "parallelism": "cpu tier, all host cores", "bytes_per_token": cfg.weight_bytes_per_token("bf16")},
+                   "parallelism": "1 device", "graph_steps": 1, "step_kernel": 0,
+                   "l2": f"weights a rank streams per step {cfg.weight_bytes_per_token('bf16') / 1e9:.2f} GB > L2 126 MB (inputs "
+                         "larger than L2)", "pdl": None, "prefill": None, "bytes_per_token": cfg.weight_bytes_per_token("bf16")},
         "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "port",
                          "sample": f"{steps} full decode steps, isa {O.isa()}"},
         "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -268,8 +273,9 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
     import dataclasses
 
     K, W = args.steps, max(args.warmup, 3)
-    cap = (((512 if args.speculative else PROMPT) + 2 * (K + W) + 96 + 511) // 512) * 512
-    storage, parallelism = "bf16", ("replicas only" if world > 1 else "1 gpu")
+    n_prompt = args.prompt or PROMPTS[args.workload]
+    cap = (((512 if args.speculative else n_prompt) + 2 * (K + W) + 96 + 511) // 512) * 512
+    storage, parallelism = "bf16", ("replicas only" if world > 1 else "1 device")
     if args.pdl is not None:
         capi.set_tuning(pdl=args.pdl)
     if args.l2_warm_kb is not None:
@@ -301,7 +307,7 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         storage = cfg.expert_fmt
         mw = MO.synth_moe_weights(cfg, seed=0, ep_rank=rank, ep_size=world)
         eng = MO.MoEEngine(mw, cap=cap)
-        parallelism = f"ep{world}" if world > 1 else "1 gpu"
+        parallelism = f"ep{world}" if world > 1 else "1 device"
     else:
         from btb_b200 import parallel as P
 
@@ -311,9 +317,10 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         shard = tp_synth_shard(cfg, rank, world)
         eng = P.TPEngine(cfg, shard, rank, world, cap=cap)
         mw = shard
-        parallelism = f"tp{world}" if world > 1 else "1 gpu"
+        parallelism = f"tp{world}" if world > 1 else "1 device"
     g = torch.Generator().manual_seed(0)
-    prompt = torch.randint(0, cfg.vocab, (PROMPT,), generator=g)
+    prompt = torch.randint(0, cfg.vocab, (n_prompt,), generator=g)
+    prefill = None
     eng.reset()
     if args.speculative:
         run_speculative(args, eng, cfg, storage, parallelism, rank, world, dist)
@@ -329,7 +336,16 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         eng.n0.fill_(ctx)
         eng.bufs(1)["ids"][0] = 1
     else:
-        last = eng.prefill(prompt)
+        # the prompt is really prefilled (outside the timed region: the metric is the rate after the first token): on the
+        # tensor cores where the engine has the GEMM path (one GPU, bf16 weights), else by chain passes of 32 rows
+        gemm = args.prefill == "gemm" or (args.prefill == "auto" and type(eng) is E.CardEngine and storage == "bf16"
+                                          and n_prompt >= 256)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        last = eng.prefill_gemm(prompt) if gemm else eng.prefill(prompt)
+        torch.cuda.synchronize()
+        prefill = {"tokens": n_prompt, "ms": (time.perf_counter() - t0) * 1000.0,
+                   "how": "tensor-core GEMMs over 256-row chunks (tcgen05)" if gemm else "chain passes of 32 rows"}
         first = int(last.float().argmax(-1)) if not hasattr(eng, "tp_bufs") else 1
         eng.bufs(1)["ids"][0] = first
     graph = eng.step_graph(args.graph_steps, publish=True)
@@ -375,57 +391,24 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
         e2e_s = float(t[0])
     e2e = world * K / e2e_s
 
-    # roofline: one token's GEMV launches over the model's own weights, nothing else on the stream
-    g1 = eng.bufs(1)
-    s = capi.stream_ptr()
-
+    # roofline: one token's GEMV launches - the variants the step itself launches (norm folded into the qkv, gate/up and
+    # head GEMVs, SwiGLU in the gate/up GEMV's epilogue) - over the model's own weights, nothing else on the stream
     dense_model = args.workload.startswith("qwen3-4b") and not hasattr(eng, "tp_bufs")
-
-    def gemvs():
-        H, D, I = cfg.hidden, cfg.head_dim, cfg.inter
-        if not dense_model:
-            return
-        for L in mw.layers:
-            eng._matvec(L.qkv, g1["x"], g1["qkv"], 1, cfg.qkv_rows, H, s)
-            eng._matvec(L.o, g1["att"], g1["y"], 1, H, cfg.q_heads * D, s)
-            eng._matvec(L.gu, g1["x"], g1["gu"], 1, 2 * I, H, s)
-            eng._matvec(L.down, g1["m"], g1["y"], 1, H, I, s)
-        eng._matvec(mw.embed, g1["x"], g1["logits"], 1, cfg.vocab, H, s)
-
-    n_gemv = 4 * cfg.layers + 1
-    for _ in range(3 if dense_model else 0):
-        gemvs()
-    torch.cuda.synchronize()
-    e0.record()
-    ROUNDS = 5
-    for _ in range(ROUNDS):
-        gemvs()
-    e1.record()
-    torch.cuda.synchronize()
-    gemv_ms = max(e0.elapsed_time(e1) / ROUNDS, 1e-6)
-    wbytes = eng.weight_bytes() if dense_model else 0
-    # algorithmic bytes of one token's GEMVs: the weights as stored, plus each launch's x and y vectors
-    H_, A_, I_ = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.inter
-    abytes = wbytes + cfg.layers * 2 * (3 * H_ + cfg.qkv_rows + A_ + 3 * I_ + H_) + 2 * (H_ + cfg.vocab)
     peak, which = measured_hbm_peak()
-    achieved = abytes / (gemv_ms / 1000.0) / 1e9
-    roof = {"bound": "hbm", "kernel": "gemv_stream (all of a token's GEMVs)", "achieved": achieved, "peak": peak,
-            "unit": "GB/s", "frac": achieved / peak, "peak_source": which, "frac_of_8tbs": achieved / 8000.0,
-            "launches": n_gemv, "avg_launch_us": gemv_ms * 1000.0 / n_gemv,
-            # DRAM bytes a launch: the ncu capture's read+write over algorithmic bytes, scaled to the average launch
-            "traffic": TRAFFIC[storage] * abytes / n_gemv if TRAFFIC.get(storage) else None}  # fmt: skip
+    roof = gemv_roofline(eng, mw, cfg, storage, peak, which) if dense_model else None
 
     line = {
         "metric": METRIC, "value": tps, "unit": "tok/s", "n_gpus": world, "steps": steps_done, "warmup": W,
         "ms_per_step": ms / steps_done, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if storage == "bf16" else f"bf16 ({STORED.get(storage, storage)} weights widened in registers)",
         "data": "synthetic",
-        "config": {"workload": f"{cfg.name}-shape {storage}, batch 1, greedy decode after a 128-token prompt"
+        "config": {"workload": f"{cfg.name}-shape {storage}, batch 1, greedy decode after a {n_prompt}-token prompt"
                    if args.workload != "llama-70b" else f"{cfg.name}-shape bf16, batch 1, greedy decode over a "
-                   f"{args.context or 32768}-row synthetic cache",
+                   f"{args.context or 32768}-row synthetic cache (seeded rows, not a prefilled prompt)",
                    "parallelism": parallelism, "graph_steps": args.graph_steps, "step_kernel": args.step_kernel,
-                   "l2": f"weights per step {cfg.weight_bytes_per_token(storage) / 1e9:.1f} GB > L2 126 MB (inputs larger "
-                         "than L2)", "pdl": args.pdl,
+                   "l2": f"weights a rank streams per step {cfg.weight_bytes_per_token(storage) / max(1, world if parallelism.startswith(('tp', 'ep')) else 1) / 1e9:.2f}"
+                         " GB > L2 126 MB (inputs larger than L2)", "pdl": args.pdl,
+                   "prefill": prefill if n_prompt != 128 else None,
                    "bytes_per_token": cfg.weight_bytes_per_token(storage)},
         "clocks": clk.summary(),
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8},
@@ -465,6 +448,84 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> None:
 
 
 STORED = {"p12": "pack12", "mx4": "MXFP4 expert", "fp8": "FP8 block-scaled"}
+
+
+def gemv_roofline(eng, mw, cfg, storage, peak, which) -> dict:
+    """CUDA events around the step's own GEMV launches over the model's own matrices (36 distinct matrices a kind: far
+    past L2): the five kinds one after another as the step orders them (the `achieved` figure: algorithmic bytes of all
+    145 launches over their time) and each kind alone (the split)"""
+    import torch
+
+    from btb_b200 import capi
+    from btb_b200 import engine as E
+    from btb_b200.capi import call, ptr
+
+    g = eng.bufs(1)
+    s = capi.stream_ptr()
+    H, A, I, V = cfg.hidden, cfg.q_heads * cfg.head_dim, cfg.inter, cfg.vocab
+
+    def parts(W):
+        if isinstance(W, E.P12Matrix):
+            return (ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val), ptr(W.esc_row))
+        return (ptr(W), 0, 0, 0, 0, 0)
+
+    def normed(W, nw, out, R, swiglu=False):
+        call("btb_b200_gemv_norm_swiglu" if swiglu else "btb_b200_gemv_norm", *parts(W), ptr(g["h"]), ptr(g["y"]), ptr(nw),
+             cfg.eps, 0, ptr(g["h2"]), ptr(out), 1, 1, R, H, capi.stream_ptr())
+
+    kinds = {
+        "qkv (norm folded in)": lambda L: normed(L.qkv, L.ln1, g["qkv"], cfg.qkv_rows),
+        "o": lambda L: eng._matvec(L.o, g["att"], g["y"], 1, H, A, capi.stream_ptr()),
+        "gate/up (norm in, SwiGLU out)": lambda L: normed(L.gu, L.ln2, g["m"], 2 * I, True),
+        "down": lambda L: eng._matvec(L.down, g["m"], g["y"], 1, H, I, capi.stream_ptr()),
+    }
+    bpw = 2.0 if storage == "bf16" else 1.5
+    shape = {"qkv (norm folded in)": (cfg.qkv_rows, H), "o": (H, A), "gate/up (norm in, SwiGLU out)": (2 * I, H), "down": (H, I)}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, rounds=5):
+        """ms a round of `fn`'s launches, replayed as a captured graph (as the step runs them: no host launch gaps)"""
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(rounds):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return max(e0.elapsed_time(e1) / rounds, 1e-6)
+
+    def whole():
+        for L in mw.layers:
+            for f in kinds.values():
+                f(L)
+        normed(mw.embed, mw.norm, g["logits"], V)
+
+    split = {}
+    for name, f in kinds.items():
+        ms = timed(lambda f=f: [f(L) for L in mw.layers])
+        R, C_ = shape[name]
+        by = R * C_ * bpw + 2 * (C_ + (R // 2 if "SwiGLU" in name else R))
+        split[name] = {"us": ms * 1000 / cfg.layers, "gbs": by * cfg.layers / ms / 1e6, "frac": by * cfg.layers / ms / 1e6 / peak}
+    ms = timed(lambda: normed(mw.embed, mw.norm, g["logits"], V), rounds=20)
+    split["head (norm folded in)"] = {"us": ms * 1000, "gbs": (V * H * 2 + 2 * (H + V)) / ms / 1e6,
+                                      "frac": (V * H * 2 + 2 * (H + V)) / ms / 1e6 / peak}  # fmt: skip
+    gemv_ms = timed(whole)
+    n_gemv = 4 * cfg.layers + 1
+    # algorithmic bytes of one token's GEMVs: the weights as stored, plus each launch's x and y vectors
+    abytes = eng.weight_bytes() + cfg.layers * 2 * (3 * H + cfg.qkv_rows + A + 2 * I + H) + 2 * (H + V)
+    achieved = abytes / (gemv_ms / 1000.0) / 1e9
+    return {"bound": "hbm", "kernel": "gemv_stream: the step's own GEMV launches (norm prologue, SwiGLU epilogue, plain), "
+            "one token's 145 in step order", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "peak_source": which, "frac_of_8tbs": achieved / 8000.0, "launches": n_gemv,
+            "avg_launch_us": gemv_ms * 1000.0 / n_gemv, "per_kind": split,
+            # DRAM bytes a launch: the ncu capture's read+write over algorithmic bytes, scaled to the average launch
+            "traffic": TRAFFIC[storage] * abytes / n_gemv if TRAFFIC.get(storage) else None}
 
 
 def tp_collective(eng, cfg, world, dist) -> dict:
@@ -510,10 +571,91 @@ def tp_collective(eng, cfg, world, dist) -> dict:
             "inside the step the send and the take are parts of the GEMV kernels"}
 
 
+def run_ref_kernels(args) -> None:
+    """the REFERENCE's own card kernels (oracle/_ref: its CUDA sources compiled for this card by oracle/build_ref.sh) and
+    this library's, launched through the same typed launchers with the reference's own grids at the Qwen3-4B shape, each
+    kind over 24 distinct matrices as one captured graph: the same-box baseline the new kernels have to beat. A checker's
+    leg, not the product's: nothing here is on the decode path."""
+    import torch
+
+    from btb_b200 import launcher as L
+    from tests import refkernels
+
+    if not refkernels.available():
+        print(json.dumps({"ref_gpu_kernels": None, "why": "oracle/_ref is not built (oracle/build_ref.sh)"}))
+        return
+    cfg_H, A, I, Hq, Hk, D = 2560, 4096, 9728, 32, 8, 128
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *sh: (torch.randn(*sh, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)  # noqa: E731
+    N = 24
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+
+    def timed(fn, rounds=5):
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(rounds):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1000.0 / rounds / N  # us a launch
+
+    out: dict = {}
+    launchers = {"reference": refkernels.RefLauncher(), "b200": L.B200Launcher()}
+    for name, (R, C_) in {"gemv_bf16_m1 19456x2560": (2 * I, cfg_H), "gemv_bf16_m1 2560x4096": (cfg_H, A),
+                          "gemv_bf16_m1 2560x9728": (cfg_H, I)}.items():  # fmt: skip
+        ws = [rnd(R, C_) for _ in range(N)]
+        x, y = rnd(1, C_), torch.zeros(1, R, dtype=torch.bfloat16, device="cuda")
+        for who, lz in launchers.items():
+            us = timed(lambda lz=lz: [L.btb_gemv_bf16(lz, 1, ((R + 3) // 4, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(),
+                                                      y.data_ptr(), R, C_) for w in ws])  # fmt: skip
+            out.setdefault(name, {})[who] = {"us": us, "gbs": R * C_ * 2 / us / 1e3}
+        del ws
+    # the tensor-core matvec at 8 live rows (the reference's grid: a block of 4 warps a 64 rows, btb/engine/cuda.py:1473-1477)
+    R, C_ = 2 * I, cfg_H
+    ws = [rnd(R, C_) for _ in range(N)]
+    x32, y32 = torch.zeros(32, C_, dtype=torch.bfloat16, device="cuda"), torch.zeros(32, R, dtype=torch.bfloat16, device="cuda")
+    x32[:8] = rnd(8, C_)
+    for who, lz in launchers.items():
+        us = timed(lambda lz=lz: [L.btb_gemv_mma_bf16(lz, ((R + 63) // 64, 1, 1), (128, 1, 1), w.data_ptr(), x32.data_ptr(),
+                                                      y32.data_ptr(), R, C_, 8) for w in ws])  # fmt: skip
+        out.setdefault("gemv_mma_bf16 19456x2560 (8 rows)", {})[who] = {"us": us, "gbs": R * C_ * 2 / us / 1e3}
+    del ws
+    # decode attention, one row over 4096 cached rows (24 arenas: the keys come from DRAM)
+    n0v, cap = 4096, 4608
+    S = cap // 512
+    Ks, Vs = [rnd(cap, Hk, D) * 50 for _ in range(N)], [rnd(cap, Hk, D) * 50 for _ in range(N)]
+    q, att = rnd(1, Hq, D) * 50, torch.zeros(1, Hq * D, dtype=torch.bfloat16, device="cuda")
+    pm, pl = torch.zeros(S * Hq, device="cuda"), torch.zeros(S * Hq, device="cuda")
+    pa, cnt = torch.zeros(S * Hq * D, device="cuda"), torch.zeros(Hq, dtype=torch.int32, device="cuda")
+    n0, par = torch.tensor([n0v], dtype=torch.int32, device="cuda"), torch.tensor([-1], dtype=torch.int32, device="cuda")
+    G = Hq // Hk
+    for who, lz in launchers.items():
+        us = timed(lambda lz=lz: [L.btb_attn_flash(lz, D, ((G + 7) // 8, S, Hk), (256, 1, 1), q.data_ptr(), K_.data_ptr(),
+                                                   V_.data_ptr(), att.data_ptr(), n0.data_ptr(), par.data_ptr(), 1, Hq, Hk, D,
+                                                   Hk * D, float(D**-0.5), pm.data_ptr(), pl.data_ptr(), pa.data_ptr(),
+                                                   cnt.data_ptr(), 0, 0) for K_, V_ in zip(Ks, Vs)])  # fmt: skip
+        out.setdefault("attn_flash_d128, 1 row over 4096 cached rows", {})[who] = {"us": us, "gbs": 2 * n0v * Hk * D * 2 / us / 1e3}
+    # residual + RMSNorm over one row
+    h, yv, wn, xo = rnd(N, cfg_H), rnd(N, cfg_H), rnd(cfg_H), torch.zeros(1, cfg_H, dtype=torch.bfloat16, device="cuda")
+    for who, lz in launchers.items():
+        us = timed(lambda lz=lz: [L.btb_add_rmsnorm(lz, (1, 1, 1), (256, 1, 1), h[i].data_ptr(), yv[i].data_ptr(), wn.data_ptr(),
+                                                    1e-6, xo.data_ptr(), cfg_H, 0) for i in range(N)])  # fmt: skip
+        out.setdefault("add_rmsnorm 1x2560", {})[who] = {"us": us}
+    print(json.dumps({"ref_gpu_kernels": out, "sms": sms, "how": "CUDA events around a captured graph of 24 launches a kind "
+                      "over 24 distinct inputs, 5 replays; the reference's kernels compiled for sm_100a with its own flags"}))
+
+
 def run_case(args) -> None:
     """one kernel on a small case, for a profiler capture or a quick look: `gemv:RxC[:M[:fmt]]` rotates over enough
-    seeded matrices to stay out of L2 (fmt bf16 | p12 | tc: the tensor-core matvec); `attn:N` is the step's fused attention row over N cached rows
-    at the Qwen3-4B head shape. Prints us a launch (CUDA events) and, for a GEMV, the weight-streaming rate."""
+    seeded matrices to stay out of L2 (fmt bf16 | p12 | fp8 | tc: the tensor-core matvec); `attn:N` is the step's fused
+    attention row over N cached rows at the Qwen3-4B head shape, `attnv:N:T` a verify pass's T rows over N cached rows. Prints us a launch (CUDA events) and, for a GEMV, the weight-streaming rate."""
     import torch
 
     from btb_b200 import capi
@@ -529,7 +671,7 @@ def run_case(args) -> None:
         R, C_ = (int(v) for v in parts[0].split("x"))
         M = int(parts[1]) if len(parts) > 1 else 1
         fmt = parts[2] if len(parts) > 2 else "bf16"
-        per = R * C_ * (1.5 if fmt == "p12" else 2)
+        per = R * C_ * {"p12": 1.5, "fp8": 1.0}.get(fmt, 2)
         nmat = max(2, int(400e6 // per) + 1)
         gen = torch.Generator(device="cuda").manual_seed(0)
         ws = []
@@ -539,6 +681,11 @@ def run_case(args) -> None:
                 from btb_b200 import pack12
 
                 w = E.P12Matrix(pack12.pack_bf16(w), R, C_, "cuda")
+            elif fmt == "fp8":  # e4m3 bytes without NaN codes, bf16-valued scales a 128 x 128 block (config 4's draw)
+                q = torch.randint(0, 256, (R, C_), device="cuda", generator=gen, dtype=torch.uint8)
+                q = torch.where((q & 0x7F) == 0x7F, q & 0xF0, q)
+                sc = (torch.randn(R // 128, C_ // 128, device="cuda", generator=gen) * 0.02).to(torch.bfloat16).float()
+                w = E.FP8Matrix(q, sc)
             ws.append(w)
         x = torch.randn(M, C_, device="cuda", generator=gen).to(torch.bfloat16)
         y = torch.zeros(M, R, device="cuda", dtype=torch.bfloat16)
@@ -553,6 +700,8 @@ def run_case(args) -> None:
             elif fmt == "p12":
                 call("btb_b200_gemv_p12", ptr(w.lo), ptr(w.hi4), w.table, ptr(w.esc_idx), ptr(w.esc_val), ptr(w.esc_row),
                      ptr(x), ptr(y), M, R, C_, sp)  # fmt: skip
+            elif fmt == "fp8":
+                call("btb_b200_gemv_fp8", ptr(w.w), ptr(w.scales), w.sr, w.sc, ptr(x), ptr(y), M, R, C_, sp)
             else:
                 call("btb_b200_gemv_bf16", ptr(w), ptr(x), ptr(y), M, R, C_, sp)
 
@@ -587,6 +736,34 @@ def run_case(args) -> None:
             e1.record()
             torch.cuda.synchronize()
         out.update(us_per_launch=e0.elapsed_time(e1) * 1000 / 20, cached_rows=n0v)
+    elif kind == "attnv":
+        # a verify pass's attention: `attnv:N:T` = T tree rows (a chain) over N cached rows, Qwen3-4B head shape,
+        # through btb_b200_norm_rope_kv + btb_b200_attn_decode; the cache's rows rotate over layers' worth of arenas so
+        # that the keys come from DRAM
+        n0v, T = (int(v) for v in rest.split(":"))
+        c = E.QWEN3_4B
+        Hq, Hk, D, cap = c.q_heads, c.kv_heads, c.head_dim, ((n0v + 64 + 511) // 512) * 512
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        rnd = lambda *sh: torch.randn(*sh, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
+        arenas = max(2, int(300e6 // (2 * cap * Hk * D * 2)) + 1)
+        Ks, Vs = [rnd(cap, Hk, D) for _ in range(arenas)], [rnd(cap, Hk, D) for _ in range(arenas)]
+        M = E.pad_rows(T)
+        q, att = rnd(M, Hq, D), torch.zeros(M, Hq * D, device="cuda", dtype=torch.bfloat16)
+        S = cap // 512
+        pm, pl = torch.zeros(S * M * Hq, device="cuda"), torch.zeros(S * M * Hq, device="cuda")
+        pa, cnt = torch.zeros(S * M * Hq * D, device="cuda"), torch.zeros(M * Hq, dtype=torch.int32, device="cuda")
+        n0 = torch.tensor([n0v], dtype=torch.int32, device="cuda")
+        par = torch.arange(-1, M - 1, dtype=torch.int32, device="cuda")
+        for it in range(3):
+            e0.record()
+            for K_, V_ in zip(Ks, Vs):
+                call("btb_b200_attn_decode", ptr(q), ptr(K_), ptr(V_), ptr(att), ptr(n0), ptr(par), T, Hq, Hk, D, D, Hk * D,
+                     float(D**-0.5), ptr(pm), ptr(pl), ptr(pa), ptr(cnt), 0, 0, 0, cap, sp)  # fmt: skip
+            e1.record()
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1000 / arenas
+        kv = 2 * (n0v + T) * Hk * D * 2
+        out.update(us_per_launch=us, cached_rows=n0v, rows=T, kv_bytes=kv, gbs=kv / us / 1e3, arenas=arenas)
     elif kind == "moe":
         # the picked experts' gate/up matvecs of one MoE layer: moe:fp8 (Qwen3-30B-A3B shape, 8 picks of 128 experts)
         # or moe:mx4 (gpt-oss-20b shape, 4 picks of 32); the picks rotate so that the rows come from DRAM
@@ -773,12 +950,17 @@ def main() -> None:
     ap.add_argument("--wide-tc", type=int, default=1, help="--batch: the tensor-core matvec for the pass of B rows")
     ap.add_argument("--case", default="", help="one kernel on a small case: gemv:RxC[:M[:fmt]], attn:N, moe:fp8|mx4, sample:V")
     ap.add_argument("--speculative", type=int, default=0, help="verify an n-gram tree of this many drafts a pass")
+    ap.add_argument("--ref-kernels", action="store_true", help="time the reference's own card kernels beside this library's")
+    ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0: the configuration's own length)")
+    ap.add_argument("--prefill", default="auto", choices=["auto", "gemm", "chain"])
     ap.add_argument("--replicas", action="store_true", help="--gpus N: N independent copies instead of one model over N ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.case:
+    if args.ref_kernels:
+        run_ref_kernels(args)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args, rank)

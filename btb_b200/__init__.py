@@ -2,8 +2,12 @@
 
 ``capi``      ctypes binding of the C-ABI in include/btb_b200.h (libbtb_b200.so, built by ``btb_b200.build``)
 ``launcher``  a drop-in for btb's ``Launcher`` protocol: the reference's kernel names on this library
-``engine``    the card graph's step (embed -> layers -> head -> pick -> publish) and greedy loop
-``pack12`` / ``mxfp4`` / ``fp8``  host-side codecs of the weight formats the kernels read as stored
+``engine``    the card graph's step (embed -> layers -> head -> pick -> publish), greedy loop and prefill
+``moe``       the MoE decoder: router, picked experts over MXFP4 / FP8 / bf16 as stored, ordered sum
+``batch``     small-batch decode: B sequences through one pass of B rows
+``parallel``  one dense model tensor-parallel over the GPUs of a box; ``exchange`` its peer-mapped memory
+``draft``     n-gram drafting and the speculative greedy loop; ``sampling`` the sampled pick's host side
+``pack12``    btb's 12-bit lossless bf16 store, encoded on the card
 """
 
-__all__ = ["capi", "launcher", "engine", "pack12"]
+__all__ = ["capi", "launcher", "engine", "moe", "batch", "parallel", "exchange", "draft", "sampling", "pack12"]

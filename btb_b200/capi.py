@@ -43,6 +43,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_gemv_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_tc_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
     "btb_b200_gemv_tc_workspace_bytes": (_SZ, [_I, _I]),
+    "btb_b200_gemm_tc_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_silu_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_p12": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_fp8": (_I, [_P, _P, _I, _I, _P, _P, _I, _I, _I, _P]),

@@ -64,7 +64,9 @@ struct GemvArgs {
 };
 
 // NWT: the most warps a CTA of this instance is launched with (its register budget); the launch picks how many
-template <int M, int FMT, int XM, int NWT>
+// XCHG: the instance built for a model cut over ranks (marked words in, marked words out); the one-GPU instance carries
+// none of that code
+template <int M, int FMT, int XM, int NWT, bool XCHG>
 __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int NT = 0;  // the staging loops stride by the block's own width
@@ -145,9 +147,9 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
     pdl_launch_dependents();
     pdl_wait();  // x is the previous kernel's output
     // ... or, in a model cut over ranks, every rank's: the words are taken as they arrive
-    const bool marked = A.recv.pass != nullptr;
+    const bool marked = XCHG && A.recv.pass != nullptr;
     const uint32_t mark_in = marked ? b2_hop_mark(A.recv.pass, A.recv.per_pass, A.recv.base) : 0u;
-    const uint32_t mark_out = A.send.n != 0 ? b2_hop_mark(A.send.pass, A.send.per_pass, A.send.base) : 0u;
+    const uint32_t mark_out = XCHG && A.send.n != 0 ? b2_hop_mark(A.send.pass, A.send.per_pass, A.send.base) : 0u;
 
     if (XS) {
         if (XM == X_SMEM) stage_x_copy<M, NT>(xs, A.x, C, marked, mark_in, A.T);
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(NWT * 32, 1) gemv_stream(const GemvArgs A) {
                     gate[m] = bfround(s);
                 } else if (lane == 0) {
                     const bf16 v = pair == 0 ? f2bf(s) : f2bf(bfround(act_silu(gate[m])) * bfround(s));
-                    if (A.send.n == 0) {
+                    if (!XCHG || A.send.n == 0) {
                         A.y[(size_t)m * R + c_row] = v;
                     } else {
                         const size_t at = (size_t)m * A.send.stride + A.send.offset + c_row;
@@ -303,14 +305,24 @@ Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     return p;
 }
 
-template <int M, int FMT, int XM, int NWT>
-int launch_nw(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
-    auto kern = gemv_stream<M, FMT, XM, NWT>;
+template <int M, int FMT, int XM, int NWT, bool XCHG>
+int launch_x(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
+    auto kern = gemv_stream<M, FMT, XM, NWT, XCHG>;
     static bool allowed[64];  // the opt-in past 48 KB of dynamic shared memory, once a device
     int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
     if (rc) return rc;
     if (p.nw > NWT) return B2_ERR_DOMAIN;
     return b2_launch(reinterpret_cast<const void*>(kern), dim3(p.grid), dim3(p.nw * 32), p.smem, stream, a, 1);
+}
+template <int M, int FMT, int XM, int NWT>
+int launch_nw(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
+    // the exchange is built for bf16 weights with x staged plainly or under the norm prologue, and for wide passes' sends
+    constexpr bool CAN = FMT == F_BF16 && XM != X_SMEM_SILU;
+    if (a.recv.pass != nullptr || a.send.n != 0) {
+        if (!CAN) return B2_ERR_DOMAIN;
+        return launch_x<M, FMT, XM, NWT, CAN>(a, p, stream);
+    }
+    return launch_x<M, FMT, XM, NWT, false>(a, p, stream);
 }
 template <int M, int FMT, int XM>
 int launch_one(const GemvArgs& a, const Plan& p, cudaStream_t stream) {

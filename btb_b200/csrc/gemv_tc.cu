@@ -24,10 +24,14 @@ B2_DEFINE_STATUS(tc)
 namespace {
 
 constexpr int TC_BM = 128;  // weight rows a tile (the MMA's M)
-constexpr int TC_BN = 32;   // x rows, padded (the MMA's N)
+constexpr int TC_BN = 32;   // x rows a tile of the matvec, padded (the MMA's N); the prefill GEMM takes up to 256
 constexpr int TC_BK = 64;   // columns a stage: one 128-byte swizzle span of bf16
 constexpr int TC_STAGES_MAX = 10;  // ring depth at most; the launch picks (four stages let two CTAs share an SM)
-constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = TC_BN * TC_BK * 2, ST_BYTES = A_BYTES + B_BYTES;
+constexpr int A_BYTES = TC_BM * TC_BK * 2;
+template <int BN>
+struct TcTile {
+    static constexpr int B_BYTES = BN * TC_BK * 2, ST_BYTES = A_BYTES + B_BYTES;
+};
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
     asm volatile(
@@ -61,8 +65,17 @@ struct TcArgs {
     int R, C, M, kblocks_per_split, splits, stages;
 };
 
-__global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtensorMap tmW,
-                                                  const __grid_constant__ CUtensorMap tmX, const TcArgs A) {
+// BN: the x rows a CTA's tile holds. GEMM false: the matvec - one accumulator of 32 columns, gridDim.y cuts K into
+// ranges whose partial sums a second launch adds in range order. GEMM true: the prefill GEMM - gridDim.y walks the x
+// rows BN at a time and the CTA takes its tile's whole K, but in the matvec's own ranges: range s accumulates into its
+// own BN columns of tensor memory and the epilogue adds the ranges in order, so an output element is the matvec's sum
+// to the bit whatever the chunk's size and wherever in the chunk the row stands.
+template <int BN, bool GEMM>
+__global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_constant__ CUtensorMap tmW,
+                                                             const __grid_constant__ CUtensorMap tmX, const TcArgs A) {
+    constexpr int ST_BYTES = TcTile<BN>::ST_BYTES;
+    const int ranges = GEMM ? A.splits : 1;  // accumulators in tensor memory
+    const uint32_t tmem_cols = GEMM ? 512u : 32u;
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t full[TC_STAGES_MAX], empty[TC_STAGES_MAX], done;
     const int TC_STAGES = A.stages;
@@ -71,9 +84,10 @@ __global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtens
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
     const int row0 = blockIdx.x * TC_BM;
-    const int kb0 = blockIdx.y * A.kblocks_per_split;
     const int total_kb = (A.C + TC_BK - 1) / TC_BK;
-    const int nkb = max(0, min(A.kblocks_per_split, total_kb - kb0));
+    const int kb0 = GEMM ? 0 : blockIdx.y * A.kblocks_per_split;
+    const int nkb = GEMM ? total_kb : max(0, min(A.kblocks_per_split, total_kb - kb0));
+    const int n0 = GEMM ? blockIdx.y * BN : 0;  // the tile's first x row
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -84,8 +98,8 @@ __global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtens
         s_fail = 0;
         mbar_fence_init();
     }
-    if (warp == 0) {  // the accumulator's 32 columns of tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(32)
+    if (warp == 0) {  // the accumulators' columns of tensor memory (the GEMM takes the SM's whole 512: one CTA an SM)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -107,11 +121,11 @@ __global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtens
             const uint32_t bar = smem_u32(&full[s]);
             mbar_expect_tx(bar, ST_BYTES);
             tma_load_2d(smem_u32(tiles + s * ST_BYTES), &tmW, (kb0 + kb) * TC_BK, row0, bar);
-            tma_load_2d(smem_u32(tiles + s * ST_BYTES + A_BYTES), &tmX, (kb0 + kb) * TC_BK, 0, bar);
+            tma_load_2d(smem_u32(tiles + s * ST_BYTES + A_BYTES), &tmX, (kb0 + kb) * TC_BK, n0, bar);
         }
     } else if (warp == 1 && lane == 0) {
         // the issuer: four K = 16 instructions a stage; D f32, A and B bf16, both K-major, N = 32, M = 128
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         for (int kb = 0; kb < nkb; ++kb) {
             const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
             if (!mbar_wait_bounded(smem_u32(&full[s]), ph)) {
@@ -120,9 +134,13 @@ __global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtens
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a0 = smem_u32(tiles + s * ST_BYTES), b0 = a0 + A_BYTES;
+            // the GEMM's K block kb belongs to range kb / kps: its own accumulator, started afresh at the range's first block
+            const int rs = GEMM ? kb / A.kblocks_per_split : 0;
+            const int first = GEMM ? kb - rs * A.kblocks_per_split : kb;
 #pragma unroll
             for (int k = 0; k < TC_BK / 16; ++k)
-                umma_bf16(tmem, umma_desc_sw128(a0 + k * 32), umma_desc_sw128(b0 + k * 32), idesc, (kb | k) != 0);
+                umma_bf16(tmem + (uint32_t)(rs * BN), umma_desc_sw128(a0 + k * 32), umma_desc_sw128(b0 + k * 32), idesc,
+                          (first | k) != 0);
             umma_commit(smem_u32(&empty[s]));  // the stage is free once these have read it
         }
         umma_commit(smem_u32(&done));
@@ -133,28 +151,40 @@ __global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtens
     if (nkb > 0) ok = mbar_wait_bounded(smem_u32(&done), 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok && nkb > 0 && !*(volatile int*)&s_fail) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
-            "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-              "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-            : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int row = row0 + warp * 32 + lane;
-        if (row < A.R) {
-            if (A.splits == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            if (GEMM && n0 + c0 >= A.M) break;  // x rows past the pass
+            uint32_t r[32];
+            float tot[32];
 #pragma unroll
-                for (int n = 0; n < 32; ++n)
-                    if (n < A.M) A.y[(size_t)n * A.R + row] = f2bf(__uint_as_float(r[n]));
-            } else {
+            for (int n = 0; n < 32; ++n) tot[n] = 0.f;
+#pragma unroll 1
+            for (int rs = 0; rs < ranges; ++rs) {
+            const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(rs * BN + c0);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+                "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                  "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int n = 0; n < 32; ++n)
-                    if (n < A.M) A.part[((size_t)blockIdx.y * 32 + n) * A.R + row] = __uint_as_float(r[n]);
+            for (int n = 0; n < 32; ++n) tot[n] += __uint_as_float(r[n]);  // the ranges in order, from zero
+            }
+            if (row < A.R) {
+                if (GEMM || A.splits == 1) {
+#pragma unroll
+                    for (int n = 0; n < 32; ++n)
+                        if (n0 + c0 + n < A.M) A.y[(size_t)(n0 + c0 + n) * A.R + row] = f2bf(tot[n]);
+                } else {
+#pragma unroll
+                    for (int n = 0; n < 32; ++n)
+                        if (n < A.M) A.part[((size_t)blockIdx.y * 32 + n) * A.R + row] = __uint_as_float(r[n]);
+                }
             }
         }
     } else if (threadIdx.x == 0 && nkb > 0) {
@@ -162,7 +192,7 @@ __global__ void __launch_bounds__(128, 2) gemv_tc(const __grid_constant__ CUtens
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
 struct TcReduceArgs {
@@ -224,6 +254,37 @@ int tc_splits(int R, int C, int* kps = nullptr) {
     return (kb + per - 1) / per;
 }
 
+// three parameters (two tensor maps by value and the argument block): launched through the runtime's own form
+template <int BN, bool GEMM>
+int launch_tc(CUtensorMap& tw, CUtensorMap& tx, TcArgs& a, dim3 grid, int stages, cudaStream_t s) {
+    constexpr int ST = TcTile<BN>::ST_BYTES;
+    const int max_stages = min(TC_STAGES_MAX, (224 * 1024 - 1024) / ST);
+    stages = min(stages, max_stages);
+    a.stages = stages;
+    static bool allowed[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
+    if (!allowed[dev]) {
+        if (cudaFuncSetAttribute(gemv_tc<BN, GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_stages * ST + 1024) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return B2_ERR_CUDA;
+        }
+        allowed[dev] = true;
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = stages * ST + 1024;
+    cfg.stream = s;
+    void* params[3] = {&tw, &tx, &a};
+    if (cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(gemv_tc<BN, GEMM>), params) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return B2_ERR_CUDA;
+    }
+    return B2_OK;
+}
+
 }  // namespace
 
 extern "C" size_t btb_b200_gemv_tc_workspace_bytes(int R, int C) {
@@ -244,33 +305,43 @@ extern "C" int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int 
     if (make_map(&tw, w, (uint64_t)R, (uint64_t)C, TC_BM) || make_map(&tx, x, (uint64_t)M, (uint64_t)C, TC_BN)) return B2_ERR_CUDA;
     const int stages = b2_tuning().tc_stages > 0 ? min(TC_STAGES_MAX, b2_tuning().tc_stages) : 4;
     TcArgs a{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, kps, splits, stages};
-    const int smem = stages * ST_BYTES + 1024;
-    static bool allowed[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
-    if (!allowed[dev]) {
-        if (cudaFuncSetAttribute(gemv_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_STAGES_MAX * ST_BYTES + 1024) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return B2_ERR_CUDA;
-        }
-        allowed[dev] = true;
-    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // three parameters (two tensor maps by value and the argument block): launched through the runtime's own form
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof cfg);
-    cfg.gridDim = dim3((R + TC_BM - 1) / TC_BM, splits);
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    void* params[3] = {&tw, &tx, &a};
-    if (cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(gemv_tc), params) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return B2_ERR_CUDA;
-    }
+    if (const int rc = launch_tc<TC_BN, false>(tw, tx, a, dim3((R + TC_BM - 1) / TC_BM, splits), stages, s)) return rc;
     if (splits > 1) {
         TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(y), R, M, splits};
         return b2_launch((const void*)gemv_tc_reduce, dim3((M * R + 255) / 256), dim3(256), 0, s, ra);
     }
     return B2_OK;
+}
+
+// ---- the prefill GEMM ------------------------------------------------------------------------------------------------
+// y [T, R] = bf16(x [T, C] W^T) for a prompt chunk of T rows, T in the hundreds or thousands: the same kernel with tiles
+// of 128 weight rows by up to 256 x rows, every tile its whole K, no second launch. What it stands in for is btb's
+// btb_gemm_mma_bf16 (native/cuda/btb_gemm.cuh:154), whose rows are the tensor-core matvec's rows: here too an output
+// element is summed exactly as btb_b200_gemv_tc_bf16 sums it - the matrix's K ranges each in an accumulator of its own,
+// added in range order - so row t of a chunk carries the bits the matvec gives that row alone (tested): a prompt
+// prefilled in chunks of any size leaves the cache rows that 32-row tensor-core passes would have.
+extern "C" int btb_b200_gemm_tc_bf16(const void* w, const void* x, void* y, int T, int R, int C, void* stream) {
+    if (!w || !x || !y) return B2_ERR_NULL;
+    if (T < 1 || R <= 0 || C <= 0 || (C & 7)) return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return B2_ERR_DOMAIN;
+    // the matvec's K ranges for this matrix, an accumulator each: ranges * BN columns of the SM's 512
+    int kps = 0;
+    const int ranges = tc_splits(R, C, &kps);
+    int BN = ranges <= 2 ? 256 : ranges <= 4 ? 128 : ranges <= 8 ? 64 : 32;
+    while (BN > 32 && BN / 2 >= T) BN /= 2;  // a short chunk does not need the wide tile
+    CUtensorMap tw, tx;
+    if (make_map(&tw, w, (uint64_t)R, (uint64_t)C, TC_BM) || make_map(&tx, x, (uint64_t)T, (uint64_t)C, BN)) return B2_ERR_CUDA;
+    const int ytiles = (T + BN - 1) / BN;
+    if (ytiles > 65535) return B2_ERR_DOMAIN;
+    TcArgs a{static_cast<bf16*>(y), nullptr, R, C, T, kps, ranges, 4};
+    const dim3 grid((R + TC_BM - 1) / TC_BM, ytiles);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int stages = b2_tuning().tc_stages > 0 ? b2_tuning().tc_stages : 4;
+    switch (BN) {
+        case 32: return launch_tc<32, true>(tw, tx, a, grid, stages, s);
+        case 64: return launch_tc<64, true>(tw, tx, a, grid, stages, s);
+        case 128: return launch_tc<128, true>(tw, tx, a, grid, stages, s);
+        default: return launch_tc<256, true>(tw, tx, a, grid, stages, s);
+    }
 }

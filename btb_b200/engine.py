@@ -408,6 +408,65 @@ class CardEngine:
             call("btb_b200_publish", ptr(self.n0), 0, 0, 0, 0, T, s)
         return g["logits"][:T]
 
+    # -- prefill on the tensor cores -------------------------------------------------------------------------------
+    def prefill_gemm(self, prompt: torch.Tensor, chunk: int = 256) -> torch.Tensor:
+        """the prompt in chunks of up to `chunk` rows with every linear a tensor-core GEMM (btb_b200_gemm_tc_bf16) - the
+        reference's prefill (btb/engine/cuda.py:2817-3039 `_forward_card_prefill`: the step's own kernels over T rows, the
+        matvecs replaced by the GEMM whose rows are the tensor-core matvec's). The attention runs the decode kernel over
+        the chunk 32 rows at a time (each row against the cache rows before it and the chunk's rows up to itself, all
+        written by the chunk's norm + RoPE pass beforehand). bf16 weights only. Returns the last row's logits [1, V];
+        a row's values are the 32-row tensor-core pass's (`wide_tc`), to rounding the fp32-chain pass's."""
+        c = self.cfg
+        if not isinstance(self.w.layers[0].qkv, torch.Tensor):
+            raise TypeError("prefill_gemm reads bf16 weights")
+        H, Hq, Hk, D, I = c.hidden, c.q_heads, c.kv_heads, c.head_dim, c.inter
+        P = int(chunk)
+        if "wide" not in self._programs or self._programs["wide"]["h"].shape[0] < P:
+            bf = lambda *s_: torch.zeros(*s_, dtype=torch.bfloat16, device=self.dev)  # noqa: E731
+            self._programs["wide"] = {
+                "h": bf(P, H), "x": bf(P, H), "y": bf(P, H), "qkv": bf(P, c.qkv_rows), "q": bf(P, Hq, D), "att": bf(P, Hq * D),
+                "gu": bf(P, 2 * I), "m": bf(P, I), "ids": torch.zeros(P, dtype=torch.int64, device=self.dev),
+                "depth": torch.arange(P, dtype=torch.int32, device=self.dev),
+                "n0s": torch.zeros((P + 31) // 32, dtype=torch.int32, device=self.dev),
+            }  # fmt: skip
+        b, g32 = self._programs["wide"], self.bufs(32)
+        s = capi.stream_ptr()
+        k = self._k
+        prompt = prompt.to(self.dev, torch.int64)
+        n = int(prompt.numel())
+        for a in range(0, n, P):
+            T = min(P, n - a)
+            b["ids"][:T].copy_(prompt[a : a + T])
+            b["n0s"].copy_(self.n0 + torch.arange(0, b["n0s"].numel() * 32, 32, dtype=torch.int32, device=self.dev))
+            k("btb_b200_embed", ptr(self.w.embed), ptr(b["ids"]), ptr(b["h"]), T, H, c.vocab, s)
+            y_prev = None
+            for i, L in enumerate(self.w.layers):
+                k("btb_b200_add_rmsnorm", ptr(b["h"]), ptr(y_prev), ptr(L.ln1), c.eps, ptr(b["x"]), T, H, 0, s)
+                k("btb_b200_gemm_tc_bf16", ptr(L.qkv), ptr(b["x"]), ptr(b["qkv"]), T, c.qkv_rows, H, s)
+                k("btb_b200_norm_rope_kv", ptr(b["qkv"]), ptr(L.wq), ptr(L.wk), c.eps, ptr(self.cos), ptr(self.sin),
+                  ptr(self.n0), ptr(b["depth"]), ptr(self.K[i]), ptr(self.V[i]), ptr(b["q"]), T, Hq, Hk, D, self.hs, self.rs,
+                  0, 0, self.cap, s)  # fmt: skip
+                for j, r0 in enumerate(range(0, T, 32)):  # rows r0 .. r0 + 31: a chain standing after n0 + r0 rows
+                    rows = min(32, T - r0)
+                    k("btb_b200_attn_decode", ptr(b["q"][r0]), ptr(self.K[i]), ptr(self.V[i]), ptr(b["att"][r0]),
+                      ptr(b["n0s"][j : j + 1]), ptr(g32["par"]), rows, Hq, Hk, D, self.hs, self.rs, float(D**-0.5),
+                      ptr(g32["part_m"]), ptr(g32["part_l"]), ptr(g32["part_acc"]), ptr(g32["cnt"]), 0, 0, 0, self.cap, s)  # fmt: skip
+                k("btb_b200_gemm_tc_bf16", ptr(L.o), ptr(b["att"]), ptr(b["y"]), T, H, Hq * D, s)
+                k("btb_b200_add_rmsnorm", ptr(b["h"]), ptr(b["y"]), ptr(L.ln2), c.eps, ptr(b["x"]), T, H, 0, s)
+                k("btb_b200_gemm_tc_bf16", ptr(L.gu), ptr(b["x"]), ptr(b["gu"]), T, 2 * I, H, s)
+                k("btb_b200_silu_mul", ptr(b["gu"]), ptr(b["m"]), T, I, s)
+                k("btb_b200_gemm_tc_bf16", ptr(L.down), ptr(b["m"]), ptr(b["y"]), T, H, I, s)
+                y_prev = b["y"]
+            call("btb_b200_publish", ptr(self.n0), 0, 0, 0, 0, T, s)
+            last = T - 1
+        # the last row's logits: the final norm and the head over that one row
+        g1 = self.bufs(1)
+        g1["h"].copy_(b["h"][last : last + 1])
+        g1["y"].copy_(b["y"][last : last + 1])
+        k("btb_b200_add_rmsnorm", ptr(g1["h"]), ptr(g1["y"]), ptr(self.w.norm), c.eps, ptr(g1["x"]), 1, H, 0, s)
+        self._matvec(self.w.embed, g1["x"], g1["logits"], 1, c.vocab, H, s)
+        return g1["logits"][:1]
+
     def prefill(self, prompt: torch.Tensor) -> torch.Tensor:
         """the prompt through chain passes of up to 32 rows; returns the last row's logits"""
         lg = None

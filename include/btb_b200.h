@@ -52,6 +52,11 @@ int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int 
  * partial sums of matrices with few rows. */
 int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* workspace, void* stream);
 size_t btb_b200_gemv_tc_workspace_bytes(int R, int C);
+/* btb_gemm_mma_bf16 (native/cuda/btb_gemm.cuh:154): the prefill GEMM y [T, R] = bf16(x [T, C] W^T) for a prompt chunk of
+ * any T >= 1 on the same tcgen05 kernel - tiles of 128 weight rows by up to 256 x rows, every tile its whole K. An output
+ * element is one accumulation over all of k in k order, so row t carries the bits btb_b200_gemv_tc_bf16 gives that row in
+ * a pass of any width (the reference's rule for its GEMM and its tensor-core matvec, btb/engine/cuda.py:2827-2832). */
+int btb_b200_gemm_tc_bf16(const void* w, const void* x, void* y, int T, int R, int C, void* stream);
 /* btb_gemv_silu_bf16_m{M} (btb_kernels.cu:171-227): gu [M,2C] (gate then up), x = bf16(bf16(silu(g)) * u)
  * computed on the way in. M <= 8 and M*C*2 <= the x staging budget, else BTB_B200_ERR_DOMAIN (use
  * btb_b200_silu_mul + btb_b200_gemv_bf16: the same bits). */

@@ -4,7 +4,7 @@
 # goes to oracle/_ref/ (git-ignored) and is loaded by the GPU tests as the bit-level oracle and as the same-box
 # speed baseline. No reference source is copied.
 set -e
-REF="${1:-/root/reference}"
+REF="${1:-${BTB_REFERENCE:-$(cd "$(dirname "$0")/../.." && pwd)/reference}}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 SRC="$REF/native/cuda/btb_kernels.cu"
 [ -f "$SRC" ] || { echo "no reference checkout at $REF: keeping what is built" >&2; exit 0; }

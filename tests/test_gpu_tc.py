@@ -127,3 +127,55 @@ def test_launcher_serves_the_reference_mma_matvec():
                         y2.data_ptr(), R, C_, M)  # fmt: skip
     torch.cuda.synchronize()
     assert float((y[:M].float() - y2[:M].float()).abs().max()) <= 2.0**-7 * float(ref.abs().max())
+
+
+# ---- the prefill GEMM: the same kernel over tiles of up to 256 x rows ------------------------------------------------
+
+
+def _gemm(w, x):
+    T, (R, C_) = x.shape[0], w.shape
+    y = torch.full((T, R), 7.0, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_gemm_tc_bf16", ptr(w), ptr(x), ptr(y), T, R, C_, capi.stream_ptr())
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    return y
+
+
+@pytest.mark.parametrize("R,C_", [(300, 2560), (2560, 4096), (6144, 2560), (129, 72), (2560, 9728)])
+@pytest.mark.parametrize("T", [1, 40, 128, 200, 300, 700])
+def test_prefill_gemm_rows_are_the_matvecs_rows(R, C_, T):
+    """row t of a chunk of any size carries the bits the tensor-core matvec gives that row in a pass of its own: one
+    accumulation over all of k in k order per output, whatever tile the row falls in"""
+    g = torch.Generator(device=DEV).manual_seed(R + C_ + T)
+    w = (torch.randn(R, C_, generator=g, device=DEV) * 0.05).bfloat16()
+    x = torch.randn(T, C_, generator=g, device=DEV).bfloat16()
+    y = _gemm(w, x)
+    ref = x.double() @ w.double().t()
+    bound = ref.abs() * 2.0**-8 + (x.double().abs() @ w.double().abs().t()) * (C_ * 2.0**-24) + 1e-30
+    assert bool(((y.double() - ref).abs() <= bound).all())
+    for a in sorted({0, max(0, T - 32), (T // 2) & ~31}):
+        rows = x[a : a + 32].contiguous()
+        assert torch.equal(_run(w, rows).view(torch.int16), y[a : a + rows.shape[0]].view(torch.int16)), a
+
+
+def test_prefill_on_the_tensor_cores_leaves_the_chain_passes_cache():
+    """`CardEngine.prefill_gemm` (GEMMs over chunks of 100 rows, the attention 32 rows at a time) writes the cache rows
+    that 32-row tensor-core passes write, bit for bit, and its last row's logits agree with theirs to rounding"""
+    from btb_b200 import engine as E
+
+    cfg = E.DenseConfig("pf", hidden=256, layers=3, q_heads=8, kv_heads=2, head_dim=128, inter=512, vocab=1000)
+    mw = E.synth_weights(cfg, seed=2, on_cpu=True, layer_std=0.1)
+    a, b = E.CardEngine(mw, cap=1024), E.CardEngine(mw, cap=1024)
+    a.wide_tc = True
+    prompt = torch.randint(0, cfg.vocab, (333,), generator=torch.Generator().manual_seed(5))
+    la = a.prefill(prompt)
+    lb = b.prefill_gemm(prompt, chunk=100)
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    assert int(a.n0[0]) == int(b.n0[0]) == 333
+    assert torch.equal(a.K[:, :333].view(torch.int16), b.K[:, :333].view(torch.int16))
+    assert torch.equal(a.V[:, :333].view(torch.int16), b.V[:, :333].view(torch.int16))
+    assert float((la.float() - lb.float()).abs().max()) <= 2.0**-5 * float(la.float().abs().max())
+    # decode goes on from either cache alike
+    ta, tb = a.step(int(la.float().argmax())), b.step(int(la.float().argmax()))
+    assert ta == tb
