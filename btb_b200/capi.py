@@ -44,6 +44,8 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_gemv_tc_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
     "btb_b200_gemv_tc_workspace_bytes": (_SZ, [_I, _I]),
     "btb_b200_gemm_tc_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "btb_b200_gemv_tc_glu_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+    "btb_b200_gemv_tc_glu_workspace_bytes": (_SZ, [_I, _I]),
     "btb_b200_gemv_silu_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_p12": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_fp8": (_I, [_P, _P, _I, _I, _P, _P, _I, _I, _I, _P]),
@@ -154,6 +156,8 @@ SIGNATURES.update({
     "btb_b200_xchg_unpack": (_I, [_P, _P, _I, _I, _RP, _P]),
     "btb_b200_xchg_pick": (_I, [_P, _I, _I, _I, _P, _I, _I, C.POINTER(C.c_void_p), _P, _P, _P, _I, _P]),
     "btb_b200_xchg_tick": (_I, [_P, _P]),
+    "btb_b200_moe_gemv_x": (_I, [_I, _P, _P, _LL, _LL, _I, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _SP, _P]),
+    "btb_b200_moe_combine_x": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _RP, _P]),
 })  # fmt: skip
 
 _lib: C.CDLL | None = None

@@ -24,6 +24,7 @@ struct B2Tuning {
     int ms_seg, ms_warps;  // the expert kernel's columns a stage and warps a CTA (0: its own choice)
     int tc_stages, tc_ctas;  // the tensor-core matvec's ring depth and CTAs an SM its K split aims at (0: 4 and 2)
     int balance;      // pick the GEMV grid and warps a CTA so that the rows divide evenly over the warps
+    int x_direct;     // a one-row plain GEMV reads x where it lies (L1/L2) instead of staging it in shared memory first
     int l2_warm_kb;   // the step's attention launch pulls at most this much of the next kernels' weights into L2 (0: off)
     int l2_warm_ctas; // blocks that do it (0: every SM the attention's own blocks leave idle)
 };

@@ -20,6 +20,7 @@ B2Tuning& b2_tuning() {
         env_int("BTB_B200_MS_WARPS", 0),           env_int("BTB_B200_TC_STAGES", 0),
         env_int("BTB_B200_TC_CTAS", 0),
         env_int("BTB_B200_BALANCE", 1),
+        env_int("BTB_B200_X_DIRECT", 1),
         env_int("BTB_B200_L2_WARM_KB", 0),         env_int("BTB_B200_L2_WARM_CTAS", 0),
     };
     return t;
@@ -54,6 +55,7 @@ extern "C" int btb_b200_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "balance")) t.balance = value != 0;
     else if (!strcmp(key, "solo")) t.solo = value != 0;
     else if (!strcmp(key, "moe_stream")) t.moe_stream = value != 0;
+    else if (!strcmp(key, "x_direct")) t.x_direct = value != 0;
     else if (!strcmp(key, "l2_warm_kb")) t.l2_warm_kb = value < 0 ? 0 : value;
     else if (!strcmp(key, "l2_warm_ctas")) t.l2_warm_ctas = value < 0 ? 0 : value;
     else return B2_ERR_DOMAIN;

@@ -426,7 +426,7 @@ static int gemv_bf16_impl(const void* w, const void* x, void* y, int T, int M, i
     a.R = R, a.C = C, a.T = T;
     if (T < 1 || T > M) return B2_ERR_DOMAIN;
     if ((rc = take_exchange(recv, send, a)) != B2_OK) return rc;
-    Plan p = make_plan<F_BF16>(M, R, C, M <= 8);
+    Plan p = make_plan<F_BF16>(M, R, C, M <= 8 && !(M == 1 && b2_tuning().x_direct && a.recv.pass == nullptr));
     // an exchanged x is decoded on its way into shared memory: a pass too wide to stage x takes btb_b200_xchg_unpack first
     if (a.recv.pass != nullptr && !p.xs) return B2_ERR_DOMAIN;
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;

@@ -53,6 +53,14 @@ __device__ __forceinline__ void fp8x2_held(uint32_t two, float scale, float& a, 
 // the activation of the SwiGLU fold, native/cuda/btb_kernels.cu:159 of the reference: silu in f32 as torch computes it
 __device__ __forceinline__ float act_silu(float g) { return g / (1.f + expf(-g)); }
 
+// the same, left as the packed bf16 pair (a in the low half): what the mixed-precision fma multiplies with
+__device__ __forceinline__ uint32_t fp8x2_held_pair(uint32_t two, float scale) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(two & 0xffffu), __NV_E4M3);
+    const __nv_bfloat162 p = __floats2bfloat162_rn(__fmul_rn(__half2float(__ushort_as_half(h.x)), scale),
+                                                   __fmul_rn(__half2float(__ushort_as_half(h.y)), scale));
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+
 // ---- pack12: eight weights of a chunk as four bf16 pairs ---------------------------------------------------------
 // lo: the chunk's 8 low bytes (two words), codes: its 8 nibbles (one word, element e in nibble e). The table's 16
 // high bytes sit in four registers; a code picks its byte with two byte-permutes (codes 0-7, 8-15) and a third that
@@ -240,6 +248,17 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
     }
 }
 
+// Two weights times two activations into the chain: acc = fma(w_lo, x_lo, acc), then acc = fma(w_hi, x_hi, acc), the
+// operands bf16 as they lie in their packed words and the sum f32 - sm_100's mixed-precision fma. A bf16 product is
+// exact in f32, so each step is fmaf(float(w), float(x), acc) to the bit, without the two widening instructions.
+__device__ __forceinline__ float fma2_bf16(uint32_t w, uint32_t x, float acc) {
+    asm("{\n.reg .b16 wl, wh, xl, xh;\nmov.b32 {wl, wh}, %1;\nmov.b32 {xl, xh}, %2;\nfma.rn.f32.bf16 %0, wl, xl, %0;\n"
+        "fma.rn.f32.bf16 %0, wh, xh, %0;\n}\n"
+        : "+f"(acc)
+        : "r"(w), "r"(x));
+    return acc;
+}
+
 // ---- one ring stage into the accumulators --------------------------------------------------------------------------
 // stg: the stage (bf16: the segment's weights; pack12: its low bytes, then at `seg` its codes); nch chunks of 8, the
 // first global column c0 of `row`. Lane l takes local chunks l, l + 32, .. - segments are multiples of 256 columns,
@@ -250,16 +269,15 @@ __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* st
                                               int C, const bf16* xv, const WidenCtx& W, int lane) {
 #pragma unroll 4
     for (int lc = lane; lc < nch; lc += 32) {
-        float wf[8];
+        uint32_t wp[4];
         if (FMT == F_FP8) {
             const uint2 wb = *reinterpret_cast<const uint2*>(stg + lc * 8);
             const float sc = __ldg(W.srow + (c0 + lc * 8) / W.bn);
-            fp8x2_held(wb.x, sc, wf[0], wf[1]);
-            fp8x2_held(wb.x >> 16, sc, wf[2], wf[3]);
-            fp8x2_held(wb.y, sc, wf[4], wf[5]);
-            fp8x2_held(wb.y >> 16, sc, wf[6], wf[7]);
+            wp[0] = fp8x2_held_pair(wb.x, sc);
+            wp[1] = fp8x2_held_pair(wb.x >> 16, sc);
+            wp[2] = fp8x2_held_pair(wb.y, sc);
+            wp[3] = fp8x2_held_pair(wb.y >> 16, sc);
         } else {
-            uint32_t wp[4];
             if (FMT == F_BF16) {
                 const uint4 wv = *reinterpret_cast<const uint4*>(stg + lc * 16);
                 wp[0] = wv.x, wp[1] = wv.y, wp[2] = wv.z, wp[3] = wv.w;
@@ -281,26 +299,18 @@ __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* st
                     }
                 }
             }
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                wf[2 * e] = bf_lo(wp[e]);
-                wf[2 * e + 1] = bf_hi(wp[e]);
-            }
         }
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             uint4 x4;
             if (XS) x4 = *reinterpret_cast<const uint4*>(xv + (size_t)m * C + c0 + lc * 8);
             else x4 = __ldg(reinterpret_cast<const uint4*>(xv + (size_t)m * C + c0 + lc * 8));  // standalone wide passes
+            // the weights as packed bf16 pairs: the chain's eight steps without a widening
             float a = acc[m];
-            a = fmaf(wf[0], bf_lo(x4.x), a);
-            a = fmaf(wf[1], bf_hi(x4.x), a);
-            a = fmaf(wf[2], bf_lo(x4.y), a);
-            a = fmaf(wf[3], bf_hi(x4.y), a);
-            a = fmaf(wf[4], bf_lo(x4.z), a);
-            a = fmaf(wf[5], bf_hi(x4.z), a);
-            a = fmaf(wf[6], bf_lo(x4.w), a);
-            a = fmaf(wf[7], bf_hi(x4.w), a);
+            a = fma2_bf16(wp[0], x4.x, a);
+            a = fma2_bf16(wp[1], x4.y, a);
+            a = fma2_bf16(wp[2], x4.z, a);
+            a = fma2_bf16(wp[3], x4.w, a);
             acc[m] = a;
         }
     }

@@ -63,6 +63,9 @@ struct TcArgs {
     bf16* y;      // [M, R]
     float* part;  // [splits, 32, R] partial sums when splits > 1
     int R, C, M, kblocks_per_split, splits, stages;
+    // the gate/up form: the matrix is [2 * glu_I, C] (gate rows, then up rows); a tile takes 64 gate rows and, glu_I rows
+    // on, their 64 up rows, and writes m [M, glu_I] = bf16(bf16(silu(bf16 g)) * bf16 u). 0: the plain matvec.
+    int glu_I;
 };
 
 // BN: the x rows a CTA's tile holds. GEMM false: the matvec - one accumulator of 32 columns, gridDim.y cuts K into
@@ -70,10 +73,14 @@ struct TcArgs {
 // rows BN at a time and the CTA takes its tile's whole K, but in the matvec's own ranges: range s accumulates into its
 // own BN columns of tensor memory and the epilogue adds the ranges in order, so an output element is the matvec's sum
 // to the bit whatever the chunk's size and wherever in the chunk the row stands.
+__device__ __forceinline__ float tc_silu(float g) { return g / (1.f + expf(-g)); }
+
 template <int BN, bool GEMM>
 __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_constant__ CUtensorMap tmW,
                                                              const __grid_constant__ CUtensorMap tmX, const TcArgs A) {
     constexpr int ST_BYTES = TcTile<BN>::ST_BYTES;
+    __shared__ float s_up[GEMM ? 1 : 64][GEMM ? 1 : 33];  // the gate/up form: a tile's up outputs on their way to the gate rows' threads
+    const bool glu = !GEMM && A.glu_I > 0;
     const int ranges = GEMM ? A.splits : 1;  // accumulators in tensor memory
     const uint32_t tmem_cols = GEMM ? 512u : 32u;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -83,7 +90,7 @@ __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_consta
     __shared__ int s_fail;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
-    const int row0 = blockIdx.x * TC_BM;
+    const int row0 = glu ? blockIdx.x * 64 : blockIdx.x * TC_BM;  // (the gate/up form: the tile's first gate row)
     const int total_kb = (A.C + TC_BK - 1) / TC_BK;
     const int kb0 = GEMM ? 0 : blockIdx.y * A.kblocks_per_split;
     const int nkb = GEMM ? total_kb : max(0, min(A.kblocks_per_split, total_kb - kb0));
@@ -120,6 +127,10 @@ __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_consta
             }
             const uint32_t bar = smem_u32(&full[s]);
             mbar_expect_tx(bar, ST_BYTES);
+            if (glu) {  // two boxes of 64 rows: the gate rows into the tile's upper half, their up rows into its lower half
+                tma_load_2d(smem_u32(tiles + s * ST_BYTES), &tmW, (kb0 + kb) * TC_BK, row0, bar);
+                tma_load_2d(smem_u32(tiles + s * ST_BYTES + A_BYTES / 2), &tmW, (kb0 + kb) * TC_BK, A.glu_I + row0, bar);
+            } else
             tma_load_2d(smem_u32(tiles + s * ST_BYTES), &tmW, (kb0 + kb) * TC_BK, row0, bar);
             tma_load_2d(smem_u32(tiles + s * ST_BYTES + A_BYTES), &tmX, (kb0 + kb) * TC_BK, n0, bar);
         }
@@ -175,7 +186,30 @@ __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_consta
 #pragma unroll
             for (int n = 0; n < 32; ++n) tot[n] += __uint_as_float(r[n]);  // the ranges in order, from zero
             }
-            if (row < A.R) {
+            if (!GEMM && glu) {
+                // thread l < 64 holds gate row row0 + l, thread 64 + l its up row
+                const int l = warp * 32 + lane;
+                if (A.splits == 1) {
+                    if (l >= 64) {
+#pragma unroll
+                        for (int n = 0; n < 32; ++n) s_up[GEMM ? 0 : l - 64][GEMM ? 0 : n] = tot[n];
+                    }
+                    __syncthreads();
+                    if (l < 64 && row0 + l < A.glu_I) {
+#pragma unroll
+                        for (int n = 0; n < 32; ++n)
+                            if (n < A.M) {
+                                const float g = bfround(tot[n]), u = bfround(s_up[GEMM ? 0 : l][GEMM ? 0 : n]);
+                                A.y[(size_t)n * A.glu_I + row0 + l] = f2bf(bfround(tc_silu(g)) * u);
+                            }
+                    }
+                } else {  // partial sums by tile position: [split][n][tile * 128 + l]
+                    const size_t Rv = (size_t)gridDim.x * TC_BM;
+#pragma unroll
+                    for (int n = 0; n < 32; ++n)
+                        if (n < A.M) A.part[((size_t)blockIdx.y * 32 + n) * Rv + (size_t)blockIdx.x * TC_BM + l] = __uint_as_float(r[n]);
+                }
+            } else if (row < A.R) {
                 if (GEMM || A.splits == 1) {
 #pragma unroll
                     for (int n = 0; n < 32; ++n)
@@ -199,12 +233,25 @@ struct TcReduceArgs {
     const float* part;
     bf16* y;
     int R, M, splits;
+    int glu_I, Rv;  // the gate/up form: y is m [M, glu_I]; the partial sums lie by tile position, Rv a range's row extent
 };
 // the K ranges' partial sums added in range order (the same sum every launch), rounded to bf16 once
 __global__ void __launch_bounds__(256) gemv_tc_reduce(const TcReduceArgs A) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x * 256 + threadIdx.x;
+    if (A.glu_I > 0) {
+        if (i >= A.M * A.glu_I) return;
+        const int n = i / A.glu_I, c = i - n * A.glu_I;
+        const size_t at = (size_t)(c >> 6) * TC_BM + (c & 63);  // the gate row's place in its tile; its up row 64 on
+        float g = 0.f, u = 0.f;
+        for (int k = 0; k < A.splits; ++k) {
+            g += __ldcg(A.part + ((size_t)k * 32 + n) * A.Rv + at);
+            u += __ldcg(A.part + ((size_t)k * 32 + n) * A.Rv + at + 64);
+        }
+        A.y[i] = f2bf(bfround(tc_silu(bfround(g))) * bfround(u));
+        return;
+    }
     if (i >= A.M * A.R) return;
     const int n = i / A.R, r = i - n * A.R;
     float s = 0.f;
@@ -310,6 +357,46 @@ extern "C" int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int 
     if (splits > 1) {
         TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(y), R, M, splits};
         return b2_launch((const void*)gemv_tc_reduce, dim3((M * R + 255) / 256), dim3(256), 0, s, ra);
+    }
+    return B2_OK;
+}
+
+// ---- the gate/up form ---------------------------------------------------------------------------------------------------
+// m [M, I] = bf16(bf16(silu(g)) * u) with g, u the tensor-core matvec's bf16 outputs at rows i and I + i of the merged
+// [2I, C] gate/up block: btb_b200_gemv_tc_bf16 followed by btb_b200_silu_mul, their bits, without the [M, 2I] buffer
+// between them. It stands in for btb's btb_gemv_mma_glu_silu (native/cuda/btb_gemv_mma.cuh:216-315). workspace:
+// btb_b200_gemv_tc_glu_workspace_bytes(I, C) bytes (0 where the matrix has tiles enough for the card).
+static int glu_splits(int I, int C, int* kps) {
+    const int tiles = (I + 63) / 64, kb = (C + TC_BK - 1) / TC_BK;
+    const int per_sm = b2_tuning().tc_ctas > 0 ? b2_tuning().tc_ctas : 2;
+    const int aim = max(1, min(min(max(1, (per_sm * b2_sm_count()) / tiles), 16), kb / 4));
+    const int per = (kb + aim - 1) / aim;
+    if (kps != nullptr) *kps = per;
+    return (kb + per - 1) / per;
+}
+extern "C" size_t btb_b200_gemv_tc_glu_workspace_bytes(int I, int C) {
+    if (I <= 0 || C <= 0) return 0;
+    const int s = glu_splits(I, C, nullptr);
+    return s > 1 ? (size_t)s * 32 * ((I + 63) / 64) * TC_BM * sizeof(float) : 0;
+}
+extern "C" int btb_b200_gemv_tc_glu_bf16(const void* w, const void* x, void* m, int M, int I, int C, void* workspace,
+                                         void* stream) {
+    if (!w || !x || !m) return B2_ERR_NULL;
+    if (M < 1 || M > 32 || I <= 0 || C <= 0 || (C & 7)) return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return B2_ERR_DOMAIN;
+    int kps = 0;
+    const int splits = glu_splits(I, C, &kps);
+    if (splits > 1 && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15))) return B2_ERR_NULL;
+    CUtensorMap tw, tx;
+    if (make_map(&tw, w, (uint64_t)2 * I, (uint64_t)C, 64) || make_map(&tx, x, (uint64_t)M, (uint64_t)C, TC_BN)) return B2_ERR_CUDA;
+    const int stages = b2_tuning().tc_stages > 0 ? min(TC_STAGES_MAX, b2_tuning().tc_stages) : 4;
+    const int tiles = (I + 63) / 64;
+    TcArgs a{static_cast<bf16*>(m), static_cast<float*>(workspace), 2 * I, C, M, kps, splits, stages, I};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (const int rc = launch_tc<TC_BN, false>(tw, tx, a, dim3(tiles, splits), stages, s)) return rc;
+    if (splits > 1) {
+        TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(m), 2 * I, M, splits, I, tiles * TC_BM};
+        return b2_launch((const void*)gemv_tc_reduce, dim3((M * I + 255) / 256), dim3(256), 0, s, ra);
     }
     return B2_OK;
 }

@@ -15,6 +15,8 @@
 
 #include "btb_b200_internal.h"
 #include "moe_widen.cuh"
+#include "tp.cuh"
+#include "../../include/btb_b200.h"
 
 B2_DEFINE_STATUS(moe)
 
@@ -24,7 +26,7 @@ bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_st
                       int R, int C, int sr, int sc);
 int b2_moe_stream_launch(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
                          const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C, int ep_rank,
-                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s);
+                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s, const B2Send* send = nullptr);
 
 namespace {
 
@@ -339,6 +341,7 @@ struct CombineArgs {
     const bf16* bias;  // [E, H] or null
     bf16* y;          // [T, H]
     int T, k, H;
+    B2Recv recv;      // pass set: dn is this rank's copy of the exchanged products, words [T, k, H] carrying bf16(product)
 };
 __global__ void __launch_bounds__(256) moe_combine(const CombineArgs A) {
     pdl_launch_dependents();
@@ -364,11 +367,14 @@ __global__ void __launch_bounds__(256) moe_combine(const CombineArgs A) {
     __syncthreads();
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= A.H) return;
+    const bool marked = A.recv.pass != nullptr;
+    const uint32_t mark = marked ? b2_hop_mark(A.recv.pass, A.recv.per_pass, A.recv.base) : 0u;
     float fin = 0.f;
     for (int a = 0; a < k; ++a) {
         const int s = order[a];
         const size_t q = (size_t)t * k + s;
-        float o = bfround(__ldcg(A.dn + q * A.H + c));
+        float o = marked ? b2_take1(reinterpret_cast<const uint32_t*>(A.dn) + q * A.H + c, mark)
+                         : bfround(__ldcg(A.dn + q * A.H + c));
         if (A.bias != nullptr) o = bfround(o + bf2f(A.bias[(size_t)__ldcg(A.idx + q) * A.H + c]));
         const unsigned short wb = __ldcg(reinterpret_cast<const unsigned short*>(A.w) + q);
         o = bfround(o * __uint_as_float((uint32_t)wb << 16));
@@ -546,6 +552,31 @@ extern "C" int btb_b200_moe_gemv(int fmt, const void* w, const void* scales, lon
     return lane16_launch(fmt, a, n_tasks, static_cast<cudaStream_t>(stream));
 }
 
+// btb_b200_moe_gemv with the experts cut over ranks and the exchange folded in: an expert this rank holds
+// (expert e on rank e % ep_size) writes bf16(output) as marked words into every rank's copy of the [n_tasks, R] vector;
+// the other picks' rows are their owners'. Shapes the streaming kernel takes only.
+extern "C" int btb_b200_moe_gemv_x(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride,
+                                   int sr, int sc, const void* idx, int n_tasks, int E, const void* x, int x_div, int R,
+                                   int C, int ep_rank, int ep_size, const btb_b200_send* send, void* stream) {
+    if (!w || !x || !send || (fmt != L_BF16 && !scales)) return B2_ERR_NULL;
+    if (n_tasks <= 0 || n_tasks > 65535 || R <= 0 || C <= 0 || x_div <= 0 || E <= 0 || ep_size < 1 || ep_rank < 0 ||
+        ep_rank >= ep_size)
+        return B2_ERR_DOMAIN;
+    if (fmt == L_FP8 && (sr <= 0 || sc <= 0 || R % sr || C % sc)) return B2_ERR_DOMAIN;
+    if (send->n < 1 || send->n > B2_MAX_RANKS || send->stride < R || send->offset != 0) return B2_ERR_DOMAIN;
+    if (send->pass == nullptr) return B2_ERR_NULL;
+    B2Send sd{};
+    sd.n = send->n, sd.stride = send->stride, sd.offset = 0;
+    sd.pass = static_cast<const unsigned*>(send->pass), sd.per_pass = send->per_pass, sd.base = send->base;
+    for (int p = 0; p < send->n; ++p) {
+        if (send->out[p] == nullptr) return B2_ERR_NULL;
+        sd.out[p] = static_cast<uint32_t*>(send->out[p]);
+    }
+    if (!b2_moe_stream_ok(fmt, w, scales, w_stride, s_stride, x, R, C, sr, sc)) return B2_ERR_DOMAIN;
+    return b2_moe_stream_launch(fmt, w, scales, w_stride, s_stride, sr, sc, idx, n_tasks, E, x, x_div, nullptr, R, C, ep_rank,
+                                ep_size, -1, 0.f, 0.f, static_cast<cudaStream_t>(stream), &sd);
+}
+
 // the picked experts' DOWN matvecs with the gated activation made on the way in: x row of task i = act(gu row i).
 // btb_b200_moe_act followed by btb_b200_moe_gemv (x_div 1), one launch and no [n, I] buffer. No bias.
 extern "C" int btb_b200_moe_gemv_act(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride,
@@ -573,13 +604,26 @@ extern "C" int btb_b200_moe_act(const void* gu, void* h, const void* bias, const
     return b2_launch((const void*)moe_act, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a, 4);
 }
 
-extern "C" int btb_b200_moe_combine(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T,
-                                    int k, int H, void* stream) {
+static int combine_impl(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T, int k, int H,
+                        const btb_b200_recv* recv, void* stream) {
     if (!dn || !idx || !w || !y) return B2_ERR_NULL;
     if (T <= 0 || k <= 0 || k > ROUTE_MAX_K || H <= 0) return B2_ERR_DOMAIN;
     CombineArgs a{static_cast<const float*>(dn), static_cast<const int*>(idx), static_cast<const bf16*>(w),
-                  static_cast<const bf16*>(bias), static_cast<bf16*>(y), T, k, H};
+                  static_cast<const bf16*>(bias), static_cast<bf16*>(y), T, k, H, B2Recv{nullptr, 0u, 0u}};
+    if (recv != nullptr && recv->pass != nullptr) a.recv = B2Recv{static_cast<const unsigned*>(recv->pass), recv->per_pass, recv->base};
     return b2_launch((const void*)moe_combine, dim3((H + 255) / 256, T), dim3(256), 0, static_cast<cudaStream_t>(stream), a, 4);
+}
+
+extern "C" int btb_b200_moe_combine(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T,
+                                    int k, int H, void* stream) {
+    return combine_impl(dn, idx, w, bias, y, T, k, H, nullptr, stream);
+}
+
+// experts cut over ranks: dn is this rank's copy of the exchanged products (marked words [T, k, H], each bf16(product))
+extern "C" int btb_b200_moe_combine_x(const void* dn_words, const void* idx, const void* w, const void* bias, void* y, int T,
+                                      int k, int H, const btb_b200_recv* recv, void* stream) {
+    if (recv == nullptr || recv->pass == nullptr) return B2_ERR_NULL;
+    return combine_impl(dn_words, idx, w, bias, y, T, k, H, recv, stream);
 }
 
 extern "C" int btb_b200_widen_f32(const void* x, void* y, int n, void* stream) {

@@ -14,6 +14,7 @@
 
 #include "btb_b200_internal.h"
 #include "moe_widen.cuh"
+#include "tp.cuh"
 
 B2_DEFINE_STATUS(moes)
 
@@ -40,6 +41,10 @@ struct MSArgs {
     // over interleaved lanes - every bf16 rounding of the host's torch ops kept
     int act_kind;
     float alpha, limit;
+    // experts cut over ranks (tp.cuh): with send.n > 0 a finished output of an expert this rank holds goes to every
+    // rank's copy of the [n_tasks, R] vector as a marked word carrying bf16(sum) - the rounding the ordered sum applies
+    // to a product first thing - and another rank's experts' rows are left to their owner
+    B2Send send;
 };
 
 __device__ __forceinline__ float moe_act_value(const float* gu, int c, int I, int kind, float alpha, float limit) {
@@ -118,6 +123,7 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
     const int gc = base + ((int)blockIdx.x < rem ? 1 : 0);
     const int my_groups = gc > warp ? (gc - warp + nw - 1) / nw : 0;
     if (!mine) {  // another rank's expert (or a refused pick): zeros, so that the ranks' sum is the whole
+        if (A.send.n != 0) return;  // (under the exchange the owner writes the row into every rank's copy)
         for (int g = g0 + warp; g < g0 + gc; g += nw) {
             const int r = g * RB + ri;
             if (r < R && q == 0) A.y[(size_t)task * R + r] = 0.f;
@@ -305,7 +311,16 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
             float s = CPT == 4 ? (acc[0] + acc[1 % CPT]) + (acc[2 % CPT] + acc[3 % CPT]) : CPT == 2 ? acc[0] + acc[1 % CPT] : acc[0];
 #pragma unroll
             for (int o = 1; o < TPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (live && q == 0) A.y[(size_t)task * R + r] = s;
+            if (live && q == 0) {
+                if (A.send.n == 0) {
+                    A.y[(size_t)task * R + r] = s;
+                } else {
+                    const uint32_t word = b2_word(f2bf(s), b2_hop_mark(A.send.pass, A.send.per_pass, A.send.base));
+                    const size_t at = (size_t)task * A.send.stride + A.send.offset + r;
+#pragma unroll 1
+                    for (int p = 0; p < A.send.n; ++p) A.send.out[p][at] = word;
+                }
+            }
 #pragma unroll
             for (int u = 0; u < CPT; ++u) acc[u] = 0.f;
             c_seg = 0;
@@ -403,10 +418,11 @@ bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_st
 
 int b2_moe_stream_launch(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
                          const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C, int ep_rank,
-                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s) {
+                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s, const B2Send* send) {
     MSArgs a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), w_stride, s_stride,
              static_cast<const int*>(idx), static_cast<const float*>(x), x_div, static_cast<float*>(y), R, C,
-             sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size, 0, 0, act_kind, alpha, limit};
+             sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size, 0, 0, act_kind, alpha, limit, B2Send{}};
+    if (send != nullptr) a.send = *send;
     switch (fmt) {
         case S_BF16: return launch_stream<S_BF16>(a, n_tasks, s);
         case S_MX4: return launch_stream<S_MX4>(a, n_tasks, s);

@@ -77,6 +77,22 @@ __device__ __forceinline__ uint2 b2_take4(const uint32_t* words, uint32_t mark) 
     }
     return make_uint2((w.x & 0xffffu) | (w.y << 16), (w.z & 0xffffu) | (w.w << 16));
 }
+// one element
+__device__ __forceinline__ float b2_take1(const uint32_t* word, uint32_t mark) {
+    uint32_t w = *reinterpret_cast<const volatile uint32_t*>(word);
+    if (((w ^ mark) & 0xffff0000u) != 0u && *(volatile int*)&g_b2_status == 0) {
+        const unsigned long long t0 = globaltimer_ns();
+        for (;;) {
+            w = *reinterpret_cast<const volatile uint32_t*>(word);
+            if (((w ^ mark) & 0xffff0000u) == 0u) break;
+            if (globaltimer_ns() - t0 > B2_XCHG_TIMEOUT_NS || *(volatile int*)&g_b2_status != 0) {
+                b2_fail(B2_ERR_TIMEOUT);
+                break;
+            }
+        }
+    }
+    return __uint_as_float(w << 16);
+}
 // eight consecutive elements (a 16-byte vector of bf16, as the kernels read activations)
 __device__ __forceinline__ uint4 b2_take8(const uint32_t* words, uint32_t mark) {
     const uint2 a = b2_take4(words, mark), b = b2_take4(words + 4, mark);

@@ -46,6 +46,8 @@ class B200Launcher:
         (r"btb_gemv_bf16_m(\d+)$", "_gemv_bf16"),
         (r"btb_gemv_silu_bf16_m(\d+)$", "_gemv_silu"),
         (r"btb_gemv_mma_bf16$", "_gemv_mma"),
+        (r"btb_gemv_mma8_bf16$", "_gemv_mma"),  # the reference's 8-rows-a-warp launch shape of the same sums
+        (r"btb_gemv_mma_glu_silu$", "_gemv_mma_glu"),
         (r"btb_add_rmsnorm$", "_add_rmsnorm"),
         (r"btb_silu_mul$", "_silu_mul"),
         (r"btb_norm_rope_kv_d(\d+)$", "_norm_rope_kv"),
@@ -93,15 +95,25 @@ class B200Launcher:
 
     def _gemv_mma(self, name, m, grid, a, s):
         # btb_gemv_mma_bf16(w [R, C], x [32, C], y [32, R], R, C, M): the tensor-core matvec, M live rows
-        import torch
-
         w, x, y, R, Cc, M = a
         R, Cc = int(_v(R)), int(_v(Cc))
-        need = int(self.lib.btb_b200_gemv_tc_workspace_bytes(R, Cc))
+        ws = self._workspace(int(self.lib.btb_b200_gemv_tc_workspace_bytes(R, Cc)))
+        capi.call("btb_b200_gemv_tc_bf16", _p(w), _p(x), _p(y), int(_v(M)), R, Cc, ws, s)
+
+    def _gemv_mma_glu(self, name, m, grid, a, s):
+        # btb_gemv_mma_glu_silu(w [2I, C], x [32, C], m [32, I], I, C, M): gate/up and the activation in one launch
+        w, x, mm, I, Cc, M = a
+        I, Cc = int(_v(I)), int(_v(Cc))
+        ws = self._workspace(int(self.lib.btb_b200_gemv_tc_glu_workspace_bytes(I, Cc)))
+        capi.call("btb_b200_gemv_tc_glu_bf16", _p(w), _p(x), _p(mm), int(_v(M)), I, Cc, ws, s)
+
+    def _workspace(self, need: int) -> int:
+        """the tensor-core matvecs' partial sums (matrices of few rows): one buffer, grown as asked"""
+        import torch
+
         if need and (self._tc_ws is None or self._tc_ws.numel() * 4 < need):
             self._tc_ws = torch.zeros(need // 4, dtype=torch.float32, device="cuda")
-        ws = 0 if not need else int(self._tc_ws.data_ptr())
-        capi.call("btb_b200_gemv_tc_bf16", _p(w), _p(x), _p(y), int(_v(M)), R, Cc, ws, s)
+        return 0 if not need else int(self._tc_ws.data_ptr())
 
     def _add_rmsnorm(self, name, m, grid, a, s):
         h, y, w, eps, x, H, cen = a
@@ -278,3 +290,11 @@ def btb_gemv_lane16_f32(launcher, M, grid, block, w, x, y, R, C_, *, stream=None
 def btb_gemv_lane16_mx4_f32(launcher, M, grid, block, blocks, scales, x, y, R, C_, *, stream=None, shared=0):
     launcher.launch(f"btb_gemv_lane16_mx4_f32_m{M}", grid, block,
                     [_P(blocks), _P(scales), _P(x), _P(y), _I(R), _I(C_)], stream, shared)  # fmt: skip
+
+
+def btb_gemv_mma8_bf16(launcher, grid, block, w, x, y, R, C_, M, *, stream=None, shared=0):
+    launcher.launch("btb_gemv_mma8_bf16", grid, block, [_P(w), _P(x), _P(y), _I(R), _I(C_), _I(M)], stream, shared)
+
+
+def btb_gemv_mma_glu_silu(launcher, grid, block, w, x, m, I, C_, M, *, stream=None, shared=0):
+    launcher.launch("btb_gemv_mma_glu_silu", grid, block, [_P(w), _P(x), _P(m), _I(I), _I(C_), _I(M)], stream, shared)

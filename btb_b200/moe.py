@@ -7,9 +7,12 @@ weights as stored (MXFP4 / FP8), the row dtype's gated activation between them, 
 expert id. btb runs those matvecs on the CPU with two bus hops a layer; here they run on the card, the picks never
 leaving it, with the same arithmetic (the 16-lane order of native/src/gemv.rs).
 
-Expert parallelism (one process a GPU): expert e lives on rank e % ep; a rank multiplies only its own picks and
-writes zeros for the others; one all-reduce of the [T, k, H] f32 products a layer puts every product on every rank
-(x + 0 is exact), and every rank then runs the same ordered bf16 sum - bit-identical to one GPU.
+Expert parallelism (one process a GPU): expert e lives on rank e % ep; a rank multiplies only its own picks, and its
+down matvecs' epilogue stores each product - rounded to bf16, which is the first thing the ordered sum does to it -
+as a marked word into every rank's copy of the layer's [T, k, H] products (`btb_b200.exchange`, csrc/tp.cuh: plain peer
+stores, no collective call); every rank then runs the same ordered bf16 sum over its own copy, taking each word as it
+arrives - bit-identical to one GPU, and the whole step stays one captured graph. Attention, router and head are
+computed by every rank.
 """
 
 from __future__ import annotations
@@ -23,7 +26,8 @@ import torch
 
 from . import capi
 from .capi import ptr
-from .engine import CardEngine, DenseConfig, FP8Matrix, pad_rows
+from .engine import CARD_ROWS, CardEngine, DenseConfig, FP8Matrix, pad_rows
+from .exchange import PeerHeap
 
 FMT = {"bf16": 0, "mx4": 1, "fp8": 2}
 
@@ -175,15 +179,50 @@ def synth_moe_weights(cfg: MoEConfig, seed: int = 0, device: Any = "cuda", on_cp
 class MoEEngine(CardEngine):
     """the MoE model on one card (or one rank of an expert-parallel group)"""
 
-    def __init__(self, weights: MoEWeights, cap: int = 4096, device: Any = "cuda", group: Any = None):
+    def __init__(self, weights: MoEWeights, cap: int = 4096, device: Any = "cuda", group: Any = None,
+                 heap: PeerHeap | None = None):
         super().__init__(weights, cap=cap, step_kernel=False, device=device)  # type: ignore[arg-type]
         self.group = group
         self.ep_rank, self.ep_size = weights.ep_rank, weights.ep_size
+        self.heap: PeerHeap | None = None
+        if self.ep_size > 1:
+            # every rank's copy of a layer's products: words [M * k, H], three buffers taken in turn so that a rank
+            # writing layer i + 1's never meets a slower rank still reading layer i's (see `_edn_buffer`)
+            c = self.cfg
+            self.heap = heap if heap is not None else PeerHeap(self.heap_bytes(c), self.ep_rank, self.ep_size)
+            self.edn_off = {M: [self.heap.carve(M * c.top_k * c.hidden * 4) for _ in range(3)] for M in CARD_ROWS}
+            if heap is None:
+                self.heap.connect_processes(group)
+            self.passes = torch.zeros(len(CARD_ROWS), dtype=torch.int32, device=self.dev)
+            self._ep: dict[int, Any] = {}
         self.fuse_router = True  # the router's matvec and the picks in one cluster launch
         # the activation inside the down matvecs' launch, the picks' sum inside the next norm's: fewer launches, the
         # same bits, but measured slower than the separate kernels (one block a token sums the picks; every CTA of the
         # down matvecs repeats the activation) - off unless asked for
         self.fold = os.environ.get("BTB_B200_MOE_FOLD", "0") != "0"
+
+    @staticmethod
+    def heap_bytes(c: MoEConfig) -> int:
+        return sum(3 * (M * c.top_k * c.hidden * 4 + 256) for M in CARD_ROWS) + 4096
+
+    def _edn_buffer(self, i: int) -> int:
+        """which of the three buffers layer i's products take: consecutive layers differ, and so do a pass's last layer
+        and the next pass's first, so a buffer is rewritten only after every rank has read it (a rank sends layer i + 2's
+        products only after its own sum over layer i + 1's, which needed every rank's, each sent after that rank's sum
+        over layer i's)"""
+        L = self.cfg.layers
+        return 2 if (i == L - 1 and L % 2 == 1) else i % 2
+
+    def ep_descs(self, M: int) -> Any:
+        """width M's exchange descriptors: hop i + 1 of a pass carries layer i's products"""
+        if M not in self._ep:
+            c, hp = self.cfg, self.heap
+            pas = int(self.passes[CARD_ROWS.index(M) : CARD_ROWS.index(M) + 1].data_ptr())
+            sends = [hp.send_desc(self.edn_off[M][self._edn_buffer(i)], c.hidden, 0, pas, c.layers, i + 1) for i in range(c.layers)]
+            recvs = [capi.Recv(pas, c.layers, i + 1) for i in range(c.layers)]
+            local = [hp.local + self.edn_off[M][self._edn_buffer(i)] for i in range(c.layers)]
+            self._ep[M] = (sends, recvs, local, pas)
+        return self._ep[M]
 
     def bufs(self, M: int) -> dict[str, torch.Tensor]:
         g = super().bufs(M)
@@ -204,13 +243,19 @@ class MoEEngine(CardEngine):
                 ptr(idx), n_tasks, self.cfg.experts, ptr(x), x_div, ptr(y), st.R, st.C, self.ep_rank, self.ep_size, s)
 
     def body(self, T: int, tail: bool = True, stream_ptr: int | None = None) -> None:
+        for _ in self.ops(T, tail, stream_ptr):
+            pass
+
+    def ops(self, T: int, tail: bool = True, stream_ptr: int | None = None):
+        """the pass's launches; under expert parallelism it yields after each layer's products are sent, so that engines
+        standing in for the ranks on ONE GPU can take turns (every rank's products sent before any rank sums them)"""
         c = self.cfg
         M = pad_rows(T)
         g = self.bufs(M)
         s = capi.stream_ptr() if stream_ptr is None else stream_ptr
         H, Hq, Hk, D, I, E, k = c.hidden, c.q_heads, c.kv_heads, c.head_dim, c.inter, c.experts, c.top_k
         K_ = self._k
-        fold = self.fold
+        fold = self.fold and self.ep_size == 1
         pending = False  # the previous layer's picks are summed by the norm that reads them
         y_prev = None
 
@@ -247,13 +292,19 @@ class MoEEngine(CardEngine):
                 K_("btb_b200_moe_gemv_act", FMT[st.fmt], ptr(st.w), ptr(st.scales), st.w_stride, st.s_stride, st.sr, st.sc,
                    ptr(g["idx"]), T * k, E, ptr(g["egu"]), c.glu_kind, c.alpha, c.limit, ptr(g["edn"]), st.R, st.C,
                    self.ep_rank, self.ep_size, s)  # fmt: skip
+            elif self.ep_size > 1:
+                # this rank's picks: the products go, rounded and marked, into every rank's copy; the sum takes them there
+                sends, recvs, local, _ = self.ep_descs(M)
+                K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
+                K_("btb_b200_moe_gemv_x", FMT[st.fmt], ptr(st.w), ptr(st.scales), st.w_stride, st.s_stride, st.sr, st.sc,
+                   ptr(g["idx"]), T * k, E, ptr(g["eh"]), 1, st.R, st.C, self.ep_rank, self.ep_size, sends[i], s)  # fmt: skip
+                yield  # (engines standing in for the ranks on one GPU take turns here)
+                K_("btb_b200_moe_combine_x", local[i], ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, recvs[i], s)
+                y_prev = g["y"]
+                continue
             else:
                 K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
                 self._expert_gemv(L.dn, g["idx"], T * k, g["eh"], 1, g["edn"], s)
-            if self.ep_size > 1:
-                import torch.distributed as dist
-
-                dist.all_reduce(g["edn"][: T * k], group=self.group)
             if fold:
                 pending = True
             else:
@@ -264,6 +315,8 @@ class MoEEngine(CardEngine):
             self._matvec(self.w.embed, g["x"], g["logits"], M, c.vocab, H, s)
         elif pending:  # a pass without its head leaves the last layer's sum in y, as the unfolded pass does
             K_("btb_b200_moe_combine", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, s)
+        if self.ep_size > 1:  # the pass is over: its hops' sequence numbers move on
+            K_("btb_b200_xchg_tick", self.ep_descs(M)[3], s)
 
     def weight_bytes(self) -> int:
         return self.cfg.weight_bytes_per_token()

@@ -52,6 +52,12 @@ int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int 
  * partial sums of matrices with few rows. */
 int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* workspace, void* stream);
 size_t btb_b200_gemv_tc_workspace_bytes(int R, int C);
+/* btb_gemv_mma_glu_silu (native/cuda/btb_gemv_mma.cuh:216-315): the gate/up form of the tensor-core matvec. w [2I, C]
+ * (gate rows, then up rows), x [M, C]; m [M, I] = bf16(bf16(silu(g)) * u) over the matvec's bf16 outputs g, u at rows i
+ * and I + i: btb_b200_gemv_tc_bf16 + btb_b200_silu_mul's bits without the [M, 2I] buffer. workspace as above
+ * (btb_b200_gemv_tc_glu_workspace_bytes(I, C); 0 for matrices of many rows). */
+int btb_b200_gemv_tc_glu_bf16(const void* w, const void* x, void* m, int M, int I, int C, void* workspace, void* stream);
+size_t btb_b200_gemv_tc_glu_workspace_bytes(int I, int C);
 /* btb_gemm_mma_bf16 (native/cuda/btb_gemm.cuh:154): the prefill GEMM y [T, R] = bf16(x [T, C] W^T) for a prompt chunk of
  * any T >= 1 on the same tcgen05 kernel - tiles of 128 weight rows by up to 256 x rows, every tile its whole K. An output
  * element is one accumulation over all of k in k order, so row t carries the bits btb_b200_gemv_tc_bf16 gives that row in
@@ -371,6 +377,15 @@ int btb_b200_xchg_unpack(const void* words, void* dst, int M, int C, const btb_b
  * the whole pick; 1: send only; 2: take and merge only (for ranks that share one GPU and take turns). T <= 32. */
 int btb_b200_xchg_pick(const void* logits, int T, int Vl, int v_offset, const void* local_idx, int rank, int ranks,
                        void* const* tables, void* ids, void* pick_pass, void* body_pass, int phase, void* stream);
+/* experts cut over ranks (expert e on rank e % ep_size): btb_b200_moe_gemv whose outputs for the experts this rank holds
+ * go to every rank's copy of the [n_tasks, R] vector as marked words carrying bf16(output) - the rounding
+ * btb_b200_moe_combine applies to a product first - and btb_b200_moe_combine reading such a copy. send->stride = R,
+ * send->offset = 0. */
+int btb_b200_moe_gemv_x(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
+                        const void* idx, int n_tasks, int E, const void* x, int x_div, int R, int C, int ep_rank, int ep_size,
+                        const btb_b200_send* send, void* stream);
+int btb_b200_moe_combine_x(const void* dn_words, const void* idx, const void* w, const void* bias, void* y, int T, int k,
+                           int H, const btb_b200_recv* recv, void* stream);
 /* a pass-count advance as a launch of its own (no counterpart in the reference) */
 int btb_b200_xchg_tick(void* pass, void* stream);
 

@@ -72,3 +72,49 @@ def greedy(engs: list[P.TPEngine], prompt, max_new: int) -> list[list[int]]:
             call("btb_b200_publish", ptr(e.n0), 0, 0, 0, 0, 1, s)
             tk.append(int(e.bufs(1)["ids"][0].item()))
     return toks
+
+
+# ---- expert parallelism -------------------------------------------------------------------------------------------------
+
+
+def make_moe(cfg, world: int, seed: int, layer_std: float, cap: int = 512):
+    """`world` MoE engines, rank r holding expert e iff e % world == r, over one seeded model"""
+    from btb_b200 import moe as MO
+
+    heaps = [PeerHeap(MO.MoEEngine.heap_bytes(cfg), r, world) for r in range(world)]
+    PeerHeap.connect_engines(heaps)
+    return [MO.MoEEngine(MO.synth_moe_weights(cfg, seed=seed, on_cpu=True, ep_rank=r, ep_size=world, layer_std=layer_std),
+                         cap=cap, heap=heaps[r]) for r in range(world)]  # fmt: skip
+
+
+def moe_forward(engs, ids: torch.Tensor) -> list[torch.Tensor]:
+    """one chain pass on every rank (every rank holds the whole logits row)"""
+    T = int(ids.numel())
+    M = E.pad_rows(T)
+    s = capi.stream_ptr()
+    for e in engs:
+        g = e.bufs(M)
+        g["ids"][:T].copy_(ids.to(e.dev, torch.int64))
+        g["depth"][:M].copy_(torch.arange(M, dtype=torch.int32))
+        g["par"][:M].copy_(torch.arange(-1, M - 1, dtype=torch.int32))
+        e._embed(g, T, s)
+    for _ in zip(*[e.ops(T) for e in engs], strict=True):
+        pass
+    for e in engs:
+        call("btb_b200_publish", ptr(e.n0), 0, 0, 0, 0, T, s)
+    return [e.bufs(M)["logits"][:T] for e in engs]
+
+
+def moe_greedy(engs, prompt, max_new: int) -> list[list[int]]:
+    prompt = torch.as_tensor(prompt, dtype=torch.int64)
+    for e in engs:
+        e.reset()
+    last = None
+    for a in range(0, int(prompt.numel()), 32):
+        last = moe_forward(engs, prompt[a : a + 32])
+    toks = [[int(lg[-1].float().argmax())] for lg in last]
+    while len(toks[0]) < max_new:
+        lgs = moe_forward(engs, torch.tensor([toks[0][-1]]))
+        for tk, lg in zip(toks, lgs):
+            tk.append(int(lg[-1].float().argmax()))
+    return toks

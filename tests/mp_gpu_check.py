@@ -32,7 +32,7 @@ def main() -> None:
                         expert_fmt="fp8")
     want = MO.MoEEngine(MO.synth_moe_weights(mcfg, seed=6, on_cpu=True, layer_std=LAYER_STD), cap=512).generate_greedy(prompt, 16)
     lively(want)
-    ep = MO.MoEEngine(MO.synth_moe_weights(mcfg, seed=6, on_cpu=True, layer_std=LAYER_STD, ep_rank=rank, ep_size=world), cap=512)
+    ep = MO.MoEEngine(MO.synth_moe_weights(mcfg, seed=6, on_cpu=True, layer_std=LAYER_STD, ep_rank=rank, ep_size=world), cap=512)  # noqa: E501
     got = ep.generate_greedy(prompt, 16)
     assert got == want, (rank, got, want)
     dist.barrier()

@@ -71,6 +71,33 @@ def test_ranks_taking_turns_on_one_gpu_equal_the_plain_engine(world):
     assert capi.status() == 0
 
 
+@pytest.mark.parametrize("world,fmt,layers", [(2, "fp8", 2), (4, "mx4", 3)])
+def test_expert_parallel_ranks_taking_turns_equal_one_gpu(world, fmt, layers):
+    """experts cut over ranks (expert e on rank e % world), the products exchanged as marked words: every rank's logits
+    are the one-GPU engine's, bit for bit; three layers make the buffers' rotation (2, then the odd last one) show"""
+    from btb_b200 import moe as MO
+
+    cfg = MO.MoEConfig("ep", 256, layers, 8, 2, 128, 128, 512, experts=8, top_k=4, router_mode=0 if fmt == "fp8" else 1,
+                       glu_kind=0 if fmt == "fp8" else 1, expert_fmt=fmt)  # fmt: skip
+    one = MO.MoEEngine(MO.synth_moe_weights(cfg, seed=6, on_cpu=True, layer_std=LAYER_STD), cap=512)
+    prompt = torch.arange(3, 48)
+    want = one.generate_greedy(prompt, 14)
+    lively(want)
+    engs = lockstep.make_moe(cfg, world, 6, LAYER_STD)
+    got = lockstep.moe_greedy(engs, prompt, 14)
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    assert all(g == want for g in got), (got, want)
+    for T in (20, 1):
+        one.reset()
+        for e in engs:
+            e.reset()
+        full = one.forward(prompt[:T])
+        for lg in lockstep.moe_forward(engs, prompt[:T]):
+            assert torch.equal(lg.view(torch.int16), full.view(torch.int16)), T
+    assert capi.status() == 0
+
+
 def test_a_vector_nobody_sends_gives_up():
     """a consumer whose producers never write (a peer that died between steps) returns after about a second with
     ERR_TIMEOUT in the status word; the context stays usable"""

@@ -179,3 +179,60 @@ def test_prefill_on_the_tensor_cores_leaves_the_chain_passes_cache():
     # decode goes on from either cache alike
     ta, tb = a.step(int(la.float().argmax())), b.step(int(la.float().argmax()))
     assert ta == tb
+
+
+# ---- the gate/up form and the reference's other names ------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("I,C_", [(9728, 2560), (512, 256), (300, 264), (96, 4096), (768, 2048)])
+@pytest.mark.parametrize("M", [1, 5, 32])
+def test_glu_form_is_the_matvec_then_silu_mul(I, C_, M):
+    """btb_b200_gemv_tc_glu_bf16 = btb_b200_gemv_tc_bf16 over the merged gate/up block + btb_b200_silu_mul, bit for bit
+    (matrices of many tiles in one launch, of few tiles through K ranges and the ordered sum)"""
+    g = torch.Generator(device=DEV).manual_seed(I + C_ + M)
+    w = (torch.randn(2 * I, C_, generator=g, device=DEV) * 0.05).bfloat16()
+    x = torch.randn(M, C_, generator=g, device=DEV).bfloat16()
+    gu = _run(w, x)
+    want = torch.zeros(M, I, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_silu_mul", ptr(gu), ptr(want), M, I, capi.stream_ptr())
+    got = torch.full((M, I), 3.0, dtype=torch.bfloat16, device=DEV)
+    ws = _workspace(int(capi.lib().btb_b200_gemv_tc_glu_workspace_bytes(I, C_)))
+    call("btb_b200_gemv_tc_glu_bf16", ptr(w), ptr(x), ptr(got), M, I, C_, ptr(ws), capi.stream_ptr())
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def test_launcher_serves_the_reference_mma8_and_glu_names():
+    """btb_gemv_mma8_bf16 and btb_gemv_mma_glu_silu by the reference's names and parameter lists; beside the
+    reference's own kernels (where built) they agree to rounding - two summation orders, as for the plain matvec"""
+    from btb_b200 import launcher as L
+
+    from . import refkernels
+
+    R, C_, M, I = 1024, 2048, 3, 512
+    g = torch.Generator(device=DEV).manual_seed(9)
+    w = (torch.randn(R, C_, generator=g, device=DEV) * 0.05).bfloat16()
+    x = torch.zeros(32, C_, dtype=torch.bfloat16, device=DEV)
+    x[:M] = torch.randn(M, C_, generator=g, device=DEV).bfloat16()
+    b200 = L.B200Launcher()
+    y8, y16 = torch.zeros(32, R, dtype=torch.bfloat16, device=DEV), torch.zeros(32, R, dtype=torch.bfloat16, device=DEV)
+    L.btb_gemv_mma8_bf16(b200, ((R + 31) // 32, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(), y8.data_ptr(), R, C_, M)
+    L.btb_gemv_mma_bf16(b200, ((R + 63) // 64, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(), y16.data_ptr(), R, C_, M)
+    assert torch.equal(y8.view(torch.int16), y16.view(torch.int16))  # the block's size moves no bit, here as there
+    m = torch.zeros(32, I, dtype=torch.bfloat16, device=DEV)
+    L.btb_gemv_mma_glu_silu(b200, ((I + 63) // 64, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(), m.data_ptr(), I, C_, M)
+    torch.cuda.synchronize()
+    gu = x[:M].double() @ w.double().t()
+    ref = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    assert float((m[:M].double() - ref).abs().max()) <= 2.0**-6 * float(ref.abs().max())
+    if not refkernels.available():
+        return
+    theirs = refkernels.RefLauncher()
+    m2 = torch.zeros(32, I, dtype=torch.bfloat16, device=DEV)
+    L.btb_gemv_mma_glu_silu(theirs, ((I + 63) // 64, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(), m2.data_ptr(), I, C_, M)
+    y2 = torch.zeros(32, R, dtype=torch.bfloat16, device=DEV)
+    L.btb_gemv_mma8_bf16(theirs, ((R + 31) // 32, 1, 1), (128, 1, 1), w.data_ptr(), x.data_ptr(), y2.data_ptr(), R, C_, M)
+    torch.cuda.synchronize()
+    assert float((m[:M].float() - m2[:M].float()).abs().max()) <= 2.0**-6 * float(ref.abs().max())
+    assert float((y8[:M].float() - y2[:M].float()).abs().max()) <= 2.0**-7 * float(y2[:M].float().abs().max())
