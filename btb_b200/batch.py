@@ -45,9 +45,9 @@ class BatchEngine(CardEngine):
         self.n0b.zero_()
 
     def _attention(self, g: dict, i: int, wq: Any, wk: Any, T: int, s: int, win: int = 0, sinks: Any = None,
-                   out: Any = None) -> None:  # fmt: skip
+                   out: Any = None, warm: tuple = ()) -> None:  # fmt: skip
         if not self._side_by_side:
-            return super()._attention(g, i, wq, wk, T, s, win, sinks, out)
+            return super()._attention(g, i, wq, wk, T, s, win, sinks, out, warm)
         c = self.cfg
         Hq, Hk, D = c.q_heads, c.kv_heads, c.head_dim
         out = g["att"] if out is None else out

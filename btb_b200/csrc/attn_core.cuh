@@ -72,10 +72,10 @@ constexpr int NWA = 2 * GT;  // warps a block: two a tile, 32 keys each (a lane 
 // (bf16-rounded) and each warp's partial outputs.
 template <int D, int G>
 struct AttnSmem {
-    float qs[G][D];
+    uint32_t qs[G][D / 2];  // the queries as packed bf16 pairs (what the mixed-precision fma multiplies with)
     float hmax[GT][2][G];
     float hsum[GT][2][G];
-    float ps[NWA][G][32];
+    unsigned short ps[NWA][G][32];  // the weights, bf16
     float ho[NWA][G][D];
 };
 
@@ -184,7 +184,8 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
     for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
         const int hh = i / D, d = i - hh * D;
         const bf16* qp = A.q + ((size_t)t * Hq + g * G + hh) * D + d;
-        sm.qs[hh][d] = COHERENT ? __uint_as_float((uint32_t)__ldcg(reinterpret_cast<const unsigned short*>(qp)) << 16) : bf2f(*qp);
+        reinterpret_cast<unsigned short*>(&sm.qs[hh][0])[d] =
+            COHERENT ? __ldcg(reinterpret_cast<const unsigned short*>(qp)) : *reinterpret_cast<const unsigned short*>(qp);
     }
     __syncthreads();
 
@@ -211,13 +212,16 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
         for (int hh = 0; hh < G; ++hh) s[hh] = 0.f;
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) {
-            const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
-                                 bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
+            // eight dims of the chain: the key's and the query's bf16 multiplied where they lie, the sum f32 (the bits
+            // of fmaf over the widened values, in index order)
 #pragma unroll
             for (int hh = 0; hh < G; ++hh) {
+                const uint4 q4 = *reinterpret_cast<const uint4*>(&sm.qs[hh][c * 4]);
                 float a = s[hh];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) a = fmaf(kf[e], sm.qs[hh][c * 8 + e], a);
+                a = fma2_bf16(kv[c].x, q4.x, a);
+                a = fma2_bf16(kv[c].y, q4.y, a);
+                a = fma2_bf16(kv[c].z, q4.z, a);
+                a = fma2_bf16(kv[c].w, q4.w, a);
                 s[hh] = a;
             }
         }
@@ -241,7 +245,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
             float l = p;
 #pragma unroll
             for (int k = 16; k > 0; k >>= 1) l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, k));
-            sm.ps[warp][hh][lane] = bfround(p);
+            sm.ps[warp][hh][lane] = __bfloat16_as_ushort(f2bf(p));
             if (lane == 0) sm.hsum[tile][half][hh] = l;
 #pragma unroll
             for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
@@ -251,7 +255,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
         constexpr int VB = 16;
 #pragma unroll 1
         for (int i0 = 0; i0 < 32; i0 += VB) {
-            float vf[VB][E];
+            unsigned short vf[VB][E];  // bf16 as loaded: the mixed-precision fma multiplies them with the bf16 weights
 #pragma unroll
             for (int u = 0; u < VB; ++u) {
                 const int rk = __shfl_sync(0xffffffffu, row, i0 + u);
@@ -259,20 +263,21 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
                 if (E == 4) {
                     const uint2 vv = rk >= 0 ? (COHERENT ? __ldcg(reinterpret_cast<const uint2*>(vr)) : __ldg(reinterpret_cast<const uint2*>(vr)))
                                              : make_uint2(0u, 0u);
-                    vf[u][0] = bf_lo(vv.x), vf[u][1] = bf_hi(vv.x), vf[u][2] = bf_lo(vv.y), vf[u][3] = bf_hi(vv.y);
+                    split_bf16(vv.x, vf[u][0], vf[u][1]);
+                    split_bf16(vv.y, vf[u][2], vf[u][3]);
                 } else {
                     const uint32_t vv = rk >= 0 ? (COHERENT ? __ldcg(reinterpret_cast<const uint32_t*>(vr)) : __ldg(reinterpret_cast<const uint32_t*>(vr)))
                                             : 0u;
-                    vf[u][0] = bf_lo(vv), vf[u][E - 1] = bf_hi(vv);
+                    split_bf16(vv, vf[u][0], vf[u][E - 1]);
                 }
             }
 #pragma unroll
             for (int u = 0; u < VB; ++u) {
 #pragma unroll
                 for (int hh = 0; hh < G; ++hh) {
-                    const float p = sm.ps[warp][hh][i0 + u];
+                    const unsigned short p = sm.ps[warp][hh][i0 + u];
 #pragma unroll
-                    for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[u][e], o[hh][e]);
+                    for (int e = 0; e < E; ++e) o[hh][e] = fma_bf16(p, vf[u][e], o[hh][e]);
                 }
             }
         }
@@ -436,7 +441,7 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
         bf16 o[E];
         rope_values<D, false>(RA, hbase + rw, 0, lane, pos, o);
 #pragma unroll
-        for (int e = 0; e < E; ++e) sm.qs[rw][lane * E + e] = bf2f(o[e]);
+        for (int e = 0; e < E; ++e) reinterpret_cast<bf16*>(&sm.qs[rw][0])[lane * E + e] = o[e];
         if (owner) {
             bf16* dst = RA.qo + (size_t)(hbase + rw) * D + lane * E;
 #pragma unroll
@@ -476,13 +481,16 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
         for (int hh = 0; hh < G; ++hh) s[hh] = 0.f;
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) {
-            const float kf[8] = {bf_lo(kv[c].x), bf_hi(kv[c].x), bf_lo(kv[c].y), bf_hi(kv[c].y),
-                                 bf_lo(kv[c].z), bf_hi(kv[c].z), bf_lo(kv[c].w), bf_hi(kv[c].w)};
+            // eight dims of the chain: the key's and the query's bf16 multiplied where they lie, the sum f32 (the bits
+            // of fmaf over the widened values, in index order)
 #pragma unroll
             for (int hh = 0; hh < G; ++hh) {
+                const uint4 q4 = *reinterpret_cast<const uint4*>(&sm.qs[hh][c * 4]);
                 float a = s[hh];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) a = fmaf(kf[e], sm.qs[hh][c * 8 + e], a);
+                a = fma2_bf16(kv[c].x, q4.x, a);
+                a = fma2_bf16(kv[c].y, q4.y, a);
+                a = fma2_bf16(kv[c].z, q4.z, a);
+                a = fma2_bf16(kv[c].w, q4.w, a);
                 s[hh] = a;
             }
         }
@@ -509,7 +517,7 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
             float l = p;
 #pragma unroll
             for (int k = 16; k > 0; k >>= 1) l = __fadd_rn(l, __shfl_xor_sync(0xffffffffu, l, k));
-            sm.ps[warp][hh][lane] = bfround(p);
+            sm.ps[warp][hh][lane] = __bfloat16_as_ushort(f2bf(p));
             if (lane == 0) sm.hsum[tile][half][hh] = l;
 #pragma unroll
             for (int e = 0; e < E; ++e) o[hh][e] = 0.f;
@@ -536,14 +544,14 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
         }
 #pragma unroll
         for (int u = 0; u < 32; ++u) {
-            float vf[E];
+            unsigned short vf[E];
 #pragma unroll
-            for (int e = 0; e < E / 2; ++e) vf[2 * e] = bf_lo(vraw[u][e]), vf[2 * e + 1] = bf_hi(vraw[u][e]);
+            for (int e = 0; e < E / 2; ++e) split_bf16(vraw[u][e], vf[2 * e], vf[2 * e + 1]);
 #pragma unroll
             for (int hh = 0; hh < G; ++hh) {
-                const float p = sm.ps[warp][hh][u];
+                const unsigned short p = sm.ps[warp][hh][u];
 #pragma unroll
-                for (int e = 0; e < E; ++e) o[hh][e] = fmaf(p, vf[e], o[hh][e]);
+                for (int e = 0; e < E; ++e) o[hh][e] = fma_bf16(p, vf[e], o[hh][e]);
             }
         }
 #pragma unroll

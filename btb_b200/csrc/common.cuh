@@ -24,6 +24,41 @@ __device__ __forceinline__ float bfround(float v) { return __bfloat162float(__fl
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// Two bf16 times two bf16 into an f32 chain: acc = fma(w_lo, x_lo, acc), then acc = fma(w_hi, x_hi, acc), the
+// operands bf16 as they lie in their packed words and the sum f32 - sm_100's mixed-precision fma. A bf16 product is
+// exact in f32, so each step is fmaf(float(w), float(x), acc) to the bit, without the two widening instructions.
+__device__ __forceinline__ float fma2_bf16(uint32_t w, uint32_t x, float acc) {
+    asm("{\n.reg .b16 wl, wh, xl, xh;\nmov.b32 {wl, wh}, %1;\nmov.b32 {xl, xh}, %2;\nfma.rn.f32.bf16 %0, wl, xl, %0;\n"
+        "fma.rn.f32.bf16 %0, wh, xh, %0;\n}\n"
+        : "+f"(acc)
+        : "r"(w), "r"(x));
+    return acc;
+}
+
+// one step of such a chain with the operands' halves named: HW, HX 0 the low half (the earlier element), 1 the high
+#define B2_FMA1(WH, XH)                                                                                              \
+    asm("{\n.reg .b16 wl, wh, xl, xh;\nmov.b32 {wl, wh}, %1;\nmov.b32 {xl, xh}, %2;\nfma.rn.f32.bf16 %0, " WH ", " XH \
+        ", %0;\n}\n"                                                                                                 \
+        : "+f"(acc)                                                                                                  \
+        : "r"(w), "r"(x))
+template <int HW, int HX>
+__device__ __forceinline__ float fma1_bf16(uint32_t w, uint32_t x, float acc) {
+    if (HW == 0 && HX == 0) B2_FMA1("wl", "xl");
+    else if (HW == 0 && HX == 1) B2_FMA1("wl", "xh");
+    else if (HW == 1 && HX == 0) B2_FMA1("wh", "xl");
+    else B2_FMA1("wh", "xh");
+    return acc;
+}
+
+// the same with the operands as 16-bit values: a packed word's halves (free: they name the word's register halves) and one step
+__device__ __forceinline__ void split_bf16(uint32_t w, unsigned short& lo, unsigned short& hi) {
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(w));
+}
+__device__ __forceinline__ float fma_bf16(unsigned short w, unsigned short x, float acc) {
+    asm("fma.rn.f32.bf16 %0, %1, %2, %0;" : "+f"(acc) : "h"(w), "h"(x));
+    return acc;
+}
+
 // the butterfly every card reduction ends with (xor 16, 8, 4, 2, 1): the order is part of the result's bits
 __device__ __forceinline__ float warp_sum(float a) {
     a += __shfl_xor_sync(0xffffffffu, a, 16);

@@ -248,17 +248,6 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
     }
 }
 
-// Two weights times two activations into the chain: acc = fma(w_lo, x_lo, acc), then acc = fma(w_hi, x_hi, acc), the
-// operands bf16 as they lie in their packed words and the sum f32 - sm_100's mixed-precision fma. A bf16 product is
-// exact in f32, so each step is fmaf(float(w), float(x), acc) to the bit, without the two widening instructions.
-__device__ __forceinline__ float fma2_bf16(uint32_t w, uint32_t x, float acc) {
-    asm("{\n.reg .b16 wl, wh, xl, xh;\nmov.b32 {wl, wh}, %1;\nmov.b32 {xl, xh}, %2;\nfma.rn.f32.bf16 %0, wl, xl, %0;\n"
-        "fma.rn.f32.bf16 %0, wh, xh, %0;\n}\n"
-        : "+f"(acc)
-        : "r"(w), "r"(x));
-    return acc;
-}
-
 // ---- one ring stage into the accumulators --------------------------------------------------------------------------
 // stg: the stage (bf16: the segment's weights; pack12: its low bytes, then at `seg` its codes); nch chunks of 8, the
 // first global column c0 of `row`. Lane l takes local chunks l, l + 32, .. - segments are multiples of 256 columns,
@@ -285,9 +274,10 @@ __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* st
                 const uint2 lo = *reinterpret_cast<const uint2*>(stg + lc * 8);
                 const uint32_t codes = *reinterpret_cast<const uint32_t*>(stg + seg + lc * 4);
                 p12_chunk(lo.x, lo.y, codes, W.table, wp);
-                // a code of 15 is an escape: its high byte comes from the row's list
-                const uint32_t f = codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u;
-                if (f != 0u && W.e1 > W.e0) {
+                // a code of 15 is an escape: its high byte comes from the row's list (most rows have none: the test for
+                // code 15 is made only in rows that do)
+                const uint32_t f = W.e1 > W.e0 ? codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u : 0u;
+                if (f != 0u) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         if ((f >> (4 * e)) & 1u) {
