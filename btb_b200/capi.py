@@ -84,6 +84,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_argmax_bf16_static": (_I, [_P, _I, _I, _P, _P]),
     "btb_b200_sample_pick": (_I, [_P, _I, _I, _I, _LL, _P, _I, _P, _P, _P, _P, C.c_uint, _P, _P, _P, _P]),
     "btb_b200_sample_out": (_I, [_P, _P, _I, _P]),
+    "btb_b200_sample_verify": (_I, [_P, _I, _I, _I, _LL, _P, _I, _P, _I, _P, _P, _I, _P, _P, _P]),
     "btb_b200_sample_keys": (_I, [_P, _P, C.c_uint, _P, _P]),
     "btb_b200_kv_commit": (_I, [_P, _P, _LL, _I, _P, _P, _I, _I, _LL, _P, _I, _P]),
     "btb_b200_publish": (_I, [_P, _P, _P, _P, _P, _I, _P]),

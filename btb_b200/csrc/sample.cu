@@ -194,70 +194,77 @@ __device__ unsigned smp_select(cg::cluster_group& cl, Shared* S, const float* sv
     return S->pre;
 }
 
-__global__ void __cluster_dims__(SMP_CTAS, 1, 1) __launch_bounds__(SMP_THREADS) sample_pick(const SampleArgs A) {
-    cg::cluster_group cl = cg::this_cluster();
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    Shared* S = reinterpret_cast<Shared*>(smem_raw);
-    float* sv = reinterpret_cast<float*>(smem_raw + sizeof(Shared));
-    const unsigned tid = threadIdx.x, rank = blockIdx.x, r = blockIdx.y;
-    const int lo = (int)rank * A.per;
-    const int n = max(0, min(A.per, A.V - lo));
+// What the pick and the verify share: the row's slice into shared memory, its max, the two thresholds, the key
+struct RowFront {
+    float M;
+    unsigned floorK, floorP, floor;
+    unsigned long long key;
+    int lo, n;
+};
+__device__ __forceinline__ float smp_scaled(const SampleArgs& A, unsigned r, int i, float invT) {
+    return A.f32 ? __fmul_rn(static_cast<const float*>(A.logits)[(size_t)r * A.ls + i], invT)
+                 : __fmul_rn(bf2f(static_cast<const bf16*>(A.logits)[(size_t)r * A.ls + i]), invT);
+}
+__device__ RowFront smp_front(cg::cluster_group& cl, Shared* S, float* sv, const SampleArgs& A, unsigned r, unsigned rank) {
+    const unsigned tid = threadIdx.x;
+    RowFront F;
+    F.lo = (int)rank * A.per;
+    F.n = max(0, min(A.per, A.V - F.lo));
     const float invT = A.fp[0], top_p = A.fp[1];
-
-    // the slice, scaled, into shared memory; the row's max
     if (tid == 0) {
         S->vmax = 0u;
         S->best = 0ull;
     }
     __syncthreads();
     float m = NEG_INF;
-    if (A.f32) {
-        const float* row = static_cast<const float*>(A.logits) + (size_t)r * A.ls + lo;
-        for (int i = tid; i < n; i += SMP_THREADS) {
-            const float s = __fmul_rn(row[i], invT);
-            sv[i] = s;
-            m = fmaxf(m, s);
-        }
-    } else {
-        const bf16* row = static_cast<const bf16*>(A.logits) + (size_t)r * A.ls + lo;
-        for (int i = tid; i < n; i += SMP_THREADS) {
-            const float s = __fmul_rn(bf2f(row[i]), invT);
-            sv[i] = s;
-            m = fmaxf(m, s);
-        }
+    for (int i = tid; i < F.n; i += SMP_THREADS) {
+        const float s = smp_scaled(A, r, F.lo + i, invT);
+        sv[i] = s;
+        m = fmaxf(m, s);
     }
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     if ((tid & 31u) == 0) atomicMax(&S->vmax, smp_ordered(m));
     cl.sync();
     unsigned om = 0u;
     for (int c = 0; c < SMP_CTAS; ++c) om = max(om, *cl.map_shared_rank(&S->vmax, c));
-    const float M = smp_unordered(om);
-
+    F.M = smp_unordered(om);
     int gen = 0;
-    unsigned floorK = 0u, floorP = 0u;
-    if (A.top_k > 0) floorK = smp_select(cl, S, sv, n, 0, 0u, M, (unsigned)A.top_k, top_p, gen);
-    if (top_p < 1.0f) floorP = smp_select(cl, S, sv, n, 1, floorK, M, 0u, top_p, gen);
-    const unsigned floor = max(floorK, floorP);
-
-    // the draw
-    unsigned long long key;
+    F.floorK = F.floorP = 0u;
+    if (A.top_k > 0) F.floorK = smp_select(cl, S, sv, F.n, 0, 0u, F.M, (unsigned)A.top_k, top_p, gen);
+    if (top_p < 1.0f) F.floorP = smp_select(cl, S, sv, F.n, 1, F.floorK, F.M, 0u, top_p, gen);
+    F.floor = max(F.floorK, F.floorP);
     if (A.keys != nullptr) {
-        key = A.keys[r];
+        F.key = A.keys[r];
     } else {
         const long long pos = (long long)*A.n0p + (A.depth != nullptr ? A.depth[r] : 0);
-        key = smp_key(*A.seed, (unsigned long long)pos, A.salt);
+        F.key = smp_key(*A.seed, (unsigned long long)pos, A.salt);
     }
+    return F;
+}
+// the Gumbel race over the kept tokens of this CTA's slice; after the cluster barrier every CTA's S->best is whole
+__device__ __forceinline__ void smp_race(cg::cluster_group& cl, Shared* S, const float* sv, const RowFront& F) {
+    const unsigned tid = threadIdx.x;
     unsigned long long best = 0ull;
-    for (int i = tid; i < n; i += SMP_THREADS) {
+    for (int i = tid; i < F.n; i += SMP_THREADS) {
         const float s = sv[i];
-        if (smp_ordered(s) < floor || !(s - M >= SMP_FLOOR)) continue;
-        const unsigned tok = (unsigned)(lo + i);
-        const float v = __fsub_rn(s, logf(-logf(smp_uniform(key, tok))));
+        if (smp_ordered(s) < F.floor || !(s - F.M >= SMP_FLOOR)) continue;
+        const unsigned tok = (unsigned)(F.lo + i);
+        const float v = __fsub_rn(s, logf(-logf(smp_uniform(F.key, tok))));
         if (v > NEG_INF) best = max(best, smp_pack(v, tok));
     }
     for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
     if ((tid & 31u) == 0 && best) atomicMax(&S->best, best);
     cl.sync();
+}
+
+__global__ void __cluster_dims__(SMP_CTAS, 1, 1) __launch_bounds__(SMP_THREADS) sample_pick(const SampleArgs A) {
+    cg::cluster_group cl = cg::this_cluster();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Shared* S = reinterpret_cast<Shared*>(smem_raw);
+    float* sv = reinterpret_cast<float*>(smem_raw + sizeof(Shared));
+    const unsigned tid = threadIdx.x, rank = blockIdx.x, r = blockIdx.y;
+    const RowFront F = smp_front(cl, S, sv, A, r, rank);
+    smp_race(cl, S, sv, F);
     if (rank == 0 && tid == 0) {
         unsigned long long b = 0ull;
         for (int c = 0; c < SMP_CTAS; ++c) b = max(b, *cl.map_shared_rank(&S->best, c));
@@ -265,11 +272,177 @@ __global__ void __cluster_dims__(SMP_CTAS, 1, 1) __launch_bounds__(SMP_THREADS) 
         if (A.out != nullptr) A.out[r] = b ? (long long)(~(unsigned)(b & 0xFFFFFFFFull)) : 0ll;
         if (A.packed != nullptr) A.packed[r] = b;
         if (A.floors != nullptr) {
-            A.floors[2 * r] = floorK;
-            A.floors[2 * r + 1] = floorP;
+            A.floors[2 * r] = F.floorK;
+            A.floors[2 * r + 1] = F.floorP;
         }
     }
     cl.sync();  // no CTA leaves while a peer may still read its shared memory
+}
+
+// ---- the verify pass's pick: exact rejection sampling at a tree node (native/cuda/btb_kernels.cu:2126-2359
+// btb_sample_verify; btb/sampling.py:272-372 `Verify`). A row is a node with up to 32 drafted children in draw order.
+// Where the drafts are point masses (hasq 0) the node draws from the target and the child that equals the draw is
+// accepted. Where the drafter gave a distribution q, child i is accepted when u_i * q_i(c) < p_i(c): p_0 the target
+// over the kept tokens, p_{i+1} = norm(max(0, p_i - q_i)), q_i = q with the earlier children taken out; when no child
+// is accepted the node draws from the last residual. Either way the emitted token is a draw from the target.
+//
+// The thresholds and the point-mass race are the pick's (the cluster of eight). The trials' sums are floating point,
+// so their order is part of the result: they run on the cluster's first CTA alone as the reference's one block of 1024
+// threads does - thread t adds tokens t, t + 1024, ... in order, a warp folds by halving strides, the 32 warps' sums
+// are added in order - reading the row where it lies (it is in L2 by then).
+constexpr int SMP_KIDS = 32;
+
+struct VerifyArgs {
+    SampleArgs P;
+    const float* q;  // [R, Vd] the drafter's masses a node
+    const int* kids;  // [R, C] children in draw order, -1 after the last
+    const unsigned* hasq;
+    unsigned* out;  // [R] (accepted slot + 1) << 24 | token; slot 0: none accepted
+    int Vd, C;
+};
+
+struct VerifyShared {
+    float red[SMP_THREADS / 32];
+    float total;
+    float zp[SMP_KIDS + 1], zq[SMP_KIDS + 1];
+    int kid[SMP_KIDS];
+    unsigned long long won;
+};
+
+// the sum of every thread's `part`, in the fixed order above; every thread returns it
+__device__ __forceinline__ float smp_block_sum(VerifyShared* W, float part) {
+    const unsigned tid = threadIdx.x;
+    for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+    if ((tid & 31u) == 0) W->red[tid >> 5] = part;
+    __syncthreads();
+    if (tid == 0) {
+        float z = 0.0f;
+        for (int w = 0; w < SMP_THREADS / 32; ++w) z = __fadd_rn(z, W->red[w]);
+        W->total = z;
+    }
+    __syncthreads();
+    const float z = W->total;
+    __syncthreads();  // `total` and `red` are free again
+    return z;
+}
+
+// token x's mass after `k` rejected trials: exp(s - M) if kept, then k times max(0, w / zp[j] - q'(x) / zq[j]) with q'
+// losing x's mass once x was itself the tried child
+__device__ __forceinline__ float smp_left(const VerifyArgs& A, const VerifyShared* W, unsigned r, const float* qrow,
+                                          unsigned x, int k, float invT, float M, unsigned floor) {
+    const float s = smp_scaled(A.P, r, (int)x, invT);
+    float w = smp_ordered(s) >= floor ? smp_exp(__fsub_rn(s, M)) : 0.0f;
+    float qx = x < (unsigned)A.Vd ? qrow[x] : 0.0f;
+    for (int j = 0; j < k; ++j) {
+        w = fmaxf(0.0f, __fsub_rn(__fdiv_rn(w, W->zp[j]), __fdiv_rn(qx, W->zq[j])));
+        if (W->kid[j] == (int)x) qx = 0.0f;
+    }
+    return w;
+}
+
+__global__ void __cluster_dims__(SMP_CTAS, 1, 1) __launch_bounds__(SMP_THREADS) sample_verify(const VerifyArgs A) {
+    cg::cluster_group cl = cg::this_cluster();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Shared* S = reinterpret_cast<Shared*>(smem_raw);
+    float* sv = reinterpret_cast<float*>(smem_raw + sizeof(Shared));
+    __shared__ VerifyShared W;
+    const unsigned tid = threadIdx.x, rank = blockIdx.x, r = blockIdx.y;
+    const RowFront F = smp_front(cl, S, sv, A.P, r, rank);
+    const bool drawn = A.hasq[r] != 0u;  // the same for every CTA of the row
+    if (!drawn) smp_race(cl, S, sv, F);
+    if (rank == 0 && tid == 0) {
+        unsigned long long b = 0ull;
+        if (!drawn)
+            for (int c = 0; c < SMP_CTAS; ++c) b = max(b, *cl.map_shared_rank(&S->best, c));
+        W.won = b;
+    }
+    cl.sync();  // the peers' shared memory is not read after this: they may leave
+    if (rank != 0) return;
+    for (int c = tid; c < SMP_KIDS; c += SMP_THREADS) W.kid[c] = c < A.C ? A.kids[(size_t)r * A.C + c] : -1;
+    __syncthreads();
+
+    if (!drawn) {
+        if (tid == 0) {
+            const unsigned tok = W.won ? ~(unsigned)(W.won & 0xFFFFFFFFull) : 0u;
+            unsigned slot = 0u;
+            for (int c = 0; c < A.C; ++c)
+                if (W.kid[c] >= 0 && (unsigned)W.kid[c] == tok) {
+                    slot = (unsigned)c + 1u;
+                    break;
+                }
+            A.out[r] = (slot << 24) | tok;
+        }
+        return;
+    }
+
+    const float invT = A.P.fp[0];
+    const float* qrow = A.q + (size_t)r * A.Vd;
+    const int V = A.P.V;
+    // zp[0]: the target's mass over the kept tokens; zq[0]: the drafter's over its vocabulary
+    float part = 0.0f;
+    for (int i = tid; i < V; i += SMP_THREADS) {
+        const float s = smp_scaled(A.P, r, i, invT);
+        if (smp_ordered(s) >= F.floor) part = __fadd_rn(part, smp_exp(__fsub_rn(s, F.M)));
+    }
+    const float z0 = smp_block_sum(&W, part);
+    part = 0.0f;
+    for (int i = tid; i < A.Vd; i += SMP_THREADS) part = __fadd_rn(part, qrow[i]);
+    const float q0 = smp_block_sum(&W, part);
+    if (tid == 0) {
+        W.zp[0] = z0;
+        W.zq[0] = q0;
+    }
+    __syncthreads();
+
+    // the trials, every thread deciding alike
+    int tried = 0;
+    unsigned accepted = 0u, token = 0u;
+    for (int i = 0; i < A.C; ++i) {
+        const int c = W.kid[i];
+        if (c < 0) break;
+        const float zqi = W.zq[i];
+        const float qc = (c < A.Vd && zqi > 0.0f) ? fminf(__fdiv_rn(qrow[c], zqi), 1.0f) : 0.0f;
+        if (!(qc > 0.0f)) break;  // a child the drafter gives no mass was no draw of its: the trials end
+        const float pc = __fdiv_rn(smp_left(A, &W, r, qrow, (unsigned)c, i, invT, F.M, F.floor), W.zp[i]);
+        const float u = smp_uniform(F.key, 0xF00000u + (unsigned)i);
+        if (__fmul_rn(u, qc) < pc) {
+            accepted = (unsigned)i + 1u, token = (unsigned)c;
+            break;
+        }
+        part = 0.0f;
+        for (int x = tid; x < V; x += SMP_THREADS)
+            part = __fadd_rn(part, smp_left(A, &W, r, qrow, (unsigned)x, i + 1, invT, F.M, F.floor));
+        // smp_left(.., i + 1, ..) reads zp[i] and zq[i] only: the entries this pass is about to add are not read yet
+        const float z = smp_block_sum(&W, part);
+        if (tid == 0) {
+            W.zp[i + 1] = z;
+            W.zq[i + 1] = __fsub_rn(zqi, qrow[c]);
+        }
+        __syncthreads();
+        if (!(z > 0.0f)) {  // nothing left: the target was the drafter's distribution, the rejection was rounding
+            accepted = (unsigned)i + 1u, token = (unsigned)c;
+            break;
+        }
+        tried = i + 1;
+    }
+    if (accepted) {
+        if (tid == 0) A.out[r] = (accepted << 24) | token;
+        return;
+    }
+    // none accepted: a draw from what is left after every trial
+    unsigned long long best = 0ull;
+    for (int x = tid; x < V; x += SMP_THREADS) {
+        const float w = smp_left(A, &W, r, qrow, (unsigned)x, tried, invT, F.M, F.floor);
+        if (!(w > 0.0f)) continue;
+        const float v = __fadd_rn(logf(w), -logf(-logf(smp_uniform(F.key, (unsigned)x))));
+        if (v > NEG_INF) best = max(best, smp_pack(v, (unsigned)x));
+    }
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if (tid == 0) W.won = 0ull;
+    __syncthreads();
+    if ((tid & 31u) == 0 && best) atomicMax(&W.won, best);
+    __syncthreads();
+    if (tid == 0) A.out[r] = W.won ? ~(unsigned)(W.won & 0xFFFFFFFFull) : 0u;
 }
 
 // btb_sample_out (native/cuda/btb_kernels.cu:2110-2114): the token of a packed winner
@@ -332,4 +505,25 @@ extern "C" int btb_b200_sample_pick(const void* logits, int f32_logits, int R, i
                  static_cast<unsigned*>(floors), static_cast<unsigned long long*>(packed), per};
     // the cluster shape is the kernel's own (__cluster_dims__); the grid is whole clusters
     return b2_launch((const void*)sample_pick, dim3(SMP_CTAS, R), dim3(SMP_THREADS), smem, static_cast<cudaStream_t>(stream), a, 0);
+}
+
+extern "C" int btb_b200_sample_verify(const void* logits, int f32_logits, int R, int V, long long ls, const void* q, int Vd,
+                                      const void* kids, int C, const void* hasq, const void* keys, int top_k,
+                                      const void* fp, void* out, void* stream) {
+    if (!logits || !q || !hasq || !keys || !fp || !out || (C > 0 && !kids)) return B2_ERR_NULL;
+    if (R <= 0 || R > 65535 || V <= 0 || V > 0xFFFFFF || ls < V || Vd < 0 || C < 0 || C > SMP_KIDS || top_k < 0) return B2_ERR_DOMAIN;
+    const int per = (V + SMP_CTAS - 1) / SMP_CTAS;
+    const size_t smem = sizeof(Shared) + (size_t)per * sizeof(float);
+    if (smem + sizeof(VerifyShared) > 227 * 1024) return B2_ERR_DOMAIN;
+    static bool allowed[64] = {};
+    if (const int rc = b2_allow_smem((const void*)sample_verify, allowed)) return rc;
+    VerifyArgs a{};
+    a.P = SampleArgs{logits, ls, V, f32_logits, top_k, 0u, static_cast<const float*>(fp),
+                     static_cast<const unsigned long long*>(keys), nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, per};
+    a.q = static_cast<const float*>(q);
+    a.kids = static_cast<const int*>(kids);
+    a.hasq = static_cast<const unsigned*>(hasq);
+    a.out = static_cast<unsigned*>(out);
+    a.Vd = Vd, a.C = C;
+    return b2_launch((const void*)sample_verify, dim3(SMP_CTAS, R), dim3(SMP_THREADS), smem, static_cast<cudaStream_t>(stream), a, 0);
 }

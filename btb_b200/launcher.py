@@ -63,6 +63,7 @@ class B200Launcher:
         (r"btb_sample_bin$", "_sample_bin"),
         (r"btb_sample_draw$", "_sample_draw"),
         (r"btb_sample_out$", "_sample_out"),
+        (r"btb_sample_verify$", "_sample_verify"),
     )
 
     def __init__(self) -> None:
@@ -189,6 +190,11 @@ class B200Launcher:
         gbest, out, R = a
         capi.call("btb_b200_sample_out", _p(gbest), _p(out), int(_v(R)), s)
 
+    def _sample_verify(self, name, m, grid, a, s):
+        x, q, kids, hasq, keys, V, Vd, Cw, top_k, fp, out = a
+        capi.call("btb_b200_sample_verify", _p(x), 1, int(grid[0]), int(_v(V)), int(_v(V)), _p(q), int(_v(Vd)), _p(kids),
+                  int(_v(Cw)), _p(hasq), _p(keys), int(_v(top_k)), _p(fp), _p(out), s)  # fmt: skip
+
 
 # -- typed launchers, the reference's names and argument order (btb/engine/card_launch.py) --------------------------
 _P, _I, _F = C.c_void_p, C.c_int, C.c_float
@@ -271,6 +277,12 @@ def btb_sample_draw(launcher, grid, block, x, keys, V, fp, gM, gpreK, gpreP, gbe
 
 def btb_sample_out(launcher, grid, block, gbest, out, R, *, stream=None, shared=0):
     launcher.launch("btb_sample_out", grid, block, [_P(gbest), _P(out), _I(R)], stream, shared)
+
+
+def btb_sample_verify(launcher, grid, block, x, q, kids, hasq, keys, V, Vd, C_, top_k, fp, out, *, stream=None, shared=0):
+    launcher.launch("btb_sample_verify", grid, block,
+                    [_P(x), _P(q), _P(kids), _P(hasq), _P(keys), _I(V), _I(Vd), _I(C_), _I(top_k), _P(fp), _P(out)],
+                    stream, shared)  # fmt: skip
 
 
 def btb_gemv_mma_bf16(launcher, grid, block, w, x, y, R, C_, M, *, stream=None, shared=0):

@@ -206,6 +206,18 @@ int btb_b200_argmax_bf16_static(const void* logits, int T, int V, void* out, voi
 int btb_b200_sample_pick(const void* logits, int f32_logits, int R, int V, long long ls, const void* fp, int top_k,
                          const void* keys, const void* seed, const void* n0p, const void* depth, unsigned salt,
                          void* out, void* floors, void* packed, void* stream);
+/* btb_sample_verify (native/cuda/btb_kernels.cu:2126-2359; host side btb/sampling.py:272-372 `Verify`): the pick of a
+ * verify pass whose rows are tree nodes with drafted children - exact rejection sampling, the emitted token a draw from
+ * the target at every node. logits [R, V] at stride ls (f32 when f32_logits, else bf16); q f32 [R, Vd] the drafter's
+ * masses a node (unnormalised is fine); kids i32 [R, C] a node's children in draw order, -1 after the last, C <= 32;
+ * hasq u32 [R] (0: the node's drafts are point masses - it draws from the target and accepts the child that equals the
+ * draw); keys u64 [R]; fp f32 [2] = [1/T, top_p] on the card. out u32 [R] = (accepted slot + 1) << 24 | token, slot 0
+ * when no child was accepted. One launch: the thresholds and the point-mass race on a cluster of 8 CTAs a row, the
+ * trials' floating-point sums on the cluster's first CTA in the reference's order (1024 threads striding the row, warps
+ * folded by halving strides, the warps' sums added in order). */
+int btb_b200_sample_verify(const void* logits, int f32_logits, int R, int V, long long ls, const void* q, int Vd,
+                           const void* kids, int C, const void* hasq, const void* keys, int top_k, const void* fp,
+                           void* out, void* stream);
 /* btb_sample_out (native/cuda/btb_kernels.cu:2110-2114): out u32 [R] = the token of each packed winner */
 int btb_b200_sample_out(const void* packed, void* out, int R, void* stream);
 /* btb_sample_keys (native/cuda/btb_kernels.cu:2116-2124): keys u32 [2] = key_for(seed u32 [2] (lo, hi), pos i32 [1],

@@ -648,6 +648,135 @@ int orc_sample_pick(const float* x, int R, int V, const uint64_t* keys, float in
     return BTB_OK;
 }
 
+/* ---- the verify pass's pick: native/cuda/btb_kernels.cu:2126-2359 (btb_sample_verify), btb/sampling.py:272-372 ----
+ * A row is a tree node with up to 32 drafted children in draw order. hasq 0: the node draws from the target, the child
+ * equal to the draw is accepted. hasq 1: child i accepted when u_i * q_i(c) < p_i(c), p_{i+1} = norm(max(0, p_i - q_i));
+ * none accepted, a draw from the last residual. The kernel's float sums run as one block of 1024 threads: thread t adds
+ * tokens t, t + 1024, ... in order, a warp folds by strides 16, 8, 4, 2, 1, the 32 warps' sums are added in order.
+ * That order is restated here so the two agree to the bit. */
+#define VRF_THREADS 1024
+static float vrf_block_sum(const float* part) {
+    float warp[VRF_THREADS / 32];
+    for (int w = 0; w < VRF_THREADS / 32; ++w) {
+        float v[32], t[32];
+        memcpy(v, part + 32 * w, sizeof v);
+        for (int o = 16; o > 0; o >>= 1) {
+            for (int l = 0; l < 32; ++l) t[l] = v[l] + v[l ^ o];
+            memcpy(v, t, sizeof v);
+        }
+        warp[w] = v[0];
+    }
+    float z = 0.0f;
+    for (int w = 0; w < VRF_THREADS / 32; ++w) z += warp[w];
+    return z;
+}
+static float vrf_left(const float* s, const float* qrow, const int* kid, int x, int k, float m, uint32_t floor, int Vd,
+                      const float* zp, const float* zq) {
+    float w = smp_ordered(s[x]) >= floor ? smp_exp(s[x] - m) : 0.0f;
+    float qx = x < Vd ? qrow[x] : 0.0f;
+    for (int j = 0; j < k; ++j) {
+        const float a = w / zp[j], b = qx / zq[j];
+        w = fmaxf(0.0f, a - b);
+        if (kid[j] == x) qx = 0.0f;
+    }
+    return w;
+}
+/* x [R, V] f32 logits, q [R, Vd], kids [R, C] (-1 after the last), hasq [R], keys [R]; out [R] packed
+ * (accepted slot + 1) << 24 | token */
+int orc_sample_verify(const float* x, int R, int V, const float* q, int Vd, const int32_t* kids, int C,
+                      const uint32_t* hasq, const uint64_t* keys, float inv_t, uint32_t top_k, float top_p,
+                      uint32_t* out) {
+    if (!x || !hasq || !keys || !out || (Vd > 0 && !q) || (C > 0 && !kids)) return BTB_ERR_NULL;
+    if (R <= 0 || V <= 0 || C < 0 || C > 32 || !(inv_t > 0.0f)) return BTB_ERR_DOMAIN;
+    float* s = (float*)malloc((size_t)V * sizeof(float));
+    uint64_t* w = (uint64_t*)malloc((size_t)V * sizeof(uint64_t));
+    float part[VRF_THREADS];
+    for (int r = 0; r < R; ++r) {
+        const float* row = x + (size_t)r * V;
+        const float* qrow = q + (size_t)r * Vd;
+        int kid[32];
+        for (int c = 0; c < 32; ++c) kid[c] = c < C ? kids[(size_t)r * C + c] : -1;
+        float m = -INFINITY;
+        for (int i = 0; i < V; ++i) {
+            s[i] = row[i] * inv_t;
+            m = fmaxf(m, s[i]);
+        }
+        uint32_t fk = 0, fp = 0;
+        if (top_k > 0) fk = smp_select(s, NULL, V, top_k, 0.0f, 0);
+        if (top_p < 1.0f) {
+            for (int i = 0; i < V; ++i) w[i] = smp_mass(s[i], m, fk);
+            fp = smp_select(s, w, V, 0, top_p, fk);
+        }
+        const uint32_t floor = fk > fp ? fk : fp;
+        const uint64_t key = keys[r];
+        if (!hasq[r]) {
+            float best = -INFINITY;
+            uint32_t bi = 0;
+            for (int i = 0; i < V; ++i) {
+                if (smp_ordered(s[i]) < floor || !(s[i] - m >= -21.0f)) continue;
+                const float v = s[i] - logf(-logf(orc_sample_uniform(key, (uint32_t)i)));
+                if (v > best) best = v, bi = (uint32_t)i;
+            }
+            uint32_t slot = 0;
+            for (int c = 0; c < C; ++c)
+                if (kid[c] >= 0 && (uint32_t)kid[c] == bi) {
+                    slot = (uint32_t)c + 1;
+                    break;
+                }
+            out[r] = (slot << 24) | bi;
+            continue;
+        }
+        float zp[33], zq[33];
+        memset(part, 0, sizeof part);
+        for (int i = 0; i < V; ++i)
+            if (smp_ordered(s[i]) >= floor) part[i % VRF_THREADS] += smp_exp(s[i] - m);
+        zp[0] = vrf_block_sum(part);
+        memset(part, 0, sizeof part);
+        for (int i = 0; i < Vd; ++i) part[i % VRF_THREADS] += qrow[i];
+        zq[0] = vrf_block_sum(part);
+        int tried = 0;
+        uint32_t accepted = 0, token = 0;
+        for (int i = 0; i < C; ++i) {
+            const int c = kid[i];
+            if (c < 0) break;
+            const float qc = (c < Vd && zq[i] > 0.0f) ? fminf(qrow[c] / zq[i], 1.0f) : 0.0f;
+            if (!(qc > 0.0f)) break;
+            const float pc = vrf_left(s, qrow, kid, c, i, m, floor, Vd, zp, zq) / zp[i];
+            const float u = orc_sample_uniform(key, 0xF00000u + (uint32_t)i);
+            if (u * qc < pc) {
+                accepted = (uint32_t)i + 1, token = (uint32_t)c;
+                break;
+            }
+            memset(part, 0, sizeof part);
+            for (int t = 0; t < V; ++t) part[t % VRF_THREADS] += vrf_left(s, qrow, kid, t, i + 1, m, floor, Vd, zp, zq);
+            const float z = vrf_block_sum(part);
+            zp[i + 1] = z;
+            zq[i + 1] = zq[i] - qrow[c];
+            if (!(z > 0.0f)) {
+                accepted = (uint32_t)i + 1, token = (uint32_t)c;
+                break;
+            }
+            tried = i + 1;
+        }
+        if (accepted) {
+            out[r] = (accepted << 24) | token;
+            continue;
+        }
+        float best = -INFINITY;
+        uint32_t bi = 0;
+        for (int t = 0; t < V; ++t) {
+            const float wl = vrf_left(s, qrow, kid, t, tried, m, floor, Vd, zp, zq);
+            if (!(wl > 0.0f)) continue;
+            const float v = logf(wl) + -logf(-logf(orc_sample_uniform(key, (uint32_t)t)));
+            if (v > best) best = v, bi = (uint32_t)t;
+        }
+        out[r] = bi;
+    }
+    free(s);
+    free(w);
+    return BTB_OK;
+}
+
 /* ------------------------------------------------------------------------------------------------------- */
 /* CPU tier: 16-lane GEMV over bf16 / pack12 / MXFP4 / FP8                                                 */
 /* ------------------------------------------------------------------------------------------------------- */

@@ -325,6 +325,25 @@ def sample_pick(x, keys, temperature: float, top_k: int = 0, top_p: float = 1.0)
     return out, floors, margin
 
 
+def sample_verify(x, q, kids, hasq, keys, temperature: float, top_k: int = 0, top_p: float = 1.0) -> np.ndarray:
+    """packed outcomes [R] ((accepted slot + 1) << 24 | token) of the verify pass's pick: x [R, V] f32 logits, q [R, Vd]
+    the drafter's masses, kids [R, C] int32 (-1 after the last), hasq [R], keys [R]"""
+    x = np.ascontiguousarray(x, np.float32)
+    q = np.ascontiguousarray(q, np.float32)
+    kids = np.ascontiguousarray(kids, np.int32)
+    hasq = np.ascontiguousarray(hasq, np.uint32)
+    keys = np.ascontiguousarray(keys, np.uint64)
+    R, V = x.shape
+    out = np.empty(R, np.uint32)
+    L = lib()
+    L.orc_sample_verify.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                    C.c_void_p, C.c_float, C.c_uint32, C.c_float, C.c_void_p]  # fmt: skip
+    _ck(L.orc_sample_verify(_p(x), R, V, _p(q), q.shape[1], _p(kids), kids.shape[1], _p(hasq), _p(keys),
+                            np.float32(1.0) / np.float32(temperature), int(top_k), float(top_p), _p(out)),
+        "orc_sample_verify")  # fmt: skip
+    return out
+
+
 def sample_key(seed: int, pos: int, salt: int = 0) -> int:
     L = lib()
     L.orc_sample_key.restype, L.orc_sample_key.argtypes = C.c_uint64, [C.c_uint64, C.c_uint64, C.c_uint32]

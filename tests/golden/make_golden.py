@@ -151,6 +151,39 @@ def sampling(ref: str, out: dict) -> None:
     out["uniform"] = S._hash_uniform(key, idx).numpy()
 
 
+def verify(ref: str, out: dict) -> None:
+    """seeded verify-pass picks through the reference's `Verify.pick_torch` on the CPU (its torch statement of the card's
+    btb_sample_verify): children drawn from a perturbed copy of the target by the reference's own `draw_torch`, rows with
+    and without a drafter distribution, with and without top-k / top-p"""
+    from btb.sampling import Sampling, Verify
+
+    cases = [(12, 4, 300, Sampling(temperature=0.8, top_p=0.9, seed=5), 8, 0.7),
+             (12, 4, 100, Sampling(temperature=1.2, top_k=6, seed=2), 4, 0.7),
+             (3000, 3, 24, Sampling(temperature=0.7, top_k=50, top_p=0.95, seed=11), 6, 0.7),
+             (3000, 3, 24, Sampling(temperature=1.0, seed=3), 3, 0.7),
+             (12, 4, 300, Sampling(temperature=0.8, seed=8), 3, 3.0),  # a drafter far from the target: rejections
+             (3000, 3, 24, Sampling(temperature=0.9, top_p=0.8, seed=4), 5, 2.0)]  # fmt: skip
+    for ci, (V, R, n, s, width, noise) in enumerate(cases):
+        g = torch.Generator().manual_seed(100 + ci)
+        logits = torch.randn(R, V, generator=g) * 3
+        dl = logits + torch.randn(R, V, generator=g) * noise
+        K, H, KEYS, OUT = [], [], [], []
+        for i in range(n):
+            keys = [s.key_for(i * R + r) for r in range(R)]
+            ids, q = s.draw_torch(dl, [s.key_for(i * R + r, salt=1) for r in range(R)], width)
+            hasq = [(i + r) % 3 != 0 for r in range(R)]
+            kids = ids.tolist()
+            got = Verify(s, q, kids, hasq).pick_torch(logits, keys)
+            K.append(np.asarray(kids, np.int32)), H.append(np.asarray(hasq, np.uint32))
+            KEYS.append(np.asarray(keys, np.uint64)), OUT.append(got.numpy().astype(np.uint32))
+        out[f"v{ci}/logits"], out[f"v{ci}/dl"] = logits.numpy(), dl.numpy()
+        out[f"v{ci}/params"] = np.asarray([s.temperature, s.top_k, s.top_p, s.seed, width], np.float64)
+        out[f"v{ci}/kids"], out[f"v{ci}/hasq"] = np.stack(K), np.stack(H)
+        out[f"v{ci}/keys"], out[f"v{ci}/out"] = np.stack(KEYS), np.stack(OUT)
+        # the drafter's distribution does not depend on the keys: the same at every trial of a case, kept once
+        out[f"v{ci}/q"] = s.dist_torch(dl).numpy()
+
+
 def drafts(ref: str) -> dict:
     """seeded token streams through the reference's n-gram proposer and its chain merge: the chains proposed after
     every few tokens and the trees built from them"""
@@ -302,7 +335,10 @@ def main() -> None:
     e: dict = {}
     tiny_moe(ref, e)
     np.savez_compressed(os.path.join(HERE, "tiny_gpt_oss.npz"), **e)
-    for f in ("codecs.npz", "tiny_qwen3.npz", "sampling.npz", "drafts.json", "moe.npz", "tiny_gpt_oss.npz"):
+    v: dict = {}
+    verify(ref, v)
+    np.savez_compressed(os.path.join(HERE, "verify.npz"), **v)
+    for f in ("codecs.npz", "tiny_qwen3.npz", "sampling.npz", "drafts.json", "moe.npz", "tiny_gpt_oss.npz", "verify.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 

@@ -193,3 +193,135 @@ def test_launcher_serves_the_reference_pipeline_and_equals_its_kernels(V, T, k, 
         a = np.uint64(mine[2][0]).item() >> 32
         b = np.uint64(theirs[2][0]).item() >> 32
         assert abs(a - b) <= 64
+
+
+# ---- the verify pass's pick (btb_sample_verify) ------------------------------------------------------------------------
+
+import os  # noqa: E402
+
+from btb_b200.sampling import Verify  # noqa: E402
+
+VGOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "verify.npz"))
+
+
+def _verify(x: torch.Tensor, q, kids, hasq, keys, T, k, p) -> np.ndarray:
+    s = Sampling(temperature=float(T), top_k=int(k), top_p=float(p), seed=0)
+    v = Verify(s, torch.as_tensor(np.asarray(q)), [[int(c) for c in row if c >= 0] for row in np.asarray(kids)], list(hasq))
+    out = v.pick(x, [int(a) for a in keys]).cpu().numpy().astype(np.uint32)
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    return out
+
+
+@pytest.mark.parametrize("ci", range(6))
+def test_verify_outcomes_are_the_reference_s_and_the_oracle_s(ci):
+    """the golden outcomes come from the reference's `Verify.pick_torch`; the oracle equals them (CPU suite)"""
+    lg, q, P = VGOLD[f"v{ci}/logits"], VGOLD[f"v{ci}/q"], VGOLD[f"v{ci}/params"]
+    x = torch.from_numpy(lg).cuda()
+    n = min(len(VGOLD[f"v{ci}/out"]), 120)
+    for i in range(n):
+        got = _verify(x, q, VGOLD[f"v{ci}/kids"][i], VGOLD[f"v{ci}/hasq"][i], VGOLD[f"v{ci}/keys"][i], P[0], P[1], P[2])
+        assert np.array_equal(got, VGOLD[f"v{ci}/out"][i]), (ci, i, got, VGOLD[f"v{ci}/out"][i])
+
+
+def _verify_case(V, R, width, noise, seed, sampling):
+    rng = np.random.default_rng(seed)
+    lg = (rng.standard_normal((R, V)) * 3).astype(np.float32)
+    dl = lg + (rng.standard_normal((R, V)) * noise).astype(np.float32)
+    q = np.exp((dl - dl.max(-1, keepdims=True)) / np.float32(sampling.temperature)).astype(np.float32)
+    q[:, V // 2 :] *= (rng.random((R, V - V // 2)) < 0.5)  # a drafter that gives many tokens no mass
+    pr = q.astype(np.float64) / q.astype(np.float64).sum(-1, keepdims=True)
+    kids = np.stack([rng.choice(V, size=width, replace=False, p=pr[r]) for r in range(R)]).astype(np.int32)
+    kids[0, width - 1] = -1  # a ragged row
+    hasq = np.asarray([(r % 4) != 3 for r in range(R)], np.uint32)
+    keys = rng.integers(0, 2**63, size=R, dtype=np.uint64)
+    return lg, q, kids, hasq, keys
+
+
+@pytest.mark.parametrize("V,R,width,noise", [(151936, 6, 4, 1.5), (32000, 9, 8, 3.0), (201088, 3, 31, 0.5), (70, 16, 5, 2.0)])
+def test_verify_equals_the_oracle_at_real_vocabularies(V, R, width, noise):
+    s = Sampling(temperature=0.8, top_k=0 if V == 70 else 200, top_p=0.95, seed=0)
+    lg, q, kids, hasq, keys = _verify_case(V, R, width, noise, V + R, s)
+    want = O.sample_verify(lg, q, kids, hasq, keys, s.temperature, s.top_k, s.top_p)
+    got = _verify(torch.from_numpy(lg).cuda(), q, kids, hasq, keys, s.temperature, s.top_k, s.top_p)
+    # the trials' sums run in the oracle's order: equal outcomes; only a draw (a race of logf values) may fall inside the
+    # last ulps between the host's logf and the card's
+    same = got == want
+    assert same.mean() >= 0.8 and np.array_equal(got >> 24, want >> 24), (got, want)
+    # bf16 logits are the same pick as their f32 widening
+    xb = torch.from_numpy(lg).cuda().bfloat16()
+    want_b = O.sample_verify(xb.float().cpu().numpy(), q, kids, hasq, keys, s.temperature, s.top_k, s.top_p)
+    got_b = _verify(xb, q, kids, hasq, keys, s.temperature, s.top_k, s.top_p)
+    assert np.array_equal(got_b >> 24, want_b >> 24) and (got_b == want_b).mean() >= 0.8
+
+
+@pytest.mark.parametrize("V,R,width,noise", [(151936, 4, 4, 1.5), (5000, 12, 8, 3.0), (12, 16, 5, 1.0)])
+def test_verify_through_the_launcher_equals_the_reference_s_kernel(V, R, width, noise):
+    from . import refkernels
+    from btb_b200 import launcher as L
+
+    if not refkernels.available():
+        pytest.skip("the reference's kernels are not built (oracle/build_ref.sh)")
+    s = Sampling(temperature=0.9, top_k=0 if V == 12 else 64, top_p=0.9, seed=0)
+    lg, q, kids, hasq, keys = _verify_case(V, R, width, noise, 7 * V + R, s)
+    dev = "cuda"
+    x, qd = torch.from_numpy(lg).to(dev), torch.from_numpy(q).to(dev)
+    kd, hd = torch.from_numpy(kids).to(dev), torch.from_numpy(hasq.view(np.int32)).to(dev)
+    kk = torch.from_numpy(keys.view(np.int64)).to(dev)
+    fp = torch.tensor([1.0 / s.temperature, s.top_p], dtype=torch.float32, device=dev)
+    outs = []
+    for la in (L.B200Launcher(), refkernels.RefLauncher()):
+        out = torch.zeros(R, dtype=torch.int32, device=dev)
+        p = lambda t: t.data_ptr()  # noqa: E731
+        L.btb_sample_verify(la, (R, 1, 1), (1024, 1, 1), p(x), p(qd), p(kd), p(hd), p(kk), V, V, width, s.top_k, p(fp), p(out))
+        torch.cuda.synchronize()
+        outs.append(out.cpu().numpy().view(np.uint32))
+    assert capi.status() == 0
+    assert np.array_equal(outs[0] >> 24, outs[1] >> 24), outs  # the accepted slots
+    assert (outs[0] == outs[1]).mean() >= 0.8, outs  # tokens: a residual draw may sit inside logf's last ulps
+
+
+def test_verify_emits_the_target_distribution():
+    """the property that makes drawn-tree speculation exact (the reference's test_the_cuda_verify_follows_the_target): over
+    the keys, the emitted token - accepted child or residual draw - follows the target p, whatever the drafter proposed"""
+    V, R, n = 12, 4, 1500
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(R, V, generator=g) * 3
+    dl = logits + torch.randn(R, V, generator=g) * 0.7
+    s = Sampling(temperature=0.8, top_p=0.9, seed=5)
+    # the target after temperature and top-p, from the oracle's thresholds
+    sc = logits.numpy() * (np.float32(1.0) / np.float32(s.temperature))  # the scaled row as the kernels make it
+    _, floors, _ = O.sample_pick(logits.numpy(), np.zeros(R, np.uint64), s.temperature, 0, s.top_p)
+    p = np.exp(sc - sc.max(-1, keepdims=True))
+    ordered = lambda f: np.where(f.view(np.uint32) >> 31, ~f.view(np.uint32), f.view(np.uint32) | np.uint32(1 << 31))  # noqa: E731
+    p = p * (ordered(sc.astype(np.float32)) >= floors[:, 1:2])
+    p /= p.sum(-1, keepdims=True)
+    qd = torch.softmax(dl / s.temperature, -1)
+    x = logits.cuda()
+    seen = np.zeros((R, V))
+    gq = torch.Generator().manual_seed(1)
+    for i in range(n):
+        keys = [s.key_for(i * R + r) for r in range(R)]
+        kids = torch.multinomial(qd, 6, replacement=False, generator=gq).tolist()  # drafts drawn without replacement from q
+        out = Verify(s, qd, kids, [True] * R).pick(x, keys).tolist()
+        for r in range(R):
+            slot, t = Verify.unpack(out[r])
+            assert 0 <= t < V and (slot < 0 or kids[r][slot] == t)
+            seen[r][t] += 1
+    assert np.abs(seen / n - p).max() < 0.04, (seen / n, p)
+
+
+def test_verify_refusals():
+    x = torch.zeros(1, 64, device="cuda")
+    z = torch.zeros(1, 64, device="cuda")
+    kids = torch.zeros(1, 40, dtype=torch.int32, device="cuda")
+    one = torch.ones(1, dtype=torch.int64, device="cuda")
+    fp = torch.ones(2, device="cuda")
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    a = (ptr(x), 1, 1, 64, 64, ptr(z), 64, ptr(kids))
+    with pytest.raises(capi.NativeError):  # more children than the kernel's table holds
+        call("btb_b200_sample_verify", *a, 40, ptr(one), ptr(one), 0, ptr(fp), ptr(out), capi.stream_ptr())
+    with pytest.raises(capi.NativeError):
+        call("btb_b200_sample_verify", *a, 4, 0, ptr(one), 0, ptr(fp), ptr(out), capi.stream_ptr())
+    with pytest.raises(ValueError):
+        Verify(Sampling(temperature=1.0), z, [list(range(33))], [True])
