@@ -769,13 +769,16 @@ def run_case(args) -> None:
         # or moe:mx4 (gpt-oss-20b shape, 4 picks of 32); the picks rotate so that the rows come from DRAM
         from btb_b200 import moe as MO
 
-        cfg = MO.QWEN3_30B_A3B if rest == "fp8" else MO.GPT_OSS_20B
+        cfg = MO.QWEN3_30B_A3B if rest.split(":")[0] == "fp8" else MO.GPT_OSS_20B
         gen = torch.Generator(device="cuda").manual_seed(0)
         st = MO.synth_expert_stack(cfg, gen, cfg.experts, 2 * cfg.inter, cfg.hidden, "cuda")
         k, E = cfg.top_k, cfg.experts
         rounds = max(2, E // k)
         picks = [torch.arange(i * k, (i + 1) * k, dtype=torch.int32, device="cuda") % E for i in range(rounds)]
+        # the row the engine's experts are given: the normed bf16 row widened to f32 (moe:fp8:f32 for any f32 row)
         xf = torch.randn(1, cfg.hidden, device="cuda", generator=gen)
+        if not args.case.endswith(":f32"):
+            xf = xf.bfloat16().float()
         yv = torch.zeros(k, 2 * cfg.inter, device="cuda")
         per = k * 2 * cfg.inter * cfg.hidden * {"fp8": 1.0, "mx4": 17 / 32, "bf16": 2.0}[st.fmt]
         for it in range(3):
@@ -954,7 +957,12 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=0, help="prompt tokens (0: the configuration's own length)")
     ap.add_argument("--prefill", default="auto", choices=["auto", "gemm", "chain"])
     ap.add_argument("--replicas", action="store_true", help="--gpus N: N independent copies instead of one model over N ranks")
+    ap.add_argument("--tune", default="", help="the library's launch tunables, k=v[,k=v...] (btb_b200_set_tuning)")
     args = ap.parse_args()
+    if args.tune and args.impl != "reference":
+        from btb_b200 import capi  # noqa: PLC0415
+
+        capi.set_tuning(**{k: int(v) for k, v in (kv.split("=") for kv in args.tune.split(","))})
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

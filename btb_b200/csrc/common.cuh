@@ -59,6 +59,25 @@ __device__ __forceinline__ float fma_bf16(unsigned short w, unsigned short x, fl
     return acc;
 }
 
+// two e4m3fn bytes (the low 16 bits of `two`) times an f32 scale, each product rounded to f32 and then to the nearest
+// bf16 (ties to even), as the packed pair (first byte in the low half): the weight btb's FP8 codec holds
+// (btb/fp8.py:36-46, 97-100). e4m3 -> f16 is one conversion a pair; f16 -> f32 goes through the fma pipe
+// (fma.rn.f32.f16 with 1 and -0: exact, the sign of a zero kept) instead of the narrower conversion unit; the pair is
+// packed by one cvt.rn.bf16x2.f32.
+__device__ __forceinline__ uint32_t e4m3x2_held_pair(uint32_t two, float scale) {
+    uint32_t h, p;
+    float f0, f1;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"((unsigned short)(two & 0xffffu)));
+    asm("{\n.reg .b16 lo, hi, one;\nmov.b32 {lo, hi}, %2;\nmov.b16 one, 0x3C00;\nfma.rn.f32.f16 %0, lo, one, %3;\n"
+        "fma.rn.f32.f16 %1, hi, one, %3;\n}\n"
+        : "=f"(f0), "=f"(f1)
+        : "r"(h), "f"(-0.0f));
+    f0 = __fmul_rn(f0, scale);
+    f1 = __fmul_rn(f1, scale);
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(f1), "f"(f0));
+    return p;
+}
+
 // the butterfly every card reduction ends with (xor 16, 8, 4, 2, 1): the order is part of the result's bits
 __device__ __forceinline__ float warp_sum(float a) {
     a += __shfl_xor_sync(0xffffffffu, a, 16);

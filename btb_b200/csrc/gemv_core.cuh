@@ -54,12 +54,7 @@ __device__ __forceinline__ void fp8x2_held(uint32_t two, float scale, float& a, 
 __device__ __forceinline__ float act_silu(float g) { return g / (1.f + expf(-g)); }
 
 // the same, left as the packed bf16 pair (a in the low half): what the mixed-precision fma multiplies with
-__device__ __forceinline__ uint32_t fp8x2_held_pair(uint32_t two, float scale) {
-    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(two & 0xffffu), __NV_E4M3);
-    const __nv_bfloat162 p = __floats2bfloat162_rn(__fmul_rn(__half2float(__ushort_as_half(h.x)), scale),
-                                                   __fmul_rn(__half2float(__ushort_as_half(h.y)), scale));
-    return *reinterpret_cast<const uint32_t*>(&p);
-}
+__device__ __forceinline__ uint32_t fp8x2_held_pair(uint32_t two, float scale) { return e4m3x2_held_pair(two, scale); }
 
 // ---- pack12: eight weights of a chunk as four bf16 pairs ---------------------------------------------------------
 // lo: the chunk's 8 low bytes (two words), codes: its 8 nibbles (one word, element e in nibble e). The table's 16

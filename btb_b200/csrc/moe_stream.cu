@@ -73,6 +73,16 @@ __device__ __forceinline__ void fp4x4_bf16(uint32_t codes, uint32_t& p01, uint32
     p23 = __byte_perm(lb, hb, 0x7362u);
 }
 
+// x in shared memory: f32 [C], then bf16 [C] (C is a multiple of 32, so both start on 128 bytes)
+__host__ __device__ constexpr int x_smem_bytes(int C) { return (C * 6 + 127) & ~127; }
+
+// a packed bf16 pair times another, each product rounded to bf16 (subnormals kept)
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 template <int FMT>
 __host__ __device__ constexpr int col_bytes2() { return FMT == S_BF16 ? 4 : FMT == S_FP8 ? 2 : 1; }  // twice a column's bytes
 
@@ -91,7 +101,8 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
     const int sbytes = RB * stride;
     const int nseg = (C + seg - 1) / seg;
     float* xs = reinterpret_cast<float*>(smem);
-    const int xbytes = (C * 4 + 127) & ~127;
+    unsigned short* xh = reinterpret_cast<unsigned short*>(smem + (size_t)C * 4);  // x again as bf16, when it is bf16-valued
+    const int xbytes = x_smem_bytes(C);
     uint8_t* ring = smem + xbytes + (size_t)warp * S * sbytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + xbytes + (size_t)nw * S * sbytes) + warp * S;
 
@@ -157,15 +168,29 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
         const int first = min(S, n_items);
         for (int i = 0; i < first; ++i) issue_next();
     }
-    // x as f32 in shared memory, once a CTA
+    // x as f32 in shared memory, once a CTA - and, when every element is a bf16 value (the rows btb's experts are given
+    // are: the normed row widened, the gated activation rounded by its last torch op), as bf16 too: then the chains run
+    // on the mixed-precision fma (bf16 x bf16 + f32, one rounding: fmaf's bits) over half the shared-memory traffic
+    int inexact = 0;
     if (A.act_kind < 0) {
         const float4* xg = reinterpret_cast<const float4*>(A.x + (size_t)(task / A.x_div) * C);
-        for (int i = threadIdx.x; i < C / 4; i += blockDim.x) reinterpret_cast<float4*>(xs)[i] = __ldcg(xg + i);
+        for (int i = threadIdx.x; i < C / 4; i += blockDim.x) {
+            const float4 v = __ldcg(xg + i);
+            reinterpret_cast<float4*>(xs)[i] = v;
+            const uint32_t a = __float_as_uint(v.x), b = __float_as_uint(v.y), c = __float_as_uint(v.z), d = __float_as_uint(v.w);
+            inexact |= (int)((a | b | c | d) & 0xffffu);
+            reinterpret_cast<uint2*>(xh)[i] = make_uint2((a >> 16) | (b & 0xffff0000u), (c >> 16) | (d & 0xffff0000u));
+        }
     } else {
         const float* gu = A.x + (size_t)task * 2 * C;
-        for (int i = threadIdx.x; i < C; i += blockDim.x) xs[i] = moe_act_value(gu, i, C, A.act_kind, A.alpha, A.limit);
+        for (int i = threadIdx.x; i < C; i += blockDim.x) {
+            const float v = moe_act_value(gu, i, C, A.act_kind, A.alpha, A.limit);
+            xs[i] = v;
+            xh[i] = (unsigned short)(__float_as_uint(v) >> 16);
+        }
     }
-    __syncthreads();
+    const bool xbf = CPT > 1 && __syncthreads_or(inexact) == 0;
+    if (CPT == 1) __syncthreads();
 
     float acc[CPT];
 #pragma unroll
@@ -207,7 +232,96 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
         }
         const uint8_t* srowp = ring + (size_t)c_st * sbytes + (size_t)ri * stride;
         const float* xp = xs + c0;
-        if (FMT == S_FP8) {
+        if (xbf) {
+            const unsigned short* xb = xh + c0 + q * CPT;
+            if (FMT == S_FP8) {
+                const int bn = C / A.sc;
+                const int steps = n >> 4;
+                const bool staged = bn == 128 && (seg & 127) == 0 && seg <= 512;
+#pragma unroll 4
+                for (int s = 0; s < steps; ++s) {
+                    const float sc = staged ? fsc[(s * 16) >> 7]
+                                            : __ldg(reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride) +
+                                                    (size_t)((live ? r : 0) / (R / A.sr)) * A.sc + (c0 + s * 16) / bn);
+                    const uint8_t* wp = srowp + s * 16 + q * CPT;
+                    if (CPT == 4) {
+                        const uint32_t wb = *reinterpret_cast<const uint32_t*>(wp);
+                        const uint2 xv = *reinterpret_cast<const uint2*>(xb + s * 16);
+                        const uint32_t w01 = e4m3x2_held_pair(wb, sc), w23 = e4m3x2_held_pair(wb >> 16, sc);
+                        acc[0] = fma1_bf16<0, 0>(w01, xv.x, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(w01, xv.x, acc[1 % CPT]);
+                        acc[2 % CPT] = fma1_bf16<0, 0>(w23, xv.y, acc[2 % CPT]);
+                        acc[3 % CPT] = fma1_bf16<1, 1>(w23, xv.y, acc[3 % CPT]);
+                    } else {
+                        const uint32_t w01 = e4m3x2_held_pair(*reinterpret_cast<const unsigned short*>(wp), sc);
+                        const uint32_t xv = *reinterpret_cast<const uint32_t*>(xb + s * 16);
+                        acc[0] = fma1_bf16<0, 0>(w01, xv, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(w01, xv, acc[1 % CPT]);
+                    }
+                }
+            } else if (FMT == S_MX4) {
+                const int nb = n >> 5;
+                constexpr int SPT = TPR >= 16 ? 1 : 16 / TPR >= 4 ? 4 : 16 / TPR;
+#pragma unroll 4
+                for (int b = 0; b < nb; ++b) {
+                    const unsigned pk = __shfl_sync(0xffffffffu, mxs, (lane / TPR) * TPR + b / SPT);
+                    // 2^(s - 127) as a bf16 pair: an e2m1 value times it is exact in bf16 (two significant bits, and the
+                    // smallest product, 2^-128, is a bf16 subnormal), so the packed multiply gives the f32 product's value
+                    const uint32_t sb = (pk >> ((b % SPT) * 8)) & 255u;
+                    const uint32_t s1 = sb != 0u ? sb << 7 : 0x0040u;
+                    const uint32_t sc2 = s1 | (s1 << 16);
+                    const uint8_t* bp = srowp + b * 16;
+                    const unsigned short* xa = xb + b * 32;
+                    if (CPT == 4) {
+                        const unsigned lo = *reinterpret_cast<const unsigned short*>(bp + q * 2);
+                        const unsigned hi = *reinterpret_cast<const unsigned short*>(bp + 8 + q * 2);
+                        const uint2 va = *reinterpret_cast<const uint2*>(xa), vb = *reinterpret_cast<const uint2*>(xa + 16);
+                        uint32_t a01, a23, b01, b23;
+                        fp4x4_bf16(lo, a01, a23);
+                        fp4x4_bf16(hi, b01, b23);
+                        a01 = mul_bf16x2(a01, sc2), a23 = mul_bf16x2(a23, sc2);
+                        b01 = mul_bf16x2(b01, sc2), b23 = mul_bf16x2(b23, sc2);
+                        acc[0] = fma1_bf16<0, 0>(a01, va.x, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(a01, va.x, acc[1 % CPT]);
+                        acc[2 % CPT] = fma1_bf16<0, 0>(a23, va.y, acc[2 % CPT]);
+                        acc[3 % CPT] = fma1_bf16<1, 1>(a23, va.y, acc[3 % CPT]);
+                        acc[0] = fma1_bf16<0, 0>(b01, vb.x, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(b01, vb.x, acc[1 % CPT]);
+                        acc[2 % CPT] = fma1_bf16<0, 0>(b23, vb.y, acc[2 % CPT]);
+                        acc[3 % CPT] = fma1_bf16<1, 1>(b23, vb.y, acc[3 % CPT]);
+                    } else {
+                        const unsigned codes = (unsigned)bp[q] | ((unsigned)bp[8 + q] << 8);
+                        const uint32_t va = *reinterpret_cast<const uint32_t*>(xa), vb = *reinterpret_cast<const uint32_t*>(xa + 16);
+                        uint32_t a01, b01;
+                        fp4x4_bf16(codes, a01, b01);
+                        a01 = mul_bf16x2(a01, sc2), b01 = mul_bf16x2(b01, sc2);
+                        acc[0] = fma1_bf16<0, 0>(a01, va, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(a01, va, acc[1 % CPT]);
+                        acc[0] = fma1_bf16<0, 0>(b01, vb, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(b01, vb, acc[1 % CPT]);
+                    }
+                }
+            } else {
+                const int steps = n >> 4;
+#pragma unroll 4
+                for (int s = 0; s < steps; ++s) {
+                    const uint8_t* wp = srowp + s * 32 + q * CPT * 2;
+                    if (CPT == 4) {
+                        const uint2 wb = *reinterpret_cast<const uint2*>(wp);
+                        const uint2 xv = *reinterpret_cast<const uint2*>(xb + s * 16);
+                        acc[0] = fma1_bf16<0, 0>(wb.x, xv.x, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(wb.x, xv.x, acc[1 % CPT]);
+                        acc[2 % CPT] = fma1_bf16<0, 0>(wb.y, xv.y, acc[2 % CPT]);
+                        acc[3 % CPT] = fma1_bf16<1, 1>(wb.y, xv.y, acc[3 % CPT]);
+                    } else {
+                        const uint32_t wb = *reinterpret_cast<const uint32_t*>(wp);
+                        const uint32_t xv = *reinterpret_cast<const uint32_t*>(xb + s * 16);
+                        acc[0] = fma1_bf16<0, 0>(wb, xv, acc[0]);
+                        acc[1 % CPT] = fma1_bf16<1, 1>(wb, xv, acc[1 % CPT]);
+                    }
+                }
+            }
+        } else if (FMT == S_FP8) {
             const int bn = C / A.sc;
             const int steps = n >> 4;
 #pragma unroll 4
@@ -366,7 +480,7 @@ bool plan_stream(int n_tasks, int R, int C, MSPlan& p) {
         const int rounds = (per_cta + p.warps - 1) / p.warps;
         p.warps = max(4, (per_cta + rounds - 1) / rounds);
     }
-    const int xbytes = (C * 4 + 127) & ~127;
+    const int xbytes = x_smem_bytes(C);
     const int budget = (per_sm == 1 ? 200 : 104) * 1024 - xbytes;
     const B2Tuning& t = b2_tuning();
     if (t.ms_warps > 0) p.warps = min(MAXW, t.ms_warps);

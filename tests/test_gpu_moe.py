@@ -114,6 +114,34 @@ def test_mx4_lane16_every_byte_every_scale():
         assert np.array_equal(got[fin].view(np.uint32) & 0x7FFFFFFF, ref[fin].view(np.uint32) & 0x7FFFFFFF)
 
 
+def test_fp8_stream_every_byte_many_scales():
+    """all 256 e4m3 bytes under scales of every size and sign through the streaming kernel's widen, on the mixed-precision
+    path (x = 1 at one column isolates a weight): the held bf16 the reference's codec makes, to the bit"""
+    scales = np.asarray([1.0, -1.0, 0.0123, 3.3e-5, 7e-20, 1.7e-38, 9.1e-41, 448.0, 2.0**100, 3e36, -6.02e-3, 0.33333334],
+                        np.float32)  # fmt: skip
+    S, C_ = len(scales), 32
+    R = 256 * S
+    w = np.zeros((R, C_), np.uint8)
+    w[:, :] = 0x38  # 1.0 elsewhere: finite
+    byte = np.tile(np.arange(256, dtype=np.uint8), S)
+    sc = np.repeat(scales, 256).reshape(R, 1)
+    for col in (0, 3, 18):
+        ww = w.copy()
+        ww[:, col] = byte
+        full = O.bits_to_f32(O.widen_fp8(ww, sc, R, C_))
+        want = full[:, col]
+        x = np.zeros((1, C_), np.float32)
+        x[0, col] = 1.0
+        wt, st_, xt = torch.from_numpy(ww).to(DEV), torch.from_numpy(sc).to(DEV), torch.from_numpy(x).to(DEV)
+        y = torch.zeros(1, R, dtype=torch.float32, device=DEV)
+        call("btb_b200_moe_gemv", 2, ptr(wt), ptr(st_), 0, 0, R, 1, 0, 1, 1, ptr(xt), 1, ptr(y), R, C_, 0, 1, s())
+        got = y.cpu().numpy()[0]
+        fin = np.isfinite(full).all(axis=1)
+        assert fin.sum() > 240 * S
+        assert np.array_equal((got[fin] + np.float32(0)).view(np.uint32), (want[fin] + np.float32(0)).view(np.uint32))
+        assert np.isnan(got[np.isnan(want)]).all()
+
+
 @pytest.mark.parametrize("kind", [0, 1])
 def test_act_and_combine(kind):
     rng = np.random.default_rng(kind)
@@ -208,12 +236,19 @@ def test_verify_rows_equal_steps_in_a_moe_model():
 @pytest.mark.parametrize("R,C_,n,k", [(1536, 2048, 8, 8), (2048, 768, 8, 1), (5760, 2880, 4, 4), (2880, 2880, 4, 1),
                                       (300, 2880, 5, 1), (13, 96, 3, 3), (64, 128, 40, 8), (8, 32, 1, 1)])  # fmt: skip
 @pytest.mark.parametrize("fmt", ["bf16", "mx4", "fp8"])
-def test_expert_gemv_stream_equals_the_cpu_tier_bits(R, C_, n, k, fmt):
-    """task i multiplies expert idx[i] with x row i // x_div: every output the oracle's 16-lane sum to the bit"""
+@pytest.mark.parametrize("xbf", [False, True])
+def test_expert_gemv_stream_equals_the_cpu_tier_bits(R, C_, n, k, fmt, xbf):
+    """task i multiplies expert idx[i] with x row i // x_div: every output the oracle's 16-lane sum to the bit - for any
+    f32 x, and for an x of bf16 values (what the engine's experts are given), which the kernel multiplies on the
+    mixed-precision fma"""
     rng = np.random.default_rng(R + C_ + n)
     E = 6
     idx = rng.integers(0, E, size=n).astype(np.int32)
     x = rng.standard_normal(((n + k - 1) // k, C_)).astype(np.float32)
+    if xbf:
+        x = O.bfround(x * np.float32(3.0))
+        x[0, : min(8, C_)] = np.asarray([0.0, -0.0, 1e-38, -3e38, 2.0**-130, 1.0, -1.0, 65280.0], np.float32)[: min(8, C_)]
+        x = O.bfround(x)
     xt, it = torch.from_numpy(x).to(DEV), torch.from_numpy(idx).to(DEV)
     y = torch.full((n, R), 7.0, dtype=torch.float32, device=DEV)
     if fmt == "bf16":
