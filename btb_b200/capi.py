@@ -63,6 +63,8 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_add_rmsnorm_wide": (_I, [_P, _P, _P, _F, _P, _P, _I, _I, _I, _P]),
     "btb_b200_silu_mul": (_I, [_P, _P, _I, _I, _P]),
     "btb_b200_norm_rope_kv": (_I, [_P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _I, _P, _I, _P]),
+    "btb_b200_norm_rope_kv_rows": (_I, [_P, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _I, _I, _P]),
+    "btb_b200_attn_decode_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _F, _P, _P, _P, _P, _I, _P, _I, _P]),
     "btb_b200_attn_decode": (
         _I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _LL, _LL, _F, _P, _P, _P, _P, _I, _P, _P, _I, _P],
     ),

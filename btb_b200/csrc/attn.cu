@@ -156,9 +156,10 @@ extern "C" size_t btb_b200_attn_scratch_floats(int S, int T, int Hq, int D) {
 static int attn_decode_impl(const void* q, const void* K, const void* V, void* out, const void* n0p,
                                     const void* par, int T, int Hq, int Hk, int D, long long hs, long long rs,
                                     float scale, void* part_m, void* part_l, void* part_acc, void* cnt, int win,
-                                    const void* tbl, const void* sinks, int cap, const btb_b200_send* send, void* stream) {
+                                    const void* tbl, const void* sinks, int cap, const btb_b200_send* send, void* stream,
+                                    const void* rw = nullptr) {
     const bool sends = send != nullptr && send->n != 0;
-    if (!q || !K || !V || (!out && !sends) || !n0p || !par || !part_m || !part_l || !part_acc || !cnt) return B2_ERR_NULL;
+    if (!q || !K || !V || (!out && !sends) || (!rw && (!n0p || !par)) || !part_m || !part_l || !part_acc || !cnt) return B2_ERR_NULL;
     if (T <= 0 || T > TMAX || Hk <= 0 || Hq <= 0 || Hq % Hk || (Hq / Hk != 1 && Hq / Hk != 2 && Hq / Hk != 4 && Hq / Hk != 8) || cap <= 0 || !(scale == scale))
         return B2_ERR_DOMAIN;
     // a key row is read as 16-byte chunks, a value row as D/32-element runs
@@ -168,6 +169,7 @@ static int attn_decode_impl(const void* q, const void* K, const void* V, void* o
     a.q = static_cast<const bf16*>(q), a.K = static_cast<const bf16*>(K), a.V = static_cast<const bf16*>(V);
     a.out = static_cast<bf16*>(out), a.n0p = static_cast<const int*>(n0p), a.par = static_cast<const int*>(par);
     a.tbl = static_cast<const int*>(tbl), a.sinks = static_cast<const float*>(sinks);
+    a.rw = static_cast<const int*>(rw);
     a.part_m = static_cast<float*>(part_m), a.part_l = static_cast<float*>(part_l);
     a.part_acc = static_cast<float*>(part_acc), a.cnt = static_cast<int*>(cnt);
     a.scale = scale, a.T = T, a.Hq = Hq, a.Hk = Hk, a.win = win, a.cap = cap, a.hs = hs, a.rs = rs;
@@ -188,6 +190,17 @@ extern "C" int btb_b200_attn_decode(const void* q, const void* K, const void* V,
                                     const void* tbl, const void* sinks, int cap, void* stream) {
     return attn_decode_impl(q, K, V, out, n0p, par, T, Hq, Hk, D, hs, rs, scale, part_m, part_l, part_acc, cnt, win, tbl,
                             sinks, cap, nullptr, stream);
+}
+
+// the rows layout: row t a sequence of its own - its prefix, then its own steps - read in logical order, the order a
+// one-row step of that sequence alone reads them in, so a row's bits are its own decode's whatever rows step beside it
+extern "C" int btb_b200_attn_decode_rows(const void* q, const void* K, const void* V, void* out, const void* rw, int T,
+                                         int Hq, int Hk, int D, long long hs, long long rs, float scale, void* part_m,
+                                         void* part_l, void* part_acc, void* cnt, int win, const void* sinks, int cap,
+                                         void* stream) {
+    if (!rw) return B2_ERR_NULL;
+    return attn_decode_impl(q, K, V, out, nullptr, nullptr, T, Hq, Hk, D, hs, rs, scale, part_m, part_l, part_acc, cnt, win,
+                            nullptr, sinks, cap, nullptr, stream, rw);
 }
 
 // btb_b200_attn_decode in a model cut over ranks by kv head: the output rows go, marked, to every rank's copy
@@ -229,7 +242,7 @@ static int attn_step_launch(const void* qkv, const void* wq, const void* wk, flo
     a.scale = scale, a.T = 1, a.Hq = Hq, a.Hk = Hk, a.win = win, a.cap = cap, a.hs = hs, a.rs = rs;
     sa.r = RopeArgs{static_cast<const bf16*>(qkv), static_cast<const bf16*>(wq), static_cast<const bf16*>(wk),
                     static_cast<const bf16*>(cos_t), static_cast<const bf16*>(sin_t), static_cast<const int*>(n0p),
-                    static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),
+                    static_cast<const int*>(depth), static_cast<const int*>(tbl), nullptr, static_cast<bf16*>(K),
                     static_cast<bf16*>(V), static_cast<bf16*>(q), eps, 1, Hq, Hk, centered, hs, rs, cap};
     if (const int rc = take_send(send, Hq, D, a.send)) return rc;
     const int S = (cap + GK - 1) / GK;

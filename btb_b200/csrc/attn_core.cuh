@@ -33,6 +33,20 @@ __device__ __forceinline__ float fold_e(float O, float o, float cO, float co) {
     return __fmaf_rn(o, co, __fmul_rn(O, cO));
 }
 
+// The rows layout (native/cuda/btb_kernels.cu:228-248 of btb): a pass's T rows as T sequences a token each - a fork's
+// rows or a batch's - each at its own position. One int32 array on the card: [base, step, W, then (col, off, len) a row].
+// Row t's keys in logical order are its prefix - `len` cache rows from `off` (forks share one prefix) - and then its own
+// steps, step i at cache row base + i * W + col (every row's step i in one stretch of W rows). len < 0: padding, the
+// row computes nothing.
+struct RowSeq {
+    int base, step, W, col, off, len;
+    __device__ __forceinline__ RowSeq(const int* rw, int t, bool on = true)
+        : base(on ? rw[0] : 0), step(on ? rw[1] : 0), W(on ? rw[2] : 0), col(on ? rw[3 + 3 * t] : 0),
+          off(on ? rw[4 + 3 * t] : 0), len(on ? rw[5 + 3 * t] : 0) {}
+    __device__ __forceinline__ int slot(int j) const { return j < len ? off + j : base + (j - len) * W + col; }
+    __device__ __forceinline__ int position() const { return len + step; }  // of the token this pass adds
+};
+
 struct AttnArgs {
     const bf16* q;    // [T, Hq, D]
     const bf16* K;    // head g, slot j at g * hs + j * rs
@@ -41,6 +55,7 @@ struct AttnArgs {
     const int* n0p;   // rows standing before the pass
     const int* par;   // [T] parents, -1 the root
     const int* tbl;   // logical slot -> cache row, or null
+    const int* rw;    // the rows layout (RowSeq), or null; with it n0p, par and tbl are not read
     const float* sinks;  // [Hq] a logit joined to the denominator, or null
     float* part_m;    // [S, T, Hq]
     float* part_l;
@@ -158,7 +173,7 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = warp >> 1, half = warp & 1;
     const int Hq = A.Hq, Hk = A.Hk, T = A.T;
-    const int n0 = COHERENT ? __ldcg(A.n0p) : *A.n0p;
+    const int n0 = A.rw != nullptr ? 0 : (COHERENT ? __ldcg(A.n0p) : *A.n0p);
 
     __shared__ int anc[TMAX];  // token t's path, root first
     __shared__ int s_len;
@@ -166,7 +181,10 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
     AttnSmem<D, G>& sm = *reinterpret_cast<AttnSmem<D, G>*>(dsm_raw);
 
     __syncthreads();  // the block's previous item is done with the shared state
-    if (threadIdx.x == 0) {
+    const bool rows = A.rw != nullptr;
+    RowSeq rp(rows ? A.rw : nullptr, rows ? t : 0, rows);
+    if (rows && rp.len < 0) return;  // padding
+    if (threadIdx.x == 0 && !rows) {
         int len = 0;
         for (int p = t; p >= 0 && p < T && len < TMAX; p = A.par[p]) ++len;
         int k = len;
@@ -174,11 +192,11 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
         s_len = len;
     }
     __syncthreads();
-    const int last = n0 + s_len - 1;
+    const int last = rows ? rp.position() : n0 + s_len - 1;
     const int first = A.win > 0 ? max(last + 1 - A.win, 0) : 0;
     const int lo = grp * GK, hi = lo + GK - 1;
-    if (lo > last || hi < first || last >= A.cap) {
-        if (last >= A.cap && threadIdx.x == 0 && grp == 0) b2_fail(B2_ERR_DOMAIN);
+    if (lo > last || hi < first || (!rows && last >= A.cap)) {
+        if (!rows && last >= A.cap && threadIdx.x == 0 && grp == 0) b2_fail(B2_ERR_DOMAIN);
         return;  // the group holds none of the row's keys: nothing stored, nothing counted
     }
     for (int i = threadIdx.x; i < G * D; i += NWA * 32) {
@@ -196,9 +214,17 @@ __device__ __forceinline__ void attn_item(const AttnArgs& A, int grp, int g, int
     const int j = lo + tile * BN + half * 32 + lane;
     int row = -1;
     if (j >= first && j <= last) {
-        int sl = j < n0 ? j : n0 + anc[j - n0];
-        if (A.tbl != nullptr) sl = A.tbl[sl];
-        row = sl;
+        if (rows) {
+            row = rp.slot(j);
+            if (row < 0 || row >= A.cap) {  // a layout that points outside the cache: refused, the key not read
+                b2_fail(B2_ERR_DOMAIN);
+                row = -1;
+            }
+        } else {
+            int sl = j < n0 ? j : n0 + anc[j - n0];
+            if (A.tbl != nullptr) sl = A.tbl[sl];
+            row = sl;
+        }
     }
     float s[G];
     {
@@ -302,6 +328,7 @@ struct RopeArgs {
     const int* n0p;
     const int* depth;
     const int* tbl;
+    const int* rw;  // the rows layout (RowSeq), or null; with it n0p, depth and tbl are not read
     bf16* K;
     bf16* V;
     bf16* qo;
@@ -373,14 +400,22 @@ __device__ __forceinline__ void rope_values(const RopeArgs& A, int head, int t, 
 template <int D, bool COHERENT>
 __device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, int lane) {
     constexpr int E = D / 32;
-    const int n0 = COHERENT ? __ldcg(A.n0p) : *A.n0p;
-    int slot = n0 + t;
-    const int pos = n0 + A.depth[t];
+    int slot, pos;
+    if (A.rw != nullptr) {
+        const RowSeq rp(A.rw, t);
+        if (rp.len < 0) return;  // padding
+        pos = rp.position();
+        slot = rp.slot(pos);
+    } else {
+        const int n0 = COHERENT ? __ldcg(A.n0p) : *A.n0p;
+        slot = n0 + t;
+        pos = n0 + A.depth[t];
+    }
     if (slot < 0 || slot >= A.cap || pos < 0 || pos >= A.cap) {
         if (lane == 0) b2_fail(B2_ERR_DOMAIN);
         return;
     }
-    if (A.tbl != nullptr) slot = A.tbl[slot];
+    if (A.rw == nullptr && A.tbl != nullptr) slot = A.tbl[slot];
     const int Hq = A.Hq, Hk = A.Hk;
     bf16 o[E];
     rope_values<D, COHERENT>(A, head, t, lane, pos, o);

@@ -271,7 +271,7 @@ extern "C" int btb_b200_attn_o_step(const void* qkv, const void* wq, const void*
     a.scale = scale, a.T = 1, a.Hq = Hq, a.Hk = Hk, a.win = win, a.cap = cap, a.hs = hs, a.rs = rs;
     A.r = RopeArgs{static_cast<const bf16*>(qkv), static_cast<const bf16*>(wq), static_cast<const bf16*>(wk),
                    static_cast<const bf16*>(cos_t), static_cast<const bf16*>(sin_t), static_cast<const int*>(n0p),
-                   static_cast<const int*>(depth), nullptr, static_cast<bf16*>(K), static_cast<bf16*>(V),
+                   static_cast<const int*>(depth), nullptr, nullptr, static_cast<bf16*>(K), static_cast<bf16*>(V),
                    static_cast<bf16*>(q), eps, 1, Hq, Hk, centered, hs, rs, cap};
     A.w = static_cast<const uint8_t*>(w_o), A.y = static_cast<bf16*>(y), A.R = R, A.C = Hq * D;
     A.S = (cap + GK - 1) / GK;

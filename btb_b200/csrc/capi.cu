@@ -58,6 +58,10 @@ extern "C" int btb_b200_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "x_direct")) t.x_direct = value != 0;
     else if (!strcmp(key, "l2_warm_kb")) t.l2_warm_kb = value < 0 ? 0 : value;
     else if (!strcmp(key, "l2_warm_ctas")) t.l2_warm_ctas = value < 0 ? 0 : value;
+    else if (!strcmp(key, "ms_tpr")) t.ms_tpr = value;
+    else if (!strcmp(key, "ms_ctas")) t.ms_ctas = value < 0 ? 0 : value;
+    else if (!strcmp(key, "ms_seg")) t.ms_seg = value < 0 ? 0 : value & ~31;
+    else if (!strcmp(key, "ms_warps")) t.ms_warps = value < 0 ? 0 : value;
     else return B2_ERR_DOMAIN;
     return B2_OK;
 }

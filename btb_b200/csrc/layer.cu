@@ -337,11 +337,11 @@ extern "C" int btb_b200_silu_mul(const void* gu, void* m, int T, int I, void* st
     return b2_launch((const void*)silu_mul, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), a);
 }
 
-extern "C" int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
-                                     const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
-                                     int T, int Hq, int Hk, int D, long long hs, long long rs, int centered,
-                                     const void* tbl, int cap, void* stream) {
-    if (!qkv || !cos_t || !sin_t || !n0p || !depth || !K || !V || !q) return B2_ERR_NULL;
+static int norm_rope_kv_impl(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                             const void* sin_t, const void* n0p, const void* depth, const void* rw, void* K, void* V,
+                             void* q, int T, int Hq, int Hk, int D, long long hs, long long rs, int centered,
+                             const void* tbl, int cap, void* stream) {
+    if (!qkv || !cos_t || !sin_t || (!rw && (!n0p || !depth)) || !K || !V || !q) return B2_ERR_NULL;
     if (T <= 0 || Hq <= 0 || Hk <= 0 || cap <= 0) return B2_ERR_DOMAIN;
     // a lane reads its D/32 elements of a head, a norm weight or a table row as one load
     if ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(wk) |
@@ -351,8 +351,8 @@ extern "C" int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void
     if ((hs & 7) || (rs & 7)) return B2_ERR_DOMAIN;
     RopeArgs a{static_cast<const bf16*>(qkv), static_cast<const bf16*>(wq), static_cast<const bf16*>(wk),
                static_cast<const bf16*>(cos_t), static_cast<const bf16*>(sin_t), static_cast<const int*>(n0p),
-               static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<bf16*>(K),
-               static_cast<bf16*>(V), static_cast<bf16*>(q), eps, T, Hq, Hk, centered, hs, rs, cap};
+               static_cast<const int*>(depth), static_cast<const int*>(tbl), static_cast<const int*>(rw),
+               static_cast<bf16*>(K), static_cast<bf16*>(V), static_cast<bf16*>(q), eps, T, Hq, Hk, centered, hs, rs, cap};
     const dim3 grid(Hq + 2 * Hk, T);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (D) {
@@ -361,6 +361,23 @@ extern "C" int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void
         case 256: return b2_launch((const void*)norm_rope_kv<256>, grid, dim3(32), 0, s, a);
         default: return B2_ERR_DOMAIN;
     }
+}
+
+extern "C" int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                     const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q,
+                                     int T, int Hq, int Hk, int D, long long hs, long long rs, int centered,
+                                     const void* tbl, int cap, void* stream) {
+    return norm_rope_kv_impl(qkv, wq, wk, eps, cos_t, sin_t, n0p, depth, nullptr, K, V, q, T, Hq, Hk, D, hs, rs, centered,
+                             tbl, cap, stream);
+}
+
+// the rows layout: row t a sequence of its own, its token at position len + step, written to its step's cache row
+extern "C" int btb_b200_norm_rope_kv_rows(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                                          const void* sin_t, const void* rw, void* K, void* V, void* q, int T, int Hq,
+                                          int Hk, int D, long long hs, long long rs, int centered, int cap, void* stream) {
+    if (!rw) return B2_ERR_NULL;
+    return norm_rope_kv_impl(qkv, wq, wk, eps, cos_t, sin_t, nullptr, nullptr, rw, K, V, q, T, Hq, Hk, D, hs, rs, centered,
+                             nullptr, cap, stream);
 }
 
 extern "C" int btb_b200_argmax_bf16(const void* logits, int T, int V, void* scratch, void* out, void* stream) {

@@ -10,6 +10,8 @@
 // bulk copy a row segment into a per-warp ring (rows padded by 16 bytes, so the eight rows' words fall in distinct
 // banks); x is staged once a CTA as f32. Every weight byte is read from DRAM once, in large transfers - the
 // per-column byte loads of the plain 16-lane kernel ran at a twentieth of the memory's rate.
+#include <cuda_fp16.h>
+#include <type_traits>
 #include <cuda_fp8.h>
 
 #include "btb_b200_internal.h"
@@ -21,6 +23,21 @@ B2_DEFINE_STATUS(moes)
 namespace {
 
 enum { S_BF16 = 0, S_MX4 = 1, S_FP8 = 2 };
+// f(0), f(1), ... f(N - 1) with the index a compile-time constant (offsets and shifts become immediates)
+template <int N>
+struct Unrolled {
+    template <class F>
+    static __device__ __forceinline__ void run(F&& f) {
+        Unrolled<N - 1>::run(f);
+        f(std::integral_constant<int, N - 1>{});
+    }
+};
+template <>
+struct Unrolled<0> {
+    template <class F>
+    static __device__ __forceinline__ void run(F&&) {}
+};
+
 constexpr int PAD = 16;     // bytes between the rows of a stage
 constexpr int MAXW = 16;    // warps a CTA at most
 
@@ -59,29 +76,111 @@ __device__ __forceinline__ float moe_act_value(const float* gu, int c, int I, in
     return bfround(bfround(u + 1.f) * glu);
 }
 
-// four e2m1 codes (the nibbles of `codes`, lowest first) as two bf16 pairs: p01 = (value 0 | value 1 << 16), p23 alike.
-// A value's bf16 pattern is two table bytes: the high byte out of eight by the code's low three bits, from the
-// positive or the negative table by its top bit, the low byte out of eight - byte permutes, no arithmetic.
-__device__ __forceinline__ void fp4x4_bf16(uint32_t codes, uint32_t& p01, uint32_t& p23) {
-    const uint32_t s7 = codes & 0x7777u;
-    const uint32_t pick = 0x3210u | ((codes & 0x8888u) >> 1);
-    const uint32_t hp = __byte_perm(0x3F3F3F00u, 0x40404040u, s7);  // 0, .5, 1, 1.5 | 2, 3, 4, 6: high bytes
-    const uint32_t hn = __byte_perm(0xBFBFBF80u, 0xC0C0C0C0u, s7);  // the same with the sign
-    const uint32_t hb = __byte_perm(hp, hn, pick);
-    const uint32_t lb = __byte_perm(0xC0800000u, 0xC0804000u, s7);  // low bytes
-    p01 = __byte_perm(lb, hb, 0x5140u);
-    p23 = __byte_perm(lb, hb, 0x7362u);
+// Four e4m3 weights (the bytes of wb, lowest first) under one block scale against four bf16 x (two packed pairs), each
+// product into its own chain: e4m3 -> f16 (exact) -> f32 through the fma pipe -> times the scale -> the nearest bf16 (the
+// weight btb holds) -> bf16 x bf16 + f32 with one rounding. One block of PTX, so that every 16-bit half is named where
+// it lies.
+__device__ __forceinline__ void fp8_step4(uint32_t wb, uint32_t x01, uint32_t x23, float sc, float& a0, float& a1,
+                                          float& a2, float& a3) {
+    asm("{\n"
+        ".reg .b16 w0, w1, a, b, c, d, one, pa, pb, pc, pd, xa, xb, xc, xd;\n"
+        ".reg .b32 h01, h23, p01, p23;\n"
+        ".reg .f32 f0, f1, f2, f3;\n"
+        "mov.b32 {w0, w1}, %4;\n"
+        "cvt.rn.f16x2.e4m3x2 h01, w0;\n"
+        "cvt.rn.f16x2.e4m3x2 h23, w1;\n"
+        "mov.b32 {a, b}, h01;\n"
+        "mov.b32 {c, d}, h23;\n"
+        "mov.b16 one, 0x3C00;\n"
+        "fma.rn.f32.f16 f0, a, one, %8;\n"
+        "fma.rn.f32.f16 f1, b, one, %8;\n"
+        "fma.rn.f32.f16 f2, c, one, %8;\n"
+        "fma.rn.f32.f16 f3, d, one, %8;\n"
+        "mul.rn.f32 f0, f0, %7;\n"
+        "mul.rn.f32 f1, f1, %7;\n"
+        "mul.rn.f32 f2, f2, %7;\n"
+        "mul.rn.f32 f3, f3, %7;\n"
+        "cvt.rn.bf16x2.f32 p01, f1, f0;\n"
+        "cvt.rn.bf16x2.f32 p23, f3, f2;\n"
+        "mov.b32 {pa, pb}, p01;\n"
+        "mov.b32 {pc, pd}, p23;\n"
+        "mov.b32 {xa, xb}, %5;\n"
+        "mov.b32 {xc, xd}, %6;\n"
+        "fma.rn.f32.bf16 %0, pa, xa, %0;\n"
+        "fma.rn.f32.bf16 %1, pb, xb, %1;\n"
+        "fma.rn.f32.bf16 %2, pc, xc, %2;\n"
+        "fma.rn.f32.bf16 %3, pd, xd, %3;\n"
+        "}\n"
+        : "+f"(a0), "+f"(a1), "+f"(a2), "+f"(a3)
+        : "r"(wb), "r"(x01), "r"(x23), "f"(sc), "f"(-0.0f));
+}
+
+// two bytes of e2m1 codes (four codes, the lowest nibble first) as two f16 pairs through the conversion unit
+__device__ __forceinline__ void e2m1x4_f16x2(uint32_t two_bytes, uint32_t& h01, uint32_t& h23) {
+    asm("{\n.reg .b8 b0, b1;\n.reg .b16 t;\ncvt.u16.u32 t, %2;\nmov.b16 {b0, b1}, t;\ncvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\n}"
+        : "=r"(h01), "=r"(h23)
+        : "r"(two_bytes));
+}
+// an f16 pair times the f16 value p, as two f32 (exact: the mixed-precision fma's product is not rounded before the sum,
+// and the addend is -0, which keeps a zero's sign)
+__device__ __forceinline__ void f16x2_times(uint32_t h, unsigned short p, float& f0, float& f1) {
+    asm("{\n.reg .b16 lo, hi;\nmov.b32 {lo, hi}, %2;\nfma.rn.f32.f16 %0, lo, %3, %4;\nfma.rn.f32.f16 %1, hi, %3, %4;\n}"
+        : "=f"(f0), "=f"(f1)
+        : "r"(h), "h"(p), "f"(-0.0f));
+}
+// One MXFP4 block's share of a thread: its CPT columns of the block's first sixteen and of its last sixteen. The weight is
+// code x 2^(s - 127). FAST: the scale is an f16 value (2^-24 .. 2^15, subnormals included), so the widen f16 -> f32 and
+// the scale are ONE mixed-precision fma, exact; else the widen multiplies by 1 and an f32 multiply (exact too, or
+// overflowing as the reference's does) follows.
+template <int CPT, bool FAST>
+__device__ __forceinline__ void mx4_block(const uint8_t* bp, int q, const float* xa, unsigned short ph, float pf, float* acc) {
+    const unsigned short mul = FAST ? ph : (unsigned short)0x3C00;
+    if (CPT == 4) {
+        const uint32_t lo = *reinterpret_cast<const unsigned short*>(bp + q * 2);
+        const uint32_t hi = *reinterpret_cast<const unsigned short*>(bp + 8 + q * 2);
+        const float4 va = *reinterpret_cast<const float4*>(xa), vb = *reinterpret_cast<const float4*>(xa + 16);
+        uint32_t a01, a23, b01, b23;
+        e2m1x4_f16x2(lo, a01, a23);
+        e2m1x4_f16x2(hi, b01, b23);
+        float w[8];
+        f16x2_times(a01, mul, w[0], w[1]);
+        f16x2_times(a23, mul, w[2], w[3]);
+        f16x2_times(b01, mul, w[4], w[5]);
+        f16x2_times(b23, mul, w[6], w[7]);
+        if (!FAST) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) w[u] = __fmul_rn(w[u], pf);
+        }
+        acc[0] = fmaf(w[0], va.x, acc[0]);
+        acc[1 % CPT] = fmaf(w[1], va.y, acc[1 % CPT]);
+        acc[2 % CPT] = fmaf(w[2], va.z, acc[2 % CPT]);
+        acc[3 % CPT] = fmaf(w[3], va.w, acc[3 % CPT]);
+        acc[0] = fmaf(w[4], vb.x, acc[0]);
+        acc[1 % CPT] = fmaf(w[5], vb.y, acc[1 % CPT]);
+        acc[2 % CPT] = fmaf(w[6], vb.z, acc[2 % CPT]);
+        acc[3 % CPT] = fmaf(w[7], vb.w, acc[3 % CPT]);
+    } else {
+        const uint32_t codes = (uint32_t)bp[q] | ((uint32_t)bp[8 + q] << 8);
+        const float2 va = *reinterpret_cast<const float2*>(xa), vb = *reinterpret_cast<const float2*>(xa + 16);
+        uint32_t a01, b01;
+        e2m1x4_f16x2(codes, a01, b01);  // the first half's two columns, then the second half's
+        float w[4];
+        f16x2_times(a01, mul, w[0], w[1]);
+        f16x2_times(b01, mul, w[2], w[3]);
+        if (!FAST) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) w[u] = __fmul_rn(w[u], pf);
+        }
+        acc[0] = fmaf(w[0], va.x, acc[0]);
+        acc[1 % CPT] = fmaf(w[1], va.y, acc[1 % CPT]);
+        acc[0] = fmaf(w[2], vb.x, acc[0]);
+        acc[1 % CPT] = fmaf(w[3], vb.y, acc[1 % CPT]);
+    }
 }
 
 // x in shared memory: f32 [C], then bf16 [C] (C is a multiple of 32, so both start on 128 bytes)
 __host__ __device__ constexpr int x_smem_bytes(int C) { return (C * 6 + 127) & ~127; }
-
-// a packed bf16 pair times another, each product rounded to bf16 (subnormals kept)
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
 
 template <int FMT>
 __host__ __device__ constexpr int col_bytes2() { return FMT == S_BF16 ? 4 : FMT == S_FP8 ? 2 : 1; }  // twice a column's bytes
@@ -151,12 +250,17 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
         const int rows = min(RB, R - p_grp * RB);
         const uint32_t nb = (uint32_t)(n * CB2 / 2);
         const uint32_t bar = smem_u32(bars + p_st);
-        if (lane == 0) mbar_expect_tx(bar, nb * rows);
-        __syncwarp();
-        if (lane < rows) {
-            const uint8_t* src = wbase + (size_t)(p_grp * RB + lane) * row_bytes + (size_t)c0 * CB2 / 2;
-            bulk_g2s_hint(smem_u32(ring + (size_t)p_st * sbytes + (size_t)lane * stride), src, nb, bar, pol);
+        // one lane issues the group's copies in a straight line (a copy a lane cost a serialised loop over the lanes,
+        // twice the instructions)
+        if (lane == 0) {
+            mbar_expect_tx(bar, nb * rows);
+            const uint8_t* src = wbase + (size_t)(p_grp * RB) * row_bytes + (size_t)c0 * CB2 / 2;
+            const uint32_t dst = smem_u32(ring + (size_t)p_st * sbytes);
+#pragma unroll
+            for (int u = 0; u < RB; ++u)
+                if (u < rows) bulk_g2s_hint(dst + u * stride, src + (size_t)u * row_bytes, nb, bar, pol);
         }
+        __syncwarp();
         ++issued;
         if (++p_st == S) p_st = 0;
         if (++p_seg == nseg) {
@@ -189,12 +293,17 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
             xh[i] = (unsigned short)(__float_as_uint(v) >> 16);
         }
     }
-    const bool xbf = CPT > 1 && __syncthreads_or(inexact) == 0;
-    if (CPT == 1) __syncthreads();
+    // (MXFP4 rows run on f32 x either way: their widen and scale are one exact fma, nothing more to save)
+    const bool xbf = CPT > 1 && FMT != S_MX4 && __syncthreads_or(inexact) == 0;
+    if (CPT == 1 || FMT == S_MX4) __syncthreads();
 
     float acc[CPT];
 #pragma unroll
     for (int u = 0; u < CPT; ++u) acc[u] = 0.f;
+    // FP8: rows a scale block holds, columns a scale block holds (the divisions made once, not a stage)
+    const int bm = FMT == S_FP8 ? R / A.sr : 1, bn = FMT == S_FP8 ? C / A.sc : 1;
+    const bool bn128 = bn == 128 && (seg & 127) == 0 && seg <= 512;  // a stage starts on a block, holds four at most
+    const float* srow_cur = nullptr;  // the scale row of the group's rows (a warp's rows share it: bm is a multiple of 8 or the rows differ)
     int c_grp = g0 + warp, c_seg = 0, c_st = 0;
     uint32_t c_par = 0;
     bool ok = true;
@@ -208,12 +317,12 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
         float fsc[4] = {1.f, 1.f, 1.f, 1.f};
         unsigned mxs = 0u;
         if (FMT == S_FP8) {
-            const int bm = R / A.sr, bn = C / A.sc;
-            const float* srow = reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride) + (size_t)((live ? r : 0) / bm) * A.sc;
+            if (c_seg == 0)
+                srow_cur = reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride) + (size_t)((live ? r : 0) / bm) * A.sc;
+            if (bn128) {
+                const int cb0 = c0 >> 7;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int cb = (c0 + u * 128) / bn;
-                fsc[u] = cb < A.sc ? __ldg(srow + cb) : 1.f;
+                for (int u = 0; u < 4; ++u) fsc[u] = cb0 + u < A.sc ? __ldg(srow_cur + cb0 + u) : 1.f;
             }
         } else if (FMT == S_MX4) {
             // a row's scale bytes of this stage (one a block of 32 columns): four a thread, shared by shuffle below
@@ -235,71 +344,32 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
         if (xbf) {
             const unsigned short* xb = xh + c0 + q * CPT;
             if (FMT == S_FP8) {
-                const int bn = C / A.sc;
-                const int steps = n >> 4;
-                const bool staged = bn == 128 && (seg & 127) == 0 && seg <= 512;
-#pragma unroll 4
-                for (int s = 0; s < steps; ++s) {
-                    const float sc = staged ? fsc[(s * 16) >> 7]
-                                            : __ldg(reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride) +
-                                                    (size_t)((live ? r : 0) / (R / A.sr)) * A.sc + (c0 + s * 16) / bn);
-                    const uint8_t* wp = srowp + s * 16 + q * CPT;
+                const uint8_t* wq = srowp + q * CPT;
+                auto step16 = [&](int off, float sc) {  // the 16 columns at `off` of the stage
                     if (CPT == 4) {
-                        const uint32_t wb = *reinterpret_cast<const uint32_t*>(wp);
-                        const uint2 xv = *reinterpret_cast<const uint2*>(xb + s * 16);
-                        const uint32_t w01 = e4m3x2_held_pair(wb, sc), w23 = e4m3x2_held_pair(wb >> 16, sc);
-                        acc[0] = fma1_bf16<0, 0>(w01, xv.x, acc[0]);
-                        acc[1 % CPT] = fma1_bf16<1, 1>(w01, xv.x, acc[1 % CPT]);
-                        acc[2 % CPT] = fma1_bf16<0, 0>(w23, xv.y, acc[2 % CPT]);
-                        acc[3 % CPT] = fma1_bf16<1, 1>(w23, xv.y, acc[3 % CPT]);
+                        const uint32_t wb = *reinterpret_cast<const uint32_t*>(wq + off);
+                        const uint2 xv = *reinterpret_cast<const uint2*>(xb + off);
+                        fp8_step4(wb, xv.x, xv.y, sc, acc[0], acc[1 % CPT], acc[2 % CPT], acc[3 % CPT]);
                     } else {
-                        const uint32_t w01 = e4m3x2_held_pair(*reinterpret_cast<const unsigned short*>(wp), sc);
-                        const uint32_t xv = *reinterpret_cast<const uint32_t*>(xb + s * 16);
+                        const uint32_t w01 = e4m3x2_held_pair(*reinterpret_cast<const unsigned short*>(wq + off), sc);
+                        const uint32_t xv = *reinterpret_cast<const uint32_t*>(xb + off);
                         acc[0] = fma1_bf16<0, 0>(w01, xv, acc[0]);
                         acc[1 % CPT] = fma1_bf16<1, 1>(w01, xv, acc[1 % CPT]);
                     }
-                }
-            } else if (FMT == S_MX4) {
-                const int nb = n >> 5;
-                constexpr int SPT = TPR >= 16 ? 1 : 16 / TPR >= 4 ? 4 : 16 / TPR;
+                };
+                if (bn128) {
+                    // one scale for each run of 128 columns (eight steps); every offset a constant
+                    Unrolled<4>::run([&](auto KB) {
+                        constexpr int kb = decltype(KB)::value;
+                        if (kb * 128 < n) {
+                            const float sc = fsc[kb];
+                            Unrolled<8>::run([&](auto U) { step16(kb * 128 + decltype(U)::value * 16, sc); });
+                        }
+                    });
+                } else {
+                    const int steps = n >> 4;
 #pragma unroll 4
-                for (int b = 0; b < nb; ++b) {
-                    const unsigned pk = __shfl_sync(0xffffffffu, mxs, (lane / TPR) * TPR + b / SPT);
-                    // 2^(s - 127) as a bf16 pair: an e2m1 value times it is exact in bf16 (two significant bits, and the
-                    // smallest product, 2^-128, is a bf16 subnormal), so the packed multiply gives the f32 product's value
-                    const uint32_t sb = (pk >> ((b % SPT) * 8)) & 255u;
-                    const uint32_t s1 = sb != 0u ? sb << 7 : 0x0040u;
-                    const uint32_t sc2 = s1 | (s1 << 16);
-                    const uint8_t* bp = srowp + b * 16;
-                    const unsigned short* xa = xb + b * 32;
-                    if (CPT == 4) {
-                        const unsigned lo = *reinterpret_cast<const unsigned short*>(bp + q * 2);
-                        const unsigned hi = *reinterpret_cast<const unsigned short*>(bp + 8 + q * 2);
-                        const uint2 va = *reinterpret_cast<const uint2*>(xa), vb = *reinterpret_cast<const uint2*>(xa + 16);
-                        uint32_t a01, a23, b01, b23;
-                        fp4x4_bf16(lo, a01, a23);
-                        fp4x4_bf16(hi, b01, b23);
-                        a01 = mul_bf16x2(a01, sc2), a23 = mul_bf16x2(a23, sc2);
-                        b01 = mul_bf16x2(b01, sc2), b23 = mul_bf16x2(b23, sc2);
-                        acc[0] = fma1_bf16<0, 0>(a01, va.x, acc[0]);
-                        acc[1 % CPT] = fma1_bf16<1, 1>(a01, va.x, acc[1 % CPT]);
-                        acc[2 % CPT] = fma1_bf16<0, 0>(a23, va.y, acc[2 % CPT]);
-                        acc[3 % CPT] = fma1_bf16<1, 1>(a23, va.y, acc[3 % CPT]);
-                        acc[0] = fma1_bf16<0, 0>(b01, vb.x, acc[0]);
-                        acc[1 % CPT] = fma1_bf16<1, 1>(b01, vb.x, acc[1 % CPT]);
-                        acc[2 % CPT] = fma1_bf16<0, 0>(b23, vb.y, acc[2 % CPT]);
-                        acc[3 % CPT] = fma1_bf16<1, 1>(b23, vb.y, acc[3 % CPT]);
-                    } else {
-                        const unsigned codes = (unsigned)bp[q] | ((unsigned)bp[8 + q] << 8);
-                        const uint32_t va = *reinterpret_cast<const uint32_t*>(xa), vb = *reinterpret_cast<const uint32_t*>(xa + 16);
-                        uint32_t a01, b01;
-                        fp4x4_bf16(codes, a01, b01);
-                        a01 = mul_bf16x2(a01, sc2), b01 = mul_bf16x2(b01, sc2);
-                        acc[0] = fma1_bf16<0, 0>(a01, va, acc[0]);
-                        acc[1 % CPT] = fma1_bf16<1, 1>(a01, va, acc[1 % CPT]);
-                        acc[0] = fma1_bf16<0, 0>(b01, vb, acc[0]);
-                        acc[1 % CPT] = fma1_bf16<1, 1>(b01, vb, acc[1 % CPT]);
-                    }
+                    for (int s = 0; s < steps; ++s) step16(s * 16, __ldg(srow_cur + (c0 + s * 16) / bn));
                 }
             } else {
                 const int steps = n >> 4;
@@ -322,77 +392,78 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
                 }
             }
         } else if (FMT == S_FP8) {
-            const int bn = C / A.sc;
-            const int steps = n >> 4;
-#pragma unroll 4
-            for (int s = 0; s < steps; ++s) {
-                // the block scale of these columns: the stage starts on a multiple of 128 columns when bn is 128
-                const float sc = (bn == 128 && (seg & 127) == 0 && seg <= 512)
-                                     ? fsc[(s * 16) >> 7]
-                                     : __ldg(reinterpret_cast<const float*>(A.scales + (size_t)e * A.s_stride) +
-                                             (size_t)((live ? r : 0) / (R / A.sr)) * A.sc + (c0 + s * 16) / bn);
-                const uint8_t* wp = srowp + s * 16 + q * CPT;
-                const float* xq = xp + s * 16 + q * CPT;
+            const uint8_t* wq = srowp + q * CPT;
+            const float* xq = xp + q * CPT;
+            auto step16 = [&](int off, float sc) {
                 if (CPT == 4) {
-                    const uint32_t wb = *reinterpret_cast<const uint32_t*>(wp);
-                    const float4 xv = *reinterpret_cast<const float4*>(xq);
-                    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb & 0xffffu), __NV_E4M3);
-                    const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(wb >> 16), __NV_E4M3);
-                    acc[0] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.x)), sc)), xv.x, acc[0]);
-                    acc[1 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.y)), sc)), xv.y, acc[1 % CPT]);
-                    acc[2 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h23.x)), sc)), xv.z, acc[2 % CPT]);
-                    acc[3 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h23.y)), sc)), xv.w, acc[3 % CPT]);
+                    const uint32_t wb = *reinterpret_cast<const uint32_t*>(wq + off);
+                    const float4 xv = *reinterpret_cast<const float4*>(xq + off);
+                    const uint32_t w01 = e4m3x2_held_pair(wb, sc), w23 = e4m3x2_held_pair(wb >> 16, sc);
+                    acc[0] = fmaf(bf_lo(w01), xv.x, acc[0]);
+                    acc[1 % CPT] = fmaf(bf_hi(w01), xv.y, acc[1 % CPT]);
+                    acc[2 % CPT] = fmaf(bf_lo(w23), xv.z, acc[2 % CPT]);
+                    acc[3 % CPT] = fmaf(bf_hi(w23), xv.w, acc[3 % CPT]);
                 } else if (CPT == 2) {
-                    const uint32_t wb = *reinterpret_cast<const unsigned short*>(wp);
-                    const float2 xv = *reinterpret_cast<const float2*>(xq);
-                    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)wb, __NV_E4M3);
-                    acc[0] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.x)), sc)), xv.x, acc[0]);
-                    acc[1 % CPT] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.y)), sc)), xv.y, acc[1 % CPT]);
+                    const uint32_t w01 = e4m3x2_held_pair(*reinterpret_cast<const unsigned short*>(wq + off), sc);
+                    const float2 xv = *reinterpret_cast<const float2*>(xq + off);
+                    acc[0] = fmaf(bf_lo(w01), xv.x, acc[0]);
+                    acc[1 % CPT] = fmaf(bf_hi(w01), xv.y, acc[1 % CPT]);
                 } else {
-                    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)*wp, __NV_E4M3);
-                    acc[0] = fmaf(bfround(__fmul_rn(__half2float(__ushort_as_half(h01.x)), sc)), *xq, acc[0]);
+                    acc[0] = fmaf(bf_lo(e4m3x2_held_pair(wq[off], sc)), xq[off], acc[0]);
                 }
+            };
+            if (bn128) {
+                Unrolled<4>::run([&](auto KB) {
+                    constexpr int kb = decltype(KB)::value;
+                    if (kb * 128 < n) {
+                        const float sc = fsc[kb];
+                        Unrolled<8>::run([&](auto U) { step16(kb * 128 + decltype(U)::value * 16, sc); });
+                    }
+                });
+            } else {
+                const int steps = n >> 4;
+#pragma unroll 4
+                for (int s = 0; s < steps; ++s) step16(s * 16, __ldg(srow_cur + (c0 + s * 16) / bn));
             }
         } else if (FMT == S_MX4) {
             const int nb = n >> 5;
             constexpr int SPT = TPR >= 16 ? 1 : 16 / TPR >= 4 ? 4 : 16 / TPR;
-#pragma unroll 4
-            for (int b = 0; b < nb; ++b) {
-                const unsigned pk = __shfl_sync(0xffffffffu, mxs, (lane / TPR) * TPR + b / SPT);
-                const float sc = e8m0_to_f32((pk >> ((b % SPT) * 8)) & 255u);
-                // the block's 16 bytes: byte i holds columns 2i (low nibble) and 2i + 1 of its first 16 columns,
-                // byte 8 + i the same of its last 16
-                const uint8_t* bp = srowp + b * 16;
-                const float* xa = xp + b * 32 + q * CPT;
-                const float* xb = xa + 16;
-                if (CPT == 4) {
-                    const unsigned lo = *reinterpret_cast<const unsigned short*>(bp + q * 2);
-                    const unsigned hi = *reinterpret_cast<const unsigned short*>(bp + 8 + q * 2);
-                    const float4 va = *reinterpret_cast<const float4*>(xa), vb = *reinterpret_cast<const float4*>(xb);
-                    uint32_t a01, a23, b01, b23;
-                    fp4x4_bf16(lo, a01, a23);
-                    fp4x4_bf16(hi, b01, b23);
-                    acc[0] = fmaf(__fmul_rn(bf_lo(a01), sc), va.x, acc[0]);
-                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(a01), sc), va.y, acc[1 % CPT]);
-                    acc[2 % CPT] = fmaf(__fmul_rn(bf_lo(a23), sc), va.z, acc[2 % CPT]);
-                    acc[3 % CPT] = fmaf(__fmul_rn(bf_hi(a23), sc), va.w, acc[3 % CPT]);
-                    acc[0] = fmaf(__fmul_rn(bf_lo(b01), sc), vb.x, acc[0]);
-                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(b01), sc), vb.y, acc[1 % CPT]);
-                    acc[2 % CPT] = fmaf(__fmul_rn(bf_lo(b23), sc), vb.z, acc[2 % CPT]);
-                    acc[3 % CPT] = fmaf(__fmul_rn(bf_hi(b23), sc), vb.w, acc[3 % CPT]);
-                } else if (CPT == 2) {
-                    const unsigned codes = (unsigned)bp[q] | ((unsigned)bp[8 + q] << 8);
-                    const float2 va = *reinterpret_cast<const float2*>(xa), vb = *reinterpret_cast<const float2*>(xb);
-                    uint32_t a01, b01;
-                    fp4x4_bf16(codes, a01, b01);  // the first half's two columns, then the second half's
-                    acc[0] = fmaf(__fmul_rn(bf_lo(a01), sc), va.x, acc[0]);
-                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(a01), sc), va.y, acc[1 % CPT]);
-                    acc[0] = fmaf(__fmul_rn(bf_lo(b01), sc), vb.x, acc[0]);
-                    acc[1 % CPT] = fmaf(__fmul_rn(bf_hi(b01), sc), vb.y, acc[1 % CPT]);
-                } else {
-                    const int sh = (q & 1) << 2;
-                    acc[0] = fmaf(__fmul_rn(fp4_to_f32((bp[q >> 1] >> sh) & 15u), sc), *xa, acc[0]);
-                    acc[0] = fmaf(__fmul_rn(fp4_to_f32((bp[8 + (q >> 1)] >> sh) & 15u), sc), *xb, acc[0]);
+            // the block's 16 bytes: byte i holds columns 2i (low nibble) and 2i + 1 of its first 16 columns, byte 8 + i
+            // the same of its last 16. 2^(s - 127) is a normal f16 for s in 113..142 (every sane checkpoint's scales):
+            // where all of the warp's scales of this stage are, the widen f16 -> f32 and the scale are one exact fma,
+            // the multiplier's f16 bits (s - 112) << 10 made by a shift of the byte
+            const bool stage_f16 = CPT > 1 && __all_sync(0xffffffffu, __vminu4(mxs, 0x71717171u) == 0x71717171u &&
+                                                                          __vmaxu4(mxs, 0x8E8E8E8Eu) == 0x8E8E8E8Eu);
+            if (stage_f16) {
+                const unsigned rel = mxs - 0x70707070u;  // every byte s - 112, 1..30: no borrow
+                const int row_lane = (lane / TPR) * TPR;
+                const uint8_t* bq = srowp + q * (CPT / 2);  // CPT codes = CPT / 2 bytes of each half of a block
+                const float* xq = xp + q * CPT;
+                // (a stage holds sixteen blocks at most: seg <= 512)
+                Unrolled<16>::run([&](auto B) {
+                    constexpr int b = decltype(B)::value;
+                    if (b < nb) {
+                        const unsigned pk = __shfl_sync(0xffffffffu, rel, row_lane + b / SPT);
+                        constexpr int sh = (b % SPT) * 8;
+                        // (s - 112) << 10: the f16 bits of 2^(s - 127)
+                        const unsigned short ph = (unsigned short)(sh >= 10 ? (pk >> (sh - 10)) & 0x7C00u : (pk << (10 - sh)) & 0x7C00u);
+                        mx4_block<CPT == 1 ? 2 : CPT, true>(bq + b * 16, 0, xq + b * 32, ph, 1.f, acc);
+                    }
+                });
+            } else {
+#pragma unroll 2
+                for (int b = 0; b < nb; ++b) {
+                    const unsigned pk = __shfl_sync(0xffffffffu, mxs, (lane / TPR) * TPR + b / SPT);
+                    const float sc = e8m0_to_f32((pk >> ((b % SPT) * 8)) & 255u);
+                    const uint8_t* bp = srowp + b * 16;
+                    const float* xa = xp + b * 32 + q * CPT;
+                    if (CPT > 1) {
+                        mx4_block<CPT == 1 ? 2 : CPT, false>(bp, q, xa, 0, sc, acc);
+                    } else {
+                        const int sh = (q & 1) << 2;
+                        acc[0] = fmaf(__fmul_rn(fp4_to_f32((bp[q >> 1] >> sh) & 15u), sc), *xa, acc[0]);
+                        acc[0] = fmaf(__fmul_rn(fp4_to_f32((bp[8 + (q >> 1)] >> sh) & 15u), sc), *(xa + 16), acc[0]);
+                    }
                 }
             }
         } else {

@@ -314,6 +314,7 @@ __global__ void __launch_bounds__(NTS, 1) step_kernel(const StepArgs A) {
             } else if (kind == OP_ROPE) {
                 const StepOp& op = ops[oi];
                 RopeArgs ra;
+                ra.rw = nullptr;
                 ra.qkv = op.x, ra.wq = op.wq, ra.wk = op.wk, ra.cos_t = A.cos_t, ra.sin_t = A.sin_t;
                 ra.n0p = A.n0, ra.depth = A.depth, ra.tbl = A.tbl, ra.K = op.K, ra.V = op.V, ra.qo = op.q;
                 ra.eps = op.eps, ra.T = A.T, ra.Hq = A.Hq, ra.Hk = A.Hk, ra.centered = op.centered;
@@ -325,6 +326,7 @@ __global__ void __launch_bounds__(NTS, 1) step_kernel(const StepArgs A) {
             } else if (kind == OP_ATTN) {
                 const StepOp& op = ops[oi];
                 AttnArgs aa;
+                aa.rw = nullptr;
                 aa.q = op.q, aa.K = op.K, aa.V = op.V, aa.out = op.att, aa.n0p = A.n0, aa.par = A.par, aa.tbl = A.tbl;
                 aa.sinks = A.sinks, aa.part_m = A.part_m, aa.part_l = A.part_l, aa.part_acc = A.part_acc, aa.cnt = A.cnt;
                 aa.scale = op.scale, aa.T = A.T, aa.Hq = A.Hq, aa.Hk = A.Hk, aa.win = op.win, aa.cap = A.cap;

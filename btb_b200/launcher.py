@@ -53,6 +53,8 @@ class B200Launcher:
         (r"btb_norm_rope_kv_d(\d+)$", "_norm_rope_kv"),
         (r"btb_norm_rope_kv_tbl_d(\d+)$", "_norm_rope_kv"),
         (r"btb_attn_flash_d(\d+)$", "_attn_flash"),
+        (r"btb_norm_rope_kv_rows_d(\d+)$", "_norm_rope_kv_rows"),
+        (r"btb_attn_flash_rows_d(\d+)$", "_attn_flash_rows"),
         (r"btb_publish$", "_publish"),
         (r"btb_moe_route$", "_moe_route"),
         (r"btb_gemv_lane16_f32_m(\d+)$", "_gemv_lane16"),
@@ -137,6 +139,18 @@ class B200Launcher:
         capi.call("btb_b200_attn_decode", _p(q), _p(K), _p(V), _p(out), _p(n0p), _p(par), int(_v(T)), int(_v(Hq)),
                   int(_v(Hk)), int(m.group(1)), int(_v(hs)), int(_v(rs)), float(_v(scale)), _p(pm), _p(pl), _p(pa),
                   _p(cnt), int(_v(win)), _p(tbl), 0, int(grid[1]) * 512, s)  # fmt: skip
+
+    def _norm_rope_kv_rows(self, name, m, grid, a, s):
+        qkv, wq, wk, eps, cos, sin, rw, K, V, qo, T, Hq, Hk, hs, rs, cen = a
+        capi.call("btb_b200_norm_rope_kv_rows", _p(qkv), _p(wq), _p(wk), float(_v(eps)), _p(cos), _p(sin), _p(rw), _p(K),
+                  _p(V), _p(qo), int(_v(T)), int(_v(Hq)), int(_v(Hk)), int(m.group(1)), int(_v(hs)), int(_v(rs)),
+                  int(_v(cen)), INT_MAX, s)  # fmt: skip
+
+    def _attn_flash_rows(self, name, m, grid, a, s):
+        q, K, V, out, rw, T, Hq, Hk, hs, rs, scale, pm, pl, pa, cnt, win = a
+        capi.call("btb_b200_attn_decode_rows", _p(q), _p(K), _p(V), _p(out), _p(rw), int(_v(T)), int(_v(Hq)), int(_v(Hk)),
+                  int(m.group(1)), int(_v(hs)), int(_v(rs)), float(_v(scale)), _p(pm), _p(pl), _p(pa), _p(cnt),
+                  int(_v(win)), 0, int(grid[1]) * 512, s)  # fmt: skip
 
     def _publish(self, name, m, grid, a, s):
         n0, ids, out_tok, out_n0, out_ts = a
@@ -244,6 +258,26 @@ def btb_attn_flash(launcher, D, grid, block, q, K, V, out, n0p, par, T, Hq, Hk, 
         f"btb_attn_flash_d{D}", grid, block,
         [_P(q), _P(K), _P(V), _P(out), _P(n0p), _P(par), _I(T), _I(Hq), _I(Hk), _I(hs), _I(rs), _F(scale),
          _P(part_m), _P(part_l), _P(part_acc), _P(cnt), _I(win), _P(tbl)],
+        stream, shared,
+    )  # fmt: skip
+
+
+def btb_norm_rope_kv_rows(launcher, D, grid, block, qkv, wq, wk, eps, cos_t, sin_t, rw, K, V, qo, T, Hq, Hk, hs, rs, centered, *,
+                          stream=None, shared=0):  # fmt: skip
+    launcher.launch(
+        f"btb_norm_rope_kv_rows_d{D}", grid, block,
+        [_P(qkv), _P(wq), _P(wk), _F(eps), _P(cos_t), _P(sin_t), _P(rw), _P(K), _P(V), _P(qo), _I(T), _I(Hq), _I(Hk), _I(hs),
+         _I(rs), _I(centered)],
+        stream, shared,
+    )  # fmt: skip
+
+
+def btb_attn_flash_rows(launcher, D, grid, block, q, K, V, out, rw, T, Hq, Hk, hs, rs, scale, part_m, part_l, part_acc, cnt,
+                        win, *, stream=None, shared=0):  # fmt: skip
+    launcher.launch(
+        f"btb_attn_flash_rows_d{D}", grid, block,
+        [_P(q), _P(K), _P(V), _P(out), _P(rw), _I(T), _I(Hq), _I(Hk), _I(hs), _I(rs), _F(scale), _P(part_m), _P(part_l),
+         _P(part_acc), _P(cnt), _I(win)],
         stream, shared,
     )  # fmt: skip
 

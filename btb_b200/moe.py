@@ -258,24 +258,42 @@ class MoEEngine(CardEngine):
         fold = self.fold and self.ep_size == 1
         pending = False  # the previous layer's picks are summed by the norm that reads them
         y_prev = None
+        # the residual ping-pongs between two buffers where the norm is folded into the matvec that reads it (a CTA must
+        # not read a row another CTA is updating); the pass ends on g["h"]
+        hcur, halt = g["h"], g["h2"]
+        fuse = self.fuse_norm and M <= 8 and M * H * 2 <= 64 * 1024
 
         def norm_in(norm_w: torch.Tensor) -> None:
             nonlocal pending
             if pending:
-                K_("btb_b200_moe_combine_norm", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), k, ptr(g["h"]), ptr(norm_w),
+                K_("btb_b200_moe_combine_norm", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), k, ptr(hcur), ptr(norm_w),
                    c.eps, ptr(g["x"]), 0, 0, T, H, 0, s)
                 pending = False
             else:
-                K_("btb_b200_add_rmsnorm", ptr(g["h"]), ptr(y_prev), ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
+                K_("btb_b200_add_rmsnorm", ptr(hcur), ptr(y_prev), ptr(norm_w), c.eps, ptr(g["x"]), T, H, 0, s)
+
+        def normed_matvec(W: Any, norm_w: torch.Tensor, out: torch.Tensor, R: int) -> None:
+            """x = norm(h + y_prev) and the matvec over it: one launch where the matrix is bf16 and the pass narrow"""
+            nonlocal hcur, halt
+            if fuse and not pending and isinstance(W, torch.Tensor):
+                if y_prev is None:  # the first layer: no add, the residual stays where it is
+                    K_("btb_b200_gemv_norm", ptr(W), 0, 0, 0, 0, 0, ptr(hcur), 0, ptr(norm_w), c.eps, 0, 0, ptr(out), T, M,
+                       R, H, s)  # fmt: skip
+                else:
+                    K_("btb_b200_gemv_norm", ptr(W), 0, 0, 0, 0, 0, ptr(hcur), ptr(y_prev), ptr(norm_w), c.eps, 0,
+                       ptr(halt), ptr(out), T, M, R, H, s)  # fmt: skip
+                    hcur, halt = halt, hcur
+                return
+            norm_in(norm_w)
+            self._matvec(W, g["x"], out, M, R, H, s)
 
         for i, L in enumerate(self.w.layers):
-            norm_in(L.ln1)
-            self._matvec(L.qkv, g["x"], g["qkv"], M, c.qkv_rows, H, s)
+            normed_matvec(L.qkv, L.ln1, g["qkv"], c.qkv_rows)
             self._attention(g, i, L.wq, L.wk, T, s)
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             # the MoE block: x.float() (made by the norm's own launch), the router's logits by the host-order GEMV,
             # the picks, the experts, the sum
-            K_("btb_b200_add_rmsnorm_wide", ptr(g["h"]), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), ptr(g["xf"]), T, H, 0,
+            K_("btb_b200_add_rmsnorm_wide", ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), ptr(g["xf"]), T, H, 0,
                s)  # fmt: skip
             # one cluster launch for the matvec and the picks where the router is small enough for it to win
             # (measured: 32 experts x 2880 yes, 128 x 2048 no)
@@ -311,10 +329,11 @@ class MoEEngine(CardEngine):
                 K_("btb_b200_moe_combine", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, s)
             y_prev = g["y"]
         if tail:
-            norm_in(self.w.norm)
-            self._matvec(self.w.embed, g["x"], g["logits"], M, c.vocab, H, s)
+            normed_matvec(self.w.embed, self.w.norm, g["logits"], c.vocab)
         elif pending:  # a pass without its head leaves the last layer's sum in y, as the unfolded pass does
             K_("btb_b200_moe_combine", ptr(g["edn"]), ptr(g["idx"]), ptr(g["rw"]), 0, ptr(g["y"]), T, k, H, s)
+        if hcur is not g["h"]:  # an odd number of folded adds: bring the residual home
+            g["h"].copy_(hcur)
         if self.ep_size > 1:  # the pass is over: its hops' sequence numbers move on
             K_("btb_b200_xchg_tick", self.ep_descs(M)[3], s)
 

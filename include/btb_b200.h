@@ -141,6 +141,14 @@ int btb_b200_norm_rope_kv(const void* qkv, const void* wq, const void* wk, float
                           const void* sin_t, const void* n0p, const void* depth, void* K, void* V, void* q, int T,
                           int Hq, int Hk, int D, long long hs, long long rs, int centered, const void* tbl, int cap,
                           void* stream);
+/* btb_norm_rope_kv_rows_d{64,128,256} (btb_kernels.cu:228-248, 258-327 ROWS): the rows layout - a pass's T rows as T
+ * sequences a token each (a fork's rows, or a batch's). rw i32 on the card: [base, step, W, then (col, off, len) a row];
+ * row t's keys are `len` cache rows from `off` (its prefix; forks share one) and then its own steps, step i at cache row
+ * base + i * W + col. This pass's token stands at position len + step and its K/V go to that step's cache row; a row
+ * with len < 0 is padding and computes nothing. cap: rows of the cache and of the tables. */
+int btb_b200_norm_rope_kv_rows(const void* qkv, const void* wq, const void* wk, float eps, const void* cos_t,
+                               const void* sin_t, const void* rw, void* K, void* V, void* q, int T, int Hq, int Hk, int D,
+                               long long hs, long long rs, int centered, int cap, void* stream);
 /* btb_attn_flash_d{64,128} (btb_attn_flash.cuh:372-675): decode / tree attention over the cache, split over groups
  * of 512 keys. part_m, part_l f32 [S,T,Hq], part_acc f32 [S,T,Hq,D], cnt i32 [T,Hk] zeroed once, S = ceil(cap/512).
  * sinks f32 [Hq] or null (gpt-oss: a logit joined to the softmax denominator, btb/engine/families/gpt_oss/sinks.py:
@@ -149,6 +157,12 @@ int btb_b200_attn_decode(const void* q, const void* K, const void* V, void* out,
                          int T, int Hq, int Hk, int D, long long hs, long long rs, float scale, void* part_m,
                          void* part_l, void* part_acc, void* cnt, int win, const void* tbl, const void* sinks, int cap,
                          void* stream);
+/* btb_attn_flash_rows_d{64,128} (btb_attn_flash.cuh:286-290, 396-401): the rows layout's attention - row t reads its
+ * own sequence's keys (rw as above) in logical order, the order a one-row step of that sequence alone reads them in, so
+ * a row's bits are its own decode's whatever rows step beside it. Scratch as btb_b200_attn_decode's. */
+int btb_b200_attn_decode_rows(const void* q, const void* K, const void* V, void* out, const void* rw, int T, int Hq,
+                              int Hk, int D, long long hs, long long rs, float scale, void* part_m, void* part_l,
+                              void* part_acc, void* cnt, int win, const void* sinks, int cap, void* stream);
 /* the decode step's row (T = 1) in one launch: btb_norm_rope_kv_d* (btb_kernels.cu:261-358) and btb_attn_flash_d*
  * (btb_attn_flash.cuh:372-675) back to back in the reference. Every block rotates its kv head's queries itself; the
  * block whose key group holds slot n0 makes the new key and value, writes them to the cache and uses them from shared

@@ -249,6 +249,47 @@ def attn_decode(q, K, V, n0, par, Hq, Hk, D, hs, rs, scale, win=0, tbl=None, sin
     return out
 
 
+# ---- the rows layout (native/cuda/btb_kernels.cu:228-248 of btb): row t a sequence of its own --------------------------------
+# rw = [base, step, W, then (col, off, len) a row]; row t's logical key j lives at cache row off + j for j < len (its
+# prefix), else base + (j - len) * W + col (its own steps). Each row is restated as the one-sequence functions above over a
+# row map built from its place: the reference's own statement of the layout ("the sequence a one-row step of that sequence
+# alone walks", btb_kernels.cu:236-239).
+def rows_map(rw, t: int) -> np.ndarray | None:
+    """row t's logical -> cache row map over its len + step + 1 keys (None: padding)"""
+    base, step, W = (int(v) for v in rw[:3])
+    col, off, ln = (int(v) for v in rw[3 + 3 * t : 6 + 3 * t])
+    if ln < 0:
+        return None
+    j = np.arange(ln + step + 1)
+    return np.where(j < ln, off + j, base + (j - ln) * W + col).astype(np.int32)
+
+
+def norm_rope_kv_rows(qkv, wq, wk, eps, cos_t, sin_t, rw, K, V, Hq, Hk, D, hs, rs, centered=False):
+    """writes each live row's K and V at its step's cache row, returns q [T, Hq, D] (zeros for padding rows)"""
+    qkv = _u16(qkv)
+    T = qkv.shape[0]
+    qo = np.zeros((T, Hq, D), np.uint16)
+    for t in range(T):
+        m = rows_map(rw, t)
+        if m is None:
+            continue
+        pos = len(m) - 1
+        qo[t] = norm_rope_kv(qkv[t : t + 1], wq, wk, eps, cos_t, sin_t, pos, [0], K, V, Hq, Hk, D, hs, rs, centered, m)[0]
+    return qo
+
+
+def attn_decode_rows(q, K, V, rw, Hq, Hk, D, hs, rs, scale, win=0, sinks=None) -> np.ndarray:
+    q = _u16(q)
+    T = q.shape[0]
+    out = np.zeros((T, Hq * D), np.uint16)
+    for t in range(T):
+        m = rows_map(rw, t)
+        if m is None:
+            continue
+        out[t] = attn_decode(q[t : t + 1], K, V, len(m) - 1, [-1], Hq, Hk, D, hs, rs, scale, win, m, sinks)[0]
+    return out
+
+
 def moe_route(logits, E: int, k: int, mode: int):
     """logits [T, ls]: uint16 (bf16 bits) or float32"""
     logits = np.ascontiguousarray(logits)
