@@ -14,6 +14,7 @@
 #include <cooperative_groups.h>
 
 #include "btb_b200_internal.h"
+#include "gemv_core.cuh"
 #include "moe_widen.cuh"
 #include "tp.cuh"
 #include "../../include/btb_b200.h"
@@ -166,11 +167,23 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route(const RouteArgs A) {
 constexpr int RR_CTAS = 8;
 struct RouterArgs {
     const bf16* w;   // [E, H]
-    const float* x;  // [T, H] f32
+    const float* x;  // [T, H] f32 (not read when h_in is given)
     float* rl;       // [T, E] the logits, or null
     int* idx;
     bf16* wout;
     int E, H, k, mode;
+    // the block's residual + RMSNorm on the way in (btb_add_rmsnorm and the row's widen, btb/engine/host.py:180-186): with
+    // h_in, x = float(bf16(rmsnorm(h_in + y_add) * norm_w)) is made by every CTA of the cluster for itself, and the
+    // leader writes the new residual to h_out (never h_in's buffer), the widened row to xf_out and, if asked, the bf16
+    // row to x_out
+    const bf16* h_in;
+    const bf16* y_add;
+    const bf16* norm_w;
+    bf16* h_out;
+    float* xf_out;
+    bf16* x_out;
+    float eps;
+    int centered;
 };
 __global__ void __cluster_dims__(RR_CTAS, 1, 1) __launch_bounds__(ROUTE_THREADS) moe_router_route(const RouterArgs A) {
     cg::cluster_group cl = cg::this_cluster();
@@ -184,7 +197,23 @@ __global__ void __cluster_dims__(RR_CTAS, 1, 1) __launch_bounds__(ROUTE_THREADS)
     bf16* wrows = reinterpret_cast<bf16*>(rsm + ((((size_t)H + 2 * (size_t)E) * 4 + 15) & ~(size_t)15));  // [16][H + 8]
     pdl_launch_dependents();
     pdl_wait();
-    {
+    if (A.h_in != nullptr) {
+        // (the rows' staging area is free until the first group of experts is staged)
+        float* scratch = reinterpret_cast<float*>(wrows);       // H + 256 floats
+        bf16* xb = reinterpret_cast<bf16*>(scratch + H + 256);  // the normed row, bf16
+        stage_x_norm<1, 0, false>(xb, scratch, A.h_in + (size_t)t * H, nullptr,
+                                  A.y_add != nullptr ? A.y_add + (size_t)t * H : nullptr, A.norm_w,
+                                  A.h_out != nullptr ? A.h_out + (size_t)t * H : nullptr, A.eps, A.centered, 1, H, rank == 0);
+        for (int i = tid; i < H; i += ROUTE_THREADS) {
+            const float v = bf2f(xb[i]);
+            xs[i] = v;
+            if (rank == 0) {
+                A.xf_out[(size_t)t * H + i] = v;
+                if (A.x_out != nullptr) A.x_out[(size_t)t * H + i] = xb[i];
+            }
+        }
+        __syncthreads();
+    } else {
         const float4* xg = reinterpret_cast<const float4*>(A.x + (size_t)t * H);
         for (int i = tid; i < H / 4; i += ROUTE_THREADS) reinterpret_cast<float4*>(xs)[i] = __ldcg(xg + i);
     }
@@ -648,19 +677,47 @@ extern "C" int btb_b200_moe_combine_norm(const void* dn, const void* idx, const 
 
 // the router's matvec and the picks as one cluster launch; shapes it does not take (H not a multiple of 8, more than 1024
 // experts, unaligned pointers) are refused: use btb_b200_gemv_lane16_f32 and btb_b200_moe_route
-extern "C" int btb_b200_moe_router(const void* w, const void* x, void* logits, int E, int H, int k, int mode, void* idx,
-                                   void* wout, int T, void* stream) {
-    if (!w || !x || !idx || !wout) return B2_ERR_NULL;
+static int moe_router_launch(RouterArgs a, const void* align_a, const void* align_b, int T, void* stream) {
+    const int E = a.E, H = a.H, k = a.k;
+    if (!a.w || !a.idx || !a.wout) return B2_ERR_NULL;
     if (T <= 0 || T > 65535 || E <= 0 || E > 1024 || k <= 0 || k > E || k > ROUTE_MAX_K || H <= 0 || (H & 7) ||
-        (mode != 0 && mode != 1))
+        (a.mode != 0 && a.mode != 1))
         return B2_ERR_DOMAIN;
-    if ((reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(a.w) & 15) || (reinterpret_cast<uintptr_t>(align_a) & 15) ||
+        (reinterpret_cast<uintptr_t>(align_b) & 15))
+        return B2_ERR_DOMAIN;
     const size_t smem = ((((size_t)H + 2 * (size_t)E) * 4 + 15) & ~(size_t)15) + 16 * ((size_t)H + 8) * 2;
-    if (smem > 200 * 1024) return B2_ERR_DOMAIN;
-    RouterArgs a{static_cast<const bf16*>(w), static_cast<const float*>(x), static_cast<float*>(logits),
-                 static_cast<int*>(idx), static_cast<bf16*>(wout), E, H, k, mode};
+    if (smem > 200 * 1024 || 16 * ((size_t)H + 8) * 2 < ((size_t)H + 256) * 4 + (size_t)H * 2) return B2_ERR_DOMAIN;
     static bool allowed[64];
     if (const int rc = b2_allow_smem((const void*)moe_router_route, allowed)) return rc;
     return b2_launch((const void*)moe_router_route, dim3(RR_CTAS, T), dim3(ROUTE_THREADS), smem,
                      static_cast<cudaStream_t>(stream), a, 4);
+}
+
+extern "C" int btb_b200_moe_router(const void* w, const void* x, void* logits, int E, int H, int k, int mode, void* idx,
+                                   void* wout, int T, void* stream) {
+    if (!x) return B2_ERR_NULL;
+    RouterArgs a{};
+    a.w = static_cast<const bf16*>(w), a.x = static_cast<const float*>(x), a.rl = static_cast<float*>(logits);
+    a.idx = static_cast<int*>(idx), a.wout = static_cast<bf16*>(wout), a.E = E, a.H = H, a.k = k, a.mode = mode;
+    return moe_router_launch(a, x, nullptr, T, stream);
+}
+
+// the same with the block's residual add, RMSNorm and widen in its prologue: one launch for btb_b200_add_rmsnorm_wide and
+// btb_b200_moe_router (the same operations in the same order: the same bits)
+extern "C" int btb_b200_moe_router_norm(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps,
+                                        int centered, void* h_out, void* x_out, void* xf_out, void* logits, int E, int H,
+                                        int k, int mode, void* idx, void* wout, int T, void* stream) {
+    if (!h_in || !norm_w || !xf_out || (y_add && !h_out)) return B2_ERR_NULL;
+    if (h_out == h_in || !(eps == eps)) return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(y_add) | reinterpret_cast<uintptr_t>(h_out) | reinterpret_cast<uintptr_t>(xf_out) |
+         reinterpret_cast<uintptr_t>(x_out)) & 15)
+        return B2_ERR_DOMAIN;
+    RouterArgs a{};
+    a.w = static_cast<const bf16*>(w), a.rl = static_cast<float*>(logits);
+    a.idx = static_cast<int*>(idx), a.wout = static_cast<bf16*>(wout), a.E = E, a.H = H, a.k = k, a.mode = mode;
+    a.h_in = static_cast<const bf16*>(h_in), a.y_add = static_cast<const bf16*>(y_add);
+    a.norm_w = static_cast<const bf16*>(norm_w), a.h_out = static_cast<bf16*>(h_out);
+    a.xf_out = static_cast<float*>(xf_out), a.x_out = static_cast<bf16*>(x_out), a.eps = eps, a.centered = centered;
+    return moe_router_launch(a, h_in, norm_w, T, stream);
 }

@@ -122,6 +122,13 @@ __device__ __forceinline__ void e2m1x4_f16x2(uint32_t two_bytes, uint32_t& h01, 
         : "=r"(h01), "=r"(h23)
         : "r"(two_bytes));
 }
+// four bytes of e2m1 codes (eight codes, the lowest nibble first) as four f16 pairs
+__device__ __forceinline__ void e2m1x8_f16x2(uint32_t four_bytes, uint32_t& h01, uint32_t& h23, uint32_t& h45, uint32_t& h67) {
+    asm("{\n.reg .b8 b0, b1, b2, b3;\nmov.b32 {b0, b1, b2, b3}, %4;\ncvt.rn.f16x2.e2m1x2 %0, b0;\n"
+        "cvt.rn.f16x2.e2m1x2 %1, b1;\ncvt.rn.f16x2.e2m1x2 %2, b2;\ncvt.rn.f16x2.e2m1x2 %3, b3;\n}"
+        : "=r"(h01), "=r"(h23), "=r"(h45), "=r"(h67)
+        : "r"(four_bytes));
+}
 // an f16 pair times the f16 value p, as two f32 (exact: the mixed-precision fma's product is not rounded before the sum,
 // and the addend is -0, which keeps a zero's sign)
 __device__ __forceinline__ void f16x2_times(uint32_t h, unsigned short p, float& f0, float& f1) {
@@ -141,8 +148,7 @@ __device__ __forceinline__ void mx4_block(const uint8_t* bp, int q, const float*
         const uint32_t hi = *reinterpret_cast<const unsigned short*>(bp + 8 + q * 2);
         const float4 va = *reinterpret_cast<const float4*>(xa), vb = *reinterpret_cast<const float4*>(xa + 16);
         uint32_t a01, a23, b01, b23;
-        e2m1x4_f16x2(lo, a01, a23);
-        e2m1x4_f16x2(hi, b01, b23);
+        e2m1x8_f16x2(__byte_perm(lo, hi, 0x5410), a01, a23, b01, b23);
         float w[8];
         f16x2_times(a01, mul, w[0], w[1]);
         f16x2_times(a23, mul, w[2], w[3]);
@@ -250,17 +256,13 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
         const int rows = min(RB, R - p_grp * RB);
         const uint32_t nb = (uint32_t)(n * CB2 / 2);
         const uint32_t bar = smem_u32(bars + p_st);
-        // one lane issues the group's copies in a straight line (a copy a lane cost a serialised loop over the lanes,
-        // twice the instructions)
-        if (lane == 0) {
-            mbar_expect_tx(bar, nb * rows);
-            const uint8_t* src = wbase + (size_t)(p_grp * RB) * row_bytes + (size_t)c0 * CB2 / 2;
-            const uint32_t dst = smem_u32(ring + (size_t)p_st * sbytes);
-#pragma unroll
-            for (int u = 0; u < RB; ++u)
-                if (u < rows) bulk_g2s_hint(dst + u * stride, src + (size_t)u * row_bytes, nb, bar, pol);
-        }
+        if (lane == 0) mbar_expect_tx(bar, nb * rows);
         __syncwarp();
+        // (a copy a lane: one lane issuing the group's copies in a straight line was measured at more instructions)
+        if (lane < rows) {
+            const uint8_t* src = wbase + (size_t)(p_grp * RB + lane) * row_bytes + (size_t)c0 * CB2 / 2;
+            bulk_g2s_hint(smem_u32(ring + (size_t)p_st * sbytes + (size_t)lane * stride), src, nb, bar, pol);
+        }
         ++issued;
         if (++p_st == S) p_st = 0;
         if (++p_seg == nseg) {
@@ -437,19 +439,29 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
             if (stage_f16) {
                 const unsigned rel = mxs - 0x70707070u;  // every byte s - 112, 1..30: no borrow
                 const int row_lane = (lane / TPR) * TPR;
+                // the row's scale bytes of the whole stage, from the threads that fetched them (outside any condition:
+                // a shuffle under one costs a divergence check each)
+                unsigned pks[16 / SPT];
+#pragma unroll
+                for (int j = 0; j < 16 / SPT; ++j) pks[j] = __shfl_sync(0xffffffffu, rel, row_lane + (j % TPR));
                 const uint8_t* bq = srowp + q * (CPT / 2);  // CPT codes = CPT / 2 bytes of each half of a block
                 const float* xq = xp + q * CPT;
-                // (a stage holds sixteen blocks at most: seg <= 512)
-                Unrolled<16>::run([&](auto B) {
+                auto block = [&](auto B) {
                     constexpr int b = decltype(B)::value;
-                    if (b < nb) {
-                        const unsigned pk = __shfl_sync(0xffffffffu, rel, row_lane + b / SPT);
-                        constexpr int sh = (b % SPT) * 8;
-                        // (s - 112) << 10: the f16 bits of 2^(s - 127)
-                        const unsigned short ph = (unsigned short)(sh >= 10 ? (pk >> (sh - 10)) & 0x7C00u : (pk << (10 - sh)) & 0x7C00u);
-                        mx4_block<CPT == 1 ? 2 : CPT, true>(bq + b * 16, 0, xq + b * 32, ph, 1.f, acc);
-                    }
-                });
+                    constexpr int sh = (b % SPT) * 8;
+                    const unsigned pk = pks[b / SPT];
+                    // (s - 112) << 10: the f16 bits of 2^(s - 127)
+                    const unsigned short ph = (unsigned short)(sh >= 10 ? (pk >> (sh - 10)) & 0x7C00u : (pk << (10 - sh)) & 0x7C00u);
+                    mx4_block<CPT == 1 ? 2 : CPT, true>(bq + b * 16, 0, xq + b * 32, ph, 1.f, acc);
+                };
+                // (a stage holds sixteen blocks at most: seg <= 512)
+                if (nb == 16) {
+                    Unrolled<16>::run(block);
+                } else {
+                    Unrolled<16>::run([&](auto B) {
+                        if (int(decltype(B)::value) < nb) block(B);
+                    });
+                }
             } else {
 #pragma unroll 2
                 for (int b = 0; b < nb; ++b) {

@@ -293,14 +293,15 @@ class MoEEngine(CardEngine):
             self._matvec(L.o, g["att"], g["y"], M, H, Hq * D, s)
             # the MoE block: x.float() (made by the norm's own launch), the router's logits by the host-order GEMV,
             # the picks, the experts, the sum
-            K_("btb_b200_add_rmsnorm_wide", ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), ptr(g["xf"]), T, H, 0,
-               s)  # fmt: skip
-            # one cluster launch for the matvec and the picks where the router is small enough for it to win
-            # (measured: 32 experts x 2880 yes, 128 x 2048 no)
+            # one cluster launch for the norm, the router's matvec and the picks where the router is small enough for it
+            # to win (measured: 32 experts x 2880 yes, 128 x 2048 no)
             if self.fuse_router and H % 8 == 0 and E * H <= 131072:
-                K_("btb_b200_moe_router", ptr(L.router), ptr(g["xf"]), 0, E, H, k, c.router_mode, ptr(g["idx"]), ptr(g["rw"]),
-                   T, s)  # fmt: skip
+                K_("btb_b200_moe_router_norm", ptr(L.router), ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, 0, ptr(halt), 0,
+                   ptr(g["xf"]), 0, E, H, k, c.router_mode, ptr(g["idx"]), ptr(g["rw"]), T, s)  # fmt: skip
+                hcur, halt = halt, hcur
             else:
+                K_("btb_b200_add_rmsnorm_wide", ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), ptr(g["xf"]), T, H,
+                   0, s)  # fmt: skip
                 K_("btb_b200_moe_gemv", 0, ptr(L.router), 0, 0, 0, 1, 1, 0, T, 1, ptr(g["xf"]), 1, ptr(g["rl"]), E, H, 0, 1, s)
                 K_("btb_b200_moe_route", ptr(g["rl"]), E, E, k, c.router_mode, 1, ptr(g["idx"]), ptr(g["rw"]), T, s)
             self._expert_gemv(L.gu, g["idx"], T * k, g["xf"], k, g["egu"], s)

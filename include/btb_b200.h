@@ -282,6 +282,14 @@ int btb_b200_moe_route(const void* logits, int ls, int E, int k, int mode, int f
  * wout bf16 [T, k]. The logits and the picks are the two calls' to the bit. H a multiple of 8, E <= 1024. */
 int btb_b200_moe_router(const void* w, const void* x, void* logits, int E, int H, int k, int mode, void* idx, void* wout,
                         int T, void* stream);
+/* btb_b200_add_rmsnorm_wide and btb_b200_moe_router as one launch: the block's residual add, RMSNorm and widen
+ * (btb_add_rmsnorm, btb_kernels.cu:365-393; the row widened to f32 for the host-order experts, btb/engine/host.py:180-186)
+ * in the router launch's prologue. h_in, y_add (may be null), norm_w bf16; h_out the new residual (required with y_add, never
+ * h_in's buffer); xf_out f32 [T, H] the widened normed row (what the experts read), x_out bf16 [T, H] or null. The same
+ * operations in the same order as the two launches: the same bits. */
+int btb_b200_moe_router_norm(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps, int centered,
+                             void* h_out, void* x_out, void* xf_out, void* logits, int E, int H, int k, int mode, void* idx,
+                             void* wout, int T, void* stream);
 /* btb_gemv_lane16_f32_m{M} (btb_kernels.cu:1635-1682): the host's bf16 GEMV order on the card (16 lane sums a row,
  * column c to lane c mod 16, reduce16's fold: native/src/gemv.rs:46-58,85-123). w [R,C] bf16, x [M,C] f32, y [M,R]
  * f32; bit-equal to btb_gemv_bf16_rows. */

@@ -335,3 +335,22 @@ def test_router_cluster_launch_equals_matvec_then_route(E, H, k, mode):
     idx_c, w_c = torch.zeros_like(idx_a), torch.zeros_like(w_a)
     call("btb_b200_moe_router", ptr(wt), ptr(xt), 0, E, H, k, mode, ptr(idx_c), ptr(w_c), T, s())  # without the logits
     assert torch.equal(idx_a, idx_c) and torch.equal(w_a.view(torch.int16), w_c.view(torch.int16))
+    # the block's add + RMSNorm + widen in the router launch's prologue: the bits of the norm's own launch, then the router's
+    hb = torch.from_numpy(O.f32_to_bits(rng.standard_normal((T, H)).astype(np.float32)).view(np.int16)).to(DEV)
+    yb = torch.from_numpy(O.f32_to_bits(rng.standard_normal((T, H)).astype(np.float32) * 0.3).view(np.int16)).to(DEV)
+    nw = torch.from_numpy(O.f32_to_bits(1 + 0.1 * rng.standard_normal(H).astype(np.float32)).view(np.int16)).to(DEV)
+    h1, x1, xf1 = hb.clone(), torch.zeros_like(hb), torch.zeros(T, H, dtype=torch.float32, device=DEV)
+    call("btb_b200_add_rmsnorm_wide", ptr(h1), ptr(yb), ptr(nw), 1e-6, ptr(x1), ptr(xf1), T, H, 0, s())
+    idx_d, w_d, rl_d = torch.zeros_like(idx_a), torch.zeros_like(w_a), torch.zeros_like(rl_a)
+    call("btb_b200_moe_router", ptr(wt), ptr(xf1), ptr(rl_d), E, H, k, mode, ptr(idx_d), ptr(w_d), T, s())
+    h2, x2, xf2 = torch.zeros_like(hb), torch.zeros_like(hb), torch.zeros_like(xf1)
+    idx_e, w_e, rl_e = torch.zeros_like(idx_a), torch.zeros_like(w_a), torch.zeros_like(rl_a)
+    call("btb_b200_moe_router_norm", ptr(wt), ptr(hb), ptr(yb), ptr(nw), 1e-6, 0, ptr(h2), ptr(x2), ptr(xf2), ptr(rl_e), E, H,
+         k, mode, ptr(idx_e), ptr(w_e), T, s())  # fmt: skip
+    torch.cuda.synchronize()
+    assert torch.equal(h1, h2) and torch.equal(x1, x2) and torch.equal(xf1.view(torch.int32), xf2.view(torch.int32))
+    assert torch.equal(rl_d.view(torch.int32), rl_e.view(torch.int32))
+    assert torch.equal(idx_d, idx_e) and torch.equal(w_d.view(torch.int16), w_e.view(torch.int16))
+    with pytest.raises(capi.NativeError):  # the new residual may not land in the buffer other CTAs still read
+        call("btb_b200_moe_router_norm", ptr(wt), ptr(hb), ptr(yb), ptr(nw), 1e-6, 0, ptr(hb), 0, ptr(xf2), 0, E, H, k, mode,
+             ptr(idx_e), ptr(w_e), T, s())  # fmt: skip
