@@ -51,6 +51,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_gemv_fp8": (_I, [_P, _P, _I, _I, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_silu_p12": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_norm": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _P]),
+    "btb_b200_gemv_norm_fp8": (_I, [_P, _P, _I, _I, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _P]),
     "btb_b200_gemv_norm_swiglu": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _F, _I, _P, _P, _I, _I, _I, _I, _P]),
     "btb_b200_p12_rows": (_I, [_P, _I, _I, _I, _P, _P]),
     "btb_b200_p12_tiles": (_SZ, [_LL]),

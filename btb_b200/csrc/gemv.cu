@@ -260,6 +260,9 @@ Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
     const int w_max = M <= 2 ? 32 : (M <= 8 ? 16 : 8);
     int NW = (M <= 2 && t.warps >= 16) ? 16 : 8;
     p.grid = max(1, min(sms * t.ctas_per_sm, (R + 1) / 2));
+    // the warps a CTA is given when the rows divide as evenly either way: 16 for bf16 rows (memory-bound: more warps only
+    // thin the rings), `warps_packed` for rows widened in registers (bound by instruction issue: more warps fill more slots)
+    const int pref = FMT == F_BF16 || t.warps_packed <= 0 ? 16 : min(w_max, t.warps_packed);
     if (t.balance && t.ctas_per_sm == 1 && R >= sms) {
         double best = 0.0;
         for (int g = sms; g >= (sms * 3) / 4; --g) {
@@ -267,7 +270,7 @@ Plan make_plan(int M, int R, int C, bool want_xs, bool norm = false) {
             for (int w = 8; w <= w_max; ++w) {
                 const int per_warp = (per_cta + w - 1) / w;
                 // rows done a unit of time, with a mild preference for more SMs and for the usual 16 warps
-                const double eff = (double)R / ((double)per_warp * g * w) * (0.9 + 0.1 * g / sms) - 0.002 * abs(w - 16);
+                const double eff = (double)R / ((double)per_warp * g * w) * (0.9 + 0.1 * g / sms) - 0.002 * abs(w - pref);
                 if (eff > best + 1e-9) best = eff, p.grid = g, NW = w;
             }
         }
@@ -448,7 +451,8 @@ extern "C" int btb_b200_gemv_bf16_x(const void* w, const void* x, void* y, int T
 static int gemv_norm_impl(const void* w, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
                           const void* esc_row, const void* h_in, const void* y_add, const void* norm_w, float eps,
                           int centered, void* h_out, void* y, int T, int M, int R, int C, bool swiglu, void* stream,
-                          const btb_b200_recv* recv = nullptr, const btb_b200_send* send = nullptr) {
+                          const btb_b200_recv* recv = nullptr, const btb_b200_send* send = nullptr,
+                          const void* fp8_scales = nullptr, int sr = 0, int sc = 0) {
     const bool sends = send != nullptr && send->n != 0;
     int rc = check_dims(w, h_in, sends ? w : y, M, R, C);
     if (rc) return rc;
@@ -474,10 +478,18 @@ static int gemv_norm_impl(const void* w, const void* hi4, const void* table, con
     a.eps = eps, a.centered = centered, a.T = T;
     if ((rc = take_exchange(recv, send, a)) != B2_OK) return rc;
     if (a.recv.pass != nullptr && y_add == nullptr) return B2_ERR_NULL;  // the exchanged input of this form is y_add
-    Plan p = p12 ? make_plan<F_P12>(M, a.R, C, true, true) : make_plan<F_BF16>(M, a.R, C, true, true);
+    const bool fp8 = fp8_scales != nullptr;
+    if (fp8) {
+        if (p12 || swiglu || sr <= 0 || sc <= 0 || R % sr || C % sc || (C & 15) || ((C / sc) & 7)) return B2_ERR_DOMAIN;
+        a.fscales = static_cast<const float*>(fp8_scales);
+        a.fsc = sc, a.fbm = R / sr, a.fbn = C / sc;
+    }
+    Plan p = fp8 ? make_plan<F_FP8>(M, a.R, C, true, true)
+                 : p12 ? make_plan<F_P12>(M, a.R, C, true, true) : make_plan<F_BF16>(M, a.R, C, true, true);
     if (!p.xs) return B2_ERR_DOMAIN;  // too wide to stage: the caller runs btb_b200_add_rmsnorm and the plain GEMV
     a.seg = p.seg, a.stages = p.stages, a.evict_first = b2_tuning().evict_first;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (fp8) return launch_m<F_FP8, X_SMEM_NORM>(M, a, p, s);
     return p12 ? launch_m<F_P12, X_SMEM_NORM>(M, a, p, s) : launch_m<F_BF16, X_SMEM_NORM>(M, a, p, s);
 }
 
@@ -504,6 +516,15 @@ extern "C" int btb_b200_gemv_norm_x(const void* w, const void* h_in, const void*
                                     const btb_b200_recv* recv, const btb_b200_send* send, void* stream) {
     return gemv_norm_impl(w, nullptr, nullptr, nullptr, nullptr, nullptr, h_in, y_add, norm_w, eps, centered, h_out, y, T, M,
                           R, C, swiglu != 0, stream, recv, send);
+}
+
+// btb_b200_gemv_norm over FP8 weights (the widen of btb_b200_gemv_fp8)
+extern "C" int btb_b200_gemv_norm_fp8(const void* w, const void* scales, int sr, int sc, const void* h_in, const void* y_add,
+                                      const void* norm_w, float eps, int centered, void* h_out, void* y, int T, int M, int R,
+                                      int C, void* stream) {
+    if (scales == nullptr) return B2_ERR_NULL;
+    return gemv_norm_impl(w, nullptr, nullptr, nullptr, nullptr, nullptr, h_in, y_add, norm_w, eps, centered, h_out, y, T, M,
+                          R, C, false, stream, nullptr, nullptr, scales, sr, sc);
 }
 
 // FP8 e4m3 weights with an f32 [sr, sc] block-scale grid, each weight the bf16 btb holds for it, widened in registers

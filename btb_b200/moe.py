@@ -196,6 +196,7 @@ class MoEEngine(CardEngine):
             self.passes = torch.zeros(len(CARD_ROWS), dtype=torch.int32, device=self.dev)
             self._ep: dict[int, Any] = {}
         self.fuse_router = True  # the router's matvec and the picks in one cluster launch
+        self.router_fuse_max = int(os.environ.get("BTB_B200_ROUTER_FUSE_MAX", "131072"))  # ... up to this many weights
         # the activation inside the down matvecs' launch, the picks' sum inside the next norm's: fewer launches, the
         # same bits, but measured slower than the separate kernels (one block a token sums the picks; every CTA of the
         # down matvecs repeats the activation) - off unless asked for
@@ -275,13 +276,16 @@ class MoEEngine(CardEngine):
         def normed_matvec(W: Any, norm_w: torch.Tensor, out: torch.Tensor, R: int) -> None:
             """x = norm(h + y_prev) and the matvec over it: one launch where the matrix is bf16 and the pass narrow"""
             nonlocal hcur, halt
-            if fuse and not pending and isinstance(W, torch.Tensor):
-                if y_prev is None:  # the first layer: no add, the residual stays where it is
-                    K_("btb_b200_gemv_norm", ptr(W), 0, 0, 0, 0, 0, ptr(hcur), 0, ptr(norm_w), c.eps, 0, 0, ptr(out), T, M,
-                       R, H, s)  # fmt: skip
+            if fuse and not pending and isinstance(W, (torch.Tensor, FP8Matrix)):
+                # (the first layer: no add, the residual stays where it is)
+                ya, ho = (0, 0) if y_prev is None else (ptr(y_prev), ptr(halt))
+                if isinstance(W, FP8Matrix):
+                    K_("btb_b200_gemv_norm_fp8", ptr(W.w), ptr(W.scales), W.sr, W.sc, ptr(hcur), ya, ptr(norm_w), c.eps, 0,
+                       ho, ptr(out), T, M, R, H, s)  # fmt: skip
                 else:
-                    K_("btb_b200_gemv_norm", ptr(W), 0, 0, 0, 0, 0, ptr(hcur), ptr(y_prev), ptr(norm_w), c.eps, 0,
-                       ptr(halt), ptr(out), T, M, R, H, s)  # fmt: skip
+                    K_("btb_b200_gemv_norm", ptr(W), 0, 0, 0, 0, 0, ptr(hcur), ya, ptr(norm_w), c.eps, 0, ho, ptr(out), T, M,
+                       R, H, s)  # fmt: skip
+                if y_prev is not None:
                     hcur, halt = halt, hcur
                 return
             norm_in(norm_w)
@@ -295,7 +299,7 @@ class MoEEngine(CardEngine):
             # the picks, the experts, the sum
             # one cluster launch for the norm, the router's matvec and the picks where the router is small enough for it
             # to win (measured: 32 experts x 2880 yes, 128 x 2048 no)
-            if self.fuse_router and H % 8 == 0 and E * H <= 131072:
+            if self.fuse_router and H % 8 == 0 and E * H <= self.router_fuse_max:
                 K_("btb_b200_moe_router_norm", ptr(L.router), ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, 0, ptr(halt), 0,
                    ptr(g["xf"]), 0, E, H, k, c.router_mode, ptr(g["idx"]), ptr(g["rw"]), T, s)  # fmt: skip
                 hcur, halt = halt, hcur

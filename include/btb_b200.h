@@ -93,6 +93,10 @@ int btb_b200_gemv_silu_p12(const void* lo, const void* hi4, const void* table, c
 int btb_b200_gemv_norm(const void* w, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
                        const void* esc_row, const void* h_in, const void* y_add, const void* norm_w, float eps,
                        int centered, void* h_out, void* y, int T, int M, int R, int C, void* stream);
+/* btb_b200_gemv_norm over FP8 weights: the prologue above, the widen of btb_b200_gemv_fp8 (scales f32 [sr, sc]) */
+int btb_b200_gemv_norm_fp8(const void* w, const void* scales, int sr, int sc, const void* h_in, const void* y_add,
+                           const void* norm_w, float eps, int centered, void* h_out, void* y, int T, int M, int R, int C,
+                           void* stream);
 /* the same with the SwiGLU of btb_silu_mul (btb_kernels.cu:481-484) in the epilogue: w is the merged gate/up block
  * [R = 2I, C] (gate rows, then up rows: btb/engine/cuda.py:1131-1164); a warp takes gate row p and up row p + I one
  * after the other and writes m[t][p] = bf16(bf16(silu(g)) * u) over the two bf16-rounded outputs - the bits

@@ -261,6 +261,28 @@ def test_gemv_fp8_equals_bf16_gemv_over_held_weights(R, Cc, sr, sc, M):
     assert np.array_equal(bits(y), want)
 
 
+@pytest.mark.parametrize("R,H,sr,sc", [(384, 2048, 3, 16), (5120, 2048, 40, 16), (128, 768, 1, 6)])
+@pytest.mark.parametrize("M,T,add", [(1, 1, True), (1, 1, False), (8, 5, True)])
+def test_gemv_fp8_with_norm_prologue_equals_two_kernels(R, H, sr, sc, M, T, add):
+    rng = np.random.default_rng(R + H + M)
+    w8 = rng.integers(0, 256, size=(R, H), dtype=np.uint8)
+    w8[(w8 & 0x7F) == 0x7F] = 0x2A
+    scales = O.bits_to_f32(O.f32_to_bits(rng.standard_normal((sr, sc)).astype(np.float32) * 0.02))
+    h0, yv, nw = rand_bf(rng, (M, H)), rand_bf(rng, (M, H), 0.1), rand_bf(rng, (H,))
+    wt, st, nt = torch.from_numpy(w8).to(DEV), torch.from_numpy(scales).to(DEV), bf(nw)
+    yt = bf(yv) if add else None
+    h1, x1, y1 = bf(h0), torch.zeros(M, H, dtype=torch.bfloat16, device=DEV), torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_add_rmsnorm", ptr(h1), ptr(yt), ptr(nt), 1e-6, ptr(x1), T, H, 0, s())
+    call("btb_b200_gemv_fp8", ptr(wt), ptr(st), sr, sc, ptr(x1), ptr(y1), M, R, H, s())
+    hin, hout, y2 = bf(h0), torch.zeros(M, H, dtype=torch.bfloat16, device=DEV), torch.zeros(M, R, dtype=torch.bfloat16, device=DEV)
+    call("btb_b200_gemv_norm_fp8", ptr(wt), ptr(st), sr, sc, ptr(hin), ptr(yt), ptr(nt), 1e-6, 0, ptr(hout) if add else 0,
+         ptr(y2), T, M, R, H, s())  # fmt: skip
+    assert torch.equal(y1[:T].view(torch.int16), y2[:T].view(torch.int16))
+    assert np.array_equal(bits(hin), h0)
+    if add:
+        assert torch.equal(h1[:T].view(torch.int16), hout[:T].view(torch.int16))
+
+
 # ---- the small kernels -------------------------------------------------------------------------------------------
 
 
