@@ -553,6 +553,30 @@ class CardEngine:
             toks.append(int(self.pin_tok[0]))
         return toks
 
+    def continue_from(self, logits: torch.Tensor, max_new: int, sampling: Any = None) -> list[int]:
+        """`max_new` tokens after the cache's rows, given the logits that follow them ([V] or [1, V], any float dtype as
+        long as the values are the pass's bf16 logits): the first picked from `logits`, the rest by the step graph - what
+        `generate_greedy` does after its prefill. The last token is drawn but not fed (its row is not in the cache)."""
+        if sampling is not None:
+            self.set_sampling(sampling)
+        g = self.bufs(1)
+        s = capi.stream_ptr()
+        last = logits.reshape(1, -1).to(self.dev, torch.bfloat16).contiguous()
+        self._pick({"logits": last, "pick": g["pick"], "depth": self._before}, 1, s, g["ids"])
+        toks = [int(g["ids"][0].item())]
+        graph = self.step_graph(1, publish=True)
+        while len(toks) < max_new:
+            graph.replay()
+            torch.cuda.current_stream().synchronize()
+            toks.append(int(self.pin_tok[0]))
+        return toks
+
+    def session(self) -> Any:
+        """a `Session` over this engine (btb's `model.session()`)"""
+        from .session import Session
+
+        return Session(self)
+
     def generate_speculative(self, prompt: Any, max_new: int, budget: int = 8, v_max: int = 8) -> tuple[list[int], dict]:
         """greedy decode with n-gram tree drafts verified a tree a pass (btb/engine/generate.py:682-795); the tokens
         are generate_greedy's"""

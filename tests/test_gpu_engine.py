@@ -211,3 +211,34 @@ def test_tiny_qwen3_fixture_on_the_card(golden_dir):
     assert np.max(np.abs(got - ref)) <= 0.05 * np.max(np.abs(ref))
     assert int(np.argmax(ref)) == int(np.argmax(got))
     assert eng.generate_greedy(prompt, 10) == tiny["rc/bf16/greedy"].tolist()
+
+
+def test_session_feed_mark_rewind_equal_a_fresh_decode():
+    """btb's session surface over the card engine: a fed draft's logits are the pass's rows, a rewind drops exactly the
+    rows after the mark, and decoding on from a rewound session gives the tokens a fresh prompt gives"""
+    from btb_b200.session import State
+
+    mw = E.synth_weights(SMALL, seed=3, layer_std=LAYER_STD)
+    eng = E.CardEngine(mw, cap=512)
+    prompt = torch.randint(0, SMALL.vocab, (45,), generator=torch.Generator().manual_seed(2)).tolist()
+    want = eng.generate_greedy(torch.tensor(prompt), 12)
+    lively(want)
+    s = eng.session()
+    st = s.feed(prompt)
+    assert st.logits.shape == (45, SMALL.vocab) and s.state is State.READY
+    assert int(st.logits[-1].argmax()) == want[0]
+    m = s.mark()
+    wrong = [(t + 1) % SMALL.vocab for t in want[:5]]
+    s.feed(wrong)  # a draft the target rejects
+    s.rewind(m)
+    assert len(s) == 45 and int(eng.n0) == 45
+    assert s.generate(12) == want and s.state is State.PENDING
+    # on from the pending token: the same as one longer decode
+    more = s.generate(4)
+    assert want + more == eng.generate_greedy(torch.tensor(prompt), 16)
+    # crop back into the prompt and feed the rest again: the same logits as the first feed's
+    s2 = eng.session()
+    first = s2.feed(prompt).logits.clone()
+    s2.crop(20)
+    again = s2.feed(prompt[20:]).logits
+    assert torch.equal(again, first[20:])
