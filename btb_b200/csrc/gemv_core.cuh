@@ -248,11 +248,17 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
 // first global column c0 of `row`. Lane l takes local chunks l, l + 32, .. - segments are multiples of 256 columns,
 // so these are the row's chunks l, l + 32, .. in order - and a chunk's elements in index order, one fmaf each.
 // xv: x in shared memory [M, C] (XS) or in global memory (read-only path: the standalone kernels' wide passes only).
-template <int M, int FMT, bool XS>
-__device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* stg, int seg, int nch, int c0, int row,
-                                              int C, const bf16* xv, const WidenCtx& W, int lane) {
+// ESC: the row has pack12 escapes (most rows have none: their loop carries no test for code 15 at all)
+template <int M, int FMT, bool XS, bool ESC>
+__device__ __forceinline__ void consume_stage_rows(float (&acc)[M], const uint8_t* stg, int seg, int nch, int c0, int row,
+                                                   int C, const bf16* xv, const WidenCtx& W, int lane) {
+    // every lane makes the same number of whole rounds (the trip count is the warp's, not the lane's: no divergence
+    // bookkeeping a chunk), then the lanes under the remainder make one more
+    const int rounds = nch >> 5, total = rounds + ((nch & 31) != 0);
 #pragma unroll 4
-    for (int lc = lane; lc < nch; lc += 32) {
+    for (int it = 0; it < total; ++it) {
+        const int lc = lane + (it << 5);
+        if (it == rounds && lc >= nch) break;
         uint32_t wp[4];
         if (FMT == F_FP8) {
             const uint2 wb = *reinterpret_cast<const uint2*>(stg + lc * 8);
@@ -271,8 +277,8 @@ __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* st
                 p12_chunk(lo.x, lo.y, codes, W.table, wp);
                 // a code of 15 is an escape: its high byte comes from the row's list (most rows have none: the test for
                 // code 15 is made only in rows that do)
-                const uint32_t f = W.e1 > W.e0 ? codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u : 0u;
-                if (f != 0u) {
+                const uint32_t f = ESC && W.e1 > W.e0 ? codes & (codes >> 1) & (codes >> 2) & (codes >> 3) & 0x11111111u : 0u;
+                if (ESC && f != 0u) {
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         if ((f >> (4 * e)) & 1u) {
@@ -299,4 +305,11 @@ __device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* st
             acc[m] = a;
         }
     }
+}
+template <int M, int FMT, bool XS>
+__device__ __forceinline__ void consume_stage(float (&acc)[M], const uint8_t* stg, int seg, int nch, int c0, int row,
+                                              int C, const bf16* xv, const WidenCtx& W, int lane) {
+    // (wide passes keep one copy of the loop: their accumulators already fill the register file)
+    if (FMT == F_P12 && (M > 8 || W.e1 > W.e0)) consume_stage_rows<M, FMT, XS, true>(acc, stg, seg, nch, c0, row, C, xv, W, lane);
+    else consume_stage_rows<M, FMT, XS, M <= 8 ? false : true>(acc, stg, seg, nch, c0, row, C, xv, W, lane);
 }
