@@ -101,6 +101,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_moe_gemv_act": (
         _I, [_I, _P, _P, _LL, _LL, _I, _I, _P, _I, _I, _P, _I, _F, _F, _P, _I, _I, _I, _I, _P],
     ),
+    "btb_b200_moe_gemv_glu": (_I, [_I, _P, _P, _LL, _LL, _I, _I, _P, _I, _I, _P, _I, _P, _I, _I, _I, _F, _F, _I, _I, _P]),
     "btb_b200_moe_combine_norm": (_I, [_P, _P, _P, _I, _P, _P, _F, _P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_moe_act": (_I, [_P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
     "btb_b200_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),

@@ -252,13 +252,8 @@ __device__ __forceinline__ void stage_x_norm(bf16* xs, float* scratch, const bf1
 template <int M, int FMT, bool XS, bool ESC>
 __device__ __forceinline__ void consume_stage_rows(float (&acc)[M], const uint8_t* stg, int seg, int nch, int c0, int row,
                                                    int C, const bf16* xv, const WidenCtx& W, int lane) {
-    // every lane makes the same number of whole rounds (the trip count is the warp's, not the lane's: no divergence
-    // bookkeeping a chunk), then the lanes under the remainder make one more
-    const int rounds = nch >> 5, total = rounds + ((nch & 31) != 0);
 #pragma unroll 4
-    for (int it = 0; it < total; ++it) {
-        const int lc = lane + (it << 5);
-        if (it == rounds && lc >= nch) break;
+    for (int lc = lane; lc < nch; lc += 32) {
         uint32_t wp[4];
         if (FMT == F_FP8) {
             const uint2 wb = *reinterpret_cast<const uint2*>(stg + lc * 8);

@@ -27,7 +27,8 @@ bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_st
                       int R, int C, int sr, int sc);
 int b2_moe_stream_launch(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
                          const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C, int ep_rank,
-                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s, const B2Send* send = nullptr);
+                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s, const B2Send* send = nullptr,
+                         int glu_kind = -1, void* glu_out = nullptr);
 
 namespace {
 
@@ -399,6 +400,22 @@ __global__ void __launch_bounds__(256) moe_combine(const CombineArgs A) {
     const bool marked = A.recv.pass != nullptr;
     const uint32_t mark = marked ? b2_hop_mark(A.recv.pass, A.recv.per_pass, A.recv.base) : 0u;
     float fin = 0.f;
+    if (!marked && A.bias == nullptr && k <= 8) {
+        // every pick's product and weight on their way at once (the sum itself is a chain): one round trip, not k
+        float pv[8];
+        unsigned short pw[8];
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const size_t q = (size_t)t * k + (a < k ? order[a] : 0);
+            pv[a] = a < k ? __ldcg(A.dn + q * A.H + c) : 0.f;
+            pw[a] = a < k ? __ldcg(reinterpret_cast<const unsigned short*>(A.w) + q) : (unsigned short)0;
+        }
+#pragma unroll
+        for (int a = 0; a < 8; ++a)
+            if (a < k) fin = bfround(fin + bfround(bfround(pv[a]) * __uint_as_float((uint32_t)pw[a] << 16)));
+        A.y[(size_t)t * A.H + c] = f2bf(fin);
+        return;
+    }
     for (int a = 0; a < k; ++a) {
         const int s = order[a];
         const size_t q = (size_t)t * k + s;
@@ -620,6 +637,22 @@ extern "C" int btb_b200_moe_gemv_act(int fmt, const void* w, const void* scales,
     if (!b2_moe_stream_ok(fmt, w, scales, w_stride, s_stride, gu, R, C, sr, sc)) return B2_ERR_DOMAIN;
     return b2_moe_stream_launch(fmt, w, scales, w_stride, s_stride, sr, sc, idx, n_tasks, E, gu, 1, y, R, C, ep_rank,
                                 ep_size, kind, alpha, limit, static_cast<cudaStream_t>(stream));
+}
+
+// the picked experts' GATE/UP matvecs with the gated activation made on the way out: h row of task i [R/2] = act(the
+// task's [R] outputs). btb_b200_moe_gemv followed by btb_b200_moe_act, one launch and no [n, R] buffer. No bias.
+extern "C" int btb_b200_moe_gemv_glu(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride,
+                                     int sr, int sc, const void* idx, int n_tasks, int E, const void* x, int x_div, void* h,
+                                     int R, int C, int kind, float alpha, float limit, int ep_rank, int ep_size,
+                                     void* stream) {
+    if (!w || !x || !h || (fmt != L_BF16 && !scales)) return B2_ERR_NULL;
+    if (n_tasks <= 0 || n_tasks > 65535 || R <= 0 || C <= 0 || x_div <= 0 || E <= 0 || ep_size < 1 || ep_rank < 0 ||
+        ep_rank >= ep_size || (kind != 0 && kind != 1))
+        return B2_ERR_DOMAIN;
+    if (fmt == L_FP8 && (sr <= 0 || sc <= 0 || R % sr || C % sc)) return B2_ERR_DOMAIN;
+    if (!b2_moe_stream_ok(fmt, w, scales, w_stride, s_stride, x, R, C, sr, sc)) return B2_ERR_DOMAIN;
+    return b2_moe_stream_launch(fmt, w, scales, w_stride, s_stride, sr, sc, idx, n_tasks, E, x, x_div, nullptr, R, C, ep_rank,
+                                ep_size, -1, alpha, limit, static_cast<cudaStream_t>(stream), nullptr, kind, h);
 }
 
 extern "C" int btb_b200_moe_act(const void* gu, void* h, const void* bias, const void* idx, int n, int I, int kind,

@@ -58,6 +58,11 @@ struct MSArgs {
     // over interleaved lanes - every bf16 rounding of the host's torch ops kept
     int act_kind;
     float alpha, limit;
+    // the gated activation made on the way OUT of the gate/up matvecs (the same operations): glu_kind 0 pairs gate row j
+    // with up row R/2 + j (a warp takes four of each), 1 pairs rows 2j and 2j + 1; the task's activated row [R/2] goes to
+    // glu_out and y is not written. -1: plain outputs
+    int glu_kind;
+    float* glu_out;
     // experts cut over ranks (tp.cuh): with send.n > 0 a finished output of an expert this rank holds goes to every
     // rank's copy of the [n_tasks, R] vector as a marked word carrying bf16(sum) - the rounding the ordered sum applies
     // to a product first thing - and another rank's experts' rows are left to their owner
@@ -67,6 +72,18 @@ struct MSArgs {
 __device__ __forceinline__ float moe_act_value(const float* gu, int c, int I, int kind, float alpha, float limit) {
     const int gi = kind == 0 ? c : 2 * c, ui = kind == 0 ? I + c : 2 * c + 1;
     float g = bfround(__ldcg(gu + gi)), u = bfround(__ldcg(gu + ui));
+    if (kind == 0) return bfround(bfround(g / (1.f + expf(-g))) * u);
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    const float t1 = bfround(g * alpha);
+    const float t2 = bfround(1.f / (1.f + expf(-t1)));
+    const float glu = bfround(g * t2);
+    return bfround(bfround(u + 1.f) * glu);
+}
+
+// the gated activation of one (gate, up) pair of f32 outputs: moe_act_value's operations
+__device__ __forceinline__ float moe_act_pair(float g, float u, int kind, float alpha, float limit) {
+    g = bfround(g), u = bfround(u);
     if (kind == 0) return bfround(bfround(g / (1.f + expf(-g))) * u);
     g = fminf(g, limit);
     u = fminf(fmaxf(u, -limit), limit);
@@ -200,6 +217,10 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
     const int ri = lane / TPR, q = lane % TPR;  // the thread's row of the warp's RB, its chains q CPT .. q CPT + CPT - 1
     const int task = blockIdx.y;
     const int R = A.R, C = A.C, seg = A.seg, S = A.stages;
+    // the row a group's slot holds: eight consecutive rows, or (glu_kind 0, four threads a row) four gate rows and the four
+    // up rows they pair with
+    const bool halves = TPR == 4 && A.glu_kind == 0;
+    auto row_of = [&](int grp, int slot) { return halves ? (slot < 4 ? grp * 4 + slot : (R >> 1) + grp * 4 + slot - 4) : grp * RB + slot; };
     constexpr int CB2 = col_bytes2<FMT>();
     const int row_bytes = C * CB2 / 2;
     const int stride = seg * CB2 / 2 + PAD;  // a stage row
@@ -241,8 +262,11 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
     if (!mine) {  // another rank's expert (or a refused pick): zeros, so that the ranks' sum is the whole
         if (A.send.n != 0) return;  // (under the exchange the owner writes the row into every rank's copy)
         for (int g = g0 + warp; g < g0 + gc; g += nw) {
-            const int r = g * RB + ri;
-            if (r < R && q == 0) A.y[(size_t)task * R + r] = 0.f;
+            const int r = row_of(g, ri);
+            if (r < R && q == 0) {
+                if (A.glu_kind < 0) A.y[(size_t)task * R + r] = 0.f;
+                else if (A.glu_kind == 0 ? r < (R >> 1) : !(r & 1)) A.glu_out[(size_t)task * (R >> 1) + (A.glu_kind == 0 ? r : r >> 1)] = 0.f;
+            }
         }
         return;
     }
@@ -253,14 +277,14 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
     auto issue_next = [&]() {
         const int c0 = p_seg * seg;
         const int n = min(seg, C - c0);
-        const int rows = min(RB, R - p_grp * RB);
+        const int rows = halves ? RB : min(RB, R - p_grp * RB);  // (halves: R/2 a multiple of four, every group whole)
         const uint32_t nb = (uint32_t)(n * CB2 / 2);
         const uint32_t bar = smem_u32(bars + p_st);
         if (lane == 0) mbar_expect_tx(bar, nb * rows);
         __syncwarp();
         // (a copy a lane: one lane issuing the group's copies in a straight line was measured at more instructions)
         if (lane < rows) {
-            const uint8_t* src = wbase + (size_t)(p_grp * RB + lane) * row_bytes + (size_t)c0 * CB2 / 2;
+            const uint8_t* src = wbase + (size_t)row_of(p_grp, lane) * row_bytes + (size_t)c0 * CB2 / 2;
             bulk_g2s_hint(smem_u32(ring + (size_t)p_st * sbytes + (size_t)lane * stride), src, nb, bar, pol);
         }
         ++issued;
@@ -311,7 +335,7 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
     bool ok = true;
     int i = 0;
     for (; i < n_items; ++i) {
-        const int r = c_grp * RB + ri;
+        const int r = row_of(c_grp, ri);
         const bool live = r < R;
         const int c0 = c_seg * seg;
         const int n = min(seg, C - c0);
@@ -508,7 +532,13 @@ __global__ void __launch_bounds__(MAXW * 32, TPR == 4 ? 1 : 2) moe_gemv_stream(c
             float s = CPT == 4 ? (acc[0] + acc[1 % CPT]) + (acc[2 % CPT] + acc[3 % CPT]) : CPT == 2 ? acc[0] + acc[1 % CPT] : acc[0];
 #pragma unroll
             for (int o = 1; o < TPR; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if (live && q == 0) {
+            if (A.glu_kind >= 0) {
+                // the row's partner (its up row, or its gate row) sits TPR lanes away (rows 2j, 2j + 1) or four rows away
+                const float other = __shfl_xor_sync(0xffffffffu, s, A.glu_kind == 0 ? 4 * TPR : TPR);
+                const bool gate = A.glu_kind == 0 ? ri < 4 : !(ri & 1);
+                if (live && q == 0 && gate)
+                    A.glu_out[(size_t)task * (R >> 1) + (A.glu_kind == 0 ? r : r >> 1)] = moe_act_pair(s, other, A.glu_kind, A.alpha, A.limit);
+            } else if (live && q == 0) {
                 if (A.send.n == 0) {
                     A.y[(size_t)task * R + r] = s;
                 } else {
@@ -615,11 +645,23 @@ bool b2_moe_stream_ok(int fmt, const void* w, const void* scales, long long w_st
 
 int b2_moe_stream_launch(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
                          const void* idx, int n_tasks, int E, const void* x, int x_div, void* y, int R, int C, int ep_rank,
-                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s, const B2Send* send) {
+                         int ep_size, int act_kind, float alpha, float limit, cudaStream_t s, const B2Send* send,
+                         int glu_kind, void* glu_out) {
     MSArgs a{static_cast<const uint8_t*>(w), static_cast<const uint8_t*>(scales), w_stride, s_stride,
              static_cast<const int*>(idx), static_cast<const float*>(x), x_div, static_cast<float*>(y), R, C,
-             sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size, 0, 0, act_kind, alpha, limit, B2Send{}};
+             sr > 0 ? sr : 1, sc > 0 ? sc : 1, E, ep_rank, ep_size, 0, 0, act_kind, alpha, limit, glu_kind,
+             static_cast<float*>(glu_out), B2Send{}};
     if (send != nullptr) a.send = *send;
+    if (glu_kind >= 0) {
+        // pairs live in one warp: four threads a row (eight rows a warp), whole groups
+        if (glu_out == nullptr || send != nullptr || act_kind >= 0 || (R & 7) || (glu_kind == 0 && ((R >> 1) & 3))) return B2_ERR_DOMAIN;
+        switch (fmt) {
+            case S_BF16: return launch_stream_t<S_BF16, 4>(a, n_tasks, s);
+            case S_MX4: return launch_stream_t<S_MX4, 4>(a, n_tasks, s);
+            case S_FP8: return launch_stream_t<S_FP8, 4>(a, n_tasks, s);
+            default: return B2_ERR_DOMAIN;
+        }
+    }
     switch (fmt) {
         case S_BF16: return launch_stream<S_BF16>(a, n_tasks, s);
         case S_MX4: return launch_stream<S_MX4>(a, n_tasks, s);

@@ -201,6 +201,7 @@ class MoEEngine(CardEngine):
         # same bits, but measured slower than the separate kernels (one block a token sums the picks; every CTA of the
         # down matvecs repeats the activation) - off unless asked for
         self.fold = os.environ.get("BTB_B200_MOE_FOLD", "0") != "0"
+        self.glu_epilogue = os.environ.get("BTB_B200_MOE_GLU", "1") != "0"  # the gated activation in the gate/up launch
 
     @staticmethod
     def heap_bytes(c: MoEConfig) -> int:
@@ -308,7 +309,15 @@ class MoEEngine(CardEngine):
                    0, s)  # fmt: skip
                 K_("btb_b200_moe_gemv", 0, ptr(L.router), 0, 0, 0, 1, 1, 0, T, 1, ptr(g["xf"]), 1, ptr(g["rl"]), E, H, 0, 1, s)
                 K_("btb_b200_moe_route", ptr(g["rl"]), E, E, k, c.router_mode, 1, ptr(g["idx"]), ptr(g["rw"]), T, s)
-            self._expert_gemv(L.gu, g["idx"], T * k, g["xf"], k, g["egu"], s)
+            # the gate/up matvecs, the gated activation in their epilogue where the layout lets a warp hold a pair's rows
+            sg = L.gu
+            glu = self.glu_epilogue and not fold and I % 4 == 0 and sg.C % 32 == 0 and getattr(L, "gu_bias", None) is None
+            if glu:
+                K_("btb_b200_moe_gemv_glu", FMT[sg.fmt], ptr(sg.w), ptr(sg.scales), sg.w_stride, sg.s_stride, sg.sr, sg.sc,
+                   ptr(g["idx"]), T * k, E, ptr(g["xf"]), k, ptr(g["eh"]), sg.R, sg.C, c.glu_kind, c.alpha, c.limit,
+                   self.ep_rank, self.ep_size, s)  # fmt: skip
+            else:
+                self._expert_gemv(L.gu, g["idx"], T * k, g["xf"], k, g["egu"], s)
             st = L.dn
             if fold and I % 32 == 0:
                 # the gated activation is made inside the down matvecs' launch
@@ -318,7 +327,8 @@ class MoEEngine(CardEngine):
             elif self.ep_size > 1:
                 # this rank's picks: the products go, rounded and marked, into every rank's copy; the sum takes them there
                 sends, recvs, local, _ = self.ep_descs(M)
-                K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
+                if not glu:
+                    K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
                 K_("btb_b200_moe_gemv_x", FMT[st.fmt], ptr(st.w), ptr(st.scales), st.w_stride, st.s_stride, st.sr, st.sc,
                    ptr(g["idx"]), T * k, E, ptr(g["eh"]), 1, st.R, st.C, self.ep_rank, self.ep_size, sends[i], s)  # fmt: skip
                 yield  # (engines standing in for the ranks on one GPU take turns here)
@@ -326,7 +336,8 @@ class MoEEngine(CardEngine):
                 y_prev = g["y"]
                 continue
             else:
-                K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
+                if not glu:
+                    K_("btb_b200_moe_act", ptr(g["egu"]), ptr(g["eh"]), 0, 0, T * k, I, c.glu_kind, c.alpha, c.limit, s)
                 self._expert_gemv(L.dn, g["idx"], T * k, g["eh"], 1, g["edn"], s)
             if fold:
                 pending = True

@@ -326,6 +326,14 @@ int btb_b200_moe_act(const void* gu, void* h, const void* bias, const void* idx,
 int btb_b200_moe_gemv_act(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr,
                           int sc, const void* idx, int n_tasks, int E, const void* gu, int kind, float alpha,
                           float limit, void* y, int R, int C, int ep_rank, int ep_size, void* stream);
+/* the picked experts' GATE/UP matvecs with the gated activation (btb/engine/host.py:439-450) made on the way out: h f32
+ * [n_tasks, R/2] row i = act(task i's [R] outputs), every bf16 rounding of the host's torch ops kept; the [n_tasks, R]
+ * outputs are never written. kind 0 pairs gate row j with up row R/2 + j (silu(gate) * up), 1 pairs rows 2j and 2j + 1
+ * (gpt-oss's clamped GLU with alpha, limit). btb_b200_moe_gemv followed by btb_b200_moe_act, one launch. No bias. Shapes
+ * the streaming kernel takes, R a multiple of 8. */
+int btb_b200_moe_gemv_glu(int fmt, const void* w, const void* scales, long long w_stride, long long s_stride, int sr, int sc,
+                          const void* idx, int n_tasks, int E, const void* x, int x_div, void* h, int R, int C, int kind,
+                          float alpha, float limit, int ep_rank, int ep_size, void* stream);
 /* host.py:426-431,565-569: out_e = bf16(down_e) (+ bias [E,H]) * w_e, summed one bf16 add at a time in ascending
  * expert id from zero. dn f32 [T,k,H], y bf16 [T,H]. */
 int btb_b200_moe_combine(const void* dn, const void* idx, const void* w, const void* bias, void* y, int T, int k, int H,

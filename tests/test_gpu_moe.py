@@ -293,6 +293,54 @@ def test_expert_gemv_stream_equals_the_cpu_tier_bits(R, C_, n, k, fmt, xbf):
     assert all(bool((parts[int(idx[i]) % 2 ^ 1][i] == 0).all()) for i in range(n))
 
 
+@pytest.mark.parametrize("I,C_,n,k", [(768, 2048, 8, 8), (2880, 2880, 4, 4), (20, 96, 3, 1), (100, 64, 5, 5)])
+@pytest.mark.parametrize("fmt", ["bf16", "mx4", "fp8"])
+@pytest.mark.parametrize("kind", [0, 1])
+def test_expert_gate_up_with_the_activation_in_its_epilogue(I, C_, n, k, fmt, kind):
+    """btb_b200_moe_gemv_glu: the activated rows are btb_b200_moe_gemv's outputs through btb_b200_moe_act, bit for bit"""
+    rng = np.random.default_rng(I + C_ + n + kind)
+    E, R = 5, 2 * I
+    idx = rng.integers(0, E, size=n).astype(np.int32)
+    x = O.bfround(rng.standard_normal(((n + k - 1) // k, C_)).astype(np.float32) * 2)
+    xt, it = torch.from_numpy(x).to(DEV), torch.from_numpy(idx).to(DEV)
+    if fmt == "bf16":
+        wb = O.f32_to_bits(rng.standard_normal((E, R, C_)).astype(np.float32) * 0.05)
+        keep = [torch.from_numpy(wb.view(np.int16)).to(DEV)]
+        args = (0, ptr(keep[0]), 0, R * C_ * 2, 0, 1, 1)
+    elif fmt == "mx4":
+        blocks, scales = _mx4(rng, E, R, C_)
+        keep = [torch.from_numpy(blocks).to(DEV), torch.from_numpy(scales).to(DEV)]
+        args = (1, ptr(keep[0]), ptr(keep[1]), R * C_ // 2, R * C_ // 32, 1, 1)
+    else:
+        sr = next(d for d in (12, 8, 4, 2, 1) if R % d == 0)
+        sc = C_ // 128 if C_ % 128 == 0 else C_ // 32
+        w8, s8 = _fp8(rng, E, R, C_, sr, sc)
+        keep = [torch.from_numpy(w8).to(DEV), torch.from_numpy(s8).to(DEV)]
+        args = (2, ptr(keep[0]), ptr(keep[1]), R * C_, sr * sc * 4, sr, sc)
+    f, w, sc_, ws, ss, sr_, scn = args
+    y = torch.zeros(n, R, dtype=torch.float32, device=DEV)
+    h1 = torch.zeros(n, I, dtype=torch.float32, device=DEV)
+    call("btb_b200_moe_gemv", f, w, sc_, ws, ss, sr_, scn, ptr(it), n, E, ptr(xt), k, ptr(y), R, C_, 0, 1, s())
+    call("btb_b200_moe_act", ptr(y), ptr(h1), 0, 0, n, I, kind, 1.702, 7.0, s())
+    h2 = torch.full((n, I), 5.0, dtype=torch.float32, device=DEV)
+    call("btb_b200_moe_gemv_glu", f, w, sc_, ws, ss, sr_, scn, ptr(it), n, E, ptr(xt), k, ptr(h2), R, C_, kind, 1.702, 7.0, 0, 1,
+         s())  # fmt: skip
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    assert torch.equal(h1.view(torch.int32), h2.view(torch.int32))
+    assert float(h1.abs().max()) > 0
+    # expert parallel: a rank activates its own picks' rows, zeros for the others'
+    h3 = torch.full((n, I), 5.0, dtype=torch.float32, device=DEV)
+    call("btb_b200_moe_gemv_glu", f, w, sc_ if sc_ else 0, 2 * ws, 2 * ss, sr_, scn, ptr(it), n, E, ptr(xt), k, ptr(h3), R, C_, kind,
+         1.702, 7.0, 0, 2, s())  # fmt: skip
+    torch.cuda.synchronize()
+    for i in range(n):
+        if int(idx[i]) % 2 == 0:
+            assert torch.equal(h3[i].view(torch.int32), h1[i].view(torch.int32)), i
+        else:
+            assert not h3[i].any()
+
+
 @pytest.mark.parametrize("name", list(SMALL))
 def test_folded_moe_pass_equals_the_unfolded_pass(name):
     """the activation inside the down matvecs' launch and the picks' sum inside the next norm's change no bit"""
