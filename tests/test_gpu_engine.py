@@ -100,6 +100,24 @@ def test_greedy_tokens_equal_the_oracle(small):
     assert capi.status() == 0
 
 
+def test_a_wrong_but_valid_cache_position_fails_the_token_comparison(small):
+    """the token tests can fail: the same decode with the cache one row short after the prompt (every later row written a
+    slot early, every position off by one - all in range) no longer passes the comparison against the oracle"""
+    mw, eng = small
+    ow = oracle_weights(mw)
+    orc = OM.CardPath(ow, cap=eng.cap, tables=(bits(eng.cos), bits(eng.sin)))
+    rng = np.random.default_rng(1)
+    prompt = rng.integers(0, SMALL.vocab, size=40).tolist()
+    want, rows = oracle_trace(orc, prompt, 24)
+    eng.reset()
+    last = eng.prefill(torch.tensor(prompt))
+    eng.n0.sub_(1)  # the fault
+    bad = eng.continue_from(last[0], 24)
+    with pytest.raises(AssertionError):
+        same_tokens_or_near_tie(bad, want, rows, min_equal=8)
+    assert capi.status() == 0
+
+
 def test_step_graph_equals_eager_steps_and_verify_rows(small):
     """the reference's card-graph invariants (tests/integration/test_card_graph.py:96-203 of btb): the graph loop's
     tokens are the step-by-step tokens, and row t of a chain pass is bit-equal to the step at its position"""
