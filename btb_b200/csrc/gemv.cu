@@ -330,7 +330,9 @@ int launch_nw(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
 template <int M, int FMT, int XM>
 int launch_one(const GemvArgs& a, const Plan& p, cudaStream_t stream) {
     // one instance a register budget: up to 16 warps (128 registers a thread) and, for one- and two-row passes, up to 32
-    if (M <= 2 && p.nw > 16) return launch_nw<M, FMT, XM, (M <= 2 ? 32 : 8)>(a, p, stream);
+    if (M <= 2 && p.nw > 24) return launch_nw<M, FMT, XM, (M <= 2 ? 32 : 8)>(a, p, stream);
+    // (24 warps leave a thread 80 registers: the packed formats' decode tables stay in them)
+    if (M <= 2 && p.nw > 16) return launch_nw<M, FMT, XM, (M <= 2 ? 24 : 8)>(a, p, stream);
     if (M <= 8 && p.nw > 8) return launch_nw<M, FMT, XM, (M <= 8 ? 16 : 8)>(a, p, stream);
     return launch_nw<M, FMT, XM, 8>(a, p, stream);
 }
