@@ -93,6 +93,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_publish": (_I, [_P, _P, _P, _P, _P, _I, _P]),
     "btb_b200_moe_route": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _I, _P]),
     "btb_b200_moe_router": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
+    "btb_b200_moe_router_grid": (_I, [_P, _P, _P, _P, _F, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
     "btb_b200_moe_router_norm": (_I, [_P, _P, _P, _P, _F, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
     "btb_b200_gemv_lane16_f32": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_lane16_mx4_f32": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),

@@ -196,11 +196,22 @@ __global__ void __cluster_dims__(RR_CTAS, 1, 1) __launch_bounds__(ROUTE_THREADS)
     float* pr = lg + E;                                                          // [E]
     const int wstride = H + 8;                                                   // bf16 elements: rows 16 bytes apart in banks
     bf16* wrows = reinterpret_cast<bf16*>(rsm + ((((size_t)H + 2 * (size_t)E) * 4 + 15) & ~(size_t)15));  // [16][H + 8]
+    const int per = (E + RR_CTAS - 1) / RR_CTAS;
+    const int r_lo = rank * per, r_hi = min(E, r_lo + per);
+    const int hv0 = H >> 3;
+    auto stage_rows = [&](int g0, int nrow) {
+        for (int i = tid; i < nrow * hv0; i += ROUTE_THREADS) {
+            const int ri = i / hv0, c8 = i - ri * hv0;
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(A.w + (size_t)(g0 + ri) * H) + c8);
+            *reinterpret_cast<uint4*>(wrows + (size_t)ri * wstride + c8 * 8) = v;
+        }
+    };
     pdl_launch_dependents();
+    // the first group of this CTA's experts' rows does not depend on the kernels before: staged ahead of the wait
+    if (r_lo < r_hi) stage_rows(r_lo, min(16, r_hi - r_lo));
     pdl_wait();
     if (A.h_in != nullptr) {
-        // (the rows' staging area is free until the first group of experts is staged)
-        float* scratch = reinterpret_cast<float*>(wrows);       // H + 256 floats
+        float* scratch = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(wrows) + 16 * (size_t)wstride * 2);  // H + 256 floats
         bf16* xb = reinterpret_cast<bf16*>(scratch + H + 256);  // the normed row, bf16
         stage_x_norm<1, 0, false>(xb, scratch, A.h_in + (size_t)t * H, nullptr,
                                   A.y_add != nullptr ? A.y_add + (size_t)t * H : nullptr, A.norm_w,
@@ -218,17 +229,10 @@ __global__ void __cluster_dims__(RR_CTAS, 1, 1) __launch_bounds__(ROUTE_THREADS)
         const float4* xg = reinterpret_cast<const float4*>(A.x + (size_t)t * H);
         for (int i = tid; i < H / 4; i += ROUTE_THREADS) reinterpret_cast<float4*>(xs)[i] = __ldcg(xg + i);
     }
-    const int per = (E + RR_CTAS - 1) / RR_CTAS;
-    const int r_lo = rank * per, r_hi = min(E, r_lo + per);
     float* lg0 = cl.map_shared_rank(lg, 0);
     for (int g0 = r_lo; g0 < r_hi; g0 += 16) {
         const int nrow = min(16, r_hi - g0);
-        const int hv = H >> 3;
-        for (int i = tid; i < nrow * hv; i += ROUTE_THREADS) {
-            const int ri = i / hv, c8 = i - ri * hv;
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(A.w + (size_t)(g0 + ri) * H) + c8);
-            *reinterpret_cast<uint4*>(wrows + (size_t)ri * wstride + c8 * 8) = v;
-        }
+        if (g0 != r_lo) stage_rows(g0, nrow);
         __syncthreads();
         const int ri = tid >> 4, j = tid & 15;
         float acc = 0.f;
@@ -251,6 +255,96 @@ __global__ void __cluster_dims__(RR_CTAS, 1, 1) __launch_bounds__(ROUTE_THREADS)
     if (rank != 0) return;
     auto logit = [&](int e) -> float { return lg[e]; };
     route_row(logit, t, E, A.k, A.mode, A.idx, A.wout, pr);
+}
+
+// ---- the same for routers too large for one cluster: a grid of CTAs a row, the last one to finish picks -----------------
+// A cluster is eight SMs; a router of 128 experts x 2048 columns read by eight SMs is slower than its matvec spread over
+// the card. Here `parts` CTAs a token take E / parts experts each (the norm prologue made by each for itself, the rows
+// staged in shared memory, the host's 16-lane order), write their logits to global memory and count themselves in; the
+// CTA that arrives last reads all E logits back and picks (no CTA waits for another). One launch for
+// btb_b200_add_rmsnorm_wide, the router's matvec and btb_b200_moe_route.
+struct RouterGridArgs {
+    RouterArgs r;
+    int* cnt;  // [T] arrivals, zero between launches
+    int parts;
+};
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_router_grid(const RouterGridArgs G) {
+    const RouterArgs& A = G.r;
+    extern __shared__ __align__(16) unsigned char rsm[];
+    const int E = A.E, H = A.H, tid = threadIdx.x;
+    const int part = blockIdx.x, t = blockIdx.y;
+    float* xs = reinterpret_cast<float*>(rsm);  // [H]
+    float* pr = xs + H;                          // [E]
+    const int wstride = H + 8;
+    bf16* wrows = reinterpret_cast<bf16*>(rsm + ((((size_t)H + (size_t)E) * 4 + 15) & ~(size_t)15));  // [16][H + 8]
+    __shared__ int s_last;
+    pdl_launch_dependents();
+    // this CTA's experts' rows do not depend on the kernels before: staged ahead of the wait
+    const int per = (E + G.parts - 1) / G.parts;
+    const int r_lo = part * per, r_hi = min(E, r_lo + per);
+    const int hv = H >> 3;
+    const bool one_group = r_hi - r_lo <= 16;
+    if (one_group) {
+        for (int i = tid; i < (r_hi - r_lo) * hv; i += ROUTE_THREADS) {
+            const int ri = i / hv, c8 = i - ri * hv;
+            *reinterpret_cast<uint4*>(wrows + (size_t)ri * wstride + c8 * 8) =
+                __ldg(reinterpret_cast<const uint4*>(A.w + (size_t)(r_lo + ri) * H) + c8);
+        }
+    }
+    pdl_wait();
+    if (A.h_in != nullptr) {
+        float* scratch = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(wrows) + 16 * (size_t)wstride * 2);  // H + 256 floats
+        bf16* xb = reinterpret_cast<bf16*>(scratch + H + 256);  // the normed row, bf16
+        stage_x_norm<1, 0, false>(xb, scratch, A.h_in + (size_t)t * H, nullptr,
+                                  A.y_add != nullptr ? A.y_add + (size_t)t * H : nullptr, A.norm_w,
+                                  A.h_out != nullptr ? A.h_out + (size_t)t * H : nullptr, A.eps, A.centered, 1, H, part == 0);
+        for (int i = tid; i < H; i += ROUTE_THREADS) {
+            const float v = bf2f(xb[i]);
+            xs[i] = v;
+            if (part == 0) {
+                A.xf_out[(size_t)t * H + i] = v;
+                if (A.x_out != nullptr) A.x_out[(size_t)t * H + i] = xb[i];
+            }
+        }
+        __syncthreads();
+    } else {
+        const float4* xg = reinterpret_cast<const float4*>(A.x + (size_t)t * H);
+        for (int i = tid; i < H / 4; i += ROUTE_THREADS) reinterpret_cast<float4*>(xs)[i] = __ldcg(xg + i);
+    }
+    for (int g0 = r_lo; g0 < r_hi; g0 += 16) {
+        const int nrow = min(16, r_hi - g0);
+        if (!one_group) {
+            for (int i = tid; i < nrow * hv; i += ROUTE_THREADS) {
+                const int ri = i / hv, c8 = i - ri * hv;
+                *reinterpret_cast<uint4*>(wrows + (size_t)ri * wstride + c8 * 8) =
+                    __ldg(reinterpret_cast<const uint4*>(A.w + (size_t)(g0 + ri) * H) + c8);
+            }
+        }
+        __syncthreads();
+        const int ri = tid >> 4, j = tid & 15;
+        float acc = 0.f;
+        if (ri < nrow) {
+            const unsigned short* wr = reinterpret_cast<const unsigned short*>(wrows + (size_t)ri * wstride);
+#pragma unroll 8
+            for (int c = j; c < H; c += 16) acc = fmaf(__uint_as_float((unsigned)wr[c] << 16), xs[c], acc);
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+        if (ri < nrow && j == 0) A.rl[(size_t)t * E + g0 + ri] = acc;
+        __syncthreads();
+    }
+    // count this CTA in; the last one to arrive picks
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(G.cnt + t, 1) == G.parts - 1 ? 1 : 0;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    auto logit = [&](int e) -> float { return __ldcg(A.rl + (size_t)t * E + e); };
+    route_row(logit, t, E, A.k, A.mode, A.idx, A.wout, pr);
+    if (tid == 0) G.cnt[t] = 0;
 }
 
 // ---- the 16-lane matvec over stored weights ---------------------------------------------------------------------------
@@ -719,8 +813,9 @@ static int moe_router_launch(RouterArgs a, const void* align_a, const void* alig
     if ((reinterpret_cast<uintptr_t>(a.w) & 15) || (reinterpret_cast<uintptr_t>(align_a) & 15) ||
         (reinterpret_cast<uintptr_t>(align_b) & 15))
         return B2_ERR_DOMAIN;
-    const size_t smem = ((((size_t)H + 2 * (size_t)E) * 4 + 15) & ~(size_t)15) + 16 * ((size_t)H + 8) * 2;
-    if (smem > 200 * 1024 || 16 * ((size_t)H + 8) * 2 < ((size_t)H + 256) * 4 + (size_t)H * 2) return B2_ERR_DOMAIN;
+    const size_t smem = ((((size_t)H + 2 * (size_t)E) * 4 + 15) & ~(size_t)15) + 16 * ((size_t)H + 8) * 2 +
+                        (a.h_in != nullptr ? ((size_t)H + 256) * 4 + (size_t)H * 2 : 0);  // + the norm's own scratch
+    if (smem > 200 * 1024) return B2_ERR_DOMAIN;
     static bool allowed[64];
     if (const int rc = b2_allow_smem((const void*)moe_router_route, allowed)) return rc;
     return b2_launch((const void*)moe_router_route, dim3(RR_CTAS, T), dim3(ROUTE_THREADS), smem,
@@ -753,4 +848,39 @@ extern "C" int btb_b200_moe_router_norm(const void* w, const void* h_in, const v
     a.norm_w = static_cast<const bf16*>(norm_w), a.h_out = static_cast<bf16*>(h_out);
     a.xf_out = static_cast<float*>(xf_out), a.x_out = static_cast<bf16*>(x_out), a.eps = eps, a.centered = centered;
     return moe_router_launch(a, h_in, norm_w, T, stream);
+}
+
+// btb_b200_moe_router_norm for routers of any size: `parts` CTAs a token over the whole card instead of one cluster, the
+// last CTA to finish picks. logits f32 [T, E] (required: the CTAs meet there) and cnt i32 [T] (zero before the first
+// launch; the kernel leaves it zero). h_in null: x f32 [T, H] is read as btb_b200_moe_router reads it (pass it as xf_out).
+extern "C" int btb_b200_moe_router_grid(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps,
+                                        int centered, void* h_out, void* x_out, void* xf_out, void* logits, void* cnt, int E,
+                                        int H, int k, int mode, void* idx, void* wout, int T, void* stream) {
+    if (!w || !xf_out || !logits || !cnt || !idx || !wout || (h_in && !norm_w) || (y_add && !h_out)) return B2_ERR_NULL;
+    if (T <= 0 || T > 65535 || E <= 0 || E > 8192 || k <= 0 || k > E || k > ROUTE_MAX_K || H <= 0 || (H & 7) ||
+        (mode != 0 && mode != 1) || (h_in && h_out == h_in) || !(eps == eps))
+        return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(h_in) | reinterpret_cast<uintptr_t>(y_add) |
+         reinterpret_cast<uintptr_t>(norm_w) | reinterpret_cast<uintptr_t>(h_out) | reinterpret_cast<uintptr_t>(xf_out) |
+         reinterpret_cast<uintptr_t>(x_out)) & 15)
+        return B2_ERR_DOMAIN;
+    const size_t smem = ((((size_t)H + (size_t)E) * 4 + 15) & ~(size_t)15) + 16 * ((size_t)H + 8) * 2 +
+                        (h_in != nullptr ? ((size_t)H + 256) * 4 + (size_t)H * 2 : 0);  // + the norm's own scratch
+    if (smem > 200 * 1024) return B2_ERR_DOMAIN;
+    RouterGridArgs g{};
+    RouterArgs& a = g.r;
+    a.w = static_cast<const bf16*>(w), a.rl = static_cast<float*>(logits);
+    a.x = h_in ? nullptr : static_cast<const float*>(xf_out);
+    a.idx = static_cast<int*>(idx), a.wout = static_cast<bf16*>(wout), a.E = E, a.H = H, a.k = k, a.mode = mode;
+    a.h_in = static_cast<const bf16*>(h_in), a.y_add = static_cast<const bf16*>(y_add);
+    a.norm_w = static_cast<const bf16*>(norm_w), a.h_out = static_cast<bf16*>(h_out);
+    a.xf_out = static_cast<float*>(xf_out), a.x_out = static_cast<bf16*>(x_out), a.eps = eps, a.centered = centered;
+    g.cnt = static_cast<int*>(cnt);
+    // four experts a CTA where the card has CTAs to spare (a row offers sixteen chains: 64 threads work, 256 stage)
+    const int per = T * ((E + 3) / 4) <= 2 * b2_sm_count() ? 4 : 16;
+    g.parts = (E + per - 1) / per;
+    static bool allowed[64];
+    if (const int rc = b2_allow_smem((const void*)moe_router_grid, allowed)) return rc;
+    return b2_launch((const void*)moe_router_grid, dim3(g.parts, T), dim3(ROUTE_THREADS), smem,
+                     static_cast<cudaStream_t>(stream), g, 4);
 }

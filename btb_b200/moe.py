@@ -236,6 +236,7 @@ class MoEEngine(CardEngine):
                 "xf": f32(M, c.hidden), "rl": f32(M, c.experts), "idx": torch.zeros(M, k, dtype=torch.int32, device=dev),
                 "rw": torch.zeros(M, k, dtype=torch.bfloat16, device=dev), "egu": f32(M * k, 2 * c.inter),
                 "eh": f32(M * k, c.inter), "edn": f32(M * k, c.hidden),
+                "rcnt": torch.zeros(M, dtype=torch.int32, device=dev),
             })  # fmt: skip
         return g
 
@@ -303,6 +304,11 @@ class MoEEngine(CardEngine):
             if self.fuse_router and H % 8 == 0 and E * H <= self.router_fuse_max:
                 K_("btb_b200_moe_router_norm", ptr(L.router), ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, 0, ptr(halt), 0,
                    ptr(g["xf"]), 0, E, H, k, c.router_mode, ptr(g["idx"]), ptr(g["rw"]), T, s)  # fmt: skip
+                hcur, halt = halt, hcur
+            elif self.fuse_router and H % 8 == 0 and E <= 8192:
+                # a larger router: the same three steps as one launch over the whole card, the last CTA to finish picking
+                K_("btb_b200_moe_router_grid", ptr(L.router), ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, 0, ptr(halt), 0,
+                   ptr(g["xf"]), ptr(g["rl"]), ptr(g["rcnt"]), E, H, k, c.router_mode, ptr(g["idx"]), ptr(g["rw"]), T, s)  # fmt: skip
                 hcur, halt = halt, hcur
             else:
                 K_("btb_b200_add_rmsnorm_wide", ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), ptr(g["xf"]), T, H,

@@ -294,6 +294,14 @@ int btb_b200_moe_router(const void* w, const void* x, void* logits, int E, int H
 int btb_b200_moe_router_norm(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps, int centered,
                              void* h_out, void* x_out, void* xf_out, void* logits, int E, int H, int k, int mode, void* idx,
                              void* wout, int T, void* stream);
+/* btb_b200_moe_router_norm for routers of any size (no counterpart in the reference: its host issues the norm, the matvec
+ * and btb_moe_route apart): a grid of CTAs a token over the whole card instead of one cluster; each takes a few experts'
+ * rows, writes their logits to `logits` f32 [T, E] (required) and counts itself in at cnt i32 [T] (zero before the first
+ * launch, left zero); the CTA that arrives last picks - no CTA waits for another. h_in null: no norm, x f32 [T, H] is read
+ * from xf_out. The same bits as the separate launches. */
+int btb_b200_moe_router_grid(const void* w, const void* h_in, const void* y_add, const void* norm_w, float eps, int centered,
+                             void* h_out, void* x_out, void* xf_out, void* logits, void* cnt, int E, int H, int k, int mode,
+                             void* idx, void* wout, int T, void* stream);
 /* btb_gemv_lane16_f32_m{M} (btb_kernels.cu:1635-1682): the host's bf16 GEMV order on the card (16 lane sums a row,
  * column c to lane c mod 16, reduce16's fold: native/src/gemv.rs:46-58,85-123). w [R,C] bf16, x [M,C] f32, y [M,R]
  * f32; bit-equal to btb_gemv_bf16_rows. */

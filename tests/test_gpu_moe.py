@@ -399,6 +399,24 @@ def test_router_cluster_launch_equals_matvec_then_route(E, H, k, mode):
     assert torch.equal(h1, h2) and torch.equal(x1, x2) and torch.equal(xf1.view(torch.int32), xf2.view(torch.int32))
     assert torch.equal(rl_d.view(torch.int32), rl_e.view(torch.int32))
     assert torch.equal(idx_d, idx_e) and torch.equal(w_d.view(torch.int16), w_e.view(torch.int16))
+    # the grid form (any router size): the same bits again, its counter left at zero, twice in a row
+    cnt = torch.zeros(T, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        h3, x3, xf3 = torch.zeros_like(hb), torch.zeros_like(hb), torch.zeros_like(xf1)
+        idx_f, w_f, rl_f = torch.zeros_like(idx_a), torch.zeros_like(w_a), torch.zeros_like(rl_a)
+        call("btb_b200_moe_router_grid", ptr(wt), ptr(hb), ptr(yb), ptr(nw), 1e-6, 0, ptr(h3), ptr(x3), ptr(xf3), ptr(rl_f),
+             ptr(cnt), E, H, k, mode, ptr(idx_f), ptr(w_f), T, s())  # fmt: skip
+        torch.cuda.synchronize()
+        assert torch.equal(h1, h3) and torch.equal(x1, x3) and torch.equal(xf1.view(torch.int32), xf3.view(torch.int32))
+        assert torch.equal(rl_d.view(torch.int32), rl_f.view(torch.int32))
+        assert torch.equal(idx_d, idx_f) and torch.equal(w_d.view(torch.int16), w_f.view(torch.int16))
+        assert int(cnt.abs().sum()) == 0
+    # ... and without the norm: x read as given
+    idx_g, w_g, rl_g = torch.zeros_like(idx_a), torch.zeros_like(w_a), torch.zeros_like(rl_a)
+    call("btb_b200_moe_router_grid", ptr(wt), 0, 0, 0, 1e-6, 0, 0, 0, ptr(xt), ptr(rl_g), ptr(cnt), E, H, k, mode, ptr(idx_g),
+         ptr(w_g), T, s())  # fmt: skip
+    torch.cuda.synchronize()
+    assert torch.equal(rl_a.view(torch.int32), rl_g.view(torch.int32)) and torch.equal(idx_a, idx_g)
     with pytest.raises(capi.NativeError):  # the new residual may not land in the buffer other CTAs still read
         call("btb_b200_moe_router_norm", ptr(wt), ptr(hb), ptr(yb), ptr(nw), 1e-6, 0, ptr(hb), 0, ptr(xf2), 0, E, H, k, mode,
              ptr(idx_e), ptr(w_e), T, s())  # fmt: skip
