@@ -88,18 +88,18 @@ __global__ void __launch_bounds__(NWA * 32) attn_step(const StepAttnArgs A) {
         a.q = r.qo, a.K = r.K, a.V = r.V, a.out += (size_t)b * Hq * D, a.n0p = r.n0p;
         a.part_m += (size_t)b * S * Hq, a.part_l += (size_t)b * S * Hq, a.part_acc += (size_t)b * S * Hq * D, a.cnt += (size_t)b * Hq;
         if (G > 1 && *a.n0p < SPLIT_ROWS) {
-            attn_step_item<D, 1, G>(a, r, blockIdx.x, g, blockIdx.z, dsm_raw);
+            attn_step_item<D, 1, G, true, true>(a, r, blockIdx.x, g, blockIdx.z, dsm_raw);
         } else if (blockIdx.z == 0) {
-            attn_step_item<D, G, G>(a, r, blockIdx.x, g, 0, dsm_raw);
+            attn_step_item<D, G, G, true, true>(a, r, blockIdx.x, g, 0, dsm_raw);
         }
         return;
     }
     // Below this many cached rows the group's heads take a block each (grid z); above, block z = 0 takes them all -
     // a long cache has blocks enough, and each key row is then read once.
     if (G > 1 && *A.a.n0p < SPLIT_ROWS) {
-        attn_step_item<D, 1, G>(A.a, A.r, blockIdx.x, blockIdx.y, blockIdx.z, dsm_raw);
+        attn_step_item<D, 1, G, true, true>(A.a, A.r, blockIdx.x, blockIdx.y, blockIdx.z, dsm_raw);
     } else if (blockIdx.z == 0) {
-        attn_step_item<D, G, G>(A.a, A.r, blockIdx.x, blockIdx.y, 0, dsm_raw);
+        attn_step_item<D, G, G, true, true>(A.a, A.r, blockIdx.x, blockIdx.y, 0, dsm_raw);
     }
 }
 template <int D, int G>
@@ -108,7 +108,9 @@ int launch_attn_step(const StepAttnArgs& a, dim3 grid, cudaStream_t s) {
     static bool allowed[64];
     int rc = b2_allow_smem(reinterpret_cast<const void*>(kern), allowed);
     if (rc) return rc;
-    return b2_launch(reinterpret_cast<const void*>(kern), grid, dim3(NWA * 32), sizeof(AttnSmem<D, G>), s, a);
+    // (the split form runs attn_step_item<D, 1, G>: its AttnSmem is the smaller one, the staging area starts no later)
+    return b2_launch(reinterpret_cast<const void*>(kern), grid, dim3(NWA * 32),
+                     attn_vstage_offset<D, G>() + attn_vstage_bytes<D>(), s, a);
 }
 template <int D>
 int launch_attn_step_g(int G, const StepAttnArgs& a, dim3 grid, cudaStream_t s) {

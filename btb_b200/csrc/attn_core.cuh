@@ -435,7 +435,19 @@ __device__ __forceinline__ void rope_item(const RopeArgs& A, int head, int t, in
 // G == 1: head z of the group - a short cache leaves most of the card idle and the per-key arithmetic is what takes
 // the time, so the group's heads spread over GQ blocks (each reads the kv head's rows: they are few). Only block z = 0
 // writes the cache.
-template <int D, int G, int GQ, bool TRIGGER = true>
+// VSTAGE: every warp's 32 value rows are copied to shared memory asynchronously (cp.async) as soon as its keys' cache rows
+// are known - they land while the scores are made, so the value products wait for no round trip of their own. The block's
+// dynamic shared memory then holds, after AttnSmem, NWA x 32 rows of D bf16 (attn_vstage_bytes).
+template <int D, int G>
+__host__ __device__ constexpr size_t attn_vstage_offset() { return (sizeof(AttnSmem<D, G>) + 127) & ~(size_t)127; }
+template <int D>
+__host__ __device__ constexpr size_t attn_vstage_bytes() { return (size_t)NWA * 32 * D * 2; }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+template <int D, int G, int GQ, bool TRIGGER = true, bool VSTAGE = false>
 __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs& RA, int grp, int g, int z,
                                                uint8_t* dsm_raw) {
     const int hbase = g * GQ + z;
@@ -469,6 +481,22 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
     if (j >= first && j <= last) row = A.tbl != nullptr ? A.tbl[j] : j;
     // a warp none of whose keys the row sees leaves its tile's half empty and stays out of the arithmetic
     const bool any = __ballot_sync(0xffffffffu, row >= 0) != 0u;
+    // the warp's value rows on their way to shared memory: two keys an instruction, sixteen lanes a row (a row is D * 2
+    // contiguous bytes on both sides: coalesced reads, conflict-free writes); the new key's row comes from `vnew` instead
+    uint8_t* vst = dsm_raw + attn_vstage_offset<D, G>() + (size_t)warp * 32 * D * 2;
+    if (VSTAGE && any) {
+        constexpr int LPR = D * 2 / 16;   // lanes a row: 16-byte pieces
+        constexpr int KPI = 32 / LPR;     // keys an instruction
+        const int piece = lane % LPR, sub = lane / LPR;
+#pragma unroll
+        for (int u0 = 0; u0 < 32; u0 += KPI) {
+            const int u = u0 + sub;
+            const int rk = __shfl_sync(0xffffffffu, row, u);
+            if (rk >= 0 && u != new_lane)
+                cp_async16(smem_u32(vst + (size_t)u * D * 2 + piece * 16),
+                           reinterpret_cast<const uint8_t*>(Vg + (size_t)rk * A.rs) + piece * 16);
+        }
+    }
     // ---- the head's queries (every block), the new key and value (the owner): the block's LAST warps take them, the
     // ones whose tiles a short cache leaves empty, and before their own keys - the rotation is what the block waits for
     const int rw = NWA - 1 - warp;
@@ -561,20 +589,26 @@ __device__ __forceinline__ void attn_step_item(const AttnArgs& A, const RopeArgs
         // all thirty-two keys' value runs in flight at once (raw, in the registers the key row has left); a key the
         // row does not see has weight 0 over zeros
         uint32_t vraw[32][E / 2];
+        if (VSTAGE) {
+            cp_async_wait_all();  // this lane's copies have landed ...
+            __syncwarp();         // ... and so have the other lanes'
+        }
 #pragma unroll
         for (int u = 0; u < 32; ++u) {
             const int rk = __shfl_sync(0xffffffffu, row, u);
             const bool from_smem = u == new_lane;
-            const bf16* vr = from_smem ? vnew + lane * E : Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
+            const bf16* vr = from_smem ? vnew + lane * E
+                             : VSTAGE  ? reinterpret_cast<const bf16*>(vst + (size_t)u * D * 2) + lane * E
+                                       : Vg + (size_t)(rk >= 0 ? rk : 0) * A.rs + lane * E;
             if (E == 4) {
                 const uint2 vv = rk < 0 ? make_uint2(0u, 0u)
-                                 : from_smem ? *reinterpret_cast<const uint2*>(vr)
-                                             : __ldg(reinterpret_cast<const uint2*>(vr));
+                                 : (from_smem || VSTAGE) ? *reinterpret_cast<const uint2*>(vr)
+                                                         : __ldg(reinterpret_cast<const uint2*>(vr));
                 vraw[u][0] = vv.x, vraw[u][E / 2 - 1] = vv.y;
             } else {
                 vraw[u][0] = rk < 0 ? 0u
-                             : from_smem ? *reinterpret_cast<const uint32_t*>(vr)
-                                         : __ldg(reinterpret_cast<const uint32_t*>(vr));
+                             : (from_smem || VSTAGE) ? *reinterpret_cast<const uint32_t*>(vr)
+                                                     : __ldg(reinterpret_cast<const uint32_t*>(vr));
             }
         }
 #pragma unroll
