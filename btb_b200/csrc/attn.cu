@@ -77,20 +77,29 @@ __global__ void __launch_bounds__(NWA * 32) attn_step(const StepAttnArgs A) {
     }
     pdl_wait();  // the trigger for the next kernel is inside, after the values are read
     if (A.B > 1) {
-        // sequence b's row: its slice of qkv, its own cache, length, partials and counters
+        // sequence b's row: its slice of qkv, its own cache, length, partials and counters. The adjusted arguments are made
+        // once a block in shared memory (a per-thread copy of the two structs lives in local memory: slower to read)
+        __shared__ __align__(16) unsigned char sa_raw[sizeof(AttnArgs)];
+        __shared__ __align__(16) unsigned char sr_raw[sizeof(RopeArgs)];
+        AttnArgs& sa = *reinterpret_cast<AttnArgs*>(sa_raw);
+        RopeArgs& sr = *reinterpret_cast<RopeArgs*>(sr_raw);
         const int b = blockIdx.y / A.a.Hk, g = blockIdx.y - b * A.a.Hk;
-        AttnArgs a = A.a;
-        RopeArgs r = A.r;
-        const int Hq = a.Hq, Hk = a.Hk;
-        const size_t S = A.S;
-        r.qkv += (size_t)b * (Hq + 2 * Hk) * D, r.n0p += b, r.depth += b, r.K += (size_t)b * A.seq_stride;
-        r.V += (size_t)b * A.seq_stride, r.qo += (size_t)b * Hq * D;
-        a.q = r.qo, a.K = r.K, a.V = r.V, a.out += (size_t)b * Hq * D, a.n0p = r.n0p;
-        a.part_m += (size_t)b * S * Hq, a.part_l += (size_t)b * S * Hq, a.part_acc += (size_t)b * S * Hq * D, a.cnt += (size_t)b * Hq;
-        if (G > 1 && *a.n0p < SPLIT_ROWS) {
-            attn_step_item<D, 1, G, true, true>(a, r, blockIdx.x, g, blockIdx.z, dsm_raw);
+        if (threadIdx.x == 0) {
+            AttnArgs a = A.a;
+            RopeArgs r = A.r;
+            const int Hq = a.Hq, Hk = a.Hk;
+            const size_t S = A.S;
+            r.qkv += (size_t)b * (Hq + 2 * Hk) * D, r.n0p += b, r.depth += b, r.K += (size_t)b * A.seq_stride;
+            r.V += (size_t)b * A.seq_stride, r.qo += (size_t)b * Hq * D;
+            a.q = r.qo, a.K = r.K, a.V = r.V, a.out += (size_t)b * Hq * D, a.n0p = r.n0p;
+            a.part_m += (size_t)b * S * Hq, a.part_l += (size_t)b * S * Hq, a.part_acc += (size_t)b * S * Hq * D, a.cnt += (size_t)b * Hq;
+            sa = a, sr = r;
+        }
+        __syncthreads();
+        if (G > 1 && *sa.n0p < SPLIT_ROWS) {
+            attn_step_item<D, 1, G, true, true>(sa, sr, blockIdx.x, g, blockIdx.z, dsm_raw);
         } else if (blockIdx.z == 0) {
-            attn_step_item<D, G, G, true, true>(a, r, blockIdx.x, g, 0, dsm_raw);
+            attn_step_item<D, G, G, true, true>(sa, sr, blockIdx.x, g, 0, dsm_raw);
         }
         return;
     }
