@@ -872,21 +872,23 @@ def run_case(args) -> None:
 
         cfg = MO.QWEN3_30B_A3B if rest.split(":")[0] == "fp8" else MO.GPT_OSS_20B
         gen = torch.Generator(device="cuda").manual_seed(0)
-        st = MO.synth_expert_stack(cfg, gen, cfg.experts, 2 * cfg.inter, cfg.hidden, "cuda")
+        down = ":dn" in args.case  # moe:fp8:dn / moe:mx4:dn: the layer's DOWN stack (an activated row a pick)
+        st = (MO.synth_expert_stack(cfg, gen, cfg.experts, cfg.hidden, cfg.inter, "cuda") if down
+              else MO.synth_expert_stack(cfg, gen, cfg.experts, 2 * cfg.inter, cfg.hidden, "cuda"))
         k, E = cfg.top_k, cfg.experts
         rounds = max(2, E // k)
         picks = [torch.arange(i * k, (i + 1) * k, dtype=torch.int32, device="cuda") % E for i in range(rounds)]
         # the row the engine's experts are given: the normed bf16 row widened to f32 (moe:fp8:f32 for any f32 row)
-        xf = torch.randn(1, cfg.hidden, device="cuda", generator=gen)
+        xf = torch.randn(k if down else 1, st.C, device="cuda", generator=gen)
         if not args.case.endswith(":f32"):
             xf = xf.bfloat16().float()
-        yv = torch.zeros(k, 2 * cfg.inter, device="cuda")
-        per = k * 2 * cfg.inter * cfg.hidden * {"fp8": 1.0, "mx4": 17 / 32, "bf16": 2.0}[st.fmt]
+        yv = torch.zeros(k, st.R, device="cuda")
+        per = k * st.R * st.C * {"fp8": 1.0, "mx4": 17 / 32, "bf16": 2.0}[st.fmt]
         for it in range(3):
             e0.record()
             for idx in picks:
                 call("btb_b200_moe_gemv", MO.FMT[st.fmt], ptr(st.w), ptr(st.scales), st.w_stride, st.s_stride, st.sr, st.sc,
-                     ptr(idx), k, E, ptr(xf), k, ptr(yv), st.R, st.C, 0, 1, sp)  # fmt: skip
+                     ptr(idx), k, E, ptr(xf), 1 if down else k, ptr(yv), st.R, st.C, 0, 1, sp)  # fmt: skip
             e1.record()
             torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1000 / rounds
