@@ -908,6 +908,30 @@ def run_case(args) -> None:
             e1.record()
             torch.cuda.synchronize()
         out.update(us_per_launch=e0.elapsed_time(e1) * 1000 / 20, vocab=V)
+    elif kind == "verify":
+        # the verify pass's pick over R tree nodes with 4 drafted children each (verify:V[:R]): the drafter a perturbed copy
+        # of the target, every other node a point-mass row
+        from btb_b200.sampling import Sampling, Verify
+
+        parts = rest.split(":")
+        V, R = int(parts[0]), int(parts[1]) if len(parts) > 1 else 8
+        gen = torch.Generator(device="cuda").manual_seed(0)
+        lg = (torch.randn(R, V, device="cuda", generator=gen) * 3).to(torch.bfloat16)
+        q = torch.softmax(lg.float() + torch.randn(R, V, device="cuda", generator=gen), -1)
+        kids = torch.multinomial(q, 4).tolist()
+        s_ = Sampling(temperature=0.8, top_k=40, top_p=0.9, seed=7)
+        v = Verify(s_, q, kids, [r % 2 == 0 for r in range(R)])
+        keys = [s_.key_for(100 + r) for r in range(R)]
+        v.pick(lg, keys)
+        for it in range(3):
+            e0.record()
+            for _ in range(10):
+                outv = v.pick(lg, keys)
+            e1.record()
+            torch.cuda.synchronize()
+        acc = int(((outv >> 24) > 0).sum())
+        out.update(us_per_call=e0.elapsed_time(e1) * 1000 / 10, vocab=V, nodes=R, children=4, accepted_nodes=acc,
+                   note="a call is the host class's: small uploads of kids / keys / parameters and one launch")
     else:
         raise SystemExit(f"unknown case {args.case}")
     assert capi.status() == 0
