@@ -948,7 +948,7 @@ def run_batch(args, mw, cfg, storage, cap, rank, world, dist) -> None:
 
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     eng = BatchEngine(mw, B, cap=cap)
-    eng.wide_tc = bool(args.wide_tc) and storage == "bf16"
+    eng.wide_tc = bool(args.wide_tc)
     prompts = [torch.randint(0, cfg.vocab, (PROMPT,), generator=torch.Generator().manual_seed(100 + b)) for b in range(B)]
     eng.prefill_all(prompts)
     graph = eng.batch_graph()

@@ -42,6 +42,7 @@ SIGNATURES: dict[str, tuple[Any, list[Any]]] = {
     "btb_b200_status": (_I, [C.POINTER(C.c_int)]),
     "btb_b200_gemv_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_tc_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+    "btb_b200_gemv_tc_p12": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "btb_b200_gemv_tc_workspace_bytes": (_SZ, [_I, _I]),
     "btb_b200_gemm_tc_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "btb_b200_gemv_tc_glu_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),

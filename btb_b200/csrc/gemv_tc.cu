@@ -18,6 +18,7 @@
 #include <cuda.h>
 
 #include "btb_b200_internal.h"
+#include "gemv_core.cuh"
 
 B2_DEFINE_STATUS(tc)
 
@@ -229,6 +230,194 @@ __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_consta
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
 }
 
+// ---- the same matvec over pack12 weights read as stored ----------------------------------------------------------------------
+// The weights' tile cannot be copied into the MMA's operand layout by TMA: it does not exist as bf16 anywhere. Here TMA
+// brings the tile's stored parts - 128 rows x 64 low bytes and 128 rows x 32 bytes of codes - into a staging area, eight
+// more warps (a 16-byte piece of a row a thread) widen them in registers (p12_chunk: the GEMV's own widen, escapes from the row's
+// list) and write the bf16 tile into shared memory in the 128-byte-swizzled layout the MMA reads (16-byte piece c of row
+// d at piece c ^ (d & 7)), make it visible to the async proxy and count themselves in on the stage's second barrier;
+// the issuer waits for that one. No widened copy is ever in global memory, and the sums are btb_b200_gemv_tc_bf16's
+// over the widened matrix to the bit (the operands are the same bits in the same places).
+constexpr int P12_LO = TC_BM * TC_BK;          // a stage's low bytes
+constexpr int P12_HI = TC_BM * TC_BK / 2;      // ... and codes
+constexpr int P12_B = TC_BN * TC_BK * 2;       // x's tile
+constexpr int P12_ST = A_BYTES + P12_B + P12_LO + P12_HI;
+struct TcP12Args {
+    TcArgs t;
+    uint32_t table[4];
+    const int32_t* esc_idx;
+    const uint8_t* esc_val;
+    const int32_t* esc_row;  // [R + 1] or null: no escapes anywhere
+};
+
+__global__ void __launch_bounds__(384, 2) gemv_tc_p12(const __grid_constant__ CUtensorMap tmLo,
+                                                      const __grid_constant__ CUtensorMap tmHi,
+                                                      const __grid_constant__ CUtensorMap tmX, const TcP12Args P) {
+    const TcArgs& A = P.t;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t full_p[TC_STAGES_MAX], full_a[TC_STAGES_MAX], empty[TC_STAGES_MAX], done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_fail;
+    const int TC_STAGES = A.stages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem) + 1023) & ~(uintptr_t)1023);
+    const int row0 = blockIdx.x * TC_BM;
+    const int total_kb = A.C / TC_BK;  // (whole K blocks: the host checks)
+    const int kb0 = blockIdx.y * A.kblocks_per_split;
+    const int nkb = max(0, min(A.kblocks_per_split, total_kb - kb0));
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(smem_u32(&full_p[s]), 1);
+            mbar_init(smem_u32(&full_a[s]), 256);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        mbar_init(smem_u32(&done), 1);
+        s_fail = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(32u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0 && lane == 0) {
+        // the producer: the stored parts of the weights' tile and x's tile
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
+            if (kb >= TC_STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
+                *(volatile int*)&s_fail = 1;
+                break;
+            }
+            const uint32_t bar = smem_u32(&full_p[s]);
+            uint8_t* st = tiles + (size_t)s * P12_ST;
+            mbar_expect_tx(bar, P12_B + P12_LO + P12_HI);
+            tma_load_2d(smem_u32(st + A_BYTES + P12_B), &tmLo, (kb0 + kb) * TC_BK, row0, bar);
+            tma_load_2d(smem_u32(st + A_BYTES + P12_B + P12_LO), &tmHi, (kb0 + kb) * (TC_BK / 2), row0, bar);
+            tma_load_2d(smem_u32(st + A_BYTES), &tmX, (kb0 + kb) * TC_BK, 0, bar);
+        }
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
+            if (!mbar_wait_bounded(smem_u32(&full_a[s]), ph)) {  // every row of the tile widened (and x landed before that)
+                *(volatile int*)&s_fail = 1;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a0 = smem_u32(tiles + (size_t)s * P12_ST), b0 = a0 + A_BYTES;
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; ++k)
+                umma_bf16(tmem, umma_desc_sw128(a0 + k * 32), umma_desc_sw128(b0 + k * 32), idesc, (kb | k) != 0);
+            umma_commit(smem_u32(&empty[s]));
+        }
+        umma_commit(smem_u32(&done));
+    } else if (warp >= 4) {
+        // the wideners: eight warps; a thread takes 16-byte piece c = t & 7 of rows (t >> 3) + 32 i. A warp's lanes then read
+        // four consecutive rows' stored bytes (256 and 128 contiguous bytes) and write four whole rows of the operand tile:
+        // no bank conflicts anywhere (a row a thread made every read a 16-way conflict)
+        const int t = threadIdx.x - 128, c = t & 7;
+        constexpr int RPT = TC_BM / 32;  // rows a thread
+        // Escapes (a code of 15: the high byte comes from the matrix's ascending list) are not looked up a weight: row d of
+        // the tile has an owner among these threads, which walks the row's run of the list once, forwards only - the
+        // tile's K blocks come in ascending order - and patches the high bytes into the tile after it is written.
+        const int own = c < RPT ? (t >> 3) + 32 * c : -1;  // the tile row this thread owns, if any
+        int cur = 0, end = 0, peek = 0x7fffffff;
+        if (own >= 0 && P.esc_row != nullptr && row0 + own < A.R) {
+            cur = __ldg(P.esc_row + row0 + own), end = __ldg(P.esc_row + row0 + own + 1);
+            // (a K range that does not start at column 0: skip the entries before it)
+            const int from = (int)((size_t)(row0 + own) * A.C + (size_t)kb0 * TC_BK);
+            int a = cur, b = end;
+            while (a < b) {
+                const int mid = (a + b) >> 1;
+                if (__ldg(P.esc_idx + mid) < from) a = mid + 1;
+                else b = mid;
+            }
+            cur = a;
+            if (cur < end) peek = __ldg(P.esc_idx + cur);
+        }
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
+            bool bad = !mbar_wait_bounded(smem_u32(&full_p[s]), ph);
+            if (bad) *(volatile int*)&s_fail = 1;
+            bad = bad || *(volatile int*)&s_fail != 0;
+            uint8_t* st = tiles + (size_t)s * P12_ST;
+            if (!bad) {
+#pragma unroll
+                for (int i = 0; i < RPT; ++i) {
+                    const int d = (t >> 3) + 32 * i;
+                    const uint2 l = *reinterpret_cast<const uint2*>(st + A_BYTES + P12_B + d * TC_BK + c * 8);
+                    const uint32_t codes = *reinterpret_cast<const uint32_t*>(st + A_BYTES + P12_B + P12_LO + d * (TC_BK / 2) + c * 4);
+                    uint32_t wp[4];
+                    p12_chunk(l.x, l.y, codes, P.table, wp);
+                    *reinterpret_cast<uint4*>(st + d * 128 + ((c ^ (d & 7)) << 4)) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+                }
+            }
+            // the tile is written: the wideners' own barrier, which also carries the one answer every one of them acts on
+            // (a thread leaving the loop alone would leave the others at the next barrier for good)
+            int any_bad;
+            asm volatile("{\n.reg .pred q, r;\nsetp.ne.b32 q, %1, 0;\nbar.red.or.pred r, 1, 256, q;\nselp.b32 %0, 1, 0, r;\n}\n"
+                         : "=r"(any_bad)
+                         : "r"((int)bad)
+                         : "memory");
+            if (any_bad) break;
+            if (own >= 0) {
+                // (prefetching a window of the row's next entries every stage was measured slower: most rows have none)
+                const int base = (int)((size_t)(row0 + own) * A.C + (size_t)(kb0 + kb) * TC_BK);
+                while (peek < base + TC_BK) {  // this K block's escapes of the row
+                    const int col = peek - base;
+                    st[own * 128 + (((col >> 3) ^ (own & 7)) << 4) + (col & 7) * 2 + 1] = __ldg(P.esc_val + cur);
+                    ++cur;
+                    peek = cur < end ? __ldg(P.esc_idx + cur) : 0x7fffffff;
+                }
+            }
+            fence_proxy_async();  // the tile's bytes, written by ordinary stores, are the MMA's (an async-proxy reader) to see
+            mbar_arrive(smem_u32(&full_a[s]));
+        }
+    }
+    __syncwarp();
+    if (warp < 4) {
+        bool ok = true;
+        if (nkb > 0) ok = mbar_wait_bounded(smem_u32(&done), 0);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok && nkb > 0 && !*(volatile int*)&s_fail) {
+            const int row = row0 + warp * 32 + lane;
+            uint32_t r[32];
+            const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
+                "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                  "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row < A.R) {
+#pragma unroll
+                for (int n = 0; n < 32; ++n) {
+                    if (n < A.M) {
+                        if (A.splits == 1) A.y[(size_t)n * A.R + row] = f2bf(0.f + __uint_as_float(r[n]));  // (the bf16 kernel's "from zero")
+                        else A.part[((size_t)blockIdx.y * 32 + n) * A.R + row] = __uint_as_float(r[n]);
+                    }
+                }
+            }
+        } else if (threadIdx.x == 0 && nkb > 0) {
+            b2_fail(B2_ERR_TIMEOUT);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32u) : "memory");
+}
+
 struct TcReduceArgs {
     const float* part;
     bf16* y;
@@ -354,6 +543,87 @@ extern "C" int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int 
     TcArgs a{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, kps, splits, stages};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (const int rc = launch_tc<TC_BN, false>(tw, tx, a, dim3((R + TC_BM - 1) / TC_BM, splits), stages, s)) return rc;
+    if (splits > 1) {
+        TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(y), R, M, splits};
+        return b2_launch((const void*)gemv_tc_reduce, dim3((M * R + 255) / 256), dim3(256), 0, s, ra);
+    }
+    return B2_OK;
+}
+
+// a [rows, cols] byte matrix as a 2-D tensor map with boxes of box_rows x box_cols bytes, no swizzle, zeros outside
+static int make_map_u8(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+    CUtensorMap probe;
+    if (make_map(&probe, base, 1, 64, 1) != B2_OK) return B2_ERR_CUDA;  // (resolves the driver entry point once)
+    cudaDriverEntryPointQueryResult q;
+    void* p = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) {
+        (void)cudaGetLastError();
+        return B2_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t es[2] = {1, 1};
+    const CUresult rc = reinterpret_cast<EncodeFn>(p)(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                                                       es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? B2_OK : B2_ERR_CUDA;
+}
+
+// btb_b200_gemv_tc_bf16 over pack12 weights read as stored (parts as btb_b200_gemv_p12's; `table` a HOST pointer to the 16
+// high bytes): the sums of the bf16 kernel over the widened matrix, to the bit. C a multiple of 64. workspace as
+// btb_b200_gemv_tc_workspace_bytes(R, C).
+extern "C" int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx,
+                                    const void* esc_val, const void* esc_row, const void* x, void* y, int M, int R, int C,
+                                    void* workspace, void* stream) {
+    if (!lo || !hi4 || !table || !x || !y) return B2_ERR_NULL;
+    if (esc_row != nullptr && (!esc_idx || !esc_val)) return B2_ERR_NULL;
+    if (M < 1 || M > 32 || R <= 0 || C <= 0 || (C & 63)) return B2_ERR_DOMAIN;
+    if ((reinterpret_cast<uintptr_t>(lo) & 15) || (reinterpret_cast<uintptr_t>(hi4) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
+        return B2_ERR_DOMAIN;
+    int kps = 0;
+    const int splits = tc_splits(R, C, &kps);
+    if (splits > 1 && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15))) return B2_ERR_NULL;
+    CUtensorMap tl, th, tx;
+    if (make_map_u8(&tl, lo, (uint64_t)R, (uint64_t)C, TC_BK, TC_BM) || make_map_u8(&th, hi4, (uint64_t)R, (uint64_t)C / 2, TC_BK / 2, TC_BM) ||
+        make_map(&tx, x, (uint64_t)M, (uint64_t)C, TC_BN))
+        return B2_ERR_CUDA;
+    int stages = b2_tuning().tc_stages > 0 ? b2_tuning().tc_stages : 3;
+    stages = max(2, min(min(stages, TC_STAGES_MAX), (224 * 1024 - 1024) / P12_ST));
+    TcP12Args a{};
+    a.t = TcArgs{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, kps, splits, stages};
+    memcpy(a.table, table, 16);
+    a.esc_idx = static_cast<const int32_t*>(esc_idx), a.esc_val = static_cast<const uint8_t*>(esc_val);
+    a.esc_row = static_cast<const int32_t*>(esc_row);
+    static bool allowed[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
+    const int max_smem = ((224 * 1024 - 1024) / P12_ST) * P12_ST + 1024;
+    if (!allowed[dev]) {
+        if (cudaFuncSetAttribute(gemv_tc_p12, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return B2_ERR_CUDA;
+        }
+        allowed[dev] = true;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3((R + TC_BM - 1) / TC_BM, splits);
+    cfg.blockDim = dim3(384);
+    cfg.dynamicSmemBytes = stages * P12_ST + 1024;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    if (b2_tuning().pdl & 1) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+    }
+    void* params[4] = {&tl, &th, &tx, &a};
+    if (cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(gemv_tc_p12), params) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return B2_ERR_CUDA;
+    }
     if (splits > 1) {
         TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(y), R, M, splits};
         return b2_launch((const void*)gemv_tc_reduce, dim3((M * R + 255) / 256), dim3(256), 0, s, ra);

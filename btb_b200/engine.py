@@ -259,12 +259,17 @@ class CardEngine:
         self._n += 1
 
     def _matvec(self, W: Any, x: torch.Tensor, y: torch.Tensor, M: int, R: int, C_: int, s: int) -> None:
-        if self.wide_tc and M >= 4 and isinstance(W, torch.Tensor):
-            # a pass of several rows over bf16 weights: the tensor-core matvec (its own summation order)
+        if self.wide_tc and M >= 4 and (isinstance(W, torch.Tensor) or (isinstance(W, P12Matrix) and C_ % 64 == 0)):
+            # a pass of several rows over bf16 or pack12 weights: the tensor-core matvec (its own summation order; the
+            # packed store is widened tile by tile on its way into the MMA's operand - the same sums as over a bf16 copy)
             need = int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, C_))
             if self._tc_ws is None or self._tc_ws.numel() * 4 < need:
                 self._tc_ws = torch.zeros(max(need // 4, 4), dtype=torch.float32, device=self.dev)
-            self._k("btb_b200_gemv_tc_bf16", ptr(W), ptr(x), ptr(y), M, R, C_, ptr(self._tc_ws), s)
+            if isinstance(W, P12Matrix):
+                self._k("btb_b200_gemv_tc_p12", ptr(W.lo), ptr(W.hi4), W.table, ptr(W.esc_idx), ptr(W.esc_val),
+                        ptr(W.esc_row), ptr(x), ptr(y), M, R, C_, ptr(self._tc_ws), s)  # fmt: skip
+            else:
+                self._k("btb_b200_gemv_tc_bf16", ptr(W), ptr(x), ptr(y), M, R, C_, ptr(self._tc_ws), s)
             if need:
                 self._n += 1  # the ordered sum of the K ranges is a launch of its own
             return
@@ -286,7 +291,7 @@ class CardEngine:
         k = self._k
         # the residual ping-pongs between two buffers when the norm is folded into the GEMV that reads it (a CTA must
         # not read a row another CTA is updating); the pass starts and ends on g["h"]
-        tc = self.wide_tc and M >= 4 and isinstance(self.w.layers[0].qkv, torch.Tensor)
+        tc = self.wide_tc and M >= 4 and isinstance(self.w.layers[0].qkv, (torch.Tensor, P12Matrix))
         fuse = self.fuse_norm and M <= 8 and M * max(H, 1) * 2 <= 64 * 1024 and not tc
         hcur, halt = g["h"], g["h2"]
 

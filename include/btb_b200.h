@@ -51,6 +51,14 @@ int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int 
  * btb_b200_gemv_tc_workspace_bytes(R, C) bytes (0 for matrices of many rows), 16-byte aligned, for the K ranges'
  * partial sums of matrices with few rows. */
 int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* workspace, void* stream);
+/* btb_b200_gemv_tc_bf16 over pack12 weights read as stored (the parts of btb_b200_gemv_p12; `table` a HOST pointer to the
+ * 16 high bytes): TMA brings a tile's stored parts, four warps widen them in registers and write the bf16 operand tile
+ * into shared memory in the MMA's swizzled layout - no widened copy in global memory, and the sums are
+ * btb_b200_gemv_tc_bf16's over the widened matrix to the bit. C a multiple of 64; workspace as
+ * btb_b200_gemv_tc_workspace_bytes(R, C). The widen of btb/pack12.py:71-97 in front of btb_gemv_mma_bf16
+ * (btb_gemv_mma.cuh:123-315), which the reference runs over a widened copy (btb/engine/tiers.py:1198-1218). */
+int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void* table, const void* esc_idx, const void* esc_val,
+                         const void* esc_row, const void* x, void* y, int M, int R, int C, void* workspace, void* stream);
 size_t btb_b200_gemv_tc_workspace_bytes(int R, int C);
 /* btb_gemv_mma_glu_silu (native/cuda/btb_gemv_mma.cuh:216-315): the gate/up form of the tensor-core matvec. w [2I, C]
  * (gate rows, then up rows), x [M, C]; m [M, I] = bf16(bf16(silu(g)) * u) over the matvec's bf16 outputs g, u at rows i

@@ -5,6 +5,8 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import oracle as O
+
 pytestmark = pytest.mark.gpu
 
 if not torch.cuda.is_available():
@@ -236,3 +238,51 @@ def test_launcher_serves_the_reference_mma8_and_glu_names():
     torch.cuda.synchronize()
     assert float((m[:M].float() - m2[:M].float()).abs().max()) <= 2.0**-6 * float(ref.abs().max())
     assert float((y8[:M].float() - y2[:M].float()).abs().max()) <= 2.0**-7 * float(y2[:M].float().abs().max())
+
+
+# ---- the tensor-core matvec over pack12 weights read as stored ------------------------------------------------------------
+
+
+@pytest.mark.parametrize("R,Cc,dense", [(300, 2560, False), (2560, 9728, False), (19456, 2560, False), (200, 256, True),
+                                        (129, 64, True), (6144, 2560, True)])  # fmt: skip
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_tc_matvec_over_pack12_equals_the_bf16_kernel_over_the_widened_matrix(R, Cc, dense, M):
+    """the packed tile is widened on its way into the MMA's operand: the same bits in the same places as the bf16 tile
+    TMA would have brought, so the same sums - escapes, partial tiles and K ranges included"""
+    from btb_b200.engine import P12Matrix
+
+    from .test_gpu_kernels import _p12_case, bf, bits, rand_bf
+
+    rng = np.random.default_rng(R + Cc + M)
+    wb, parts = _p12_case(rng, R, Cc, dense)
+    if dense:
+        assert parts[3].size > 0
+    x = rand_bf(rng, (M, Cc))
+    P = P12Matrix(parts, R, Cc, "cuda")
+    wt, xt = bf(wb), bf(x)
+    need = int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, Cc))
+    ws = torch.full((max(need // 4, 4),), float("nan"), dtype=torch.float32, device="cuda")
+    ya = torch.zeros(M, R, dtype=torch.bfloat16, device="cuda")
+    yb = torch.full((M, R), 3.0, dtype=torch.bfloat16, device="cuda")
+    call("btb_b200_gemv_tc_bf16", ptr(wt), ptr(xt), ptr(ya), M, R, Cc, ptr(ws), capi.stream_ptr())
+    ws.fill_(float("nan"))
+    call("btb_b200_gemv_tc_p12", ptr(P.lo), ptr(P.hi4), P.table, ptr(P.esc_idx), ptr(P.esc_val), ptr(P.esc_row), ptr(xt), ptr(yb),
+         M, R, Cc, ptr(ws), capi.stream_ptr())  # fmt: skip
+    torch.cuda.synchronize()
+    assert capi.status() == 0
+    assert torch.equal(ya.view(torch.int16), yb.view(torch.int16))
+    # and it tracks the fp32-chain kernel to rounding, as the bf16 form does
+    want = O.bits_to_f32(O.gemv_card_bf16(wb, x))
+    got = yb.float().cpu().numpy()
+    assert np.max(np.abs(got - want)) <= 2.0**-6 * max(1.0, float(np.max(np.abs(want))))
+
+
+def test_tc_p12_refusals():
+    z = torch.zeros(64, 96, dtype=torch.uint8, device="cuda")
+    x = torch.zeros(1, 96, dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros(1, 64, dtype=torch.bfloat16, device="cuda")
+    tab = bytes(16)
+    with pytest.raises(capi.NativeError):  # C not a multiple of 64
+        call("btb_b200_gemv_tc_p12", ptr(z), ptr(z), tab, 0, 0, 0, ptr(x), ptr(y), 1, 64, 96, 0, capi.stream_ptr())
+    with pytest.raises(capi.NativeError):
+        call("btb_b200_gemv_tc_p12", 0, ptr(z), tab, 0, 0, 0, ptr(x), ptr(y), 1, 64, 128, 0, capi.stream_ptr())
