@@ -755,7 +755,7 @@ def ref_kernel_tokens(args, ref, n_prompt: int = 48, n_new: int = 16) -> dict:
 
 def run_case(args) -> None:
     """one kernel on a small case, for a profiler capture or a quick look: `gemv:RxC[:M[:fmt]]` rotates over enough
-    seeded matrices to stay out of L2 (fmt bf16 | p12 | fp8 | tc: the tensor-core matvec); `attn:N` is the step's fused
+    seeded matrices to stay out of L2 (fmt bf16 | p12 | fp8 | tc: the tensor-core matvec | tcp12: the same over pack12 weights); `attn:N` is the step's fused
     attention row over N cached rows at the Qwen3-4B head shape, `attnv:N:T` a verify pass's T rows over N cached rows. Prints us a launch (CUDA events) and, for a GEMV, the weight-streaming rate."""
     import torch
 
@@ -772,13 +772,13 @@ def run_case(args) -> None:
         R, C_ = (int(v) for v in parts[0].split("x"))
         M = int(parts[1]) if len(parts) > 1 else 1
         fmt = parts[2] if len(parts) > 2 else "bf16"
-        per = R * C_ * {"p12": 1.5, "fp8": 1.0}.get(fmt, 2)
+        per = R * C_ * {"p12": 1.5, "tcp12": 1.5, "fp8": 1.0}.get(fmt, 2)
         nmat = max(2, int(400e6 // per) + 1)
         gen = torch.Generator(device="cuda").manual_seed(0)
         ws = []
         for _ in range(nmat):
             w = torch.randn(R, C_, device="cuda", generator=gen).mul_(0.02).to(torch.bfloat16)
-            if fmt == "p12":
+            if fmt in ("p12", "tcp12"):
                 from btb_b200 import pack12
 
                 w = E.P12Matrix(pack12.pack_bf16(w), R, C_, "cuda")
@@ -792,12 +792,15 @@ def run_case(args) -> None:
         y = torch.zeros(M, R, device="cuda", dtype=torch.bfloat16)
 
         ws_tc = None
-        if fmt == "tc":
+        if fmt in ("tc", "tcp12"):
             ws_tc = torch.zeros(max(int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, C_)) // 4, 4), device="cuda")
 
         def one(w):
             if fmt == "tc":
                 call("btb_b200_gemv_tc_bf16", ptr(w), ptr(x), ptr(y), M, R, C_, ptr(ws_tc), sp)
+            elif fmt == "tcp12":
+                call("btb_b200_gemv_tc_p12", ptr(w.lo), ptr(w.hi4), w.table, ptr(w.esc_idx), ptr(w.esc_val), ptr(w.esc_row),
+                     ptr(x), ptr(y), M, R, C_, ptr(ws_tc), sp)  # fmt: skip
             elif fmt == "p12":
                 call("btb_b200_gemv_p12", ptr(w.lo), ptr(w.hi4), w.table, ptr(w.esc_idx), ptr(w.esc_val), ptr(w.esc_row),
                      ptr(x), ptr(y), M, R, C_, sp)  # fmt: skip

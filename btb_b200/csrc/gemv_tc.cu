@@ -235,9 +235,15 @@ __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_consta
 // brings the tile's stored parts - 128 rows x 64 low bytes and 128 rows x 32 bytes of codes - into a staging area, eight
 // more warps (a 16-byte piece of a row a thread) widen them in registers (p12_chunk: the GEMV's own widen, escapes from the row's
 // list) and write the bf16 tile into shared memory in the 128-byte-swizzled layout the MMA reads (16-byte piece c of row
-// d at piece c ^ (d & 7)), make it visible to the async proxy and count themselves in on the stage's second barrier;
-// the issuer waits for that one. No widened copy is ever in global memory, and the sums are btb_b200_gemv_tc_bf16's
-// over the widened matrix to the bit (the operands are the same bits in the same places).
+// d at piece c ^ (d & 7)), make it visible to the async proxy, meet on a named barrier and one of them counts the tile
+// in on the stage's second mbarrier; the issuer waits for that one. No widened copy is ever in global memory, and the
+// sums are btb_b200_gemv_tc_bf16's over the widened matrix to the bit (the operands are the same bits in the same places).
+//
+// What bounds it is not memory: with the loads, the widening and the MMAs all taken out, a K block still cost about
+// half a microsecond of barrier hand-offs (wait, named barrier, arrive, the issuer's wait and commit, the producer's
+// wait), whatever the ring's depth, and the widening's own dependent chain added as much again in series. Hence one
+// arrival a tile instead of one a thread, and two groups of wideners on alternate K blocks, so that one group's
+// hand-offs run under the other's arithmetic.
 constexpr int P12_LO = TC_BM * TC_BK;          // a stage's low bytes
 constexpr int P12_HI = TC_BM * TC_BK / 2;      // ... and codes
 constexpr int P12_B = TC_BN * TC_BK * 2;       // x's tile
@@ -250,7 +256,19 @@ struct TcP12Args {
     const int32_t* esc_row;  // [R + 1] or null: no escapes anywhere
 };
 
-__global__ void __launch_bounds__(384, 2) gemv_tc_p12(const __grid_constant__ CUtensorMap tmLo,
+// one group's named barrier (ids 1 ..): true if any of its `GT` threads came with `bad`
+template <int ID, int GT>
+__device__ __forceinline__ int p12_group_bar(bool bad) {
+    int any_bad;
+    asm volatile("{\n.reg .pred q, r;\nsetp.ne.b32 q, %1, 0;\nbar.red.or.pred r, %3, %2, q;\nselp.b32 %0, 1, 0, r;\n}\n"
+                 : "=r"(any_bad)
+                 : "r"((int)bad), "n"(GT), "n"(ID)
+                 : "memory");
+    return any_bad;
+}
+
+template <int NW, int NG>
+__global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_constant__ CUtensorMap tmLo,
                                                       const __grid_constant__ CUtensorMap tmHi,
                                                       const __grid_constant__ CUtensorMap tmX, const TcP12Args P) {
     const TcArgs& A = P.t;
@@ -268,7 +286,7 @@ __global__ void __launch_bounds__(384, 2) gemv_tc_p12(const __grid_constant__ CU
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
             mbar_init(smem_u32(&full_p[s]), 1);
-            mbar_init(smem_u32(&full_a[s]), 256);
+            mbar_init(smem_u32(&full_a[s]), 1);
             mbar_init(smem_u32(&empty[s]), 1);
         }
         mbar_init(smem_u32(&done), 1);
@@ -319,21 +337,25 @@ __global__ void __launch_bounds__(384, 2) gemv_tc_p12(const __grid_constant__ CU
         }
         umma_commit(smem_u32(&done));
     } else if (warp >= 4) {
-        // the wideners: eight warps; a thread takes 16-byte piece c = t & 7 of rows (t >> 3) + 32 i. A warp's lanes then read
-        // four consecutive rows' stored bytes (256 and 128 contiguous bytes) and write four whole rows of the operand tile:
-        // no bank conflicts anywhere (a row a thread made every read a 16-way conflict)
-        const int t = threadIdx.x - 128, c = t & 7;
-        constexpr int RPT = TC_BM / 32;  // rows a thread
+        // the wideners: NG groups of NW / NG warps that take the tile's K blocks in turn (group g the blocks kb = g, g + NG,
+        // ...), so that one group's barrier round trips run under the other's arithmetic. A thread takes 16-byte piece
+        // c of rows (tg >> 3) + RG i: a warp's lanes read four consecutive rows' stored bytes (256 and 128 contiguous bytes)
+        // and write four whole rows of the operand tile - no bank conflicts anywhere.
+        constexpr int GT = NW * 32 / NG;  // threads a group
+        const int t = threadIdx.x - 128, grp = t / GT, tg = t - grp * GT, c = tg & 7;
+        constexpr int RG = GT / 8;       // rows in work at once: eight lanes a row
+        constexpr int RPT = TC_BM / RG;  // rows a thread
         // Escapes (a code of 15: the high byte comes from the matrix's ascending list) are not looked up a weight: row d of
-        // the tile has an owner among these threads, which walks the row's run of the list once, forwards only - the
-        // tile's K blocks come in ascending order - and patches the high bytes into the tile after it is written.
-        const int own = c < RPT ? (t >> 3) + 32 * c : -1;  // the tile row this thread owns, if any
+        // a tile has an owner among the eight lanes that write it, which walks the row's run of the list forwards - the
+        // group's K blocks come in ascending order; the entries of the other group's blocks are passed over - and patches
+        // the high bytes in once the warp has written the row.
+        const int own = c < RPT ? (tg >> 3) + RG * c : -1;  // the tile row this thread owns, if any
         int cur = 0, end = 0, peek = 0x7fffffff;
         if (own >= 0 && P.esc_row != nullptr && row0 + own < A.R) {
             cur = __ldg(P.esc_row + row0 + own), end = __ldg(P.esc_row + row0 + own + 1);
             // (a K range that does not start at column 0: skip the entries before it)
             const int from = (int)((size_t)(row0 + own) * A.C + (size_t)kb0 * TC_BK);
-            int a = cur, b = end;
+            int a = cur, b = kb0 > 0 ? end : cur;
             while (a < b) {
                 const int mid = (a + b) >> 1;
                 if (__ldg(P.esc_idx + mid) < from) a = mid + 1;
@@ -342,43 +364,44 @@ __global__ void __launch_bounds__(384, 2) gemv_tc_p12(const __grid_constant__ CU
             cur = a;
             if (cur < end) peek = __ldg(P.esc_idx + cur);
         }
-        for (int kb = 0; kb < nkb; ++kb) {
+        for (int kb = grp; kb < nkb; kb += NG) {
             const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
             bool bad = !mbar_wait_bounded(smem_u32(&full_p[s]), ph);
             if (bad) *(volatile int*)&s_fail = 1;
-            bad = bad || *(volatile int*)&s_fail != 0;
+            bad = __any_sync(0xffffffffu, bad || *(volatile int*)&s_fail != 0);  // (one answer a warp: it syncs below)
             uint8_t* st = tiles + (size_t)s * P12_ST;
             if (!bad) {
 #pragma unroll
                 for (int i = 0; i < RPT; ++i) {
-                    const int d = (t >> 3) + 32 * i;
+                    const int d = (tg >> 3) + RG * i;
                     const uint2 l = *reinterpret_cast<const uint2*>(st + A_BYTES + P12_B + d * TC_BK + c * 8);
                     const uint32_t codes = *reinterpret_cast<const uint32_t*>(st + A_BYTES + P12_B + P12_LO + d * (TC_BK / 2) + c * 4);
                     uint32_t wp[4];
                     p12_chunk(l.x, l.y, codes, P.table, wp);
                     *reinterpret_cast<uint4*>(st + d * 128 + ((c ^ (d & 7)) << 4)) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
                 }
-            }
-            // the tile is written: the wideners' own barrier, which also carries the one answer every one of them acts on
-            // (a thread leaving the loop alone would leave the others at the next barrier for good)
-            int any_bad;
-            asm volatile("{\n.reg .pred q, r;\nsetp.ne.b32 q, %1, 0;\nbar.red.or.pred r, 1, 256, q;\nselp.b32 %0, 1, 0, r;\n}\n"
-                         : "=r"(any_bad)
-                         : "r"((int)bad)
-                         : "memory");
-            if (any_bad) break;
-            if (own >= 0) {
-                // (prefetching a window of the row's next entries every stage was measured slower: most rows have none)
-                const int base = (int)((size_t)(row0 + own) * A.C + (size_t)(kb0 + kb) * TC_BK);
-                while (peek < base + TC_BK) {  // this K block's escapes of the row
-                    const int col = peek - base;
-                    st[own * 128 + (((col >> 3) ^ (own & 7)) << 4) + (col & 7) * 2 + 1] = __ldg(P.esc_val + cur);
-                    ++cur;
-                    peek = cur < end ? __ldg(P.esc_idx + cur) : 0x7fffffff;
+                __syncwarp();  // a row's eight writers are lanes of one warp, its owner among them
+                if (own >= 0) {
+                    // (prefetching a window of the row's next entries every stage was measured slower: most rows have none)
+                    const int base = (int)((size_t)(row0 + own) * A.C + (size_t)(kb0 + kb) * TC_BK);
+                    while (peek < base + TC_BK) {  // the row's entries up to the end of this K block
+                        const int col = peek - base;
+                        if (col >= 0) st[own * 128 + (((col >> 3) ^ (own & 7)) << 4) + (col & 7) * 2 + 1] = __ldg(P.esc_val + cur);
+                        ++cur;
+                        peek = cur < end ? __ldg(P.esc_idx + cur) : 0x7fffffff;
+                    }
                 }
             }
             fence_proxy_async();  // the tile's bytes, written by ordinary stores, are the MMA's (an async-proxy reader) to see
-            mbar_arrive(smem_u32(&full_a[s]));
+            // the tile is written: the group's own barrier, which also carries the one answer every one of its threads acts
+            // on (a thread leaving the loop alone would leave the others at the next barrier for good); one of them then
+            // counts the tile in for the issuer (an arrival a thread on one barrier word was most of a stage's time)
+            const int any_bad = grp == 0   ? p12_group_bar<1, GT>(bad)
+                                : grp == 1 ? p12_group_bar<2, GT>(bad)
+                                : grp == 2 ? p12_group_bar<3, GT>(bad)
+                                           : p12_group_bar<4, GT>(bad);
+            if (any_bad) break;
+            if (tg == 0) mbar_arrive(smem_u32(&full_a[s]));
         }
     }
     __syncwarp();
@@ -388,24 +411,22 @@ __global__ void __launch_bounds__(384, 2) gemv_tc_p12(const __grid_constant__ CU
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok && nkb > 0 && !*(volatile int*)&s_fail) {
             const int row = row0 + warp * 32 + lane;
-            uint32_t r[32];
-            const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
-                "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                  "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-                  "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                : "r"(taddr));
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (row < A.R) {
+            // (eight columns at a time keeps the kernel's registers at the wideners' need)
+            for (int n0 = 0; n0 < A.M; n0 += 8) {
+                uint32_t r[8];
+                const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)n0;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                             : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row < A.R) {
 #pragma unroll
-                for (int n = 0; n < 32; ++n) {
-                    if (n < A.M) {
-                        if (A.splits == 1) A.y[(size_t)n * A.R + row] = f2bf(0.f + __uint_as_float(r[n]));  // (the bf16 kernel's "from zero")
-                        else A.part[((size_t)blockIdx.y * 32 + n) * A.R + row] = __uint_as_float(r[n]);
+                    for (int j = 0; j < 8; ++j) {
+                        const int n = n0 + j;
+                        if (n < A.M) {
+                            if (A.splits == 1) A.y[(size_t)n * A.R + row] = f2bf(0.f + __uint_as_float(r[j]));  // (the bf16 kernel's "from zero")
+                            else A.part[((size_t)blockIdx.y * 32 + n) * A.R + row] = __uint_as_float(r[j]);
+                        }
                     }
                 }
             }
@@ -600,7 +621,7 @@ extern "C" int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void*
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2_ERR_CUDA;
     const int max_smem = ((224 * 1024 - 1024) / P12_ST) * P12_ST + 1024;
     if (!allowed[dev]) {
-        if (cudaFuncSetAttribute(gemv_tc_p12, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) {
+        if (cudaFuncSetAttribute(gemv_tc_p12<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) {
             (void)cudaGetLastError();
             return B2_ERR_CUDA;
         }
@@ -610,7 +631,8 @@ extern "C" int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void*
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3((R + TC_BM - 1) / TC_BM, splits);
-    cfg.blockDim = dim3(384);
+    // (eight widener warps in two groups: twelve in three and sixteen in two or four were measured slower)
+    cfg.blockDim = dim3(128 + 32 * 8);
     cfg.dynamicSmemBytes = stages * P12_ST + 1024;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -620,7 +642,8 @@ extern "C" int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void*
         cfg.attrs = attr, cfg.numAttrs = 1;
     }
     void* params[4] = {&tl, &th, &tx, &a};
-    if (cudaLaunchKernelExC(&cfg, reinterpret_cast<const void*>(gemv_tc_p12), params) != cudaSuccess) {
+    const void* kern = reinterpret_cast<const void*>(gemv_tc_p12<8, 2>);
+    if (cudaLaunchKernelExC(&cfg, kern, params) != cudaSuccess) {
         (void)cudaGetLastError();
         return B2_ERR_CUDA;
     }
