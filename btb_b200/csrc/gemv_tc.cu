@@ -15,6 +15,8 @@
 // accumulator with tcgen05.ld (a weight row a thread) and writes bf16. Matrices of few tiles (2560 rows: 20) split K
 // over gridDim.y; the partial sums meet in a second, ordered pass (the same order every launch). No cluster
 // multicast; every wait is bounded and a CTA that gives up still frees its tensor memory.
+// (Adding the ranges in the matvec kernel itself - the CTA that arrives last on a tile's counter sums the partial
+// sums - was measured slower than the second launch: one CTA's threads have too few loads in flight for the job.)
 #include <cuda.h>
 
 #include "btb_b200_internal.h"

@@ -52,7 +52,7 @@ int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int 
  * partial sums of matrices with few rows. */
 int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* workspace, void* stream);
 /* btb_b200_gemv_tc_bf16 over pack12 weights read as stored (the parts of btb_b200_gemv_p12; `table` a HOST pointer to the
- * 16 high bytes): TMA brings a tile's stored parts, four warps widen them in registers and write the bf16 operand tile
+ * 16 high bytes): TMA brings a tile's stored parts, eight warps widen them in registers and write the bf16 operand tile
  * into shared memory in the MMA's swizzled layout - no widened copy in global memory, and the sums are
  * btb_b200_gemv_tc_bf16's over the widened matrix to the bit. C a multiple of 64; workspace as
  * btb_b200_gemv_tc_workspace_bytes(R, C). The widen of btb/pack12.py:71-97 in front of btb_gemv_mma_bf16
