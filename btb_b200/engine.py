@@ -328,6 +328,18 @@ class CardEngine:
                 self._matvec(L.down, g["m"], g["y"], M, H, I, s)
                 y_prev = g["y"]
                 continue
+            if tc and isinstance(L.gu, torch.Tensor):
+                # the tensor-core matvec's gate/up form: the activation in its epilogue (the matvec and silu_mul, to the bit)
+                k("btb_b200_add_rmsnorm", ptr(hcur), ptr(g["y"]), ptr(L.ln2), c.eps, ptr(g["x"]), T, H, 0, s)
+                need = int(capi.lib().btb_b200_gemv_tc_glu_workspace_bytes(I, H))
+                if self._tc_ws is None or self._tc_ws.numel() * 4 < need:
+                    self._tc_ws = torch.zeros(max(need // 4, 4), dtype=torch.float32, device=self.dev)
+                k("btb_b200_gemv_tc_glu_bf16", ptr(L.gu), ptr(g["x"]), ptr(g["m"]), M, I, H, ptr(self._tc_ws), s)
+                if need:
+                    self._n += 1
+                self._matvec(L.down, g["m"], g["y"], M, H, I, s)
+                y_prev = g["y"]
+                continue
             normed_matvec(L.gu, L.ln2, g["y"], g["gu"], 2 * I)
             if self.silu_fold and M <= 8 and M * I * 2 <= 160 * 1024 and not tc:
                 if isinstance(L.down, P12Matrix):
