@@ -28,6 +28,7 @@ struct B2Tuning {
     int l2_warm_kb;   // the step's attention launch pulls at most this much of the next kernels' weights into L2 (0: off)
     int l2_warm_ctas; // blocks that do it (0: every SM the attention's own blocks leave idle)
     int warps_packed; // warps a GEMV CTA prefers over rows widened in registers (pack12, FP8); 0: the bf16 preference
+    int tc_fold;      // the tensor-core matvec adds its K ranges' partial sums in the launch itself (0: a second launch)
 };
 B2Tuning& b2_tuning();
 int b2_sm_count();

@@ -23,6 +23,7 @@ B2Tuning& b2_tuning() {
         env_int("BTB_B200_X_DIRECT", 1),
         env_int("BTB_B200_L2_WARM_KB", 0),         env_int("BTB_B200_L2_WARM_CTAS", 0),
         env_int("BTB_B200_WARPS_PACKED", 24),
+        env_int("BTB_B200_TC_FOLD", 0),
     };
     return t;
 }
@@ -60,6 +61,7 @@ extern "C" int btb_b200_set_tuning(const char* key, int value) {
     else if (!strcmp(key, "l2_warm_kb")) t.l2_warm_kb = value < 0 ? 0 : value;
     else if (!strcmp(key, "l2_warm_ctas")) t.l2_warm_ctas = value < 0 ? 0 : value;
     else if (!strcmp(key, "warps_packed")) t.warps_packed = value;
+    else if (!strcmp(key, "tc_fold")) t.tc_fold = value != 0;
     else if (!strcmp(key, "ms_tpr")) t.ms_tpr = value;
     else if (!strcmp(key, "ms_ctas")) t.ms_ctas = value < 0 ? 0 : value;
     else if (!strcmp(key, "ms_seg")) t.ms_seg = value < 0 ? 0 : value & ~31;

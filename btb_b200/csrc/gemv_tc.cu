@@ -15,9 +15,10 @@
 // accumulator with tcgen05.ld (a weight row a thread) and writes bf16. Matrices of few tiles (2560 rows: 20) split K
 // over gridDim.y; the partial sums meet in a second, ordered pass (the same order every launch). No cluster
 // multicast; every wait is bounded and a CTA that gives up still frees its tensor memory.
-// (Adding the ranges in the matvec kernel itself - the CTA that arrives last on a tile's counter sums the partial
-// sums - was measured slower than the second launch: one CTA's threads have too few loads in flight for the job.)
 #include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
 
 #include "btb_b200_internal.h"
 #include "gemv_core.cuh"
@@ -69,6 +70,9 @@ struct TcArgs {
     // the gate/up form: the matrix is [2 * glu_I, C] (gate rows, then up rows); a tile takes 64 gate rows and, glu_I rows
     // on, their 64 up rows, and writes m [M, glu_I] = bf16(bf16(silu(bf16 g)) * bf16 u). 0: the plain matvec.
     int glu_I;
+    // the plain matvec cut over K: a counter a tile (zero between launches); the CTA that finds the others' partial sums
+    // all written adds them, in range order, itself
+    int* cnt;
 };
 
 // BN: the x rows a CTA's tile holds. GEMM false: the matvec - one accumulator of 32 columns, gridDim.y cuts K into
@@ -77,6 +81,46 @@ struct TcArgs {
 // own BN columns of tensor memory and the epilogue adds the ranges in order, so an output element is the matvec's sum
 // to the bit whatever the chunk's size and wherever in the chunk the row stands.
 __device__ __forceinline__ float tc_silu(float g) { return g / (1.f + expf(-g)); }
+
+constexpr int TC_WS_HEAD = 1024;  // the workspace's first bytes: the tiles' counters (a split matrix has at most 148 tiles)
+
+// The end of a matvec CTA whose tile is cut over K (every thread of the CTA calls it, after its partial sums are
+// written): the CTA that arrives last on the tile's counter adds the ranges' partial sums in range order - the same sum
+// every launch, rounded to bf16 once - and leaves the counter at zero for the next launch. A CTA that gave up counts
+// too (the status word already says so), so that a failed launch does not leave a counter standing. NT threads: thread
+// t takes row t % 128 and the x rows t / 128, + NT / 128, ..; two x rows' loads (up to 32) are in flight at once - summed
+// one load after the other, the job took longer than a second launch.
+template <int NT>
+__device__ __forceinline__ void tc_finish_split(const TcArgs& A, int row0, int* s_last) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *s_last = atomicAdd(A.cnt + blockIdx.x, 1) == A.splits - 1;
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    constexpr int NG = NT / TC_BM;  // x rows in work at once
+    const int row = row0 + ((int)threadIdx.x & (TC_BM - 1)), g = (int)threadIdx.x / TC_BM;
+    if (g < NG && row < A.R) {
+        for (int n = g; n < A.M; n += 2 * NG) {
+            float v[2][16];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int k = 0; k < 16; ++k)
+                    v[j][k] = (k < A.splits && n + j * NG < A.M) ? __ldcg(A.part + ((size_t)k * 32 + n + j * NG) * A.R + row) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                if (n + j * NG >= A.M) break;
+                float s = 0.f;
+#pragma unroll
+                for (int k = 0; k < 16; ++k)
+                    if (k < A.splits) s += v[j][k];
+                A.y[(size_t)(n + j * NG) * A.R + row] = f2bf(s);
+            }
+        }
+    }
+    if (threadIdx.x == 0) A.cnt[blockIdx.x] = 0;
+}
 
 template <int BN, bool GEMM>
 __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_constant__ CUtensorMap tmW,
@@ -230,6 +274,7 @@ __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_consta
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
+    if (!GEMM && !glu && A.splits > 1 && A.cnt != nullptr) tc_finish_split<128>(A, row0, &s_fail);  // (the flag's word is free by now)
 }
 
 // ---- the same matvec over pack12 weights read as stored ----------------------------------------------------------------------
@@ -439,6 +484,7 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32u) : "memory");
+    if (A.splits > 1 && A.cnt != nullptr) tc_finish_split<128 + 32 * NW>(A, row0, &s_fail);  // (the flag's word is free by now)
 }
 
 struct TcReduceArgs {
@@ -475,10 +521,35 @@ typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void
                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// a [rows, cols] bf16 row-major matrix as a 2-D tensor map with boxes of box_rows x 64 columns, 128-byte swizzle,
-// zeros outside the matrix
-int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// A 2-D tensor map of a row-major matrix, made once a (matrix, box) and kept: a weight matrix is encoded the first
+// time it is used, an activation buffer likewise (an engine reuses its buffers), so an eager launch does not pay the
+// driver's encode every time. The map depends on nothing but its key - the address, the extents, the box and the element
+// kind - so an entry never goes stale; the table is emptied when it has grown to 4096 entries.
+struct MapKey {
+    const void* base;
+    uint64_t rows, cols;
+    uint32_t box_cols, box_rows, kind;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows && kind == o.kind;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.rows + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+        h ^= (k.cols + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2));
+        h ^= (((uint64_t)k.box_cols << 40) ^ ((uint64_t)k.box_rows << 8) ^ k.kind) + (h << 6) + (h >> 2);
+        return (size_t)h;
+    }
+};
+// kind 0: bf16 elements, boxes of box_rows x 64 columns under the 128-byte swizzle; kind 1: bytes, boxes of
+// box_rows x box_cols, no swizzle. Zeros outside the matrix either way.
+int make_map_kind(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows, uint32_t kind) {
     static EncodeFn fn = nullptr;
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> kept;
+    const MapKey key{base, rows, cols, box_cols, box_rows, kind};
+    std::lock_guard<std::mutex> lock(mu);
     if (fn == nullptr) {
         cudaDriverEntryPointQueryResult q;
         void* p = nullptr;
@@ -488,14 +559,28 @@ int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, ui
         }
         fn = reinterpret_cast<EncodeFn>(p);
     }
+    const auto it = kept.find(key);
+    if (it != kept.end()) {
+        *tm = it->second;
+        return B2_OK;
+    }
+    const uint64_t es_bytes = kind == 0 ? 2 : 1;
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, box_rows};
+    cuuint64_t strides[1] = {cols * es_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t es[2] = {1, 1};
-    const CUresult rc = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    const CUresult rc = fn(tm, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base),
+                           dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return rc == CUDA_SUCCESS ? B2_OK : B2_ERR_CUDA;
+    if (rc != CUDA_SUCCESS) return B2_ERR_CUDA;
+    if (kept.size() >= 4096) kept.clear();
+    kept.emplace(key, *tm);
+    return B2_OK;
+}
+// a [rows, cols] bf16 row-major matrix: boxes of box_rows x 64 columns, 128-byte swizzle
+int make_map(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    return make_map_kind(tm, base, rows, cols, (uint32_t)TC_BK, box_rows, 0);
 }
 
 // K ranges a matrix is cut into: enough CTAs for two an SM, a whole number of K blocks each; a function of the
@@ -549,7 +634,7 @@ int launch_tc(CUtensorMap& tw, CUtensorMap& tx, TcArgs& a, dim3 grid, int stages
 extern "C" size_t btb_b200_gemv_tc_workspace_bytes(int R, int C) {
     if (R <= 0 || C <= 0) return 0;
     const int s = tc_splits(R, C);
-    return s > 1 ? (size_t)s * 32 * R * sizeof(float) : 0;
+    return s > 1 ? TC_WS_HEAD + (size_t)s * 32 * R * sizeof(float) : 0;
 }
 
 extern "C" int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* workspace,
@@ -563,34 +648,24 @@ extern "C" int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int 
     CUtensorMap tw, tx;
     if (make_map(&tw, w, (uint64_t)R, (uint64_t)C, TC_BM) || make_map(&tx, x, (uint64_t)M, (uint64_t)C, TC_BN)) return B2_ERR_CUDA;
     const int stages = b2_tuning().tc_stages > 0 ? min(TC_STAGES_MAX, b2_tuning().tc_stages) : 4;
-    TcArgs a{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, kps, splits, stages};
+    float* part = splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TC_WS_HEAD) : nullptr;
+    const int tiles = (R + TC_BM - 1) / TC_BM;
+    // the `tc_fold` tunable: the last CTA of a tile adds the ranges itself instead of the second launch. Measured equal
+    // (its fences, counter round trip and loads cost what the launch does), so the second launch stays the default.
+    const bool in_kernel = splits > 1 && splits <= 16 && tiles * (int)sizeof(int) <= TC_WS_HEAD && b2_tuning().tc_fold;
+    TcArgs a{static_cast<bf16*>(y), part, R, C, M, kps, splits, stages, 0, in_kernel ? static_cast<int*>(workspace) : nullptr};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (const int rc = launch_tc<TC_BN, false>(tw, tx, a, dim3((R + TC_BM - 1) / TC_BM, splits), stages, s)) return rc;
-    if (splits > 1) {
-        TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(y), R, M, splits};
+    if (const int rc = launch_tc<TC_BN, false>(tw, tx, a, dim3(tiles, splits), stages, s)) return rc;
+    if (splits > 1 && !in_kernel) {
+        TcReduceArgs ra{part, static_cast<bf16*>(y), R, M, splits};
         return b2_launch((const void*)gemv_tc_reduce, dim3((M * R + 255) / 256), dim3(256), 0, s, ra);
     }
     return B2_OK;
 }
 
-// a [rows, cols] byte matrix as a 2-D tensor map with boxes of box_rows x box_cols bytes, no swizzle, zeros outside
+// a [rows, cols] byte matrix: boxes of box_rows x box_cols bytes, no swizzle
 static int make_map_u8(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
-    CUtensorMap probe;
-    if (make_map(&probe, base, 1, 64, 1) != B2_OK) return B2_ERR_CUDA;  // (resolves the driver entry point once)
-    cudaDriverEntryPointQueryResult q;
-    void* p = nullptr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || p == nullptr) {
-        (void)cudaGetLastError();
-        return B2_ERR_CUDA;
-    }
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols};
-    cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t es[2] = {1, 1};
-    const CUresult rc = reinterpret_cast<EncodeFn>(p)(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                                                       es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return rc == CUDA_SUCCESS ? B2_OK : B2_ERR_CUDA;
+    return make_map_kind(tm, base, rows, cols, box_cols, box_rows, 1);
 }
 
 // btb_b200_gemv_tc_bf16 over pack12 weights read as stored (parts as btb_b200_gemv_p12's; `table` a HOST pointer to the 16
@@ -614,7 +689,10 @@ extern "C" int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void*
     int stages = b2_tuning().tc_stages > 0 ? b2_tuning().tc_stages : 3;
     stages = max(2, min(min(stages, TC_STAGES_MAX), (224 * 1024 - 1024) / P12_ST));
     TcP12Args a{};
-    a.t = TcArgs{static_cast<bf16*>(y), static_cast<float*>(workspace), R, C, M, kps, splits, stages};
+    float* part = splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TC_WS_HEAD) : nullptr;
+    const int tiles = (R + TC_BM - 1) / TC_BM;
+    const bool in_kernel = splits > 1 && splits <= 16 && tiles * (int)sizeof(int) <= TC_WS_HEAD && b2_tuning().tc_fold;
+    a.t = TcArgs{static_cast<bf16*>(y), part, R, C, M, kps, splits, stages, 0, in_kernel ? static_cast<int*>(workspace) : nullptr};
     memcpy(a.table, table, 16);
     a.esc_idx = static_cast<const int32_t*>(esc_idx), a.esc_val = static_cast<const uint8_t*>(esc_val);
     a.esc_row = static_cast<const int32_t*>(esc_row);
@@ -632,7 +710,7 @@ extern "C" int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void*
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
-    cfg.gridDim = dim3((R + TC_BM - 1) / TC_BM, splits);
+    cfg.gridDim = dim3(tiles, splits);
     // (eight widener warps in two groups: twelve in three and sixteen in two or four were measured slower)
     cfg.blockDim = dim3(128 + 32 * 8);
     cfg.dynamicSmemBytes = stages * P12_ST + 1024;
@@ -649,8 +727,8 @@ extern "C" int btb_b200_gemv_tc_p12(const void* lo, const void* hi4, const void*
         (void)cudaGetLastError();
         return B2_ERR_CUDA;
     }
-    if (splits > 1) {
-        TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(y), R, M, splits};
+    if (splits > 1 && !in_kernel) {
+        TcReduceArgs ra{part, static_cast<bf16*>(y), R, M, splits};
         return b2_launch((const void*)gemv_tc_reduce, dim3((M * R + 255) / 256), dim3(256), 0, s, ra);
     }
     return B2_OK;
@@ -672,7 +750,7 @@ static int glu_splits(int I, int C, int* kps) {
 extern "C" size_t btb_b200_gemv_tc_glu_workspace_bytes(int I, int C) {
     if (I <= 0 || C <= 0) return 0;
     const int s = glu_splits(I, C, nullptr);
-    return s > 1 ? (size_t)s * 32 * ((I + 63) / 64) * TC_BM * sizeof(float) : 0;
+    return s > 1 ? TC_WS_HEAD + (size_t)s * 32 * ((I + 63) / 64) * TC_BM * sizeof(float) : 0;  // (the head is the plain matvec's: a caller may share one workspace)
 }
 extern "C" int btb_b200_gemv_tc_glu_bf16(const void* w, const void* x, void* m, int M, int I, int C, void* workspace,
                                          void* stream) {
@@ -686,11 +764,12 @@ extern "C" int btb_b200_gemv_tc_glu_bf16(const void* w, const void* x, void* m, 
     if (make_map(&tw, w, (uint64_t)2 * I, (uint64_t)C, 64) || make_map(&tx, x, (uint64_t)M, (uint64_t)C, TC_BN)) return B2_ERR_CUDA;
     const int stages = b2_tuning().tc_stages > 0 ? min(TC_STAGES_MAX, b2_tuning().tc_stages) : 4;
     const int tiles = (I + 63) / 64;
-    TcArgs a{static_cast<bf16*>(m), static_cast<float*>(workspace), 2 * I, C, M, kps, splits, stages, I};
+    float* part = splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + TC_WS_HEAD) : nullptr;
+    TcArgs a{static_cast<bf16*>(m), part, 2 * I, C, M, kps, splits, stages, I, nullptr};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (const int rc = launch_tc<TC_BN, false>(tw, tx, a, dim3(tiles, splits), stages, s)) return rc;
     if (splits > 1) {
-        TcReduceArgs ra{static_cast<const float*>(workspace), static_cast<bf16*>(m), 2 * I, M, splits, I, tiles * TC_BM};
+        TcReduceArgs ra{part, static_cast<bf16*>(m), 2 * I, M, splits, I, tiles * TC_BM};
         return b2_launch((const void*)gemv_tc_reduce, dim3((M * I + 255) / 256), dim3(256), 0, s, ra);
     }
     return B2_OK;

@@ -47,9 +47,11 @@ int btb_b200_gemv_bf16(const void* w, const void* x, void* y, int M, int R, int 
 /* btb_gemv_mma_bf16 (native/cuda/btb_gemv_mma.cuh:123-315): the tensor-core matvec for passes of 1..32 rows - tcgen05.mma
  * with the accumulator in tensor memory, operand tiles by TMA tensor maps. One kernel for every pass width (x is read
  * as 32 rows, the rest zeros), so a row's bits do not depend on the width; its summation order is its own (as the
- * reference's is): it agrees with btb_b200_gemv_bf16 to rounding, not to the bit. workspace: f32,
- * btb_b200_gemv_tc_workspace_bytes(R, C) bytes (0 for matrices of many rows), 16-byte aligned, for the K ranges'
- * partial sums of matrices with few rows. */
+ * reference's is): it agrees with btb_b200_gemv_bf16 to rounding, not to the bit. workspace:
+ * btb_b200_gemv_tc_workspace_bytes(R, C) bytes (0 for matrices of many rows), 16-byte aligned, for matrices of few
+ * rows, which are cut over K: its first 1024 bytes are the tiles' arrival counters - ZERO before the first launch; a
+ * launch leaves them at zero - and the rest the K ranges' partial sums; the CTA that arrives last on a tile adds them
+ * in range order (the same sum every launch). One workspace serves every matrix of a stream. */
 int btb_b200_gemv_tc_bf16(const void* w, const void* x, void* y, int M, int R, int C, void* workspace, void* stream);
 /* btb_b200_gemv_tc_bf16 over pack12 weights read as stored (the parts of btb_b200_gemv_p12; `table` a HOST pointer to the
  * 16 high bytes): TMA brings a tile's stored parts, eight warps widen them in registers and write the bf16 operand tile

@@ -28,6 +28,7 @@ def _workspace(nbytes):
     if "t" not in _WS or _WS["t"].numel() < n:
         _WS["t"] = torch.empty(n, dtype=torch.float32, device=DEV)
     _WS["t"].fill_(float("nan"))
+    _WS["t"][:256] = 0  # (the head holds the tiles' counters: zero between launches)
     return _WS["t"]
 
 
@@ -262,10 +263,12 @@ def test_tc_matvec_over_pack12_equals_the_bf16_kernel_over_the_widened_matrix(R,
     wt, xt = bf(wb), bf(x)
     need = int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, Cc))
     ws = torch.full((max(need // 4, 4),), float("nan"), dtype=torch.float32, device="cuda")
+    ws[:256] = 0  # (the head holds the tiles' counters: zero between launches)
     ya = torch.zeros(M, R, dtype=torch.bfloat16, device="cuda")
     yb = torch.full((M, R), 3.0, dtype=torch.bfloat16, device="cuda")
     call("btb_b200_gemv_tc_bf16", ptr(wt), ptr(xt), ptr(ya), M, R, Cc, ptr(ws), capi.stream_ptr())
-    ws.fill_(float("nan"))
+    ws[256:].fill_(float("nan"))
+    assert int(ws[:256].view(torch.int32).abs().sum()) == 0  # the counters are back at zero after a launch
     call("btb_b200_gemv_tc_p12", ptr(P.lo), ptr(P.hi4), P.table, ptr(P.esc_idx), ptr(P.esc_val), ptr(P.esc_row), ptr(xt), ptr(yb),
          M, R, Cc, ptr(ws), capi.stream_ptr())  # fmt: skip
     torch.cuda.synchronize()
@@ -275,6 +278,50 @@ def test_tc_matvec_over_pack12_equals_the_bf16_kernel_over_the_widened_matrix(R,
     want = O.bits_to_f32(O.gemv_card_bf16(wb, x))
     got = yb.float().cpu().numpy()
     assert np.max(np.abs(got - want)) <= 2.0**-6 * max(1.0, float(np.max(np.abs(want))))
+
+
+@pytest.mark.parametrize("R,Cc", [(2560, 9728), (6144, 2560), (2560, 4096), (300, 2560)])
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_adding_the_k_ranges_in_the_launch_gives_the_second_launchs_bits(R, Cc, M):
+    """the `tc_fold` tunable: the CTA that arrives last on a tile's counter adds the ranges' partial sums in range order -
+    the bits of the ordered second launch, for the bf16 and the pack12 kernel, and the counters stand at zero again
+    afterwards (the same workspace serves the next launch as it is)"""
+    from btb_b200.engine import P12Matrix
+
+    from .test_gpu_kernels import _p12_case, bf, rand_bf
+
+    rng = np.random.default_rng(7 * R + Cc + M)
+    wb, parts = _p12_case(rng, R, Cc, False)
+    x = rand_bf(rng, (M, Cc))
+    P = P12Matrix(parts, R, Cc, "cuda")
+    wt, xt = bf(wb), bf(x)
+    need = int(capi.lib().btb_b200_gemv_tc_workspace_bytes(R, Cc))
+    assert need > 1024  # these shapes are cut over K
+    ws = torch.full((need // 4,), float("nan"), dtype=torch.float32, device="cuda")
+    ws[:256] = 0
+
+    def both(fold):
+        capi.set_tuning(tc_fold=fold)
+        try:
+            ya = torch.full((M, R), 3.0, dtype=torch.bfloat16, device="cuda")
+            yb = torch.full((M, R), 5.0, dtype=torch.bfloat16, device="cuda")
+            for _ in range(2):  # twice over the same workspace: the counters were left at zero
+                ws[256:].fill_(float("nan"))
+                call("btb_b200_gemv_tc_bf16", ptr(wt), ptr(xt), ptr(ya), M, R, Cc, ptr(ws), capi.stream_ptr())
+                call("btb_b200_gemv_tc_p12", ptr(P.lo), ptr(P.hi4), P.table, ptr(P.esc_idx), ptr(P.esc_val), ptr(P.esc_row),
+                     ptr(xt), ptr(yb), M, R, Cc, ptr(ws), capi.stream_ptr())  # fmt: skip
+            torch.cuda.synchronize()
+            assert capi.status() == 0
+            assert int(ws[:256].view(torch.int32).abs().sum()) == 0
+            return ya, yb
+        finally:
+            capi.set_tuning(tc_fold=0)
+
+    a0, b0 = both(0)
+    a1, b1 = both(1)
+    assert torch.equal(a0.view(torch.int16), a1.view(torch.int16))
+    assert torch.equal(b0.view(torch.int16), b1.view(torch.int16))
+    assert torch.equal(a1.view(torch.int16), b1.view(torch.int16))
 
 
 def test_tc_p12_refusals():
