@@ -947,6 +947,7 @@ def run_batch(args, mw, cfg, storage, cap, rank, world, dist) -> None:
     import torch
 
     from btb_b200 import capi
+    from btb_b200 import engine as E
     from btb_b200.batch import BatchEngine
 
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
@@ -954,6 +955,27 @@ def run_batch(args, mw, cfg, storage, cap, rank, world, dist) -> None:
     eng.wide_tc = bool(args.wide_tc)
     prompts = [torch.randint(0, cfg.vocab, (PROMPT,), generator=torch.Generator().manual_seed(100 + b)) for b in range(B)]
     eng.prefill_all(prompts)
+    # outside the timed region: the first step's logits of the pass as timed against the same step through the fp32-chain
+    # GEMVs (the two families sum in different orders: they agree to rounding, and a wrong partial sum does not)
+    check = None
+    if eng.wide_tc:
+        gB = eng.bufs(E.pad_rows(B))
+        keep_n, keep_ids = eng.n0b.clone(), gB["ids"].clone()
+
+        def first_step(tc: bool):
+            eng.wide_tc = tc
+            eng._batch_step(capi.stream_ptr())
+            torch.cuda.synchronize()
+            out = gB["logits"][:B].float().clone(), eng.pin_toks.clone()
+            eng.n0b.copy_(keep_n)
+            gB["ids"].copy_(keep_ids)
+            return out
+
+        (lc, tc_), (lt, tt) = first_step(False), first_step(True)
+        diff, top = float((lt - lc).abs().max()), float(lc.abs().max())
+        check = {"first_step_logits_max_abs_diff_vs_fp32_chain": diff, "max_abs_logit": top,
+                 "picks_equal": int((tc_ == tt).sum()), "of": B}
+        assert diff <= 0.1 * max(1.0, top), f"the tensor-core pass is off the fp32-chain pass: {check}"
     graph = eng.batch_graph()
     for _ in range(W):
         graph.replay()
@@ -995,6 +1017,7 @@ def run_batch(args, mw, cfg, storage, cap, rank, world, dist) -> None:
         "e2e": {"value": world * B * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8 * B},
         "gpu_launches": eng.launches_per_step * K, "roofline": None,
         "step_roofline_frac": (cfg.weight_bytes_per_token(storage) * K / (ms / 1000.0) / 1e9) / peak,
+        "check": check,
     }  # fmt: skip
     if rank == 0:
         print(json.dumps(line), flush=True)
