@@ -164,42 +164,58 @@ __global__ void __launch_bounds__(128, GEMM ? 1 : 2) gemv_tc(const __grid_consta
     pdl_launch_dependents();
     pdl_wait();  // x is the kernel's before this one
 
+    // (The two loops below are single threads: what a K block costs them is their instruction count times the issue
+    // latency of a lone thread, so nothing is recomputed a block - the stage and its phase are running counters, not a
+    // division by the ring's depth, and addresses, coordinates and descriptors advance by additions.)
     if (warp == 0 && lane == 0) {
         // the producer: the weights' tile and x's tile of every K block of this CTA's range
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
-            if (kb >= TC_STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
+        const uint32_t tiles0 = smem_u32(tiles), full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
+        int s = 0, wrapped = 0;
+        uint32_t ph = 0;
+        int xk = kb0 * TC_BK;  // the K block's first column
+        for (int kb = 0; kb < nkb; ++kb, xk += TC_BK) {
+            if (wrapped && !mbar_wait_bounded(empty0 + s * 8, ph ^ 1)) {
                 *(volatile int*)&s_fail = 1;
                 break;
             }
-            const uint32_t bar = smem_u32(&full[s]);
+            const uint32_t bar = full0 + s * 8, at = tiles0 + s * ST_BYTES;
             mbar_expect_tx(bar, ST_BYTES);
             if (glu) {  // two boxes of 64 rows: the gate rows into the tile's upper half, their up rows into its lower half
-                tma_load_2d(smem_u32(tiles + s * ST_BYTES), &tmW, (kb0 + kb) * TC_BK, row0, bar);
-                tma_load_2d(smem_u32(tiles + s * ST_BYTES + A_BYTES / 2), &tmW, (kb0 + kb) * TC_BK, A.glu_I + row0, bar);
-            } else
-            tma_load_2d(smem_u32(tiles + s * ST_BYTES), &tmW, (kb0 + kb) * TC_BK, row0, bar);
-            tma_load_2d(smem_u32(tiles + s * ST_BYTES + A_BYTES), &tmX, (kb0 + kb) * TC_BK, n0, bar);
+                tma_load_2d(at, &tmW, xk, row0, bar);
+                tma_load_2d(at + A_BYTES / 2, &tmW, xk, A.glu_I + row0, bar);
+            } else {
+                tma_load_2d(at, &tmW, xk, row0, bar);
+            }
+            tma_load_2d(at + A_BYTES, &tmX, xk, n0, bar);
+            if (++s == TC_STAGES) s = 0, ph ^= 1, wrapped = 1;
         }
     } else if (warp == 1 && lane == 0) {
         // the issuer: four K = 16 instructions a stage; D f32, A and B bf16, both K-major, N = 32, M = 128
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        // a stage's descriptors are the first stage's plus the stage's offset in the address field (16-byte units; the
+        // ring lies below 256 KB, so the field never carries), a K = 16 step 32 bytes further
+        const uint64_t da0 = umma_desc_sw128(smem_u32(tiles)), db0 = umma_desc_sw128(smem_u32(tiles) + A_BYTES);
+        const uint32_t full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
+        int s = 0;
+        uint32_t ph = 0;
+        int rs = 0, first = 0;  // the GEMM's K block kb belongs to range kb / kps: its own accumulator, started afresh at the range's first block
         for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
-            if (!mbar_wait_bounded(smem_u32(&full[s]), ph)) {
+            if (!mbar_wait_bounded(full0 + s * 8, ph)) {
                 *(volatile int*)&s_fail = 1;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a0 = smem_u32(tiles + s * ST_BYTES), b0 = a0 + A_BYTES;
-            // the GEMM's K block kb belongs to range kb / kps: its own accumulator, started afresh at the range's first block
-            const int rs = GEMM ? kb / A.kblocks_per_split : 0;
-            const int first = GEMM ? kb - rs * A.kblocks_per_split : kb;
+            const uint64_t da = da0 + (uint64_t)(s * (ST_BYTES >> 4)), db = db0 + (uint64_t)(s * (ST_BYTES >> 4));
 #pragma unroll
             for (int k = 0; k < TC_BK / 16; ++k)
-                umma_bf16(tmem + (uint32_t)(rs * BN), umma_desc_sw128(a0 + k * 32), umma_desc_sw128(b0 + k * 32), idesc,
-                          (first | k) != 0);
-            umma_commit(smem_u32(&empty[s]));  // the stage is free once these have read it
+                umma_bf16(tmem + (uint32_t)(rs * BN), da + 2 * k, db + 2 * k, idesc, (first | k) != 0);
+            umma_commit(empty0 + s * 8);  // the stage is free once these have read it
+            if (++s == TC_STAGES) s = 0, ph ^= 1;
+            if (GEMM) {
+                if (++first == A.kblocks_per_split) first = 0, ++rs;
+            } else {
+                first = 1;
+            }
         }
         umma_commit(smem_u32(&done));
     }
@@ -352,35 +368,42 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
     pdl_launch_dependents();
     pdl_wait();
 
+    // (single-thread loops: running counters and additions, as in gemv_tc)
     if (warp == 0 && lane == 0) {
         // the producer: the stored parts of the weights' tile and x's tile
-        for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
-            if (kb >= TC_STAGES && !mbar_wait_bounded(smem_u32(&empty[s]), ph ^ 1)) {
+        const uint32_t tiles0 = smem_u32(tiles), full0 = smem_u32(&full_p[0]), empty0 = smem_u32(&empty[0]);
+        int s = 0, wrapped = 0;
+        uint32_t ph = 0;
+        int xk = kb0 * TC_BK;
+        for (int kb = 0; kb < nkb; ++kb, xk += TC_BK) {
+            if (wrapped && !mbar_wait_bounded(empty0 + s * 8, ph ^ 1)) {
                 *(volatile int*)&s_fail = 1;
                 break;
             }
-            const uint32_t bar = smem_u32(&full_p[s]);
-            uint8_t* st = tiles + (size_t)s * P12_ST;
+            const uint32_t bar = full0 + s * 8, at = tiles0 + s * P12_ST;
             mbar_expect_tx(bar, P12_B + P12_LO + P12_HI);
-            tma_load_2d(smem_u32(st + A_BYTES + P12_B), &tmLo, (kb0 + kb) * TC_BK, row0, bar);
-            tma_load_2d(smem_u32(st + A_BYTES + P12_B + P12_LO), &tmHi, (kb0 + kb) * (TC_BK / 2), row0, bar);
-            tma_load_2d(smem_u32(st + A_BYTES), &tmX, (kb0 + kb) * TC_BK, 0, bar);
+            tma_load_2d(at + A_BYTES + P12_B, &tmLo, xk, row0, bar);
+            tma_load_2d(at + A_BYTES + P12_B + P12_LO, &tmHi, xk >> 1, row0, bar);
+            tma_load_2d(at + A_BYTES, &tmX, xk, 0, bar);
+            if (++s == TC_STAGES) s = 0, ph ^= 1, wrapped = 1;
         }
     } else if (warp == 1 && lane == 0) {
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        const uint64_t da0 = umma_desc_sw128(smem_u32(tiles)), db0 = umma_desc_sw128(smem_u32(tiles) + A_BYTES);
+        const uint32_t full0 = smem_u32(&full_a[0]), empty0 = smem_u32(&empty[0]);
+        int s = 0;
+        uint32_t ph = 0;
         for (int kb = 0; kb < nkb; ++kb) {
-            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
-            if (!mbar_wait_bounded(smem_u32(&full_a[s]), ph)) {  // every row of the tile widened (and x landed before that)
+            if (!mbar_wait_bounded(full0 + s * 8, ph)) {  // every row of the tile widened (and x landed before that)
                 *(volatile int*)&s_fail = 1;
                 break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a0 = smem_u32(tiles + (size_t)s * P12_ST), b0 = a0 + A_BYTES;
+            const uint64_t da = da0 + (uint64_t)(s * (P12_ST >> 4)), db = db0 + (uint64_t)(s * (P12_ST >> 4));
 #pragma unroll
-            for (int k = 0; k < TC_BK / 16; ++k)
-                umma_bf16(tmem, umma_desc_sw128(a0 + k * 32), umma_desc_sw128(b0 + k * 32), idesc, (kb | k) != 0);
-            umma_commit(smem_u32(&empty[s]));
+            for (int k = 0; k < TC_BK / 16; ++k) umma_bf16(tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+            umma_commit(empty0 + s * 8);
+            if (++s == TC_STAGES) s = 0, ph ^= 1;
         }
         umma_commit(smem_u32(&done));
     } else if (warp >= 4) {
@@ -411,9 +434,12 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
             cur = a;
             if (cur < end) peek = __ldg(P.esc_idx + cur);
         }
-        for (int kb = grp; kb < nkb; kb += NG) {
-            const int s = kb % TC_STAGES, ph = (kb / TC_STAGES) & 1;
-            bool bad = !mbar_wait_bounded(smem_u32(&full_p[s]), ph);
+        const uint32_t fullp0 = smem_u32(&full_p[0]), fulla0 = smem_u32(&full_a[0]);
+        int s = grp;  // (NG <= the ring's depth: the host keeps at least two stages)
+        uint32_t ph = 0;
+        int base = own >= 0 ? (int)((size_t)(row0 + own) * A.C + (size_t)(kb0 + grp) * TC_BK) : 0;  // the owned row's first element of the K block
+        for (int kb = grp; kb < nkb; kb += NG, base += NG * TC_BK) {
+            bool bad = !mbar_wait_bounded(fullp0 + s * 8, ph);
             if (bad) *(volatile int*)&s_fail = 1;
             bad = __any_sync(0xffffffffu, bad || *(volatile int*)&s_fail != 0);  // (one answer a warp: it syncs below)
             uint8_t* st = tiles + (size_t)s * P12_ST;
@@ -430,7 +456,6 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
                 __syncwarp();  // a row's eight writers are lanes of one warp, its owner among them
                 if (own >= 0) {
                     // (prefetching a window of the row's next entries every stage was measured slower: most rows have none)
-                    const int base = (int)((size_t)(row0 + own) * A.C + (size_t)(kb0 + kb) * TC_BK);
                     while (peek < base + TC_BK) {  // the row's entries up to the end of this K block
                         const int col = peek - base;
                         if (col >= 0) st[own * 128 + (((col >> 3) ^ (own & 7)) << 4) + (col & 7) * 2 + 1] = __ldg(P.esc_val + cur);
@@ -448,7 +473,9 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
                                 : grp == 2 ? p12_group_bar<3, GT>(bad)
                                            : p12_group_bar<4, GT>(bad);
             if (any_bad) break;
-            if (tg == 0) mbar_arrive(smem_u32(&full_a[s]));
+            if (tg == 0) mbar_arrive(fulla0 + s * 8);
+            s += NG;
+            if (s >= TC_STAGES) s -= TC_STAGES, ph ^= 1;
         }
     }
     __syncwarp();
