@@ -434,31 +434,37 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
             cur = a;
             if (cur < end) peek = __ldg(P.esc_idx + cur);
         }
-        const uint32_t fullp0 = smem_u32(&full_p[0]), fulla0 = smem_u32(&full_a[0]);
+        const uint32_t fullp0 = smem_u32(&full_p[0]), fulla0 = smem_u32(&full_a[0]), tiles0 = smem_u32(tiles);
         int s = grp;  // (NG <= the ring's depth: the host keeps at least two stages)
         uint32_t ph = 0;
         int base = own >= 0 ? (int)((size_t)(row0 + own) * A.C + (size_t)(kb0 + grp) * TC_BK) : 0;  // the owned row's first element of the K block
         for (int kb = grp; kb < nkb; kb += NG, base += NG * TC_BK) {
             bool bad = !mbar_wait_bounded(fullp0 + s * 8, ph);
             if (bad) *(volatile int*)&s_fail = 1;
-            bad = __any_sync(0xffffffffu, bad || *(volatile int*)&s_fail != 0);  // (one answer a warp: it syncs below)
-            uint8_t* st = tiles + (size_t)s * P12_ST;
+            bad = __any_sync(0xffffffffu, bad);  // (one answer a warp: it syncs below; another agent's failure shows as this wait's own)
+            const uint32_t st = tiles0 + (uint32_t)s * P12_ST;  // (shared-space addresses: 32-bit arithmetic, no generic loads)
             if (!bad) {
 #pragma unroll
                 for (int i = 0; i < RPT; ++i) {
                     const int d = (tg >> 3) + RG * i;
-                    const uint2 l = *reinterpret_cast<const uint2*>(st + A_BYTES + P12_B + d * TC_BK + c * 8);
-                    const uint32_t codes = *reinterpret_cast<const uint32_t*>(st + A_BYTES + P12_B + P12_LO + d * (TC_BK / 2) + c * 4);
+                    uint32_t l0, l1, codes;
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(l0), "=r"(l1) : "r"(st + A_BYTES + P12_B + d * TC_BK + c * 8) : "memory");
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(codes) : "r"(st + A_BYTES + P12_B + P12_LO + d * (TC_BK / 2) + c * 4) : "memory");
                     uint32_t wp[4];
-                    p12_chunk(l.x, l.y, codes, P.table, wp);
-                    *reinterpret_cast<uint4*>(st + d * 128 + ((c ^ (d & 7)) << 4)) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+                    p12_chunk(l0, l1, codes, P.table, wp);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(st + d * 128 + ((c ^ (d & 7)) << 4)), "r"(wp[0]),
+                                 "r"(wp[1]), "r"(wp[2]), "r"(wp[3])
+                                 : "memory");
                 }
                 __syncwarp();  // a row's eight writers are lanes of one warp, its owner among them
                 if (own >= 0) {
                     // (prefetching a window of the row's next entries every stage was measured slower: most rows have none)
                     while (peek < base + TC_BK) {  // the row's entries up to the end of this K block
                         const int col = peek - base;
-                        if (col >= 0) st[own * 128 + (((col >> 3) ^ (own & 7)) << 4) + (col & 7) * 2 + 1] = __ldg(P.esc_val + cur);
+                        if (col >= 0)
+                            asm volatile("st.shared.u8 [%0], %1;" ::"r"(st + own * 128 + (((col >> 3) ^ (own & 7)) << 4) + (col & 7) * 2 + 1),
+                                         "r"((uint32_t)__ldg(P.esc_val + cur))
+                                         : "memory");
                         ++cur;
                         peek = cur < end ? __ldg(P.esc_idx + cur) : 0x7fffffff;
                     }
