@@ -62,14 +62,16 @@ __device__ __forceinline__ uint32_t fp8x2_held_pair(uint32_t two, float scale) {
 // chooses between them by the code's top bit. Returns pairs p[k] = (elem 2k low half, elem 2k+1 high half).
 __device__ __forceinline__ void p12_chunk(uint32_t lo0, uint32_t lo1, uint32_t codes, const uint32_t (&t)[4],
                                           uint32_t (&p)[4]) {
+    // both halves' selectors at once (a byte permute reads only the low 16 bits of its selector: the second half's are
+    // a shift away): the codes' low three bits pick within a table half, their top bits pick the half
+    const uint32_t s7 = codes & 0x77777777u;
+    const uint32_t pick = 0x32103210u | ((codes >> 1) & 0x44444444u);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        const uint32_t sel = (codes >> (16 * h)) & 0xffffu;  // four codes
-        const uint32_t s7 = sel & 0x7777u;
-        const uint32_t a = __byte_perm(t[0], t[1], s7);
-        const uint32_t b = __byte_perm(t[2], t[3], s7);
-        const uint32_t pick = 0x3210u | ((sel & 0x8888u) >> 1);
-        const uint32_t hi = __byte_perm(a, b, pick);  // the four high bytes
+        const uint32_t sel = h ? s7 >> 16 : s7, pk = h ? pick >> 16 : pick;
+        const uint32_t a = __byte_perm(t[0], t[1], sel);
+        const uint32_t b = __byte_perm(t[2], t[3], sel);
+        const uint32_t hi = __byte_perm(a, b, pk);  // the four high bytes
         const uint32_t lo = h ? lo1 : lo0;
         p[2 * h] = __byte_perm(lo, hi, 0x5140u);      // lo0 hi0 lo1 hi1
         p[2 * h + 1] = __byte_perm(lo, hi, 0x7362u);  // lo2 hi2 lo3 hi3

@@ -19,6 +19,7 @@
 
 #include <mutex>
 #include <unordered_map>
+#include <utility>
 
 #include "btb_b200_internal.h"
 #include "gemv_core.cuh"
@@ -319,6 +320,25 @@ struct TcP12Args {
     const int32_t* esc_row;  // [R + 1] or null: no escapes anywhere
 };
 
+// one 16-byte piece of the operand tile from its stored parts, row I * RG on from the thread's first: the offsets are
+// immediates of the shared-space loads and the store (one address each a stage, not one a row)
+template <int I, int RG>
+__device__ __forceinline__ void p12_widen_row(uint32_t a_lo, uint32_t a_hi, uint32_t a_out, const uint32_t (&table)[4]) {
+    uint32_t l0, l1, codes;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(l0), "=r"(l1) : "r"(a_lo), "n"(I * RG * TC_BK) : "memory");
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(codes) : "r"(a_hi), "n"(I * RG * (TC_BK / 2)) : "memory");
+    uint32_t wp[4];
+    p12_chunk(l0, l1, codes, table, wp);
+    asm volatile("st.shared.v4.u32 [%0+%1], {%2, %3, %4, %5};" ::"r"(a_out), "n"(I * RG * 128), "r"(wp[0]), "r"(wp[1]), "r"(wp[2]),
+                 "r"(wp[3])
+                 : "memory");
+}
+template <int RG, int... Is>
+__device__ __forceinline__ void p12_widen_rows(uint32_t a_lo, uint32_t a_hi, uint32_t a_out, const uint32_t (&table)[4],
+                                               std::integer_sequence<int, Is...>) {
+    (p12_widen_row<Is, RG>(a_lo, a_hi, a_out, table), ...);
+}
+
 // one group's named barrier (ids 1 ..): true if any of its `GT` threads came with `bad`
 template <int ID, int GT>
 __device__ __forceinline__ int p12_group_bar(bool bad) {
@@ -435,6 +455,9 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
             if (cur < end) peek = __ldg(P.esc_idx + cur);
         }
         const uint32_t fullp0 = smem_u32(&full_p[0]), fulla0 = smem_u32(&full_a[0]), tiles0 = smem_u32(tiles);
+        static_assert(RG % 8 == 0, "a thread's rows share their swizzle");
+        const uint32_t off_lo = (uint32_t)((tg >> 3) * TC_BK + c * 8), off_hi = (uint32_t)((tg >> 3) * (TC_BK / 2) + c * 4);
+        const uint32_t off_out = (uint32_t)((tg >> 3) * 128 + ((c ^ ((tg >> 3) & 7)) << 4));
         int s = grp;  // (NG <= the ring's depth: the host keeps at least two stages)
         uint32_t ph = 0;
         int base = own >= 0 ? (int)((size_t)(row0 + own) * A.C + (size_t)(kb0 + grp) * TC_BK) : 0;  // the owned row's first element of the K block
@@ -444,18 +467,9 @@ __global__ void __launch_bounds__(128 + 32 * NW, 2) gemv_tc_p12(const __grid_con
             bad = __any_sync(0xffffffffu, bad);  // (one answer a warp: it syncs below; another agent's failure shows as this wait's own)
             const uint32_t st = tiles0 + (uint32_t)s * P12_ST;  // (shared-space addresses: 32-bit arithmetic, no generic loads)
             if (!bad) {
-#pragma unroll
-                for (int i = 0; i < RPT; ++i) {
-                    const int d = (tg >> 3) + RG * i;
-                    uint32_t l0, l1, codes;
-                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(l0), "=r"(l1) : "r"(st + A_BYTES + P12_B + d * TC_BK + c * 8) : "memory");
-                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(codes) : "r"(st + A_BYTES + P12_B + P12_LO + d * (TC_BK / 2) + c * 4) : "memory");
-                    uint32_t wp[4];
-                    p12_chunk(l0, l1, codes, P.table, wp);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(st + d * 128 + ((c ^ (d & 7)) << 4)), "r"(wp[0]),
-                                 "r"(wp[1]), "r"(wp[2]), "r"(wp[3])
-                                 : "memory");
-                }
+                // (RG is a multiple of 8: a thread's rows all have its first row's swizzle; row i lies a constant on)
+                const uint32_t a_lo = st + A_BYTES + P12_B + off_lo, a_hi = st + A_BYTES + P12_B + P12_LO + off_hi, a_out = st + off_out;
+                p12_widen_rows<RG>(a_lo, a_hi, a_out, P.table, std::make_integer_sequence<int, RPT>{});
                 __syncwarp();  // a row's eight writers are lanes of one warp, its owner among them
                 if (own >= 0) {
                     // (prefetching a window of the row's next entries every stage was measured slower: most rows have none)
